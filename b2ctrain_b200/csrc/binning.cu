@@ -1,0 +1,364 @@
+// Binning stage: depth-keyed radix sort of the splats, scan of tile counts in depth order fused with the emission of
+// (tile id, splat index) pairs, stable radix sort by tile id, per-tile ranges. Reference semantics: bin_and_sort
+// (src/gpu/binning.cu:109-145) with its kernels (:10-105); the two library sorts and the library scan of the
+// reference are replaced by the kernels in this file.
+//
+// Everything here is integer work bound by HBM traffic. Design points:
+//  * No host round trip: the element counts of the later stages (intersections) are read from device memory by
+//    persistent kernels whose grids are sized from the SM count, so the whole view is one asynchronous chain.
+//  * The radix sort is the wait-free three-kernel form (per-block digit counts, row scan, ranked scatter): no kernel
+//    ever spins on another block. Each block owns one contiguous segment and walks it tile by tile, so the count
+//    table is 256 x (a few hundred) words whatever the input size.
+//  * Scatter is staged through shared memory so global writes go out in digit runs (coalesced), keys and values
+//    move as 32-bit words, loads are warp-contiguous.
+//  * Sorting is LSD with 8-bit digits and is stable, so order = ascending (key, original position): exactly the
+//    order the reference's stable sorts define.
+#include "common.cuh"
+
+namespace b2k {
+namespace {
+
+constexpr int SORT_THREADS = 256;
+constexpr int SORT_ITEMS = 16;
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;   // 4096 pairs per tile
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+constexpr int RADIX = 256;
+constexpr int BLOCKS_PER_SM = 4;
+
+__device__ __forceinline__ uint32_t seg_len(uint32_t n, uint32_t blocks) {
+  uint32_t per = (n + blocks - 1) / blocks;
+  return ((per + SORT_TILE - 1) / SORT_TILE) * SORT_TILE;
+}
+__device__ __forceinline__ uint32_t load_n(const uint32_t* n_ptr, uint32_t n_max) {
+  const uint32_t n = *n_ptr;
+  return n < n_max ? n : n_max;
+}
+
+// Pass kernel 1: digit counts of each block's segment. hist is [RADIX][blocks].
+__global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ n_ptr, uint32_t n_max,
+                                                                   int shift, uint32_t mask, uint32_t* __restrict__ hist) {
+  __shared__ uint32_t s_hist[SORT_WARPS][RADIX];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_hist[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t n = load_n(n_ptr, n_max);
+  const uint32_t len = seg_len(n, gridDim.x);
+  const uint64_t begin64 = (uint64_t)blockIdx.x * len;
+  const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
+  const uint32_t end = (begin64 + len) < n ? (uint32_t)(begin64 + len) : n;
+  for (uint32_t base = begin + warp * 32; base < end; base += SORT_THREADS) {   // warp-uniform trip count
+    const uint32_t i = base + lane;
+    const bool valid = i < end;
+    const uint32_t d = valid ? ((keys[i] >> shift) & mask) : (0x10000u | lane);
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    if (valid && lane == __ffs(peers) - 1) s_hist[warp][d] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < RADIX; d += SORT_THREADS) {
+    uint32_t t = 0;
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; w++) t += s_hist[w][d];
+    hist[(size_t)d * gridDim.x + blockIdx.x] = t;
+  }
+}
+
+// Pass kernel 2: one block per digit turns its row of per-block counts into exclusive offsets and records the row
+// total. blocks <= 1024.
+__global__ void __launch_bounds__(1024) radix_rows_kernel(uint32_t* __restrict__ hist, int blocks, uint32_t* __restrict__ totals) {
+  __shared__ uint32_t s_warp[32];
+  const int d = blockIdx.x, t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  uint32_t v = t < blocks ? hist[(size_t)d * blocks + t] : 0u;
+  uint32_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = s_warp[lane], wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += u; }
+    s_warp[lane] = wi - w;
+    if (lane == 31) totals[d] = wi;
+  }
+  __syncthreads();
+  if (t < blocks) hist[(size_t)d * blocks + t] = s_warp[warp] + incl - v;
+}
+
+// Pass kernel 3: ranked, stable scatter of each block's segment.
+__global__ void __launch_bounds__(SORT_THREADS) radix_scatter_kernel(
+    const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
+    const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask, const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals) {
+  __shared__ uint32_t s_cnt[SORT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
+  __shared__ uint32_t s_start[RADIX];             // first local slot of the digit inside the tile
+  __shared__ uint32_t s_gbase[RADIX];             // running global slot of the digit for this block
+  __shared__ uint32_t s_delta[RADIX];             // global slot = s_delta[digit] + local slot (mod 2^32)
+  __shared__ uint32_t s_scan[SORT_WARPS];
+  __shared__ uint32_t s_keys[SORT_TILE];
+  __shared__ uint32_t s_vals[SORT_TILE];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t lane_lt = (1u << lane) - 1u;
+  // Global base of (digit, block): exclusive scan of the digit totals + the block's offset inside the digit.
+  {
+    const uint32_t tot = totals[tid];
+    uint32_t incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    if (lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    uint32_t pre = 0;
+    for (int w = 0; w < warp; w++) pre += s_scan[w];
+    s_gbase[tid] = pre + incl - tot + hist[(size_t)tid * gridDim.x + blockIdx.x];
+    __syncthreads();
+  }
+  const uint32_t n = load_n(n_ptr, n_max);
+  const uint32_t len = seg_len(n, gridDim.x);
+  const uint64_t begin64 = (uint64_t)blockIdx.x * len;
+  const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
+  const uint32_t end = (begin64 + len) < n ? (uint32_t)(begin64 + len) : n;
+  for (uint32_t tile = begin; tile < end; tile += SORT_TILE) {
+    const uint32_t tile_n = end - tile < SORT_TILE ? end - tile : SORT_TILE;
+    for (int i = tid; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_cnt[0][0])[i] = 0;
+    __syncthreads();
+    // Each warp owns 512 consecutive pairs; item j of lane l is pair j*32 + l of them, so (j, lane) order is input order.
+    uint32_t key[SORT_ITEMS], rank[SORT_ITEMS];
+    const uint32_t wbase = warp * (32 * SORT_ITEMS);
+#pragma unroll
+    for (int j = 0; j < SORT_ITEMS; j++) {
+      const uint32_t li = wbase + j * 32 + lane;
+      const bool valid = li < tile_n;
+      key[j] = valid ? keys_in[tile + li] : 0xFFFFFFFFu;
+      const uint32_t d = valid ? ((key[j] >> shift) & mask) : (0x10000u | lane);
+      const uint32_t peers = __match_any_sync(0xffffffffu, d);
+      uint32_t before = 0;
+      if (valid) before = s_cnt[warp][d];
+      __syncwarp();
+      if (valid && lane == __ffs(peers) - 1) s_cnt[warp][d] = before + __popc(peers);
+      __syncwarp();
+      rank[j] = before + __popc(peers & lane_lt);
+    }
+    __syncthreads();
+    // Digit `tid`: offsets of the warps inside the digit, digit total, then the digit's first slot in the tile.
+    uint32_t total = 0;
+#pragma unroll
+    for (int w = 0; w < SORT_WARPS; w++) { const uint32_t c = s_cnt[w][tid]; s_cnt[w][tid] = total; total += c; }
+    uint32_t incl = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    if (lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    uint32_t pre = 0;
+    for (int w = 0; w < warp; w++) pre += s_scan[w];
+    const uint32_t start = pre + incl - total;
+    s_start[tid] = start;
+    s_delta[tid] = s_gbase[tid] - start;
+    s_gbase[tid] += total;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < SORT_ITEMS; j++) {
+      const uint32_t li = wbase + j * 32 + lane;
+      if (li < tile_n) {
+        const uint32_t d = (key[j] >> shift) & mask;
+        const uint32_t slot = s_start[d] + s_cnt[warp][d] + rank[j];
+        s_keys[slot] = key[j];
+        s_vals[slot] = vals_in[tile + li];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < SORT_ITEMS; j++) {
+      const uint32_t slot = j * SORT_THREADS + tid;
+      if (slot < tile_n) {
+        const uint32_t k = s_keys[slot];
+        const uint32_t dst = s_delta[(k >> shift) & mask] + slot;
+        keys_out[dst] = k;
+        vals_out[dst] = s_vals[slot];
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---- scan of tile counts in depth order, fused with the emission of intersections ----
+
+constexpr int EMIT_THREADS = 256;
+
+__device__ __forceinline__ uint32_t emit_seg_len(uint32_t n, uint32_t blocks) {
+  uint32_t per = (n + blocks - 1) / blocks;
+  return ((per + EMIT_THREADS - 1) / EMIT_THREADS) * EMIT_THREADS;
+}
+
+__global__ void __launch_bounds__(EMIT_THREADS) count_sums_kernel(int n, const uint32_t* __restrict__ order, const uint32_t* __restrict__ tile_count,
+                                                                  uint32_t* __restrict__ block_sums) {
+  __shared__ uint32_t s_red[EMIT_THREADS / 32];
+  const uint32_t len = emit_seg_len((uint32_t)n, gridDim.x);
+  const uint64_t begin = (uint64_t)blockIdx.x * len;
+  uint32_t acc = 0;
+  for (uint64_t r = begin + threadIdx.x; r < begin + len && r < (uint64_t)n; r += EMIT_THREADS) acc += tile_count[order[r]];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) { uint32_t t = 0; for (int w = 0; w < EMIT_THREADS / 32; w++) t += s_red[w]; block_sums[blockIdx.x] = t; }
+}
+
+// Thread r takes the r-th nearest splat: its slot range follows from the scan, its tiles from the same decision
+// functions the projection counted with, visited in row-major order.
+__global__ void __launch_bounds__(EMIT_THREADS) scan_emit_kernel(
+    int n, const uint32_t* __restrict__ order, const uint32_t* __restrict__ tile_count, const uint32_t* __restrict__ block_sums,
+    const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H, int tiles_x, int tiles_y, uint32_t cap,
+    uint32_t* __restrict__ tile_off, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals, uint32_t* __restrict__ num_isect) {
+  __shared__ uint32_t s_warp[EMIT_THREADS / 32];
+  __shared__ uint32_t s_base;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  {
+    uint32_t acc = 0;
+    for (int b = tid; b < (int)blockIdx.x; b += EMIT_THREADS) acc += block_sums[b];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_warp[warp] = acc;
+    __syncthreads();
+    if (tid == 0) { uint32_t t = 0; for (int w = 0; w < EMIT_THREADS / 32; w++) t += s_warp[w]; s_base = t; }
+    __syncthreads();
+  }
+  uint32_t running = s_base;
+  const uint32_t len = emit_seg_len((uint32_t)n, gridDim.x);
+  const uint64_t begin = (uint64_t)blockIdx.x * len;
+  for (uint64_t r0 = begin; r0 < begin + len && r0 < (uint64_t)n; r0 += EMIT_THREADS) {
+    const uint64_t r = r0 + tid;
+    const bool valid = r < (uint64_t)n;
+    const uint32_t i = valid ? order[r] : 0u;
+    const uint32_t cnt = valid ? tile_count[i] : 0u;
+    uint32_t incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    __syncthreads();   // s_warp reuse
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t pre = 0, tile_total = 0;
+#pragma unroll
+    for (int w = 0; w < EMIT_THREADS / 32; w++) { const uint32_t v = s_warp[w]; if (w < warp) pre += v; tile_total += v; }
+    const uint32_t end = running + pre + incl;
+    if (valid) tile_off[r] = end;
+    if (cnt) {
+      uint32_t at = end - cnt;
+      const float4 a = proj0[i], b = proj1[i];
+      const TileRec rec{a.x, a.y, a.z, a.w, b.x, b.w};
+      TileBox bb;
+      if (tile_box(rec, W, H, tiles_x, tiles_y, bb)) {
+        for (int ty = bb.min_y; ty < bb.max_y; ty++)
+          for (int tx = bb.min_x; tx < bb.max_x; tx++)
+            if (tile_hit(tx, ty, rec)) {
+              if (at < cap) { keys[at] = (uint32_t)(ty * tiles_x + tx); vals[at] = i; }
+              at++;
+            }
+      }
+    }
+    running += tile_total;
+  }
+  if (blockIdx.x == gridDim.x - 1 && tid == 0) *num_isect = running;
+}
+
+__global__ void tile_ranges_kernel(const uint32_t* __restrict__ keys_sorted, const uint32_t* __restrict__ n_ptr, uint32_t n_max, uint32_t n_tiles,
+                                   uint2* __restrict__ ranges) {
+  const uint32_t n = load_n(n_ptr, n_max);
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t tile = keys_sorted[i];
+    const uint32_t prev = i == 0 ? 0xFFFFFFFFu : keys_sorted[i - 1];
+    if (i == 0 || tile != prev) {
+      if (tile < n_tiles) ranges[tile].x = i;
+      if (i > 0 && prev < n_tiles) ranges[prev].y = i;
+    }
+    if (i == n - 1 && tile < n_tiles) ranges[tile].y = n;
+  }
+}
+
+__global__ void set_word_kernel(uint32_t* p, uint32_t v) { *p = v; }
+
+struct SortScratch { uint32_t* hist; uint32_t* totals; uint32_t* block_sums; uint32_t* n_word; };
+
+int sort_blocks() { int b = sm_count() * BLOCKS_PER_SM; return b > 1024 ? 1024 : b; }
+
+SortScratch carve(void* tmp, int blocks) {
+  SortScratch s;
+  s.hist = (uint32_t*)tmp;
+  s.totals = s.hist + (size_t)RADIX * blocks;
+  s.block_sums = s.totals + RADIX;
+  s.n_word = s.block_sums + blocks;
+  return s;
+}
+
+// LSD radix sort of (key, value) pairs over bits [0, bits). The element count is read from *n_ptr on the device and
+// clamped to n_max. Buffers (k0, v0) hold the input; the result lands in (k0, v0) when the number of passes is even
+// and in (k1, v1) when it is odd.
+int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uint32_t* n_ptr, uint32_t n_max, int bits, const SortScratch& sc,
+               int blocks, cudaStream_t s) {
+  const int passes = (bits + 7) / 8;
+  for (int p = 0; p < passes; p++) {
+    const int shift = p * 8;
+    const int pb = bits - shift < 8 ? bits - shift : 8;
+    const uint32_t mask = (1u << pb) - 1u;
+    radix_count_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist);
+    radix_rows_kernel<<<RADIX, 1024, 0, s>>>(sc.hist, blocks, sc.totals);
+    radix_scatter_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals);
+    uint32_t* t = k0; k0 = k1; k1 = t;
+    t = v0; v0 = v1; v1 = t;
+  }
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace b2k
+
+using namespace b2k;
+
+extern "C" uint64_t b2k_sort_tmp_bytes(int32_t n, uint64_t isect_cap) {
+  (void)n; (void)isect_cap;
+  const int blocks = 1024;   // upper bound of sort_blocks()
+  return (uint64_t)sizeof(uint32_t) * ((uint64_t)RADIX * blocks + RADIX + blocks + 16);
+}
+
+extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
+  B2K_REQUIRE(c && n >= 0);
+  B2K_REQUIRE(c->tile_ranges && c->num_isect && c->n_tiles == c->tiles_x * c->tiles_y && c->tile_bits >= 1 && c->tile_bits <= 24);
+  cudaStream_t s = (cudaStream_t)stream;
+  B2K_CUDA(cudaMemsetAsync(c->tile_ranges, 0, sizeof(uint32_t) * 2 * (size_t)c->n_tiles, s));
+  if (n == 0) { B2K_CUDA(cudaMemsetAsync(c->num_isect, 0, sizeof(uint32_t), s)); return B2K_OK; }
+  B2K_REQUIRE(c->proj0 && c->proj1 && c->tile_count && c->depth_keys && c->depth_keys_sorted && c->order_in && c->order && c->tile_off);
+  B2K_REQUIRE(c->keys && c->vals && c->keys_sorted && c->vals_sorted && c->sort_tmp);
+  if (c->n_cap < n) return B2K_ERR_CAPACITY;
+  if (c->sort_tmp_bytes < b2k_sort_tmp_bytes(n, c->isect_cap) || c->isect_cap == 0 || c->isect_cap > 0xFFFFFFF0ull) return B2K_ERR_CAPACITY;
+  const int blocks = sort_blocks();
+  const SortScratch sc = carve(c->sort_tmp, blocks);
+  // 1. Splats by depth: key = bits of view z (culled splats carry 0xFFFFFFFF and land last), value = index. The
+  //    projection left its keys and indices in the (depth_keys_sorted, order) pair: with four passes (an even count)
+  //    the ping-pong returns to the pair it started from, so the sorted result lands where callers expect it and
+  //    (depth_keys, order_in) is the scratch pair.
+  set_word_kernel<<<1, 1, 0, s>>>(sc.n_word, (uint32_t)n);
+  int st = radix_sort(c->depth_keys_sorted, c->order, c->depth_keys, c->order_in, sc.n_word, (uint32_t)n, 32, sc, blocks, s);
+  if (st) return st;
+  // 2 + 3. Scan of the counts in depth order and emission, into the pair the tile sort will read first.
+  const int tile_passes = (c->tile_bits + 7) / 8;
+  uint32_t* ek = (tile_passes % 2 == 0) ? c->keys_sorted : c->keys;
+  uint32_t* ev = (tile_passes % 2 == 0) ? c->vals_sorted : c->vals;
+  uint32_t* ok = (tile_passes % 2 == 0) ? c->keys : c->keys_sorted;
+  uint32_t* ov = (tile_passes % 2 == 0) ? c->vals : c->vals_sorted;
+  count_sums_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums);
+  scan_emit_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums, (const float4*)c->proj0, (const float4*)c->proj1,
+                                                  c->W, c->H, c->tiles_x, c->tiles_y, (uint32_t)c->isect_cap, c->tile_off, ek, ev, c->num_isect);
+  st = check_launch();
+  if (st) return st;
+  // 4. Stable sort by tile id: depth order survives inside each tile.
+  st = radix_sort(ek, ev, ok, ov, c->num_isect, (uint32_t)c->isect_cap, c->tile_bits, sc, blocks, s);
+  if (st) return st;
+  tile_ranges_kernel<<<sm_count() * 8, 256, 0, s>>>(c->keys_sorted, c->num_isect, (uint32_t)c->isect_cap, (uint32_t)c->n_tiles, (uint2*)c->tile_ranges);
+  return check_launch();
+}
+
+extern "C" int b2k_read_num_isect(const B2kCtx* c, b2k_stream_t stream, uint32_t* total) {
+  B2K_REQUIRE(c && c->num_isect && total);
+  cudaStream_t s = (cudaStream_t)stream;
+  B2K_CUDA(cudaMemcpyAsync(total, c->num_isect, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+  B2K_CUDA(cudaStreamSynchronize(s));
+  return *total > c->isect_cap ? B2K_ERR_OVERFLOW : B2K_OK;
+}

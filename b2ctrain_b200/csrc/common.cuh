@@ -1,0 +1,182 @@
+// Shared device code of the b2k kernels: constants, status plumbing, the fp32 EWA projection and the exact tile
+// decision functions.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/b2k.h"
+
+namespace b2k {
+
+constexpr int RT_W = 8;                 // rasteriser tile edge (reference: src/gpu/util.cuh:19)
+constexpr int RT_PX = RT_W * RT_W;
+constexpr int LOSS_TILE = 16;           // loss tile edge (util.cuh:17)
+constexpr int GRAD_LANES = 13;          // xy 2, conic 3, rgb 3, opacity 1, refine 1, feat 3 (splat_math.cuh:10)
+constexpr float ALPHA_CUTOFF = 1.0f / 255.0f;
+constexpr float T_CUTOFF = 1e-4f;
+constexpr float ALPHA_MAX = 0.999f;
+constexpr int NUM_SMS_HINT = 148;       // B200; grids of persistent kernels are sized from the device at run time
+
+extern int g_last_cuda_error;
+int check_launch();                     // cudaGetLastError -> status
+int sm_count();
+
+#define B2K_REQUIRE(cond) do { if (!(cond)) return B2K_ERR_ARG; } while (0)
+#define B2K_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) { b2k::g_last_cuda_error = (int)e_; return B2K_ERR_CUDA; } } while (0)
+
+__host__ __device__ inline int div_up(long long a, int b) { return (int)((a + b - 1) / b); }
+
+struct CamDev {
+  float R[9]; float t[3]; float pos[3]; float fx, fy, cx, cy; int W, H; float lim_pos_x, lim_pos_y, lim_neg_x, lim_neg_y;
+};
+inline CamDev to_camdev(const B2kCamera& c) {
+  CamDev d;
+  for (int i = 0; i < 9; i++) d.R[i] = c.R[i];
+  for (int i = 0; i < 3; i++) { d.t[i] = c.t[i]; d.pos[i] = c.pos[i]; }
+  d.fx = c.fx; d.fy = c.fy; d.cx = c.cx; d.cy = c.cy; d.W = c.W; d.H = c.H;
+  d.lim_pos_x = c.lim_pos_x; d.lim_pos_y = c.lim_pos_y; d.lim_neg_x = c.lim_neg_x; d.lim_neg_y = c.lim_neg_y;
+  return d;
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Exact tile decisions. Everything below is a fixed tree of IEEE round-to-nearest single-precision operations (no
+// contraction into FMA, no approximate division or square root), so a host evaluation of the same tree in plain
+// float arithmetic gives the same tiles bit for bit. Inputs are the fp32 record the projection stored.
+// Reference semantics: tile_bbox / tile_hit (src/gpu/splat_math.cuh:27-53), extent and on-screen culls
+// (splat_math.cuh:284-290).
+// ---------------------------------------------------------------------------------------------------------------
+struct TileRec { float mx, my, c00, c01, c11, power; };
+struct TileBox { int min_x, min_y, max_x, max_y; };
+
+__device__ __forceinline__ float rn_mul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float rn_add(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float rn_sub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float rn_div(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float clamp01(float x) { return fminf(fmaxf(x, 0.f), 1.f); }
+
+__device__ __forceinline__ bool tile_box(const TileRec& r, int W, int H, int tiles_x, int tiles_y, TileBox& b) {
+  const float detc = rn_sub(rn_mul(r.c00, r.c11), rn_mul(r.c01, r.c01));
+  if (!(detc > 0.f)) return false;
+  const float inv = rn_div(1.f, detc);
+  const float p2 = rn_mul(2.f, r.power);
+  const float ex = __fsqrt_rn(rn_mul(rn_mul(p2, r.c11), inv)), ey = __fsqrt_rn(rn_mul(rn_mul(p2, r.c00), inv));
+  if (!(ex >= 0.f && ey >= 0.f)) return false;
+  const bool on = rn_add(r.mx, ex) > 0.f && rn_sub(r.mx, ex) < (float)W && rn_add(r.my, ey) > 0.f && rn_sub(r.my, ey) < (float)H;
+  if (!on) return false;
+  const float tw = (float)RT_W, txs = (float)tiles_x, tys = (float)tiles_y;
+  const float cx = rn_div(r.mx, tw), cy = rn_div(r.my, tw), dx = rn_div(ex, tw), dy = rn_div(ey, tw);
+  b.min_x = (int)fminf(fmaxf(rn_sub(cx, dx), 0.f), txs);
+  b.min_y = (int)fminf(fmaxf(rn_sub(cy, dy), 0.f), tys);
+  b.max_x = (int)fminf(fmaxf(rn_add(rn_add(cx, dx), 1.f), 0.f), txs);
+  b.max_y = (int)fminf(fmaxf(rn_add(rn_add(cy, dy), 1.f), 0.f), tys);
+  return true;
+}
+
+__device__ __forceinline__ bool tile_hit(int tx, int ty, const TileRec& r) {
+  const float rmin_x = (float)(tx * RT_W), rmin_y = (float)(ty * RT_W);
+  const float rmax_x = rmin_x + (float)RT_W, rmax_y = rmin_y + (float)RT_W;   // exact: small integers
+  const bool x_left = r.mx < rmin_x, x_right = r.mx > rmax_x, in_x = !(x_left || x_right);
+  const bool y_above = r.my < rmin_y, y_below = r.my > rmax_y, in_y = !(y_above || y_below);
+  if (in_x && in_y) return true;
+  const float corner_x = x_left ? rmin_x : rmax_x, corner_y = y_above ? rmin_y : rmax_y;
+  const float dxf = x_left ? (float)RT_W : -(float)RT_W, dyf = y_above ? (float)RT_W : -(float)RT_W;
+  const float diff_x = rn_sub(r.mx, corner_x), diff_y = rn_sub(r.my, corner_y);
+  const float tx_raw = rn_div(rn_add(rn_mul(rn_mul(dxf, r.c00), diff_x), rn_mul(rn_mul(dxf, r.c01), diff_y)), rn_mul(rn_mul(dxf, r.c00), dxf));
+  const float ty_raw = rn_div(rn_add(rn_mul(rn_mul(dyf, r.c01), diff_x), rn_mul(rn_mul(dyf, r.c11), diff_y)), rn_mul(rn_mul(dyf, r.c11), dyf));
+  const float tx_c = in_y ? 0.f : clamp01(tx_raw), ty_c = in_x ? 0.f : clamp01(ty_raw);
+  const float px = rn_add(corner_x, rn_mul(tx_c, dxf)), py = rn_add(corner_y, rn_mul(ty_c, dyf));
+  const float dx = rn_sub(px, r.mx), dy = rn_sub(py, r.my);
+  const float q = rn_add(rn_mul(rn_mul(r.c00, dx), dx), rn_mul(rn_mul(r.c11, dy), dy));
+  const float sigma = rn_add(rn_mul(0.5f, q), rn_mul(rn_mul(r.c01, dx), dy));
+  return sigma <= r.power;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// EWA projection of one splat with the 3D-filter scale floor. Reference semantics: project_one
+// (src/gpu/splat_math.cuh:224-293) without its mip branch (rejected by the reference's CLI, main.cpp:26). The
+// extent / on-screen culls live in tile_box above so that they are decided from the stored record.
+// ---------------------------------------------------------------------------------------------------------------
+struct Proj {
+  float3 mean_c;
+  float3 s, s2_raw;
+  float comp_floor;
+  float Rq[9];
+  float J02, J12, dx, dy;     // J = [[dx, 0, J02], [0, dy, J12]]
+  bool clamp_x, clamp_y;
+  float c00, c01, c11;        // conic
+  float opac, sig;
+  float mx, my;
+  float power;
+};
+
+__device__ __forceinline__ void quat_to_mat(float w, float x, float y, float z, float* R) {
+  const float x2 = x * x, y2 = y * y, z2 = z * z, xy = x * y, xz = x * z, yz = y * z, wx = w * x, wy = w * y, wz = w * z;
+  R[0] = 1.f - 2.f * (y2 + z2); R[1] = 2.f * (xy - wz);       R[2] = 2.f * (xz + wy);
+  R[3] = 2.f * (xy + wz);       R[4] = 1.f - 2.f * (x2 + z2); R[5] = 2.f * (yz - wx);
+  R[6] = 2.f * (xz - wy);       R[7] = 2.f * (yz + wx);       R[8] = 1.f - 2.f * (x2 + y2);
+}
+
+__device__ __forceinline__ bool project_one(const float4 po, const float4 q, const float4 ls, const CamDev& cam, Proj& r) {
+  const float* R = cam.R;
+  r.mean_c = make_float3(R[0] * po.x + R[1] * po.y + R[2] * po.z + cam.t[0], R[3] * po.x + R[4] * po.y + R[5] * po.z + cam.t[1],
+                         R[6] * po.x + R[7] * po.y + R[8] * po.z + cam.t[2]);
+  const float3 mc = r.mean_c;
+  if (!(isfinite(mc.x) && isfinite(mc.y) && isfinite(mc.z) && mc.z <= 1e10f)) return false;
+  if (!(mc.z >= 0.01f)) return false;
+  r.s2_raw = make_float3(expf(2.f * ls.x), expf(2.f * ls.y), expf(2.f * ls.z));
+  const float f2 = ls.w * ls.w;
+  const float3 s2f = make_float3(r.s2_raw.x + f2, r.s2_raw.y + f2, r.s2_raw.z + f2);
+  r.s = make_float3(sqrtf(s2f.x), sqrtf(s2f.y), sqrtf(s2f.z));
+  r.comp_floor = ls.w > 0.f ? sqrtf((r.s2_raw.x * r.s2_raw.y * r.s2_raw.z) / (s2f.x * s2f.y * s2f.z)) : 1.f;
+  if (!(isfinite(r.s.x) && isfinite(r.s.y) && isfinite(r.s.z))) return false;
+  const float qn2 = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+  if (!(qn2 >= 1e-6f && isfinite(qn2))) return false;
+  if (!isfinite(po.w)) return false;
+  const float inv_qn = 1.f / sqrtf(qn2);
+  quat_to_mat(q.x * inv_qn, q.y * inv_qn, q.z * inv_qn, q.w * inv_qn, r.Rq);
+  float M[9];   // R_view * Rq * diag(s)
+#pragma unroll
+  for (int i = 0; i < 3; i++) {
+    M[i * 3 + 0] = (R[i * 3] * r.Rq[0] + R[i * 3 + 1] * r.Rq[3] + R[i * 3 + 2] * r.Rq[6]) * r.s.x;
+    M[i * 3 + 1] = (R[i * 3] * r.Rq[1] + R[i * 3 + 1] * r.Rq[4] + R[i * 3 + 2] * r.Rq[7]) * r.s.y;
+    M[i * 3 + 2] = (R[i * 3] * r.Rq[2] + R[i * 3 + 1] * r.Rq[5] + R[i * 3 + 2] * r.Rq[8]) * r.s.z;
+  }
+  const float inv_z = 1.f / mc.z;
+  const float rx = mc.x * inv_z, ry = mc.y * inv_z;
+  const float cxr = fminf(fmaxf(rx, cam.lim_neg_x), cam.lim_pos_x), cyr = fminf(fmaxf(ry, cam.lim_neg_y), cam.lim_pos_y);
+  r.clamp_x = !(rx <= cam.lim_pos_x && rx >= cam.lim_neg_x);
+  r.clamp_y = !(ry <= cam.lim_pos_y && ry >= cam.lim_neg_y);
+  r.dx = cam.fx * inv_z; r.dy = cam.fy * inv_z;
+  r.J02 = -r.dx * cxr; r.J12 = -r.dy * cyr;
+  float V[6];
+#pragma unroll
+  for (int j = 0; j < 3; j++) { V[j] = r.dx * M[j] + r.J02 * M[6 + j]; V[3 + j] = r.dy * M[3 + j] + r.J12 * M[6 + j]; }
+  float c00 = V[0] * V[0] + V[1] * V[1] + V[2] * V[2], c01 = V[0] * V[3] + V[1] * V[4] + V[2] * V[5], c11 = V[3] * V[3] + V[4] * V[4] + V[5] * V[5];
+  const float max_abs = fmaxf(fabsf(c00), fmaxf(fabsf(c01), fabsf(c11)));
+  if (max_abs > 1e18f) { const float k = 1e18f / max_abs; c00 *= k; c01 *= k; c11 *= k; }
+  c00 += 0.3f; c11 += 0.3f;   // screen-space blur
+  r.sig = 1.f / (1.f + expf(-po.w));
+  r.opac = r.sig * r.comp_floor;
+  if (!(isfinite(c00) && isfinite(c01) && isfinite(c11))) return false;
+  const float det = c00 * c11 - c01 * c01;
+  if (!(det > 0.f)) return false;
+  const float inv_det = 1.f / det;
+  r.c00 = c11 * inv_det; r.c01 = -c01 * inv_det; r.c11 = c00 * inv_det;
+  r.mx = cam.fx * rx + cam.cx; r.my = cam.fy * ry + cam.cy;
+  if (!(r.opac >= ALPHA_CUTOFF)) return false;
+  r.power = logf(r.opac * 255.f);
+  const float detc = r.c00 * r.c11 - r.c01 * r.c01;
+  if (!(detc > 0.f)) return false;
+  return true;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace b2k

@@ -1,0 +1,306 @@
+// Fused photometric loss: L1 + 11-tap Gaussian SSIM (sigma 1.5, zero padding) + alpha-match lane, value and
+// per-pixel gradient in one kernel. Reference semantics: photometric_kernel (src/gpu/loss.cu:18-195),
+// accumulate_kernel (loss.cu:317), eval_kernel (loss.cu:241-293).
+//
+// One CTA of 256 threads owns a 16x16 pixel tile and runs the three colour channels back to back over one staged
+// 36x36 footprint, so the float4 prediction and the packed target are read from global memory once per CTA (the
+// reference launches one CTA per channel and reads them three times) and the gradient leaves as one 128-bit store
+// per pixel. The work is a shared-memory stencil: forward separable blur of five moments, SSIM and its five partial
+// derivative maps, the same blur applied backwards.
+#include "common.cuh"
+
+namespace b2k {
+namespace {
+
+constexpr int HALO = 5;
+constexpr int STAT_W = LOSS_TILE + 2 * HALO;   // 26: positions whose SSIM statistics reach the tile
+constexpr int IN_W = STAT_W + 2 * HALO;        // 36: input footprint
+constexpr int TILE_PX = LOSS_TILE * LOSS_TILE;
+constexpr float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
+
+struct Gauss { float w[11]; };
+
+Gauss make_gauss() {
+  Gauss g; float sum = 0.f;
+  for (int i = 0; i < 11; i++) { const float x = (float)i - 5.f; g.w[i] = expf(-x * x / (2.f * 1.5f * 1.5f)); sum += g.w[i]; }
+  for (int i = 0; i < 11; i++) g.w[i] /= sum;
+  return g;
+}
+
+__device__ __forceinline__ float unpack(uint32_t p, int c) { return (float)((p >> (8 * c)) & 0xffu) * (1.f / 255.f); }
+
+struct LossArgs {
+  float l1_w, ssim_w, bg[3]; int composite, mask, alpha_lane; float match_alpha_weight, scale, grad_scale;
+};
+
+constexpr size_t LOSS_SMEM = sizeof(float) * (4 * IN_W * IN_W      // pred r, g, b + alpha
+                                              + 3 * IN_W * IN_W    // effective target r, g, b
+                                              + IN_W * STAT_W * 5  // horizontal pass
+                                              + STAT_W * STAT_W * 5)
+                             + sizeof(float) * IN_W * IN_W;        // per-position loss mask M
+
+__global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __restrict__ pred, const uint32_t* __restrict__ gt, const uint8_t* __restrict__ weights,
+                                                              int W, int H, int tiles_x, LossArgs lp, Gauss gauss, float4* __restrict__ v_out, float* __restrict__ loss_accum) {
+  extern __shared__ float smem[];
+  float* s_p = smem;                            // [4][IN_W*IN_W]
+  float* s_g = s_p + 4 * IN_W * IN_W;           // [3][IN_W*IN_W]
+  float* s_h = s_g + 3 * IN_W * IN_W;           // [IN_W*STAT_W][5]
+  float* s_v = s_h + IN_W * STAT_W * 5;         // [STAT_W*STAT_W][5]
+  float* s_m = s_v + STAT_W * STAT_W * 5;       // [IN_W*IN_W] M = weight * (mask ? gt alpha : 1) * scale / (3WH), 0 outside
+  __shared__ float s_red[TILE_PX / 32];
+
+  const int tile = blockIdx.x, tid = threadIdx.x;
+  const int tx0 = (tile % tiles_x) * LOSS_TILE, ty0 = (tile / tiles_x) * LOSS_TILE;
+  const float norm = lp.scale / (3.f * (float)W * (float)H);
+  const int ly = tid / LOSS_TILE, lx = tid % LOSS_TILE;
+  const int gy = ty0 + ly, gx = tx0 + lx;
+  const bool inside = gy < H && gx < W;
+  const int pix = inside ? gy * W + gx : 0;
+  const int centre = (ly + 2 * HALO) * IN_W + lx + 2 * HALO;
+
+  float flat_r = 0.f, flat_g = 0.f, flat_b = 0.f;   // per channel: max |pred - target| over the footprint
+  for (int i = tid; i < IN_W * IN_W; i += TILE_PX) {
+    const int fy = i / IN_W, fx = i % IN_W;
+    const int y = ty0 + fy - 2 * HALO, x = tx0 + fx - 2 * HALO;
+    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+    float g0 = 0.f, g1 = 0.f, g2 = 0.f, M = 0.f;
+    if (y >= 0 && y < H && x >= 0 && x < W) {
+      const int q = y * W + x;
+      p = pred[q];
+      const uint32_t gp = gt[q];
+      const float ga = unpack(gp, 3);
+      g0 = unpack(gp, 0); g1 = unpack(gp, 1); g2 = unpack(gp, 2);
+      if (lp.composite) { g0 += (1.f - ga) * lp.bg[0]; g1 += (1.f - ga) * lp.bg[1]; g2 += (1.f - ga) * lp.bg[2]; }
+      const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
+      M = wp * (lp.mask ? ga : 1.f) * norm;
+    }
+    s_p[i] = p.x; s_p[IN_W * IN_W + i] = p.y; s_p[2 * IN_W * IN_W + i] = p.z; s_p[3 * IN_W * IN_W + i] = p.w;
+    s_g[i] = g0; s_g[IN_W * IN_W + i] = g1; s_g[2 * IN_W * IN_W + i] = g2;
+    s_m[i] = M;
+    flat_r = fmaxf(flat_r, fabsf(p.x - g0)); flat_g = fmaxf(flat_g, fabsf(p.y - g1)); flat_b = fmaxf(flat_b, fabsf(p.z - g2));
+  }
+  float gt_a = 0.f, wp_c = 1.f;
+  if (inside) {
+    gt_a = unpack(gt[pix], 3);
+    wp_c = weights ? (float)weights[pix] * (1.f / 255.f) : 1.f;
+  }
+  __syncthreads();
+  if (lp.alpha_lane && inside) flat_r = fmaxf(flat_r, fabsf(s_p[3 * IN_W * IN_W + centre] - gt_a));
+
+  float loss_local = 0.f;
+  float4 grad = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Exact early exit per channel: where the prediction equals the effective target on the whole footprint (for the
+  // first channel: and alpha matches on the tile) every gradient of that channel is exactly zero and SSIM is exactly
+  // one, so only the constant term enters the loss.
+  const bool nonflat[3] = {__syncthreads_or(flat_r > 0.f) != 0, __syncthreads_or(flat_g > 0.f) != 0, __syncthreads_or(flat_b > 0.f) != 0};
+  {
+    for (int c = 0; c < 3; c++) {
+      if (!nonflat[c]) { if (inside) loss_local += s_m[centre] * lp.ssim_w; continue; }
+      const float* P = s_p + c * IN_W * IN_W;
+      const float* G = s_g + c * IN_W * IN_W;
+      // Horizontal blur of the five moments: rows 0..35, output columns 0..25.
+      for (int i = tid; i < IN_W * STAT_W; i += TILE_PX) {
+        const int row = i / STAT_W, ox = i % STAT_W;
+        float sx = 0.f, sx2 = 0.f, sy = 0.f, sy2 = 0.f, sxy = 0.f;
+#pragma unroll
+        for (int d = 0; d < 11; d++) {
+          const float w = gauss.w[d];
+          const float x = P[row * IN_W + ox + d], y = G[row * IN_W + ox + d];
+          sx += w * x; sx2 += w * x * x; sy += w * y; sy2 += w * y * y; sxy += w * x * y;
+        }
+        float* o = s_h + i * 5; o[0] = sx; o[1] = sx2; o[2] = sy; o[3] = sy2; o[4] = sxy;
+      }
+      __syncthreads();
+      // Vertical blur -> statistics at 26x26, SSIM there, partial derivative maps scaled by M * ssim_w.
+      for (int i = tid; i < STAT_W * STAT_W; i += TILE_PX) {
+        const int oy = i / STAT_W, ox = i % STAT_W;
+        float st[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int d = 0; d < 11; d++) {
+          const float w = gauss.w[d];
+          const float* h = s_h + ((oy + d) * STAT_W + ox) * 5;
+#pragma unroll
+          for (int k = 0; k < 5; k++) st[k] += w * h[k];
+        }
+        const int fi = (oy + HALO) * IN_W + ox + HALO;
+        const float M = s_m[fi];   // zero outside the image
+        float A = 0.f, B = 0.f, Bm = 0.f, Cc = 0.f, Cm = 0.f;
+        const int y = ty0 + oy - HALO, x = tx0 + ox - HALO;
+        if (y >= 0 && y < H && x >= 0 && x < W) {
+          const float mu1 = st[0], mu2 = st[2];
+          const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
+          const float s1_raw = st[1] - mu1_sq, s2_raw = st[3] - mu2_sq;
+          const float sigma1_sq = fmaxf(0.f, s1_raw), sigma2_sq = fmaxf(0.f, s2_raw);
+          const float sigma12 = st[4] - mu1 * mu2;
+          const float A1 = 2.f * mu1 * mu2 + C1, A2 = 2.f * sigma12 + C2, B1 = mu1_sq + mu2_sq + C1, B2 = sigma1_sq + sigma2_sq + C2;
+          const float inv_BB = 1.f / (B1 * B2);
+          const float raw = A1 * A2 * inv_BB;
+          const float ssim = fminf(fmaxf(raw, -1.f), 1.f);
+          if (oy >= HALO && oy < HALO + LOSS_TILE && ox >= HALO && ox < HALO + LOSS_TILE)
+            loss_local += M * (lp.l1_w * fabsf(P[fi] - G[fi]) + lp.ssim_w * ssim);
+          if (raw > -1.f && raw < 1.f) {
+            const float k = M * lp.ssim_w;
+            const float d_mu1 = 2.f * mu2 * A2 * inv_BB - 2.f * mu1 * ssim / B1;
+            const float d_s1 = s1_raw > 0.f ? -ssim / B2 : 0.f;
+            const float d_s12 = 2.f * A1 * inv_BB;
+            A = k * d_mu1; B = k * d_s1; Bm = B * mu1; Cc = k * d_s12; Cm = Cc * mu2;
+          }
+        }
+        float* o = s_v + i * 5; o[0] = A; o[1] = B; o[2] = Bm; o[3] = Cc; o[4] = Cm;
+      }
+      __syncthreads();
+      // Backward blur, horizontal: rows 0..25, output columns 0..15.
+      for (int i = tid; i < STAT_W * LOSS_TILE; i += TILE_PX) {
+        const int row = i / LOSS_TILE, ox = i % LOSS_TILE;
+        float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int d = 0; d < 11; d++) {
+          const float w = gauss.w[d];
+          const float* v = s_v + (row * STAT_W + ox + d) * 5;
+#pragma unroll
+          for (int k = 0; k < 5; k++) acc[k] += w * v[k];
+        }
+        float* o = s_h + i * 5;
+#pragma unroll
+        for (int k = 0; k < 5; k++) o[k] = acc[k];
+      }
+      __syncthreads();
+      // Backward blur, vertical: one pixel per thread, then the chain rule through the five moments.
+      if (inside) {
+        float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int d = 0; d < 11; d++) {
+          const float w = gauss.w[d];
+          const float* v = s_h + ((ly + d) * LOSS_TILE + lx) * 5;
+#pragma unroll
+          for (int k = 0; k < 5; k++) acc[k] += w * v[k];
+        }
+        const float p = P[centre], g = G[centre];
+        const float sgn = p > g ? 1.f : (p < g ? -1.f : 0.f);
+        const float gr = (s_m[centre] * lp.l1_w * sgn + acc[0] + 2.f * p * acc[1] - 2.f * acc[2] + g * acc[3] - acc[4]) * lp.grad_scale;
+        if (c == 0) grad.x = gr; else if (c == 1) grad.y = gr; else grad.z = gr;
+      }
+      __syncthreads();   // s_h / s_v are reused by the next channel
+    }
+    if (inside && lp.alpha_lane && nonflat[0]) {
+      const float da = s_p[3 * IN_W * IN_W + centre] - gt_a;
+      const float sa = da > 0.f ? 1.f : (da < 0.f ? -1.f : 0.f);
+      const float Ma = wp_c * lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
+      grad.w = Ma * sa * lp.grad_scale;
+      loss_local += Ma * fabsf(da);
+    }
+  }
+  if (inside) v_out[pix] = grad;
+  const float s = warp_sum(loss_local);
+  if ((tid & 31) == 0) s_red[tid >> 5] = s;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int i = 0; i < TILE_PX / 32; i++) t += s_red[i];
+    if (t != 0.f) atomicAdd(loss_accum, t);
+  }
+}
+
+// PSNR / SSIM sums on the 8-bit-quantised prediction against the target on a black background.
+__global__ void __launch_bounds__(TILE_PX) eval_kernel(const float4* __restrict__ pred, const uint32_t* __restrict__ gt, int W, int H, int tiles_x, int mask_w,
+                                                       Gauss gauss, float* __restrict__ accum) {
+  __shared__ float s_in[2][IN_W * IN_W];
+  __shared__ float s_h[STAT_W * LOSS_TILE * 5];
+  __shared__ float s_red[2][TILE_PX / 32];
+  const int c = blockIdx.y, tile = blockIdx.x, tid = threadIdx.x;
+  const int tx0 = (tile % tiles_x) * LOSS_TILE, ty0 = (tile / tiles_x) * LOSS_TILE;
+  for (int i = tid; i < IN_W * IN_W; i += TILE_PX) {
+    const int fy = i / IN_W, fx = i % IN_W;
+    const int y = ty0 + fy - 2 * HALO, x = tx0 + fx - 2 * HALO;
+    float p = 0.f, g = 0.f;
+    if (y >= 0 && y < H && x >= 0 && x < W) {
+      const float4 pv = pred[y * W + x];
+      p = c == 0 ? pv.x : (c == 1 ? pv.y : pv.z);
+      p = rintf(fminf(fmaxf(p, 0.f), 1.f) * 255.f) / 255.f;
+      g = unpack(gt[y * W + x], c);
+    }
+    s_in[0][i] = p; s_in[1][i] = g;
+  }
+  __syncthreads();
+  for (int i = tid; i < STAT_W * LOSS_TILE; i += TILE_PX) {
+    const int row = i / LOSS_TILE + HALO, ox = i % LOSS_TILE + HALO;
+    float sx = 0.f, sx2 = 0.f, sy = 0.f, sy2 = 0.f, sxy = 0.f;
+#pragma unroll
+    for (int d = 0; d < 11; d++) {
+      const float w = gauss.w[d];
+      const float x = s_in[0][row * IN_W + ox + d], y = s_in[1][row * IN_W + ox + d];
+      sx += w * x; sx2 += w * x * x; sy += w * y; sy2 += w * y * y; sxy += w * x * y;
+    }
+    float* o = s_h + i * 5; o[0] = sx; o[1] = sx2; o[2] = sy; o[3] = sy2; o[4] = sxy;
+  }
+  __syncthreads();
+  float mse = 0.f, ssim_v = 0.f;
+  const int ly = tid / LOSS_TILE, lx = tid % LOSS_TILE;
+  const int gy = ty0 + ly, gx = tx0 + lx;
+  if (gy < H && gx < W) {
+    float st[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < 11; d++) {
+      const float w = gauss.w[d];
+      const float* h = s_h + ((ly + d) * LOSS_TILE + lx) * 5;
+#pragma unroll
+      for (int k = 0; k < 5; k++) st[k] += w * h[k];
+    }
+    const float mu1 = st[0], mu2 = st[2], s1 = fmaxf(0.f, st[1] - mu1 * mu1), s2 = fmaxf(0.f, st[3] - mu2 * mu2), s12 = st[4] - mu1 * mu2;
+    const float ssim = fminf(fmaxf(((2.f * mu1 * mu2 + C1) * (2.f * s12 + C2)) / ((mu1 * mu1 + mu2 * mu2 + C1) * (s1 + s2 + C2)), -1.f), 1.f);
+    const int ci = (ly + 2 * HALO) * IN_W + lx + 2 * HALO;
+    const float d = fabsf(s_in[0][ci] - s_in[1][ci]);
+    const float m = mask_w ? unpack(gt[gy * W + gx], 3) : 1.f;
+    mse = (d * m) * (d * m); ssim_v = ssim * m;
+  }
+  const float a = warp_sum(mse), b = warp_sum(ssim_v);
+  if ((tid & 31) == 0) { s_red[0][tid >> 5] = a; s_red[1][tid >> 5] = b; }
+  __syncthreads();
+  if (tid == 0) {
+    float ta = 0.f, tb = 0.f;
+    for (int i = 0; i < TILE_PX / 32; i++) { ta += s_red[0][i]; tb += s_red[1][i]; }
+    atomicAdd(accum + 4, ta); atomicAdd(accum + 5, tb);
+  }
+}
+
+__global__ void accumulate_kernel(float* a) { a[2] += a[0] + a[1]; a[3] += 1.f; }
+
+bool g_smem_set[64] = {false};
+
+}  // namespace
+}  // namespace b2k
+
+using namespace b2k;
+
+extern "C" int b2k_loss_photometric(const B2kCtx* c, const B2kLoss* lp, b2k_stream_t stream) {
+  B2K_REQUIRE(c && lp && lp->rgba && c->out_rgba && c->v_out && c->loss_accum && c->W > 0 && c->H > 0);
+  int dev = 0;
+  B2K_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !g_smem_set[dev]) {
+    B2K_CUDA(cudaFuncSetAttribute(photometric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LOSS_SMEM));
+    g_smem_set[dev] = true;
+  }
+  const int tiles_x = div_up(c->W, LOSS_TILE), tiles = tiles_x * div_up(c->H, LOSS_TILE);
+  LossArgs a;
+  a.l1_w = lp->l1_w; a.ssim_w = lp->ssim_w; a.bg[0] = lp->bg[0]; a.bg[1] = lp->bg[1]; a.bg[2] = lp->bg[2];
+  a.composite = lp->composite; a.mask = lp->mask; a.alpha_lane = lp->alpha_lane;
+  a.match_alpha_weight = lp->match_alpha_weight; a.scale = lp->scale; a.grad_scale = lp->grad_scale;
+  static const Gauss g = make_gauss();
+  photometric_kernel<<<tiles, TILE_PX, LOSS_SMEM, (cudaStream_t)stream>>>((const float4*)c->out_rgba, lp->rgba, lp->weights, c->W, c->H, tiles_x, a, g,
+                                                                        (float4*)c->v_out, c->loss_accum);
+  return check_launch();
+}
+
+extern "C" int b2k_loss_accumulate(const B2kCtx* c, b2k_stream_t stream) {
+  B2K_REQUIRE(c && c->loss_accum);
+  accumulate_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(c->loss_accum);
+  return check_launch();
+}
+
+extern "C" int b2k_eval_metrics(const B2kCtx* c, const uint32_t* rgba, int32_t mask_weighted, b2k_stream_t stream) {
+  B2K_REQUIRE(c && rgba && c->out_rgba && c->loss_accum && c->W > 0 && c->H > 0);
+  const int tiles_x = div_up(c->W, LOSS_TILE), tiles = tiles_x * div_up(c->H, LOSS_TILE);
+  static const Gauss g = make_gauss();
+  eval_kernel<<<dim3(tiles, 3), TILE_PX, 0, (cudaStream_t)stream>>>((const float4*)c->out_rgba, rgba, c->W, c->H, tiles_x, mask_weighted, g, c->loss_accum);
+  return check_launch();
+}

@@ -1,0 +1,448 @@
+// Projection backward (screen-space gradient lanes -> parameter gradients) and sparse Adam with the Adam-mini SH
+// second moment. Reference semantics: optim_kernel (src/gpu/optim.cu:100-378), adam4 (optim.cu:90-97).
+//
+// Three kernels share the device functions below:
+//   optim_fused_kernel  the reference's single-view step: gradient and update in one pass over the splats
+//   proj_bwd_kernel     gradient half only, ADDED into a dense [n][11+3K] accumulator (several views, then an
+//                       all-reduce across GPUs)
+//   adam_kernel         update half only, from that accumulator
+// All are HBM-bound streams over the model: one thread per splat, 128-bit loads of the float4 parameter and moment
+// groups, planar (coalesced) SH lanes.
+#include "common.cuh"
+#include "sh.cuh"
+
+namespace b2k {
+namespace {
+
+constexpr int OPT_BLOCK = 128;
+
+struct ParamGrad { float3 pos; float op; float4 q; float3 ls; };
+
+// Matrix form of the chain: T = J Rv M with M = Rq diag(s); cov = T T^T + blur; conic = cov^-1.
+__device__ __forceinline__ void geometry_backward(const float* g, const Proj& pr, const CamDev& cam, const float4 qv, const float4 lsv, ParamGrad& o) {
+  const float* Rv = cam.R;
+  // conic -> covariance: dL/dcov = -X G X, G the symmetric gradient of the conic (off-diagonal lane halved).
+  const float G00 = g[2], G01 = 0.5f * g[3], G11 = g[4];
+  const float X00 = pr.c00, X01 = pr.c01, X11 = pr.c11;
+  const float a00 = X00 * G00 + X01 * G01, a01 = X00 * G01 + X01 * G11, a10 = X01 * G00 + X11 * G01, a11 = X01 * G01 + X11 * G11;
+  const float v00 = -(a00 * X00 + a01 * X01), v01 = -(a00 * X01 + a01 * X11), v11 = -(a10 * X01 + a11 * X11);
+  float M[9], RvM[9];
+#pragma unroll
+  for (int r = 0; r < 3; r++) { M[r * 3] = pr.Rq[r * 3] * pr.s.x; M[r * 3 + 1] = pr.Rq[r * 3 + 1] * pr.s.y; M[r * 3 + 2] = pr.Rq[r * 3 + 2] * pr.s.z; }
+#pragma unroll
+  for (int r = 0; r < 3; r++)
+#pragma unroll
+    for (int c = 0; c < 3; c++) RvM[r * 3 + c] = Rv[r * 3] * M[c] + Rv[r * 3 + 1] * M[3 + c] + Rv[r * 3 + 2] * M[6 + c];
+  float T[6], vT[6];
+#pragma unroll
+  for (int c = 0; c < 3; c++) { T[c] = pr.dx * RvM[c] + pr.J02 * RvM[6 + c]; T[3 + c] = pr.dy * RvM[3 + c] + pr.J12 * RvM[6 + c]; }
+#pragma unroll
+  for (int c = 0; c < 3; c++) { vT[c] = 2.f * (v00 * T[c] + v01 * T[3 + c]); vT[3 + c] = 2.f * (v01 * T[c] + v11 * T[3 + c]); }
+  // dL/dJ = vT (Rv M)^T: only J00, J11, J02, J12 are live.
+  const float vJ00 = vT[0] * RvM[0] + vT[1] * RvM[1] + vT[2] * RvM[2];
+  const float vJ02 = vT[0] * RvM[6] + vT[1] * RvM[7] + vT[2] * RvM[8];
+  const float vJ11 = vT[3] * RvM[3] + vT[4] * RvM[4] + vT[5] * RvM[5];
+  const float vJ12 = vT[3] * RvM[6] + vT[4] * RvM[7] + vT[5] * RvM[8];
+  // dL/dM = (J Rv)^T vT.
+  float JR[6], vM[9];
+#pragma unroll
+  for (int c = 0; c < 3; c++) { JR[c] = pr.dx * Rv[c] + pr.J02 * Rv[6 + c]; JR[3 + c] = pr.dy * Rv[3 + c] + pr.J12 * Rv[6 + c]; }
+#pragma unroll
+  for (int r = 0; r < 3; r++)
+#pragma unroll
+    for (int c = 0; c < 3; c++) vM[r * 3 + c] = JR[r] * vT[c] + JR[3 + r] * vT[3 + c];
+  // Camera-space mean through the pinhole and the clamped Jacobian (optim.cu:186-202).
+  const float x = pr.mean_c.x, y = pr.mean_c.y, z = pr.mean_c.z;
+  const float iz = 1.f / z, iz2 = iz * iz, iz3 = iz2 * iz;
+  const float cxr = fminf(fmaxf(x * iz, cam.lim_neg_x), cam.lim_pos_x), cyr = fminf(fmaxf(y * iz, cam.lim_neg_y), cam.lim_pos_y);
+  const float v2x = g[0], v2y = g[1];
+  const float vmx = cam.fx * iz * v2x + (pr.clamp_x ? 0.f : -cam.fx * iz2 * vJ02);
+  const float vmy = cam.fy * iz * v2y + (pr.clamp_y ? 0.f : -cam.fy * iz2 * vJ12);
+  const float vmz = -(cam.fx * x * v2x + cam.fy * y * v2y) * iz2 - cam.fx * iz2 * vJ00 - cam.fy * iz2 * vJ11
+                    + (pr.clamp_x ? cam.fx * cxr * iz2 : 2.f * cam.fx * x * iz3) * vJ02
+                    + (pr.clamp_y ? cam.fy * cyr * iz2 : 2.f * cam.fy * y * iz3) * vJ12;
+  o.pos.x += Rv[0] * vmx + Rv[3] * vmy + Rv[6] * vmz;
+  o.pos.y += Rv[1] * vmx + Rv[4] * vmy + Rv[7] * vmz;
+  o.pos.z += Rv[2] * vmx + Rv[5] * vmy + Rv[8] * vmz;
+  // Scales through s_eff = sqrt(exp(2l) + f^2) and the floor's opacity compensation (optim.cu:219-225).
+  const float f2 = lsv.w * lsv.w, v_alpha = g[8];
+  const float vs0 = pr.Rq[0] * vM[0] + pr.Rq[3] * vM[3] + pr.Rq[6] * vM[6];
+  const float vs1 = pr.Rq[1] * vM[1] + pr.Rq[4] * vM[4] + pr.Rq[7] * vM[7];
+  const float vs2 = pr.Rq[2] * vM[2] + pr.Rq[5] * vM[5] + pr.Rq[8] * vM[8];
+  o.ls.x = vs0 * pr.s2_raw.x / pr.s.x + v_alpha * pr.opac * f2 / (pr.s2_raw.x + f2);
+  o.ls.y = vs1 * pr.s2_raw.y / pr.s.y + v_alpha * pr.opac * f2 / (pr.s2_raw.y + f2);
+  o.ls.z = vs2 * pr.s2_raw.z / pr.s.z + v_alpha * pr.opac * f2 / (pr.s2_raw.z + f2);
+  // Rotation: dL/dRq = vM diag(s), through R(q / |q|).
+  float V[9];
+#pragma unroll
+  for (int r = 0; r < 3; r++) { V[r * 3] = vM[r * 3] * pr.s.x; V[r * 3 + 1] = vM[r * 3 + 1] * pr.s.y; V[r * 3 + 2] = vM[r * 3 + 2] * pr.s.z; }
+  const float ql2 = qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w;
+  const float iql = 1.f / sqrtf(ql2);
+  const float qw = qv.x * iql, qx = qv.y * iql, qy = qv.z * iql, qz = qv.w * iql;
+  const float gw = 2.f * (-qz * V[1] + qy * V[2] + qz * V[3] - qx * V[5] - qy * V[6] + qx * V[7]);
+  const float gx = 2.f * (qy * V[1] + qz * V[2] + qy * V[3] - 2.f * qx * V[4] - qw * V[5] + qz * V[6] + qw * V[7] - 2.f * qx * V[8]);
+  const float gy = 2.f * (-2.f * qy * V[0] + qx * V[1] + qw * V[2] + qx * V[3] + qz * V[5] - qw * V[6] + qz * V[7] - 2.f * qy * V[8]);
+  const float gz = 2.f * (-2.f * qz * V[0] - qw * V[1] + qx * V[2] + qw * V[3] - 2.f * qz * V[4] + qy * V[5] + qx * V[6] + qy * V[7]);
+  const float gd = gw * qw + gx * qx + gy * qy + gz * qz;
+  o.q = make_float4((gw - qw * gd) * iql, (gx - qx * gd) * iql, (gy - qy * gd) * iql, (gz - qz * gd) * iql);
+}
+
+struct SplatGrad {
+  bool any;        // the splat has a usable gradient this view
+  bool visible;
+  ParamGrad pg;
+  float3 vc;       // dL/dcolour
+  float refine;    // growth statistic lane
+};
+
+// Reads and clears the splat's screen-space lanes, updates the refine statistics, and derives the parameter
+// gradients. basis[] receives the SH basis (zero above the active degree, and all zero when there is no gradient).
+template <int DEG>
+__device__ __forceinline__ void splat_gradient(int i, size_t cap, const float4* __restrict__ pos_op, const float4* __restrict__ quat, const float4* __restrict__ lscale,
+                                               const float* __restrict__ sh_dc, const float* __restrict__ sh_hi, float* __restrict__ v_splat,
+                                               uint32_t* __restrict__ vis_flag, const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
+                                               float* __restrict__ vis_count, const CamDev& cam, int active, const float4* pos_ov, const float4* quat_ov,
+                                               const float4* ls_ov, SplatGrad& sg, float* basis) {
+  constexpr int K = (DEG + 1) * (DEG + 1);
+  float g[GRAD_LANES];
+  const uint32_t vis = vis_flag[i];
+  float* vs = v_splat + (size_t)i * GRAD_LANES;
+  if (vis) {
+    vis_flag[i] = 0u;
+#pragma unroll
+    for (int k = 0; k < GRAD_LANES; k++) { g[k] = vs[k]; vs[k] = 0.f; }
+  } else {
+#pragma unroll
+    for (int k = 0; k < GRAD_LANES; k++) g[k] = 0.f;
+  }
+  sg.visible = vis != 0u && tile_count[i] != 0u;
+  if (vis_count) vis_count[i] += sg.visible ? 1.f : 0.f;
+  sg.refine = isfinite(g[9]) ? fminf(fmaxf(g[9], 0.f), 1e32f) : 0.f;
+  if (refine_norm && sg.refine > 0.f) refine_norm[i] = fmaxf(refine_norm[i], sg.refine);
+  bool any = false, finite = true;
+#pragma unroll
+  for (int k = 0; k < GRAD_LANES; k++) { if (k != 9 && g[k] != 0.f) any = true; finite = finite && isfinite(g[k]); }
+  sg.any = any && sg.visible && finite;
+  sg.pg.pos = make_float3(0.f, 0.f, 0.f); sg.pg.op = 0.f; sg.pg.q = make_float4(0.f, 0.f, 0.f, 0.f); sg.pg.ls = make_float3(0.f, 0.f, 0.f);
+  sg.vc = make_float3(0.f, 0.f, 0.f);
+#pragma unroll
+  for (int k = 0; k < K; k++) basis[k] = 0.f;
+  if (!sg.any) return;
+  const float4 pv = pos_ov ? pos_ov[i] : pos_op[i];
+  const float4 qv = quat_ov ? quat_ov[i] : quat[i];
+  const float4 lsv = ls_ov ? ls_ov[i] : lscale[i];
+  Proj pr;
+  if (!project_one(pv, qv, lsv, cam, pr)) return;
+  // SH: colour gradient onto the coefficients (outer product with the basis) and onto the view direction.
+  float3 u = make_float3(pv.x - cam.pos[0], pv.y - cam.pos[1], pv.z - cam.pos[2]);
+  const float ul = sqrtf(u.x * u.x + u.y * u.y + u.z * u.z), iul = 1.f / ul;
+  const float3 v = make_float3(u.x * iul, u.y * iul, u.z * iul);
+  sh_basis<DEG>(v, active, basis);
+  sg.vc = make_float3(g[5], g[6], g[7]);
+  float w[K];
+  w[0] = 0.f;
+  const int kact = (active + 1) * (active + 1);
+#pragma unroll
+  for (int k = 1; k < K; k++) {
+    w[k] = 0.f;
+    if (k < kact) {
+      const size_t o = (size_t)((k - 1) * 3) * cap + i;
+      w[k] = sh_hi[o] * sg.vc.x + sh_hi[o + cap] * sg.vc.y + sh_hi[o + 2 * cap] * sg.vc.z;
+    }
+  }
+  const float3 v_v = sh_dir_grad<DEG>(v, w);
+  const float vdot = v.x * v_v.x + v.y * v_v.y + v.z * v_v.z;
+  sg.pg.pos = make_float3((v_v.x - v.x * vdot) * iul, (v_v.y - v.y * vdot) * iul, (v_v.z - v.z * vdot) * iul);
+  sg.pg.op = g[8] * pr.comp_floor * pr.sig * (1.f - pr.sig);
+  geometry_backward(g, pr, cam, qv, lsv, sg.pg);
+  const ParamGrad& p = sg.pg;
+  const bool ok = isfinite(p.pos.x) && isfinite(p.pos.y) && isfinite(p.pos.z) && isfinite(p.op) && isfinite(p.ls.x) && isfinite(p.ls.y) && isfinite(p.ls.z) &&
+                  isfinite(p.q.x + p.q.y + p.q.z + p.q.w);
+  if (!ok) { sg.pg.pos = make_float3(0.f, 0.f, 0.f); sg.pg.op = 0.f; sg.pg.q = make_float4(0.f, 0.f, 0.f, 0.f); sg.pg.ls = make_float3(0.f, 0.f, 0.f); }
+  (void)sh_dc;
+}
+
+// ---- Adam ----
+struct AdamConsts { float b1, b2, eps, bc1, bc2, d1, d2, drift; bool catch_up; };
+
+__device__ __forceinline__ AdamConsts adam_consts(const B2kOptim& op, float skipped) {
+  AdamConsts a;
+  a.b1 = op.beta1; a.b2 = op.beta2; a.eps = op.eps;
+  a.bc1 = 1.f / (1.f - powf(op.beta1, (float)op.t)); a.bc2 = 1.f / (1.f - powf(op.beta2, (float)op.t));
+  a.d1 = 1.f; a.d2 = 1.f; a.drift = 0.f; a.catch_up = skipped > 0.f;
+  if (a.catch_up) {   // closed form of the zero-gradient steps a lazily updated splat missed (optim.cu:299-313)
+    a.d1 = powf(op.beta1, skipped); a.d2 = powf(op.beta2, skipped);
+    const float r = op.beta1 / sqrtf(op.beta2);
+    a.drift = r * (1.f - powf(r, skipped)) / (1.f - r);
+  }
+  return a;
+}
+__device__ __forceinline__ void adam1(float& p, float& m, float& v, float g, float lr, const AdamConsts& a) {
+  if (a.catch_up) { p -= lr * a.drift * (m * a.bc1) / (sqrtf(v * a.bc2) + a.eps); m *= a.d1; v *= a.d2; }
+  m = a.b1 * m + (1.f - a.b1) * g;
+  v = a.b2 * v + (1.f - a.b2) * g * g;
+  p -= lr * (m * a.bc1) / (sqrtf(v * a.bc2) + a.eps);
+}
+__device__ __forceinline__ void adam4(float4& p, float4& m, float4& v, float4 g, float4 lr, const AdamConsts& a) {
+  adam1(p.x, m.x, v.x, g.x, lr.x, a); adam1(p.y, m.y, v.y, g.y, lr.y, a); adam1(p.z, m.z, v.z, g.z, lr.z, a); adam1(p.w, m.w, v.w, g.w, lr.w, a);
+}
+
+// lowbias32 integer hash and the counter-based uniform / normal draws of the reference's per-step noise
+// (src/gpu/util.cuh:103-116), restated so a seeded run reproduces the same perturbations.
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) { x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16; return x; }
+__device__ __forceinline__ float hash_uniform(uint32_t a, uint32_t b, uint32_t c) {
+  const uint32_t h = hash_u32(a * 0x9E3779B1U ^ hash_u32(b * 0x85EBCA77U ^ hash_u32(c * 0xC2B2AE3DU)));
+  return (float)(h >> 8) * (1.0f / 16777216.0f);
+}
+__device__ __forceinline__ float hash_normal(uint32_t a, uint32_t b, uint32_t c) {
+  const float u1 = fmaxf(hash_uniform(a, b, c), 1e-7f), u2 = hash_uniform(a, b, c + 0x1234567U);
+  return sqrtf(-2.f * __logf(u1)) * __cosf(6.28318530718f * u2);
+}
+
+struct ModelPtrs {
+  float4 *pos_op, *quat, *lscale, *m_pos, *v_pos, *m_q, *v_q, *m_ls, *v_ls;
+  float *sh_dc, *sh_hi, *m_sh_dc, *m_sh_hi, *v_sh;
+  uint32_t* last_step;
+  size_t cap;
+};
+
+// Update of one splat. g_sh(k, ch) yields the SH gradient lane; gsq is the mean squared SH gradient.
+template <int DEG, class ShGrad>
+__device__ __forceinline__ void adam_update(int i, const ModelPtrs& mp, const B2kOptim& op, const ParamGrad& pg, float gsq, ShGrad g_sh, bool visible) {
+  constexpr int K = (DEG + 1) * (DEG + 1);
+  float skipped = 0.f;
+  if (op.sparse) {
+    const uint32_t ls = mp.last_step[i];
+    skipped = ls == 0u ? 0.f : fmaxf((float)op.t - (float)ls - 1.f, 0.f);
+    mp.last_step[i] = (uint32_t)op.t;
+  }
+  const AdamConsts a = adam_consts(op, skipped);
+  float4 po = mp.pos_op[i];
+  {
+    float4 m = mp.m_pos[i], v = mp.v_pos[i];
+    adam4(po, m, v, make_float4(pg.pos.x, pg.pos.y, pg.pos.z, pg.op), make_float4(op.lr_mean, op.lr_mean, op.lr_mean, op.lr_opac), a);
+    mp.m_pos[i] = m; mp.v_pos[i] = v;
+  }
+  {
+    float4 q = mp.quat[i], m = mp.m_q[i], v = mp.v_q[i];
+    adam4(q, m, v, pg.q, make_float4(op.lr_rot, op.lr_rot, op.lr_rot, op.lr_rot), a);
+    mp.m_q[i] = m; mp.v_q[i] = v; mp.quat[i] = q;
+  }
+  float4 ls = mp.lscale[i];
+  {
+    float4 m = mp.m_ls[i], v = mp.v_ls[i];
+    const float keep = ls.w;
+    adam4(ls, m, v, make_float4(pg.ls.x, pg.ls.y, pg.ls.z, 0.f), make_float4(op.lr_scale, op.lr_scale, op.lr_scale, 0.f), a);
+    ls.w = keep; m.w = 0.f; v.w = 0.f;   // the floor lane is a frozen constant
+    mp.m_ls[i] = m; mp.v_ls[i] = v; mp.lscale[i] = ls;
+  }
+  {
+    // Adam-mini: one second moment per splat, the EMA of the mean squared SH gradient (optim.cu:337-345).
+    const float v_old = mp.v_sh[i] * a.d2;
+    const float denom_old = a.catch_up ? a.drift * a.bc1 / (sqrtf(v_old * a.bc2) + a.eps) : 0.f;
+    const float v = a.b2 * v_old + (1.f - a.b2) * gsq;
+    mp.v_sh[i] = v;
+    const float denom = a.bc1 / (sqrtf(v * a.bc2) + a.eps);
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+      const float lrk = k == 0 ? op.lr_dc : op.lr_sh_rest;
+#pragma unroll
+      for (int ch = 0; ch < 3; ch++) {
+        float* pp = k == 0 ? mp.sh_dc + (size_t)ch * mp.cap + i : mp.sh_hi + (size_t)((k - 1) * 3 + ch) * mp.cap + i;
+        float* pm = k == 0 ? mp.m_sh_dc + (size_t)ch * mp.cap + i : mp.m_sh_hi + (size_t)((k - 1) * 3 + ch) * mp.cap + i;
+        float m_old = *pm, p = *pp;
+        if (a.catch_up) { p -= lrk * denom_old * m_old; m_old *= a.d1; }
+        const float m = a.b1 * m_old + (1.f - a.b1) * g_sh(k, ch);
+        *pm = m;
+        *pp = p - lrk * denom * m;
+      }
+    }
+  }
+  // MCMC noise on the means, strongest for near-transparent splats (optim.cu:363-376).
+  if (op.noise_weight > 0.f && visible) {
+    const float sig = 1.f / (1.f + __expf(-po.w));
+    const float f2 = ls.w * ls.w;
+    const float3 s2 = make_float3(__expf(2.f * ls.x), __expf(2.f * ls.y), __expf(2.f * ls.z));
+    const float comp = ls.w > 0.f ? sqrtf((s2.x * s2.y * s2.z) / ((s2.x + f2) * (s2.y + f2) * (s2.z + f2))) : 1.f;
+    const float o = fminf(fmaxf(sig * comp, 0.f), 1.f);
+    const float w = fminf(fmaxf(powf(1.f - o, 150.f), 0.f), 1.f) * op.noise_weight;
+    if (w > 0.f) {
+      const uint32_t s = op.seed ^ (op.step * 0x9E3779B9u);
+      const float cl = op.noise_clamp;
+      po.x += fminf(fmaxf(hash_normal(s, (uint32_t)i, 0u) * w, -cl), cl);
+      po.y += fminf(fmaxf(hash_normal(s, (uint32_t)i, 1u) * w, -cl), cl);
+      po.z += fminf(fmaxf(hash_normal(s, (uint32_t)i, 2u) * w, -cl), cl);
+    }
+  }
+  mp.pos_op[i] = po;
+}
+
+template <int DEG>
+__global__ void __launch_bounds__(OPT_BLOCK) optim_fused_kernel(int n, ModelPtrs mp, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
+                                                                const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
+                                                                float* __restrict__ vis_count, CamDev cam, B2kOptim op) {
+  constexpr int K = (DEG + 1) * (DEG + 1);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  SplatGrad sg; float basis[K];
+  const int active = op.active_sh_degree < DEG ? (op.active_sh_degree < 0 ? 0 : op.active_sh_degree) : DEG;
+  splat_gradient<DEG>(i, mp.cap, mp.pos_op, mp.quat, mp.lscale, mp.sh_dc, mp.sh_hi, v_splat, vis_flag, tile_count, refine_norm, vis_count, cam, active,
+                      (const float4*)op.pos_override, (const float4*)op.quat_override, (const float4*)op.lscale_override, sg, basis);
+  if (op.grad_out) {
+    if (op.sparse && !sg.any) return;
+    float* o = op.grad_out + (size_t)i * (11 + K * 3);
+    o[0] = sg.pg.pos.x; o[1] = sg.pg.pos.y; o[2] = sg.pg.pos.z; o[3] = sg.pg.op;
+    o[4] = sg.pg.q.x; o[5] = sg.pg.q.y; o[6] = sg.pg.q.z; o[7] = sg.pg.q.w; o[8] = sg.pg.ls.x; o[9] = sg.pg.ls.y; o[10] = sg.pg.ls.z;
+#pragma unroll
+    for (int k = 0; k < K; k++) { o[11 + k * 3] = basis[k] * sg.vc.x; o[12 + k * 3] = basis[k] * sg.vc.y; o[13 + k * 3] = basis[k] * sg.vc.z; }
+    return;
+  }
+  if (op.sparse && !sg.any) return;
+  float bsq = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; k++) bsq += basis[k] * basis[k];
+  const float gsq = bsq * (sg.vc.x * sg.vc.x + sg.vc.y * sg.vc.y + sg.vc.z * sg.vc.z) * (1.f / (float)(K * 3));
+  const float3 vc = sg.vc;
+  adam_update<DEG>(i, mp, op, sg.pg, gsq, [&](int k, int ch) { return basis[k] * (ch == 0 ? vc.x : (ch == 1 ? vc.y : vc.z)); }, sg.visible);
+}
+
+template <int DEG>
+__global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
+                                                             const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
+                                                             float* __restrict__ vis_count, CamDev cam, B2kOptim op, float* __restrict__ grad) {
+  constexpr int K = (DEG + 1) * (DEG + 1);
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  SplatGrad sg; float basis[K];
+  const int active = op.active_sh_degree < DEG ? (op.active_sh_degree < 0 ? 0 : op.active_sh_degree) : DEG;
+  splat_gradient<DEG>(i, mp.cap, mp.pos_op, mp.quat, mp.lscale, mp.sh_dc, mp.sh_hi, v_splat, vis_flag, tile_count, refine_norm, vis_count, cam, active,
+                      (const float4*)op.pos_override, (const float4*)op.quat_override, (const float4*)op.lscale_override, sg, basis);
+  if (!sg.any) return;
+  float* o = grad + (size_t)i * (11 + K * 3);
+  o[0] += sg.pg.pos.x; o[1] += sg.pg.pos.y; o[2] += sg.pg.pos.z; o[3] += sg.pg.op;
+  o[4] += sg.pg.q.x; o[5] += sg.pg.q.y; o[6] += sg.pg.q.z; o[7] += sg.pg.q.w; o[8] += sg.pg.ls.x; o[9] += sg.pg.ls.y; o[10] += sg.pg.ls.z;
+#pragma unroll
+  for (int k = 0; k < K; k++) { o[11 + k * 3] += basis[k] * sg.vc.x; o[12 + k * 3] += basis[k] * sg.vc.y; o[13 + k * 3] += basis[k] * sg.vc.z; }
+}
+
+template <int DEG>
+__global__ void __launch_bounds__(OPT_BLOCK) adam_kernel(int n, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
+  constexpr int K = (DEG + 1) * (DEG + 1), PER = 11 + 3 * K;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float* gp = grad + (size_t)i * PER;
+  float g[PER];
+  bool any = false;
+#pragma unroll
+  for (int k = 0; k < PER; k++) { g[k] = gp[k]; any = any || g[k] != 0.f; }
+  if (op.sparse && !any) return;
+#pragma unroll
+  for (int k = 0; k < PER; k++) gp[k] = 0.f;
+  ParamGrad pg;
+  pg.pos = make_float3(g[0], g[1], g[2]); pg.op = g[3]; pg.q = make_float4(g[4], g[5], g[6], g[7]); pg.ls = make_float3(g[8], g[9], g[10]);
+  float gsq = 0.f;
+#pragma unroll
+  for (int k = 11; k < PER; k++) gsq += g[k] * g[k];
+  gsq *= 1.f / (float)(K * 3);
+  adam_update<DEG>(i, mp, op, pg, gsq, [&](int k, int ch) { return g[11 + k * 3 + ch]; }, any);
+}
+
+ModelPtrs model_ptrs(const B2kModel* m) {
+  ModelPtrs p;
+  p.pos_op = (float4*)m->pos_op; p.quat = (float4*)m->quat; p.lscale = (float4*)m->lscale;
+  p.m_pos = (float4*)m->m_pos_op; p.v_pos = (float4*)m->v_pos_op; p.m_q = (float4*)m->m_quat; p.v_q = (float4*)m->v_quat;
+  p.m_ls = (float4*)m->m_lscale; p.v_ls = (float4*)m->v_lscale;
+  p.sh_dc = m->sh_dc; p.sh_hi = m->sh_hi; p.m_sh_dc = m->m_sh_dc; p.m_sh_hi = m->m_sh_hi; p.v_sh = m->v_sh; p.last_step = m->last_step; p.cap = (size_t)m->cap;
+  return p;
+}
+
+bool has_moments(const B2kModel* m) {
+  return m->m_pos_op && m->v_pos_op && m->m_quat && m->v_quat && m->m_lscale && m->v_lscale && m->m_sh_dc && m->v_sh && m->last_step && (m->degree == 0 || m->m_sh_hi);
+}
+
+__global__ void min_scale_kernel(int n, const float4* __restrict__ pos, float4* __restrict__ ls, const float* __restrict__ cam_pos, const float* __restrict__ cam_focal, int n_cams) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 p = pos[i];
+  float best = INFINITY;
+  for (int c = 0; c < n_cams; c++) {
+    const float dx = p.x - cam_pos[c * 3], dy = p.y - cam_pos[c * 3 + 1], dz = p.z - cam_pos[c * 3 + 2];
+    best = fminf(best, sqrtf(dx * dx + dy * dy + dz * dz) / fmaxf(cam_focal[c], 1e-6f));
+  }
+  float4 l = ls[i]; l.w = sqrtf(0.1f) * best; ls[i] = l;
+}
+
+__global__ void pack_rgba8_kernel(int n, const float4* __restrict__ img, uint32_t* __restrict__ out, int alpha_override) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 v = img[i];
+  auto q = [](float x) { return (uint32_t)fminf(fmaxf(x * 255.f + 0.5f, 0.f), 255.f); };
+  const uint32_t a = alpha_override >= 0 ? (uint32_t)alpha_override : q(v.w);
+  const uint32_t r = min(q(v.x), a), g = min(q(v.y), a), b = min(q(v.z), a);
+  out[i] = r | (g << 8) | (b << 16) | (a << 24);
+}
+
+}  // namespace
+}  // namespace b2k
+
+using namespace b2k;
+
+#define B2K_DISPATCH_DEG(deg, CALL) \
+  switch (deg) { case 0: { constexpr int D = 0; CALL; } break; case 1: { constexpr int D = 1; CALL; } break; case 2: { constexpr int D = 2; CALL; } break; \
+                 case 3: { constexpr int D = 3; CALL; } break; default: { constexpr int D = 4; CALL; } break; }
+
+static int check_optim_args(const B2kCtx* c, const B2kModel* m, const B2kOptim* op) {
+  B2K_REQUIRE(c && m && op && m->n >= 0 && m->cap >= m->n && m->degree >= 0 && m->degree <= 4);
+  B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi));
+  B2K_REQUIRE(c->v_splat && c->vis_flag && c->tile_count);
+  if (c->n_cap < m->n) return B2K_ERR_CAPACITY;
+  return B2K_OK;
+}
+
+extern "C" int b2k_optim_fused(const B2kCtx* c, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, b2k_stream_t stream) {
+  int st = check_optim_args(c, m, op);
+  if (st) return st;
+  B2K_REQUIRE(cam);
+  if (m->n == 0) return B2K_OK;
+  if (!op->grad_out) B2K_REQUIRE(has_moments(m) && op->t >= 1);
+  const CamDev cd = to_camdev(*cam);
+  const ModelPtrs mp = model_ptrs(m);
+  B2K_DISPATCH_DEG(m->degree, (optim_fused_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(
+      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op)));
+  return check_launch();
+}
+
+extern "C" int b2k_proj_bwd(const B2kCtx* c, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, float* grad, b2k_stream_t stream) {
+  int st = check_optim_args(c, m, op);
+  if (st) return st;
+  B2K_REQUIRE(cam && grad);
+  if (m->n == 0) return B2K_OK;
+  const CamDev cd = to_camdev(*cam);
+  const ModelPtrs mp = model_ptrs(m);
+  B2K_DISPATCH_DEG(m->degree, (proj_bwd_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(
+      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, grad)));
+  return check_launch();
+}
+
+extern "C" int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t stream) {
+  B2K_REQUIRE(m && op && grad && m->n >= 0 && m->cap >= m->n && m->degree >= 0 && m->degree <= 4);
+  B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi) && has_moments(m) && op->t >= 1);
+  if (m->n == 0) return B2K_OK;
+  const ModelPtrs mp = model_ptrs(m);
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(m->n, mp, *op, grad)));
+  return check_launch();
+}
+
+extern "C" int b2k_min_scale(const B2kModel* m, const float* cam_pos, const float* cam_focal, int32_t n_cams, b2k_stream_t stream) {
+  B2K_REQUIRE(m && m->pos_op && m->lscale && cam_pos && cam_focal && n_cams > 0 && m->n >= 0);
+  if (m->n == 0) return B2K_OK;
+  min_scale_kernel<<<div_up(m->n, 256), 256, 0, (cudaStream_t)stream>>>(m->n, (const float4*)m->pos_op, (float4*)m->lscale, cam_pos, cam_focal, n_cams);
+  return check_launch();
+}
+
+extern "C" int b2k_pack_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, int32_t alpha_override, b2k_stream_t stream) {
+  B2K_REQUIRE(rgba && out && n_pixels >= 0 && alpha_override <= 255);
+  if (n_pixels == 0) return B2K_OK;
+  pack_rgba8_kernel<<<div_up(n_pixels, 256), 256, 0, (cudaStream_t)stream>>>(n_pixels, (const float4*)rgba, out, alpha_override);
+  return check_launch();
+}

@@ -1,0 +1,133 @@
+// Projection stage: EWA projection with the 3D-filter floor, SH colour, exact tile count and the depth sort key, one
+// pass over the splats. Reference semantics: project_kernel (src/gpu/project.cu:9-84) and depth_keys_kernel
+// (src/gpu/binning.cu:10-15), fused.
+//
+// HBM-bound stream: per splat 48 B of float4 parameters + 12 K B of planar SH in, 48 B of records + 12 B of
+// count / key / index out. One thread per splat; the three float4 loads are 128-bit and coalesced, the planar SH
+// lanes are coalesced across the warp.
+#include "common.cuh"
+#include "sh.cuh"
+
+namespace b2k {
+
+int g_last_cuda_error = 0;
+int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return B2K_ERR_CUDA; }
+  return B2K_OK;
+}
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NUM_SMS_HINT;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = NUM_SMS_HINT;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+namespace {
+
+constexpr int PROJ_BLOCK = 256;
+
+template <int DEG>
+__global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
+    int n, size_t cap, const float4* __restrict__ pos_op, const float4* __restrict__ quat, const float4* __restrict__ lscale,
+    const float* __restrict__ sh_dc, const float* __restrict__ sh_hi, CamDev cam, int active, int tiles_x, int tiles_y,
+    float4* __restrict__ proj0, float4* __restrict__ proj1, float4* __restrict__ proj2, uint32_t* __restrict__ tile_count,
+    uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 po = pos_op[i], q = quat[i], ls = lscale[i];
+  Proj pr;
+  uint32_t hits = 0;
+  uint32_t key = 0xFFFFFFFFu;
+  if (project_one(po, q, ls, cam, pr)) {
+    const TileRec rec{pr.mx, pr.my, pr.c00, pr.c01, pr.c11, pr.power};
+    TileBox bb;
+    float ms = 0.f;
+    if (tile_box(rec, cam.W, cam.H, tiles_x, tiles_y, bb)) {
+      for (int ty = bb.min_y; ty < bb.max_y; ty++)
+        for (int tx = bb.min_x; tx < bb.max_x; tx++) hits += tile_hit(tx, ty, rec) ? 1u : 0u;
+      const float detc = pr.c00 * pr.c11 - pr.c01 * pr.c01;
+      const float ex = sqrtf(2.f * pr.power * pr.c11 / detc), ey = sqrtf(2.f * pr.power * pr.c00 / detc);
+      ms = fmaxf(ex / (float)cam.W, ey / (float)cam.H);
+      if (max_screen) max_screen[i] = fmaxf(max_screen[i], ms);
+    }
+    proj0[i] = make_float4(pr.mx, pr.my, pr.c00, pr.c01);
+    proj1[i] = make_float4(pr.c11, pr.opac, pr.mean_c.z, pr.power);
+    if (hits) {
+      key = __float_as_uint(pr.mean_c.z);
+      // Colour from SH along the direction camera -> splat (+0.5, clamped to +-100 as in project.cu:52-55).
+      float3 v = make_float3(po.x - cam.pos[0], po.y - cam.pos[1], po.z - cam.pos[2]);
+      const float inv = 1.f / fmaxf(sqrtf(v.x * v.x + v.y * v.y + v.z * v.z), 1e-12f);
+      v.x *= inv; v.y *= inv; v.z *= inv;
+      constexpr int K = (DEG + 1) * (DEG + 1);
+      float b[K];
+      sh_basis<DEG>(v, active, b);
+      float c[3];
+#pragma unroll
+      for (int ch = 0; ch < 3; ch++) c[ch] = b[0] * sh_dc[(size_t)ch * cap + i];
+      const int kact = (active + 1) * (active + 1);
+#pragma unroll
+      for (int k = 1; k < K; k++) {
+        if (k < kact) {
+#pragma unroll
+          for (int ch = 0; ch < 3; ch++) c[ch] += b[k] * sh_hi[(size_t)((k - 1) * 3 + ch) * cap + i];
+        }
+      }
+#pragma unroll
+      for (int ch = 0; ch < 3; ch++) { const float t = c[ch] + 0.5f; c[ch] = isfinite(t) ? fminf(fmaxf(t, -100.f), 100.f) : 0.f; }
+      proj2[i] = make_float4(c[0], c[1], c[2], 0.f);
+    }
+  } else {
+    proj1[i] = make_float4(0.f, 0.f, 0.f, -1.f);   // no record
+  }
+  tile_count[i] = hits;
+  depth_keys[i] = key;
+  order_in[i] = (uint32_t)i;
+}
+
+template <int DEG>
+int launch(const B2kModel* m, const CamDev& cam, const B2kRenderOpts* o, const B2kCtx* c, cudaStream_t s) {
+  const float4* pos = (const float4*)(o->pos_override ? o->pos_override : m->pos_op);
+  const float4* quat = (const float4*)(o->quat_override ? o->quat_override : m->quat);
+  const float4* lscale = (const float4*)(o->lscale_override ? o->lscale_override : m->lscale);
+  const int active = o->sh_degree < m->degree ? o->sh_degree : m->degree;
+  project_kernel<DEG><<<div_up(m->n, PROJ_BLOCK), PROJ_BLOCK, 0, s>>>(
+      m->n, (size_t)m->cap, pos, quat, lscale, m->sh_dc, m->sh_hi, cam, active < 0 ? 0 : active, c->tiles_x, c->tiles_y,
+      (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, c->depth_keys_sorted, c->order, m->max_screen);
+  return check_launch();
+}
+
+}  // namespace
+}  // namespace b2k
+
+using namespace b2k;
+
+extern "C" int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s) {
+  B2K_REQUIRE(m && cam && opts && ctx);
+  if (m->n == 0) return B2K_OK;
+  B2K_REQUIRE(m->n > 0 && m->cap >= m->n && m->pos_op && m->quat && m->lscale && m->sh_dc);
+  B2K_REQUIRE(m->degree >= 0 && m->degree <= 4 && (m->degree == 0 || m->sh_hi));
+  B2K_REQUIRE(ctx->proj0 && ctx->proj1 && ctx->proj2 && ctx->tile_count && ctx->depth_keys_sorted && ctx->order);
+  B2K_REQUIRE(cam->W == ctx->W && cam->H == ctx->H && ctx->tiles_x == div_up(ctx->W, RT_W) && ctx->tiles_y == div_up(ctx->H, RT_W));
+  if (ctx->n_cap < m->n) return B2K_ERR_CAPACITY;
+  const CamDev cd = to_camdev(*cam);
+  cudaStream_t st = (cudaStream_t)s;
+  switch (m->degree) {
+    case 0: return launch<0>(m, cd, opts, ctx, st);
+    case 1: return launch<1>(m, cd, opts, ctx, st);
+    case 2: return launch<2>(m, cd, opts, ctx, st);
+    case 3: return launch<3>(m, cd, opts, ctx, st);
+    default: return launch<4>(m, cd, opts, ctx, st);
+  }
+}
+
+static const char* kErrors[] = {"ok", "bad argument", "buffer capacity exceeded", "unsupported lane", "CUDA error",
+                                "intersection buffers overflowed"};
+extern "C" const char* b2k_error_string(int status) { return status >= 0 && status <= 5 ? kErrors[status] : "unknown status"; }
+extern "C" int b2k_last_cuda_error(void) { return g_last_cuda_error; }
+extern "C" const char* b2k_version(void) { return "b2k 0.1 (sm_100a)"; }

@@ -1,0 +1,170 @@
+/* b2k: C ABI of the B200 (sm_100a) splat render-and-backprop path.
+ *
+ * This is the drop-in boundary: every entry point takes plain structs of raw device pointers and sizes, enqueues its
+ * kernels on the caller's CUDA stream and returns an int status (0 = B2K_OK). Nothing here allocates device memory:
+ * the caller (the C++ mirror of the reference's host API under b2ctrain_b200/host/, or the ctypes wrapper) owns and
+ * sizes every buffer. Each declaration cites the reference interface it stands in for (path:line in the b2ctrain
+ * tree).
+ */
+#ifndef B2K_H
+#define B2K_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* b2k_stream_t; /* a cudaStream_t */
+
+enum {
+  B2K_OK = 0,
+  B2K_ERR_ARG = 1,          /* null pointer, bad size, bad degree */
+  B2K_ERR_CAPACITY = 2,     /* a caller-provided buffer is too small (message names it) */
+  B2K_ERR_UNSUPPORTED = 3,  /* an optional lane of the reference API that this library does not implement */
+  B2K_ERR_CUDA = 4,         /* a CUDA runtime call failed; b2k_last_cuda_error() has the code */
+  B2K_ERR_OVERFLOW = 5      /* more tile intersections than the intersection buffers hold; grow and redo the view */
+};
+
+/* CameraGPU, src/gpu/render.h:10-24 (same fields, same order). */
+typedef struct {
+  float R[9];
+  float t[3];
+  float pos[3];
+  float fx, fy, cx, cy;
+  int32_t W, H;
+  float lim_pos_x, lim_pos_y, lim_neg_x, lim_neg_y;
+} B2kCamera;
+
+/* Device buffers of Model, src/model.h:14-40. SH is planar: lane (k*3+ch) of splat i lives at sh_dc[lane*cap + i] for
+ * lanes 0..2 and at sh_hi[(lane-3)*cap + i] above (fp32; the reference's optional fp16 storage is not implemented).
+ * Moment and statistic pointers may be NULL for forward-only use. float4 buffers are passed as float*. */
+typedef struct {
+  int32_t n, cap, degree;
+  float* pos_op;  /* [cap][4] x, y, z, opacity logit */
+  float* quat;    /* [cap][4] w, x, y, z (unnormalised) */
+  float* lscale;  /* [cap][4] log sx, log sy, log sz, 3D-filter floor f */
+  float* sh_dc;   /* [3][cap] */
+  float* sh_hi;   /* [3(K-1)][cap] */
+  float *m_pos_op, *v_pos_op, *m_quat, *v_quat, *m_lscale, *v_lscale; /* Adam moments, [cap][4] each */
+  float *m_sh_dc, *m_sh_hi; /* first moments of SH, planar like the parameters */
+  float* v_sh;              /* [cap] Adam-mini second moment, one per splat */
+  float *refine_norm, *max_screen, *vis_count, *vis_weight; /* [cap] refine statistics */
+  uint32_t* last_step;      /* [cap] lazy sparse Adam bookkeeping */
+} B2kModel;
+
+/* Per-view scratch of RenderCtx, src/gpu/render.h:66-95. Names, element types and index meaning follow the
+ * reference members that its callers read directly. */
+typedef struct {
+  int32_t W, H, tiles_x, tiles_y, n_tiles, tile_bits;
+  int32_t n_cap;           /* per-splat buffers hold this many entries */
+  float* proj0;            /* [n][4] mean2d x, y, conic c00, c01 */
+  float* proj1;            /* [n][4] conic c11, opacity, view depth z, power = ln(255 opacity); power = -1: no record */
+  float* proj2;            /* [n][4] r, g, b, 0 */
+  uint32_t* tile_count;    /* [n] tiles hit */
+  uint32_t* depth_keys;    /* [n] scratch of the depth sort */
+  uint32_t* depth_keys_sorted; /* [n] b2k_project leaves the unsorted keys here; b2k_bin_sort sorts them in place */
+  uint32_t* order_in;      /* [n] scratch of the depth sort */
+  uint32_t* order;         /* [n] after b2k_project: identity; after b2k_bin_sort: splat index by depth rank (culled last) */
+  uint32_t* tile_off;      /* [n] inclusive scan of tile counts in depth order */
+  uint32_t *keys, *vals, *keys_sorted, *vals_sorted; /* [isect_cap] tile id / splat index before and after the tile sort */
+  uint64_t isect_cap;
+  uint32_t* num_isect;     /* device word: intersections of this view (may exceed isect_cap: overflow) */
+  void* sort_tmp;          /* scratch of b2k_sort_tmp_bytes() bytes */
+  uint64_t sort_tmp_bytes;
+  uint32_t* tile_ranges;   /* [n_tiles][2] start, end into vals_sorted; end shrunk by the forward when bwd_info */
+  float* out_rgba;         /* [P][4] */
+  float* out_feat;         /* [P][4] feature lanes x, y, z (zero: feature modes are not implemented), w = final transmittance */
+  float* out_depth;        /* [P] expected depth, or NULL: sum(vis z) / alpha where alpha > 0.05 else +inf (the mean-depth
+                              mode of probe_kernel, src/gpu/probe.cu:30-46, fused into the forward) */
+  uint32_t* last_idx;      /* [P] one past the last contributing sorted index */
+  float* v_splat;          /* [n][13] screen-space gradient lanes, accumulated; cleared by the optimizer */
+  uint32_t* vis_flag;      /* [n] */
+  float* v_out;            /* [P][4] dL/d(rgba) */
+  float* loss_accum;       /* [16] */
+} B2kCtx;
+
+/* RenderParams, src/gpu/render.h:29-63: the fields this path implements. */
+typedef struct {
+  float bg[3];
+  int32_t sh_degree;                /* active degree <= model degree */
+  int32_t bwd_info;
+  const float* pos_override;        /* [n][4] or NULL (render.h:42) */
+  const float* quat_override;       /* render.h:46 */
+  const float* lscale_override;     /* render.h:47 */
+} B2kRenderOpts;
+
+/* ViewGPU + LossParams, src/gpu/loss.h:7-30. */
+typedef struct {
+  const uint32_t* rgba;    /* packed RGBA8 target */
+  const uint8_t* weights;  /* per-pixel loss weight or NULL */
+  float l1_w, ssim_w;
+  float bg[3];
+  int32_t composite, mask, alpha_lane;
+  float match_alpha_weight, scale, grad_scale;
+} B2kLoss;
+
+/* OptimParams, src/gpu/optim.h:6-45: the fields this path implements. */
+typedef struct {
+  int32_t active_sh_degree;
+  int32_t t;
+  float beta1, beta2, eps;
+  float lr_mean, lr_rot, lr_scale, lr_opac, lr_dc, lr_sh_rest;
+  float noise_weight, noise_clamp;
+  uint32_t seed, step;
+  int32_t sparse;
+  const float* pos_override;
+  const float* quat_override;
+  const float* lscale_override;
+  float* grad_out;         /* [n][11+3K]: write parameter gradients and skip the update (optim.h:44) */
+} B2kOptim;
+
+/* ---- forward ---- */
+/* project_splats, src/gpu/render.h:101 (project_kernel, src/gpu/project.cu:9-84). */
+int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s);
+/* bin_and_sort, src/gpu/render.h:102 (src/gpu/binning.cu:109-145), without the host round trip: the intersection
+ * total stays on the device in ctx->num_isect and the later stages read it there. */
+int b2k_bin_sort(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
+/* The 4-byte count readback of binning.cu:125-127 as its own call: waits for the stream, returns the total and
+ * B2K_ERR_OVERFLOW when it exceeds ctx->isect_cap (the caller grows the four buffers and redoes the view). */
+int b2k_read_num_isect(const B2kCtx* ctx, b2k_stream_t s, uint32_t* total);
+/* rasterize_forward, src/gpu/render.h:103 (raster_fwd_kernel, src/gpu/raster_fwd.cu:9-71). */
+int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s);
+/* Scratch bytes b2k_bin_sort needs for n splats and isect_cap intersections (replaces RenderCtx::cub_tmp). */
+uint64_t b2k_sort_tmp_bytes(int32_t n, uint64_t isect_cap);
+
+/* ---- loss ---- */
+/* photometric_loss, src/gpu/loss.h:33 (photometric_kernel, src/gpu/loss.cu:18-195). */
+int b2k_loss_photometric(const B2kCtx* ctx, const B2kLoss* lp, b2k_stream_t s);
+/* accumulate_loss, src/gpu/loss.h:37. */
+int b2k_loss_accumulate(const B2kCtx* ctx, b2k_stream_t s);
+/* eval_metrics, src/gpu/loss.h:41 (eval_kernel, src/gpu/loss.cu:241-293). */
+int b2k_eval_metrics(const B2kCtx* ctx, const uint32_t* rgba, int32_t mask_weighted, b2k_stream_t s);
+
+/* ---- backward ---- */
+/* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). */
+int b2k_raster_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kRenderOpts* opts, b2k_stream_t s);
+/* optimizer_step, src/gpu/optim.h:50 (optim_kernel, src/gpu/optim.cu:100-378): projection backward fused with
+ * sparse Adam; consumes and clears ctx->v_splat / vis_flag. With grad_out set it writes gradients and returns. */
+int b2k_optim_fused(const B2kCtx* ctx, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, b2k_stream_t s);
+/* Data-parallel split of optimizer_step. b2k_proj_bwd: the gradient half (optim.cu:100-297) ADDING into a dense
+ * accumulator grad[n][11+3K] (the grad_out layout) so several views and, after an all-reduce, several GPUs sum;
+ * consumes and clears v_splat / vis_flag. b2k_adam: the update half (optim.cu:299-376) from that accumulator; splats
+ * whose accumulated gradient is all zero are skipped when op->sparse; clears the accumulator rows it consumed. */
+int b2k_proj_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, float* grad, b2k_stream_t s);
+int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t s);
+
+/* ---- helpers around the path ---- */
+/* min_scale_kernel, src/gpu/refine.cu:27-38: lscale.w = sqrt(0.1) * min over cameras of distance / focal. */
+int b2k_min_scale(const B2kModel* m, const float* cam_pos, const float* cam_focal, int32_t n_cams, b2k_stream_t s);
+/* pack_kernel, src/train/teacher.cu:11-17: float RGBA -> packed RGBA8 target. alpha_override < 0 keeps the image's. */
+int b2k_pack_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, int32_t alpha_override, b2k_stream_t s);
+
+const char* b2k_error_string(int status);
+int b2k_last_cuda_error(void);
+const char* b2k_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,253 @@
+"""ctypes bindings of the CPU oracle (liboracle.so) and of the reference's own CPU check (_ref/libref.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the benchmark's CPU-baseline leg, never by
+the package. Build with `make -C oracle`.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORC_REC = 16
+MX, MY, C00, C01, C11, OPAC, Z, POWER, R, G, B, EX, EY, OK, MAXSCREEN = range(15)
+
+
+class OrcCamera(C.Structure):
+    _fields_ = [("R", C.c_float * 9), ("t", C.c_float * 3), ("pos", C.c_float * 3), ("fx", C.c_float), ("fy", C.c_float),
+                ("cx", C.c_float), ("cy", C.c_float), ("W", C.c_int32), ("H", C.c_int32), ("lim_pos_x", C.c_float),
+                ("lim_pos_y", C.c_float), ("lim_neg_x", C.c_float), ("lim_neg_y", C.c_float)]
+
+
+class OrcLoss(C.Structure):
+    _fields_ = [("l1_w", C.c_float), ("ssim_w", C.c_float), ("bg", C.c_float * 3), ("composite", C.c_int32),
+                ("mask", C.c_int32), ("alpha_lane", C.c_int32), ("match_alpha_weight", C.c_float), ("scale", C.c_float),
+                ("grad_scale", C.c_float)]
+
+
+class OrcAdam(C.Structure):
+    _fields_ = [("t", C.c_int32), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float), ("lr_mean", C.c_float),
+                ("lr_rot", C.c_float), ("lr_scale", C.c_float), ("lr_opac", C.c_float), ("lr_dc", C.c_float),
+                ("lr_sh_rest", C.c_float), ("sparse", C.c_int32)]
+
+
+_lib = None
+_ref = None
+
+
+def build():
+    import subprocess
+    subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _lib = C.CDLL(path)
+        _lib.orc_loss.restype = C.c_double
+        _lib.orc_step.restype = C.c_double
+        _lib.orc_bin.restype = C.c_int64
+    return _lib
+
+
+def ref_lib():
+    """The reference's unmodified CPU check, or None when it was never built here."""
+    global _ref
+    if _ref is None:
+        path = os.path.join(_HERE, "_ref", "libref.so")
+        if not os.path.exists(path):
+            return None
+        _ref = C.CDLL(path)
+        _ref.ref_reference_loss.restype = C.c_double
+    return _ref
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _f64(a):
+    return np.ascontiguousarray(a, dtype=np.float64)
+
+
+def _u32(a):
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def camera_struct(cam):
+    """cam: dict with R[9], t[3], pos[3], fx, fy, cx, cy, W, H and the four Jacobian clamp limits."""
+    s = OrcCamera()
+    for i in range(9):
+        s.R[i] = float(cam["R"][i])
+    for i in range(3):
+        s.t[i] = float(cam["t"][i])
+        s.pos[i] = float(cam["pos"][i])
+    for k in ("fx", "fy", "cx", "cy", "lim_pos_x", "lim_pos_y", "lim_neg_x", "lim_neg_y"):
+        setattr(s, k, float(cam[k]))
+    s.W, s.H = int(cam["W"]), int(cam["H"])
+    return s
+
+
+def loss_struct(lp):
+    s = OrcLoss()
+    s.l1_w, s.ssim_w = lp.get("l1_w", 0.8), lp.get("ssim_w", -0.2)
+    for i in range(3):
+        s.bg[i] = float(lp.get("bg", (0, 0, 0))[i])
+    s.composite, s.mask, s.alpha_lane = int(lp.get("composite", 0)), int(lp.get("mask", 0)), int(lp.get("alpha_lane", 0))
+    s.match_alpha_weight, s.scale, s.grad_scale = lp.get("match_alpha_weight", 0.1), lp.get("scale", 1.0), lp.get("grad_scale", 1.0)
+    return s
+
+
+def adam_struct(op):
+    s = OrcAdam()
+    s.t = int(op.get("t", 1))
+    s.beta1, s.beta2, s.eps = op.get("beta1", 0.9), op.get("beta2", 0.999), op.get("eps", 1e-15)
+    s.lr_mean, s.lr_rot, s.lr_scale = op.get("lr_mean", 0.0), op.get("lr_rot", 2e-3), op.get("lr_scale", 5e-3)
+    s.lr_opac, s.lr_dc, s.lr_sh_rest = op.get("lr_opac", 0.012), op.get("lr_dc", 2e-3), op.get("lr_sh_rest", 2e-4)
+    s.sparse = int(op.get("sparse", 0))
+    return s
+
+
+def project(scene, cam, active_degree=None):
+    n, deg = scene["n"], scene["degree"]
+    act = deg if active_degree is None else active_degree
+    rec = np.zeros((n, ORC_REC), np.float64)
+    cs = camera_struct(cam)
+    lib().orc_project(n, deg, act, _p(_f32(scene["pos_op"])), _p(_f32(scene["quat"])), _p(_f32(scene["lscale"])),
+                      _p(_f32(scene["sh"])), C.byref(cs), _p(rec))
+    return rec
+
+
+def records_to_proj(rec):
+    """Double records -> the fp32 (proj0, proj1) pair the binning stage consumes; power = -1 marks 'no record'."""
+    ok = rec[:, OK] != 0
+    p0 = rec[:, [MX, MY, C00, C01]].astype(np.float32)
+    p1 = rec[:, [C11, OPAC, Z, POWER]].astype(np.float32)
+    p1[~ok, 3] = -1.0
+    return np.ascontiguousarray(p0), np.ascontiguousarray(p1)
+
+
+def tiles_of_record(r, W, H, max_tiles=4096):
+    tiles = np.zeros(max_tiles, np.uint32)
+    f = C.c_float
+    k = lib().orc_tiles_of_record(f(r[0]), f(r[1]), f(r[2]), f(r[3]), f(r[4]), f(r[5]), W, H, _p(tiles), max_tiles)
+    return tiles[:min(k, max_tiles)], k
+
+
+def bin_sort(p0, p1, W, H):
+    n = p0.shape[0]
+    n_tiles = ((W + 7) // 8) * ((H + 7) // 8)
+    p0, p1 = _f32(p0), _f32(p1)
+    tile_count = np.zeros(n, np.uint32)
+    ranges = np.zeros((n_tiles, 2), np.uint32)
+    total = lib().orc_bin(n, _p(p0), _p(p1), W, H, _p(tile_count), None, None, C.c_int64(0), _p(ranges))
+    vals = np.zeros(max(total, 1), np.uint32)
+    keys = np.zeros(max(total, 1), np.uint32)
+    lib().orc_bin(n, _p(p0), _p(p1), W, H, _p(tile_count), _p(vals), _p(keys), C.c_int64(total), _p(ranges))
+    return tile_count, vals[:total], keys[:total], ranges
+
+
+def raster_fwd(W, H, geo, col, vals, ranges, bg, bwd_info=True, want_depth=False):
+    P = W * H
+    geo, col = _f64(geo), _f64(col)
+    ranges = np.array(ranges, dtype=np.uint32, copy=True)
+    rgba = np.zeros((P, 4)); T = np.zeros(P); last = np.zeros(P, np.uint32)
+    depth = np.zeros(P) if want_depth else None
+    bgd = _f64(bg)
+    vals = _u32(vals) if len(vals) else np.zeros(1, np.uint32)
+    lib().orc_raster_fwd(W, H, _p(geo), _p(col), _p(vals), _p(ranges), _p(bgd), int(bwd_info), _p(rgba), _p(T), _p(last), _p(depth))
+    return rgba, T, last, ranges, depth
+
+
+def loss(W, H, pred, gt, weights, lp, want_grad=True):
+    pred = _f64(pred)
+    v_out = np.zeros((W * H, 4)) if want_grad else None
+    ls = loss_struct(lp)
+    w = None if weights is None else np.ascontiguousarray(weights, dtype=np.uint8)
+    val = lib().orc_loss(W, H, _p(pred), _p(_u32(gt)), _p(w), C.byref(ls), _p(v_out))
+    return val, v_out
+
+
+def raster_bwd(n, W, H, geo, col, vals, ranges, bg, rgba, T, last, v_out):
+    v_splat = np.zeros((n, 13)); vis = np.zeros(n, np.uint32); visw = np.zeros(n)
+    vals = _u32(vals) if len(vals) else np.zeros(1, np.uint32)
+    lib().orc_raster_bwd(n, W, H, _p(_f64(geo)), _p(_f64(col)), _p(vals), _p(_u32(ranges)), _p(_f64(bg)), _p(_f64(rgba)),
+                         _p(_f64(T)), _p(_u32(last)), _p(_f64(v_out)), _p(v_splat), _p(vis), _p(visw))
+    return v_splat, vis, visw
+
+
+def proj_bwd(scene, cam, v_splat, vis, tile_count, active_degree=None):
+    n, deg = scene["n"], scene["degree"]
+    act = deg if active_degree is None else active_degree
+    K = (deg + 1) ** 2
+    grad = np.zeros((n, 11 + 3 * K))
+    cs = camera_struct(cam)
+    lib().orc_proj_bwd(n, deg, act, _p(_f32(scene["pos_op"])), _p(_f32(scene["quat"])), _p(_f32(scene["lscale"])),
+                       _p(_f32(scene["sh"])), C.byref(cs), _p(_f64(v_splat)), _p(_u32(vis)), _p(_u32(tile_count)), _p(grad))
+    return grad
+
+
+def adam(state, grad, active, op, degree):
+    """state: dict of fp32 arrays pos_op, quat, lscale, sh[n][K][3], m_pos, v_pos, m_q, v_q, m_ls, v_ls, m_sh, v_sh and
+    uint32 last_step; updated in place (arrays must be C-contiguous and of the right dtype)."""
+    n = state["pos_op"].shape[0]
+    s = adam_struct(op)
+    act = np.ascontiguousarray(active, dtype=np.uint8)
+    keys = ["pos_op", "quat", "lscale", "sh", "m_pos", "v_pos", "m_q", "v_q", "m_ls", "v_ls", "m_sh", "v_sh"]
+    for k in keys:
+        assert state[k].dtype == np.float32 and state[k].flags["C_CONTIGUOUS"], k
+    assert state["last_step"].dtype == np.uint32
+    lib().orc_adam(n, degree, *[_p(state[k]) for k in keys], _p(state["last_step"]), _p(_f64(grad)), _p(act), C.byref(s))
+
+
+def min_scale(pos_op, lscale, cam_pos, cam_focal):
+    ls = np.array(lscale, dtype=np.float32, copy=True)
+    cp, cf = _f32(cam_pos), _f32(cam_focal)
+    lib().orc_min_scale(pos_op.shape[0], _p(_f32(pos_op)), _p(ls), _p(cp), _p(cf), len(cf))
+    return ls
+
+
+def step(scene, cam, bg, gt, weights, lp, backward=True, want_image=False):
+    """Pure double chain: forward + loss (+ analytic backward). Returns dict(loss, grad, rgba, counters)."""
+    n, deg = scene["n"], scene["degree"]
+    K = (deg + 1) ** 2
+    W, H = cam["W"], cam["H"]
+    rgba = np.zeros((W * H, 4)) if want_image else None
+    grad = np.zeros((n, 11 + 3 * K)) if backward else None
+    counters = np.zeros(4, np.int64)
+    cs, ls = camera_struct(cam), loss_struct(lp)
+    w = None if weights is None else np.ascontiguousarray(weights, dtype=np.uint8)
+    g = None if gt is None else _u32(gt)
+    val = lib().orc_step(n, deg, scene.get("active_degree", deg), _p(_f32(scene["pos_op"])), _p(_f32(scene["quat"])),
+                         _p(_f32(scene["lscale"])), _p(_f32(scene["sh"])), C.byref(cs), _p(_f64(bg)), _p(g), _p(w),
+                         C.byref(ls), int(backward), _p(rgba), _p(grad), _p(counters))
+    return dict(loss=val, grad=grad, rgba=rgba, V=int(counters[0]), I=int(counters[1]), I_b=int(counters[2]))
+
+
+def reference_loss(scene, cam, bg, gt, weights, lp):
+    """The reference's own `reference_loss` (no floor, SH degree <= 3)."""
+    r = ref_lib()
+    if r is None:
+        return None
+    n, deg = scene["n"], scene["degree"]
+    assert deg <= 3 and not np.any(scene["lscale"][:, 3] != 0), "reference_loss has no floor and stops at SH degree 3"
+    pos = _f32(scene["pos_op"][:, :3]); opac = _f32(scene["pos_op"][:, 3]); ls = _f32(scene["lscale"][:, :3])
+    intr = np.array([cam["fx"], cam["fy"], cam["cx"], cam["cy"]], np.float32)
+    w = None if weights is None else np.ascontiguousarray(weights, dtype=np.uint8)
+    d = C.c_double
+    return r.ref_reference_loss(n, deg, _p(pos), _p(ls), _p(_f32(scene["quat"])), _p(opac), _p(_f32(scene["sh"])),
+                                int(cam["W"]), int(cam["H"]), _p(intr), _p(_f32(cam["R"])), _p(_f32(cam["t"])),
+                                _p(_f32(cam["pos"])), _p(_f64(bg)), int(lp.get("composite", 0)), int(lp.get("mask", 0)),
+                                int(lp.get("alpha_lane", 0)), d(lp.get("l1_w", 0.8)), d(lp.get("ssim_w", -0.2)),
+                                d(lp.get("match_alpha_weight", 0.1)), d(lp.get("scale", 1.0)), _p(_u32(gt)), _p(w))
+
+
+def num_threads():
+    return int(lib().orc_num_threads())
