@@ -48,7 +48,7 @@ def build(force=False, verbose=False, ptxas_info=False):
             sys.stderr.write(f"--- {src} ---\n{out}\n")
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.run([nvcc(), "-shared", "-o", LIB, *objs, "-lcudart"], check=True)
+    subprocess.run([nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs], check=True)
     return LIB
 
 

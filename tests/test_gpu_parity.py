@@ -1,0 +1,320 @@
+"""GPU parity tests: every CUDA stage, called through the C ABI, against the CPU oracle on the same seeded inputs,
+and the whole chain against the golden outputs of the reference's own CPU check."""
+import numpy as np
+import pytest
+
+from b2ctrain_b200 import scenes
+from oracle import orc
+from tests.util import (TOL_ADAM_REL, TOL_GRAD_REL_L2, TOL_IMAGE_ABS, TOL_LOSS_REL, TOL_RECORD_REL, Harness, check_against_fd,
+                        load_gradcheck, rel_l2)
+
+pytestmark = pytest.mark.gpu
+
+
+def small_scene(n=4000, degree=3, seed=21, W=160, H=120, floor=True):
+    scene = scenes.make_splats(n, degree, seed, log_scale=(-3.2, 0.5))
+    cam = scenes.look_at_camera(scenes.orbit_eye(3.0, 25.0, 10.0), W, H, float(H))
+    if floor:
+        scene = scenes.floor_for_cameras(scene, [cam])
+    return scene, cam
+
+
+def gpu_records(h):
+    n = h.model.n
+    return h.ctx.proj0[:n].cpu().numpy(), h.ctx.proj1[:n].cpu().numpy(), h.ctx.proj2[:n].cpu().numpy(), h.u32(h.ctx.tile_count, n)
+
+
+@pytest.mark.parametrize("degree", [0, 1, 2, 3, 4])
+def test_projection_records(degree):
+    scene, cam = small_scene(degree=degree)
+    h = Harness(scene, cam)
+    h.api.project_splats(h.ctx, h.model, h.rp)
+    p0, p1, p2, tc = gpu_records(h)
+    rec = orc.project(scene, cam)
+    ok_o = rec[:, orc.OK] != 0
+    ok_g = p1[:, 3] > -0.5
+    # Cull decisions may only differ where the oracle itself sits on a threshold.
+    differ = np.nonzero(ok_o != ok_g)[0]
+    assert len(differ) <= 2 and all(abs(rec[i, orc.OPAC] - 1 / 255) < 1e-6 or not ok_o[i] for i in differ)
+    both = ok_o & ok_g
+    assert both.sum() > 0.5 * scene["n"]
+    want = np.concatenate([rec[both][:, [orc.MX, orc.MY, orc.C00, orc.C01]], rec[both][:, [orc.C11, orc.OPAC, orc.Z, orc.POWER]]], 1)
+    got = np.concatenate([p0[both], p1[both]], 1).astype(np.float64)
+    # Conic entries lose relative precision with the conditioning of the 2x2 inverse: scale their tolerance by the
+    # largest conic entry of the splat.
+    cmax = np.abs(want[:, [2, 3, 4]]).max(1, keepdims=True)
+    scale = np.abs(want) + np.array([1.0, 1.0, 0, 0, 0, 0, 0, 1.0])[None, :]
+    scale[:, [2, 3, 4]] = cmax
+    assert np.max(np.abs(got - want) / scale) <= TOL_RECORD_REL
+    vis = both & (tc > 0)
+    assert np.max(np.abs(p2[vis][:, :3] - rec[vis][:, orc.R:orc.B + 1])) <= 5e-6
+
+
+def test_binning_bit_exact():
+    """Tile sets, tile counts, sorted fragment order and tile ranges are bit-exact functions of the fp32 records."""
+    scene, cam = small_scene(n=6000)
+    h = Harness(scene, cam)
+    h.api.project_splats(h.ctx, h.model, h.rp)
+    h.api.bin_and_sort(h.ctx, h.model)
+    p0, p1, _, tc = gpu_records(h)
+    tc_o, vals_o, keys_o, ranges_o = orc.bin_sort(p0, p1, cam["W"], cam["H"])
+    assert np.array_equal(tc, tc_o)
+    assert h.ctx.num_isect == len(vals_o) and len(vals_o) > 10000
+    assert np.array_equal(h.u32(h.ctx.vals_sorted, len(vals_o)), vals_o)
+    assert np.array_equal(h.u32(h.ctx.keys_sorted, len(vals_o)), keys_o)
+    assert np.array_equal(h.u32(h.ctx.tile_ranges).reshape(-1, 2), ranges_o)
+    order = h.u32(h.ctx.order, scene["n"])
+    zb = np.where(tc > 0, p1[:, 2].view(np.uint32), 0xFFFFFFFF).astype(np.uint64)
+    want_order = np.argsort(zb * np.uint64(1 << 32) + np.arange(scene["n"], dtype=np.uint64), kind="stable")
+    assert np.array_equal(order, want_order.astype(np.uint32))
+
+
+def test_binning_depth_ties_and_big_splats():
+    scene, cam = small_scene(n=3000, degree=0)
+    scene["lscale"][:40, :3] = -1.0                       # splats spanning hundreds of tiles
+    scene["pos_op"][100:200, :3] = scene["pos_op"][100, :3]   # identical depth: the index breaks the tie
+    h = Harness(scene, cam)
+    h.api.project_splats(h.ctx, h.model, h.rp)
+    h.api.bin_and_sort(h.ctx, h.model)
+    p0, p1, _, tc = gpu_records(h)
+    tc_o, vals_o, keys_o, ranges_o = orc.bin_sort(p0, p1, cam["W"], cam["H"])
+    assert tc.max() > 100
+    assert np.array_equal(tc, tc_o)
+    assert np.array_equal(h.u32(h.ctx.vals_sorted, len(vals_o)), vals_o)
+    assert np.array_equal(h.u32(h.ctx.tile_ranges).reshape(-1, 2), ranges_o)
+
+
+def test_binning_overflow_grows_and_matches():
+    scene, cam = small_scene(n=6000)
+    h = Harness(scene, cam, isect_cap=1024)   # far too small: the wrapper must grow it like binning.cu:129-133
+    h.forward()
+    p0, p1, _, tc = gpu_records(h)
+    _, vals_o, _, _ = orc.bin_sort(p0, p1, cam["W"], cam["H"])
+    assert h.ctx.isect_cap >= len(vals_o) > 1024
+    assert np.array_equal(h.u32(h.ctx.vals_sorted, len(vals_o)), vals_o)
+
+
+def oracle_forward_from_gpu_records(h, scene, cam):
+    p0, p1, p2, tc = gpu_records(h)
+    geo = np.concatenate([p0, p1], 1).astype(np.float64)[:, [0, 1, 2, 3, 4, 5, 6, 7]]
+    vals = h.u32(h.ctx.vals_sorted, h.ctx.num_isect)
+    return geo, p2[:, :3].astype(np.float64), vals
+
+
+def test_forward_image_stagewise():
+    scene, cam = small_scene()
+    bg = (0.2, 0.1, 0.3)
+    h = Harness(scene, cam, bg=bg, want_depth=True)
+    h.api.project_splats(h.ctx, h.model, h.rp)
+    h.api.bin_and_sort(h.ctx, h.model)
+    ranges_before = h.u32(h.ctx.tile_ranges).reshape(-1, 2).copy()
+    h.api.rasterize_forward(h.ctx, h.rp)
+    geo, col, vals = oracle_forward_from_gpu_records(h, scene, cam)
+    rgba, T, last, ranges, depth = orc.raster_fwd(cam["W"], cam["H"], geo, col, vals, ranges_before, np.array(bg), True, want_depth=True)
+    got = h.ctx.out_rgba.cpu().numpy()
+    assert np.max(np.abs(got - rgba)) <= TOL_IMAGE_ABS
+    assert np.max(np.abs(h.ctx.out_feat.cpu().numpy()[:, 3] - T)) <= TOL_IMAGE_ABS
+    # last_idx / shrunk ranges are discrete: they may differ only at pixels sitting on a cut-off.
+    last_g = h.u32(h.ctx.last_idx)
+    assert np.mean(last_g != last) < 2e-3
+    assert np.mean(h.u32(h.ctx.tile_ranges).reshape(-1, 2)[:, 1] != ranges[:, 1]) < 1e-2
+    alpha = rgba[:, 3]
+    want_depth = np.where(alpha > 0.05, depth / np.maximum(alpha, 1e-30), np.inf)
+    got_depth = h.ctx.out_depth.cpu().numpy()
+    sure = np.abs(alpha - 0.05) > 1e-3
+    fin = sure & np.isfinite(want_depth)
+    assert np.array_equal(np.isfinite(got_depth[sure]), np.isfinite(want_depth[sure]))
+    assert np.max(np.abs(got_depth[fin] - want_depth[fin])) <= 2e-3
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_loss_kernel_stagewise(mode):
+    """The fused loss kernel on a random prediction, value and gradient, against the oracle in double."""
+    rng = np.random.Generator(np.random.PCG64(40 + mode))
+    W, H = 83, 61                                          # ragged: not a multiple of the 16-pixel tile
+    scene, cam = small_scene(n=16, W=W, H=H)
+    gt = rng.integers(0, 2 ** 32, W * H, dtype=np.uint64).astype(np.uint32)
+    wts = rng.integers(64, 256, W * H).astype(np.uint8) if mode != 2 else None
+    lp = dict(l1_w=0.8, ssim_w=-0.2, bg=(0.2, 0.1, 0.3), composite=mode == 0, mask=mode == 1, alpha_lane=mode == 0,
+              match_alpha_weight=0.3, scale=1.7 if mode == 1 else 1.0, grad_scale=1.0)
+    h = Harness(scene, cam, gt, wts, lp)
+    pred = rng.random((W * H, 4)).astype(np.float32)
+    pred[: W * 20] = 0.0                                   # a flat region
+    gt[: W * 20] = 0xFF000000 if mode else 0               # equal to the prediction there
+    h = Harness(scene, cam, gt, wts, lp)
+    h.ctx.out_rgba.copy_(h.torch.from_numpy(pred))
+    h.ctx.loss_accum.zero_()
+    h.api.photometric_loss(h.ctx, h.view, h.lp)
+    f32 = {k: (np.float32(v) if isinstance(v, float) else v) for k, v in lp.items()}
+    f32["bg"] = tuple(np.float32(x) for x in lp["bg"])
+    want, v_out = orc.loss(W, H, pred, gt, wts, f32)
+    got = float(h.ctx.loss_accum[0].item())
+    assert abs(got - want) <= 2e-5 * abs(want)
+    v = h.ctx.v_out.cpu().numpy()
+    assert rel_l2(v, v_out) <= 2e-4
+    assert np.max(np.abs(v - v_out)) <= 2e-3 * np.max(np.abs(v_out))
+
+
+def test_backward_stagewise():
+    """Reverse replay on the GPU's own forward state against the oracle's replay of the same state."""
+    scene, cam = small_scene()
+    rng = np.random.Generator(np.random.PCG64(9))
+    bg = (0.2, 0.1, 0.3)
+    h = Harness(scene, cam, bg=bg)
+    h.forward()
+    P = cam["W"] * cam["H"]
+    v_out = (rng.standard_normal((P, 4)) * 1e-3).astype(np.float32)
+    h.ctx.v_out.copy_(h.torch.from_numpy(v_out))
+    h.api.rasterize_backward(h.ctx, h.model, h.rp)
+    geo, col, vals = oracle_forward_from_gpu_records(h, scene, cam)
+    ranges = h.u32(h.ctx.tile_ranges).reshape(-1, 2)
+    want, vis, visw = orc.raster_bwd(scene["n"], cam["W"], cam["H"], geo, col, vals, ranges, np.array(bg), h.ctx.out_rgba.cpu().numpy(),
+                                     h.ctx.out_feat.cpu().numpy()[:, 3], h.u32(h.ctx.last_idx), v_out)
+    got = h.ctx.v_splat[: scene["n"]].cpu().numpy()
+    assert np.array_equal(h.u32(h.ctx.vis_flag, scene["n"]) != 0, vis != 0)
+    for lane in range(10):
+        assert rel_l2(got[:, lane], want[:, lane]) <= 5e-5, lane
+    assert np.all(got[:, 10:] == 0)
+    assert rel_l2(h.model.vis_weight[: scene["n"]].cpu().numpy(), visw) <= 1e-5
+
+
+@pytest.mark.parametrize("degree", [1, 3, 4])
+def test_projection_backward_stagewise(degree):
+    scene, cam = small_scene(n=3000, degree=degree)
+    rng = np.random.Generator(np.random.PCG64(12))
+    h = Harness(scene, cam)
+    h.api.project_splats(h.ctx, h.model, h.rp)
+    n = scene["n"]
+    tc = h.u32(h.ctx.tile_count, n)
+    v_splat = rng.standard_normal((n, 13)).astype(np.float32)
+    v_splat[:, 10:] = 0
+    vis = (rng.random(n) < 0.7).astype(np.uint32)
+    h.ctx.v_splat[:n].copy_(h.torch.from_numpy(v_splat))
+    h.ctx.vis_flag[:n].copy_(h.torch.from_numpy(vis.view(np.int32)))
+    K = (degree + 1) ** 2
+    grads = h.torch.zeros((n, 11 + 3 * K), dtype=h.torch.float32, device="cuda:0")
+    h.api.optimizer_step(h.ctx, h.model, h.api.OptimParams(cam, active_sh_degree=degree, grad_out=grads))
+    want = orc.proj_bwd(scene, cam, v_splat, vis, tc)
+    got = grads.cpu().numpy()
+    for lo, hi in ((0, 3), (3, 4), (4, 8), (8, 11), (11, 11 + 3 * K)):
+        assert rel_l2(got[:, lo:hi], want[:, lo:hi]) <= 2e-5, (lo, hi)
+    # the optimizer consumed and cleared the lanes
+    assert float(h.ctx.v_splat[:n][h.torch.from_numpy(vis != 0).cuda()].abs().max()) == 0.0
+    assert int(h.ctx.vis_flag[:n].abs().max()) == 0
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_full_chain_against_reference_golden(mode):
+    """Forward + loss + backward + projection backward on the reference's gradient-check scenes: loss within
+    tolerance of `reference_loss`, gradients within the reference's finite-difference rule and within 1e-4 relative
+    L2 of the analytic double oracle."""
+    scene, cam, gt, wts, lp, z = load_gradcheck(mode)
+    h = Harness(scene, cam, gt, wts, lp)
+    loss, grad = h.analytic()
+    assert abs(loss - float(z["ref_loss"])) <= TOL_LOSS_REL * abs(float(z["ref_loss"]))
+    fails, total, fails_1e4 = check_against_fd(grad, z)
+    assert fails == 0 and fails_1e4 <= 0.05 * total
+    want = orc.step(scene, cam, np.array(lp["bg"], np.float64), gt, wts, lp, backward=True)["grad"]
+    assert rel_l2(grad, want) <= TOL_GRAD_REL_L2
+
+
+def test_config0_full_chain():
+    """BASELINE config 0: 2,000 splats, SH degree 1, 64x64, target = perturbed scene rendered."""
+    z = np.load("tests/golden/config0.npz")
+    scene = scenes.make_splats(2000, 1, 1000)
+    cam = scenes.config_cameras(0)[0]
+    lp = dict(l1_w=np.float32(0.8), ssim_w=np.float32(-0.2))
+    h = Harness(scene, cam, z["gt"], None, lp)
+    loss, grad = h.analytic()
+    assert abs(loss - float(z["ref_loss"])) <= TOL_LOSS_REL * abs(float(z["ref_loss"]))
+    out = orc.step(scene, cam, np.zeros(3), z["gt"], None, lp, backward=True, want_image=True)
+    assert np.max(np.abs(h.ctx.out_rgba.cpu().numpy() - out["rgba"])) <= TOL_IMAGE_ABS
+    assert rel_l2(grad, out["grad"]) <= TOL_GRAD_REL_L2
+
+
+def test_adam_fused_and_split_match_oracle():
+    scene, cam = small_scene(n=3000, degree=2)
+    rng = np.random.Generator(np.random.PCG64(31))
+    n, K = scene["n"], 9
+    for split in (False, True):
+        h = Harness(scene, cam)
+        h.api.project_splats(h.ctx, h.model, h.rp)
+        tc = h.u32(h.ctx.tile_count, n)
+        state = None
+        for t in (1, 2, 5):   # t = 5 after 2 exercises the lazy catch-up of splats that skipped steps
+            v_splat = (rng.standard_normal((n, 13)) * 1e-2).astype(np.float32); v_splat[:, 10:] = 0
+            vis = (rng.random(n) < 0.6).astype(np.uint32)
+            h.ctx.v_splat[:n].copy_(h.torch.from_numpy(v_splat))
+            h.ctx.vis_flag[:n].copy_(h.torch.from_numpy(vis.view(np.int32)))
+            cur = h.model.download()
+            if state is None:
+                z4 = lambda: np.zeros((n, 4), np.float32)
+                state = dict(m_pos=z4(), v_pos=z4(), m_q=z4(), v_q=z4(), m_ls=z4(), v_ls=z4(), m_sh=np.zeros((n, K, 3), np.float32),
+                             v_sh=np.zeros(n, np.float32), last_step=np.zeros(n, np.uint32))
+            state.update(pos_op=cur["pos_op"].copy(), quat=cur["quat"].copy(), lscale=cur["lscale"].copy(), sh=cur["sh"].copy())
+            grad = orc.proj_bwd(cur, cam, v_splat, vis, tc)
+            active = np.any(grad != 0, axis=1)
+            opd = dict(t=t, lr_mean=1.6e-4, sparse=1)
+            orc.adam(state, grad, active, opd, 2)
+            op = h.api.OptimParams(cam, active_sh_degree=2, t=t, lr_mean=1.6e-4, sparse=True)
+            if split:
+                g = h.torch.zeros((n, 11 + 3 * K), dtype=h.torch.float32, device="cuda:0")
+                h.api.projection_backward(h.ctx, h.model, op, g)
+                h.api.adam_step(h.model, op, g)
+                assert float(g.abs().max()) == 0.0
+            else:
+                h.api.optimizer_step(h.ctx, h.model, op)
+            got = h.model.download()
+            # fp32 bias corrections 1 - beta^t cancel (1 - 0.999^5 keeps ~1e-5 relative precision), and the catch-up
+            # multiplies that into a several-step drift: parameters are held to 2e-5 on plain steps, 1e-4 after a gap.
+            tol = 2e-5 if t <= 2 else 1e-4
+            for k in ("pos_op", "quat", "lscale", "sh"):
+                assert np.max(np.abs(got[k] - state[k]) / (np.abs(state[k]) + 1e-3)) <= tol, (split, t, k)
+            assert rel_l2(h.model.m_pos_op[:n].cpu().numpy(), state["m_pos"]) <= TOL_ADAM_REL
+            assert rel_l2(h.model.v_quat[:n].cpu().numpy(), state["v_q"]) <= TOL_ADAM_REL
+            assert rel_l2(h.model.v_sh[:n].cpu().numpy(), state["v_sh"]) <= TOL_ADAM_REL
+            assert rel_l2(h.model.sh_planar_to_host(h.model.m_sh_dc, h.model.m_sh_hi), state["m_sh"]) <= TOL_ADAM_REL
+            assert np.array_equal(h.u32(h.model.last_step, n), state["last_step"])
+            # keep the two sides in lock step: the next step starts from the GPU's parameters on both
+            state.update(m_pos=h.model.m_pos_op[:n].cpu().numpy().copy(), v_pos=h.model.v_pos_op[:n].cpu().numpy().copy(),
+                         m_q=h.model.m_quat[:n].cpu().numpy().copy(), v_q=h.model.v_quat[:n].cpu().numpy().copy(),
+                         m_ls=h.model.m_lscale[:n].cpu().numpy().copy(), v_ls=h.model.v_lscale[:n].cpu().numpy().copy(),
+                         m_sh=h.model.sh_planar_to_host(h.model.m_sh_dc, h.model.m_sh_hi).copy(), v_sh=h.model.v_sh[:n].cpu().numpy().copy())
+
+
+def test_empty_scene_and_all_culled():
+    cam = scenes.look_at_camera((0.0, 0.0, 3.0), 40, 24, 40.0)
+    scene = scenes.make_splats(16, 0, 3)
+    scene["pos_op"][:, 2] += 10.0
+    h = Harness(scene, cam, bg=(0.1, 0.2, 0.3))
+    h.forward()
+    assert h.ctx.num_isect == 0
+    img = h.ctx.out_rgba.cpu().numpy()
+    assert np.allclose(img[:, :3], [0.1, 0.2, 0.3]) and np.all(img[:, 3] == 0)
+
+
+def test_determinism_of_integer_outputs():
+    scene, cam = small_scene(n=5000)
+    outs = []
+    for _ in range(2):
+        h = Harness(scene, cam)
+        h.forward()
+        outs.append((h.u32(h.ctx.vals_sorted, h.ctx.num_isect).copy(), h.u32(h.ctx.tile_ranges).copy(), h.u32(h.ctx.last_idx).copy(),
+                     h.ctx.out_rgba.cpu().numpy().copy()))
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
+
+
+def test_min_scale_and_pack():
+    scene, cam = small_scene(n=500, floor=False)
+    h = Harness(scene, cam)
+    cams = [scenes.look_at_camera(scenes.orbit_eye(4, a, 10), 64, 64, 64.0) for a in (0, 90, 200)]
+    cp = h.torch.tensor(np.stack([c["pos"] for c in cams]), dtype=h.torch.float32, device="cuda:0")
+    cf = h.torch.tensor([64.0] * 3, dtype=h.torch.float32, device="cuda:0")
+    h.api.update_min_scale(h.model, cp, cf)
+    want = orc.min_scale(scene["pos_op"], scene["lscale"], cp.cpu().numpy(), cf.cpu().numpy())[:, 3]
+    assert np.allclose(h.model.lscale[:500, 3].cpu().numpy(), want, rtol=1e-5)
+    img = np.random.Generator(np.random.PCG64(1)).random((1000, 4)).astype(np.float32)
+    out = h.torch.zeros(1000, dtype=h.torch.int32, device="cuda:0")
+    h.api.pack_rgba8(h.torch.from_numpy(img).cuda(), out)
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), scenes.pack_rgba8(img))
