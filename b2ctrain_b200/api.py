@@ -40,7 +40,7 @@ class B2kModel(C.Structure):
 class B2kCtx(C.Structure):
     _fields_ = [("W", C.c_int32), ("H", C.c_int32), ("tiles_x", C.c_int32), ("tiles_y", C.c_int32), ("n_tiles", C.c_int32),
                 ("tile_bits", C.c_int32), ("n_cap", C.c_int32),
-                ("proj0", C.c_void_p), ("proj1", C.c_void_p), ("proj2", C.c_void_p), ("tile_count", C.c_void_p),
+                ("proj0", C.c_void_p), ("proj1", C.c_void_p), ("proj2", C.c_void_p), ("tile_count", C.c_void_p), ("hit_info", C.c_void_p),
                 ("depth_keys", C.c_void_p), ("depth_keys_sorted", C.c_void_p), ("order_in", C.c_void_p), ("order", C.c_void_p),
                 ("tile_off", C.c_void_p), ("keys", C.c_void_p), ("vals", C.c_void_p), ("keys_sorted", C.c_void_p),
                 ("vals_sorted", C.c_void_p), ("isect_cap", C.c_uint64), ("num_isect", C.c_void_p), ("sort_tmp", C.c_void_p),
@@ -245,6 +245,7 @@ class RenderCtx:
         if n > self.n_cap:
             self.proj0, self.proj1, self.proj2 = f32(n, 4), f32(n, 4), f32(n, 4)
             self.tile_count, self.tile_off = u32(n), u32(n)
+            self.hit_info = u32(n, 4)
             self.depth_keys, self.depth_keys_sorted, self.order_in, self.order = u32(n), u32(n), u32(n), u32(n)
             self.v_splat, self.vis_flag = f32(n, GRAD_LANES), u32(n)
             self.n_cap = n
@@ -257,7 +258,7 @@ class RenderCtx:
         self.d_num_isect = u32(4)
         if self.isect_cap == 0 or (isect_cap and isect_cap > self.isect_cap):
             self._alloc_isect(isect_cap or (1 << 22))
-        nbytes = int(lib().b2k_sort_tmp_bytes(n, self.isect_cap))
+        nbytes = int(lib().b2k_sort_tmp_bytes(self.n_cap, self.isect_cap))
         self.sort_tmp = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         return self
 
@@ -270,7 +271,7 @@ class RenderCtx:
         s = B2kCtx()
         for k in ("W", "H", "tiles_x", "tiles_y", "n_tiles", "tile_bits", "n_cap"):
             setattr(s, k, getattr(self, k))
-        for k in ("proj0", "proj1", "proj2", "tile_count", "depth_keys", "depth_keys_sorted", "order_in", "order", "tile_off", "keys",
+        for k in ("proj0", "proj1", "proj2", "tile_count", "hit_info", "depth_keys", "depth_keys_sorted", "order_in", "order", "tile_off", "keys",
                   "vals", "keys_sorted", "vals_sorted", "sort_tmp", "tile_ranges", "out_rgba", "out_feat", "out_depth", "last_idx",
                   "v_splat", "vis_flag", "v_out", "loss_accum"):
             t = getattr(self, k, None)

@@ -34,7 +34,8 @@ __device__ __forceinline__ uint32_t load_n(const uint32_t* n_ptr, uint32_t n_max
   return n < n_max ? n : n_max;
 }
 
-// Pass kernel 1: digit counts of each block's segment. hist is [RADIX][blocks].
+// Pass kernel 1: digit counts of each block's segment. hist is [RADIX][blocks]. Each lane keeps 16 keys in flight
+// (four 128-bit loads) so that a few hundred resident warps cover the HBM latency-bandwidth product.
 __global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ n_ptr, uint32_t n_max,
                                                                    int shift, uint32_t mask, uint32_t* __restrict__ hist) {
   __shared__ uint32_t s_hist[SORT_WARPS][RADIX];
@@ -46,13 +47,34 @@ __global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_
   const uint64_t begin64 = (uint64_t)blockIdx.x * len;
   const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
   const uint32_t end = (begin64 + len) < n ? (uint32_t)(begin64 + len) : n;
-  for (uint32_t base = begin + warp * 32; base < end; base += SORT_THREADS) {   // warp-uniform trip count
-    const uint32_t i = base + lane;
-    const bool valid = i < end;
-    const uint32_t d = valid ? ((keys[i] >> shift) & mask) : (0x10000u | lane);
-    const uint32_t peers = __match_any_sync(0xffffffffu, d);
-    if (valid && lane == __ffs(peers) - 1) s_hist[warp][d] += __popc(peers);
-    __syncwarp();
+  // Segments start on a multiple of the tile size, so 128-bit loads are aligned.
+  for (uint32_t tile = begin + warp * (32 * SORT_ITEMS); tile < end; tile += SORT_TILE) {   // warp-uniform trip count
+    uint32_t k[SORT_ITEMS];
+    if (tile + 32 * SORT_ITEMS <= end) {
+#pragma unroll
+      for (int v = 0; v < SORT_ITEMS / 4; v++) {
+        const uint4 q = *reinterpret_cast<const uint4*>(keys + tile + v * 128 + lane * 4);
+        k[v * 4] = q.x; k[v * 4 + 1] = q.y; k[v * 4 + 2] = q.z; k[v * 4 + 3] = q.w;
+      }
+#pragma unroll
+      for (int j = 0; j < SORT_ITEMS; j++) {
+        const uint32_t d = (k[j] >> shift) & mask;
+        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        if (lane == __ffs(peers) - 1) s_hist[warp][d] += __popc(peers);
+        __syncwarp();
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < SORT_ITEMS; j++) { const uint32_t i = tile + j * 32 + lane; k[j] = i < end ? keys[i] : 0u; }
+#pragma unroll
+      for (int j = 0; j < SORT_ITEMS; j++) {
+        const bool valid = tile + j * 32 + lane < end;
+        const uint32_t d = valid ? ((k[j] >> shift) & mask) : (0x10000u | lane);
+        const uint32_t peers = __match_any_sync(0xffffffffu, d);
+        if (valid && lane == __ffs(peers) - 1) s_hist[warp][d] += __popc(peers);
+        __syncwarp();
+      }
+    }
   }
   __syncthreads();
   for (int d = threadIdx.x; d < RADIX; d += SORT_THREADS) {
@@ -86,7 +108,7 @@ __global__ void __launch_bounds__(1024) radix_rows_kernel(uint32_t* __restrict__
 }
 
 // Pass kernel 3: ranked, stable scatter of each block's segment.
-__global__ void __launch_bounds__(SORT_THREADS) radix_scatter_kernel(
+__global__ void __launch_bounds__(SORT_THREADS, 2) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
     const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask, const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals) {
   __shared__ uint32_t s_cnt[SORT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
@@ -121,13 +143,17 @@ __global__ void __launch_bounds__(SORT_THREADS) radix_scatter_kernel(
     for (int i = tid; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_cnt[0][0])[i] = 0;
     __syncthreads();
     // Each warp owns 512 consecutive pairs; item j of lane l is pair j*32 + l of them, so (j, lane) order is input order.
-    uint32_t key[SORT_ITEMS], rank[SORT_ITEMS];
+    uint32_t key[SORT_ITEMS], val[SORT_ITEMS], rank[SORT_ITEMS];
     const uint32_t wbase = warp * (32 * SORT_ITEMS);
+    // All loads of the tile are issued before any ranking work: 32 independent requests per lane.
+#pragma unroll
+    for (int j = 0; j < SORT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; key[j] = li < tile_n ? keys_in[tile + li] : 0xFFFFFFFFu; }
+#pragma unroll
+    for (int j = 0; j < SORT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; val[j] = li < tile_n ? vals_in[tile + li] : 0u; }
 #pragma unroll
     for (int j = 0; j < SORT_ITEMS; j++) {
       const uint32_t li = wbase + j * 32 + lane;
       const bool valid = li < tile_n;
-      key[j] = valid ? keys_in[tile + li] : 0xFFFFFFFFu;
       const uint32_t d = valid ? ((key[j] >> shift) & mask) : (0x10000u | lane);
       const uint32_t peers = __match_any_sync(0xffffffffu, d);
       uint32_t before = 0;
@@ -161,7 +187,7 @@ __global__ void __launch_bounds__(SORT_THREADS) radix_scatter_kernel(
         const uint32_t d = (key[j] >> shift) & mask;
         const uint32_t slot = s_start[d] + s_cnt[warp][d] + rank[j];
         s_keys[slot] = key[j];
-        s_vals[slot] = vals_in[tile + li];
+        s_vals[slot] = val[j];
       }
     }
     __syncthreads();
@@ -202,12 +228,27 @@ __global__ void __launch_bounds__(EMIT_THREADS) count_sums_kernel(int n, const u
   if (threadIdx.x == 0) { uint32_t t = 0; for (int w = 0; w < EMIT_THREADS / 32; w++) t += s_red[w]; block_sums[blockIdx.x] = t; }
 }
 
-// Thread r takes the r-th nearest splat: its slot range follows from the scan, its tiles from the same decision
-// functions the projection counted with, visited in row-major order.
+// Position of the k-th (0-based) set bit of m; k < popc(m).
+__device__ __forceinline__ int nth_set_bit(uint32_t m, int k) {
+  int pos = 0;
+#pragma unroll
+  for (int w = 16; w >= 1; w >>= 1) {
+    const int c = __popc((m >> pos) & ((1u << w) - 1u));
+    if (k >= c) { k -= c; pos += w; }
+  }
+  return pos;
+}
+
+// Scan of the tile counts in depth order fused with the emission of (tile id, splat index) pairs.
+// Thread r owns the r-th nearest splat; the block scan gives its slot range. The 32 splats of a warp own a contiguous
+// slot range, which the lanes then sweep 32 slots at a time: each slot finds its owning lane by a shuffle binary
+// search over the lanes' first slots and its tile as the k-th set bit of the owner's hit mask, so every store
+// instruction writes 32 consecutive words. Splats with a large tile box (no mask) are appended to a list with their
+// first slot; emit_big_kernel fills their slots.
 __global__ void __launch_bounds__(EMIT_THREADS) scan_emit_kernel(
     int n, const uint32_t* __restrict__ order, const uint32_t* __restrict__ tile_count, const uint32_t* __restrict__ block_sums,
-    const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H, int tiles_x, int tiles_y, uint32_t cap,
-    uint32_t* __restrict__ tile_off, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals, uint32_t* __restrict__ num_isect) {
+    const uint4* __restrict__ hit_info, int tiles_x, uint32_t cap, uint32_t* __restrict__ tile_off, uint32_t* __restrict__ keys,
+    uint32_t* __restrict__ vals, uint32_t* __restrict__ num_isect, uint32_t* __restrict__ big_emit, uint32_t* __restrict__ big_emit_count) {
   __shared__ uint32_t s_warp[EMIT_THREADS / 32];
   __shared__ uint32_t s_base;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -239,24 +280,67 @@ __global__ void __launch_bounds__(EMIT_THREADS) scan_emit_kernel(
 #pragma unroll
     for (int w = 0; w < EMIT_THREADS / 32; w++) { const uint32_t v = s_warp[w]; if (w < warp) pre += v; tile_total += v; }
     const uint32_t end = running + pre + incl;
+    const uint32_t start = end - cnt;
     if (valid) tile_off[r] = end;
-    if (cnt) {
-      uint32_t at = end - cnt;
-      const float4 a = proj0[i], b = proj1[i];
-      const TileRec rec{a.x, a.y, a.z, a.w, b.x, b.w};
-      TileBox bb;
-      if (tile_box(rec, W, H, tiles_x, tiles_y, bb)) {
-        for (int ty = bb.min_y; ty < bb.max_y; ty++)
-          for (int tx = bb.min_x; tx < bb.max_x; tx++)
-            if (tile_hit(tx, ty, rec)) {
-              if (at < cap) { keys[at] = (uint32_t)(ty * tiles_x + tx); vals[at] = i; }
-              at++;
-            }
+    uint4 hi = make_uint4(0u, 0u, 0u, 0u);
+    if (cnt) hi = hit_info[i];
+    const bool big = cnt != 0 && hi.z == 0xFFFFFFFFu;
+    if (big) { const uint32_t e = atomicAdd(big_emit_count, 1u); big_emit[2 * e] = i; big_emit[2 * e + 1] = start; }
+    // Warp sweep over [wstart, wend).
+    const uint32_t wstart = __shfl_sync(0xffffffffu, start, 0), wend = __shfl_sync(0xffffffffu, end, 31);
+    const uint32_t inv_bw = big || !cnt ? 0u : (65536u + (hi.z >> 24) - 1u) / (hi.z >> 24);   // exact x / bw for x < 64
+    for (uint32_t sb = wstart; sb < wend; sb += 32) {
+      const uint32_t s = sb + lane;
+      int o = 0;
+#pragma unroll
+      for (int step = 16; step >= 1; step >>= 1) {   // largest lane whose first slot is <= s
+        const uint32_t st = __shfl_sync(0xffffffffu, start, (o + step) & 31);
+        if (o + step < 32 && st <= s) o += step;
+      }
+      const uint32_t o_start = __shfl_sync(0xffffffffu, start, o);
+      const uint32_t o_lo = __shfl_sync(0xffffffffu, hi.x, o), o_hi = __shfl_sync(0xffffffffu, hi.y, o), o_box = __shfl_sync(0xffffffffu, hi.z, o);
+      const uint32_t o_i = __shfl_sync(0xffffffffu, i, o), o_inv = __shfl_sync(0xffffffffu, inv_bw, o);
+      if (s < wend && s < cap && o_box != 0xFFFFFFFFu) {
+        int k = (int)(s - o_start);
+        const int nlo = __popc(o_lo);
+        const int bit = k < nlo ? nth_set_bit(o_lo, k) : 32 + nth_set_bit(o_hi, k - nlo);
+        const uint32_t bw = o_box >> 24, row = ((uint32_t)bit * o_inv) >> 16, col = (uint32_t)bit - row * bw;
+        keys[s] = (((o_box >> 12) & 0xFFFu) + row) * (uint32_t)tiles_x + (o_box & 0xFFFu) + col;
+        vals[s] = o_i;
       }
     }
     running += tile_total;
   }
   if (blockIdx.x == gridDim.x - 1 && tid == 0) *num_isect = running;
+}
+
+// One warp per listed big splat: the tile box is re-tested 32 tiles at a time in row-major order and the hits are
+// written to the splat's slot range in that order.
+__global__ void __launch_bounds__(256) emit_big_kernel(const uint32_t* __restrict__ big_emit, const uint32_t* __restrict__ big_emit_count,
+                                                       const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H, int tiles_x,
+                                                       int tiles_y, uint32_t cap, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = *big_emit_count;
+  for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
+    const uint32_t i = big_emit[2 * e];
+    uint32_t at = big_emit[2 * e + 1];
+    const float4 a = proj0[i], b = proj1[i];
+    const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
+    TileBox bb;
+    if (!tile_box(rec, W, H, tiles_x, tiles_y, bb)) continue;
+    const int bw = bb.max_x - bb.min_x, area = bw * (bb.max_y - bb.min_y);
+    for (int t0 = 0; t0 < area; t0 += 32) {
+      const int t = t0 + lane;
+      const int tx = bb.min_x + t % bw, ty = bb.min_y + t / bw;
+      const bool hit = t < area && tile_hit(tx, ty, rec);
+      const uint32_t m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const uint32_t s = at + __popc(m & ((1u << lane) - 1u));
+        if (s < cap) { keys[s] = (uint32_t)(ty * tiles_x + tx); vals[s] = i; }
+      }
+      at += __popc(m);
+    }
+  }
 }
 
 __global__ void tile_ranges_kernel(const uint32_t* __restrict__ keys_sorted, const uint32_t* __restrict__ n_ptr, uint32_t n_max, uint32_t n_tiles,
@@ -279,9 +363,9 @@ struct SortScratch { uint32_t* hist; uint32_t* totals; uint32_t* block_sums; uin
 
 int sort_blocks() { int b = sm_count() * BLOCKS_PER_SM; return b > 1024 ? 1024 : b; }
 
-SortScratch carve(void* tmp, int blocks) {
+SortScratch carve(const B2kCtx* c, int blocks) {
   SortScratch s;
-  s.hist = (uint32_t*)tmp;
+  s.hist = sort_tables_ptr(c);
   s.totals = s.hist + (size_t)RADIX * blocks;
   s.block_sums = s.totals + RADIX;
   s.n_word = s.block_sums + blocks;
@@ -313,9 +397,10 @@ int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uin
 using namespace b2k;
 
 extern "C" uint64_t b2k_sort_tmp_bytes(int32_t n, uint64_t isect_cap) {
-  (void)n; (void)isect_cap;
+  (void)isect_cap;
   const int blocks = 1024;   // upper bound of sort_blocks()
-  return (uint64_t)sizeof(uint32_t) * ((uint64_t)RADIX * blocks + RADIX + blocks + 16);
+  const uint64_t n_cap = n > 0 ? (uint64_t)n : 0;
+  return (uint64_t)sizeof(uint32_t) * (BIG_HEADER_WORDS + 3 * n_cap + (uint64_t)RADIX * blocks + RADIX + blocks + 16);
 }
 
 extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
@@ -324,12 +409,12 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
   cudaStream_t s = (cudaStream_t)stream;
   B2K_CUDA(cudaMemsetAsync(c->tile_ranges, 0, sizeof(uint32_t) * 2 * (size_t)c->n_tiles, s));
   if (n == 0) { B2K_CUDA(cudaMemsetAsync(c->num_isect, 0, sizeof(uint32_t), s)); return B2K_OK; }
-  B2K_REQUIRE(c->proj0 && c->proj1 && c->tile_count && c->depth_keys && c->depth_keys_sorted && c->order_in && c->order && c->tile_off);
+  B2K_REQUIRE(c->proj0 && c->proj1 && c->tile_count && c->hit_info && c->depth_keys && c->depth_keys_sorted && c->order_in && c->order && c->tile_off);
   B2K_REQUIRE(c->keys && c->vals && c->keys_sorted && c->vals_sorted && c->sort_tmp);
   if (c->n_cap < n) return B2K_ERR_CAPACITY;
-  if (c->sort_tmp_bytes < b2k_sort_tmp_bytes(n, c->isect_cap) || c->isect_cap == 0 || c->isect_cap > 0xFFFFFFF0ull) return B2K_ERR_CAPACITY;
+  if (c->sort_tmp_bytes < b2k_sort_tmp_bytes(c->n_cap, c->isect_cap) || c->isect_cap == 0 || c->isect_cap > 0xFFFFFFF0ull) return B2K_ERR_CAPACITY;
   const int blocks = sort_blocks();
-  const SortScratch sc = carve(c->sort_tmp, blocks);
+  const SortScratch sc = carve(c, blocks);
   // 1. Splats by depth: key = bits of view z (culled splats carry 0xFFFFFFFF and land last), value = index. The
   //    projection left its keys and indices in the (depth_keys_sorted, order) pair: with four passes (an even count)
   //    the ping-pong returns to the pair it started from, so the sorted result lands where callers expect it and
@@ -343,9 +428,13 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
   uint32_t* ev = (tile_passes % 2 == 0) ? c->vals_sorted : c->vals;
   uint32_t* ok = (tile_passes % 2 == 0) ? c->keys : c->keys_sorted;
   uint32_t* ov = (tile_passes % 2 == 0) ? c->vals : c->vals_sorted;
+  uint32_t* big_emit_count = big_count_ptr(c) + 1;
+  B2K_CUDA(cudaMemsetAsync(big_emit_count, 0, sizeof(uint32_t), s));
   count_sums_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums);
-  scan_emit_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums, (const float4*)c->proj0, (const float4*)c->proj1,
-                                                  c->W, c->H, c->tiles_x, c->tiles_y, (uint32_t)c->isect_cap, c->tile_off, ek, ev, c->num_isect);
+  scan_emit_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums, (const uint4*)c->hit_info, c->tiles_x,
+                                                  (uint32_t)c->isect_cap, c->tile_off, ek, ev, c->num_isect, big_emit_ptr(c), big_emit_count);
+  emit_big_kernel<<<sm_count() * 4, 256, 0, s>>>(big_emit_ptr(c), big_emit_count, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
+                                                 c->tiles_x, c->tiles_y, (uint32_t)c->isect_cap, ek, ev);
   st = check_launch();
   if (st) return st;
   // 4. Stable sort by tile id: depth order survives inside each tile.

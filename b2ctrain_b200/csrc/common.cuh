@@ -25,6 +25,14 @@ int sm_count();
 
 __host__ __device__ inline int div_up(long long a, int b) { return (int)((a + b - 1) / b); }
 
+// Layout of the caller's sort_tmp scratch. The first words hold the list of splats with large tile boxes, shared by
+// the projection (which fills it) and the binning (which emits from it); the radix sort's tables follow.
+constexpr size_t BIG_HEADER_WORDS = 16;   // [0] projection's big-splat count, [1] emit's big-splat count
+inline uint32_t* big_count_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp; }
+inline uint32_t* big_list_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp + BIG_HEADER_WORDS; }
+inline uint32_t* big_emit_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp + BIG_HEADER_WORDS + (size_t)c->n_cap; }       // [n_cap][2]
+inline uint32_t* sort_tables_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp + BIG_HEADER_WORDS + 3 * (size_t)c->n_cap; }
+
 struct CamDev {
   float R[9]; float t[3]; float pos[3]; float fx, fy, cx, cy; int W, H; float lim_pos_x, lim_pos_y, lim_neg_x, lim_neg_y;
 };
@@ -52,7 +60,16 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Reference semantics: tile_bbox / tile_hit (src/gpu/splat_math.cuh:27-53), extent and on-screen culls
 // (splat_math.cuh:284-290).
 // ---------------------------------------------------------------------------------------------------------------
-struct TileRec { float mx, my, c00, c01, c11, power; };
+struct TileRec {
+  float mx, my, c00, c01, c11, power;
+  float ia, ib;   // 1 / (64 c00), 1 / (64 c11): the per-splat denominators of the closest-point parameters
+};
+__device__ __forceinline__ TileRec make_tile_rec(float mx, float my, float c00, float c01, float c11, float power) {
+  TileRec r{mx, my, c00, c01, c11, power, 0.f, 0.f};
+  r.ia = __fdiv_rn(1.f, __fmul_rn(64.f, c00));
+  r.ib = __fdiv_rn(1.f, __fmul_rn(64.f, c11));
+  return r;
+}
 struct TileBox { int min_x, min_y, max_x, max_y; };
 
 __device__ __forceinline__ float rn_mul(float a, float b) { return __fmul_rn(a, b); }
@@ -88,8 +105,9 @@ __device__ __forceinline__ bool tile_hit(int tx, int ty, const TileRec& r) {
   const float corner_x = x_left ? rmin_x : rmax_x, corner_y = y_above ? rmin_y : rmax_y;
   const float dxf = x_left ? (float)RT_W : -(float)RT_W, dyf = y_above ? (float)RT_W : -(float)RT_W;
   const float diff_x = rn_sub(r.mx, corner_x), diff_y = rn_sub(r.my, corner_y);
-  const float tx_raw = rn_div(rn_add(rn_mul(rn_mul(dxf, r.c00), diff_x), rn_mul(rn_mul(dxf, r.c01), diff_y)), rn_mul(rn_mul(dxf, r.c00), dxf));
-  const float ty_raw = rn_div(rn_add(rn_mul(rn_mul(dyf, r.c01), diff_x), rn_mul(rn_mul(dyf, r.c11), diff_y)), rn_mul(rn_mul(dyf, r.c11), dyf));
+  // t = d (c00 diff_x + c01 diff_y) / (d^2 c00) with d = +-8: the division is by a per-splat constant.
+  const float tx_raw = rn_mul(rn_mul(dxf, rn_add(rn_mul(r.c00, diff_x), rn_mul(r.c01, diff_y))), r.ia);
+  const float ty_raw = rn_mul(rn_mul(dyf, rn_add(rn_mul(r.c01, diff_x), rn_mul(r.c11, diff_y))), r.ib);
   const float tx_c = in_y ? 0.f : clamp01(tx_raw), ty_c = in_x ? 0.f : clamp01(ty_raw);
   const float px = rn_add(corner_x, rn_mul(tx_c, dxf)), py = rn_add(corner_y, rn_mul(ty_c, dyf));
   const float dx = rn_sub(px, r.mx), dy = rn_sub(py, r.my);

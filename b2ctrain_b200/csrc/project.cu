@@ -32,34 +32,47 @@ namespace {
 
 constexpr int PROJ_BLOCK = 256;
 
+// Tile boxes of at most this many tiles are tested by the projecting thread and remembered as a bit mask; larger
+// ones go to a list that a warp-per-splat kernel counts (and later emits) cooperatively.
+constexpr int MASK_TILES = 64;
+
 template <int DEG>
 __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
     int n, size_t cap, const float4* __restrict__ pos_op, const float4* __restrict__ quat, const float4* __restrict__ lscale,
     const float* __restrict__ sh_dc, const float* __restrict__ sh_hi, CamDev cam, int active, int tiles_x, int tiles_y,
     float4* __restrict__ proj0, float4* __restrict__ proj1, float4* __restrict__ proj2, uint32_t* __restrict__ tile_count,
-    uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen) {
+    uint4* __restrict__ hit_info, uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen,
+    uint32_t* __restrict__ big_list, uint32_t* __restrict__ big_count) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float4 po = pos_op[i], q = quat[i], ls = lscale[i];
   Proj pr;
-  uint32_t hits = 0;
-  uint32_t key = 0xFFFFFFFFu;
+  uint32_t hits = 0, mask_lo = 0, mask_hi = 0, box = 0;
+  bool shade = false, big = false;
   if (project_one(po, q, ls, cam, pr)) {
-    const TileRec rec{pr.mx, pr.my, pr.c00, pr.c01, pr.c11, pr.power};
+    const TileRec rec = make_tile_rec(pr.mx, pr.my, pr.c00, pr.c01, pr.c11, pr.power);
     TileBox bb;
-    float ms = 0.f;
     if (tile_box(rec, cam.W, cam.H, tiles_x, tiles_y, bb)) {
-      for (int ty = bb.min_y; ty < bb.max_y; ty++)
-        for (int tx = bb.min_x; tx < bb.max_x; tx++) hits += tile_hit(tx, ty, rec) ? 1u : 0u;
+      const int bw = bb.max_x - bb.min_x, bh = bb.max_y - bb.min_y;
+      if (bw * bh > MASK_TILES) {
+        big = true; shade = true;
+        box = 0xFFFFFFFFu;
+        big_list[atomicAdd(big_count, 1u)] = (uint32_t)i;
+      } else if (bw > 0 && bh > 0) {
+        int bit = 0;
+        for (int ty = bb.min_y; ty < bb.max_y; ty++)
+          for (int tx = bb.min_x; tx < bb.max_x; tx++, bit++)
+            if (tile_hit(tx, ty, rec)) { hits++; if (bit < 32) mask_lo |= 1u << bit; else mask_hi |= 1u << (bit - 32); }
+        box = (uint32_t)bb.min_x | ((uint32_t)bb.min_y << 12) | ((uint32_t)bw << 24);
+        shade = hits != 0;
+      }
       const float detc = pr.c00 * pr.c11 - pr.c01 * pr.c01;
       const float ex = sqrtf(2.f * pr.power * pr.c11 / detc), ey = sqrtf(2.f * pr.power * pr.c00 / detc);
-      ms = fmaxf(ex / (float)cam.W, ey / (float)cam.H);
-      if (max_screen) max_screen[i] = fmaxf(max_screen[i], ms);
+      if (max_screen) max_screen[i] = fmaxf(max_screen[i], fmaxf(ex / (float)cam.W, ey / (float)cam.H));
     }
     proj0[i] = make_float4(pr.mx, pr.my, pr.c00, pr.c01);
     proj1[i] = make_float4(pr.c11, pr.opac, pr.mean_c.z, pr.power);
-    if (hits) {
-      key = __float_as_uint(pr.mean_c.z);
+    if (shade) {
       // Colour from SH along the direction camera -> splat (+0.5, clamped to +-100 as in project.cu:52-55).
       float3 v = make_float3(po.x - cam.pos[0], po.y - cam.pos[1], po.z - cam.pos[2]);
       const float inv = 1.f / fmaxf(sqrtf(v.x * v.x + v.y * v.y + v.z * v.z), 1e-12f);
@@ -85,9 +98,36 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
   } else {
     proj1[i] = make_float4(0.f, 0.f, 0.f, -1.f);   // no record
   }
-  tile_count[i] = hits;
-  depth_keys[i] = key;
+  hit_info[i] = make_uint4(mask_lo, mask_hi, box, 0u);
   order_in[i] = (uint32_t)i;
+  if (!big) {   // big splats get their count and key from count_big_kernel
+    tile_count[i] = hits;
+    depth_keys[i] = hits ? __float_as_uint(pr.mean_c.z) : 0xFFFFFFFFu;
+  }
+}
+
+// One warp per listed splat: lanes sweep the tile box 32 tiles at a time.
+__global__ void __launch_bounds__(256) count_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ big_count,
+                                                        const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H, int tiles_x,
+                                                        int tiles_y, uint32_t* __restrict__ tile_count, uint32_t* __restrict__ depth_keys) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = *big_count;
+  for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
+    const uint32_t i = big_list[e];
+    const float4 a = proj0[i], b = proj1[i];
+    const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
+    TileBox bb;
+    uint32_t hits = 0;
+    if (tile_box(rec, W, H, tiles_x, tiles_y, bb)) {
+      const int bw = bb.max_x - bb.min_x, area = bw * (bb.max_y - bb.min_y);
+      for (int t0 = 0; t0 < area; t0 += 32) {
+        const int t = t0 + lane;
+        const bool hit = t < area && tile_hit(bb.min_x + t % bw, bb.min_y + t / bw, rec);
+        hits += __popc(__ballot_sync(0xffffffffu, hit));
+      }
+    }
+    if (lane == 0) { tile_count[i] = hits; depth_keys[i] = hits ? __float_as_uint(b.z) : 0xFFFFFFFFu; }
+  }
 }
 
 template <int DEG>
@@ -96,9 +136,15 @@ int launch(const B2kModel* m, const CamDev& cam, const B2kRenderOpts* o, const B
   const float4* quat = (const float4*)(o->quat_override ? o->quat_override : m->quat);
   const float4* lscale = (const float4*)(o->lscale_override ? o->lscale_override : m->lscale);
   const int active = o->sh_degree < m->degree ? o->sh_degree : m->degree;
+  uint32_t* big_count = big_count_ptr(c);
+  uint32_t* big_list = big_list_ptr(c);
+  if (cudaMemsetAsync(big_count, 0, sizeof(uint32_t), s) != cudaSuccess) return check_launch();
   project_kernel<DEG><<<div_up(m->n, PROJ_BLOCK), PROJ_BLOCK, 0, s>>>(
       m->n, (size_t)m->cap, pos, quat, lscale, m->sh_dc, m->sh_hi, cam, active < 0 ? 0 : active, c->tiles_x, c->tiles_y,
-      (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, c->depth_keys_sorted, c->order, m->max_screen);
+      (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, (uint4*)c->hit_info, c->depth_keys_sorted, c->order, m->max_screen,
+      big_list, big_count);
+  count_big_kernel<<<sm_count() * 4, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, cam.W, cam.H, c->tiles_x,
+                                                  c->tiles_y, c->tile_count, c->depth_keys_sorted);
   return check_launch();
 }
 
@@ -112,7 +158,8 @@ extern "C" int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRen
   if (m->n == 0) return B2K_OK;
   B2K_REQUIRE(m->n > 0 && m->cap >= m->n && m->pos_op && m->quat && m->lscale && m->sh_dc);
   B2K_REQUIRE(m->degree >= 0 && m->degree <= 4 && (m->degree == 0 || m->sh_hi));
-  B2K_REQUIRE(ctx->proj0 && ctx->proj1 && ctx->proj2 && ctx->tile_count && ctx->depth_keys_sorted && ctx->order);
+  B2K_REQUIRE(ctx->proj0 && ctx->proj1 && ctx->proj2 && ctx->tile_count && ctx->hit_info && ctx->depth_keys_sorted && ctx->order && ctx->sort_tmp);
+  if (ctx->sort_tmp_bytes < b2k_sort_tmp_bytes(ctx->n_cap, ctx->isect_cap)) return B2K_ERR_CAPACITY;
   B2K_REQUIRE(cam->W == ctx->W && cam->H == ctx->H && ctx->tiles_x == div_up(ctx->W, RT_W) && ctx->tiles_y == div_up(ctx->H, RT_W));
   if (ctx->n_cap < m->n) return B2K_ERR_CAPACITY;
   const CamDev cd = to_camdev(*cam);

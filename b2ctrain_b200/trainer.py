@@ -1,0 +1,161 @@
+"""The per-step sequence of the reference's trainer and renderer over the operator API, with view-level data
+parallelism.
+
+`Trainer.step` follows one iteration of train_phase (src/train/trainer.cpp:452-529): per view render_forward,
+photometric_loss, accumulate_loss, rasterize_backward, then the parameter update. The reference's step is one view on
+one GPU; here a step may hold several views and several ranks:
+
+  * every rank holds a full model replica and renders the views `rank, rank + world, ...` of the step;
+  * each view's projection backward ADDS into a dense per-splat gradient accumulator [n][11+3K] (the layout of the
+    reference's OptimParams::grad_out lane, src/gpu/optim.cu:292-297);
+  * one all-reduce (sum) of that accumulator over NCCL, then the identical Adam update on every rank, so replicas stay
+    bit-identical. The step loss is the sum of the per-view losses (its gradient is the all-reduced sum).
+
+A single-view, single-rank step uses the fused projection-backward + Adam kernel exactly like the reference.
+`Renderer.render` follows render_main's per-camera loop (src/render/renderer.cpp:345-363) up to the device image.
+"""
+import numpy as np
+import torch
+
+from . import api
+
+
+class Trainer:
+    def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, lr_mean=1.6e-4, sparse=True, noise_weight=0.0,
+                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None):
+        self.device = torch.device(device)
+        self.rank, self.world = rank, world
+        self.model = api.Model(device).upload(cloud)
+        self.ctx = api.RenderCtx(device)
+        self.ctx.setup(W, H, self.model.cap, isect_cap=isect_cap)
+        self.W, self.H = W, H
+        self.lr_mean, self.sparse = lr_mean, sparse
+        self.noise_weight, self.noise_clamp = noise_weight, noise_clamp
+        self.lp = api.LossParams(l1_w=1.0 - ssim_weight, ssim_w=-ssim_weight)
+        K = self.model.K()
+        self.grad = torch.zeros((self.model.n, 11 + 3 * K), dtype=torch.float32, device=self.device)
+        self.step_no = 0
+        P = W * H
+        # device staging for targets that arrive from host memory (double-buffered on a copy stream)
+        self._stage = [torch.zeros(P, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._copy_stream = torch.cuda.Stream(device=self.device)
+        self._staged_evt = [torch.cuda.Event() for _ in range(2)]
+        self._free_evt = [torch.cuda.Event() for _ in range(2)]
+        self.h2d_bytes = 0
+
+    def my_views(self, n_views):
+        return list(range(self.rank, n_views, self.world))
+
+    def _target(self, t, slot):
+        """A device int32 tensor of packed RGBA8. Host (pinned) tensors are copied on the copy stream."""
+        if t.is_cuda:
+            return t
+        dst = self._stage[slot]
+        cur = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(self._free_evt[slot])
+            dst.copy_(t, non_blocking=True)
+            self._staged_evt[slot].record(self._copy_stream)
+        cur.wait_event(self._staged_evt[slot])
+        self.h2d_bytes += t.numel() * 4
+        return dst
+
+    def view_pass(self, cam, target, bg=(0.0, 0.0, 0.0), weights=None, slot=0, fused_op=None):
+        """forward + loss + backward of one view; then either the fused optimizer (fused_op given) or the gradient
+        accumulation."""
+        m, ctx = self.model, self.ctx
+        rp = api.RenderParams(cam, bg=bg, sh_degree=m.degree, bwd_info=True)
+        api.render_forward(ctx, m, rp, sync=False)
+        tgt = self._target(target, slot)
+        view = api.ViewGPU(tgt, weights, self.W, self.H)
+        api.photometric_loss(ctx, view, self.lp)
+        if not target.is_cuda:
+            self._free_evt[slot].record(torch.cuda.current_stream(self.device))
+        api.accumulate_loss(ctx)
+        api.rasterize_backward(ctx, m, rp)
+        if fused_op is not None:
+            api.optimizer_step(ctx, m, fused_op)
+        else:
+            api.projection_backward(ctx, m, self._op(cam), self.grad)
+
+    def _op(self, cam):
+        return api.OptimParams(cam, active_sh_degree=self.model.degree, t=self.model.adam_t, lr_mean=self.lr_mean, sparse=self.sparse,
+                               noise_weight=self.noise_weight, noise_clamp=self.noise_clamp, step=self.step_no)
+
+    def step(self, cams, targets, bg=(0.0, 0.0, 0.0)):
+        """One optimisation step over `cams` / `targets` (the whole step's views; this rank takes its share).
+        Returns the device tensor loss_accum (index 0: loss of the last view, 2: running sum, 3: count)."""
+        m = self.model
+        m.adam_t += 1
+        self.step_no += 1
+        mine = self.my_views(len(cams))
+        self.ctx.loss_accum.zero_()
+        if self.world == 1 and len(cams) == 1:
+            self.view_pass(cams[0], targets[0], bg, fused_op=self._op(cams[0]))
+            return self.ctx.loss_accum
+        for j, v in enumerate(mine):
+            self.ctx.loss_accum[:2].zero_()
+            self.view_pass(cams[v], targets[v], bg, slot=j & 1)
+        if self.world > 1:
+            torch.distributed.all_reduce(self.grad, op=torch.distributed.ReduceOp.SUM)
+        api.adam_step(m, self._op(cams[0]), self.grad)
+        return self.ctx.loss_accum
+
+    def check_overflow(self):
+        """Reads the last view's intersection count back; grows the buffers when it did not fit (the reference does this
+        inside every bin_and_sort, src/gpu/binning.cu:125-133). Returns (count, overflowed)."""
+        total = int(self.ctx.d_num_isect[0].item()) & 0xFFFFFFFF
+        if total > self.ctx.isect_cap:
+            cap = self.ctx.isect_cap
+            while cap < total:
+                cap *= 2
+            self.ctx._alloc_isect(cap)
+            return total, True
+        return total, False
+
+
+class Renderer:
+    """Forward-only rendering of cameras split round-robin over ranks; outputs stay on the producing GPU."""
+
+    def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, want_depth=True, isect_cap=None):
+        self.device = torch.device(device)
+        self.rank, self.world = rank, world
+        self.model = api.Model(device).upload(cloud)
+        self.ctx = api.RenderCtx(device)
+        self.ctx.want_depth = want_depth
+        self.ctx.setup(W, H, self.model.cap, isect_cap=isect_cap)
+
+    def render(self, cam, bg=(0.0, 0.0, 0.0), sync=False):
+        rp = api.RenderParams(cam, bg=bg, sh_degree=self.model.degree, bwd_info=False)
+        api.render_forward(self.ctx, self.model, rp, sync=sync)
+        return self.ctx.out_rgba, self.ctx.out_depth
+
+
+def render_targets(cloud, cams, device="cuda:0", noise_sigma=0.0, seed=0, alpha=255, isect_cap=None):
+    """Targets for the synthetic benchmark: renders of a ground-truth splat set on black, optional N(0, sigma) pixel
+    noise, clamped and quantised to packed RGBA8 like the reference's rendered targets (src/train/teacher.cu:11-17).
+    Returns a list of host (pinned) int32 tensors."""
+    W, H = cams[0]["W"], cams[0]["H"]
+    r = Renderer(cloud, W, H, device, want_depth=False, isect_cap=isect_cap)
+    gen = torch.Generator(device=device); gen.manual_seed(seed)
+    out = []
+    for cam in cams:
+        while True:
+            img, _ = r.render(cam, sync=False)
+            total = int(r.ctx.d_num_isect[0].item()) & 0xFFFFFFFF
+            if total <= r.ctx.isect_cap:
+                break
+            cap = r.ctx.isect_cap
+            while cap < total:
+                cap *= 2
+            r.ctx._alloc_isect(cap)
+        img = img.clone()
+        if noise_sigma > 0:
+            img[:, :3] += torch.randn((W * H, 3), generator=gen, device=device) * noise_sigma
+        packed = torch.zeros(W * H, dtype=torch.int32, device=device)
+        api.pack_rgba8(img.clamp_(0.0, 1.0), packed, alpha_override=alpha)
+        host = torch.empty(W * H, dtype=torch.int32).pin_memory()
+        host.copy_(packed)
+        out.append(host)
+    torch.cuda.synchronize()
+    return out, r.ctx.isect_cap

@@ -1,0 +1,373 @@
+"""Benchmark of the splat render-and-backprop hot path.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: under torchrun, one rank per GPU)
+    python bench.py --impl reference ...                     (the CPU restatement of the reference path, host cores)
+
+Workload (N = 1 and up): BASELINE config 2 -- 3M splats, SH degree 3, 64 views of 1920x1080 per step on a radius-4
+sphere, targets = renders of a seed-distinct 3M-splat ground-truth set on black. One step = forward + L1/SSIM loss +
+backward + projection backward for all 64 views (sharded over the ranks), one all-reduce of the 59-float per-splat
+gradients when N > 1, then sparse Adam. Metric: train views/s, whole job. Inputs are seeded synthetic data.
+`--workload render` measures BASELINE config 3 (6M splats, SH degree 4, 3840x2160 cameras, RGB + alpha + depth) in
+Mpix/s instead; `--workload step1` BASELINE config 1 (500k splats, one 1080p view per step, fused optimizer).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b2k", choices=["b2k", "reference"])
+    ap.add_argument("--workload", default="train", choices=["train", "render", "step1"])
+    ap.add_argument("--splats", type=int, default=None, help="override the splat count (testing only; the line says so)")
+    ap.add_argument("--views", type=int, default=None, help="override views per step / cameras (testing only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
+    return ap.parse_args()
+
+
+WORKLOADS = {"train": 2, "step1": 1, "render": 3}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [nm for k, nm in enumerate(names) if any(len(r) >= 7 and r[3 + k].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_reference_arm(args, cfg):
+    """The reference path on the host cores: the oracle port (forward + loss + analytic backward + Adam), all OpenMP
+    threads, one view of the workload per step."""
+    from b2ctrain_b200 import scenes
+    from oracle import orc
+    n0, deg = scenes.CONFIG_SPLATS[cfg]
+    n = args.splats or n0
+    scene = scenes.config_scene(cfg, n=n)
+    cams = scenes.config_cameras(cfg)
+    W, H = cams[0]["W"], cams[0]["H"]
+    gt = np.full(W * H, 0xFF000000, np.uint32)
+    lp = dict(l1_w=np.float32(0.8), ssim_w=np.float32(-0.2))
+    K = (deg + 1) ** 2
+    state = None
+    times = []
+    for s in range(args.warmup + args.steps):
+        cam = cams[s % len(cams)]
+        t0 = time.perf_counter()
+        if args.workload == "render":
+            orc.step(scene, cam, np.zeros(3), None, None, lp, backward=False, want_image=True)
+        else:
+            out = orc.step(scene, cam, np.zeros(3), gt, None, lp, backward=True)
+            if state is None:
+                z4 = lambda: np.zeros((n, 4), np.float32)
+                state = dict(pos_op=scene["pos_op"], quat=scene["quat"], lscale=scene["lscale"], sh=scene["sh"], m_pos=z4(), v_pos=z4(), m_q=z4(),
+                             v_q=z4(), m_ls=z4(), v_ls=z4(), m_sh=np.zeros((n, K, 3), np.float32), v_sh=np.zeros(n, np.float32),
+                             last_step=np.zeros(n, np.uint32))
+            orc.adam(state, out["grad"], np.any(out["grad"] != 0, axis=1), dict(t=s + 1, lr_mean=1.6e-4, sparse=1), deg)
+        dt = time.perf_counter() - t0
+        if s >= args.warmup:
+            times.append(dt)
+        if s == 0 and dt > 60:   # keep the arm within minutes
+            times.append(dt)
+            break
+    sec = float(np.mean(times))
+    if args.workload == "render":
+        value, unit, metric = W * H / sec / 1e6, "Mpix/s", "render Mpix/s"
+    else:
+        value, unit, metric = 1.0 / sec, "views/s", "train views/s"
+    return dict(value=value, unit=unit, metric=metric, cores=orc.num_threads(), sec_per_unit=sec, n=n, W=W, H=H,
+                sample=f"{len(times)} x one view of the workload ({n} splats, {W}x{H}), forward+loss+backward+Adam" if args.workload != "render"
+                else f"{len(times)} x one camera of the workload ({n} splats, {W}x{H}), forward only")
+
+
+def main():
+    args = parse()
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        r = cpu_reference_arm(args, cfg)
+        line = {"metric": r["metric"], "value": r["value"], "unit": r["unit"], "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": r["sec_per_unit"] * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+                "data": "synthetic", "impl": "reference",
+                "config": {"workload": workload_name(args, cfg, r["n"]), "views_per_step": 1, "l2_policy": "inputs larger than L2"},
+                "cpu_baseline": {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                "e2e": {"value": r["value"], "unit": r["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from b2ctrain_b200 import api, scenes
+    from b2ctrain_b200.trainer import Renderer, Trainer, render_targets
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = f"cuda:{local_rank}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(device))
+    api.lib()
+
+    n0, deg = scenes.CONFIG_SPLATS[cfg]
+    n = args.splats or n0
+    cams = scenes.config_cameras(cfg)
+    if args.views:
+        cams = cams[: args.views]
+    W, H = cams[0]["W"], cams[0]["H"]
+    scene = scenes.config_scene(cfg, n=n)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    if args.workload == "render":
+        result = bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks, sampler)
+    else:
+        result = bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_ranks, sampler)
+    if rank == 0:
+        result.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
+                       "dtype": "f32"})
+        result["config"]["workload"] = workload_name(args, cfg, n)
+        if not args.no_cpu_baseline and world == 1:
+            r = cpu_reference_arm(argparse.Namespace(**{**vars(args), "steps": 1, "warmup": 0}), cfg)
+            result["cpu_baseline"] = {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": "port", "sample": r["sample"]}
+        print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def workload_name(args, cfg, n):
+    base = {1: "config1: 500k splats SH3, one 1920x1080 view per step, fused projection-backward + sparse Adam",
+            2: "config2: 3M splats SH3, 64 views of 1920x1080 per step sharded by view, all-reduce of 59 floats per splat, sparse Adam",
+            3: "config3: 6M splats SH4, 256 cameras of 3840x2160, RGB + alpha + depth, forward only"}[cfg]
+    if args.splats or args.views:
+        base += f" [REDUCED for testing: splats={n}, views={args.views}]"
+    return base
+
+
+def presize(tr_or_r, cams, mine, targets, is_train):
+    """Runs each of this rank's views once to size the intersection buffers (the reference grows them inside
+    bin_and_sort; here the count stays on the device during the timed steps)."""
+    import torch
+    from b2ctrain_b200 import api
+    ctx, m = tr_or_r.ctx, tr_or_r.model
+    stats = []
+    for v in mine:
+        while True:
+            rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=is_train)
+            api.render_forward(ctx, m, rp, sync=False)
+            total = int(ctx.d_num_isect[0].item()) & 0xFFFFFFFF
+            if total <= ctx.isect_cap:
+                break
+            cap = ctx.isect_cap
+            while cap < total:
+                cap *= 2
+            ctx._alloc_isect(cap)
+        tc = ctx.tile_count[: m.n]
+        ranges = ctx.tile_ranges.view(-1, 2)
+        stats.append(dict(V=int((tc != 0).sum().item()), I=total, I_b=int((ranges[:, 1] - ranges[:, 0]).sum().item())))
+    torch.cuda.synchronize()
+    return stats
+
+
+def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_ranks, sampler):
+    import torch
+    from b2ctrain_b200 import api, scenes
+    from b2ctrain_b200.trainer import Trainer, render_targets
+    n, deg = scene["n"], scene["degree"]
+    W, H = cams[0]["W"], cams[0]["H"]
+    P = W * H
+    n_views = len(cams)
+    gt_scene = scenes.config_scene(cfg, n=n, gt_set=True)
+    mine = list(range(rank, n_views, world))
+    noise = 0.05 if cfg == 1 else 0.0
+    host_targets_mine, cap = render_targets(gt_scene, [cams[v] for v in mine], device, noise_sigma=noise, seed=1234 + rank)
+    del gt_scene
+    torch.cuda.empty_cache()
+    host_targets = [None] * n_views
+    dev_targets = [None] * n_views
+    for j, v in enumerate(mine):
+        host_targets[v] = host_targets_mine[j]
+        dev_targets[v] = host_targets_mine[j].to(device)
+    median_scale = float(np.median(np.exp(scene["lscale"][:, :3])))
+    tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=0.0, isect_cap=cap)
+    stats = presize(tr, cams, mine, dev_targets, True)
+
+    def timed(targets, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        loss = None
+        for _ in range(steps):
+            acc = tr.step(cams, targets)
+            loss = acc.cpu() if targets is host_targets else None   # the step's result read back (16 floats)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)), loss
+
+    timed(dev_targets, args.warmup)
+    sampler.start()
+    ms, _ = timed(dev_targets, args.steps)
+    clocks = sampler.stop()
+    tr.h2d_bytes = 0
+    timed(host_targets, 1)
+    tr.h2d_bytes = 0
+    ms_e2e, loss = timed(host_targets, args.steps)
+    h2d = tr.h2d_bytes / args.steps
+    total_isect, over = tr.check_overflow()
+    assert not over, "intersection buffers overflowed inside the timed region"
+
+    views_per_step = n_views
+    value = views_per_step * args.steps / (ms / 1e3)
+    e2e_value = views_per_step * args.steps / (ms_e2e / 1e3)
+    launches_view = 1 + (1 + 12 + 2 + 3 * ((tr.ctx.tile_bits + 7) // 8) + 1) + 1 + 1 + 1 + 1 + 1
+    launches = args.steps * (len(mine) * launches_view + (0 if (world == 1 and n_views == 1) else 1))
+    res = {"metric": "train views/s", "value": value, "unit": "views/s", "ms_per_step": ms / args.steps, "scaling": "strong",
+           "config": {"views_per_step": views_per_step, "splats": n, "sh_degree": deg, "resolution": f"{W}x{H}", "parallelism": f"dp{world} by view",
+                      "l2_policy": "inputs larger than L2 (per view > 126 MB of records, lists and images; 64 distinct views per step)",
+                      "scene_counts_view0": stats[0] if stats else None},
+           "e2e": {"value": e2e_value, "unit": "views/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 64, "ms_per_step": ms_e2e / args.steps},
+           "gpu_launches": launches, "clocks": clocks, "loss_last_view": float(loss[0]) if loss is not None else None}
+    if rank == 0:
+        res["roofline"], res["stages"] = stage_roofline(args, tr, cams, dev_targets, mine, stats)
+    return res
+
+
+def stage_roofline(args, tr, cams, targets, mine, stats):
+    """Times each stage of a view with CUDA events (on the launching stream), a few views, and derives the roofline
+    object for the dominant kernel. Algorithmic bytes per stage follow the per-unit figures stated in DESIGN.md."""
+    import torch
+    from b2ctrain_b200 import api
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
+    m, ctx = tr.model, tr.ctx
+    K = m.K()
+    names = ["project", "bin_sort", "raster_fwd", "loss", "raster_bwd", "proj_bwd"]
+    acc = {k: 0.0 for k in names}
+    views = mine[: max(1, args.stage_views)]
+    for v in views:
+        rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True)
+        view = api.ViewGPU(targets[v], None, ctx.W, ctx.H)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
+        torch.cuda.synchronize()
+        ev[0].record(); api.project_splats(ctx, m, rp)
+        ev[1].record(); api.bin_and_sort(ctx, m, sync=False)
+        ev[2].record(); api.rasterize_forward(ctx, rp)
+        ev[3].record(); api.photometric_loss(ctx, view, tr.lp)
+        ev[4].record(); api.rasterize_backward(ctx, m, rp)
+        ev[5].record(); api.projection_backward(ctx, m, tr._op(cams[v]), tr.grad)
+        ev[6].record()
+        torch.cuda.synchronize()
+        for k, nm in enumerate(names):
+            acc[nm] += ev[k].elapsed_time(ev[k + 1])
+    tr.grad.zero_()
+    nv = len(views)
+    st = stats[0]
+    V, I, Ib, n, P, tiles = st["V"], st["I"], st["I_b"], m.n, ctx.W * ctx.H, ctx.n_tiles
+    passes = (ctx.tile_bits + 7) // 8
+    alg = {"project": 48 * n + 12 * K * V + 48 * V + 12 * n,
+           "bin_sort": 16 * n * 4 + 8 * n + 8 * I + 16 * I * passes + 4 * I + 8 * tiles,
+           "raster_fwd": 52 * Ib + 36 * P, "loss": 20 * P + 16 * P, "raster_bwd": 28 * P + 52 * Ib + 52 * V,
+           "proj_bwd": (52 + 48 + 12 * K) * V + 2 * 4 * (11 + 3 * K) * V + 8 * n}
+    stages = {nm: {"ms": acc[nm] / nv, "algorithmic_bytes": int(alg[nm]), "achieved_gbs": alg[nm] / (acc[nm] / nv * 1e-3) / 1e9} for nm in names}
+    top = max(names, key=lambda k: acc[k])
+    a = stages[top]["achieved_gbs"]
+    roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": None, "peak_source": peak_src,
+            "ms_per_launch_group": stages[top]["ms"]}
+    return roof, stages
+
+
+def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks, sampler):
+    import torch
+    from b2ctrain_b200.trainer import Renderer
+    W, H = cams[0]["W"], cams[0]["H"]
+    mine = list(range(rank, len(cams), world))
+    r = Renderer(scene, W, H, device, rank, world, want_depth=True)
+    stats = presize(r, cams, mine, None, False)
+    host_out = torch.empty((W * H, 4), dtype=torch.float32).pin_memory()
+
+    def timed(steps, e2e):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            for v in mine:
+                img, depth = r.render(cams[v])
+                if e2e:
+                    host_out.copy_(img, non_blocking=True)
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1))
+
+    timed(max(1, args.warmup // 3), False)
+    sampler.start()
+    ms = timed(args.steps, False)
+    clocks = sampler.stop()
+    ms_e2e = timed(args.steps, True)
+    mpix = len(cams) * W * H * args.steps / 1e6
+    launches_view = 1 + (1 + 12 + 2 + 3 * ((r.ctx.tile_bits + 7) // 8) + 1) + 1
+    return {"metric": "render Mpix/s", "value": mpix / (ms / 1e3), "unit": "Mpix/s", "ms_per_step": ms / args.steps, "scaling": "strong",
+            "config": {"cameras": len(cams), "splats": scene["n"], "sh_degree": scene["degree"], "resolution": f"{W}x{H}", "parallelism": f"cameras over {world} GPUs",
+                       "l2_policy": "inputs larger than L2", "scene_counts_view0": stats[0] if stats else None},
+            "e2e": {"value": mpix / (ms_e2e / 1e3), "unit": "Mpix/s", "h2d_bytes_per_step": 100 * len(cams), "d2h_bytes_per_step": 16 * W * H * len(mine)},
+            "gpu_launches": args.steps * len(mine) * launches_view, "clocks": clocks}
+
+
+if __name__ == "__main__":
+    main()

@@ -62,6 +62,9 @@ typedef struct {
   float* proj1;            /* [n][4] conic c11, opacity, view depth z, power = ln(255 opacity); power = -1: no record */
   float* proj2;            /* [n][4] r, g, b, 0 */
   uint32_t* tile_count;    /* [n] tiles hit */
+  uint32_t* hit_info;      /* [n][4] bit mask (lo, hi) of the hit tiles inside the splat's tile box, row-major; packed box
+                              min_x | min_y << 12 | width << 24; unused. Boxes above 64 tiles carry box = 0xFFFFFFFF and are
+                              re-tested when emitted (the reference keeps a 32-tile mask, src/gpu/project.cu:33-43) */
   uint32_t* depth_keys;    /* [n] scratch of the depth sort */
   uint32_t* depth_keys_sorted; /* [n] b2k_project leaves the unsorted keys here; b2k_bin_sort sorts them in place */
   uint32_t* order_in;      /* [n] scratch of the depth sort */
@@ -130,8 +133,9 @@ int b2k_bin_sort(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
 int b2k_read_num_isect(const B2kCtx* ctx, b2k_stream_t s, uint32_t* total);
 /* rasterize_forward, src/gpu/render.h:103 (raster_fwd_kernel, src/gpu/raster_fwd.cu:9-71). */
 int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s);
-/* Scratch bytes b2k_bin_sort needs for n splats and isect_cap intersections (replaces RenderCtx::cub_tmp). */
-uint64_t b2k_sort_tmp_bytes(int32_t n, uint64_t isect_cap);
+/* Scratch bytes b2k_project and b2k_bin_sort need in ctx->sort_tmp for a context whose per-splat buffers hold n_cap
+ * entries (replaces RenderCtx::cub_tmp, src/gpu/render.h:80). */
+uint64_t b2k_sort_tmp_bytes(int32_t n_cap, uint64_t isect_cap);
 
 /* ---- loss ---- */
 /* photometric_loss, src/gpu/loss.h:33 (photometric_kernel, src/gpu/loss.cu:18-195). */

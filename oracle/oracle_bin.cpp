@@ -17,7 +17,11 @@ inline float fsub(float a, float b) { return a - b; }
 inline float fdiv(float a, float b) { return a / b; }
 inline float clamp01(float x) { return fminf(fmaxf(x, 0.f), 1.f); }
 
-struct Rec { float mx, my, c00, c01, c11, power; };
+struct Rec {
+  float mx, my, c00, c01, c11, power;
+  float ia() const { return fdiv(1.f, fmul(64.f, c00)); }   // per-splat denominators of the closest-point parameters
+  float ib() const { return fdiv(1.f, fmul(64.f, c11)); }
+};
 
 inline float sigma_at(float px, float py, const Rec& r) {
   const float dx = fsub(px, r.mx), dy = fsub(py, r.my);
@@ -35,8 +39,8 @@ inline bool tile_hit(int tx, int ty, const Rec& r) {
   const float corner_x = x_left ? rmin_x : rmax_x, corner_y = y_above ? rmin_y : rmax_y;
   const float dxf = x_left ? (float)orc::TILE : -(float)orc::TILE, dyf = y_above ? (float)orc::TILE : -(float)orc::TILE;
   const float diff_x = fsub(r.mx, corner_x), diff_y = fsub(r.my, corner_y);
-  const float tx_raw = fdiv(fadd(fmul(fmul(dxf, r.c00), diff_x), fmul(fmul(dxf, r.c01), diff_y)), fmul(fmul(dxf, r.c00), dxf));
-  const float ty_raw = fdiv(fadd(fmul(fmul(dyf, r.c01), diff_x), fmul(fmul(dyf, r.c11), diff_y)), fmul(fmul(dyf, r.c11), dyf));
+  const float tx_raw = fmul(fmul(dxf, fadd(fmul(r.c00, diff_x), fmul(r.c01, diff_y))), r.ia());
+  const float ty_raw = fmul(fmul(dyf, fadd(fmul(r.c01, diff_x), fmul(r.c11, diff_y))), r.ib());
   const float tx_c = in_y ? 0.f : clamp01(tx_raw), ty_c = in_x ? 0.f : clamp01(ty_raw);
   const float px = fadd(corner_x, fmul(tx_c, dxf)), py = fadd(corner_y, fmul(ty_c, dyf));
   return sigma_at(px, py, r) <= r.power;
