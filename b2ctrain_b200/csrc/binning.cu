@@ -57,23 +57,13 @@ __global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_
         k[v * 4] = q.x; k[v * 4 + 1] = q.y; k[v * 4 + 2] = q.z; k[v * 4 + 3] = q.w;
       }
 #pragma unroll
-      for (int j = 0; j < SORT_ITEMS; j++) {
-        const uint32_t d = (k[j] >> shift) & mask;
-        const uint32_t peers = __match_any_sync(0xffffffffu, d);
-        if (lane == __ffs(peers) - 1) s_hist[warp][d] += __popc(peers);
-        __syncwarp();
-      }
+      for (int j = 0; j < SORT_ITEMS; j++) atomicAdd(&s_hist[warp][(k[j] >> shift) & mask], 1u);
     } else {
 #pragma unroll
       for (int j = 0; j < SORT_ITEMS; j++) { const uint32_t i = tile + j * 32 + lane; k[j] = i < end ? keys[i] : 0u; }
 #pragma unroll
-      for (int j = 0; j < SORT_ITEMS; j++) {
-        const bool valid = tile + j * 32 + lane < end;
-        const uint32_t d = valid ? ((k[j] >> shift) & mask) : (0x10000u | lane);
-        const uint32_t peers = __match_any_sync(0xffffffffu, d);
-        if (valid && lane == __ffs(peers) - 1) s_hist[warp][d] += __popc(peers);
-        __syncwarp();
-      }
+      for (int j = 0; j < SORT_ITEMS; j++)
+        if (tile + j * 32 + lane < end) atomicAdd(&s_hist[warp][(k[j] >> shift) & mask], 1u);
     }
   }
   __syncthreads();
@@ -154,8 +144,14 @@ __global__ void __launch_bounds__(SORT_THREADS, 2) radix_scatter_kernel(
     for (int j = 0; j < SORT_ITEMS; j++) {
       const uint32_t li = wbase + j * 32 + lane;
       const bool valid = li < tile_n;
-      const uint32_t d = valid ? ((key[j] >> shift) & mask) : (0x10000u | lane);
-      const uint32_t peers = __match_any_sync(0xffffffffu, d);
+      const uint32_t d = (key[j] >> shift) & mask;
+      uint32_t peers = __ballot_sync(0xffffffffu, valid);   // lanes holding the same digit, from one vote per digit bit
+#pragma unroll
+      for (int b = 0; b < 8; b++) {
+        const bool bit = (d >> b) & 1u;
+        const uint32_t vote = __ballot_sync(0xffffffffu, bit);
+        peers &= bit ? vote : ~vote;
+      }
       uint32_t before = 0;
       if (valid) before = s_cnt[warp][d];
       __syncwarp();

@@ -1,69 +1,81 @@
-// Forward compositing: one CTA per 8x8 tile walks the tile's depth-ordered fragment list front to back.
-// Reference semantics: raster_fwd_kernel (src/gpu/raster_fwd.cu:9-71); the optional expected-depth output follows
-// the mean-depth mode of probe_kernel (src/gpu/probe.cu:30-46).
+// Forward compositing: one warp per 8x8 tile walks the tile's depth-ordered fragment list front to back, each lane
+// carrying two horizontally adjacent pixels. Reference semantics: raster_fwd_kernel (src/gpu/raster_fwd.cu:9-71); the
+// optional expected-depth output follows the mean-depth mode of probe_kernel (src/gpu/probe.cu:30-46).
 //
-// FP32-issue bound (one ex2 and ~25 flops per fragment-pixel); memory traffic is the gather of 48 B per staged
-// fragment, served mostly by L2. Fragments are staged 64 at a time in shared memory with 128-bit loads.
+// FP32-issue / latency bound (one ex2 and ~25 flops per fragment-pixel); memory traffic is the gather of 48 B per
+// staged fragment, served mostly by L2. Fragments are staged 32 at a time per warp in shared memory with 128-bit
+// loads; warps never synchronise with each other.
 #include "common.cuh"
 
 namespace b2k {
 namespace {
 
+constexpr int FWD_WARPS = 4;
+constexpr int FWD_BATCH = 32;
+
 template <bool BWD, bool DEPTH>
-__global__ void __launch_bounds__(RT_PX) raster_fwd_kernel(
+__global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
-    const float4* __restrict__ proj2, int W, int H, int tiles_x, float3 bg, float4* __restrict__ out_rgba, float4* __restrict__ out_feat,
+    const float4* __restrict__ proj2, int W, int H, int tiles_x, int n_tiles, float3 bg, float4* __restrict__ out_rgba, float4* __restrict__ out_feat,
     float* __restrict__ out_depth, uint32_t* __restrict__ last_idx) {
-  __shared__ float4 s0[RT_PX], s1[RT_PX], s2[RT_PX];
-  __shared__ uint32_t s_max_last;
-  const int tile = blockIdx.x;
+  __shared__ float4 s0[FWD_WARPS][FWD_BATCH], s1[FWD_WARPS][FWD_BATCH], s2[FWD_WARPS][FWD_BATCH];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x * FWD_WARPS + warp;
+  if (tile >= n_tiles) return;
   const int tx = tile % tiles_x, ty = tile / tiles_x;
-  const int lx = threadIdx.x % RT_W, ly = threadIdx.x / RT_W;
-  const int px = tx * RT_W + lx, py = ty * RT_W + ly;
-  const bool inside = px < W && py < H;
-  const float pcx = (float)px + 0.5f, pcy = (float)py + 0.5f;
+  const int px0 = tx * RT_W + (lane & 3) * 2, py = ty * RT_W + (lane >> 2);
+  const bool in0 = px0 < W && py < H, in1 = px0 + 1 < W && py < H;
+  const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
   const uint2 range = tile_ranges[tile];
-  if (threadIdx.x == 0) s_max_last = range.x;
-  float T = 1.f, r = 0.f, g = 0.f, b = 0.f, zs = 0.f;
-  bool done = !inside;
-  uint32_t last = range.x;
-  for (uint32_t start = range.x; start < range.y; start += RT_PX) {
-    if (__syncthreads_count(done) == RT_PX) break;
-    const uint32_t remaining = min((uint32_t)RT_PX, range.y - start);
-    if (threadIdx.x < remaining) {
-      const uint32_t gid = vals_sorted[start + threadIdx.x];
-      s0[threadIdx.x] = proj0[gid]; s1[threadIdx.x] = proj1[gid]; s2[threadIdx.x] = proj2[gid];
+  float T[2] = {1.f, 1.f}, r[2] = {0.f, 0.f}, g[2] = {0.f, 0.f}, b[2] = {0.f, 0.f}, zs[2] = {0.f, 0.f};
+  bool done[2] = {!in0, !in1};
+  uint32_t last[2] = {range.x, range.x};
+  for (uint32_t start = range.x; start < range.y; start += FWD_BATCH) {
+    if (__all_sync(0xffffffffu, done[0] && done[1])) break;
+    const uint32_t remaining = min((uint32_t)FWD_BATCH, range.y - start);
+    __syncwarp();
+    if ((uint32_t)lane < remaining) {
+      const uint32_t gid = vals_sorted[start + lane];
+      s0[warp][lane] = proj0[gid]; s1[warp][lane] = proj1[gid]; s2[warp][lane] = proj2[gid];
     }
-    __syncthreads();
-    if (!done) {
-      for (uint32_t t = 0; t < remaining; t++) {
-        const float4 a = s0[t], c = s1[t];
-        const float dx = pcx - a.x, dy = pcy - a.y;
+    __syncwarp();
+    for (uint32_t t = 0; t < remaining; t++) {
+      const float4 a = s0[warp][t], c = s1[warp][t], col = s2[warp][t];
+      const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+      const float dy = pcy - a.y;
+#pragma unroll
+      for (int p = 0; p < 2; p++) {
+        const float dx = pcx + (float)p - a.x;
         const float sigma = 0.5f * (a.z * dx * dx + c.x * dy * dy) + a.w * dx * dy;
-        if (sigma < 0.f || sigma > c.w) continue;          // alpha below 1/255
         const float alpha = fminf(ALPHA_MAX, c.y * __expf(-sigma));
-        const float next_T = T * (1.f - alpha);
-        if (next_T <= T_CUTOFF) { done = true; break; }    // stop before the fragment that would saturate the pixel
-        const float vis = alpha * T;
-        const float4 col = s2[t];
-        r += fmaxf(col.x, 0.f) * vis; g += fmaxf(col.y, 0.f) * vis; b += fmaxf(col.z, 0.f) * vis;
-        if constexpr (DEPTH) zs += vis * c.z;
-        T = next_T;
-        last = start + t + 1;
+        const float next_T = T[p] * (1.f - alpha);
+        const bool hit = !done[p] && sigma >= 0.f && sigma <= c.w;      // alpha >= 1/255
+        if (hit && next_T <= T_CUTOFF) done[p] = true;                   // stop before the fragment that would saturate the pixel
+        if (hit && !done[p]) {
+          const float vis = alpha * T[p];
+          r[p] += cr * vis; g[p] += cg * vis; b[p] += cb * vis;
+          if constexpr (DEPTH) zs[p] += vis * c.z;
+          T[p] = next_T;
+          last[p] = start + t + 1;
+        }
       }
     }
   }
-  if (inside) {
-    const int pix = py * W + px;
-    out_rgba[pix] = make_float4(r + T * bg.x, g + T * bg.y, b + T * bg.z, 1.f - T);
-    out_feat[pix] = make_float4(0.f, 0.f, 0.f, T);
-    if constexpr (DEPTH) out_depth[pix] = (1.f - T) > 0.05f ? zs / (1.f - T) : INFINITY;
-    if constexpr (BWD) last_idx[pix] = last;
+#pragma unroll
+  for (int p = 0; p < 2; p++) {
+    if (p == 0 ? in0 : in1) {
+      const int pix = py * W + px0 + p;
+      out_rgba[pix] = make_float4(r[p] + T[p] * bg.x, g[p] + T[p] * bg.y, b[p] + T[p] * bg.z, 1.f - T[p]);
+      out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
+      if constexpr (DEPTH) out_depth[pix] = (1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY;
+      if constexpr (BWD) last_idx[pix] = last[p];
+    }
   }
   if constexpr (BWD) {
-    atomicMax(&s_max_last, last);
-    __syncthreads();
-    if (threadIdx.x == 0) tile_ranges[tile].y = s_max_last;
+    uint32_t m = max(last[0], last[1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) tile_ranges[tile].y = m;   // the backward never needs to look past the last fragment any pixel used
   }
 }
 
@@ -78,8 +90,8 @@ extern "C" int b2k_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, b2k_strea
   B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y);
   cudaStream_t s = (cudaStream_t)stream;
   const float3 bg = make_float3(o->bg[0], o->bg[1], o->bg[2]);
-#define L(B, D) raster_fwd_kernel<B, D><<<c->n_tiles, RT_PX, 0, s>>>((uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, \
-    (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx)
+#define L(B, D) raster_fwd_kernel<B, D><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>((uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, \
+    (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, c->n_tiles, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx)
   if (o->bwd_info) { if (c->out_depth) L(true, true); else L(true, false); }
   else { if (c->out_depth) L(false, true); else L(false, false); }
 #undef L
