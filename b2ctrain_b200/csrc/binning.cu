@@ -23,7 +23,7 @@ constexpr int SORT_ITEMS = 16;
 constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;   // 4096 pairs per tile
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int RADIX = 256;
-constexpr int BLOCKS_PER_SM = 4;
+constexpr int BLOCKS_PER_SM = 2;               // resident scatter CTAs per SM: one wave covers the input
 
 __device__ __forceinline__ uint32_t seg_len(uint32_t n, uint32_t blocks) {
   uint32_t per = (n + blocks - 1) / blocks;
@@ -97,30 +97,41 @@ __global__ void __launch_bounds__(1024) radix_rows_kernel(uint32_t* __restrict__
   if (t < blocks) hist[(size_t)d * blocks + t] = s_warp[warp] + incl - v;
 }
 
-// Pass kernel 3: ranked, stable scatter of each block's segment.
-__global__ void __launch_bounds__(SORT_THREADS, 2) radix_scatter_kernel(
+// Pass kernel 3: ranked, stable scatter of each block's segment. 512 threads x 8 pairs per tile; the next tile's keys
+// and this tile's values are in flight while the current tile is ranked, so memory and ranking phases overlap.
+constexpr int SCAT_THREADS = 512;
+constexpr int SCAT_ITEMS = SORT_TILE / SCAT_THREADS;   // 8
+constexpr int SCAT_WARPS = SCAT_THREADS / 32;
+constexpr size_t SCAT_SMEM = 2 * SORT_TILE * sizeof(uint32_t);
+
+__global__ void __launch_bounds__(SCAT_THREADS, 2) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
     const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask, const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals) {
-  __shared__ uint32_t s_cnt[SORT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
+  __shared__ uint32_t s_cnt[SCAT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
   __shared__ uint32_t s_start[RADIX];             // first local slot of the digit inside the tile
   __shared__ uint32_t s_gbase[RADIX];             // running global slot of the digit for this block
   __shared__ uint32_t s_delta[RADIX];             // global slot = s_delta[digit] + local slot (mod 2^32)
-  __shared__ uint32_t s_scan[SORT_WARPS];
-  __shared__ uint32_t s_keys[SORT_TILE];
-  __shared__ uint32_t s_vals[SORT_TILE];
+  __shared__ uint32_t s_scan[RADIX / 32];
+  extern __shared__ uint32_t s_stage[];           // [2][SORT_TILE]: the tile's keys and values in digit order
+  uint32_t* s_keys = s_stage;
+  uint32_t* s_vals = s_stage + SORT_TILE;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t lane_lt = (1u << lane) - 1u;
   // Global base of (digit, block): exclusive scan of the digit totals + the block's offset inside the digit.
   {
-    const uint32_t tot = totals[tid];
-    uint32_t incl = tot;
+    uint32_t tot = 0, incl = 0;
+    if (tid < RADIX) {
+      tot = totals[tid]; incl = tot;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
-    if (lane == 31) s_scan[warp] = incl;
+      for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+      if (lane == 31) s_scan[warp] = incl;
+    }
     __syncthreads();
-    uint32_t pre = 0;
-    for (int w = 0; w < warp; w++) pre += s_scan[w];
-    s_gbase[tid] = pre + incl - tot + hist[(size_t)tid * gridDim.x + blockIdx.x];
+    if (tid < RADIX) {
+      uint32_t pre = 0;
+      for (int w = 0; w < warp; w++) pre += s_scan[w];
+      s_gbase[tid] = pre + incl - tot + hist[(size_t)tid * gridDim.x + blockIdx.x];
+    }
     __syncthreads();
   }
   const uint32_t n = load_n(n_ptr, n_max);
@@ -128,30 +139,24 @@ __global__ void __launch_bounds__(SORT_THREADS, 2) radix_scatter_kernel(
   const uint64_t begin64 = (uint64_t)blockIdx.x * len;
   const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
   const uint32_t end = (begin64 + len) < n ? (uint32_t)(begin64 + len) : n;
+  // Each warp owns 256 consecutive pairs of the tile; item j of lane l is pair j*32 + l of them, so (j, lane) order is
+  // input order.
+  const uint32_t wbase = warp * (32 * SCAT_ITEMS);
+  uint32_t key[SCAT_ITEMS];
+#pragma unroll
+  for (int j = 0; j < SCAT_ITEMS; j++) { const uint32_t i = begin + wbase + j * 32 + lane; key[j] = i < end ? keys_in[i] : 0xFFFFFFFFu; }
   for (uint32_t tile = begin; tile < end; tile += SORT_TILE) {
     const uint32_t tile_n = end - tile < SORT_TILE ? end - tile : SORT_TILE;
-    for (int i = tid; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_cnt[0][0])[i] = 0;
+    uint32_t val[SCAT_ITEMS], rank[SCAT_ITEMS];
+#pragma unroll
+    for (int j = 0; j < SCAT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; val[j] = li < tile_n ? vals_in[tile + li] : 0u; }
+    for (int i = tid; i < SCAT_WARPS * RADIX; i += SCAT_THREADS) (&s_cnt[0][0])[i] = 0;
     __syncthreads();
-    // Each warp owns 512 consecutive pairs; item j of lane l is pair j*32 + l of them, so (j, lane) order is input order.
-    uint32_t key[SORT_ITEMS], val[SORT_ITEMS], rank[SORT_ITEMS];
-    const uint32_t wbase = warp * (32 * SORT_ITEMS);
-    // All loads of the tile are issued before any ranking work: 32 independent requests per lane.
 #pragma unroll
-    for (int j = 0; j < SORT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; key[j] = li < tile_n ? keys_in[tile + li] : 0xFFFFFFFFu; }
-#pragma unroll
-    for (int j = 0; j < SORT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; val[j] = li < tile_n ? vals_in[tile + li] : 0u; }
-#pragma unroll
-    for (int j = 0; j < SORT_ITEMS; j++) {
-      const uint32_t li = wbase + j * 32 + lane;
-      const bool valid = li < tile_n;
-      const uint32_t d = (key[j] >> shift) & mask;
-      uint32_t peers = __ballot_sync(0xffffffffu, valid);   // lanes holding the same digit, from one vote per digit bit
-#pragma unroll
-      for (int b = 0; b < 8; b++) {
-        const bool bit = (d >> b) & 1u;
-        const uint32_t vote = __ballot_sync(0xffffffffu, bit);
-        peers &= bit ? vote : ~vote;
-      }
+    for (int j = 0; j < SCAT_ITEMS; j++) {
+      const bool valid = wbase + j * 32 + lane < tile_n;
+      const uint32_t d = valid ? ((key[j] >> shift) & mask) : (0x10000u | lane);
+      const uint32_t peers = __match_any_sync(0xffffffffu, d);
       uint32_t before = 0;
       if (valid) before = s_cnt[warp][d];
       __syncwarp();
@@ -161,35 +166,44 @@ __global__ void __launch_bounds__(SORT_THREADS, 2) radix_scatter_kernel(
     }
     __syncthreads();
     // Digit `tid`: offsets of the warps inside the digit, digit total, then the digit's first slot in the tile.
-    uint32_t total = 0;
+    uint32_t total = 0, incl = 0;
+    if (tid < RADIX) {
 #pragma unroll
-    for (int w = 0; w < SORT_WARPS; w++) { const uint32_t c = s_cnt[w][tid]; s_cnt[w][tid] = total; total += c; }
-    uint32_t incl = total;
+      for (int w = 0; w < SCAT_WARPS; w++) { const uint32_t c = s_cnt[w][tid]; s_cnt[w][tid] = total; total += c; }
+      incl = total;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
-    if (lane == 31) s_scan[warp] = incl;
+      for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+      if (lane == 31) s_scan[warp] = incl;
+    }
     __syncthreads();
-    uint32_t pre = 0;
-    for (int w = 0; w < warp; w++) pre += s_scan[w];
-    const uint32_t start = pre + incl - total;
-    s_start[tid] = start;
-    s_delta[tid] = s_gbase[tid] - start;
-    s_gbase[tid] += total;
+    if (tid < RADIX) {
+      uint32_t pre = 0;
+      for (int w = 0; w < warp; w++) pre += s_scan[w];
+      const uint32_t start = pre + incl - total;
+      s_start[tid] = start;
+      s_delta[tid] = s_gbase[tid] - start;
+      s_gbase[tid] += total;
+    }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < SORT_ITEMS; j++) {
-      const uint32_t li = wbase + j * 32 + lane;
-      if (li < tile_n) {
+    for (int j = 0; j < SCAT_ITEMS; j++) {
+      if (wbase + j * 32 + lane < tile_n) {
         const uint32_t d = (key[j] >> shift) & mask;
         const uint32_t slot = s_start[d] + s_cnt[warp][d] + rank[j];
         s_keys[slot] = key[j];
         s_vals[slot] = val[j];
       }
     }
+    // Prefetch the next tile's keys; they land while this tile is written out.
+    {
+      const uint32_t next = tile + SORT_TILE;
+#pragma unroll
+      for (int j = 0; j < SCAT_ITEMS; j++) { const uint64_t i = (uint64_t)next + wbase + j * 32 + lane; key[j] = i < end ? keys_in[i] : 0xFFFFFFFFu; }
+    }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < SORT_ITEMS; j++) {
-      const uint32_t slot = j * SORT_THREADS + tid;
+    for (int j = 0; j < SCAT_ITEMS; j++) {
+      const uint32_t slot = j * SCAT_THREADS + tid;
       if (slot < tile_n) {
         const uint32_t k = s_keys[slot];
         const uint32_t dst = s_delta[(k >> shift) & mask] + slot;
@@ -364,7 +378,7 @@ SortScratch carve(const B2kCtx* c, int blocks) {
   s.hist = sort_tables_ptr(c);
   s.totals = s.hist + (size_t)RADIX * blocks;
   s.block_sums = s.totals + RADIX;
-  s.n_word = s.block_sums + blocks;
+  s.n_word = s.block_sums + 1024;   // block_sums holds up to 1024 entries (the emit grid differs from the sort grid)
   return s;
 }
 
@@ -374,13 +388,19 @@ SortScratch carve(const B2kCtx* c, int blocks) {
 int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uint32_t* n_ptr, uint32_t n_max, int bits, const SortScratch& sc,
                int blocks, cudaStream_t s) {
   const int passes = (bits + 7) / 8;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(radix_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAT_SMEM) != cudaSuccess) return check_launch();
+    attr_set[dev] = true;
+  }
   for (int p = 0; p < passes; p++) {
     const int shift = p * 8;
     const int pb = bits - shift < 8 ? bits - shift : 8;
     const uint32_t mask = (1u << pb) - 1u;
     radix_count_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist);
     radix_rows_kernel<<<RADIX, 1024, 0, s>>>(sc.hist, blocks, sc.totals);
-    radix_scatter_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals);
+    radix_scatter_kernel<<<blocks, SCAT_THREADS, SCAT_SMEM, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals);
     uint32_t* t = k0; k0 = k1; k1 = t;
     t = v0; v0 = v1; v1 = t;
   }
@@ -426,8 +446,9 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
   uint32_t* ov = (tile_passes % 2 == 0) ? c->vals : c->vals_sorted;
   uint32_t* big_emit_count = big_count_ptr(c) + 1;
   B2K_CUDA(cudaMemsetAsync(big_emit_count, 0, sizeof(uint32_t), s));
-  count_sums_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums);
-  scan_emit_kernel<<<blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums, (const uint4*)c->hit_info, c->tiles_x,
+  const int emit_blocks = sm_count() * 4 > 1024 ? 1024 : sm_count() * 4;
+  count_sums_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums);
+  scan_emit_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(n, c->order, c->tile_count, sc.block_sums, (const uint4*)c->hit_info, c->tiles_x,
                                                   (uint32_t)c->isect_cap, c->tile_off, ek, ev, c->num_isect, big_emit_ptr(c), big_emit_count);
   emit_big_kernel<<<sm_count() * 4, 256, 0, s>>>(big_emit_ptr(c), big_emit_count, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
                                                  c->tiles_x, c->tiles_y, (uint32_t)c->isect_cap, ek, ev);
