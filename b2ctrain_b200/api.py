@@ -74,6 +74,8 @@ SIGNATURES = {
     "b2k_project": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_bin_sort": (C.c_int, [_P, C.c_int32, _S]),
     "b2k_read_num_isect": (C.c_int, [_P, _S, _P]),
+    "b2k_bin_sort_static": (C.c_int, [_P, C.c_int32, _S]),
+    "b2k_static_max_splats": (C.c_uint32, []),
     "b2k_raster_fwd": (C.c_int, [_P, _P, _S]),
     "b2k_sort_tmp_bytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
     "b2k_loss_photometric": (C.c_int, [_P, _P, _S]),

@@ -468,3 +468,44 @@ extern "C" int b2k_read_num_isect(const B2kCtx* c, b2k_stream_t stream, uint32_t
   B2K_CUDA(cudaStreamSynchronize(s));
   return *total > c->isect_cap ? B2K_ERR_OVERFLOW : B2K_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Binning without any allocation on the caller's side.
+//
+// b2k_bin_sort needs a scratch buffer (ctx->sort_tmp) that somebody has to cudaMalloc. Some hosts of this library
+// cannot: a plugin loaded into a process whose memory pool is owned and fully reserved by the host application, a
+// render thread that must never take the allocator's lock, or a caller inside a region where the CUDA allocator is
+// off limits. For them the same scratch lives here, inside the library image, as a fixed device array. It is sized
+// for contexts of at most B2K_STATIC_MAX_SPLATS per-splat entries (about 4.2 MB, held by every GPU that loads the
+// library, until the process exits).
+// ---------------------------------------------------------------------------------------------------------------
+namespace b2k {
+namespace {
+constexpr uint32_t STATIC_MAX_SPLATS = 262144;
+constexpr size_t STATIC_WORDS = BIG_HEADER_WORDS + 3 * (size_t)STATIC_MAX_SPLATS + (size_t)RADIX * 1024 + RADIX + 1024 + 16;
+static __device__ __align__(256) uint32_t g_static_sort_tmp[STATIC_WORDS];
+// Device address of the array above, per device. In host code the array's name is only a handle for the runtime,
+// never a pointer a kernel may be given; the address has to be asked for, once per device, with that device current.
+void* g_static_addr[64] = {nullptr};
+}  // namespace
+}  // namespace b2k
+
+extern "C" uint32_t b2k_static_max_splats(void) { return b2k::STATIC_MAX_SPLATS; }
+
+extern "C" int b2k_bin_sort_static(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
+  B2K_REQUIRE(c && n >= 0);
+  if (c->n_cap < 0 || (uint32_t)c->n_cap > STATIC_MAX_SPLATS || (uint32_t)n > STATIC_MAX_SPLATS) return B2K_ERR_CAPACITY;
+  int dev = 0;
+  B2K_CUDA(cudaGetDevice(&dev));
+  B2K_REQUIRE(dev >= 0 && dev < 64);
+  if (!g_static_addr[dev]) {   // first call on this device: resolve the array's device address
+    void* p = nullptr;
+    B2K_CUDA(cudaGetSymbolAddress(&p, g_static_sort_tmp));
+    B2K_REQUIRE(p != nullptr);
+    g_static_addr[dev] = p;
+  }
+  B2kCtx local = *c;            // same buffers, scratch redirected to the library's own array
+  local.sort_tmp = g_static_addr[dev];
+  local.sort_tmp_bytes = sizeof(uint32_t) * STATIC_WORDS;
+  return b2k_bin_sort(&local, n, stream);
+}

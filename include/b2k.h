@@ -131,6 +131,14 @@ int b2k_bin_sort(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
 /* The 4-byte count readback of binning.cu:125-127 as its own call: waits for the stream, returns the total and
  * B2K_ERR_OVERFLOW when it exceeds ctx->isect_cap (the caller grows the four buffers and redoes the view). */
 int b2k_read_num_isect(const B2kCtx* ctx, b2k_stream_t s, uint32_t* total);
+/* b2k_bin_sort for callers that cannot allocate device memory (no counterpart in the reference). Identical results
+ * to b2k_bin_sort, but ctx->sort_tmp is ignored: the scratch is a fixed array inside the library, sized for contexts
+ * with n_cap <= b2k_static_max_splats() (262,144; larger ones get B2K_ERR_CAPACITY). The first call on a device looks
+ * the array's device address up (a synchronising runtime query): make that first call outside any stream capture.
+ * All calls on a device share the one array, so two calls whose kernels overlap on the GPU (different streams or
+ * threads) race; calls on one stream are safe. Nothing in it needs clearing by the caller. */
+int b2k_bin_sort_static(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
+uint32_t b2k_static_max_splats(void);
 /* rasterize_forward, src/gpu/render.h:103 (raster_fwd_kernel, src/gpu/raster_fwd.cu:9-71). */
 int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s);
 /* Scratch bytes b2k_project and b2k_bin_sort need in ctx->sort_tmp for a context whose per-splat buffers hold n_cap
