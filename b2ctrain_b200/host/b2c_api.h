@@ -1,0 +1,209 @@
+// C++ host mirror of the reference's operator interface for the splat hot path, implemented over the C ABI of
+// include/b2k.h. Same namespace, type names, member names and free-function signatures as the reference headers
+// (src/gpu/util.cuh, src/model.h, src/gpu/render.h, src/gpu/loss.h, src/gpu/optim.h), so a caller written against
+// those (the trainer's step loop, the render subcommand, the gradient test harness) compiles against this header.
+// Buffers are owned here (DevBuf); the C layer never allocates. Errors throw std::runtime_error, as CUDA_CHECK does in
+// the reference (src/gpu/util.cuh:13-15). Lanes that libb2k does not implement throw "unsupported lane".
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace b2c {
+
+#define B2C_CUDA_CHECK(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) \
+  throw std::runtime_error(std::string("CUDA error ") + cudaGetErrorString(e_) + " at " + __FILE__ + ":" + std::to_string(__LINE__)); } while (0)
+
+constexpr int RT_W = 8;   // rasteriser tile edge
+
+// Owning, grow-only device buffer (the role of DevBuf in src/gpu/util.cuh:26-57).
+template <typename T>
+struct DevBuf {
+  T* ptr = nullptr;
+  size_t count = 0;
+  DevBuf() = default;
+  DevBuf(const DevBuf&) = delete;
+  DevBuf& operator=(const DevBuf&) = delete;
+  DevBuf(DevBuf&& o) noexcept : ptr(o.ptr), count(o.count) { o.ptr = nullptr; o.count = 0; }
+  DevBuf& operator=(DevBuf&& o) noexcept { if (this != &o) { free(); ptr = o.ptr; count = o.count; o.ptr = nullptr; o.count = 0; } return *this; }
+  ~DevBuf() { free(); }
+  void free() { if (ptr) cudaFree(ptr); ptr = nullptr; count = 0; }
+  void reserve(size_t n, bool keep = false, cudaStream_t stream = 0) {
+    if (n <= count) return;
+    T* fresh = nullptr;
+    B2C_CUDA_CHECK(cudaMalloc(&fresh, n * sizeof(T)));
+    if (ptr) {
+      if (keep && count) B2C_CUDA_CHECK(cudaMemcpyAsync(fresh, ptr, count * sizeof(T), cudaMemcpyDeviceToDevice, stream));
+      B2C_CUDA_CHECK(cudaStreamSynchronize(stream));
+      cudaFree(ptr);
+    }
+    ptr = fresh; count = n;
+  }
+  void zero(cudaStream_t stream = 0, size_t n = (size_t)-1) { if (ptr) B2C_CUDA_CHECK(cudaMemsetAsync(ptr, 0, (n == (size_t)-1 ? count : n) * sizeof(T), stream)); }
+  void upload(const T* src, size_t n, cudaStream_t stream = 0) { reserve(n); B2C_CUDA_CHECK(cudaMemcpyAsync(ptr, src, n * sizeof(T), cudaMemcpyHostToDevice, stream)); }
+  void upload(const std::vector<T>& v, cudaStream_t stream = 0) { upload(v.data(), v.size(), stream); }
+  std::vector<T> download(size_t n = (size_t)-1, cudaStream_t stream = 0) const {
+    if (n == (size_t)-1) n = count;
+    std::vector<T> v(n);
+    if (n) { B2C_CUDA_CHECK(cudaMemcpyAsync(v.data(), ptr, n * sizeof(T), cudaMemcpyDeviceToHost, stream)); B2C_CUDA_CHECK(cudaStreamSynchronize(stream)); }
+    return v;
+  }
+  operator T*() const { return ptr; }
+};
+
+// Host splat cloud in the layout of SplatCloud (src/ply.h:12-22).
+struct SplatCloud {
+  size_t n = 0;
+  int sh_degree = 0;
+  std::vector<float> pos, log_scale, quat, opacity, sh;   // [n][3], [n][3], [n][4] (w,x,y,z), [n], [n][K][3]
+  std::vector<float> floor;                               // [n] 3D-filter floor, empty = none
+  int K() const { return (sh_degree + 1) * (sh_degree + 1); }
+  void resize(size_t count, int degree) {
+    n = count; sh_degree = degree;
+    pos.assign(n * 3, 0.f); log_scale.assign(n * 3, 0.f); quat.assign(n * 4, 0.f); opacity.assign(n, 0.f); sh.assign(n * K() * 3, 0.f);
+  }
+};
+
+// Pinhole camera, world-to-camera, OpenCV axes (src/dataset/camera.h:9-16).
+struct Camera {
+  int width = 0, height = 0;
+  float fx = 0, fy = 0, cx = 0, cy = 0;
+  float R[9] = {1, 0, 0, 0, 1, 0, 0, 0, 1};
+  float t[3] = {0, 0, 0};
+  float pos[3] = {0, 0, 0};
+  void update_pos() { for (int i = 0; i < 3; i++) pos[i] = -(R[i] * t[0] + R[3 + i] * t[1] + R[6 + i] * t[2]); }
+};
+
+// Device model (src/model.h:14-40): float4 parameter groups, planar SH with stride cap, moments, refine statistics.
+struct Model {
+  int n = 0, cap = 0, degree = 3;
+  bool sh_fp16 = false;   // not implemented by libb2k: upload() throws when set
+  DevBuf<float4> pos_op, quat, lscale;
+  DevBuf<float> sh_dc, sh_hi32;
+  DevBuf<float4> m_pos_op, v_pos_op, m_quat, v_quat, m_lscale, v_lscale;
+  DevBuf<float> m_sh_dc, m_sh_hi32, v_sh;
+  DevBuf<float> refine_norm, max_screen, vis_count, vis_weight;
+  DevBuf<uint32_t> last_step;
+  int adam_t = 0;
+  int K() const { return (degree + 1) * (degree + 1); }
+  void upload(const SplatCloud& c, cudaStream_t stream = 0);
+  SplatCloud download(cudaStream_t stream = 0) const;
+  void zero_optimizer(cudaStream_t stream = 0);
+  void zero_stats(cudaStream_t stream = 0);
+};
+
+// src/gpu/render.h:10-24.
+struct CameraGPU {
+  float R[9]; float t[3]; float pos[3];
+  float fx, fy, cx, cy;
+  int W, H;
+  float lim_pos_x, lim_pos_y, lim_neg_x, lim_neg_y;
+  static CameraGPU from(const Camera& c, int W, int H);
+};
+
+enum class FeatureMode { None, Normals, Buffer };
+
+// src/gpu/render.h:29-63. Fields of lanes libb2k does not implement are kept so callers compile; setting them throws.
+struct RenderParams {
+  CameraGPU cam;
+  float bg[3] = {0, 0, 0};
+  int sh_degree = 3;
+  FeatureMode feat = FeatureMode::None;
+  const float* feat_buffer = nullptr;
+  bool mip = false;
+  bool bwd_info = true;
+  const float2* warp = nullptr; int warp_w = 0, warp_h = 0;
+  const float4* pos_override = nullptr;
+  const float4* quat_override = nullptr;
+  const float4* lscale_override = nullptr;
+  const float4* sh_frame = nullptr;
+  const float4* app = nullptr; float4* col_base = nullptr; bool app_add = false;
+  const float* hollow_z = nullptr; float hollow_margin = 0.05f; float hollow_lam = 0.f;
+};
+
+// src/gpu/render.h:66-95; members the reference's callers read keep their names and element types.
+struct RenderCtx {
+  int W = 0, H = 0, tiles_x = 0, tiles_y = 0, n_tiles = 0, tile_bits = 0, n_cap = 0;
+  DevBuf<float4> proj0, proj1, proj2;
+  DevBuf<uint32_t> tile_count, tile_off;
+  DevBuf<uint4> hit_info;
+  DevBuf<uint32_t> depth_keys, depth_keys_sorted, order_in, order;
+  DevBuf<uint32_t> keys, vals, keys_sorted, vals_sorted;
+  size_t isect_cap = 0;
+  uint32_t num_isect = 0;
+  DevBuf<uint32_t> d_num_isect;
+  DevBuf<unsigned char> cub_tmp;       // the radix sort's scratch
+  DevBuf<uint2> tile_ranges;
+  DevBuf<float4> out_rgba, out_feat;
+  DevBuf<float> out_depth;             // optional expected depth (reserve it to enable)
+  DevBuf<uint32_t> last_idx;
+  DevBuf<float> v_splat;
+  DevBuf<uint32_t> vis_flag;
+  DevBuf<float4> v_out;
+  DevBuf<float> loss_accum;
+  bool want_depth = false;
+  void setup(int W, int H, int n_splats, cudaStream_t stream);
+};
+
+void render_forward(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream);
+void project_splats(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream);
+void bin_and_sort(RenderCtx& ctx, const Model& m, cudaStream_t stream);
+void rasterize_forward(RenderCtx& ctx, const RenderParams& p, cudaStream_t stream);
+void rasterize_backward(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream);
+// Same result as rasterize_backward: v_out carries grad_scale and the accumulated lanes are divided by it afterwards.
+void rasterize_backward_tc(RenderCtx& ctx, const Model& m, const RenderParams& p, float grad_scale, cudaStream_t stream);
+
+// src/gpu/loss.h:7-30.
+struct ViewGPU {
+  const uint32_t* rgba = nullptr;
+  const uint32_t* normals = nullptr;
+  const uint8_t* weights = nullptr;
+  const uint8_t* labels = nullptr;
+  int W = 0, H = 0;
+  bool has_alpha = false, masked = false;
+  float alpha_coverage = 1.f;
+};
+struct LossParams {
+  float l1_w = 0.8f, ssim_w = -0.2f;
+  float bg[3] = {0, 0, 0};
+  bool composite = false, mask = false, alpha_lane = false;
+  float match_alpha_weight = 0.1f;
+  float scale = 1.f;
+  float normal_scale = 0.f;
+  float grad_scale = 1.f;
+};
+void photometric_loss(RenderCtx& ctx, const ViewGPU& view, const LossParams& lp, cudaStream_t stream);
+void accumulate_loss(RenderCtx& ctx, cudaStream_t stream);
+void eval_metrics(RenderCtx& ctx, const ViewGPU& view, bool mask_weighted, cudaStream_t stream);
+
+// src/gpu/optim.h:6-45 (the fields of this path; the cage / deformation lanes throw when set).
+struct OptimParams {
+  CameraGPU cam;
+  bool mip = false;
+  int active_sh_degree = 3;
+  int t = 1;
+  float beta1 = 0.9f, beta2 = 0.999f, eps = 1e-15f;
+  float lr_mean = 0.f;
+  float lr_rot = 2e-3f, lr_scale = 5e-3f, lr_opac = 0.012f, lr_dc = 2e-3f, lr_sh_rest = 2e-4f;
+  float noise_weight = 0.f, noise_clamp = 0.f;
+  uint32_t seed = 42, step = 0;
+  const float4* pos_override = nullptr;
+  float3* g_pos_out = nullptr;
+  const float4* quat_override = nullptr;
+  const float4* lscale_override = nullptr;
+  const float4* sh_frame = nullptr;
+  bool frozen = false;
+  const uint8_t* update_mask = nullptr;
+  const float4* canon_rot = nullptr;
+  bool sparse = false;
+  float* grad_out = nullptr;
+};
+void optimizer_step(RenderCtx& ctx, Model& m, const OptimParams& op, cudaStream_t stream);
+// Data-parallel split of optimizer_step: gradient half adding into grad[n][11+3K], update half from it.
+void projection_backward(RenderCtx& ctx, Model& m, const OptimParams& op, float* grad, cudaStream_t stream);
+void adam_step(Model& m, const OptimParams& op, float* grad, cudaStream_t stream);
+void update_min_scale(Model& m, const float* cam_pos, const float* cam_focal, int n_cams, cudaStream_t stream);
+
+}  // namespace b2c

@@ -20,6 +20,18 @@ import torch
 from . import api
 
 
+def partition_views(n_views, rank, world):
+    """Views of a step taken by `rank`: round-robin, so every rank gets the same count (+-1) whatever the step size."""
+    return list(range(rank, n_views, world))
+
+
+def reduce_gradients(grad, world):
+    """Sum of the per-rank gradient accumulators over all ranks (NCCL on GPUs, gloo in the CPU tests)."""
+    if world > 1:
+        torch.distributed.all_reduce(grad, op=torch.distributed.ReduceOp.SUM)
+    return grad
+
+
 class Trainer:
     def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, lr_mean=1.6e-4, sparse=True, noise_weight=0.0,
                  noise_clamp=0.0, ssim_weight=0.2, isect_cap=None):
@@ -44,7 +56,7 @@ class Trainer:
         self.h2d_bytes = 0
 
     def my_views(self, n_views):
-        return list(range(self.rank, n_views, self.world))
+        return partition_views(n_views, self.rank, self.world)
 
     def _target(self, t, slot):
         """A device int32 tensor of packed RGBA8. Host (pinned) tensors are copied on the copy stream."""
@@ -96,8 +108,7 @@ class Trainer:
         for j, v in enumerate(mine):
             self.ctx.loss_accum[:2].zero_()
             self.view_pass(cams[v], targets[v], bg, slot=j & 1)
-        if self.world > 1:
-            torch.distributed.all_reduce(self.grad, op=torch.distributed.ReduceOp.SUM)
+        reduce_gradients(self.grad, self.world)
         api.adam_step(m, self._op(cams[0]), self.grad)
         return self.ctx.loss_accum
 

@@ -1,0 +1,58 @@
+"""Host-side logic of the data-parallel step on CPU: two gloo ranks share a step's views round-robin, each sums the
+(oracle) per-view parameter gradients of its share, one all-reduce gives every rank the sum over all views, and the
+identical Adam update keeps the replicas bit-identical. The GPU path runs the same partition / reduce code with NCCL."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r'''
+import os, sys
+sys.path.insert(0, os.environ["B2K_ROOT"])
+import numpy as np, torch, torch.distributed as dist
+from b2ctrain_b200 import scenes
+from b2ctrain_b200.trainer import partition_views, reduce_gradients
+from oracle import orc
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+scene = scenes.make_splats(300, 1, 5, log_scale=(-2.5, 0.4))
+cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, 40.0 * v, 10.0), 48, 40, 40.0) for v in range(5)]
+gt = np.random.Generator(np.random.PCG64(1)).integers(0, 2 ** 32, 48 * 40, dtype=np.uint64).astype(np.uint32)
+lp = dict(l1_w=np.float32(0.8), ssim_w=np.float32(-0.2))
+def view_grad(v): return orc.step(scene, cams[v], np.zeros(3), gt, None, lp, backward=True)["grad"]
+mine = partition_views(len(cams), rank, world)
+acc = np.zeros((scene["n"], 11 + 3 * 4))
+for v in mine: acc += view_grad(v)
+g = reduce_gradients(torch.from_numpy(acc.copy()), world).numpy()
+z4 = lambda: np.zeros((scene["n"], 4), np.float32)
+state = dict(pos_op=scene["pos_op"].copy(), quat=scene["quat"].copy(), lscale=scene["lscale"].copy(), sh=scene["sh"].copy(), m_pos=z4(), v_pos=z4(), m_q=z4(),
+             v_q=z4(), m_ls=z4(), v_ls=z4(), m_sh=np.zeros((scene["n"], 4, 3), np.float32), v_sh=np.zeros(scene["n"], np.float32), last_step=np.zeros(scene["n"], np.uint32))
+orc.adam(state, g, np.any(g != 0, axis=1), dict(t=1, lr_mean=1e-4, sparse=1), 1)
+np.savez(os.path.join(os.environ["B2K_OUT"], f"rank{rank}.npz"), mine=np.array(mine), g=g, pos=state["pos_op"], sh=state["sh"])
+if rank == 0:
+    total = np.zeros_like(acc)
+    for v in range(len(cams)): total += view_grad(v)
+    np.save(os.path.join(os.environ["B2K_OUT"], "serial.npy"), total)
+dist.destroy_process_group()
+'''
+
+
+def test_two_rank_gloo_step(tmp_path):
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29613", B2K_ROOT=ROOT, B2K_OUT=str(tmp_path),
+                   OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, "-c", WORKER], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    for p in procs:
+        out, err = p.communicate(timeout=240)
+        assert p.returncode == 0, err[-2000:]
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    serial = np.load(tmp_path / "serial.npy")
+    assert sorted(list(r0["mine"]) + list(r1["mine"])) == [0, 1, 2, 3, 4] and abs(len(r0["mine"]) - len(r1["mine"])) <= 1
+    assert np.array_equal(r0["g"], r1["g"])                       # every rank holds the same reduced gradient
+    assert np.allclose(r0["g"], serial, rtol=1e-12, atol=1e-15)    # = the sum of the per-view gradients
+    assert np.array_equal(r0["pos"], r1["pos"]) and np.array_equal(r0["sh"], r1["sh"])   # replicas stay bit-identical
+    assert np.abs(r0["g"]).max() > 0

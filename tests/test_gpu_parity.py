@@ -318,3 +318,34 @@ def test_min_scale_and_pack():
     out = h.torch.zeros(1000, dtype=h.torch.int32, device="cuda:0")
     h.api.pack_rgba8(h.torch.from_numpy(img).cuda(), out)
     assert np.array_equal(out.cpu().numpy().view(np.uint32), scenes.pack_rgba8(img))
+
+
+def test_multi_view_accumulation_equals_sum_of_view_gradients():
+    """Data-parallel semantics: the accumulator after several views == the sum of the per-view grad_out gradients, and
+    the split Adam consumes (and clears) it."""
+    from b2ctrain_b200.trainer import Trainer
+    scene, cam0 = small_scene(n=3000, degree=2)
+    cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, a, 10.0), 160, 120, 120.0) for a in (10.0, 60.0, 130.0)]
+    rng = np.random.Generator(np.random.PCG64(77))
+    gts = [rng.integers(0, 2 ** 32, 160 * 120, dtype=np.uint64).astype(np.uint32) | np.uint32(0xFF000000) for _ in cams]
+    lp = dict(l1_w=0.8, ssim_w=-0.2)
+    total = 0
+    for cam, gt in zip(cams, gts):
+        _, g = Harness(scene, cam, gt, None, lp).analytic()
+        total = total + g.astype(np.float64)
+    import torch
+    tr = Trainer(scene, 160, 120, "cuda:0", 0, 1, lr_mean=1e-4, sparse=True)
+    targets = [torch.from_numpy(g.view(np.int32)).cuda() for g in gts]
+    tr.model.adam_t += 1
+    for cam, t in zip(cams, targets):
+        tr.view_pass(cam, t)
+    got = tr.grad.cpu().numpy()
+    assert rel_l2(got, total) <= 1e-5
+    before = tr.model.download()
+    tr.api = None
+    from b2ctrain_b200 import api
+    api.adam_step(tr.model, tr._op(cams[0]), tr.grad)
+    after = tr.model.download()
+    assert float(tr.grad.abs().max()) == 0.0
+    moved = np.any(before["pos_op"] != after["pos_op"], axis=1)
+    assert np.array_equal(moved, np.any(got[:, :4] != 0, axis=1) | moved) and moved.sum() > 100

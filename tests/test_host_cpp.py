@@ -1,0 +1,65 @@
+"""The C++ host mirror of the reference API (b2ctrain_b200/host): it builds with the host compiler, and its Harness
+(the mould of the reference's own test harness, tests/tests.cpp:61-102) reproduces the oracle's loss and gradients."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from oracle import orc
+from tests.util import TOL_GRAD_REL_L2, TOL_IMAGE_ABS, TOL_LOSS_REL, check_against_fd, load_gradcheck, rel_l2
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HOST = os.path.join(ROOT, "b2ctrain_b200", "host")
+
+
+def build_harness():
+    from b2ctrain_b200 import build
+    build.build()
+    subprocess.run(["make", "-C", HOST], check=True, capture_output=True)
+    return os.path.join(HOST, "harness")
+
+
+def test_host_mirror_builds():
+    exe = build_harness()
+    assert os.path.exists(exe)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 2 and "usage" in r.stderr
+
+
+def write_scene(path, scene, cam, gt, wts, lp):
+    n, deg = scene["n"], scene["degree"]
+    with open(path, "wb") as f:
+        np.array([n, deg, cam["W"], cam["H"], int(lp.get("composite", 0)), int(lp.get("mask", 0)), int(lp.get("alpha_lane", 0)),
+                  int(wts is not None)], np.int32).tofile(f)
+        fl = [cam["fx"], cam["fy"], cam["cx"], cam["cy"], *cam["R"], *cam["t"], *lp.get("bg", (0, 0, 0)), lp.get("l1_w", 0.8),
+              lp.get("ssim_w", -0.2), lp.get("match_alpha_weight", 0.1), lp.get("scale", 1.0)]
+        np.array(fl, np.float32).tofile(f)
+        for a in (scene["pos_op"][:, :3], scene["lscale"][:, :3], scene["quat"], scene["pos_op"][:, 3], scene["lscale"][:, 3], scene["sh"]):
+            np.ascontiguousarray(a, np.float32).tofile(f)
+        np.ascontiguousarray(gt, np.uint32).tofile(f)
+        if wts is not None:
+            np.ascontiguousarray(wts, np.uint8).tofile(f)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1])
+def test_host_harness_matches_oracle_and_reference_golden(mode, tmp_path):
+    exe = build_harness()
+    scene, cam, gt, wts, lp, z = load_gradcheck(mode)
+    write_scene(tmp_path / "scene.bin", scene, cam, gt, wts, lp)
+    r = subprocess.run([exe, str(tmp_path / "scene.bin"), str(tmp_path / "out.bin")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    raw = open(tmp_path / "out.bin", "rb").read()
+    loss = np.frombuffer(raw, np.float64, 1, 0)[0]
+    isect, threw = np.frombuffer(raw, np.uint32, 2, 8)
+    P, per = cam["W"] * cam["H"], 11 + 3 * (scene["degree"] + 1) ** 2
+    img = np.frombuffer(raw, np.float32, P * 4, 16).reshape(P, 4)
+    grad = np.frombuffer(raw, np.float32, scene["n"] * per, 16 + P * 16).reshape(scene["n"], per)
+    assert threw == 1 and isect > 0
+    assert abs(loss - float(z["ref_loss"])) <= TOL_LOSS_REL * abs(float(z["ref_loss"]))
+    want = orc.step(scene, cam, np.array(lp["bg"], np.float64), gt, wts, lp, backward=True, want_image=True)
+    assert np.max(np.abs(img - want["rgba"])) <= TOL_IMAGE_ABS
+    assert rel_l2(grad, want["grad"]) <= TOL_GRAD_REL_L2
+    fails, total, _ = check_against_fd(grad, z)
+    assert fails == 0 and total > 150
