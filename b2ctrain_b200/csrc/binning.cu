@@ -108,7 +108,6 @@ __global__ void __launch_bounds__(SCAT_THREADS, 2) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
     const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask, const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals) {
   __shared__ uint32_t s_cnt[SCAT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
-  __shared__ uint32_t s_start[RADIX];             // first local slot of the digit inside the tile
   __shared__ uint32_t s_gbase[RADIX];             // running global slot of the digit for this block
   __shared__ uint32_t s_delta[RADIX];             // global slot = s_delta[digit] + local slot (mod 2^32)
   __shared__ uint32_t s_scan[RADIX / 32];
@@ -147,29 +146,35 @@ __global__ void __launch_bounds__(SCAT_THREADS, 2) radix_scatter_kernel(
   for (int j = 0; j < SCAT_ITEMS; j++) { const uint32_t i = begin + wbase + j * 32 + lane; key[j] = i < end ? keys_in[i] : 0xFFFFFFFFu; }
   for (uint32_t tile = begin; tile < end; tile += SORT_TILE) {
     const uint32_t tile_n = end - tile < SORT_TILE ? end - tile : SORT_TILE;
+    const bool full = tile_n == SORT_TILE;
     uint32_t val[SCAT_ITEMS], rank[SCAT_ITEMS];
+    if (full) {
 #pragma unroll
-    for (int j = 0; j < SCAT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; val[j] = li < tile_n ? vals_in[tile + li] : 0u; }
+      for (int j = 0; j < SCAT_ITEMS; j++) val[j] = vals_in[tile + wbase + j * 32 + lane];
+    } else {
+#pragma unroll
+      for (int j = 0; j < SCAT_ITEMS; j++) { const uint32_t li = wbase + j * 32 + lane; val[j] = li < tile_n ? vals_in[tile + li] : 0u; }
+    }
     for (int i = tid; i < SCAT_WARPS * RADIX; i += SCAT_THREADS) (&s_cnt[0][0])[i] = 0;
     __syncthreads();
+    // Rank of every pair among the warp's pairs with the same digit: lanes holding the digit are found with one match,
+    // the lowest of them bumps the warp's counter for the digit (one shared-memory atomic) and hands the old value out.
 #pragma unroll
     for (int j = 0; j < SCAT_ITEMS; j++) {
-      const bool valid = wbase + j * 32 + lane < tile_n;
+      const bool valid = full || wbase + j * 32 + lane < tile_n;
       const uint32_t d = valid ? ((key[j] >> shift) & mask) : (0x10000u | lane);
       const uint32_t peers = __match_any_sync(0xffffffffu, d);
-      uint32_t before = 0;
-      if (valid) before = s_cnt[warp][d];
-      __syncwarp();
-      if (valid && lane == __ffs(peers) - 1) s_cnt[warp][d] = before + __popc(peers);
-      __syncwarp();
-      rank[j] = before + __popc(peers & lane_lt);
+      const int leader = __ffs(peers) - 1;
+      uint32_t old = 0;
+      if (valid && lane == leader) old = atomicAdd(&s_cnt[warp][d], (uint32_t)__popc(peers));
+      rank[j] = __shfl_sync(0xffffffffu, old, leader) + __popc(peers & lane_lt);
     }
     __syncthreads();
-    // Digit `tid`: offsets of the warps inside the digit, digit total, then the digit's first slot in the tile.
+    // Digit `tid`: the digit's first slot in the tile, and for every warp its first slot inside the digit.
     uint32_t total = 0, incl = 0;
     if (tid < RADIX) {
 #pragma unroll
-      for (int w = 0; w < SCAT_WARPS; w++) { const uint32_t c = s_cnt[w][tid]; s_cnt[w][tid] = total; total += c; }
+      for (int w = 0; w < SCAT_WARPS; w++) total += s_cnt[w][tid];
       incl = total;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
@@ -179,17 +184,17 @@ __global__ void __launch_bounds__(SCAT_THREADS, 2) radix_scatter_kernel(
     if (tid < RADIX) {
       uint32_t pre = 0;
       for (int w = 0; w < warp; w++) pre += s_scan[w];
-      const uint32_t start = pre + incl - total;
-      s_start[tid] = start;
-      s_delta[tid] = s_gbase[tid] - start;
+      uint32_t at = pre + incl - total;       // first slot of the digit
+      s_delta[tid] = s_gbase[tid] - at;
       s_gbase[tid] += total;
+#pragma unroll
+      for (int w = 0; w < SCAT_WARPS; w++) { const uint32_t c = s_cnt[w][tid]; s_cnt[w][tid] = at; at += c; }
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < SCAT_ITEMS; j++) {
-      if (wbase + j * 32 + lane < tile_n) {
-        const uint32_t d = (key[j] >> shift) & mask;
-        const uint32_t slot = s_start[d] + s_cnt[warp][d] + rank[j];
+      if (full || wbase + j * 32 + lane < tile_n) {
+        const uint32_t slot = s_cnt[warp][(key[j] >> shift) & mask] + rank[j];
         s_keys[slot] = key[j];
         s_vals[slot] = val[j];
       }
@@ -204,7 +209,7 @@ __global__ void __launch_bounds__(SCAT_THREADS, 2) radix_scatter_kernel(
 #pragma unroll
     for (int j = 0; j < SCAT_ITEMS; j++) {
       const uint32_t slot = j * SCAT_THREADS + tid;
-      if (slot < tile_n) {
+      if (full || slot < tile_n) {
         const uint32_t k = s_keys[slot];
         const uint32_t dst = s_delta[(k >> shift) & mask] + slot;
         keys_out[dst] = k;
