@@ -45,7 +45,7 @@ class B2kCtx(C.Structure):
                 ("tile_off", C.c_void_p), ("keys", C.c_void_p), ("vals", C.c_void_p), ("keys_sorted", C.c_void_p),
                 ("vals_sorted", C.c_void_p), ("isect_cap", C.c_uint64), ("num_isect", C.c_void_p), ("sort_tmp", C.c_void_p),
                 ("sort_tmp_bytes", C.c_uint64), ("tile_ranges", C.c_void_p), ("out_rgba", C.c_void_p), ("out_feat", C.c_void_p),
-                ("out_depth", C.c_void_p), ("last_idx", C.c_void_p), ("v_splat", C.c_void_p), ("vis_flag", C.c_void_p),
+                ("out_depth", C.c_void_p), ("last_idx", C.c_void_p), ("v_splat", C.c_void_p), ("vis_flag", C.c_void_p), ("vis_list", C.c_void_p),
                 ("v_out", C.c_void_p), ("loss_accum", C.c_void_p)]
 
 
@@ -250,6 +250,7 @@ class RenderCtx:
             self.hit_info = u32(n, 4)
             self.depth_keys, self.depth_keys_sorted, self.order_in, self.order = u32(n), u32(n), u32(n), u32(n)
             self.v_splat, self.vis_flag = f32(n, GRAD_LANES), u32(n)
+            self.vis_list = u32(n)
             self.n_cap = n
         P = self.W * self.H
         self.tile_ranges = u32(self.n_tiles, 2)
@@ -275,7 +276,7 @@ class RenderCtx:
             setattr(s, k, getattr(self, k))
         for k in ("proj0", "proj1", "proj2", "tile_count", "hit_info", "depth_keys", "depth_keys_sorted", "order_in", "order", "tile_off", "keys",
                   "vals", "keys_sorted", "vals_sorted", "sort_tmp", "tile_ranges", "out_rgba", "out_feat", "out_depth", "last_idx",
-                  "v_splat", "vis_flag", "v_out", "loss_accum"):
+                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum"):
             t = getattr(self, k, None)
             setattr(s, k, None if t is None else t.data_ptr())
         s.num_isect = self.d_num_isect.data_ptr()

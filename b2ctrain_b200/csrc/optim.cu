@@ -280,9 +280,11 @@ __device__ __forceinline__ void adam_update(int i, const ModelPtrs& mp, const B2
 template <int DEG>
 __global__ void __launch_bounds__(OPT_BLOCK) optim_fused_kernel(int n, ModelPtrs mp, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
                                                                 const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
-                                                                float* __restrict__ vis_count, CamDev cam, B2kOptim op) {
+                                                                float* __restrict__ vis_count, CamDev cam, B2kOptim op,
+                                                                const uint32_t* __restrict__ vis_list, const uint32_t* __restrict__ vis_list_count) {
   constexpr int K = (DEG + 1) * (DEG + 1);
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (vis_list) { if ((uint32_t)i >= *vis_list_count) return; i = (int)vis_list[i]; }   // sparse walk over the splats the backward touched
   if (i >= n) return;
   SplatGrad sg; float basis[K];
   const int active = op.active_sh_degree < DEG ? (op.active_sh_degree < 0 ? 0 : op.active_sh_degree) : DEG;
@@ -309,9 +311,11 @@ __global__ void __launch_bounds__(OPT_BLOCK) optim_fused_kernel(int n, ModelPtrs
 template <int DEG>
 __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
                                                              const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
-                                                             float* __restrict__ vis_count, CamDev cam, B2kOptim op, float* __restrict__ grad) {
+                                                             float* __restrict__ vis_count, CamDev cam, B2kOptim op, float* __restrict__ grad,
+                                                             const uint32_t* __restrict__ vis_list, const uint32_t* __restrict__ vis_list_count) {
   constexpr int K = (DEG + 1) * (DEG + 1);
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (vis_list) { if ((uint32_t)i >= *vis_list_count) return; i = (int)vis_list[i]; }
   if (i >= n) return;
   SplatGrad sg; float basis[K];
   const int active = op.active_sh_degree < DEG ? (op.active_sh_degree < 0 ? 0 : op.active_sh_degree) : DEG;
@@ -345,6 +349,25 @@ __global__ void __launch_bounds__(OPT_BLOCK) adam_kernel(int n, ModelPtrs mp, B2
   for (int k = 11; k < PER; k++) gsq += g[k] * g[k];
   gsq *= 1.f / (float)(K * 3);
   adam_update<DEG>(i, mp, op, pg, gsq, [&](int k, int ch) { return g[11 + k * 3 + ch]; }, any);
+}
+
+// Indices of the splats whose visibility flag the backward set, appended in no particular order (one atomic per warp).
+__global__ void __launch_bounds__(256) compact_vis_kernel(int n, const uint32_t* __restrict__ vis_flag, uint32_t* __restrict__ list, uint32_t* __restrict__ count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool on = i < n && vis_flag[i] != 0u;
+  const uint32_t m = __ballot_sync(0xffffffffu, on);
+  if (m == 0u) return;
+  const int lane = threadIdx.x & 31;
+  uint32_t base = 0;
+  if (lane == 0) base = atomicAdd(count, (uint32_t)__popc(m));
+  base = __shfl_sync(0xffffffffu, base, 0);
+  if (on) list[base + __popc(m & ((1u << lane) - 1u))] = (uint32_t)i;
+}
+
+int build_vis_list(const B2kCtx* c, int n, cudaStream_t s) {
+  B2K_CUDA(cudaMemsetAsync(c->num_isect + 1, 0, sizeof(uint32_t), s));
+  compact_vis_kernel<<<div_up(n, 256), 256, 0, s>>>(n, c->vis_flag, c->vis_list, c->num_isect + 1);
+  return check_launch();
 }
 
 ModelPtrs model_ptrs(const B2kModel* m) {
@@ -407,8 +430,11 @@ extern "C" int b2k_optim_fused(const B2kCtx* c, const B2kModel* m, const B2kCame
   if (!op->grad_out) B2K_REQUIRE(has_moments(m) && op->t >= 1);
   const CamDev cd = to_camdev(*cam);
   const ModelPtrs mp = model_ptrs(m);
+  // The list is complete only for what the sparse update needs: splats the backward touched.
+  const uint32_t* list = (c->vis_list && c->num_isect && op->sparse && !op->grad_out) ? c->vis_list : nullptr;
+  if (list) { st = build_vis_list(c, m->n, (cudaStream_t)stream); if (st) return st; }
   B2K_DISPATCH_DEG(m->degree, (optim_fused_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(
-      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op)));
+      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, list, list ? c->num_isect + 1 : nullptr)));
   return check_launch();
 }
 
@@ -419,8 +445,10 @@ extern "C" int b2k_proj_bwd(const B2kCtx* c, const B2kModel* m, const B2kCamera*
   if (m->n == 0) return B2K_OK;
   const CamDev cd = to_camdev(*cam);
   const ModelPtrs mp = model_ptrs(m);
+  const uint32_t* list = (c->vis_list && c->num_isect) ? c->vis_list : nullptr;   // the gradient half only ever needs touched splats
+  if (list) { st = build_vis_list(c, m->n, (cudaStream_t)stream); if (st) return st; }
   B2K_DISPATCH_DEG(m->degree, (proj_bwd_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(
-      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, grad)));
+      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, grad, list, list ? c->num_isect + 1 : nullptr)));
   return check_launch();
 }
 

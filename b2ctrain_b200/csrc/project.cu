@@ -143,7 +143,7 @@ int launch(const B2kModel* m, const CamDev& cam, const B2kRenderOpts* o, const B
       m->n, (size_t)m->cap, pos, quat, lscale, m->sh_dc, m->sh_hi, cam, active < 0 ? 0 : active, c->tiles_x, c->tiles_y,
       (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, (uint4*)c->hit_info, c->depth_keys_sorted, c->order, m->max_screen,
       big_list, big_count);
-  count_big_kernel<<<sm_count() * 4, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, cam.W, cam.H, c->tiles_x,
+  count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, cam.W, cam.H, c->tiles_x,
                                                   c->tiles_y, c->tile_count, c->depth_keys_sorted);
   return check_launch();
 }

@@ -6,8 +6,8 @@
 // reduced across the warp with a halving butterfly (16 shuffles for all lanes together, against 5 shuffles per lane
 // in a plain tree), after which lane 2L holds the tile's total of lane L and issues one global reduction. Fragment
 // records are staged per warp in shared memory, so the kernel has no block-wide barrier: warps are independent.
-// The per-pixel math is branch-free (a non-contributing fragment has alpha = 0 and adds exact zeros), which lets the
-// two pixels' dependent chains (ex2, rcp) interleave.
+// A fragment no pixel of the tile sees is rejected after the sigma test; otherwise the pair's math is branch-free (a
+// pixel that does not see the fragment has alpha = 0 and adds exact zeros) and runs on packed fp32x2 instructions.
 //
 // FP32-issue / latency bound: ~90 flops, one ex2 and one rcp per fragment-pixel, plus the reduction.
 #include "common.cuh"
@@ -49,36 +49,12 @@ __device__ __forceinline__ float warp_transpose_sum(float (&v)[16], int lane) {
 
 __device__ __forceinline__ float fast_sqrt(float x) { float r; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 
-struct PixelState { float T, Sr, Sg, Sb, vr, vg, vb, vow, inv_fa; uint32_t last; };
+// State of this lane's pixel pair, one float2 per quantity: the replay below runs on Blackwell's packed fp32x2
+// arithmetic (fma.rn.f32x2 and friends), one instruction for both pixels.
+struct PairState { float2 T, Sr, Sg, Sb, vr, vg, vb, vow, inv_fa; uint32_t last0, last1; };
 
-// One fragment against one pixel, branch-free. Adds into acc; returns whether the fragment contributed.
-__device__ __forceinline__ bool replay(PixelState& s, float pcx, float pcy, uint32_t idx, const float4 a, const float4 c, float cr, float cg, float cb,
-                                       float Wf, float Hf, float (&acc)[16]) {
-  const float dx = pcx - a.x, dy = pcy - a.y;
-  const float sigma = 0.5f * (a.z * dx * dx + c.x * dy * dy) + a.w * dx * dy;
-  const bool on = idx < s.last && sigma >= 0.f && sigma <= c.w;
-  const float gauss = __expf(-sigma);
-  const float a_raw = c.y * gauss;
-  const float alpha = on ? fminf(ALPHA_MAX, a_raw) : 0.f;
-  const float ra = __fdividef(1.f, 1.f - alpha);
-  const float Tb = s.T * ra;
-  const float vis = alpha * Tb;
-  acc[5] += vis * s.vr; acc[6] += vis * s.vg; acc[7] += vis * s.vb;
-  const float v_alpha = (Tb * cr - s.Sr * ra) * s.vr + (Tb * cg - s.Sg * ra) * s.vg + (Tb * cb - s.Sb * ra) * s.vb + s.vow * ra;
-  // The alpha clamp has zero slope: the geometry and opacity lanes vanish where it is active.
-  const bool live = on && a_raw <= ALPHA_MAX;
-  const float v_sigma = live ? -alpha * v_alpha : 0.f;
-  const float gx = -v_sigma * (a.z * dx + a.w * dy), gy = -v_sigma * (a.w * dx + c.x * dy);
-  acc[0] += gx; acc[1] += gy;
-  acc[2] += 0.5f * v_sigma * dx * dx; acc[3] += v_sigma * dx * dy; acc[4] += 0.5f * v_sigma * dy * dy;
-  acc[8] += live ? v_alpha * gauss : 0.f;
-  const float sx = gx * Wf, sy = gy * Hf;
-  acc[9] += fast_sqrt(sx * sx + sy * sy) * s.inv_fa;
-  s.Sr += cr * vis; s.Sg += cg * vis; s.Sb += cb * vis;
-  s.T = Tb;
-  acc[10] += vis;
-  return on;
-}
+__device__ __forceinline__ float2 f2(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float hsum(float2 v) { return v.x + v.y; }
 
 __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
@@ -95,21 +71,27 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
   const int tx = tile % tiles_x, ty = tile / tiles_x;
   const int px0 = tx * RT_W + (lane & 3) * 2, py = ty * RT_W + (lane >> 2);   // this lane's pixel pair (px0, px0 + 1) on row py
 
-  PixelState st[2];
+  PairState st;
+  {
+    float T[2] = {0.f, 0.f}, vr[2] = {0.f, 0.f}, vg[2] = {0.f, 0.f}, vb[2] = {0.f, 0.f}, vow[2] = {0.f, 0.f}, ifa[2] = {0.f, 0.f};
+    uint32_t last[2] = {range.x, range.x};
 #pragma unroll
-  for (int p = 0; p < 2; p++) {
-    const int px = px0 + p;
-    PixelState& s = st[p];
-    s.T = 0.f; s.Sr = s.Sg = s.Sb = 0.f; s.vr = s.vg = s.vb = s.vow = 0.f; s.inv_fa = 0.f; s.last = range.x;
-    if (px < W && py < H) {
-      const int pix = py * W + px;
-      const float4 vo = v_out[pix];
-      s.T = out_feat[pix].w;
-      s.vr = vo.x; s.vg = vo.y; s.vb = vo.z;
-      s.vow = (vo.w - (bg.x * vo.x + bg.y * vo.y + bg.z * vo.z)) * s.T;
-      s.inv_fa = 1.f / fmaxf(out_rgba[pix].w, 1e-5f);
-      s.last = last_idx[pix];
+    for (int p = 0; p < 2; p++) {
+      const int px = px0 + p;
+      if (px < W && py < H) {
+        const int pix = py * W + px;
+        const float4 vo = v_out[pix];
+        T[p] = out_feat[pix].w;
+        vr[p] = vo.x; vg[p] = vo.y; vb[p] = vo.z;
+        vow[p] = (vo.w - (bg.x * vo.x + bg.y * vo.y + bg.z * vo.z)) * T[p];
+        ifa[p] = 1.f / fmaxf(out_rgba[pix].w, 1e-5f);
+        last[p] = last_idx[pix];
+      }
     }
+    st.T = make_float2(T[0], T[1]); st.Sr = st.Sg = st.Sb = f2(0.f);
+    st.vr = make_float2(vr[0], vr[1]); st.vg = make_float2(vg[0], vg[1]); st.vb = make_float2(vb[0], vb[1]);
+    st.vow = make_float2(vow[0], vow[1]); st.inv_fa = make_float2(ifa[0], ifa[1]);
+    st.last0 = last[0]; st.last1 = last[1];
   }
   const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
   const float Wf = (float)W, Hf = (float)H;
@@ -129,14 +111,49 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     __syncwarp();
     for (int j = (int)count - 1; j >= 0; j--) {
       const uint32_t idx = batch_start + (uint32_t)j;
-      const float4 a = frag[j].a, c = frag[j].c, col = frag[j].col;
+      const float4 a = frag[j].a, c = frag[j].c;
+      // sigma for the pair: the two pixels share the row, so dy and the dy terms are scalars.
+      const float dy = pcy - a.y;
+      const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
+      const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, f2(0.5f * a.z), f2(a.w * dy)), f2(0.5f * c.x * dy * dy));
+      const bool on0 = idx < st.last0 && sigma.x >= 0.f && sigma.x <= c.w;
+      const bool on1 = idx < st.last1 && sigma.y >= 0.f && sigma.y <= c.w;
+      if (__ballot_sync(FULL, on0 || on1) == 0) continue;   // nobody in the tile sees this fragment: skip the heavy part
+      const float4 col = frag[j].col;
       const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+      // Branch-free from here: a pixel that does not see the fragment has alpha = 0 and adds exact zeros.
+      const float2 gauss = make_float2(__expf(-sigma.x), __expf(-sigma.y));
+      const float2 a_raw = __fmul2_rn(f2(c.y), gauss);
+      const float2 alpha = make_float2(on0 ? fminf(ALPHA_MAX, a_raw.x) : 0.f, on1 ? fminf(ALPHA_MAX, a_raw.y) : 0.f);
+      const float2 ra = make_float2(__fdividef(1.f, 1.f - alpha.x), __fdividef(1.f, 1.f - alpha.y));
+      const float2 nra = make_float2(-ra.x, -ra.y);
+      const float2 Tb = __fmul2_rn(st.T, ra);
+      const float2 vis = __fmul2_rn(alpha, Tb);
+      float2 va = __fmul2_rn(st.vow, ra);
+      va = __ffma2_rn(__ffma2_rn(st.Sr, nra, __fmul2_rn(Tb, f2(cr))), st.vr, va);
+      va = __ffma2_rn(__ffma2_rn(st.Sg, nra, __fmul2_rn(Tb, f2(cg))), st.vg, va);
+      va = __ffma2_rn(__ffma2_rn(st.Sb, nra, __fmul2_rn(Tb, f2(cb))), st.vb, va);
+      // The alpha clamp has zero slope: the geometry and opacity lanes vanish where it is active.
+      const bool live0 = on0 && a_raw.x <= ALPHA_MAX, live1 = on1 && a_raw.y <= ALPHA_MAX;
+      const float2 av = __fmul2_rn(alpha, va);
+      const float2 mvs = make_float2(live0 ? av.x : 0.f, live1 ? av.y : 0.f);          // -v_sigma
+      const float2 gx = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.z), f2(a.w * dy)));
+      const float2 gy = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.w), f2(c.x * dy)));
+      const float2 mdx = __fmul2_rn(mvs, dx);
+      const float2 og = __fmul2_rn(va, gauss);
+      const float2 sx = __fmul2_rn(gx, f2(Wf)), sy = __fmul2_rn(gy, f2(Hf));
+      const float2 q = __ffma2_rn(sx, sx, __fmul2_rn(sy, sy));
+      const float2 rf = __fmul2_rn(make_float2(fast_sqrt(q.x), fast_sqrt(q.y)), st.inv_fa);
       float acc[16];
+      acc[0] = hsum(gx); acc[1] = hsum(gy);
+      acc[2] = -0.5f * hsum(__fmul2_rn(mdx, dx)); acc[3] = -hsum(mdx) * dy; acc[4] = -0.5f * dy * dy * hsum(mvs);
+      acc[5] = hsum(__fmul2_rn(vis, st.vr)); acc[6] = hsum(__fmul2_rn(vis, st.vg)); acc[7] = hsum(__fmul2_rn(vis, st.vb));
+      acc[8] = (live0 ? og.x : 0.f) + (live1 ? og.y : 0.f);
+      acc[9] = hsum(rf); acc[10] = hsum(vis);
 #pragma unroll
-      for (int k = 0; k < 16; k++) acc[k] = 0.f;
-      const bool on0 = replay(st[0], pcx, pcy, idx, a, c, cr, cg, cb, Wf, Hf, acc);
-      const bool on1 = replay(st[1], pcx + 1.f, pcy, idx, a, c, cr, cg, cb, Wf, Hf, acc);
-      if (__ballot_sync(FULL, on0 || on1) == 0) continue;
+      for (int k = 11; k < 16; k++) acc[k] = 0.f;
+      st.Sr = __ffma2_rn(f2(cr), vis, st.Sr); st.Sg = __ffma2_rn(f2(cg), vis, st.Sg); st.Sb = __ffma2_rn(f2(cb), vis, st.Sb);
+      st.T = Tb;
       if (col.x < 0.f) acc[5] = 0.f;   // the colour clamp at zero has zero slope
       if (col.y < 0.f) acc[6] = 0.f;
       if (col.z < 0.f) acc[7] = 0.f;

@@ -40,18 +40,23 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     }
     __syncwarp();
     for (uint32_t t = 0; t < remaining; t++) {
-      const float4 a = s0[warp][t], c = s1[warp][t], col = s2[warp][t];
-      const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+      const float4 a = s0[warp][t], c = s1[warp][t];
+      // sigma for the pixel pair in one packed fp32x2 chain (the pixels share the row: dy terms are scalars)
       const float dy = pcy - a.y;
+      const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
+      const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, make_float2(0.5f * a.z, 0.5f * a.z), make_float2(a.w * dy, a.w * dy)),
+                                      make_float2(0.5f * c.x * dy * dy, 0.5f * c.x * dy * dy));
+      bool hit[2] = {!done[0] && sigma.x >= 0.f && sigma.x <= c.w, !done[1] && sigma.y >= 0.f && sigma.y <= c.w};   // alpha >= 1/255
+      if (!__any_sync(0xffffffffu, hit[0] || hit[1])) continue;
+      const float4 col = s2[warp][t];
+      const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+      const float sg[2] = {sigma.x, sigma.y};
 #pragma unroll
       for (int p = 0; p < 2; p++) {
-        const float dx = pcx + (float)p - a.x;
-        const float sigma = 0.5f * (a.z * dx * dx + c.x * dy * dy) + a.w * dx * dy;
-        const float alpha = fminf(ALPHA_MAX, c.y * __expf(-sigma));
+        const float alpha = fminf(ALPHA_MAX, c.y * __expf(-sg[p]));
         const float next_T = T[p] * (1.f - alpha);
-        const bool hit = !done[p] && sigma >= 0.f && sigma <= c.w;      // alpha >= 1/255
-        if (hit && next_T <= T_CUTOFF) done[p] = true;                   // stop before the fragment that would saturate the pixel
-        if (hit && !done[p]) {
+        if (hit[p] && next_T <= T_CUTOFF) { done[p] = true; hit[p] = false; }   // stop before the fragment that would saturate the pixel
+        if (hit[p]) {
           const float vis = alpha * T[p];
           r[p] += cr * vis; g[p] += cg * vis; b[p] += cb * vis;
           if constexpr (DEPTH) zs[p] += vis * c.z;

@@ -40,7 +40,7 @@ B2kCtx view_of(const RenderCtx& c) {
   v.sort_tmp = c.cub_tmp.ptr; v.sort_tmp_bytes = c.cub_tmp.count;
   v.tile_ranges = (uint32_t*)c.tile_ranges.ptr;
   v.out_rgba = (float*)c.out_rgba.ptr; v.out_feat = (float*)c.out_feat.ptr; v.out_depth = c.out_depth.ptr;
-  v.last_idx = c.last_idx.ptr; v.v_splat = c.v_splat.ptr; v.vis_flag = c.vis_flag.ptr; v.v_out = (float*)c.v_out.ptr;
+  v.last_idx = c.last_idx.ptr; v.v_splat = c.v_splat.ptr; v.vis_flag = c.vis_flag.ptr; v.vis_list = c.vis_list.ptr; v.v_out = (float*)c.v_out.ptr;
   v.loss_accum = c.loss_accum.ptr;
   return v;
 }
@@ -147,13 +147,15 @@ void RenderCtx::setup(int w, int h, int n, cudaStream_t stream) {
     depth_keys.reserve(nn); depth_keys_sorted.reserve(nn); order_in.reserve(nn); order.reserve(nn);
     v_splat.free(); v_splat.reserve(nn * 13); v_splat.zero(stream);   // later clears are the optimizer's job (render.cu:13-14)
     vis_flag.free(); vis_flag.reserve(nn); vis_flag.zero(stream);
+    vis_list.free(); vis_list.reserve(nn);
     n_cap = (int)nn;
   }
   tile_ranges.reserve(n_tiles);
   const size_t npx = (size_t)W * H;
   out_rgba.reserve(npx); out_feat.reserve(npx); last_idx.reserve(npx); v_out.reserve(npx);
   if (want_depth) out_depth.reserve(npx);
-  loss_accum.reserve(16); d_num_isect.reserve(4);
+  loss_accum.reserve(16);
+  if (!d_num_isect.ptr) { d_num_isect.reserve(4); d_num_isect.zero(stream); }
   if (isect_cap == 0) alloc_isect(*this, (size_t)1 << 22);   // starting capacity of the reference (render.cu:20)
   cub_tmp.reserve((size_t)b2k_sort_tmp_bytes(n_cap, isect_cap));
 }

@@ -141,6 +141,7 @@ struct RenderCtx {
   DevBuf<uint32_t> last_idx;
   DevBuf<float> v_splat;
   DevBuf<uint32_t> vis_flag;
+  DevBuf<uint32_t> vis_list;        // splats the backward touched (count in d_num_isect[1]); walked by the sparse optimizer
   DevBuf<float4> v_out;
   DevBuf<float> loss_accum;
   bool want_depth = false;

@@ -72,7 +72,8 @@ typedef struct {
   uint32_t* tile_off;      /* [n] inclusive scan of tile counts in depth order */
   uint32_t *keys, *vals, *keys_sorted, *vals_sorted; /* [isect_cap] tile id / splat index before and after the tile sort */
   uint64_t isect_cap;
-  uint32_t* num_isect;     /* device word: intersections of this view (may exceed isect_cap: overflow) */
+  uint32_t* num_isect;     /* [4] device words: [0] intersections of this view (may exceed isect_cap: overflow);
+                              [1] entries of vis_list */
   void* sort_tmp;          /* scratch of b2k_sort_tmp_bytes() bytes */
   uint64_t sort_tmp_bytes;
   uint32_t* tile_ranges;   /* [n_tiles][2] start, end into vals_sorted; end shrunk by the forward when bwd_info */
@@ -82,7 +83,10 @@ typedef struct {
                               mode of probe_kernel, src/gpu/probe.cu:30-46, fused into the forward) */
   uint32_t* last_idx;      /* [P] one past the last contributing sorted index */
   float* v_splat;          /* [n][13] screen-space gradient lanes, accumulated; cleared by the optimizer */
-  uint32_t* vis_flag;      /* [n] */
+  uint32_t* vis_flag;      /* [n] set by the backward for splats that contributed; cleared by the optimizer */
+  uint32_t* vis_list;      /* [n] scratch or NULL. When present, the sparse optimizer entry points first compact the set
+                              visibility flags into this list (count in num_isect[1]) and then walk only those splats
+                              instead of all n. */
   float* v_out;            /* [P][4] dL/d(rgba) */
   float* loss_accum;       /* [16] */
 } B2kCtx;
