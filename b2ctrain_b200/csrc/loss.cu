@@ -5,8 +5,10 @@
 // One CTA of 256 threads owns a 16x16 pixel tile and runs the three colour channels back to back over one staged
 // 36x36 footprint, so the float4 prediction and the packed target are read from global memory once per CTA (the
 // reference launches one CTA per channel and reads them three times) and the gradient leaves as one 128-bit store
-// per pixel. The work is a shared-memory stencil: forward separable blur of five moments, SSIM and its five partial
-// derivative maps, the same blur applied backwards.
+// per pixel. The work is a shared-memory stencil (forward separable blur of five moments, SSIM and its five partial
+// derivative maps, the same blur applied backwards) and shared-memory bandwidth bounds it, so every blur pass is
+// register-tiled: a thread produces four consecutive outputs from a fourteen-wide sliding window (3x fewer
+// shared-memory reads than one output per thread), fetched with 128-bit loads along rows.
 #include "common.cuh"
 
 namespace b2k {
@@ -33,20 +35,42 @@ struct LossArgs {
   float l1_w, ssim_w, bg[3]; int composite, mask, alpha_lane; float match_alpha_weight, scale, grad_scale;
 };
 
-constexpr size_t LOSS_SMEM = sizeof(float) * (4 * IN_W * IN_W      // pred r, g, b + alpha
-                                              + 3 * IN_W * IN_W    // effective target r, g, b
-                                              + IN_W * STAT_W * 5  // horizontal pass
-                                              + STAT_W * STAT_W * 5)
-                             + sizeof(float) * IN_W * IN_W;        // per-position loss mask M
+// Shared-memory planes of the loss kernel. Rows are padded so that every thread can fetch its sliding window with
+// aligned 128-bit loads: 36-wide footprint planes use a stride of 40 floats, 26-wide planes a stride of 28.
+constexpr int IN_S = 40, ST_S = 28;
+constexpr int H_ROWS = 40;                        // rows of the horizontal-pass planes (36 used; the vertical windows overrun into the pad)
+constexpr int OFF_P = 0;                          // [4][36][IN_S]   prediction r, g, b, alpha
+constexpr int OFF_GT = OFF_P + 4 * IN_W * IN_S;   // [36][IN_S]      packed target
+constexpr int OFF_M = OFF_GT + IN_W * IN_S;       // [26][ST_S]      loss weight M at the statistics positions
+constexpr int OFF_H = OFF_M + STAT_W * ST_S;      // [5][H_ROWS][ST_S]
+constexpr int OFF_V = OFF_H + 5 * H_ROWS * ST_S;  // [5][26][ST_S]
+constexpr int OFF_G = OFF_V + 5 * STAT_W * ST_S;  // [3][256]        per-channel gradients of the tile
+constexpr size_t LOSS_SMEM = sizeof(float) * (OFF_G + 3 * TILE_PX);
+
+// Eleven-tap sliding window: four consecutive outputs from fourteen consecutive inputs.
+__device__ __forceinline__ void window4(const float (&in)[16], const Gauss& g, float (&out)[4]) {
+#pragma unroll
+  for (int o = 0; o < 4; o++) {
+    float a = 0.f;
+#pragma unroll
+    for (int d = 0; d < 11; d++) a += g.w[d] * in[o + d];
+    out[o] = a;
+  }
+}
+__device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int q = 0; q < 4; q++) { const float4 t = reinterpret_cast<const float4*>(p)[q]; v[q * 4] = t.x; v[q * 4 + 1] = t.y; v[q * 4 + 2] = t.z; v[q * 4 + 3] = t.w; }
+}
 
 __global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __restrict__ pred, const uint32_t* __restrict__ gt, const uint8_t* __restrict__ weights,
                                                               int W, int H, int tiles_x, LossArgs lp, Gauss gauss, float4* __restrict__ v_out, float* __restrict__ loss_accum) {
-  extern __shared__ float smem[];
-  float* s_p = smem;                            // [4][IN_W*IN_W]
-  float* s_g = s_p + 4 * IN_W * IN_W;           // [3][IN_W*IN_W]
-  float* s_h = s_g + 3 * IN_W * IN_W;           // [IN_W*STAT_W][5]
-  float* s_v = s_h + IN_W * STAT_W * 5;         // [STAT_W*STAT_W][5]
-  float* s_m = s_v + STAT_W * STAT_W * 5;       // [IN_W*IN_W] M = weight * (mask ? gt alpha : 1) * scale / (3WH), 0 outside
+  extern __shared__ __align__(16) float smem[];
+  float* s_p = smem + OFF_P;
+  uint32_t* s_gt = reinterpret_cast<uint32_t*>(smem + OFF_GT);
+  float* s_m = smem + OFF_M;
+  float* s_h = smem + OFF_H;
+  float* s_v = smem + OFF_V;
+  float* s_grad = smem + OFF_G;
   __shared__ float s_red[TILE_PX / 32];
 
   const int tile = blockIdx.x, tid = threadIdx.x;
@@ -56,28 +80,35 @@ __global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __re
   const int gy = ty0 + ly, gx = tx0 + lx;
   const bool inside = gy < H && gx < W;
   const int pix = inside ? gy * W + gx : 0;
-  const int centre = (ly + 2 * HALO) * IN_W + lx + 2 * HALO;
+  const int centre = (ly + 2 * HALO) * IN_S + lx + 2 * HALO;
+  const int centre_m = (ly + HALO) * ST_S + lx + HALO;
 
+  // Stage the 36x36 footprint (zero outside the image, zero in the row pads).
   float flat_r = 0.f, flat_g = 0.f, flat_b = 0.f;   // per channel: max |pred - target| over the footprint
-  for (int i = tid; i < IN_W * IN_W; i += TILE_PX) {
-    const int fy = i / IN_W, fx = i % IN_W;
+  for (int i = tid; i < IN_W * IN_S; i += TILE_PX) {
+    const int fy = i / IN_S, fx = i % IN_S;
     const int y = ty0 + fy - 2 * HALO, x = tx0 + fx - 2 * HALO;
     float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-    float g0 = 0.f, g1 = 0.f, g2 = 0.f, M = 0.f;
-    if (y >= 0 && y < H && x >= 0 && x < W) {
+    uint32_t gp = 0xFF000000u;   // outside the image: opaque black, so the effective target is zero there (zero padding)
+    if (fx < IN_W && y >= 0 && y < H && x >= 0 && x < W) {
       const int q = y * W + x;
       p = pred[q];
-      const uint32_t gp = gt[q];
+      gp = gt[q];
       const float ga = unpack(gp, 3);
-      g0 = unpack(gp, 0); g1 = unpack(gp, 1); g2 = unpack(gp, 2);
+      float g0 = unpack(gp, 0), g1 = unpack(gp, 1), g2 = unpack(gp, 2);
       if (lp.composite) { g0 += (1.f - ga) * lp.bg[0]; g1 += (1.f - ga) * lp.bg[1]; g2 += (1.f - ga) * lp.bg[2]; }
-      const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
-      M = wp * (lp.mask ? ga : 1.f) * norm;
+      flat_r = fmaxf(flat_r, fabsf(p.x - g0)); flat_g = fmaxf(flat_g, fabsf(p.y - g1)); flat_b = fmaxf(flat_b, fabsf(p.z - g2));
+      const int sy = fy - HALO, sx = fx - HALO;
+      if (sy >= 0 && sy < STAT_W && sx >= 0 && sx < STAT_W) {
+        const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
+        s_m[sy * ST_S + sx] = wp * (lp.mask ? ga : 1.f) * norm;
+      }
+    } else {
+      const int sy = fy - HALO, sx = fx - HALO;
+      if (fx < IN_W && sy >= 0 && sy < STAT_W && sx >= 0 && sx < STAT_W) s_m[sy * ST_S + sx] = 0.f;   // outside the image
     }
-    s_p[i] = p.x; s_p[IN_W * IN_W + i] = p.y; s_p[2 * IN_W * IN_W + i] = p.z; s_p[3 * IN_W * IN_W + i] = p.w;
-    s_g[i] = g0; s_g[IN_W * IN_W + i] = g1; s_g[2 * IN_W * IN_W + i] = g2;
-    s_m[i] = M;
-    flat_r = fmaxf(flat_r, fabsf(p.x - g0)); flat_g = fmaxf(flat_g, fabsf(p.y - g1)); flat_b = fmaxf(flat_b, fabsf(p.z - g2));
+    s_p[i] = p.x; s_p[IN_W * IN_S + i] = p.y; s_p[2 * IN_W * IN_S + i] = p.z; s_p[3 * IN_W * IN_S + i] = p.w;
+    s_gt[i] = gp;
   }
   float gt_a = 0.f, wp_c = 1.f;
   if (inside) {
@@ -85,59 +116,85 @@ __global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __re
     wp_c = weights ? (float)weights[pix] * (1.f / 255.f) : 1.f;
   }
   __syncthreads();
-  if (lp.alpha_lane && inside) flat_r = fmaxf(flat_r, fabsf(s_p[3 * IN_W * IN_W + centre] - gt_a));
+  if (lp.alpha_lane && inside) flat_r = fmaxf(flat_r, fabsf(s_p[3 * IN_W * IN_S + centre] - gt_a));
 
   float loss_local = 0.f;
-  float4 grad = make_float4(0.f, 0.f, 0.f, 0.f);
   // Exact early exit per channel: where the prediction equals the effective target on the whole footprint (for the
   // first channel: and alpha matches on the tile) every gradient of that channel is exactly zero and SSIM is exactly
   // one, so only the constant term enters the loss.
   const bool nonflat[3] = {__syncthreads_or(flat_r > 0.f) != 0, __syncthreads_or(flat_g > 0.f) != 0, __syncthreads_or(flat_b > 0.f) != 0};
-  {
-    for (int c = 0; c < 3; c++) {
-      if (!nonflat[c]) { if (inside) loss_local += s_m[centre] * lp.ssim_w; continue; }
-      const float* P = s_p + c * IN_W * IN_W;
-      const float* G = s_g + c * IN_W * IN_W;
-      // Horizontal blur of the five moments: rows 0..35, output columns 0..25.
-      for (int i = tid; i < IN_W * STAT_W; i += TILE_PX) {
-        const int row = i / STAT_W, ox = i % STAT_W;
-        float sx = 0.f, sx2 = 0.f, sy = 0.f, sy2 = 0.f, sxy = 0.f;
+  for (int c = 0; c < 3; c++) {
+    if (!nonflat[c]) {
+      if (inside) loss_local += s_m[centre_m] * lp.ssim_w;
+      s_grad[c * TILE_PX + tid] = 0.f;
+      continue;
+    }
+    const float* P = s_p + c * IN_W * IN_S;
+    const float bg_c = lp.composite ? lp.bg[c] : 0.f;
+    // Pass 1, horizontal blur of the five moments. One thread = one row x four output columns (36 x 7 items).
+    if (tid < IN_W * 7) {
+      const int row = tid / 7, g4 = (tid % 7) * 4;
+      float x[16], y[16];
+      load16(P + row * IN_S + g4, x);
 #pragma unroll
-        for (int d = 0; d < 11; d++) {
-          const float w = gauss.w[d];
-          const float x = P[row * IN_W + ox + d], y = G[row * IN_W + ox + d];
-          sx += w * x; sx2 += w * x * x; sy += w * y; sy2 += w * y * y; sxy += w * x * y;
-        }
-        float* o = s_h + i * 5; o[0] = sx; o[1] = sx2; o[2] = sy; o[3] = sy2; o[4] = sxy;
+      for (int q = 0; q < 4; q++) {
+        const uint4 t = reinterpret_cast<const uint4*>(s_gt + row * IN_S + g4)[q];
+        const uint32_t w4[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) y[q * 4 + e] = unpack(w4[e], c) + (1.f - unpack(w4[e], 3)) * bg_c;
       }
-      __syncthreads();
-      // Vertical blur -> statistics at 26x26, SSIM there, partial derivative maps scaled by M * ssim_w.
-      for (int i = tid; i < STAT_W * STAT_W; i += TILE_PX) {
-        const int oy = i / STAT_W, ox = i % STAT_W;
-        float st[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+      float in[16], out[4];
+      float* hb = s_h + row * ST_S + g4;
+      window4(x, gauss, out); *reinterpret_cast<float4*>(hb) = make_float4(out[0], out[1], out[2], out[3]);
 #pragma unroll
-        for (int d = 0; d < 11; d++) {
-          const float w = gauss.w[d];
-          const float* h = s_h + ((oy + d) * STAT_W + ox) * 5;
+      for (int k = 0; k < 16; k++) in[k] = x[k] * x[k];
+      window4(in, gauss, out); *reinterpret_cast<float4*>(hb + H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
+      window4(y, gauss, out); *reinterpret_cast<float4*>(hb + 2 * H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
 #pragma unroll
-          for (int k = 0; k < 5; k++) st[k] += w * h[k];
-        }
-        const int fi = (oy + HALO) * IN_W + ox + HALO;
-        const float M = s_m[fi];   // zero outside the image
+      for (int k = 0; k < 16; k++) in[k] = y[k] * y[k];
+      window4(in, gauss, out); *reinterpret_cast<float4*>(hb + 3 * H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
+#pragma unroll
+      for (int k = 0; k < 16; k++) in[k] = x[k] * y[k];
+      window4(in, gauss, out); *reinterpret_cast<float4*>(hb + 4 * H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
+    }
+    __syncthreads();
+    // Pass 2, vertical blur -> statistics at 26 x 26, SSIM there, partial derivative maps scaled by M * ssim_w.
+    // One thread = one column x four output rows (26 x 7 items).
+    if (tid < STAT_W * 7) {
+      const int col = tid % STAT_W, r4 = (tid / STAT_W) * 4;
+      float st[5][4];
+#pragma unroll
+      for (int m = 0; m < 5; m++) {
+        float in[16];
+        const float* hp = s_h + m * H_ROWS * ST_S + r4 * ST_S + col;
+#pragma unroll
+        for (int k = 0; k < 14; k++) in[k] = hp[k * ST_S];
+        in[14] = in[15] = 0.f;
+        window4(in, gauss, st[m]);
+      }
+#pragma unroll
+      for (int o = 0; o < 4; o++) {
+        const int oy = r4 + o;
+        if (oy >= STAT_W) break;
+        const float M = s_m[oy * ST_S + col];   // zero outside the image
         float A = 0.f, B = 0.f, Bm = 0.f, Cc = 0.f, Cm = 0.f;
-        const int y = ty0 + oy - HALO, x = tx0 + ox - HALO;
-        if (y >= 0 && y < H && x >= 0 && x < W) {
-          const float mu1 = st[0], mu2 = st[2];
+        const int y = ty0 + oy - HALO, xg = tx0 + col - HALO;
+        if (y >= 0 && y < H && xg >= 0 && xg < W) {
+          const float mu1 = st[0][o], mu2 = st[2][o];
           const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
-          const float s1_raw = st[1] - mu1_sq, s2_raw = st[3] - mu2_sq;
+          const float s1_raw = st[1][o] - mu1_sq, s2_raw = st[3][o] - mu2_sq;
           const float sigma1_sq = fmaxf(0.f, s1_raw), sigma2_sq = fmaxf(0.f, s2_raw);
-          const float sigma12 = st[4] - mu1 * mu2;
+          const float sigma12 = st[4][o] - mu1 * mu2;
           const float A1 = 2.f * mu1 * mu2 + C1, A2 = 2.f * sigma12 + C2, B1 = mu1_sq + mu2_sq + C1, B2 = sigma1_sq + sigma2_sq + C2;
           const float inv_BB = 1.f / (B1 * B2);
           const float raw = A1 * A2 * inv_BB;
           const float ssim = fminf(fmaxf(raw, -1.f), 1.f);
-          if (oy >= HALO && oy < HALO + LOSS_TILE && ox >= HALO && ox < HALO + LOSS_TILE)
-            loss_local += M * (lp.l1_w * fabsf(P[fi] - G[fi]) + lp.ssim_w * ssim);
+          if (oy >= HALO && oy < HALO + LOSS_TILE && col >= HALO && col < HALO + LOSS_TILE) {
+            const int fi = (oy + HALO) * IN_S + col + HALO;
+            const uint32_t gp = s_gt[fi];
+            const float gv = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
+            loss_local += M * (lp.l1_w * fabsf(P[fi] - gv) + lp.ssim_w * ssim);
+          }
           if (raw > -1.f && raw < 1.f) {
             const float k = M * lp.ssim_w;
             const float d_mu1 = 2.f * mu2 * A2 * inv_BB - 2.f * mu1 * ssim / B1;
@@ -146,49 +203,57 @@ __global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __re
             A = k * d_mu1; B = k * d_s1; Bm = B * mu1; Cc = k * d_s12; Cm = Cc * mu2;
           }
         }
-        float* o = s_v + i * 5; o[0] = A; o[1] = B; o[2] = Bm; o[3] = Cc; o[4] = Cm;
+        float* vp = s_v + oy * ST_S + col;
+        vp[0] = A; vp[STAT_W * ST_S] = B; vp[2 * STAT_W * ST_S] = Bm; vp[3 * STAT_W * ST_S] = Cc; vp[4 * STAT_W * ST_S] = Cm;
       }
-      __syncthreads();
-      // Backward blur, horizontal: rows 0..25, output columns 0..15.
-      for (int i = tid; i < STAT_W * LOSS_TILE; i += TILE_PX) {
-        const int row = i / LOSS_TILE, ox = i % LOSS_TILE;
-        float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    }
+    __syncthreads();
+    // Pass 3, backward blur, horizontal: rows 0..25, output columns 0..15. One thread = one row x four columns.
+    if (tid < STAT_W * 4) {
+      const int row = tid / 4, g4 = (tid % 4) * 4;
 #pragma unroll
-        for (int d = 0; d < 11; d++) {
-          const float w = gauss.w[d];
-          const float* v = s_v + (row * STAT_W + ox + d) * 5;
-#pragma unroll
-          for (int k = 0; k < 5; k++) acc[k] += w * v[k];
-        }
-        float* o = s_h + i * 5;
-#pragma unroll
-        for (int k = 0; k < 5; k++) o[k] = acc[k];
+      for (int m = 0; m < 5; m++) {
+        float in[16], out[4];
+        load16(s_v + m * STAT_W * ST_S + row * ST_S + g4, in);
+        window4(in, gauss, out);
+        *reinterpret_cast<float4*>(s_h + m * H_ROWS * ST_S + row * ST_S + g4) = make_float4(out[0], out[1], out[2], out[3]);
       }
-      __syncthreads();
-      // Backward blur, vertical: one pixel per thread, then the chain rule through the five moments.
-      if (inside) {
-        float acc[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    }
+    __syncthreads();
+    // Pass 4, backward blur, vertical, then the chain rule through the five moments. One thread = one column x four rows.
+    if (tid < LOSS_TILE * 4) {
+      const int col = tid % LOSS_TILE, r4 = (tid / LOSS_TILE) * 4;
+      float acc[5][4];
 #pragma unroll
-        for (int d = 0; d < 11; d++) {
-          const float w = gauss.w[d];
-          const float* v = s_h + ((ly + d) * LOSS_TILE + lx) * 5;
+      for (int m = 0; m < 5; m++) {
+        float in[16];
+        const float* hp = s_h + m * H_ROWS * ST_S + r4 * ST_S + col;
 #pragma unroll
-          for (int k = 0; k < 5; k++) acc[k] += w * v[k];
-        }
-        const float p = P[centre], g = G[centre];
+        for (int k = 0; k < 14; k++) in[k] = hp[k * ST_S];
+        in[14] = in[15] = 0.f;
+        window4(in, gauss, acc[m]);
+      }
+#pragma unroll
+      for (int o = 0; o < 4; o++) {
+        const int row = r4 + o;
+        const int fi = (row + 2 * HALO) * IN_S + col + 2 * HALO;
+        const uint32_t gp = s_gt[fi];
+        const float p = P[fi], g = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
         const float sgn = p > g ? 1.f : (p < g ? -1.f : 0.f);
-        const float gr = (s_m[centre] * lp.l1_w * sgn + acc[0] + 2.f * p * acc[1] - 2.f * acc[2] + g * acc[3] - acc[4]) * lp.grad_scale;
-        if (c == 0) grad.x = gr; else if (c == 1) grad.y = gr; else grad.z = gr;
+        const float M = s_m[(row + HALO) * ST_S + col + HALO];
+        s_grad[c * TILE_PX + row * LOSS_TILE + col] =
+            (M * lp.l1_w * sgn + acc[0][o] + 2.f * p * acc[1][o] - 2.f * acc[2][o] + g * acc[3][o] - acc[4][o]) * lp.grad_scale;
       }
-      __syncthreads();   // s_h / s_v are reused by the next channel
     }
-    if (inside && lp.alpha_lane && nonflat[0]) {
-      const float da = s_p[3 * IN_W * IN_W + centre] - gt_a;
-      const float sa = da > 0.f ? 1.f : (da < 0.f ? -1.f : 0.f);
-      const float Ma = wp_c * lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
-      grad.w = Ma * sa * lp.grad_scale;
-      loss_local += Ma * fabsf(da);
-    }
+    __syncthreads();   // s_h / s_v are reused by the next channel; s_grad is read below
+  }
+  float4 grad = make_float4(s_grad[tid], s_grad[TILE_PX + tid], s_grad[2 * TILE_PX + tid], 0.f);
+  if (inside && lp.alpha_lane && nonflat[0]) {
+    const float da = s_p[3 * IN_W * IN_S + centre] - gt_a;
+    const float sa = da > 0.f ? 1.f : (da < 0.f ? -1.f : 0.f);
+    const float Ma = wp_c * lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
+    grad.w = Ma * sa * lp.grad_scale;
+    loss_local += Ma * fabsf(da);
   }
   if (inside) v_out[pix] = grad;
   const float s = warp_sum(loss_local);

@@ -7,6 +7,7 @@ Workload (N = 1 and up): BASELINE config 2 -- 3M splats, SH degree 3, 64 views o
 sphere, targets = renders of a seed-distinct 3M-splat ground-truth set on black. One step = forward + L1/SSIM loss +
 backward + projection backward for all 64 views (sharded over the ranks), one all-reduce of the 59-float per-splat
 gradients when N > 1, then sparse Adam. Metric: train views/s, whole job. Inputs are seeded synthetic data.
+`--workload stress` is BASELINE config 4 (1M heavy-tailed splats, 1024x1024, masked loss + alpha lane, one step);
 `--workload render` measures BASELINE config 3 (6M splats, SH degree 4, 3840x2160 cameras, RGB + alpha + depth) in
 Mpix/s instead; `--workload step1` BASELINE config 1 (500k splats, one 1080p view per step, fused optimizer).
 """
@@ -30,7 +31,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b2k", choices=["b2k", "reference"])
-    ap.add_argument("--workload", default="train", choices=["train", "render", "step1"])
+    ap.add_argument("--workload", default="train", choices=["train", "render", "step1", "stress"])
     ap.add_argument("--splats", type=int, default=None, help="override the splat count (testing only; the line says so)")
     ap.add_argument("--views", type=int, default=None, help="override views per step / cameras (testing only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -38,7 +39,7 @@ def parse():
     return ap.parse_args()
 
 
-WORKLOADS = {"train": 2, "step1": 1, "render": 3}
+WORKLOADS = {"train": 2, "step1": 1, "render": 3, "stress": 4}
 
 
 class ClockSampler:
@@ -190,7 +191,8 @@ def main():
 def workload_name(args, cfg, n):
     base = {1: "config1: 500k splats SH3, one 1920x1080 view per step, fused projection-backward + sparse Adam",
             2: "config2: 3M splats SH3, 64 views of 1920x1080 per step sharded by view, all-reduce of 59 floats per splat, sparse Adam",
-            3: "config3: 6M splats SH4, 256 cameras of 3840x2160, RGB + alpha + depth, forward only"}[cfg]
+            3: "config3: 6M splats SH4, 256 cameras of 3840x2160, RGB + alpha + depth, forward only",
+            4: "config4: 1M heavy-tailed splats SH3, one 1024x1024 view per step, masked loss (ellipse, 40%) + alpha lane, scale 1/0.4, fused optimizer"}[cfg]
     if args.splats or args.views:
         base += f" [REDUCED for testing: splats={n}, views={args.views}]"
     return base
@@ -242,6 +244,15 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         dev_targets[v] = host_targets_mine[j].to(device)
     median_scale = float(np.median(np.exp(scene["lscale"][:, :3])))
     tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=0.0, isect_cap=cap)
+    if cfg == 4:   # per-pixel binary mask in the alpha byte, alpha-match lane, --normalize-masked-loss
+        mask = torch.from_numpy(scenes.ellipse_mask(W, H, 0.4).astype(np.int64))
+        for v in mine:
+            t = host_targets[v].to(torch.int64) & 0xFFFFFFFF
+            t = torch.where(mask > 0, (t & 0x00FFFFFF) | (255 << 24), torch.zeros_like(t))
+            t = torch.where(t >= 2 ** 31, t - 2 ** 32, t).to(torch.int32)
+            host_targets[v].copy_(t)
+            dev_targets[v] = host_targets[v].to(device)
+        tr.lp.mask, tr.lp.alpha_lane, tr.lp.scale = True, True, 1.0 / 0.4
     stats = presize(tr, cams, mine, dev_targets, True)
 
     def timed(targets, steps):
