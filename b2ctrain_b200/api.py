@@ -75,6 +75,7 @@ SIGNATURES = {
     "b2k_bin_sort": (C.c_int, [_P, C.c_int32, _S]),
     "b2k_read_num_isect": (C.c_int, [_P, _S, _P]),
     "b2k_bin_sort_static": (C.c_int, [_P, C.c_int32, _S]),
+    "b2k_bin_sort_profile": (C.c_int, [_P, C.c_int32, _S, _P]),
     "b2k_static_max_splats": (C.c_uint32, []),
     "b2k_raster_fwd": (C.c_int, [_P, _P, _S]),
     "b2k_sort_tmp_bytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
@@ -412,6 +413,15 @@ def bin_and_sort(ctx, m, stream=None, sync=True):
         st = lib().b2k_read_num_isect(C.byref(cs), _stream(stream), C.byref(total))
     _check(st, "bin_and_sort")
     ctx.num_isect = int(total.value)
+
+
+def bin_and_sort_profile(ctx, m, stream=None):
+    """bin_and_sort timed phase by phase with CUDA events inside the library; returns the ten durations in ms (see
+    b2k_bin_sort_profile in include/b2k.h). Synchronises."""
+    cs = ctx.struct()
+    ms = (C.c_float * 10)()
+    _check(lib().b2k_bin_sort_profile(C.byref(cs), m.n, _stream(stream), ms), "bin_and_sort_profile")
+    return list(ms)
 
 
 def rasterize_forward(ctx, p, stream=None):

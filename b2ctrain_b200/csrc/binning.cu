@@ -394,6 +394,11 @@ SortScratch carve(const B2kCtx* c, int blocks) {
   return s;
 }
 
+// Optional timing marks for b2k_bin_sort_profile: when armed, an event is recorded on the stream at each mark.
+struct Marks { cudaEvent_t ev[32]; int n = 0; bool armed = false; };
+thread_local Marks g_marks;
+void mark(cudaStream_t s) { if (g_marks.armed && g_marks.n < 32) cudaEventRecord(g_marks.ev[g_marks.n++], s); }
+
 // LSD radix sort of (key, value) pairs over bits [0, bits). The element count is read from *n_ptr on the device and
 // clamped to n_max. Buffers (k0, v0) hold the input; the result lands in (k0, v0) when the number of passes is even
 // and in (k1, v1) when it is odd.
@@ -412,7 +417,9 @@ int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uin
     const uint32_t mask = (1u << pb) - 1u;
     radix_count_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist);
     radix_rows_kernel<<<RADIX, 1024, 0, s>>>(sc.hist, blocks, sc.totals);
+    mark(s);
     radix_scatter_kernel<<<blocks, SCAT_THREADS, SCAT_SMEM, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals);
+    mark(s);
     uint32_t* t = k0; k0 = k1; k1 = t;
     t = v0; v0 = v1; v1 = t;
   }
@@ -448,6 +455,7 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
   //    the ping-pong returns to the pair it started from, so the sorted result lands where callers expect it and
   //    (depth_keys, order_in) is the scratch pair.
   set_word_kernel<<<1, 1, 0, s>>>(sc.n_word, (uint32_t)n);
+  mark(s);
   int st = radix_sort(c->depth_keys_sorted, c->order, c->depth_keys, c->order_in, sc.n_word, (uint32_t)n, 32, sc, blocks, s);
   if (st) return st;
   // 2 + 3. Scan of the counts in depth order and emission, into the pair the tile sort will read first.
@@ -472,13 +480,37 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
                                                   (uint32_t)c->isect_cap, c->tile_off, ek, ev, c->num_isect, big_emit_ptr(c), big_emit_count);
   emit_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_emit_ptr(c), big_emit_count, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
                                                  c->tiles_x, c->tiles_y, (uint32_t)c->isect_cap, ek, ev);
+  mark(s);
   st = check_launch();
   if (st) return st;
   // 4. Stable sort by tile id: depth order survives inside each tile.
   st = radix_sort(ek, ev, ok, ov, c->num_isect, (uint32_t)c->isect_cap, c->tile_bits, sc, blocks, s);
   if (st) return st;
   tile_ranges_kernel<<<sm_count() * 8, 256, 0, s>>>(c->keys_sorted, c->num_isect, (uint32_t)c->isect_cap, (uint32_t)c->n_tiles, (uint2*)c->tile_ranges);
+  mark(s);
   return check_launch();
+}
+
+extern "C" int b2k_bin_sort_profile(const B2kCtx* c, int32_t n, b2k_stream_t stream, float* ms) {
+  B2K_REQUIRE(c && ms);
+  Marks& mk = g_marks;
+  for (int i = 0; i < 32; i++) B2K_CUDA(cudaEventCreate(&mk.ev[i]));
+  mk.n = 0; mk.armed = true;
+  const int st = b2k_bin_sort(c, n, stream);
+  mk.armed = false;
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+  // Marks: [0] start, then per depth pass (after count+rows, after scatter) x 4, [9] after emit, then per tile pass x P, last after ranges.
+  const int tile_passes = (c->tile_bits + 7) / 8, expect = 1 + 8 + 1 + 2 * tile_passes + 1;
+  for (int i = 0; i < 10; i++) ms[i] = 0.f;
+  if (st == B2K_OK && e == cudaSuccess && mk.n == expect && n > 0) {
+    auto dt = [&](int a, int b) { float t = 0.f; cudaEventElapsedTime(&t, mk.ev[a], mk.ev[b]); return t; };
+    ms[0] = dt(0, 8); ms[1] = dt(8, 9);
+    for (int p = 0; p < tile_passes && p < 3; p++) { ms[2 + 2 * p] = dt(9 + 2 * p, 10 + 2 * p); ms[3 + 2 * p] = dt(10 + 2 * p, 11 + 2 * p); }
+    ms[8] = dt(9 + 2 * tile_passes, 10 + 2 * tile_passes); ms[9] = dt(0, mk.n - 1);
+  }
+  for (int i = 0; i < 32; i++) cudaEventDestroy(mk.ev[i]);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return B2K_ERR_CUDA; }
+  return st;
 }
 
 extern "C" int b2k_read_num_isect(const B2kCtx* c, b2k_stream_t stream, uint32_t* total) {

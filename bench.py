@@ -225,6 +225,7 @@ def presize(tr_or_r, cams, mine, targets, is_train):
 
 def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_ranks, sampler):
     import torch
+    import torch.distributed as dist
     from b2ctrain_b200 import api, scenes
     from b2ctrain_b200.trainer import Trainer, render_targets
     n, deg = scene["n"], scene["degree"]
@@ -276,6 +277,10 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     tr.h2d_bytes = 0
     ms_e2e, loss = timed(host_targets, args.steps)
     h2d = tr.h2d_bytes / args.steps
+    if world > 1:   # whole-job totals
+        t = torch.tensor([h2d], dtype=torch.float64, device=device)
+        dist.all_reduce(t)
+        h2d = float(t.item())
     total_isect, over = tr.check_overflow()
     assert not over, "intersection buffers overflowed inside the timed region"
 
@@ -283,7 +288,7 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     value = views_per_step * args.steps / (ms / 1e3)
     e2e_value = views_per_step * args.steps / (ms_e2e / 1e3)
     launches_view = 1 + (1 + 12 + 2 + 3 * ((tr.ctx.tile_bits + 7) // 8) + 1) + 1 + 1 + 1 + 1 + 1
-    launches = args.steps * (len(mine) * launches_view + (0 if (world == 1 and n_views == 1) else 1))
+    launches = args.steps * (n_views * launches_view + (0 if (world == 1 and n_views == 1) else world))   # all ranks
     res = {"metric": "train views/s", "value": value, "unit": "views/s", "ms_per_step": ms / args.steps, "scaling": "strong",
            "config": {"views_per_step": views_per_step, "splats": n, "sh_degree": deg, "resolution": f"{W}x{H}", "parallelism": f"dp{world} by view",
                       "l2_policy": "inputs larger than L2 (per view > 126 MB of records, lists and images; 64 distinct views per step)",
@@ -329,18 +334,43 @@ def stage_roofline(args, tr, cams, targets, mine, stats):
             acc[nm] += ev[k].elapsed_time(ev[k + 1])
     tr.grad.zero_()
     nv = len(views)
+    # Kernel-level split of the binning stage (events inside the library) on the same views.
+    passes = (ctx.tile_bits + 7) // 8
+    ph = np.zeros(10)
+    for v in views:
+        rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True)
+        api.project_splats(ctx, m, rp)
+        ph += np.array(api.bin_and_sort_profile(ctx, m))
+    ph /= nv
+    scatter_ms = [ph[3 + 2 * p] for p in range(min(passes, 3))]
     st = stats[0]
     V, I, Ib, n, P, tiles = st["V"], st["I"], st["I_b"], m.n, ctx.W * ctx.H, ctx.n_tiles
-    passes = (ctx.tile_bits + 7) // 8
-    alg = {"project": 48 * n + 12 * K * V + 48 * V + 12 * n,
-           "bin_sort": 16 * n * 4 + 8 * n + 8 * I + 16 * I * passes + 4 * I + 8 * tiles,
+    alg = {"project": 48 * n + 12 * K * V + 48 * V + 28 * n,
+           "bin_sort": 16 * n * 4 + 24 * n + 8 * I + 20 * I * passes + 4 * I + 8 * tiles,
            "raster_fwd": 52 * Ib + 36 * P, "loss": 20 * P + 16 * P, "raster_bwd": 28 * P + 52 * Ib + 52 * V,
            "proj_bwd": (52 + 48 + 12 * K) * V + 2 * 4 * (11 + 3 * K) * V + 8 * n}
     stages = {nm: {"ms": acc[nm] / nv, "algorithmic_bytes": int(alg[nm]), "achieved_gbs": alg[nm] / (acc[nm] / nv * 1e-3) / 1e9} for nm in names}
-    top = max(names, key=lambda k: acc[k])
-    a = stages[top]["achieved_gbs"]
+    stages["bin_sort"]["phases_ms"] = {"depth_sort": ph[0], "scan_emit": ph[1], "tile_count": [ph[2 + 2 * p] for p in range(min(passes, 3))],
+                                       "tile_scatter": scatter_ms, "tile_ranges": ph[8], "total": ph[9]}
+    # Dominant kernel: by total time per view among the single-kernel stages and the radix scatter launches.
+    kernel_ms = {"project_kernel": stages["project"]["ms"], "raster_fwd_kernel": stages["raster_fwd"]["ms"], "photometric_kernel": stages["loss"]["ms"],
+                 "raster_bwd_kernel": stages["raster_bwd"]["ms"], "proj_bwd_kernel": stages["proj_bwd"]["ms"], "scan_emit_kernel": ph[1],
+                 "radix_scatter_kernel": float(sum(scatter_ms))}
+    top = max(kernel_ms, key=kernel_ms.get)
+    if top == "radix_scatter_kernel":
+        per_launch_ms = float(np.mean(scatter_ms))
+        bytes_launch = 16 * I          # keys + values read, keys + values written
+        note = f"{len(scatter_ms)} launches per view on I = {I} pairs; 16 B per pair per launch"
+    else:
+        stage = {"project_kernel": "project", "raster_fwd_kernel": "raster_fwd", "photometric_kernel": "loss", "raster_bwd_kernel": "raster_bwd",
+                 "proj_bwd_kernel": "proj_bwd", "scan_emit_kernel": "bin_sort"}[top]
+        per_launch_ms = kernel_ms[top]
+        bytes_launch = alg[stage] if top != "scan_emit_kernel" else 24 * n + 8 * I
+        note = "one launch per view"
+    a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": None, "peak_source": peak_src,
-            "ms_per_launch_group": stages[top]["ms"]}
+            "ms_per_launch": per_launch_ms, "algorithmic_bytes_per_launch": int(bytes_launch), "note": note,
+            "kernel_ms_per_view": {k: float(v) for k, v in kernel_ms.items()}}
     return roof, stages
 
 

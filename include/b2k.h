@@ -132,6 +132,10 @@ int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* op
 /* bin_and_sort, src/gpu/render.h:102 (src/gpu/binning.cu:109-145), without the host round trip: the intersection
  * total stays on the device in ctx->num_isect and the later stages read it there. */
 int b2k_bin_sort(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
+/* b2k_bin_sort with CUDA events between its phases (measurement aid; waits for the stream). ms[10]: [0] depth sort,
+ * [1] scan + emit, [2],[3] / [4],[5] / [6],[7] count+row-scan and scatter of tile-sort passes 0 / 1 / 2, [8] tile
+ * ranges, [9] whole call. The role of the reference's StageTimer (src/train/trainer.cpp:57-73) at kernel granularity. */
+int b2k_bin_sort_profile(const B2kCtx* ctx, int32_t n, b2k_stream_t s, float* ms);
 /* The 4-byte count readback of binning.cu:125-127 as its own call: waits for the stream, returns the total and
  * B2K_ERR_OVERFLOW when it exceeds ctx->isect_cap (the caller grows the four buffers and redoes the view). */
 int b2k_read_num_isect(const B2kCtx* ctx, b2k_stream_t s, uint32_t* total);
