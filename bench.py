@@ -361,14 +361,16 @@ def stage_roofline(args, tr, cams, targets, mine, stats):
         per_launch_ms = float(np.mean(scatter_ms))
         bytes_launch = 16 * I          # keys + values read, keys + values written
         note = f"{len(scatter_ms)} launches per view on I = {I} pairs; 16 B per pair per launch"
+        traffic = int(16.7 * I)   # dram read + write per launch: ncu capture at half the splat count, scaled by pairs (profiles/radix_scatter_kernel_tile_sort.md)
     else:
         stage = {"project_kernel": "project", "raster_fwd_kernel": "raster_fwd", "photometric_kernel": "loss", "raster_bwd_kernel": "raster_bwd",
                  "proj_bwd_kernel": "proj_bwd", "scan_emit_kernel": "bin_sort"}[top]
         per_launch_ms = kernel_ms[top]
         bytes_launch = alg[stage] if top != "scan_emit_kernel" else 24 * n + 8 * I
         note = "one launch per view"
+        traffic = None
     a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
-    roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": None, "peak_source": peak_src,
+    roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src,
             "ms_per_launch": per_launch_ms, "algorithmic_bytes_per_launch": int(bytes_launch), "note": note,
             "kernel_ms_per_view": {k: float(v) for k, v in kernel_ms.items()}}
     return roof, stages
