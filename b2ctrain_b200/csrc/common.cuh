@@ -47,6 +47,10 @@ inline CamDev to_camdev(const B2kCamera& c) {
 
 #ifdef __CUDACC__
 
+// max-update of a non-negative float statistic that several views may touch at once (bit patterns of non-negative
+// floats order like integers).
+__device__ __forceinline__ void atomic_max_nonneg(float* p, float v) { atomicMax(reinterpret_cast<int*>(p), __float_as_int(v)); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

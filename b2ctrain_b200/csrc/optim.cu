@@ -116,9 +116,9 @@ __device__ __forceinline__ void splat_gradient(int i, size_t cap, const float4* 
     for (int k = 0; k < GRAD_LANES; k++) g[k] = 0.f;
   }
   sg.visible = vis != 0u && tile_count[i] != 0u;
-  if (vis_count) vis_count[i] += sg.visible ? 1.f : 0.f;
+  if (vis_count && sg.visible) atomicAdd(vis_count + i, 1.f);   // statistics may be updated by views running on other streams
   sg.refine = isfinite(g[9]) ? fminf(fmaxf(g[9], 0.f), 1e32f) : 0.f;
-  if (refine_norm && sg.refine > 0.f) refine_norm[i] = fmaxf(refine_norm[i], sg.refine);
+  if (refine_norm && sg.refine > 0.f) atomic_max_nonneg(refine_norm + i, sg.refine);
   bool any = false, finite = true;
 #pragma unroll
   for (int k = 0; k < GRAD_LANES; k++) { if (k != 9 && g[k] != 0.f) any = true; finite = finite && isfinite(g[k]); }

@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
       }
       const float detc = pr.c00 * pr.c11 - pr.c01 * pr.c01;
       const float ex = sqrtf(2.f * pr.power * pr.c11 / detc), ey = sqrtf(2.f * pr.power * pr.c00 / detc);
-      if (max_screen) max_screen[i] = fmaxf(max_screen[i], fmaxf(ex / (float)cam.W, ey / (float)cam.H));
+      if (max_screen) { const float ms = fmaxf(ex / (float)cam.W, ey / (float)cam.H); if (ms > max_screen[i]) atomic_max_nonneg(max_screen + i, ms); }
     }
     proj0[i] = make_float4(pr.mx, pr.my, pr.c00, pr.c01);
     proj1[i] = make_float4(pr.c11, pr.opac, pr.mean_c.z, pr.power);

@@ -34,25 +34,32 @@ def reduce_gradients(grad, world):
 
 class Trainer:
     def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, lr_mean=1.6e-4, sparse=True, noise_weight=0.0,
-                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None):
+                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None, views_in_flight=1):
         self.device = torch.device(device)
         self.rank, self.world = rank, world
         self.model = api.Model(device).upload(cloud)
-        self.ctx = api.RenderCtx(device)
-        self.ctx.setup(W, H, self.model.cap, isect_cap=isect_cap)
+        # One context, stream and gradient accumulator per view in flight: views of a step are independent until the
+        # update, so the latency-bound raster kernels of one view overlap the throughput-bound binning of another.
+        self.lanes = max(1, int(views_in_flight))
+        self.ctxs = [api.RenderCtx(device) for _ in range(self.lanes)]
+        for c in self.ctxs:
+            c.setup(W, H, self.model.cap, isect_cap=isect_cap)
+        self.ctx = self.ctxs[0]
+        self.streams = [torch.cuda.Stream(device=self.device) for _ in range(self.lanes)] if self.lanes > 1 else [None]
         self.W, self.H = W, H
         self.lr_mean, self.sparse = lr_mean, sparse
         self.noise_weight, self.noise_clamp = noise_weight, noise_clamp
         self.lp = api.LossParams(l1_w=1.0 - ssim_weight, ssim_w=-ssim_weight)
         K = self.model.K()
-        self.grad = torch.zeros((self.model.n, 11 + 3 * K), dtype=torch.float32, device=self.device)
+        self.grads = [torch.zeros((self.model.n, 11 + 3 * K), dtype=torch.float32, device=self.device) for _ in range(self.lanes)]
+        self.grad = self.grads[0]
         self.step_no = 0
         P = W * H
         # device staging for targets that arrive from host memory (double-buffered on a copy stream)
-        self._stage = [torch.zeros(P, dtype=torch.int32, device=self.device) for _ in range(2)]
+        self._stage = [torch.zeros(P, dtype=torch.int32, device=self.device) for _ in range(2 * self.lanes)]
         self._copy_stream = torch.cuda.Stream(device=self.device)
-        self._staged_evt = [torch.cuda.Event() for _ in range(2)]
-        self._free_evt = [torch.cuda.Event() for _ in range(2)]
+        self._staged_evt = [torch.cuda.Event() for _ in range(2 * self.lanes)]
+        self._free_evt = [torch.cuda.Event() for _ in range(2 * self.lanes)]
         self.h2d_bytes = 0
 
     def my_views(self, n_views):
@@ -72,10 +79,10 @@ class Trainer:
         self.h2d_bytes += t.numel() * 4
         return dst
 
-    def view_pass(self, cam, target, bg=(0.0, 0.0, 0.0), weights=None, slot=0, fused_op=None):
+    def view_pass(self, cam, target, bg=(0.0, 0.0, 0.0), weights=None, slot=0, fused_op=None, lane=0):
         """forward + loss + backward of one view; then either the fused optimizer (fused_op given) or the gradient
-        accumulation."""
-        m, ctx = self.model, self.ctx
+        accumulation into the lane's accumulator. Runs on the current stream with the lane's context."""
+        m, ctx = self.model, self.ctxs[lane]
         rp = api.RenderParams(cam, bg=bg, sh_degree=m.degree, bwd_info=True)
         api.render_forward(ctx, m, rp, sync=False)
         tgt = self._target(target, slot)
@@ -88,7 +95,7 @@ class Trainer:
         if fused_op is not None:
             api.optimizer_step(ctx, m, fused_op)
         else:
-            api.projection_backward(ctx, m, self._op(cam), self.grad)
+            api.projection_backward(ctx, m, self._op(cam), self.grads[lane])
 
     def _op(self, cam):
         return api.OptimParams(cam, active_sh_degree=self.model.degree, t=self.model.adam_t, lr_mean=self.lr_mean, sparse=self.sparse,
@@ -105,9 +112,26 @@ class Trainer:
         if self.world == 1 and len(cams) == 1:
             self.view_pass(cams[0], targets[0], bg, fused_op=self._op(cams[0]))
             return self.ctx.loss_accum
-        for j, v in enumerate(mine):
-            self.ctx.loss_accum[:2].zero_()
-            self.view_pass(cams[v], targets[v], bg, slot=j & 1)
+        if self.lanes == 1:
+            for j, v in enumerate(mine):
+                self.ctx.loss_accum[:2].zero_()
+                self.view_pass(cams[v], targets[v], bg, slot=j & 1)
+        else:
+            main = torch.cuda.current_stream(self.device)
+            start = torch.cuda.Event(); start.record(main)
+            for j, v in enumerate(mine):
+                lane = j % self.lanes
+                with torch.cuda.stream(self.streams[lane]):
+                    if j < self.lanes:
+                        self.streams[lane].wait_event(start)
+                        self.ctxs[lane].loss_accum.zero_()
+                    self.ctxs[lane].loss_accum[:2].zero_()
+                    self.view_pass(cams[v], targets[v], bg, slot=2 * lane + ((j // self.lanes) & 1), lane=lane)
+            for lane in range(min(self.lanes, len(mine))):
+                done = torch.cuda.Event(); done.record(self.streams[lane]); main.wait_event(done)
+            for lane in range(1, self.lanes):       # fold the lanes' accumulators and running losses into lane 0
+                self.grad.add_(self.grads[lane]); self.grads[lane].zero_()
+                self.ctx.loss_accum[2:4].add_(self.ctxs[lane].loss_accum[2:4])
         reduce_gradients(self.grad, self.world)
         api.adam_step(m, self._op(cams[0]), self.grad)
         return self.ctx.loss_accum
@@ -115,14 +139,17 @@ class Trainer:
     def check_overflow(self):
         """Reads the last view's intersection count back; grows the buffers when it did not fit (the reference does this
         inside every bin_and_sort, src/gpu/binning.cu:125-133). Returns (count, overflowed)."""
-        total = int(self.ctx.d_num_isect[0].item()) & 0xFFFFFFFF
-        if total > self.ctx.isect_cap:
-            cap = self.ctx.isect_cap
-            while cap < total:
-                cap *= 2
-            self.ctx._alloc_isect(cap)
-            return total, True
-        return total, False
+        total, over = 0, False
+        for ctx in self.ctxs:
+            t = int(ctx.d_num_isect[0].item()) & 0xFFFFFFFF
+            total = max(total, t)
+            if t > ctx.isect_cap:
+                cap = ctx.isect_cap
+                while cap < t:
+                    cap *= 2
+                ctx._alloc_isect(cap)
+                over = True
+        return total, over
 
 
 class Renderer:

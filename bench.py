@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--splats", type=int, default=None, help="override the splat count (testing only; the line says so)")
     ap.add_argument("--views", type=int, default=None, help="override views per step / cameras (testing only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--views-in-flight", type=int, default=2, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
 
@@ -244,7 +245,8 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         host_targets[v] = host_targets_mine[j]
         dev_targets[v] = host_targets_mine[j].to(device)
     median_scale = float(np.median(np.exp(scene["lscale"][:, :3])))
-    tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=0.0, isect_cap=cap)
+    tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=0.0, isect_cap=cap,
+                 views_in_flight=1 if n_views == 1 else args.views_in_flight)
     if cfg == 4:   # per-pixel binary mask in the alpha byte, alpha-match lane, --normalize-masked-loss
         mask = torch.from_numpy(scenes.ellipse_mask(W, H, 0.4).astype(np.int64))
         for v in mine:
@@ -255,6 +257,9 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
             dev_targets[v] = host_targets[v].to(device)
         tr.lp.mask, tr.lp.alpha_lane, tr.lp.scale = True, True, 1.0 / 0.4
     stats = presize(tr, cams, mine, dev_targets, True)
+    for c in tr.ctxs[1:]:   # every lane gets the sized intersection buffers
+        if c.isect_cap < tr.ctx.isect_cap:
+            c._alloc_isect(tr.ctx.isect_cap)
 
     def timed(targets, steps):
         barrier()
