@@ -20,7 +20,8 @@ namespace {
 
 constexpr int SORT_THREADS = 256;
 constexpr int SORT_ITEMS = 16;
-constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;   // 4096 pairs per tile
+constexpr int COUNT_TILE = SORT_THREADS * SORT_ITEMS;   // 4096 keys per counting step of a CTA
+constexpr int SORT_TILE = 4096;                         // pairs per scatter tile (a multiple of COUNT_TILE)
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 constexpr int RADIX = 256;
 constexpr int BLOCKS_PER_SM = 2;               // resident scatter CTAs per SM: one wave covers the input
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_
   const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
   const uint32_t end = (begin64 + len) < n ? (uint32_t)(begin64 + len) : n;
   // Segments start on a multiple of the tile size, so 128-bit loads are aligned.
-  for (uint32_t tile = begin + warp * (32 * SORT_ITEMS); tile < end; tile += SORT_TILE) {   // warp-uniform trip count
+  for (uint32_t tile = begin + warp * (32 * SORT_ITEMS); tile < end; tile += COUNT_TILE) {   // warp-uniform trip count
     uint32_t k[SORT_ITEMS];
     if (tile + 32 * SORT_ITEMS <= end) {
 #pragma unroll
@@ -104,7 +105,7 @@ constexpr int SCAT_ITEMS = SORT_TILE / SCAT_THREADS;   // 8
 constexpr int SCAT_WARPS = SCAT_THREADS / 32;
 constexpr size_t SCAT_SMEM = 2 * SORT_TILE * sizeof(uint32_t);
 
-__global__ void __launch_bounds__(SCAT_THREADS, 2) radix_scatter_kernel(
+__global__ void __launch_bounds__(SCAT_THREADS, SCAT_THREADS <= 512 ? 2 : 1) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
     const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask, const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals) {
   __shared__ uint32_t s_cnt[SCAT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit

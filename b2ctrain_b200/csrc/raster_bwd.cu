@@ -97,6 +97,9 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
   const float Wf = (float)W, Hf = (float)H;
   Staged* frag = s_frag[warp];
   uint32_t* gids = s_gid[warp];
+#ifdef B2K_BWD_ABLATE_REDUCTION
+  float ablate_sink = 0.f;
+#endif
 
   for (uint32_t batch_end = range.y; batch_end > range.x;) {
     const uint32_t remaining = batch_end - range.x;
@@ -157,6 +160,13 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
       if (col.x < 0.f) acc[5] = 0.f;   // the colour clamp at zero has zero slope
       if (col.y < 0.f) acc[6] = 0.f;
       if (col.z < 0.f) acc[7] = 0.f;
+#ifdef B2K_BWD_ABLATE_REDUCTION
+      // Ablation build (never shipped): the replay alone, with the cross-lane reduction and the global reductions
+      // removed, bounds from above what any other reduction scheme (tensor cores included) could save.
+#pragma unroll
+      for (int k = 0; k < 11; k++) ablate_sink += acc[k];
+      continue;
+#endif
       const float total = warp_transpose_sum(acc, lane);
       if ((lane & 1) == 0) {
         const int k = lane >> 1;
@@ -167,6 +177,9 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     }
     batch_end = batch_start;
   }
+#ifdef B2K_BWD_ABLATE_REDUCTION
+  if (ablate_sink == 123456.789f) v_splat[0] = ablate_sink;   // keeps the replay alive
+#endif
 }
 
 }  // namespace
