@@ -72,6 +72,7 @@ class B2kOptim(C.Structure):
 _P, _S = C.c_void_p, C.c_void_p
 SIGNATURES = {
     "b2k_project": (C.c_int, [_P, _P, _P, _P, _S]),
+    "b2k_count_tiles": (C.c_int, [_P, C.c_int32, _S]),
     "b2k_bin_sort": (C.c_int, [_P, C.c_int32, _S]),
     "b2k_read_num_isect": (C.c_int, [_P, _S, _P]),
     "b2k_bin_sort_static": (C.c_int, [_P, C.c_int32, _S]),
@@ -392,6 +393,12 @@ class OptimParams:
 def project_splats(ctx, m, p, stream=None):
     ms, cs, os_, cam = m.struct(), ctx.struct(), p.struct(), p.camera()
     _check(lib().b2k_project(C.byref(ms), C.byref(cam), C.byref(os_), C.byref(cs), _stream(stream)), "project_splats")
+
+
+def count_tiles(ctx, m, stream=None):
+    """Tile counts, hit masks and depth keys from the records already in ctx.proj0 / ctx.proj1."""
+    cs = ctx.struct()
+    _check(lib().b2k_count_tiles(C.byref(cs), m.n, _stream(stream)), "count_tiles")
 
 
 def bin_and_sort(ctx, m, stream=None, sync=True):

@@ -130,6 +130,39 @@ __global__ void __launch_bounds__(256) count_big_kernel(const uint32_t* __restri
   }
 }
 
+// The decision half of the projection on its own: tile counts, hit masks and depth keys recomputed from the records
+// already in proj0 / proj1 (power < -0.5 marks "no record").
+__global__ void __launch_bounds__(PROJ_BLOCK) count_tiles_kernel(int n, const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H,
+                                                                 int tiles_x, int tiles_y, uint32_t* __restrict__ tile_count, uint4* __restrict__ hit_info,
+                                                                 uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in,
+                                                                 uint32_t* __restrict__ big_list, uint32_t* __restrict__ big_count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 a = proj0[i], b = proj1[i];
+  uint32_t hits = 0, mask_lo = 0, mask_hi = 0, box = 0;
+  bool big = false;
+  if (b.w > -0.5f) {
+    const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
+    TileBox bb;
+    if (tile_box(rec, W, H, tiles_x, tiles_y, bb)) {
+      const int bw = bb.max_x - bb.min_x, bh = bb.max_y - bb.min_y;
+      if (bw * bh > MASK_TILES) {
+        big = true; box = 0xFFFFFFFFu;
+        big_list[atomicAdd(big_count, 1u)] = (uint32_t)i;
+      } else if (bw > 0 && bh > 0) {
+        int bit = 0;
+        for (int ty = bb.min_y; ty < bb.max_y; ty++)
+          for (int tx = bb.min_x; tx < bb.max_x; tx++, bit++)
+            if (tile_hit(tx, ty, rec)) { hits++; if (bit < 32) mask_lo |= 1u << bit; else mask_hi |= 1u << (bit - 32); }
+        box = (uint32_t)bb.min_x | ((uint32_t)bb.min_y << 12) | ((uint32_t)bw << 24);
+      }
+    }
+  }
+  hit_info[i] = make_uint4(mask_lo, mask_hi, box, 0u);
+  order_in[i] = (uint32_t)i;
+  if (!big) { tile_count[i] = hits; depth_keys[i] = hits ? __float_as_uint(b.z) : 0xFFFFFFFFu; }
+}
+
 template <int DEG>
 int launch(const B2kModel* m, const CamDev& cam, const B2kRenderOpts* o, const B2kCtx* c, cudaStream_t s) {
   const float4* pos = (const float4*)(o->pos_override ? o->pos_override : m->pos_op);
@@ -171,6 +204,23 @@ extern "C" int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRen
     case 3: return launch<3>(m, cd, opts, ctx, st);
     default: return launch<4>(m, cd, opts, ctx, st);
   }
+}
+
+extern "C" int b2k_count_tiles(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
+  B2K_REQUIRE(c && n >= 0);
+  if (n == 0) return B2K_OK;
+  B2K_REQUIRE(c->proj0 && c->proj1 && c->tile_count && c->hit_info && c->depth_keys_sorted && c->order && c->sort_tmp);
+  B2K_REQUIRE(c->W > 0 && c->H > 0 && c->tiles_x == div_up(c->W, RT_W) && c->tiles_y == div_up(c->H, RT_W));
+  if (c->n_cap < n || c->sort_tmp_bytes < b2k_sort_tmp_bytes(c->n_cap, c->isect_cap)) return B2K_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t* big_count = big_count_ptr(c);
+  uint32_t* big_list = big_list_ptr(c);
+  B2K_CUDA(cudaMemsetAsync(big_count, 0, sizeof(uint32_t), s));
+  count_tiles_kernel<<<div_up(n, 256), 256, 0, s>>>(n, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H, c->tiles_x, c->tiles_y, c->tile_count,
+                                                   (uint4*)c->hit_info, c->depth_keys_sorted, c->order, big_list, big_count);
+  count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H, c->tiles_x, c->tiles_y,
+                                                  c->tile_count, c->depth_keys_sorted);
+  return check_launch();
 }
 
 static const char* kErrors[] = {"ok", "bad argument", "buffer capacity exceeded", "unsupported lane", "CUDA error",

@@ -129,6 +129,11 @@ typedef struct {
 /* ---- forward ---- */
 /* project_splats, src/gpu/render.h:101 (project_kernel, src/gpu/project.cu:9-84). */
 int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s);
+/* The tile-decision half of project_kernel alone (src/gpu/project.cu:31-43 with depth_keys_kernel, src/gpu/binning.cu:10-15):
+ * recomputes tile_count, hit_info and the depth sort input from the records already in ctx->proj0 / proj1 (proj1.w <
+ * -0.5 = no record). Lets a caller bin records that came from elsewhere (a stage exposed for tests, like the
+ * reference's, src/gpu/render.h:100). */
+int b2k_count_tiles(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
 /* bin_and_sort, src/gpu/render.h:102 (src/gpu/binning.cu:109-145), without the host round trip: the intersection
  * total stays on the device in ctx->num_isect and the later stages read it there. */
 int b2k_bin_sort(const B2kCtx* ctx, int32_t n, b2k_stream_t s);

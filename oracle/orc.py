@@ -251,3 +251,89 @@ def reference_loss(scene, cam, bg, gt, weights, lp):
 
 def num_threads():
     return int(lib().orc_num_threads())
+
+
+# ---- the reference's own CUDA kernels (oracle/_ref/librefcuda.so), second oracle and speed incumbent ----
+
+_refcu = None
+
+
+def refcuda_lib():
+    """The reference's unmodified CUDA implementation built for sm_100a, or None when it was never built here."""
+    global _refcu
+    if _refcu is None:
+        path = os.path.join(_HERE, "_ref", "librefcuda.so")
+        if not os.path.exists(path):
+            return None
+        _refcu = C.CDLL(path)
+        _refcu.refcu_create.restype = C.c_void_p
+        _refcu.refcu_error.restype = C.c_char_p
+        _refcu.refcu_num_isect.restype = C.c_uint32
+        _refcu.refcu_time_steps.restype = C.c_float
+    return _refcu
+
+
+class RefCuda:
+    """One scene + view on the reference's CUDA path. Methods mirror the reference's test Harness (tests/tests.cpp:61-102)."""
+
+    def __init__(self, scene, cam):
+        self.l = refcuda_lib()
+        assert self.l is not None, "oracle/_ref/librefcuda.so is missing"
+        self.scene, self.cam = scene, cam
+        n, self.W, self.H = scene["n"], int(cam["W"]), int(cam["H"])
+        self.K = (scene["degree"] + 1) ** 2
+        floor = _f32(scene["lscale"][:, 3])
+        self.h = C.c_void_p(self.l.refcu_create(n, scene["degree"], _p(_f32(scene["pos_op"][:, :3])), _p(_f32(scene["lscale"][:, :3])), _p(_f32(scene["quat"])),
+                                                _p(_f32(scene["pos_op"][:, 3])), _p(_f32(scene["sh"])), _p(floor) if np.any(floor != 0) else None, self.W, self.H))
+        self._check(0)
+        self.intr = np.array([cam["fx"], cam["fy"], cam["cx"], cam["cy"]], np.float32)
+        self.R, self.t = _f32(cam["R"]), _f32(cam["t"])
+
+    def _check(self, rc):
+        err = self.l.refcu_error(self.h).decode()
+        if rc != 0 or err:
+            raise RuntimeError(f"reference CUDA path: {err}")
+
+    def close(self):
+        if self.h:
+            self.l.refcu_destroy(self.h)
+            self.h = None
+
+    def set_view(self, gt, weights=None):
+        w = None if weights is None else np.ascontiguousarray(weights, dtype=np.uint8)
+        self._check(self.l.refcu_set_view(self.h, _p(_u32(gt)), _p(w)))
+
+    def forward(self, bg=(0, 0, 0), bwd_info=True):
+        self.bg = _f32(bg)
+        self._check(self.l.refcu_forward(self.h, _p(self.intr), _p(self.R), _p(self.t), _p(self.bg), int(bwd_info)))
+
+    def loss(self, lp):
+        p = np.array([lp.get("l1_w", 0.8), lp.get("ssim_w", -0.2), *lp.get("bg", (0, 0, 0)), lp.get("match_alpha_weight", 0.1), lp.get("scale", 1.0),
+                      lp.get("grad_scale", 1.0)], np.float32)
+        f = np.array([int(lp.get("composite", 0)), int(lp.get("mask", 0)), int(lp.get("alpha_lane", 0))], np.int32)
+        out = C.c_float(0)
+        self._check(self.l.refcu_loss(self.h, _p(p), _p(f), C.byref(out)))
+        return float(out.value)
+
+    def backward(self, tensor_core=False, grad_scale=1.0):
+        self._check(self.l.refcu_backward(self.h, _p(self.intr), _p(self.R), _p(self.t), _p(self.bg), int(tensor_core), C.c_float(grad_scale)))
+
+    def grads(self):
+        out = np.zeros((self.scene["n"], 11 + 3 * self.K), np.float32)
+        self._check(self.l.refcu_grads(self.h, _p(self.intr), _p(self.R), _p(self.t), _p(out)))
+        return out
+
+    def download(self, what, shape, dtype):
+        sel = dict(proj0=0, proj1=1, proj2=2, tile_count=3, vals_sorted=4, keys_sorted=5, tile_ranges=6, out_rgba=7, last_idx=8, v_splat=9, pos_op=10, quat=11,
+                   lscale=12)[what]
+        out = np.zeros(shape, dtype)
+        self._check(self.l.refcu_download(self.h, sel, _p(out), C.c_size_t(out.nbytes)))
+        return out
+
+    def num_isect(self):
+        return int(self.l.refcu_num_isect(self.h))
+
+    def time_steps(self, bg=(0, 0, 0), tensor_core=True, warm=3, iters=10, lr_mean=1e-5):
+        ms = self.l.refcu_time_steps(self.h, _p(self.intr), _p(self.R), _p(self.t), _p(_f32(bg)), int(tensor_core), warm, iters, C.c_float(lr_mean))
+        self._check(0 if ms >= 0 else 1)
+        return float(ms)

@@ -1,0 +1,81 @@
+"""The product against the reference's OWN CUDA kernels (built unmodified for sm_100a into oracle/_ref/librefcuda.so)
+on the same seeded inputs: records, image, loss and parameter gradients within tolerance; and, with the reference's
+records fed to the product's binning, the tile lists and the sorted fragment order compared pair by pair."""
+import numpy as np
+import pytest
+
+from b2ctrain_b200 import scenes
+from oracle import orc
+from tests.util import Harness, rel_l2
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(orc.refcuda_lib() is None, reason="oracle/_ref/librefcuda.so was not built (no reference tree at build time)")]
+
+
+def scene_and_view(n=20000, degree=3, W=320, H=240, seed=5):
+    scene = scenes.make_splats(n, degree, seed, log_scale=(-3.4, 0.5))
+    cam = scenes.look_at_camera(scenes.orbit_eye(3.0, 25.0, 10.0), W, H, float(H))
+    scene = scenes.floor_for_cameras(scene, [cam])
+    gt = np.random.Generator(np.random.PCG64(seed)).integers(0, 2 ** 32, W * H, dtype=np.uint64).astype(np.uint32) | np.uint32(0xFF000000)
+    return scene, cam, gt
+
+
+def test_records_image_loss_and_gradients_match_the_reference_kernels():
+    scene, cam, gt = scene_and_view()
+    lp = dict(l1_w=0.8, ssim_w=-0.2)
+    n, P = scene["n"], cam["W"] * cam["H"]
+    ref = orc.RefCuda(scene, cam)
+    ref.set_view(gt)
+    ref.forward()
+    ref_loss = ref.loss(lp)
+    ref_img = ref.download("out_rgba", (P, 4), np.float32)
+    ref_p0, ref_p1 = ref.download("proj0", (n, 4), np.float32), ref.download("proj1", (n, 4), np.float32)
+    ref_tc = ref.download("tile_count", (n,), np.uint32)
+    ref.backward(tensor_core=False)
+    ref_grad = ref.grads()
+    ref.close()
+
+    h = Harness(scene, cam, gt, None, lp)
+    loss, grad = h.analytic()
+    p0, p1 = h.ctx.proj0[:n].cpu().numpy(), h.ctx.proj1[:n].cpu().numpy()
+    tc = h.u32(h.ctx.tile_count, n)
+    both = (tc > 0) & (ref_tc > 0)
+    assert both.sum() > 0.8 * n and np.mean((tc > 0) != (ref_tc > 0)) < 1e-3
+    got, want = np.concatenate([p0, p1], 1)[both], np.concatenate([ref_p0, ref_p1], 1)[both]
+    scale = np.abs(want) + np.array([1.0, 1.0, 0, 0, 0, 0, 0, 1.0])[None, :]
+    scale[:, [2, 3, 4]] = np.abs(want[:, [2, 3, 4]]).max(1, keepdims=True)
+    assert np.max(np.abs(got - want) / scale) <= 1e-4          # the reference runs under --use_fast_math
+    assert np.mean(tc != ref_tc) < 2e-3                        # tile counts may differ on boundary tiles only
+    assert np.max(np.abs(h.ctx.out_rgba.cpu().numpy() - ref_img)) <= 1e-3
+    assert abs(loss - ref_loss) <= 1e-4 * abs(ref_loss)
+    assert rel_l2(grad, ref_grad) <= 2e-3                      # fp32 fast-math kernels on both sides of the comparison
+
+
+def test_binning_of_the_reference_records_matches_the_reference_lists():
+    """The reference's own projection records go through the product's tile decisions, sort and ranges; the result is
+    compared with the reference's own bin_and_sort. Differences can only come from the reference's fast-math division
+    inside its tile test on boundary tiles: they are counted, and must be rare."""
+    scene, cam, gt = scene_and_view(n=30000, seed=9)
+    n = scene["n"]
+    ref = orc.RefCuda(scene, cam)
+    ref.forward(bwd_info=False)
+    I_ref = ref.num_isect()
+    ref_p0, ref_p1 = ref.download("proj0", (n, 4), np.float32), ref.download("proj1", (n, 4), np.float32)
+    ref_tc = ref.download("tile_count", (n,), np.uint32)
+    ref_vals, ref_keys = ref.download("vals_sorted", (I_ref,), np.uint32), ref.download("keys_sorted", (I_ref,), np.uint32)
+    ref.close()
+    ref_p1[ref_tc == 0, 3] = -1.0                              # culled splats of the reference have no record
+    h = Harness(scene, cam)
+    h.ctx.proj0[:n].copy_(h.torch.from_numpy(ref_p0)); h.ctx.proj1[:n].copy_(h.torch.from_numpy(ref_p1))
+    h.api.count_tiles(h.ctx, h.model)
+    h.api.bin_and_sort(h.ctx, h.model)
+    I = h.ctx.num_isect
+    vals, keys = h.u32(h.ctx.vals_sorted, I), h.u32(h.ctx.keys_sorted, I)
+    a = set(zip(keys.tolist(), vals.tolist())); b = set(zip(ref_keys.tolist(), ref_vals.tolist()))
+    differing = len(a ^ b)
+    print(f"intersections: product {I}, reference {I_ref}; differing (tile, splat) pairs: {differing}")
+    assert I > 100000 and differing <= 2e-4 * I
+    # Order inside every tile: identical wherever the two lists hold the same pairs.
+    common = a & b
+    mine = [(k, v) for k, v in zip(keys.tolist(), vals.tolist()) if (k, v) in common]
+    theirs = [(k, v) for k, v in zip(ref_keys.tolist(), ref_vals.tolist()) if (k, v) in common]
+    assert mine == theirs
