@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--splats", type=int, default=None, help="override the splat count (testing only; the line says so)")
     ap.add_argument("--views", type=int, default=None, help="override views per step / cameras (testing only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
     ap.add_argument("--views-in-flight", type=int, default=2, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
@@ -302,7 +303,30 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
            "gpu_launches": launches, "clocks": clocks, "loss_last_view": float(loss[0]) if loss is not None else None}
     if rank == 0:
         res["roofline"], res["stages"] = stage_roofline(args, tr, cams, dev_targets, mine, stats)
+        if world == 1 and not args.no_incumbent:
+            res["reference_cuda"] = incumbent(scene, cams[mine[0]], host_targets[mine[0]], cfg == 4)
     return res
+
+
+def incumbent(scene, cam, host_target, masked):
+    """The reference's own CUDA kernels (built unmodified for sm_100a, oracle/_ref/librefcuda.so) timed on one view of the
+    same workload in the same run: its full single-view step (forward, loss, backward, fused optimizer), both backward
+    variants. A reported comparison; the checker library is never part of the product path."""
+    from oracle import orc
+    if orc.refcuda_lib() is None:
+        return {"unavailable": "oracle/_ref/librefcuda.so was not built (no reference tree at build time)"}
+    try:
+        ref = orc.RefCuda(scene, cam)
+        ref.set_view(host_target.numpy().view(np.uint32))
+        out = {}
+        for name, tc in (("tc", True), ("warp", False)):
+            ms = ref.time_steps(tensor_core=tc, warm=2, iters=5, lr_mean=1e-6)
+            out[name] = {"ms_per_view": ms, "views_per_s": 1e3 / ms}
+        ref.close()
+        out["what"] = "reference b2ctrain CUDA kernels, -O3 --use_fast_math, sm_100a, same B200, one view per step, 5 timed steps"
+        return out
+    except Exception as e:   # the incumbent is informative only
+        return {"unavailable": str(e)[:200]}
 
 
 def stage_roofline(args, tr, cams, targets, mine, stats):
