@@ -332,16 +332,22 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
 template <int DEG>
 __global__ void __launch_bounds__(OPT_BLOCK) adam_kernel(int n, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
   constexpr int K = (DEG + 1) * (DEG + 1), PER = 11 + 3 * K;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  // The accumulator is row-major [n][PER] (the all-reduce buffer): a CTA's 128 rows are one contiguous block, staged
+  // through shared memory with coalesced loads and cleared with coalesced stores; a thread then reads its own row at
+  // stride PER (odd: conflict-free).
+  extern __shared__ float s_rows[];
+  const int base = blockIdx.x * OPT_BLOCK;
+  const int rows = n - base < OPT_BLOCK ? n - base : OPT_BLOCK;
+  float* gblock = grad + (size_t)base * PER;
+  for (int k = threadIdx.x; k < rows * PER; k += OPT_BLOCK) { s_rows[k] = gblock[k]; gblock[k] = 0.f; }
+  __syncthreads();
+  const int i = base + threadIdx.x;
   if (i >= n) return;
-  float* gp = grad + (size_t)i * PER;
-  float g[PER];
+  const float* g = s_rows + threadIdx.x * PER;
   bool any = false;
 #pragma unroll
-  for (int k = 0; k < PER; k++) { g[k] = gp[k]; any = any || g[k] != 0.f; }
+  for (int k = 0; k < PER; k++) any = any || g[k] != 0.f;
   if (op.sparse && !any) return;
-#pragma unroll
-  for (int k = 0; k < PER; k++) gp[k] = 0.f;
   ParamGrad pg;
   pg.pos = make_float3(g[0], g[1], g[2]); pg.op = g[3]; pg.q = make_float4(g[4], g[5], g[6], g[7]); pg.ls = make_float3(g[8], g[9], g[10]);
   float gsq = 0.f;
@@ -457,7 +463,8 @@ extern "C" int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_
   B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi) && has_moments(m) && op->t >= 1);
   if (m->n == 0) return B2K_OK;
   const ModelPtrs mp = model_ptrs(m);
-  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(m->n, mp, *op, grad)));
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, sizeof(float) * OPT_BLOCK * (11 + 3 * (D + 1) * (D + 1)), (cudaStream_t)stream>>>(
+      m->n, mp, *op, grad)));
   return check_launch();
 }
 

@@ -349,3 +349,21 @@ def test_multi_view_accumulation_equals_sum_of_view_gradients():
     assert float(tr.grad.abs().max()) == 0.0
     moved = np.any(before["pos_op"] != after["pos_op"], axis=1)
     assert np.array_equal(moved, np.any(got[:, :4] != 0, axis=1) | moved) and moved.sum() > 100
+
+
+def test_full_chain_ragged_image_size():
+    """Image sizes that are multiples of neither the 8-pixel raster tile nor the 16-pixel loss tile."""
+    scene = scenes.make_splats(1500, 2, 33, log_scale=(-2.8, 0.5))
+    cam = scenes.look_at_camera(scenes.orbit_eye(3.0, -40.0, 20.0), 150, 97, 110.0)
+    scene = scenes.floor_for_cameras(scene, [cam])
+    rng = np.random.Generator(np.random.PCG64(3))
+    gt = rng.integers(0, 2 ** 32, 150 * 97, dtype=np.uint64).astype(np.uint32)
+    wts = rng.integers(0, 256, 150 * 97).astype(np.uint8)
+    lp = dict(l1_w=np.float32(0.8), ssim_w=np.float32(-0.2), bg=(np.float32(0.3), np.float32(0.2), np.float32(0.1)), composite=1, alpha_lane=1,
+              match_alpha_weight=np.float32(0.25))
+    h = Harness(scene, cam, gt, wts, lp)
+    loss, grad = h.analytic()
+    want = orc.step(scene, cam, np.array(lp["bg"], np.float64), gt, wts, lp, backward=True, want_image=True)
+    assert np.max(np.abs(h.ctx.out_rgba.cpu().numpy() - want["rgba"])) <= TOL_IMAGE_ABS
+    assert abs(loss - want["loss"]) <= TOL_LOSS_REL * abs(want["loss"])
+    assert rel_l2(grad, want["grad"]) <= TOL_GRAD_REL_L2
