@@ -108,9 +108,8 @@ __device__ __forceinline__ void splat_gradient(int i, size_t cap, const float4* 
   const uint32_t vis = vis_flag[i];
   float* vs = v_splat + (size_t)i * GRAD_LANES;
   if (vis) {
-    vis_flag[i] = 0u;
 #pragma unroll
-    for (int k = 0; k < GRAD_LANES; k++) { g[k] = vs[k]; vs[k] = 0.f; }
+    for (int k = 0; k < GRAD_LANES; k++) g[k] = vs[k];
   } else {
 #pragma unroll
     for (int k = 0; k < GRAD_LANES; k++) g[k] = 0.f;
@@ -122,6 +121,11 @@ __device__ __forceinline__ void splat_gradient(int i, size_t cap, const float4* 
   bool any = false, finite = true;
 #pragma unroll
   for (int k = 0; k < GRAD_LANES; k++) { if (k != 9 && g[k] != 0.f) any = true; finite = finite && isfinite(g[k]); }
+  if (vis) {   // cleared only once the loads have landed: a store issued right behind the load of its own line stalls both
+    vis_flag[i] = 0u;
+#pragma unroll
+    for (int k = 0; k < GRAD_LANES; k++) vs[k] = 0.f;
+  }
   sg.any = any && sg.visible && finite;
   sg.pg.pos = make_float3(0.f, 0.f, 0.f); sg.pg.op = 0.f; sg.pg.q = make_float4(0.f, 0.f, 0.f, 0.f); sg.pg.ls = make_float3(0.f, 0.f, 0.f);
   sg.vc = make_float3(0.f, 0.f, 0.f);
@@ -206,10 +210,37 @@ struct ModelPtrs {
   size_t cap;
 };
 
-// Update of one splat. g_sh(k, ch) yields the SH gradient lane; gsq is the mean squared SH gradient.
-template <int DEG, class ShGrad>
-__device__ __forceinline__ void adam_update(int i, const ModelPtrs& mp, const B2kOptim& op, const ParamGrad& pg, float gsq, ShGrad g_sh, bool visible) {
-  constexpr int K = (DEG + 1) * (DEG + 1);
+// MCMC noise on the means, strongest for near-transparent splats (optim.cu:363-376). ls holds the updated log scales
+// and the 3D-filter floor.
+__device__ __forceinline__ void add_mcmc_noise(float4& po, const float4& ls, int i, const B2kOptim& op, bool visible) {
+  if (!(op.noise_weight > 0.f) || !visible) return;
+  const float sig = 1.f / (1.f + __expf(-po.w));
+  const float f2 = ls.w * ls.w;
+  const float3 s2 = make_float3(__expf(2.f * ls.x), __expf(2.f * ls.y), __expf(2.f * ls.z));
+  const float comp = ls.w > 0.f ? sqrtf((s2.x * s2.y * s2.z) / ((s2.x + f2) * (s2.y + f2) * (s2.z + f2))) : 1.f;
+  const float o = fminf(fmaxf(sig * comp, 0.f), 1.f);
+  const float w = fminf(fmaxf(powf(1.f - o, 150.f), 0.f), 1.f) * op.noise_weight;
+  if (w > 0.f) {
+    const uint32_t s = op.seed ^ (op.step * 0x9E3779B9u);
+    const float cl = op.noise_clamp;
+    po.x += fminf(fmaxf(hash_normal(s, (uint32_t)i, 0u) * w, -cl), cl);
+    po.y += fminf(fmaxf(hash_normal(s, (uint32_t)i, 1u) * w, -cl), cl);
+    po.z += fminf(fmaxf(hash_normal(s, (uint32_t)i, 2u) * w, -cl), cl);
+  }
+}
+
+// What the SH lanes of a splat need from its per-splat part of the update.
+struct ShStep { float denom, denom_old, d1; bool catch_up; };
+
+__device__ __forceinline__ void adam_sh_lane(float& p, float& m, float g, float lrk, float b1, const ShStep& st) {
+  if (st.catch_up) { p -= lrk * st.denom_old * m; m *= st.d1; }
+  m = b1 * m + (1.f - b1) * g;
+  p -= lrk * st.denom * m;
+}
+
+// Everything of one splat's update except its SH lanes: lazy catch-up bookkeeping, means / opacity / rotation / scale,
+// the Adam-mini second moment of the SH block (gsq is the mean squared SH gradient), MCMC noise.
+__device__ __forceinline__ ShStep adam_geometry(int i, const ModelPtrs& mp, const B2kOptim& op, const ParamGrad& pg, float gsq, bool visible) {
   float skipped = 0.f;
   if (op.sparse) {
     const uint32_t ls = mp.last_step[i];
@@ -217,64 +248,62 @@ __device__ __forceinline__ void adam_update(int i, const ModelPtrs& mp, const B2
     mp.last_step[i] = (uint32_t)op.t;
   }
   const AdamConsts a = adam_consts(op, skipped);
-  float4 po = mp.pos_op[i];
+  // All records are loaded before the first store: the arrays may alias as far as the compiler knows, so a
+  // load-update-store sequence per record would run one memory round trip each.
+  float4 po = mp.pos_op[i], q = mp.quat[i], ls = mp.lscale[i];
+  float4 m_po = mp.m_pos[i], v_po = mp.v_pos[i], m_q = mp.m_q[i], v_q = mp.v_q[i], m_l = mp.m_ls[i], v_l = mp.v_ls[i];
+  const float v_sh_in = mp.v_sh[i];
+  adam4(po, m_po, v_po, make_float4(pg.pos.x, pg.pos.y, pg.pos.z, pg.op), make_float4(op.lr_mean, op.lr_mean, op.lr_mean, op.lr_opac), a);
+  adam4(q, m_q, v_q, pg.q, make_float4(op.lr_rot, op.lr_rot, op.lr_rot, op.lr_rot), a);
   {
-    float4 m = mp.m_pos[i], v = mp.v_pos[i];
-    adam4(po, m, v, make_float4(pg.pos.x, pg.pos.y, pg.pos.z, pg.op), make_float4(op.lr_mean, op.lr_mean, op.lr_mean, op.lr_opac), a);
-    mp.m_pos[i] = m; mp.v_pos[i] = v;
-  }
-  {
-    float4 q = mp.quat[i], m = mp.m_q[i], v = mp.v_q[i];
-    adam4(q, m, v, pg.q, make_float4(op.lr_rot, op.lr_rot, op.lr_rot, op.lr_rot), a);
-    mp.m_q[i] = m; mp.v_q[i] = v; mp.quat[i] = q;
-  }
-  float4 ls = mp.lscale[i];
-  {
-    float4 m = mp.m_ls[i], v = mp.v_ls[i];
     const float keep = ls.w;
-    adam4(ls, m, v, make_float4(pg.ls.x, pg.ls.y, pg.ls.z, 0.f), make_float4(op.lr_scale, op.lr_scale, op.lr_scale, 0.f), a);
-    ls.w = keep; m.w = 0.f; v.w = 0.f;   // the floor lane is a frozen constant
-    mp.m_ls[i] = m; mp.v_ls[i] = v; mp.lscale[i] = ls;
+    adam4(ls, m_l, v_l, make_float4(pg.ls.x, pg.ls.y, pg.ls.z, 0.f), make_float4(op.lr_scale, op.lr_scale, op.lr_scale, 0.f), a);
+    ls.w = keep; m_l.w = 0.f; v_l.w = 0.f;   // the floor lane is a frozen constant
   }
-  {
-    // Adam-mini: one second moment per splat, the EMA of the mean squared SH gradient (optim.cu:337-345).
-    const float v_old = mp.v_sh[i] * a.d2;
-    const float denom_old = a.catch_up ? a.drift * a.bc1 / (sqrtf(v_old * a.bc2) + a.eps) : 0.f;
-    const float v = a.b2 * v_old + (1.f - a.b2) * gsq;
-    mp.v_sh[i] = v;
-    const float denom = a.bc1 / (sqrtf(v * a.bc2) + a.eps);
+  mp.m_pos[i] = m_po; mp.v_pos[i] = v_po;
+  mp.m_q[i] = m_q; mp.v_q[i] = v_q; mp.quat[i] = q;
+  mp.m_ls[i] = m_l; mp.v_ls[i] = v_l; mp.lscale[i] = ls;
+  // Adam-mini: one second moment per splat, the EMA of the mean squared SH gradient (optim.cu:337-345).
+  ShStep st;
+  const float v_old = v_sh_in * a.d2;
+  st.catch_up = a.catch_up; st.d1 = a.d1;
+  st.denom_old = a.catch_up ? a.drift * a.bc1 / (sqrtf(v_old * a.bc2) + a.eps) : 0.f;
+  const float v = a.b2 * v_old + (1.f - a.b2) * gsq;
+  mp.v_sh[i] = v;
+  st.denom = a.bc1 / (sqrtf(v * a.bc2) + a.eps);
+  add_mcmc_noise(po, ls, i, op, visible);
+  mp.pos_op[i] = po;
+  return st;
+}
+
+__device__ __forceinline__ float* sh_lane_ptr(float* dc, float* hi, size_t cap, int l, int i) {
+  return l < 3 ? dc + (size_t)l * cap + i : hi + (size_t)(l - 3) * cap + i;
+}
+
+// Update of one splat by one thread. g_sh(k, ch) yields the SH gradient lane.
+template <int DEG, class ShGrad>
+__device__ __forceinline__ void adam_update(int i, const ModelPtrs& mp, const B2kOptim& op, const ParamGrad& pg, float gsq, ShGrad g_sh, bool visible) {
+  constexpr int K = (DEG + 1) * (DEG + 1);
+  const ShStep st = adam_geometry(i, mp, op, pg, gsq, visible);
+  constexpr int GROUP = 12;   // lanes whose loads are issued together before the group's stores
 #pragma unroll
-    for (int k = 0; k < K; k++) {
-      const float lrk = k == 0 ? op.lr_dc : op.lr_sh_rest;
+  for (int l0 = 0; l0 < K * 3; l0 += GROUP) {
+    float m_in[GROUP], p_in[GROUP];
 #pragma unroll
-      for (int ch = 0; ch < 3; ch++) {
-        float* pp = k == 0 ? mp.sh_dc + (size_t)ch * mp.cap + i : mp.sh_hi + (size_t)((k - 1) * 3 + ch) * mp.cap + i;
-        float* pm = k == 0 ? mp.m_sh_dc + (size_t)ch * mp.cap + i : mp.m_sh_hi + (size_t)((k - 1) * 3 + ch) * mp.cap + i;
-        float m_old = *pm, p = *pp;
-        if (a.catch_up) { p -= lrk * denom_old * m_old; m_old *= a.d1; }
-        const float m = a.b1 * m_old + (1.f - a.b1) * g_sh(k, ch);
-        *pm = m;
-        *pp = p - lrk * denom * m;
+    for (int u = 0; u < GROUP; u++) {
+      const int l = l0 + u;
+      if (l < K * 3) { m_in[u] = *sh_lane_ptr(mp.m_sh_dc, mp.m_sh_hi, mp.cap, l, i); p_in[u] = *sh_lane_ptr(mp.sh_dc, mp.sh_hi, mp.cap, l, i); }
+    }
+#pragma unroll
+    for (int u = 0; u < GROUP; u++) {
+      const int l = l0 + u;
+      if (l < K * 3) {
+        adam_sh_lane(p_in[u], m_in[u], g_sh(l / 3, l % 3), l < 3 ? op.lr_dc : op.lr_sh_rest, op.beta1, st);
+        *sh_lane_ptr(mp.m_sh_dc, mp.m_sh_hi, mp.cap, l, i) = m_in[u];
+        *sh_lane_ptr(mp.sh_dc, mp.sh_hi, mp.cap, l, i) = p_in[u];
       }
     }
   }
-  // MCMC noise on the means, strongest for near-transparent splats (optim.cu:363-376).
-  if (op.noise_weight > 0.f && visible) {
-    const float sig = 1.f / (1.f + __expf(-po.w));
-    const float f2 = ls.w * ls.w;
-    const float3 s2 = make_float3(__expf(2.f * ls.x), __expf(2.f * ls.y), __expf(2.f * ls.z));
-    const float comp = ls.w > 0.f ? sqrtf((s2.x * s2.y * s2.z) / ((s2.x + f2) * (s2.y + f2) * (s2.z + f2))) : 1.f;
-    const float o = fminf(fmaxf(sig * comp, 0.f), 1.f);
-    const float w = fminf(fmaxf(powf(1.f - o, 150.f), 0.f), 1.f) * op.noise_weight;
-    if (w > 0.f) {
-      const uint32_t s = op.seed ^ (op.step * 0x9E3779B9u);
-      const float cl = op.noise_clamp;
-      po.x += fminf(fmaxf(hash_normal(s, (uint32_t)i, 0u) * w, -cl), cl);
-      po.y += fminf(fmaxf(hash_normal(s, (uint32_t)i, 1u) * w, -cl), cl);
-      po.z += fminf(fmaxf(hash_normal(s, (uint32_t)i, 2u) * w, -cl), cl);
-    }
-  }
-  mp.pos_op[i] = po;
 }
 
 template <int DEG>
@@ -329,32 +358,131 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
   for (int k = 0; k < K; k++) { o[11 + k * 3] += basis[k] * sg.vc.x; o[12 + k * 3] += basis[k] * sg.vc.y; o[13 + k * 3] += basis[k] * sg.vc.z; }
 }
 
+// The update half of the data-parallel split. The accumulator is row-major [n][PER] (the all-reduce buffer); parameters
+// and moments are float4 records per splat plus planar SH lanes. One thread per splat is a long latency-bound chain
+// (a hundred loads, a dozen square roots and divisions) with too few warps to hide it: it measured under a third of
+// the copy bandwidth. Here FOUR threads share a splat, and a CTA takes 128 splats (64 at SH degree 4):
+//   1. all warps stage the accumulator rows through shared memory (coalesced 16-byte loads issued together) and clear
+//      them;
+//   2. the four threads of a splat each reduce a quarter of its row (touched? sum of squared SH gradients);
+//   3. role 0 updates mean + opacity, role 1 the rotation, role 2 the scales, role 3 the Adam-mini second moment of
+//      the SH block, whose step size it publishes; every role has already issued the loads of its quarter of the SH
+//      lanes (lane l belongs to role l mod 4; a warp holds one role of 32 consecutive splats, so every access is a
+//      coalesced 128- or 512-byte run);
+//   4. the SH lanes are updated; role 0 adds the MCMC noise (it needs role 2's scales) and stores the mean; role 3
+//      stamps last_step, which all four read in step 3.
+#ifndef B2K_ADAM_SPLATS
+#define B2K_ADAM_SPLATS 128
+#endif
+template <int DEG> struct AdamShape { static constexpr int SPLATS = DEG <= 3 ? B2K_ADAM_SPLATS : 64, THREADS = 4 * SPLATS; };
+
 template <int DEG>
-__global__ void __launch_bounds__(OPT_BLOCK) adam_kernel(int n, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
-  constexpr int K = (DEG + 1) * (DEG + 1), PER = 11 + 3 * K;
-  // The accumulator is row-major [n][PER] (the all-reduce buffer): a CTA's 128 rows are one contiguous block, staged
-  // through shared memory with coalesced loads and cleared with coalesced stores; a thread then reads its own row at
-  // stride PER (odd: conflict-free).
-  extern __shared__ float s_rows[];
-  const int base = blockIdx.x * OPT_BLOCK;
-  const int rows = n - base < OPT_BLOCK ? n - base : OPT_BLOCK;
+__global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>::THREADS) adam_kernel(int n, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
+  constexpr int SPLATS = AdamShape<DEG>::SPLATS, THREADS = AdamShape<DEG>::THREADS;
+  constexpr int K = (DEG + 1) * (DEG + 1), L = 3 * K, PER = 11 + L, QUARTER = (PER + 3) / 4, LPT = (L + 3) / 4;
+  __shared__ __align__(16) float s_rows[SPLATS * PER];
+  __shared__ float s_sq[4][SPLATS], s_denom[SPLATS], s_denom_old[SPLATS];
+  __shared__ int s_any[4][SPLATS];
+  __shared__ float4 s_ls[SPLATS];
+  const int base = blockIdx.x * SPLATS;
+  const int rows = n - base < SPLATS ? n - base : SPLATS;
   float* gblock = grad + (size_t)base * PER;
-  for (int k = threadIdx.x; k < rows * PER; k += OPT_BLOCK) { s_rows[k] = gblock[k]; gblock[k] = 0.f; }
+  if (rows == SPLATS) {
+    constexpr int WORDS = SPLATS * PER / 4, BATCH = (WORDS + THREADS - 1) / THREADS;   // whole 16-byte words from an aligned start
+    float4* g4 = reinterpret_cast<float4*>(gblock);
+    float4* s4 = reinterpret_cast<float4*>(s_rows);
+    float4 r[BATCH];
+#pragma unroll
+    for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) r[u] = __ldcs(g4 + k); }
+#pragma unroll
+    for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) s4[k] = r[u]; }
+  } else {
+    for (int k = threadIdx.x; k < rows * PER; k += THREADS) { s_rows[k] = gblock[k]; gblock[k] = 0.f; }
+  }
   __syncthreads();
-  const int i = base + threadIdx.x;
-  if (i >= n) return;
-  const float* g = s_rows + threadIdx.x * PER;
-  bool any = false;
+  // The rows are cleared only now, once the loads above have landed: a store issued right behind the load of the same
+  // line measured 2.5x slower for the whole kernel than one issued after it.
+  if (rows == SPLATS) {
+    constexpr int WORDS = SPLATS * PER / 4;
+    float4* g4 = reinterpret_cast<float4*>(gblock);
+    for (int k = threadIdx.x; k < WORDS; k += THREADS) __stcs(g4 + k, make_float4(0.f, 0.f, 0.f, 0.f));
+  }
+  const int role = threadIdx.x / SPLATS, sp = threadIdx.x % SPLATS, i = base + sp;
+  const float* g = s_rows + sp * PER;
+  {
+    bool any_q = false; float sq_q = 0.f;
+    if (sp < rows) {
 #pragma unroll
-  for (int k = 0; k < PER; k++) any = any || g[k] != 0.f;
-  if (op.sparse && !any) return;
-  ParamGrad pg;
-  pg.pos = make_float3(g[0], g[1], g[2]); pg.op = g[3]; pg.q = make_float4(g[4], g[5], g[6], g[7]); pg.ls = make_float3(g[8], g[9], g[10]);
-  float gsq = 0.f;
+      for (int u = 0; u < QUARTER; u++) {
+        const int k = role * QUARTER + u;
+        if (k < PER) { const float x = g[k]; any_q = any_q || x != 0.f; if (k >= 11) sq_q += x * x; }
+      }
+    }
+    s_any[role][sp] = any_q; s_sq[role][sp] = sq_q;
+  }
+  __syncthreads();
+  const bool any = (s_any[0][sp] | s_any[1][sp] | s_any[2][sp] | s_any[3][sp]) != 0;
+  const bool live = sp < rows && (!op.sparse || any);   // a splat no view touched is skipped whole in sparse mode
+  float m_in[LPT], p_in[LPT];
+  AdamConsts a;
+  float4 po;
+  if (live) {
 #pragma unroll
-  for (int k = 11; k < PER; k++) gsq += g[k] * g[k];
-  gsq *= 1.f / (float)(K * 3);
-  adam_update<DEG>(i, mp, op, pg, gsq, [&](int k, int ch) { return g[11 + k * 3 + ch]; }, any);
+    for (int u = 0; u < LPT; u++) {
+      const int l = role + 4 * u;
+      if (l < L) { m_in[u] = *sh_lane_ptr(mp.m_sh_dc, mp.m_sh_hi, mp.cap, l, i); p_in[u] = *sh_lane_ptr(mp.sh_dc, mp.sh_hi, mp.cap, l, i); }
+    }
+    float skipped = 0.f;
+    if (op.sparse) {
+      const uint32_t ls = mp.last_step[i];
+      skipped = ls == 0u ? 0.f : fmaxf((float)op.t - (float)ls - 1.f, 0.f);
+    }
+    a = adam_consts(op, skipped);
+    if (role == 0) {
+      po = mp.pos_op[i];
+      float4 m = mp.m_pos[i], v = mp.v_pos[i];
+      adam4(po, m, v, make_float4(g[0], g[1], g[2], g[3]), make_float4(op.lr_mean, op.lr_mean, op.lr_mean, op.lr_opac), a);
+      mp.m_pos[i] = m; mp.v_pos[i] = v;
+    } else if (role == 1) {
+      float4 q = mp.quat[i], m = mp.m_q[i], v = mp.v_q[i];
+      adam4(q, m, v, make_float4(g[4], g[5], g[6], g[7]), make_float4(op.lr_rot, op.lr_rot, op.lr_rot, op.lr_rot), a);
+      mp.m_q[i] = m; mp.v_q[i] = v; mp.quat[i] = q;
+    } else if (role == 2) {
+      float4 ls = mp.lscale[i], m = mp.m_ls[i], v = mp.v_ls[i];
+      const float keep = ls.w;
+      adam4(ls, m, v, make_float4(g[8], g[9], g[10], 0.f), make_float4(op.lr_scale, op.lr_scale, op.lr_scale, 0.f), a);
+      ls.w = keep; m.w = 0.f; v.w = 0.f;   // the floor lane is a frozen constant
+      mp.m_ls[i] = m; mp.v_ls[i] = v; mp.lscale[i] = ls;
+      s_ls[sp] = ls;
+    } else {
+      // Adam-mini: one second moment per splat, the EMA of the mean squared SH gradient (optim.cu:337-345).
+      const float gsq = (s_sq[0][sp] + s_sq[1][sp] + s_sq[2][sp] + s_sq[3][sp]) * (1.f / (float)L);
+      const float v_old = mp.v_sh[i] * a.d2;
+      s_denom_old[sp] = a.catch_up ? a.drift * a.bc1 / (sqrtf(v_old * a.bc2) + a.eps) : 0.f;
+      const float v = a.b2 * v_old + (1.f - a.b2) * gsq;
+      mp.v_sh[i] = v;
+      s_denom[sp] = a.bc1 / (sqrtf(v * a.bc2) + a.eps);
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+  ShStep st;
+  st.denom = s_denom[sp]; st.denom_old = s_denom_old[sp]; st.d1 = a.d1; st.catch_up = a.catch_up;
+#pragma unroll
+  for (int u = 0; u < LPT; u++) {
+    const int l = role + 4 * u;
+    if (l < L) {
+      adam_sh_lane(p_in[u], m_in[u], g[11 + l], l < 3 ? op.lr_dc : op.lr_sh_rest, op.beta1, st);
+      *sh_lane_ptr(mp.m_sh_dc, mp.m_sh_hi, mp.cap, l, i) = m_in[u];
+      *sh_lane_ptr(mp.sh_dc, mp.sh_hi, mp.cap, l, i) = p_in[u];
+    }
+  }
+  if (role == 0) {
+    add_mcmc_noise(po, s_ls[sp], i, op, any);
+    mp.pos_op[i] = po;
+  } else if (role == 3 && op.sparse) {
+    mp.last_step[i] = (uint32_t)op.t;
+  }
 }
 
 // Indices of the splats whose visibility flag the backward set, appended in no particular order (one atomic per warp).
@@ -463,7 +591,7 @@ extern "C" int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_
   B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi) && has_moments(m) && op->t >= 1);
   if (m->n == 0) return B2K_OK;
   const ModelPtrs mp = model_ptrs(m);
-  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, sizeof(float) * OPT_BLOCK * (11 + 3 * (D + 1) * (D + 1)), (cudaStream_t)stream>>>(
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(m->n, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
       m->n, mp, *op, grad)));
   return check_launch();
 }

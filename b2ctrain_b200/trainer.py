@@ -61,6 +61,22 @@ class Trainer:
         self._staged_evt = [torch.cuda.Event() for _ in range(2 * self.lanes)]
         self._free_evt = [torch.cuda.Event() for _ in range(2 * self.lanes)]
         self.h2d_bytes = 0
+        self.profile = False     # when set, step() records an event after each phase (read with phase_ms())
+        self._marks = []
+
+    def _mark(self, name):
+        if self.profile:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(torch.cuda.current_stream(self.device))
+            self._marks.append((name, e))
+
+    def phase_ms(self):
+        """Device time of each phase of the last profiled step: {'views', 'fold', 'all_reduce', 'adam'}."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for (_, a), (name, b) in zip(self._marks[:-1], self._marks[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
 
     def my_views(self, n_views):
         return partition_views(n_views, self.rank, self.world)
@@ -109,6 +125,8 @@ class Trainer:
         self.step_no += 1
         mine = self.my_views(len(cams))
         self.ctx.loss_accum.zero_()
+        self._marks = []
+        self._mark("start")
         if self.world == 1 and len(cams) == 1:
             self.view_pass(cams[0], targets[0], bg, fused_op=self._op(cams[0]))
             return self.ctx.loss_accum
@@ -129,11 +147,15 @@ class Trainer:
                     self.view_pass(cams[v], targets[v], bg, slot=2 * lane + ((j // self.lanes) & 1), lane=lane)
             for lane in range(min(self.lanes, len(mine))):
                 done = torch.cuda.Event(); done.record(self.streams[lane]); main.wait_event(done)
+            self._mark("views")
             for lane in range(1, self.lanes):       # fold the lanes' accumulators and running losses into lane 0
                 self.grad.add_(self.grads[lane]); self.grads[lane].zero_()
                 self.ctx.loss_accum[2:4].add_(self.ctxs[lane].loss_accum[2:4])
+        self._mark("fold" if self.lanes > 1 else "views")
         reduce_gradients(self.grad, self.world)
+        self._mark("all_reduce")
         api.adam_step(m, self._op(cams[0]), self.grad)
+        self._mark("adam")
         return self.ctx.loss_accum
 
     def check_overflow(self):

@@ -289,6 +289,15 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         h2d = float(t.item())
     total_isect, over = tr.check_overflow()
     assert not over, "intersection buffers overflowed inside the timed region"
+    phases = None
+    if n_views > 1:   # one more step with an event after each phase; every phase reported as the max over ranks
+        barrier()
+        tr.profile = True
+        tr.step(cams, dev_targets)
+        tr.profile = False
+        mine_ms = tr.phase_ms()
+        phases = {k: max_over_ranks(v) for k, v in sorted(mine_ms.items())}
+        phases["views_fastest_rank"] = -max_over_ranks(-mine_ms["views"])
 
     views_per_step = n_views
     value = views_per_step * args.steps / (ms / 1e3)
@@ -301,6 +310,8 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
                       "scene_counts_view0": stats[0] if stats else None},
            "e2e": {"value": e2e_value, "unit": "views/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 64, "ms_per_step": ms_e2e / args.steps},
            "gpu_launches": launches, "clocks": clocks, "loss_last_view": float(loss[0]) if loss is not None else None}
+    if phases:
+        res["step_phases_ms_max_over_ranks"] = phases
     if rank == 0:
         res["roofline"], res["stages"] = stage_roofline(args, tr, cams, dev_targets, mine, stats)
         if world == 1 and not args.no_incumbent:
