@@ -87,6 +87,7 @@ SIGNATURES = {
     "b2k_optim_fused": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_proj_bwd": (C.c_int, [_P, _P, _P, _P, _P, _S]),
     "b2k_adam": (C.c_int, [_P, _P, _P, _S]),
+    "b2k_adam_range": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _S]),
     "b2k_min_scale": (C.c_int, [_P, _P, _P, C.c_int32, _S]),
     "b2k_pack_rgba8": (C.c_int, [_P, _P, C.c_int32, C.c_int32, _S]),
     "b2k_error_string": (C.c_char_p, [C.c_int]),
@@ -474,9 +475,15 @@ def projection_backward(ctx, m, op, grad, stream=None):
     _check(lib().b2k_proj_bwd(C.byref(cs), C.byref(ms), C.byref(cam), C.byref(os_), _ptr(grad), _stream(stream)), "projection_backward")
 
 
-def adam_step(m, op, grad, stream=None):
+def adam_step(m, op, grad, stream=None, first=0, count=None):
+    """The update half of the data-parallel split from the accumulator grad[n][11+3K]; first/count restrict it to a
+    slice of splats (first a multiple of 4)."""
     ms, os_ = m.struct(), op.struct()
-    _check(lib().b2k_adam(C.byref(ms), C.byref(os_), _ptr(grad), _stream(stream)), "adam_step")
+    if first == 0 and count is None:
+        _check(lib().b2k_adam(C.byref(ms), C.byref(os_), _ptr(grad), _stream(stream)), "adam_step")
+    else:
+        count = m.n - first if count is None else count
+        _check(lib().b2k_adam_range(C.byref(ms), C.byref(os_), _ptr(grad), int(first), int(count), _stream(stream)), "adam_step")
 
 
 def update_min_scale(m, cam_pos, cam_focal, stream=None):

@@ -377,15 +377,15 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
 template <int DEG> struct AdamShape { static constexpr int SPLATS = DEG <= 3 ? B2K_ADAM_SPLATS : 64, THREADS = 4 * SPLATS; };
 
 template <int DEG>
-__global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>::THREADS) adam_kernel(int n, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
+__global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>::THREADS) adam_kernel(int first, int end, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
   constexpr int SPLATS = AdamShape<DEG>::SPLATS, THREADS = AdamShape<DEG>::THREADS;
   constexpr int K = (DEG + 1) * (DEG + 1), L = 3 * K, PER = 11 + L, QUARTER = (PER + 3) / 4, LPT = (L + 3) / 4;
   __shared__ __align__(16) float s_rows[SPLATS * PER];
   __shared__ float s_sq[4][SPLATS], s_denom[SPLATS], s_denom_old[SPLATS];
   __shared__ int s_any[4][SPLATS];
   __shared__ float4 s_ls[SPLATS];
-  const int base = blockIdx.x * SPLATS;
-  const int rows = n - base < SPLATS ? n - base : SPLATS;
+  const int base = first + blockIdx.x * SPLATS;   // first is a multiple of four, which keeps the block 16-byte aligned
+  const int rows = end - base < SPLATS ? end - base : SPLATS;
   float* gblock = grad + (size_t)base * PER;
   if (rows == SPLATS) {
     constexpr int WORDS = SPLATS * PER / 4, BATCH = (WORDS + THREADS - 1) / THREADS;   // whole 16-byte words from an aligned start
@@ -586,14 +586,20 @@ extern "C" int b2k_proj_bwd(const B2kCtx* c, const B2kModel* m, const B2kCamera*
   return check_launch();
 }
 
-extern "C" int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t stream) {
+extern "C" int b2k_adam_range(const B2kModel* m, const B2kOptim* op, float* grad, int32_t first, int32_t count, b2k_stream_t stream) {
   B2K_REQUIRE(m && op && grad && m->n >= 0 && m->cap >= m->n && m->degree >= 0 && m->degree <= 4);
   B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi) && has_moments(m) && op->t >= 1);
-  if (m->n == 0) return B2K_OK;
+  B2K_REQUIRE(first >= 0 && count >= 0 && first % 4 == 0 && (int64_t)first + count <= m->n);
+  if (count == 0) return B2K_OK;
   const ModelPtrs mp = model_ptrs(m);
-  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(m->n, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
-      m->n, mp, *op, grad)));
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(count, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
+      first, first + count, mp, *op, grad)));
   return check_launch();
+}
+
+extern "C" int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t stream) {
+  B2K_REQUIRE(m && m->n >= 0);
+  return b2k_adam_range(m, op, grad, 0, m->n, stream);
 }
 
 extern "C" int b2k_min_scale(const B2kModel* m, const float* cam_pos, const float* cam_focal, int32_t n_cams, b2k_stream_t stream) {

@@ -8,8 +8,9 @@ one GPU; here a step may hold several views and several ranks:
   * every rank holds a full model replica and renders the views `rank, rank + world, ...` of the step;
   * each view's projection backward ADDS into a dense per-splat gradient accumulator [n][11+3K] (the layout of the
     reference's OptimParams::grad_out lane, src/gpu/optim.cu:292-297);
-  * one all-reduce (sum) of that accumulator over NCCL, then the identical Adam update on every rank, so replicas stay
-    bit-identical. The step loss is the sum of the per-view losses (its gradient is the all-reduced sum).
+  * an all-reduce (sum) of that accumulator over NCCL, then the identical Adam update on every rank, so replicas stay
+    bit-identical. The accumulator is reduced in a few slices of splats and the update of a slice runs while the next
+    slice is still on the wire. The step loss is the sum of the per-view losses (its gradient is the all-reduced sum).
 
 A single-view, single-rank step uses the fused projection-backward + Adam kernel exactly like the reference.
 `Renderer.render` follows render_main's per-camera loop (src/render/renderer.cpp:345-363) up to the device image.
@@ -25,6 +26,16 @@ def partition_views(n_views, rank, world):
     return list(range(rank, n_views, world))
 
 
+def slice_bounds(n, slices, align=128):
+    """Splits the splats [0, n) into up to `slices` contiguous ranges whose starts are multiples of `align` (the update
+    kernel's block), returned as (first, count) pairs that cover [0, n) exactly."""
+    if n <= 0:
+        return []
+    per = -(-n // max(1, slices))
+    per = -(-per // align) * align
+    return [(a, min(per, n - a)) for a in range(0, n, per)]
+
+
 def reduce_gradients(grad, world):
     """Sum of the per-rank gradient accumulators over all ranks (NCCL on GPUs, gloo in the CPU tests)."""
     if world > 1:
@@ -34,13 +45,14 @@ def reduce_gradients(grad, world):
 
 class Trainer:
     def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, lr_mean=1.6e-4, sparse=True, noise_weight=0.0,
-                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None, views_in_flight=1):
+                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None, views_in_flight=1, reduce_slices=4):
         self.device = torch.device(device)
         self.rank, self.world = rank, world
         self.model = api.Model(device).upload(cloud)
         # One context, stream and gradient accumulator per view in flight: views of a step are independent until the
         # update, so the latency-bound raster kernels of one view overlap the throughput-bound binning of another.
         self.lanes = max(1, int(views_in_flight))
+        self.reduce_slices = int(reduce_slices)
         self.ctxs = [api.RenderCtx(device) for _ in range(self.lanes)]
         for c in self.ctxs:
             c.setup(W, H, self.model.cap, isect_cap=isect_cap)
@@ -71,7 +83,8 @@ class Trainer:
             self._marks.append((name, e))
 
     def phase_ms(self):
-        """Device time of each phase of the last profiled step: {'views', 'fold', 'all_reduce', 'adam'}."""
+        """Device time of each phase of the last profiled step: 'views', 'fold', then 'all_reduce' and 'adam' or, when
+        the two are pipelined by slices, 'all_reduce+adam'."""
         torch.cuda.synchronize(self.device)
         out = {}
         for (_, a), (name, b) in zip(self._marks[:-1], self._marks[1:]):
@@ -152,10 +165,20 @@ class Trainer:
                 self.grad.add_(self.grads[lane]); self.grads[lane].zero_()
                 self.ctx.loss_accum[2:4].add_(self.ctxs[lane].loss_accum[2:4])
         self._mark("fold" if self.lanes > 1 else "views")
-        reduce_gradients(self.grad, self.world)
-        self._mark("all_reduce")
-        api.adam_step(m, self._op(cams[0]), self.grad)
-        self._mark("adam")
+        op = self._op(cams[0])
+        if self.world == 1 or self.reduce_slices <= 1:
+            reduce_gradients(self.grad, self.world)
+            self._mark("all_reduce")
+            api.adam_step(m, op, self.grad)
+            self._mark("adam")
+        else:
+            # NCCL runs the slices in issue order on its own stream; the update of slice k waits for reduction k only.
+            bounds = slice_bounds(m.n, self.reduce_slices)
+            works = [torch.distributed.all_reduce(self.grad[a:a + c], op=torch.distributed.ReduceOp.SUM, async_op=True) for a, c in bounds]
+            for (a, c), w in zip(bounds, works):
+                w.wait()
+                api.adam_step(m, op, self.grad, first=a, count=c)
+            self._mark("all_reduce+adam")
         return self.ctx.loss_accum
 
     def check_overflow(self):

@@ -37,6 +37,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
     ap.add_argument("--views-in-flight", type=int, default=2, help="views of a step processed concurrently on separate streams")
+    ap.add_argument("--reduce-slices", type=int, default=4, help="slices of the gradient all-reduce pipelined with the Adam update (N > 1)")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
 
@@ -247,7 +248,7 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         dev_targets[v] = host_targets_mine[j].to(device)
     median_scale = float(np.median(np.exp(scene["lscale"][:, :3])))
     tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=0.0, isect_cap=cap,
-                 views_in_flight=1 if n_views == 1 else args.views_in_flight)
+                 views_in_flight=1 if n_views == 1 else args.views_in_flight, reduce_slices=args.reduce_slices)
     if cfg == 4:   # per-pixel binary mask in the alpha byte, alpha-match lane, --normalize-masked-loss
         mask = torch.from_numpy(scenes.ellipse_mask(W, H, 0.4).astype(np.int64))
         for v in mine:

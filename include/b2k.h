@@ -178,6 +178,10 @@ int b2k_optim_fused(const B2kCtx* ctx, const B2kModel* m, const B2kCamera* cam, 
  * whose accumulated gradient is all zero are skipped when op->sparse; clears the accumulator rows it consumed. */
 int b2k_proj_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, float* grad, b2k_stream_t s);
 int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t s);
+/* b2k_adam on the splats [first, first + count) only (grad is still the whole accumulator; first a multiple of 4), so
+ * that the update of one slice can run while the all-reduce of the next slice is in flight. Same device code and the
+ * same results as b2k_adam over the whole model (optim.cu:299-376). */
+int b2k_adam_range(const B2kModel* m, const B2kOptim* op, float* grad, int32_t first, int32_t count, b2k_stream_t s);
 
 /* ---- helpers around the path ---- */
 /* min_scale_kernel, src/gpu/refine.cu:27-38: lscale.w = sqrt(0.1) * min over cameras of distance / focal. */

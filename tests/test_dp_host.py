@@ -14,7 +14,7 @@ import os, sys
 sys.path.insert(0, os.environ["B2K_ROOT"])
 import numpy as np, torch, torch.distributed as dist
 from b2ctrain_b200 import scenes
-from b2ctrain_b200.trainer import partition_views, reduce_gradients
+from b2ctrain_b200.trainer import partition_views, reduce_gradients, slice_bounds
 from oracle import orc
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -27,6 +27,11 @@ mine = partition_views(len(cams), rank, world)
 acc = np.zeros((scene["n"], 11 + 3 * 4))
 for v in mine: acc += view_grad(v)
 g = reduce_gradients(torch.from_numpy(acc.copy()), world).numpy()
+# the sliced reduction the GPU step pipelines with the update gives the same bits as the whole-buffer one
+gs = torch.from_numpy(acc.copy())
+works = [dist.all_reduce(gs[a:a + c], async_op=True) for a, c in slice_bounds(scene["n"], 3)]
+for w in works: w.wait()
+assert np.array_equal(gs.numpy(), g)
 z4 = lambda: np.zeros((scene["n"], 4), np.float32)
 state = dict(pos_op=scene["pos_op"].copy(), quat=scene["quat"].copy(), lscale=scene["lscale"].copy(), sh=scene["sh"].copy(), m_pos=z4(), v_pos=z4(), m_q=z4(),
              v_q=z4(), m_ls=z4(), v_ls=z4(), m_sh=np.zeros((scene["n"], 4, 3), np.float32), v_sh=np.zeros(scene["n"], np.float32), last_step=np.zeros(scene["n"], np.uint32))
@@ -56,3 +61,15 @@ def test_two_rank_gloo_step(tmp_path):
     assert np.allclose(r0["g"], serial, rtol=1e-12, atol=1e-15)    # = the sum of the per-view gradients
     assert np.array_equal(r0["pos"], r1["pos"]) and np.array_equal(r0["sh"], r1["sh"])   # replicas stay bit-identical
     assert np.abs(r0["g"]).max() > 0
+
+
+def test_slice_bounds_cover_the_model_on_block_boundaries():
+    from b2ctrain_b200.trainer import slice_bounds
+    for n in (0, 1, 127, 128, 129, 3000, 3_000_000, 3_000_001):
+        for slices in (1, 3, 4, 7):
+            b = slice_bounds(n, slices)
+            assert len(b) <= max(1, slices) and sum(c for _, c in b) == n
+            pos = 0
+            for a, c in b:
+                assert a == pos and a % 128 == 0 and c > 0
+                pos += c
