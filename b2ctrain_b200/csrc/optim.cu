@@ -351,11 +351,17 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
   splat_gradient<DEG>(i, mp.cap, mp.pos_op, mp.quat, mp.lscale, mp.sh_dc, mp.sh_hi, v_splat, vis_flag, tile_count, refine_norm, vis_count, cam, active,
                       (const float4*)op.pos_override, (const float4*)op.quat_override, (const float4*)op.lscale_override, sg, basis);
   if (!sg.any) return;
+  // Several views of a step may be in flight on different streams and add into the same accumulator: reductions
+  // (fire-and-forget RED.ADD at the L2), not read-modify-write.
   float* o = grad + (size_t)i * (11 + K * 3);
-  o[0] += sg.pg.pos.x; o[1] += sg.pg.pos.y; o[2] += sg.pg.pos.z; o[3] += sg.pg.op;
-  o[4] += sg.pg.q.x; o[5] += sg.pg.q.y; o[6] += sg.pg.q.z; o[7] += sg.pg.q.w; o[8] += sg.pg.ls.x; o[9] += sg.pg.ls.y; o[10] += sg.pg.ls.z;
+  atomicAdd(o + 0, sg.pg.pos.x); atomicAdd(o + 1, sg.pg.pos.y); atomicAdd(o + 2, sg.pg.pos.z); atomicAdd(o + 3, sg.pg.op);
+  atomicAdd(o + 4, sg.pg.q.x); atomicAdd(o + 5, sg.pg.q.y); atomicAdd(o + 6, sg.pg.q.z); atomicAdd(o + 7, sg.pg.q.w);
+  atomicAdd(o + 8, sg.pg.ls.x); atomicAdd(o + 9, sg.pg.ls.y); atomicAdd(o + 10, sg.pg.ls.z);
 #pragma unroll
-  for (int k = 0; k < K; k++) { o[11 + k * 3] += basis[k] * sg.vc.x; o[12 + k * 3] += basis[k] * sg.vc.y; o[13 + k * 3] += basis[k] * sg.vc.z; }
+  for (int k = 0; k < K; k++) {
+    const float bk = basis[k];
+    if (bk != 0.f) { atomicAdd(o + 11 + k * 3, bk * sg.vc.x); atomicAdd(o + 12 + k * 3, bk * sg.vc.y); atomicAdd(o + 13 + k * 3, bk * sg.vc.z); }
+  }
 }
 
 // The update half of the data-parallel split. The accumulator is row-major [n][PER] (the all-reduce buffer); parameters

@@ -49,8 +49,9 @@ class Trainer:
         self.device = torch.device(device)
         self.rank, self.world = rank, world
         self.model = api.Model(device).upload(cloud)
-        # One context, stream and gradient accumulator per view in flight: views of a step are independent until the
-        # update, so the latency-bound raster kernels of one view overlap the throughput-bound binning of another.
+        # One context and stream per view in flight: views of a step are independent until the update, so the
+        # latency-bound raster kernels of one view overlap the throughput-bound binning of another. All of them add
+        # into one gradient accumulator (the projection backward accumulates with reductions at the L2).
         self.lanes = max(1, int(views_in_flight))
         self.reduce_slices = int(reduce_slices)
         self.ctxs = [api.RenderCtx(device) for _ in range(self.lanes)]
@@ -63,8 +64,7 @@ class Trainer:
         self.noise_weight, self.noise_clamp = noise_weight, noise_clamp
         self.lp = api.LossParams(l1_w=1.0 - ssim_weight, ssim_w=-ssim_weight)
         K = self.model.K()
-        self.grads = [torch.zeros((self.model.n, 11 + 3 * K), dtype=torch.float32, device=self.device) for _ in range(self.lanes)]
-        self.grad = self.grads[0]
+        self.grad = torch.zeros((self.model.n, 11 + 3 * K), dtype=torch.float32, device=self.device)
         self.step_no = 0
         P = W * H
         # device staging for targets that arrive from host memory (double-buffered on a copy stream)
@@ -83,7 +83,7 @@ class Trainer:
             self._marks.append((name, e))
 
     def phase_ms(self):
-        """Device time of each phase of the last profiled step: 'views', 'fold', then 'all_reduce' and 'adam' or, when
+        """Device time of each phase of the last profiled step: 'views', then 'all_reduce' and 'adam' or, when
         the two are pipelined by slices, 'all_reduce+adam'."""
         torch.cuda.synchronize(self.device)
         out = {}
@@ -124,7 +124,7 @@ class Trainer:
         if fused_op is not None:
             api.optimizer_step(ctx, m, fused_op)
         else:
-            api.projection_backward(ctx, m, self._op(cam), self.grads[lane])
+            api.projection_backward(ctx, m, self._op(cam), self.grad)
 
     def _op(self, cam):
         return api.OptimParams(cam, active_sh_degree=self.model.degree, t=self.model.adam_t, lr_mean=self.lr_mean, sparse=self.sparse,
@@ -160,11 +160,9 @@ class Trainer:
                     self.view_pass(cams[v], targets[v], bg, slot=2 * lane + ((j // self.lanes) & 1), lane=lane)
             for lane in range(min(self.lanes, len(mine))):
                 done = torch.cuda.Event(); done.record(self.streams[lane]); main.wait_event(done)
-            self._mark("views")
-            for lane in range(1, self.lanes):       # fold the lanes' accumulators and running losses into lane 0
-                self.grad.add_(self.grads[lane]); self.grads[lane].zero_()
+            for lane in range(1, self.lanes):       # fold the lanes' running losses into lane 0
                 self.ctx.loss_accum[2:4].add_(self.ctxs[lane].loss_accum[2:4])
-        self._mark("fold" if self.lanes > 1 else "views")
+        self._mark("views")
         op = self._op(cams[0])
         if self.world == 1 or self.reduce_slices <= 1:
             reduce_gradients(self.grad, self.world)

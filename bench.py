@@ -36,7 +36,7 @@ def parse():
     ap.add_argument("--views", type=int, default=None, help="override views per step / cameras (testing only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
-    ap.add_argument("--views-in-flight", type=int, default=2, help="views of a step processed concurrently on separate streams")
+    ap.add_argument("--views-in-flight", type=int, default=4, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--reduce-slices", type=int, default=4, help="slices of the gradient all-reduce pipelined with the Adam update (N > 1)")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
@@ -314,7 +314,7 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     if phases:
         res["step_phases_ms_max_over_ranks"] = phases
     if rank == 0:
-        res["roofline"], res["stages"] = stage_roofline(args, tr, cams, dev_targets, mine, stats)
+        res["roofline"], res["stages"] = stage_roofline(args, tr, cams, dev_targets, mine, stats, clocks)
         if world == 1 and not args.no_incumbent:
             res["reference_cuda"] = incumbent(scene, cams[mine[0]], host_targets[mine[0]], cfg == 4)
     return res
@@ -341,7 +341,7 @@ def incumbent(scene, cam, host_target, masked):
         return {"unavailable": str(e)[:200]}
 
 
-def stage_roofline(args, tr, cams, targets, mine, stats):
+def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     """Times each stage of a view with CUDA events (on the launching stream), a few views, and derives the roofline
     object for the dominant kernel. Algorithmic bytes per stage follow the per-unit figures stated in DESIGN.md."""
     import torch
@@ -410,6 +410,27 @@ def stage_roofline(args, tr, cams, targets, mine, stats):
         bytes_launch = alg[stage] if top != "scan_emit_kernel" else 24 * n + 8 * I
         note = "one launch per view"
         traffic = None
+    # Step roofline: every stage at the better of its HBM time and (for the two compositing kernels) its FP32 time.
+    # F = fragment-pixel evaluations of the last timed view (per pixel: last contributing index - start of its tile's
+    # list), charged 24 flop forward and 90 flop backward each; FP32 peak = 2 * 128 lanes * SMs * the SM clock.
+    rp = api.RenderParams(cams[views[-1]], sh_degree=m.degree, bwd_info=True)
+    api.render_forward(ctx, m, rp, sync=True)
+    tx = (torch.arange(ctx.W, device=ctx.last_idx.device) // 8).repeat(ctx.H)
+    ty = (torch.arange(ctx.H, device=ctx.last_idx.device) // 8).repeat_interleave(ctx.W)
+    start = ctx.tile_ranges.view(-1, 2)[:, 0].to(torch.int64)[ty * ctx.tiles_x + tx]
+    F = int((ctx.last_idx[:P].to(torch.int64) - start).clamp_(min=0).sum().item())
+    props = torch.cuda.get_device_properties(ctx.last_idx.device)
+    sm_mhz = float((clocks or {}).get("sm_mhz") or 1965.0)   # median SM clock sampled during the timed region
+    fp32_peak = 2 * 128 * props.multi_processor_count * sm_mhz * 1e6
+    t_roof = {nm: alg[nm] / (hbm * 1e9) * 1e3 for nm in names}
+    t_roof["raster_fwd"] = max(t_roof["raster_fwd"], 24 * F / fp32_peak * 1e3)
+    t_roof["raster_bwd"] = max(t_roof["raster_bwd"], 90 * F / fp32_peak * 1e3)
+    measured = sum(stages[nm]["ms"] for nm in names)
+    step_roof = {"t_roof_ms_per_view": sum(t_roof.values()), "t_measured_ms_per_view": measured, "frac": sum(t_roof.values()) / measured,
+                 "per_stage_frac": {nm: t_roof[nm] / stages[nm]["ms"] for nm in names}, "fragment_pixel_evaluations": F,
+                 "fp32_peak_tflops": fp32_peak / 1e12, "sm_mhz": sm_mhz,
+                 "note": "stages timed back to back on one stream; the optimizer update (once per step) is not included"}
+    stages["step_roofline"] = step_roof
     a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src,
             "ms_per_launch": per_launch_ms, "algorithmic_bytes_per_launch": int(bytes_launch), "note": note,
