@@ -51,31 +51,45 @@ class ClockSampler:
         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, gpu_index):
-        self.rows, self.proc, self.idx = [], None, gpu_index
+        self.rows, self.proc, self.idx, self.t_mark = [], None, gpu_index, None
 
     def start(self):
+        """Starts sampling (nvidia-smi needs about half a second before its first line: call this before the warm-up)."""
+        if self.proc is not None:
+            return
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
+    def mark(self):
+        """The timed region starts now: stop() reports the samples taken from here on."""
+        self.t_mark = time.monotonic()
+
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.monotonic(), [c.strip() for c in line.split(",")]))
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         self.thread.join(timeout=2)
-        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        self.proc = None
+        good = [(t, r) for t, r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        rows = [r for t, r in good if self.t_mark is None or t >= self.t_mark]
+        window = "timed region"
+        if not rows and good:   # a timed region shorter than the sampling period: the warm-up ran the same load just before it
+            rows, window = [r for _, r in good[-4:]], "warm-up and timed region"
+        sm = [float(r[0]) for r in rows]
+        mx = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [nm for k, nm in enumerate(names) if any(len(r) >= 7 and r[3 + k].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm)}
+        reasons = [nm for k, nm in enumerate(names) if any(r[3 + k].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm),
+                "window": window}
 
 
 def cpu_reference_arm(args, cfg):
@@ -275,8 +289,9 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         barrier()
         return max_over_ranks(e0.elapsed_time(e1)), loss
 
-    timed(dev_targets, args.warmup)
     sampler.start()
+    timed(dev_targets, args.warmup)
+    sampler.mark()
     ms, _ = timed(dev_targets, args.steps)
     clocks = sampler.stop()
     tr.h2d_bytes = 0
@@ -332,10 +347,10 @@ def incumbent(scene, cam, host_target, masked):
         ref.set_view(host_target.numpy().view(np.uint32))
         out = {}
         for name, tc in (("tc", True), ("warp", False)):
-            ms = ref.time_steps(tensor_core=tc, warm=2, iters=5, lr_mean=1e-6)
+            ms = ref.time_steps(tensor_core=tc, warm=2, iters=5, lr_mean=0.0)
             out[name] = {"ms_per_view": ms, "views_per_s": 1e3 / ms}
         ref.close()
-        out["what"] = "reference b2ctrain CUDA kernels, -O3 --use_fast_math, sm_100a, same B200, one view per step, 5 timed steps"
+        out["what"] = "reference b2ctrain CUDA kernels, -O3 --use_fast_math, sm_100a, same B200, one view per step, 5 timed steps, learning rates 0 so the scene stays fixed"
         return out
     except Exception as e:   # the incumbent is informative only
         return {"unavailable": str(e)[:200]}
@@ -460,8 +475,9 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
         barrier()
         return max_over_ranks(e0.elapsed_time(e1))
 
-    timed(max(1, args.warmup // 3), False)
     sampler.start()
+    timed(max(1, args.warmup // 3), False)
+    sampler.mark()
     ms = timed(args.steps, False)
     clocks = sampler.stop()
     ms_e2e = timed(args.steps, True)

@@ -138,6 +138,7 @@ uint32_t refcu_num_isect(void* hp) { return ((Handle*)hp)->ctx.num_isect; }
 
 // One training step of the reference (trainer.cpp:487-529): forward, loss, backward (tensor-core or warp), optimizer.
 // Returns the average milliseconds per step over `iters` timed steps (after `warm` untimed ones), CUDA events.
+// lr_mean == 0 zeroes every learning rate: the optimizer does all of its work but the scene does not drift between steps.
 float refcu_time_steps(void* hp, const float* intr, const float* R, const float* t, const float* bg, int tensor_core, int warm, int iters, float lr_mean) {
   Handle* h = (Handle*)hp;
   float ms = -1.f;
@@ -154,6 +155,7 @@ float refcu_time_steps(void* hp, const float* intr, const float* R, const float*
       accumulate_loss(h->ctx, 0);
       if (tensor_core) rasterize_backward_tc(h->ctx, h->model, rp, lp.grad_scale, 0); else rasterize_backward(h->ctx, h->model, rp, 0);
       OptimParams op; op.cam = rp.cam; op.active_sh_degree = h->model.degree; op.t = ++h->model.adam_t; op.lr_mean = lr_mean; op.sparse = true;
+      if (lr_mean == 0.f) op.lr_rot = op.lr_scale = op.lr_opac = op.lr_dc = op.lr_sh_rest = 0.f;   // timing on a scene that stays put
       optimizer_step(h->ctx, h->model, op, 0);
     }
     CUDA_CHECK(cudaEventRecord(e1, 0)); CUDA_CHECK(cudaEventSynchronize(e1));
