@@ -43,6 +43,24 @@ def reduce_gradients(grad, world):
     return grad
 
 
+# How each refinement statistic combines over ranks that saw different views: refine_norm and max_screen are running
+# maxima (optim.cu:122-124, project.cu:82-83), vis_count and vis_weight running sums (optim.cu:122, raster_bwd.cu:134).
+STATISTIC_REDUCTIONS = {"refine_norm": "max", "max_screen": "max", "vis_count": "sum", "vis_weight": "sum"}
+
+
+def reduce_statistics(stats, world):
+    """All-reduces the per-splat refinement statistics in place so that every rank holds what a single process that
+    rendered all views would hold. `stats` maps the names of STATISTIC_REDUCTIONS to tensors [n]. Call it once before
+    the statistics are read (the refinement pass) and clear them afterwards on every rank: reducing twice without a
+    clear would count the sums twice."""
+    if world > 1:
+        ops = {"max": torch.distributed.ReduceOp.MAX, "sum": torch.distributed.ReduceOp.SUM}
+        for name, how in STATISTIC_REDUCTIONS.items():
+            if name in stats and stats[name] is not None:
+                torch.distributed.all_reduce(stats[name], op=ops[how])
+    return stats
+
+
 class Trainer:
     def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, lr_mean=1.6e-4, sparse=True, noise_weight=0.0,
                  noise_clamp=0.0, ssim_weight=0.2, isect_cap=None, views_in_flight=1, reduce_slices=4):
@@ -178,6 +196,11 @@ class Trainer:
                 api.adam_step(m, op, self.grad, first=a, count=c)
             self._mark("all_reduce+adam")
         return self.ctx.loss_accum
+
+    def reduce_statistics(self):
+        """Makes the refinement statistics of the model global over the ranks (see reduce_statistics above)."""
+        m = self.model
+        reduce_statistics({k: getattr(m, k)[:m.n] for k in STATISTIC_REDUCTIONS}, self.world)
 
     def check_overflow(self):
         """Reads the last view's intersection count back; grows the buffers when it did not fit (the reference does this

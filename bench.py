@@ -358,7 +358,7 @@ def incumbent(scene, cam, host_target, masked):
 
 def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     """Times each stage of a view with CUDA events (on the launching stream), a few views, and derives the roofline
-    object for the dominant kernel. Algorithmic bytes per stage follow the per-unit figures stated in DESIGN.md."""
+    object for the dominant kernel. Algorithmic bytes per stage are the `alg` table below (per-unit figures times the counts V, I, I_b, P of the view)."""
     import torch
     from b2ctrain_b200 import api
     peaks = {}
@@ -417,7 +417,7 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
         per_launch_ms = float(np.mean(scatter_ms))
         bytes_launch = 16 * I          # keys + values read, keys + values written
         note = f"{len(scatter_ms)} launches per view on I = {I} pairs; 16 B per pair per launch"
-        traffic = int(16.7 * I)   # dram read + write per launch: ncu capture at half the splat count, scaled by pairs (profiles/radix_scatter_kernel_tile_sort.md)
+        traffic = int(16.7 * I)   # dram read + write per launch: ncu capture at half the splat count, scaled by pairs
     else:
         stage = {"project_kernel": "project", "raster_fwd_kernel": "raster_fwd", "photometric_kernel": "loss", "raster_bwd_kernel": "raster_bwd",
                  "proj_bwd_kernel": "proj_bwd", "scan_emit_kernel": "bin_sort"}[top]

@@ -14,7 +14,7 @@ import os, sys
 sys.path.insert(0, os.environ["B2K_ROOT"])
 import numpy as np, torch, torch.distributed as dist
 from b2ctrain_b200 import scenes
-from b2ctrain_b200.trainer import partition_views, reduce_gradients, slice_bounds
+from b2ctrain_b200.trainer import partition_views, reduce_gradients, slice_bounds, reduce_statistics
 from oracle import orc
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -36,6 +36,18 @@ z4 = lambda: np.zeros((scene["n"], 4), np.float32)
 state = dict(pos_op=scene["pos_op"].copy(), quat=scene["quat"].copy(), lscale=scene["lscale"].copy(), sh=scene["sh"].copy(), m_pos=z4(), v_pos=z4(), m_q=z4(),
              v_q=z4(), m_ls=z4(), v_ls=z4(), m_sh=np.zeros((scene["n"], 4, 3), np.float32), v_sh=np.zeros(scene["n"], np.float32), last_step=np.zeros(scene["n"], np.uint32))
 orc.adam(state, g, np.any(g != 0, axis=1), dict(t=1, lr_mean=1e-4, sparse=1), 1)
+# refinement statistics: each rank holds maxima / sums over its own views; the reduction makes them global
+rng = np.random.Generator(np.random.PCG64(100 + rank))
+local = {k: torch.from_numpy(rng.random(scene["n"]).astype(np.float32)) for k in ("refine_norm", "max_screen", "vis_count", "vis_weight")}
+both = []
+for r in range(world):   # every rank's arrays, drawn in the same order as `local`
+    g2 = np.random.Generator(np.random.PCG64(100 + r))
+    both.append({k: g2.random(scene["n"]).astype(np.float32) for k in ("refine_norm", "max_screen", "vis_count", "vis_weight")})
+reduce_statistics(local, world)
+for k in ("refine_norm", "max_screen"):
+    assert np.array_equal(local[k].numpy(), np.maximum(both[0][k], both[1][k])), k
+for k in ("vis_count", "vis_weight"):
+    assert np.array_equal(local[k].numpy(), both[0][k] + both[1][k]), k
 np.savez(os.path.join(os.environ["B2K_OUT"], f"rank{rank}.npz"), mine=np.array(mine), g=g, pos=state["pos_op"], sh=state["sh"])
 if rank == 0:
     total = np.zeros_like(acc)
