@@ -46,7 +46,7 @@ class B2kCtx(C.Structure):
                 ("vals_sorted", C.c_void_p), ("isect_cap", C.c_uint64), ("num_isect", C.c_void_p), ("sort_tmp", C.c_void_p),
                 ("sort_tmp_bytes", C.c_uint64), ("tile_ranges", C.c_void_p), ("out_rgba", C.c_void_p), ("out_feat", C.c_void_p),
                 ("out_depth", C.c_void_p), ("last_idx", C.c_void_p), ("v_splat", C.c_void_p), ("vis_flag", C.c_void_p), ("vis_list", C.c_void_p),
-                ("v_out", C.c_void_p), ("loss_accum", C.c_void_p)]
+                ("v_out", C.c_void_p), ("loss_accum", C.c_void_p), ("n_chunks", C.c_int32), ("chunk_words", C.c_void_p)]
 
 
 class B2kRenderOpts(C.Structure):
@@ -79,6 +79,7 @@ SIGNATURES = {
     "b2k_bin_sort_profile": (C.c_int, [_P, C.c_int32, _S, _P]),
     "b2k_static_max_splats": (C.c_uint32, []),
     "b2k_raster_fwd": (C.c_int, [_P, _P, _S]),
+    "b2k_render_chunked": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_sort_tmp_bytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
     "b2k_loss_photometric": (C.c_int, [_P, _P, _S]),
     "b2k_loss_accumulate": (C.c_int, [_P, _S]),
@@ -235,8 +236,12 @@ class RenderCtx:
         self.isect_cap = 0
         self.num_isect = 0
         self.want_depth = False
+        self.n_chunks = 1          # > 1: render_forward composites the view front to back in this many depth chunks
+        self.chunk_words = None
 
-    def setup(self, W, H, n_splats, stream=None, isect_cap=None):
+    def setup(self, W, H, n_splats, stream=None, isect_cap=None, n_chunks=None):
+        if n_chunks is not None:
+            self.n_chunks = max(1, int(n_chunks))
         dev = self.device
         self.W, self.H = int(W), int(H)
         self.tiles_x, self.tiles_y = (self.W + 7) // 8, (self.H + 7) // 8
@@ -256,7 +261,8 @@ class RenderCtx:
             self.vis_list = u32(n)
             self.n_cap = n
         P = self.W * self.H
-        self.tile_ranges = u32(self.n_tiles, 2)
+        self.tile_ranges = u32(self.n_chunks * self.n_tiles, 2)
+        self.chunk_words = u32(32 + self.n_tiles + (self.tiles_x + 1) * (self.tiles_y + 1)) if self.n_chunks > 1 else None
         self.out_rgba, self.out_feat, self.v_out = f32(P, 4), f32(P, 4), f32(P, 4)
         self.out_depth = f32(P) if self.want_depth else None
         self.last_idx = u32(P)
@@ -279,12 +285,13 @@ class RenderCtx:
             setattr(s, k, getattr(self, k))
         for k in ("proj0", "proj1", "proj2", "tile_count", "hit_info", "depth_keys", "depth_keys_sorted", "order_in", "order", "tile_off", "keys",
                   "vals", "keys_sorted", "vals_sorted", "sort_tmp", "tile_ranges", "out_rgba", "out_feat", "out_depth", "last_idx",
-                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum"):
+                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum", "chunk_words"):
             t = getattr(self, k, None)
             setattr(s, k, None if t is None else t.data_ptr())
         s.num_isect = self.d_num_isect.data_ptr()
         s.isect_cap = self.isect_cap
         s.sort_tmp_bytes = self.sort_tmp.numel()
+        s.n_chunks = self.n_chunks
         return s
 
 
@@ -438,9 +445,33 @@ def rasterize_forward(ctx, p, stream=None):
 
 
 def render_forward(ctx, m, p, stream=None, sync=True):
+    """render_forward (src/gpu/render.h:97). A context set up with n_chunks > 1 renders front to back in depth chunks
+    (b2k_render_chunked: same image and gradients, intersections behind saturated pixels never sorted)."""
+    if ctx.n_chunks > 1:
+        return render_chunked(ctx, m, p, stream, sync=sync)
     project_splats(ctx, m, p, stream)
     bin_and_sort(ctx, m, stream, sync=sync)
     rasterize_forward(ctx, p, stream)
+
+
+def render_chunked(ctx, m, p, stream=None, sync=True):
+    """b2k_render_chunked; with sync the slot count is read back and the view redone with larger buffers on overflow."""
+    while True:
+        cs, ms, os_, cam = ctx.struct(), m.struct(), p.struct(), p.camera()
+        _check(lib().b2k_render_chunked(C.byref(ms), C.byref(cam), C.byref(os_), C.byref(cs), _stream(stream)), "render_chunked")
+        if not sync:
+            return None
+        total = C.c_uint32(0)
+        st = lib().b2k_read_num_isect(C.byref(cs), _stream(stream), C.byref(total))
+        ctx.num_isect = int(total.value)
+        if st == B2K_ERR_OVERFLOW:
+            cap = ctx.isect_cap
+            while cap < ctx.num_isect + 32 * ctx.n_chunks:
+                cap *= 2
+            ctx._alloc_isect(cap)
+            continue
+        _check(st, "render_chunked")
+        return ctx.num_isect
 
 
 def photometric_loss(ctx, view, lp, stream=None):

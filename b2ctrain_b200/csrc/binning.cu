@@ -34,16 +34,24 @@ __device__ __forceinline__ uint32_t load_n(const uint32_t* n_ptr, uint32_t n_max
   const uint32_t n = *n_ptr;
   return n < n_max ? n : n_max;
 }
+// A sort may work on a window of its buffers that starts `*off_ptr` elements in (a depth chunk of the view): the
+// window's length is clamped to what is left of the buffers.
+__device__ __forceinline__ uint32_t load_off(const uint32_t* off_ptr) { return off_ptr ? *off_ptr : 0u; }
+__device__ __forceinline__ uint32_t load_n(const uint32_t* n_ptr, uint32_t n_max, uint32_t off) {
+  return load_n(n_ptr, off < n_max ? n_max - off : 0u);
+}
 
 // Pass kernel 1: digit counts of each block's segment. hist is [RADIX][blocks]. Each lane keeps 16 keys in flight
 // (four 128-bit loads) so that a few hundred resident warps cover the HBM latency-bandwidth product.
-__global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ n_ptr, uint32_t n_max,
-                                                                   int shift, uint32_t mask, uint32_t* __restrict__ hist) {
+__global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_t* __restrict__ keys_base, const uint32_t* __restrict__ n_ptr, uint32_t n_max,
+                                                                   int shift, uint32_t mask, uint32_t* __restrict__ hist, const uint32_t* __restrict__ off_ptr) {
   __shared__ uint32_t s_hist[SORT_WARPS][RADIX];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_hist[0][0])[i] = 0;
   __syncthreads();
-  const uint32_t n = load_n(n_ptr, n_max);
+  const uint32_t off = load_off(off_ptr);   // a multiple of 32 elements: 128-bit loads stay aligned
+  const uint32_t* __restrict__ keys = keys_base + off;
+  const uint32_t n = load_n(n_ptr, n_max, off);
   const uint32_t len = seg_len(n, gridDim.x);
   const uint64_t begin64 = (uint64_t)blockIdx.x * len;
   const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
@@ -106,8 +114,14 @@ constexpr int SCAT_WARPS = SCAT_THREADS / 32;
 constexpr size_t SCAT_SMEM = 2 * SORT_TILE * sizeof(uint32_t);
 
 __global__ void __launch_bounds__(SCAT_THREADS, SCAT_THREADS <= 512 ? 2 : 1) radix_scatter_kernel(
-    const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
-    const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask, const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals) {
+    const uint32_t* __restrict__ keys_in_base, const uint32_t* __restrict__ vals_in_base, uint32_t* __restrict__ keys_out_base,
+    uint32_t* __restrict__ vals_out_base, const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask,
+    const uint32_t* __restrict__ hist, const uint32_t* __restrict__ totals, const uint32_t* __restrict__ off_ptr) {
+  const uint32_t off = load_off(off_ptr);
+  const uint32_t* __restrict__ keys_in = keys_in_base + off;
+  const uint32_t* __restrict__ vals_in = vals_in_base + off;
+  uint32_t* __restrict__ keys_out = keys_out_base + off;
+  uint32_t* __restrict__ vals_out = vals_out_base + off;
   __shared__ uint32_t s_cnt[SCAT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
   __shared__ uint32_t s_gbase[RADIX];             // running global slot of the digit for this block
   __shared__ uint32_t s_delta[RADIX];             // global slot = s_delta[digit] + local slot (mod 2^32)
@@ -134,7 +148,7 @@ __global__ void __launch_bounds__(SCAT_THREADS, SCAT_THREADS <= 512 ? 2 : 1) rad
     }
     __syncthreads();
   }
-  const uint32_t n = load_n(n_ptr, n_max);
+  const uint32_t n = load_n(n_ptr, n_max, off);
   const uint32_t len = seg_len(n, gridDim.x);
   const uint64_t begin64 = (uint64_t)blockIdx.x * len;
   const uint32_t begin = begin64 < n ? (uint32_t)begin64 : n;
@@ -366,17 +380,19 @@ __global__ void __launch_bounds__(256) emit_big_kernel(const uint32_t* __restric
   }
 }
 
-__global__ void tile_ranges_kernel(const uint32_t* __restrict__ keys_sorted, const uint32_t* __restrict__ n_ptr, uint32_t n_max, uint32_t n_tiles,
-                                   uint2* __restrict__ ranges) {
-  const uint32_t n = load_n(n_ptr, n_max);
+__global__ void tile_ranges_kernel(const uint32_t* __restrict__ keys_sorted_base, const uint32_t* __restrict__ n_ptr, uint32_t n_max, uint32_t n_tiles,
+                                   uint2* __restrict__ ranges, const uint32_t* __restrict__ off_ptr) {
+  const uint32_t off = load_off(off_ptr);
+  const uint32_t* __restrict__ keys_sorted = keys_sorted_base + off;
+  const uint32_t n = load_n(n_ptr, n_max, off);
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const uint32_t tile = keys_sorted[i];
     const uint32_t prev = i == 0 ? 0xFFFFFFFFu : keys_sorted[i - 1];
     if (i == 0 || tile != prev) {
-      if (tile < n_tiles) ranges[tile].x = i;
-      if (i > 0 && prev < n_tiles) ranges[prev].y = i;
+      if (tile < n_tiles) ranges[tile].x = off + i;
+      if (i > 0 && prev < n_tiles) ranges[prev].y = off + i;
     }
-    if (i == n - 1 && tile < n_tiles) ranges[tile].y = n;
+    if (i == n - 1 && tile < n_tiles) ranges[tile].y = off + n;
   }
 }
 
@@ -404,7 +420,7 @@ void mark(cudaStream_t s) { if (g_marks.armed && g_marks.n < 32) cudaEventRecord
 // clamped to n_max. Buffers (k0, v0) hold the input; the result lands in (k0, v0) when the number of passes is even
 // and in (k1, v1) when it is odd.
 int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uint32_t* n_ptr, uint32_t n_max, int bits, const SortScratch& sc,
-               int blocks, cudaStream_t s) {
+               int blocks, cudaStream_t s, const uint32_t* off_ptr = nullptr) {
   const int passes = (bits + 7) / 8;
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -416,15 +432,272 @@ int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uin
     const int shift = p * 8;
     const int pb = bits - shift < 8 ? bits - shift : 8;
     const uint32_t mask = (1u << pb) - 1u;
-    radix_count_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist);
+    radix_count_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist, off_ptr);
     radix_rows_kernel<<<RADIX, 1024, 0, s>>>(sc.hist, blocks, sc.totals);
     mark(s);
-    radix_scatter_kernel<<<blocks, SCAT_THREADS, SCAT_SMEM, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals);
+    radix_scatter_kernel<<<blocks, SCAT_THREADS, SCAT_SMEM, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals, off_ptr);
     mark(s);
     uint32_t* t = k0; k0 = k1; k1 = t;
     t = v0; v0 = v1; v1 = t;
   }
   return check_launch();
+}
+
+
+// ---- front-to-back rendering in depth chunks ------------------------------------------------------------------------
+// The view's splats are taken in a few chunks of increasing depth rank. A chunk is binned (its intersections emitted,
+// sorted by tile, ranged) and composited before the next one is touched, and a tile whose pixels have all reached the
+// transmittance cutoff emits nothing from then on: in a dense scene most intersections lie behind saturated pixels and
+// are never composited, so they need not be sorted either. Chunk c covers the ranks [V b(c-1), V b(c)) of the V
+// splats that hit a tile, with b = 1/2^(C-1), ..., 1/4, 1/2, 1 (small chunks first: the nearest splats decide most
+// pixels). Every chunk's sorted pairs occupy their own window of the key / value buffers, and a tile has one range per
+// chunk. The words that chain the chunks live on the device:
+//   words[0] = V, words[1 + c] = first slot of chunk c's window, words[16 + c] = pairs of chunk c.
+constexpr int MAX_CHUNKS = 8;
+constexpr int CW_V = 0, CW_BASE = 1, CW_COUNT = 16, CW_WORDS = 32;   // the tile-alive flags follow the header
+
+__device__ __forceinline__ void chunk_ranks(const uint32_t* words, int lo_num, int hi_num, uint32_t& r0, uint32_t& r1) {
+  const uint64_t V = words[CW_V];
+  r0 = (uint32_t)((V * (uint64_t)lo_num) >> 8);
+  r1 = (uint32_t)((V * (uint64_t)hi_num) >> 8);
+}
+
+// V = number of depth-sorted keys that are not the culled marker (they sort last).
+__global__ void chunk_prepare_kernel(const uint32_t* __restrict__ keys_sorted, int n, uint32_t* __restrict__ words) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int lo = 0, hi = n;
+  while (lo < hi) { const int mid = (lo + hi) >> 1; if (keys_sorted[mid] != 0xFFFFFFFFu) lo = mid + 1; else hi = mid; }
+  words[CW_V] = (uint32_t)lo;
+  words[CW_BASE] = 0u;
+}
+
+// Summed-area table of the tile-alive flags, (tiles_y + 1) x (tiles_x + 1) words with a zero first row and column:
+// "is any tile of this box still alive" becomes four loads, which lets the count and emit kernels drop a splat whose
+// whole tile box has died without walking its hit mask. One CTA: rows are scanned by warps, then columns by threads.
+__global__ void __launch_bounds__(1024) alive_sat_kernel(const uint32_t* __restrict__ alive, int tiles_x, int tiles_y, uint32_t* __restrict__ sat) {
+  const int SX = tiles_x + 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int x = threadIdx.x; x < SX; x += blockDim.x) sat[x] = 0u;
+  for (int y = warp; y < tiles_y; y += (int)(blockDim.x >> 5)) {
+    uint32_t carry = 0;
+    if (lane == 0) sat[(size_t)(y + 1) * SX] = 0u;
+    for (int x0 = 0; x0 < tiles_x; x0 += 32) {
+      const int x = x0 + lane;
+      uint32_t v = x < tiles_x ? (alive[(size_t)y * tiles_x + x] != 0u ? 1u : 0u) : 0u;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+      if (x < tiles_x) sat[(size_t)(y + 1) * SX + x + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  for (int x = threadIdx.x + 1; x < SX; x += blockDim.x) {
+    uint32_t run = 0;
+    for (int y = 1; y <= tiles_y; y++) { run += sat[(size_t)y * SX + x]; sat[(size_t)y * SX + x] = run; }
+  }
+}
+
+__device__ __forceinline__ uint32_t box_alive(const uint32_t* __restrict__ sat, int SX, int x0, int y0, int x1, int y1) {
+  return sat[(size_t)y1 * SX + x1] - sat[(size_t)y0 * SX + x1] - sat[(size_t)y1 * SX + x0] + sat[(size_t)y0 * SX + x0];
+}
+
+// Tiles of a masked splat that are still alive (alive == nullptr: all of them).
+__device__ __forceinline__ uint32_t alive_hits(const uint4 hi, uint32_t cnt, const uint32_t* __restrict__ alive, const uint32_t* __restrict__ sat,
+                                               int tiles_x) {
+  if (!alive) return cnt;
+  unsigned long long bits = ((unsigned long long)hi.y << 32) | hi.x;
+  if (bits == 0ull) return 0u;
+  const uint32_t bw = hi.z >> 24, min_x = hi.z & 0xFFFu, min_y = (hi.z >> 12) & 0xFFFu;
+  const uint32_t inv_bw = bw ? (65536u + bw - 1u) / bw : 0u;
+  const uint32_t bh = (((63u - (uint32_t)__clzll((long long)bits)) * inv_bw) >> 16) + 1u;   // rows up to the highest hit
+  if (box_alive(sat, tiles_x + 1, (int)min_x, (int)min_y, (int)(min_x + bw), (int)(min_y + bh)) == 0u) return 0u;
+  uint32_t f = 0;
+  while (bits != 0ull) {
+    const uint32_t bit = (uint32_t)__ffsll((long long)bits) - 1u;
+    bits &= bits - 1ull;
+    const uint32_t row = (bit * inv_bw) >> 16, col = bit - row * bw;
+    f += alive[(min_y + row) * (uint32_t)tiles_x + min_x + col] != 0u;
+  }
+  return f;
+}
+
+// Per rank of the chunk: how many pairs the splat will emit. Big-box splats are listed (rank, index) for the
+// warp-per-splat kernels; with every tile alive their count is the projection's.
+__global__ void __launch_bounds__(256) chunk_count_kernel(const uint32_t* __restrict__ words, int lo_num, int hi_num, const uint32_t* __restrict__ order,
+                                                          const uint32_t* __restrict__ tile_count, const uint4* __restrict__ hit_info,
+                                                          const uint32_t* __restrict__ alive, const uint32_t* __restrict__ sat, int tiles_x,
+                                                          uint32_t* __restrict__ fcount,
+                                                          uint32_t* __restrict__ big_list, uint32_t* __restrict__ big_count) {
+  uint32_t r0, r1;
+  chunk_ranks(words, lo_num, hi_num, r0, r1);
+  for (uint32_t r = r0 + blockIdx.x * blockDim.x + threadIdx.x; r < r1; r += gridDim.x * blockDim.x) {
+    const uint32_t i = order[r];
+    const uint32_t cnt = tile_count[i];
+    uint32_t f = 0;
+    if (cnt) {
+      const uint4 hi = hit_info[i];
+      if (hi.z == 0xFFFFFFFFu) {
+        const uint32_t e = atomicAdd(big_count, 1u);
+        big_list[2 * e] = r; big_list[2 * e + 1] = i;
+        f = cnt;                       // replaced by chunk_count_big_kernel when tiles have died
+      } else {
+        f = alive_hits(hi, cnt, alive, sat, tiles_x);
+      }
+    }
+    fcount[r] = f;
+  }
+}
+
+__global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ big_count,
+                                                              const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H, int tiles_x,
+                                                              int tiles_y, const uint32_t* __restrict__ alive, const uint32_t* __restrict__ sat,
+                                                              uint32_t* __restrict__ fcount) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = *big_count;
+  for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
+    const uint32_t r = big_list[2 * e], i = big_list[2 * e + 1];
+    const float4 a = proj0[i], b = proj1[i];
+    const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
+    TileBox bb;
+    uint32_t hits = 0;
+    if (tile_box(rec, W, H, tiles_x, tiles_y, bb) && box_alive(sat, tiles_x + 1, bb.min_x, bb.min_y, bb.max_x, bb.max_y) != 0u) {
+      const int bw = bb.max_x - bb.min_x, area = bw * (bb.max_y - bb.min_y);
+      for (int t0 = 0; t0 < area; t0 += 32) {
+        const int t = t0 + lane;
+        const int tx = bb.min_x + t % bw, ty = bb.min_y + t / bw;
+        const bool hit = t < area && alive[ty * tiles_x + tx] != 0u && tile_hit(tx, ty, rec);
+        hits += __popc(__ballot_sync(0xffffffffu, hit));
+      }
+    }
+    if (lane == 0) fcount[r] = hits;
+  }
+}
+
+__global__ void __launch_bounds__(EMIT_THREADS) chunk_sums_kernel(const uint32_t* __restrict__ words, int lo_num, int hi_num,
+                                                                  const uint32_t* __restrict__ fcount, uint32_t* __restrict__ block_sums) {
+  __shared__ uint32_t s_red[EMIT_THREADS / 32];
+  uint32_t r0, r1;
+  chunk_ranks(words, lo_num, hi_num, r0, r1);
+  const uint32_t len = emit_seg_len(r1 - r0, gridDim.x);
+  const uint64_t begin = (uint64_t)r0 + (uint64_t)blockIdx.x * len;
+  uint32_t acc = 0;
+  for (uint64_t r = begin + threadIdx.x; r < begin + len && r < (uint64_t)r1; r += EMIT_THREADS) acc += fcount[r];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) { uint32_t t = 0; for (int w = 0; w < EMIT_THREADS / 32; w++) t += s_red[w]; block_sums[blockIdx.x] = t; }
+}
+
+// scan_emit_kernel for one chunk: counts come from fcount, dead tiles are skipped, slots start at the chunk's window.
+// The last block records the chunk's pair count, the next window's first slot (rounded up to 32 so that the sort's
+// vector loads stay aligned) and the running total of the view.
+__global__ void __launch_bounds__(EMIT_THREADS) chunk_emit_kernel(
+    uint32_t* __restrict__ words, int chunk, int lo_num, int hi_num, const uint32_t* __restrict__ order, const uint32_t* __restrict__ fcount,
+    const uint32_t* __restrict__ block_sums, const uint4* __restrict__ hit_info, const uint32_t* __restrict__ alive, int tiles_x, uint32_t cap,
+    uint32_t* __restrict__ big_start, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals, uint32_t* __restrict__ num_isect) {
+  __shared__ uint32_t s_warp[EMIT_THREADS / 32];
+  __shared__ uint32_t s_base;
+  extern __shared__ uint32_t s_win[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t* wk = s_win + (size_t)warp * EMIT_WINDOW * 2;
+  uint32_t* wv = wk + EMIT_WINDOW;
+  const uint32_t window = words[CW_BASE + chunk];
+  {
+    uint32_t acc = 0;
+    for (int b = tid; b < (int)blockIdx.x; b += EMIT_THREADS) acc += block_sums[b];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_warp[warp] = acc;
+    __syncthreads();
+    if (tid == 0) { uint32_t t = 0; for (int w = 0; w < EMIT_THREADS / 32; w++) t += s_warp[w]; s_base = t; }
+    __syncthreads();
+  }
+  uint32_t running = window + s_base;
+  uint32_t r0, r1;
+  chunk_ranks(words, lo_num, hi_num, r0, r1);
+  const uint32_t len = emit_seg_len(r1 - r0, gridDim.x);
+  const uint64_t begin = (uint64_t)r0 + (uint64_t)blockIdx.x * len;
+  const uint64_t seg_end = (begin + len) < (uint64_t)r1 ? begin + len : (uint64_t)r1;
+  for (uint64_t q0 = begin; q0 < seg_end; q0 += EMIT_THREADS) {
+    const uint64_t r = q0 + tid;
+    const bool valid = r < seg_end;
+    uint32_t i = 0, cnt = 0;
+    uint4 hi = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) { cnt = fcount[r]; if (cnt) { i = order[r]; hi = hit_info[i]; } }
+    uint32_t incl = cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    __syncthreads();   // s_warp reuse
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t pre = 0, tile_total = 0;
+#pragma unroll
+    for (int w = 0; w < EMIT_THREADS / 32; w++) { const uint32_t v = s_warp[w]; if (w < warp) pre += v; tile_total += v; }
+    const uint32_t end = running + pre + incl;
+    const uint32_t start = end - cnt;
+    const bool big = cnt != 0 && hi.z == 0xFFFFFFFFu;
+    if (big) big_start[r] = start;
+    unsigned long long bits = big ? 0ull : ((unsigned long long)hi.y << 32) | hi.x;
+    const uint32_t bw = hi.z >> 24, min_x = hi.z & 0xFFFu, min_y = (hi.z >> 12) & 0xFFFu;
+    const uint32_t inv_bw = bw ? (65536u + bw - 1u) / bw : 0u;
+    uint32_t cur = start;
+    const uint32_t wstart = __shfl_sync(0xffffffffu, start, 0), wend = __shfl_sync(0xffffffffu, end, 31);
+    for (uint32_t w0 = wstart; w0 < wend; w0 += EMIT_WINDOW) {
+      const uint32_t w1 = wend - w0 < (uint32_t)EMIT_WINDOW ? wend : w0 + EMIT_WINDOW;
+      while (bits != 0ull && cur < w1) {
+        const uint32_t bit = (uint32_t)__ffsll((long long)bits) - 1u;
+        bits &= bits - 1ull;
+        const uint32_t row = (bit * inv_bw) >> 16, col = bit - row * bw;
+        const uint32_t tile = (min_y + row) * (uint32_t)tiles_x + min_x + col;
+        if (alive && alive[tile] == 0u) continue;
+        wk[cur - w0] = tile;
+        wv[cur - w0] = i;
+        cur++;
+      }
+      __syncwarp();
+      for (uint32_t s = w0 + lane; s < w1; s += 32)
+        if (s < cap) { keys[s] = wk[s - w0]; vals[s] = wv[s - w0]; }
+      __syncwarp();
+    }
+    running += tile_total;
+  }
+  if (blockIdx.x == gridDim.x - 1 && tid == 0) {
+    const uint32_t pairs = running - window;
+    words[CW_COUNT + chunk] = pairs;
+    words[CW_BASE + chunk + 1] = (running + 31u) & ~31u;
+    *num_isect = running;
+  }
+}
+
+__global__ void __launch_bounds__(256) chunk_emit_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ big_count,
+                                                             const uint32_t* __restrict__ fcount, const uint32_t* __restrict__ big_start,
+                                                             const float4* __restrict__ proj0,
+                                                             const float4* __restrict__ proj1, int W, int H, int tiles_x, int tiles_y,
+                                                             const uint32_t* __restrict__ alive, uint32_t cap, uint32_t* __restrict__ keys,
+                                                             uint32_t* __restrict__ vals) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = *big_count;
+  for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
+    const uint32_t r = big_list[2 * e], i = big_list[2 * e + 1];
+    if (fcount[r] == 0u) continue;   // every tile of the splat has died
+    uint32_t at = big_start[r];
+    const float4 a = proj0[i], b = proj1[i];
+    const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
+    TileBox bb;
+    if (!tile_box(rec, W, H, tiles_x, tiles_y, bb)) continue;
+    const int bw = bb.max_x - bb.min_x, area = bw * (bb.max_y - bb.min_y);
+    for (int t0 = 0; t0 < area; t0 += 32) {
+      const int t = t0 + lane;
+      const int tx = bb.min_x + t % bw, ty = bb.min_y + t / bw;
+      const bool hit = t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec);
+      const uint32_t m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const uint32_t s = at + __popc(m & ((1u << lane) - 1u));
+        if (s < cap) { keys[s] = (uint32_t)(ty * tiles_x + tx); vals[s] = i; }
+      }
+      at += __popc(m);
+    }
+  }
 }
 
 }  // namespace
@@ -487,9 +760,82 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
   // 4. Stable sort by tile id: depth order survives inside each tile.
   st = radix_sort(ek, ev, ok, ov, c->num_isect, (uint32_t)c->isect_cap, c->tile_bits, sc, blocks, s);
   if (st) return st;
-  tile_ranges_kernel<<<sm_count() * 8, 256, 0, s>>>(c->keys_sorted, c->num_isect, (uint32_t)c->isect_cap, (uint32_t)c->n_tiles, (uint2*)c->tile_ranges);
+  tile_ranges_kernel<<<sm_count() * 8, 256, 0, s>>>(c->keys_sorted, c->num_isect, (uint32_t)c->isect_cap, (uint32_t)c->n_tiles, (uint2*)c->tile_ranges, nullptr);
   mark(s);
   return check_launch();
+}
+
+extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* o, const B2kCtx* c, b2k_stream_t stream) {
+  B2K_REQUIRE(m && cam && o && c);
+  const int C = c->n_chunks;
+  B2K_REQUIRE(C >= 2 && C <= MAX_CHUNKS && c->chunk_words && c->last_idx && c->tile_off && c->depth_keys);
+  B2K_REQUIRE(c->tile_ranges && c->num_isect && c->n_tiles == c->tiles_x * c->tiles_y && c->tile_bits >= 1 && c->tile_bits <= 24);
+  B2K_REQUIRE(c->out_rgba && c->out_feat && c->keys && c->vals && c->keys_sorted && c->vals_sorted && c->sort_tmp);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int n = m->n;
+  int st = b2k_project(m, cam, o, c, stream);
+  if (st) return st;
+  B2K_CUDA(cudaMemsetAsync(c->tile_ranges, 0, sizeof(uint32_t) * 2 * (size_t)c->n_tiles * C, s));
+  if (n == 0) {
+    B2K_CUDA(cudaMemsetAsync(c->num_isect, 0, sizeof(uint32_t), s));
+    for (int ch = 0; ch < C; ch++) { st = launch_raster_fwd(c, o, ch, C, c->chunk_words + CW_WORDS, s); if (st) return st; }
+    return B2K_OK;
+  }
+  if (c->n_cap < n) return B2K_ERR_CAPACITY;
+  if (c->sort_tmp_bytes < b2k_sort_tmp_bytes(c->n_cap, c->isect_cap) || c->isect_cap == 0 || c->isect_cap > 0x7FFFFFF0ull) return B2K_ERR_CAPACITY;
+  const int blocks = sort_blocks();
+  const SortScratch sc = carve(c, blocks);
+  uint32_t* words = c->chunk_words;
+  uint32_t* alive = words + CW_WORDS;
+  uint32_t* sat = alive + c->n_tiles;
+  // Splats by depth, exactly as in b2k_bin_sort.
+  set_word_kernel<<<1, 1, 0, s>>>(sc.n_word, (uint32_t)n);
+  st = radix_sort(c->depth_keys_sorted, c->order, c->depth_keys, c->order_in, sc.n_word, (uint32_t)n, 32, sc, blocks, s);
+  if (st) return st;
+  chunk_prepare_kernel<<<1, 32, 0, s>>>(c->depth_keys_sorted, n, words);
+  const int tile_passes = (c->tile_bits + 7) / 8;
+  uint32_t* ek = (tile_passes % 2 == 0) ? c->keys_sorted : c->keys;
+  uint32_t* ev = (tile_passes % 2 == 0) ? c->vals_sorted : c->vals;
+  uint32_t* ok = (tile_passes % 2 == 0) ? c->keys : c->keys_sorted;
+  uint32_t* ov = (tile_passes % 2 == 0) ? c->vals : c->vals_sorted;
+  uint32_t* fcount = c->depth_keys;          // scratch pair of the depth sort: free from here on
+  uint32_t* big_start = c->tile_off;         // first slot of each listed big-box splat, by rank
+  uint32_t* big_list = big_emit_ptr(c);      // [n_cap][2] (rank, splat)
+  uint32_t* big_count = big_count_ptr(c) + 1;
+  {
+    static bool emit_attr[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !emit_attr[dev]) {
+      B2K_CUDA(cudaFuncSetAttribute(chunk_emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EMIT_SMEM));
+      emit_attr[dev] = true;
+    }
+  }
+  const int emit_blocks = sm_count() * 4 > 1024 ? 1024 : sm_count() * 4;
+  for (int ch = 0; ch < C; ch++) {
+    const int lo = ch == 0 ? 0 : 256 >> (C - ch), hi = 256 >> (C - 1 - ch);
+    const uint32_t* live = ch == 0 ? nullptr : alive;   // the first chunk meets only live tiles
+    B2K_CUDA(cudaMemsetAsync(big_count, 0, sizeof(uint32_t), s));
+    if (live) alive_sat_kernel<<<1, 1024, 0, s>>>(live, c->tiles_x, c->tiles_y, sat);
+    chunk_count_kernel<<<sm_count() * 8, 256, 0, s>>>(words, lo, hi, c->order, c->tile_count, (const uint4*)c->hit_info, live, sat, c->tiles_x, fcount,
+                                                      big_list, big_count);
+    if (live)
+      chunk_count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
+                                                            c->tiles_x, c->tiles_y, live, sat, fcount);
+    chunk_sums_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(words, lo, hi, fcount, sc.block_sums);
+    chunk_emit_kernel<<<emit_blocks, EMIT_THREADS, EMIT_SMEM, s>>>(words, ch, lo, hi, c->order, fcount, sc.block_sums, (const uint4*)c->hit_info, live,
+                                                                   c->tiles_x, (uint32_t)c->isect_cap, big_start, ek, ev, c->num_isect);
+    chunk_emit_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, fcount, big_start, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
+                                                         c->tiles_x, c->tiles_y, live, (uint32_t)c->isect_cap, ek, ev);
+    st = check_launch();
+    if (st) return st;
+    st = radix_sort(ek, ev, ok, ov, words + CW_COUNT + ch, (uint32_t)c->isect_cap, c->tile_bits, sc, blocks, s, words + CW_BASE + ch);
+    if (st) return st;
+    tile_ranges_kernel<<<sm_count() * 8, 256, 0, s>>>(c->keys_sorted, words + CW_COUNT + ch, (uint32_t)c->isect_cap, (uint32_t)c->n_tiles,
+                                                      (uint2*)c->tile_ranges + (size_t)ch * c->n_tiles, words + CW_BASE + ch);
+    st = launch_raster_fwd(c, o, ch, C, alive, s);
+    if (st) return st;
+  }
+  return B2K_OK;
 }
 
 extern "C" int b2k_bin_sort_profile(const B2kCtx* c, int32_t n, b2k_stream_t stream, float* ms) {

@@ -19,6 +19,8 @@ constexpr int NUM_SMS_HINT = 148;       // B200; grids of persistent kernels are
 extern int g_last_cuda_error;
 int check_launch();                     // cudaGetLastError -> status
 int sm_count();
+// One depth chunk of a chunked view, or the whole view when n_chunks <= 1 (raster_fwd.cu).
+int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_chunks, uint32_t* alive, cudaStream_t s);
 
 #define B2K_REQUIRE(cond) do { if (!(cond)) return B2K_ERR_ARG; } while (0)
 #define B2K_CUDA(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) { b2k::g_last_cuda_error = (int)e_; return B2K_ERR_CUDA; } } while (0)

@@ -60,21 +60,26 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, const float4* __restrict__ out_rgba, const float4* __restrict__ out_feat, const uint32_t* __restrict__ last_idx,
     const float4* __restrict__ v_out, int W, int H, int tiles_x, int n_tiles, float3 bg, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
-    float* __restrict__ vis_weight) {
+    float* __restrict__ vis_weight, int n_chunks) {
   __shared__ Staged s_frag[BWD_WARPS][BWD_BATCH];
   __shared__ uint32_t s_gid[BWD_WARPS][BWD_BATCH];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x * BWD_WARPS + warp;
   if (tile >= n_tiles) return;
-  const uint2 range = tile_ranges[tile];
-  if (range.y <= range.x) return;
+  // A view composited in depth chunks has one range per chunk and tile ([chunk][tile]); the replay walks the chunks
+  // from the farthest to the nearest, the pixel state running through.
+  {
+    bool any = false;
+    for (int ch = 0; ch < n_chunks; ch++) { const uint2 rg = tile_ranges[(size_t)ch * n_tiles + tile]; any = any || rg.y > rg.x; }
+    if (!any) return;
+  }
   const int tx = tile % tiles_x, ty = tile / tiles_x;
   const int px0 = tx * RT_W + (lane & 3) * 2, py = ty * RT_W + (lane >> 2);   // this lane's pixel pair (px0, px0 + 1) on row py
 
   PairState st;
   {
     float T[2] = {0.f, 0.f}, vr[2] = {0.f, 0.f}, vg[2] = {0.f, 0.f}, vb[2] = {0.f, 0.f}, vow[2] = {0.f, 0.f}, ifa[2] = {0.f, 0.f};
-    uint32_t last[2] = {range.x, range.x};
+    uint32_t last[2] = {0u, 0u};   // outside the image: sees no fragment
 #pragma unroll
     for (int p = 0; p < 2; p++) {
       const int px = px0 + p;
@@ -101,6 +106,8 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
   float ablate_sink = 0.f;
 #endif
 
+  for (int ch = n_chunks - 1; ch >= 0; ch--) {
+  const uint2 range = tile_ranges[(size_t)ch * n_tiles + tile];
   for (uint32_t batch_end = range.y; batch_end > range.x;) {
     const uint32_t remaining = batch_end - range.x;
     const uint32_t count = remaining < (uint32_t)BWD_BATCH ? remaining : (uint32_t)BWD_BATCH;
@@ -177,6 +184,7 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     }
     batch_end = batch_start;
   }
+  }
 #ifdef B2K_BWD_ABLATE_REDUCTION
   if (ablate_sink == 123456.789f) v_splat[0] = ablate_sink;   // keeps the replay alive
 #endif
@@ -195,6 +203,6 @@ extern "C" int b2k_raster_bwd(const B2kCtx* c, const B2kModel* m, const B2kRende
   raster_bwd_kernel<<<div_up(c->n_tiles, BWD_WARPS), BWD_WARPS * 32, 0, (cudaStream_t)stream>>>(
       (const uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, (const float4*)c->proj1, (const float4*)c->proj2,
       (const float4*)c->out_rgba, (const float4*)c->out_feat, c->last_idx, (const float4*)c->v_out, c->W, c->H, c->tiles_x, c->n_tiles, bg,
-      c->v_splat, c->vis_flag, m->vis_weight);
+      c->v_splat, c->vis_flag, m->vis_weight, c->n_chunks > 1 ? c->n_chunks : 1);
   return check_launch();
 }

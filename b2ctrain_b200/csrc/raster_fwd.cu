@@ -13,11 +13,18 @@ namespace {
 constexpr int FWD_WARPS = 4;
 constexpr int FWD_BATCH = 32;
 
-template <bool BWD, bool DEPTH>
+// CHUNKED: the view is composited in depth chunks (chunk `chunk` of `n_chunks`, one launch each, nearest first). Between
+// launches a pixel's state lives in the output buffers: colour sums in out_rgba.xyz, transmittance in out_feat.w, the
+// depth sum in out_depth, and last_idx with bit 31 set once the pixel has reached the cutoff. The last chunk turns the
+// state into the finished pixel. alive[tile] tells the binning of the next chunk whether any pixel of the tile can
+// still take a fragment.
+constexpr uint32_t DONE_BIT = 0x80000000u;
+
+template <bool BWD, bool DEPTH, bool CHUNKED>
 __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, int W, int H, int tiles_x, int n_tiles, float3 bg, float4* __restrict__ out_rgba, float4* __restrict__ out_feat,
-    float* __restrict__ out_depth, uint32_t* __restrict__ last_idx) {
+    float* __restrict__ out_depth, uint32_t* __restrict__ last_idx, int chunk, int n_chunks, uint32_t* __restrict__ alive) {
   __shared__ float4 s0[FWD_WARPS][FWD_BATCH], s1[FWD_WARPS][FWD_BATCH], s2[FWD_WARPS][FWD_BATCH];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x * FWD_WARPS + warp;
@@ -27,9 +34,26 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
   const bool in0 = px0 < W && py < H, in1 = px0 + 1 < W && py < H;
   const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
   const uint2 range = tile_ranges[tile];
+  const bool first = !CHUNKED || chunk == 0, final = !CHUNKED || chunk == n_chunks - 1;
+  if (CHUNKED && !first && !final && range.y <= range.x) return;   // nothing of this chunk lands here: state and flag stay
   float T[2] = {1.f, 1.f}, r[2] = {0.f, 0.f}, g[2] = {0.f, 0.f}, b[2] = {0.f, 0.f}, zs[2] = {0.f, 0.f};
   bool done[2] = {!in0, !in1};
   uint32_t last[2] = {range.x, range.x};
+  if (CHUNKED && !first) {
+#pragma unroll
+    for (int p = 0; p < 2; p++) {
+      if (p == 0 ? in0 : in1) {
+        const int pix = py * W + px0 + p;
+        const float4 acc = out_rgba[pix];
+        r[p] = acc.x; g[p] = acc.y; b[p] = acc.z;
+        T[p] = out_feat[pix].w;
+        if constexpr (DEPTH) zs[p] = out_depth[pix];
+        const uint32_t l = last_idx[pix];
+        done[p] = (l & DONE_BIT) != 0u;
+        last[p] = l & ~DONE_BIT;
+      }
+    }
+  }
   for (uint32_t start = range.x; start < range.y; start += FWD_BATCH) {
     if (__all_sync(0xffffffffu, done[0] && done[1])) break;
     const uint32_t remaining = min((uint32_t)FWD_BATCH, range.y - start);
@@ -70,17 +94,30 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
   for (int p = 0; p < 2; p++) {
     if (p == 0 ? in0 : in1) {
       const int pix = py * W + px0 + p;
-      out_rgba[pix] = make_float4(r[p] + T[p] * bg.x, g[p] + T[p] * bg.y, b[p] + T[p] * bg.z, 1.f - T[p]);
-      out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
-      if constexpr (DEPTH) out_depth[pix] = (1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY;
-      if constexpr (BWD) last_idx[pix] = last[p];
+      if (final) {
+        out_rgba[pix] = make_float4(r[p] + T[p] * bg.x, g[p] + T[p] * bg.y, b[p] + T[p] * bg.z, 1.f - T[p]);
+        out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
+        if constexpr (DEPTH) out_depth[pix] = (1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY;
+        if constexpr (BWD || CHUNKED) last_idx[pix] = last[p];
+      } else {
+        out_rgba[pix] = make_float4(r[p], g[p], b[p], 0.f);
+        out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
+        if constexpr (DEPTH) out_depth[pix] = zs[p];
+        last_idx[pix] = last[p] | (done[p] ? DONE_BIT : 0u);
+      }
     }
   }
+  if (CHUNKED && !final) {
+    const bool open = __any_sync(0xffffffffu, !done[0] || !done[1]);
+    if (lane == 0) alive[tile] = open ? 1u : 0u;
+  }
   if constexpr (BWD) {
+    // The backward never needs to look past the last fragment any pixel used. (A pixel whose last fragment lies in an
+    // earlier chunk contributes this chunk's start: an empty range.)
     uint32_t m = max(last[0], last[1]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) tile_ranges[tile].y = m;   // the backward never needs to look past the last fragment any pixel used
+    if (lane == 0) tile_ranges[tile].y = CHUNKED ? min(max(m, range.x), range.y) : m;
   }
 }
 
@@ -89,16 +126,29 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
 
 using namespace b2k;
 
+namespace b2k {
+// One chunk of a chunked view (n_chunks > 1), or the whole view (n_chunks <= 1).
+int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_chunks, uint32_t* alive, cudaStream_t s) {
+  const float3 bg = make_float3(o->bg[0], o->bg[1], o->bg[2]);
+  uint2* ranges = (uint2*)c->tile_ranges + (n_chunks > 1 ? (size_t)chunk * c->n_tiles : 0);
+#define L(B, D, C) raster_fwd_kernel<B, D, C><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>(ranges, c->vals_sorted, (const float4*)c->proj0, \
+    (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, c->n_tiles, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx, \
+    chunk, n_chunks, alive)
+  if (n_chunks > 1) {
+    if (o->bwd_info) { if (c->out_depth) L(true, true, true); else L(true, false, true); }
+    else { if (c->out_depth) L(false, true, true); else L(false, false, true); }
+  } else {
+    if (o->bwd_info) { if (c->out_depth) L(true, true, false); else L(true, false, false); }
+    else { if (c->out_depth) L(false, true, false); else L(false, false, false); }
+  }
+#undef L
+  return check_launch();
+}
+}  // namespace b2k
+
 extern "C" int b2k_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, b2k_stream_t stream) {
   B2K_REQUIRE(c && o && c->tile_ranges && c->vals_sorted && c->proj0 && c->proj1 && c->proj2 && c->out_rgba && c->out_feat);
   B2K_REQUIRE(!o->bwd_info || c->last_idx);
   B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y);
-  cudaStream_t s = (cudaStream_t)stream;
-  const float3 bg = make_float3(o->bg[0], o->bg[1], o->bg[2]);
-#define L(B, D) raster_fwd_kernel<B, D><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>((uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, \
-    (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, c->n_tiles, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx)
-  if (o->bwd_info) { if (c->out_depth) L(true, true); else L(true, false); }
-  else { if (c->out_depth) L(false, true); else L(false, false); }
-#undef L
-  return check_launch();
+  return launch_raster_fwd(c, o, 0, 1, nullptr, (cudaStream_t)stream);
 }

@@ -63,7 +63,7 @@ def reduce_statistics(stats, world):
 
 class Trainer:
     def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, lr_mean=1.6e-4, sparse=True, noise_weight=0.0,
-                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None, views_in_flight=1, reduce_slices=4):
+                 noise_clamp=0.0, ssim_weight=0.2, isect_cap=None, views_in_flight=1, reduce_slices=4, render_chunks=1):
         self.device = torch.device(device)
         self.rank, self.world = rank, world
         self.model = api.Model(device).upload(cloud)
@@ -74,7 +74,7 @@ class Trainer:
         self.reduce_slices = int(reduce_slices)
         self.ctxs = [api.RenderCtx(device) for _ in range(self.lanes)]
         for c in self.ctxs:
-            c.setup(W, H, self.model.cap, isect_cap=isect_cap)
+            c.setup(W, H, self.model.cap, isect_cap=isect_cap, n_chunks=render_chunks)   # > 1: front-to-back depth chunks
         self.ctx = self.ctxs[0]
         self.streams = [torch.cuda.Stream(device=self.device) for _ in range(self.lanes)] if self.lanes > 1 else [None]
         self.W, self.H = W, H
@@ -221,13 +221,13 @@ class Trainer:
 class Renderer:
     """Forward-only rendering of cameras split round-robin over ranks; outputs stay on the producing GPU."""
 
-    def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, want_depth=True, isect_cap=None):
+    def __init__(self, cloud, W, H, device="cuda:0", rank=0, world=1, want_depth=True, isect_cap=None, render_chunks=1):
         self.device = torch.device(device)
         self.rank, self.world = rank, world
         self.model = api.Model(device).upload(cloud)
         self.ctx = api.RenderCtx(device)
         self.ctx.want_depth = want_depth
-        self.ctx.setup(W, H, self.model.cap, isect_cap=isect_cap)
+        self.ctx.setup(W, H, self.model.cap, isect_cap=isect_cap, n_chunks=render_chunks)
 
     def render(self, cam, bg=(0.0, 0.0, 0.0), sync=False):
         rp = api.RenderParams(cam, bg=bg, sh_degree=self.model.degree, bwd_info=False)

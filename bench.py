@@ -38,6 +38,7 @@ def parse():
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
     ap.add_argument("--views-in-flight", type=int, default=4, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--reduce-slices", type=int, default=4, help="slices of the gradient all-reduce pipelined with the Adam update (N > 1)")
+    ap.add_argument("--chunks", type=int, default=1, help="depth chunks of the front-to-back renderer (1 = bin the whole view first, as the reference does)")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
 
@@ -235,7 +236,8 @@ def presize(tr_or_r, cams, mine, targets, is_train):
             ctx._alloc_isect(cap)
         tc = ctx.tile_count[: m.n]
         ranges = ctx.tile_ranges.view(-1, 2)
-        stats.append(dict(V=int((tc != 0).sum().item()), I=total, I_b=int((ranges[:, 1] - ranges[:, 0]).sum().item())))
+        stats.append(dict(V=int((tc != 0).sum().item()), I=int(tc.to(torch.int64).sum().item()), I_sorted=total,
+                          I_b=int((ranges[:, 1].to(torch.int64) - ranges[:, 0]).clamp_(min=0).sum().item())))
     torch.cuda.synchronize()
     return stats
 
@@ -262,7 +264,7 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         dev_targets[v] = host_targets_mine[j].to(device)
     median_scale = float(np.median(np.exp(scene["lscale"][:, :3])))
     tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=0.0, isect_cap=cap,
-                 views_in_flight=1 if n_views == 1 else args.views_in_flight, reduce_slices=args.reduce_slices)
+                 views_in_flight=1 if n_views == 1 else args.views_in_flight, reduce_slices=args.reduce_slices, render_chunks=args.chunks)
     if cfg == 4:   # per-pixel binary mask in the alpha byte, alpha-match lane, --normalize-masked-loss
         mask = torch.from_numpy(scenes.ellipse_mask(W, H, 0.4).astype(np.int64))
         for v in mine:
@@ -318,10 +320,13 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     views_per_step = n_views
     value = views_per_step * args.steps / (ms / 1e3)
     e2e_value = views_per_step * args.steps / (ms_e2e / 1e3)
-    launches_view = 1 + (1 + 12 + 2 + 3 * ((tr.ctx.tile_bits + 7) // 8) + 1) + 1 + 1 + 1 + 1 + 1
+    passes = (tr.ctx.tile_bits + 7) // 8
+    launches_view = 1 + (1 + 12 + 2 + 3 * passes + 1) + 1 + 1 + 1 + 1 + 1
+    if args.chunks > 1:   # projection 2, depth sort 13, chunk words 1, per chunk 6 (+1 after the first) + the tile-sort passes, then loss .. projection backward
+        launches_view = 2 + 13 + 1 + sum(6 + (1 if ch else 0) + 3 * passes for ch in range(args.chunks)) + 5
     launches = args.steps * (n_views * launches_view + (0 if (world == 1 and n_views == 1) else world))   # all ranks
     res = {"metric": "train views/s", "value": value, "unit": "views/s", "ms_per_step": ms / args.steps, "scaling": "strong",
-           "config": {"views_per_step": views_per_step, "splats": n, "sh_degree": deg, "resolution": f"{W}x{H}", "parallelism": f"dp{world} by view",
+           "config": {"views_per_step": views_per_step, "render": ("front to back in %d depth chunks, saturated tiles stop emitting" % args.chunks) if args.chunks > 1 else "whole view binned before compositing", "splats": n, "sh_degree": deg, "resolution": f"{W}x{H}", "parallelism": f"dp{world} by view",
                       "l2_policy": "inputs larger than L2 (per view > 126 MB of records, lists and images; 64 distinct views per step)",
                       "scene_counts_view0": stats[0] if stats else None},
            "e2e": {"value": e2e_value, "unit": "views/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 64, "ms_per_step": ms_e2e / args.steps},
@@ -370,6 +375,20 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
     m, ctx = tr.model, tr.ctx
     K = m.K()
+    chunks = ctx.n_chunks
+    chunked_ms = None
+    if chunks > 1:   # the chunked renderer as one stage (project + per-chunk binning and compositing), then the stages of the whole-view form
+        views0 = mine[: max(1, args.stage_views)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tot = 0.0
+        for v in views0:
+            rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True)
+            torch.cuda.synchronize()
+            e0.record(); api.render_forward(ctx, m, rp, sync=False); e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        chunked_ms = tot / len(views0)
+        ctx.n_chunks = 1
     names = ["project", "bin_sort", "raster_fwd", "loss", "raster_bwd", "proj_bwd"]
     acc = {k: 0.0 for k in names}
     views = mine[: max(1, args.stage_views)]
@@ -446,6 +465,10 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
                  "fp32_peak_tflops": fp32_peak / 1e12, "sm_mhz": sm_mhz,
                  "note": "stages timed back to back on one stream; the optimizer update (once per step) is not included"}
     stages["step_roofline"] = step_roof
+    if chunked_ms is not None:
+        ctx.n_chunks = chunks
+        stages["render_chunked"] = {"ms": chunked_ms, "chunks": chunks, "replaces": "project + bin_sort + raster_fwd",
+                                    "whole_view_ms": stages["project"]["ms"] + stages["bin_sort"]["ms"] + stages["raster_fwd"]["ms"]}
     a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src,
             "ms_per_launch": per_launch_ms, "algorithmic_bytes_per_launch": int(bytes_launch), "note": note,

@@ -76,7 +76,8 @@ typedef struct {
                               [1] entries of vis_list */
   void* sort_tmp;          /* scratch of b2k_sort_tmp_bytes() bytes */
   uint64_t sort_tmp_bytes;
-  uint32_t* tile_ranges;   /* [n_tiles][2] start, end into vals_sorted; end shrunk by the forward when bwd_info */
+  uint32_t* tile_ranges;   /* [n_tiles][2] start, end into vals_sorted; end shrunk by the forward when bwd_info
+                              ([n_chunks][n_tiles][2] when n_chunks > 1) */
   float* out_rgba;         /* [P][4] */
   float* out_feat;         /* [P][4] feature lanes x, y, z (zero: feature modes are not implemented), w = final transmittance */
   float* out_depth;        /* [P] expected depth, or NULL: sum(vis z) / alpha where alpha > 0.05 else +inf (the mean-depth
@@ -89,6 +90,12 @@ typedef struct {
                               instead of all n. */
   float* v_out;            /* [P][4] dL/d(rgba) */
   float* loss_accum;       /* [16] */
+  int32_t n_chunks;        /* 0 or 1: the view is binned whole, as the reference does. 2..8: b2k_render_chunked renders it
+                              front to back in this many depth chunks; tile_ranges then holds [n_chunks][n_tiles][2] (one
+                              range per chunk and tile, indices into vals_sorted) and b2k_raster_bwd walks them all */
+  uint32_t* chunk_words;   /* [32 + n_tiles + (tiles_x + 1)(tiles_y + 1)] device scratch of b2k_render_chunked (chunk windows
+                              and counts, one "some pixel can still take a fragment" flag per tile, the summed-area table
+                              of those flags), or NULL when n_chunks <= 1 */
 } B2kCtx;
 
 /* RenderParams, src/gpu/render.h:29-63: the fields this path implements. */
@@ -154,6 +161,16 @@ int b2k_bin_sort_static(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
 uint32_t b2k_static_max_splats(void);
 /* rasterize_forward, src/gpu/render.h:103 (raster_fwd_kernel, src/gpu/raster_fwd.cu:9-71). */
 int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s);
+/* render_forward (src/gpu/render.h:97) for dense scenes, with no counterpart in the reference, which always bins every
+ * intersection of the view before compositing any: project, then bin + composite the splats in ctx->n_chunks chunks of
+ * increasing depth (the nearest 1/2^(C-1) of the visible splats first, then as many again, ... the far half last). A
+ * tile whose pixels have all reached the transmittance cutoff emits no intersections in later chunks, so most of a
+ * dense view is never sorted. out_rgba, out_feat.w, out_depth and every gradient of the backward are bit-identical to
+ * b2k_project + b2k_bin_sort + b2k_raster_fwd; what differs is the bookkeeping a caller can see: vals_sorted /
+ * keys_sorted hold one sorted window per chunk (without the intersections that were skipped), tile_ranges one range
+ * per chunk and tile, last_idx an index into that layout, num_isect[0] the slots used. Needs last_idx and chunk_words;
+ * tile_off and depth_keys are scratch. Overflow of the intersection buffers is reported like b2k_bin_sort's. */
+int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s);
 /* Scratch bytes b2k_project and b2k_bin_sort need in ctx->sort_tmp for a context whose per-splat buffers hold n_cap
  * entries (replaces RenderCtx::cub_tmp, src/gpu/render.h:80). */
 uint64_t b2k_sort_tmp_bytes(int32_t n_cap, uint64_t isect_cap);

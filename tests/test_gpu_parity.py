@@ -398,3 +398,45 @@ def test_adam_by_slices_equals_adam_over_the_whole_model():
         assert np.array_equal(results[0][0][k], results[1][0][k]), k
     assert np.array_equal(results[0][1], results[1][1]) and np.array_equal(results[0][2], results[1][2])
     assert np.count_nonzero(results[0][2]) == n - len(range(0, n, 3))
+
+
+@pytest.mark.parametrize("n_chunks", [2, 5, 8])
+def test_chunked_front_to_back_render_matches_whole_view_binning(n_chunks):
+    """b2k_render_chunked composites the same fragments in the same order as project + bin_sort + raster_fwd, so the
+    image, transmittance, depth and (after the loss) the per-splat gradient lanes agree; dense, opaque splats make
+    tiles saturate early, so later chunks skip them and fewer intersections are sorted. Big-box splats are present."""
+    import torch
+    from b2ctrain_b200 import api
+    W, H, n = 200, 136, 30000
+    scene = scenes.make_splats(n, 2, 91, log_scale=(-3.0, 0.7), opacity=(2.0, 1.0))
+    scene["lscale"][::20, :3] = -1.5   # every 20th splat covers more than 64 tiles (the warp-per-splat paths)
+    cam = scenes.look_at_camera(scenes.orbit_eye(3.0, 40.0, 15.0), W, H, float(H) * 1.4)
+    scene = scenes.floor_for_cameras(scene, [cam])
+    rng = np.random.Generator(np.random.PCG64(4))
+    gt = torch.from_numpy(rng.integers(0, 2 ** 31, W * H, dtype=np.int64).astype(np.int32)).cuda()
+    m = api.Model("cuda:0").upload(scene)
+    out = []
+    for chunks in (1, n_chunks):
+        ctx = api.RenderCtx("cuda:0"); ctx.want_depth = True
+        ctx.setup(W, H, m.cap, n_chunks=chunks)
+        rp = api.RenderParams(cam, bg=(0.2, 0.1, 0.3), sh_degree=2, bwd_info=True)
+        api.render_forward(ctx, m, rp, sync=True)
+        used = ctx.num_isect
+        api.photometric_loss(ctx, api.ViewGPU(gt, None, W, H), api.LossParams())
+        api.rasterize_backward(ctx, m, rp)
+        torch.cuda.synchronize()
+        big = int((ctx.hit_info[:n].cpu().numpy().view(np.uint32).reshape(-1, 4)[:, 2] == 0xFFFFFFFF).sum())
+        out.append(dict(rgba=ctx.out_rgba.cpu().numpy(), T=ctx.out_feat[:, 3].cpu().numpy(), depth=ctx.out_depth.cpu().numpy(),
+                        v=ctx.v_splat[:n].cpu().numpy(), vis=ctx.vis_flag[:n].cpu().numpy(), loss=float(ctx.loss_accum[0]), used=used, big=big,
+                        ranges=ctx.tile_ranges.cpu().numpy().view(np.uint32).reshape(chunks, -1, 2), last=ctx.last_idx.cpu().numpy().view(np.uint32)))
+    a, b = out
+    assert a["big"] > 50
+    assert np.array_equal(a["rgba"], b["rgba"]) and np.array_equal(a["T"], b["T"]) and np.array_equal(a["depth"], b["depth"])
+    assert abs(a["loss"] - b["loss"]) <= 1e-6 * abs(a["loss"])   # the same image; the loss sums its tiles with atomics
+    assert np.array_equal(a["vis"], b["vis"])
+    assert rel_l2(b["v"], a["v"]) <= 1e-5
+    assert b["used"] < 0.7 * a["used"], (a["used"], b["used"])          # saturated tiles stopped emitting
+    # the ranges the backward walks are never longer than in the whole-view binning (a chunk's unused tail is dropped)
+    walked = int((b["ranges"][:, :, 1].astype(np.int64) - b["ranges"][:, :, 0]).clip(min=0).sum())
+    assert 0 < walked <= int((a["ranges"][0, :, 1].astype(np.int64) - a["ranges"][0, :, 0]).sum())
+    assert int(b["last"].max()) < 2 ** 31
