@@ -449,11 +449,11 @@ int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uin
 // sorted by tile, ranged) and composited before the next one is touched, and a tile whose pixels have all reached the
 // transmittance cutoff emits nothing from then on: in a dense scene most intersections lie behind saturated pixels and
 // are never composited, so they need not be sorted either. Chunk c covers the ranks [V b(c-1), V b(c)) of the V
-// splats that hit a tile, with b = 1/2^(C-1), ..., 1/4, 1/2, 1 (small chunks first: the nearest splats decide most
-// pixels). Every chunk's sorted pairs occupy their own window of the key / value buffers, and a tile has one range per
+// splats that hit a tile, with b = 1/4^(C-1), ..., 1/16, 1/4, 1 (small chunks first: the nearest splats decide most
+// pixels, and every chunk costs a dozen launches whatever its size). Every chunk's sorted pairs occupy their own window of the key / value buffers, and a tile has one range per
 // chunk. The words that chain the chunks live on the device:
 //   words[0] = V, words[1 + c] = first slot of chunk c's window, words[16 + c] = pairs of chunk c.
-constexpr int MAX_CHUNKS = 8;
+constexpr int MAX_CHUNKS = 5;
 constexpr int CW_V = 0, CW_BASE = 1, CW_COUNT = 16, CW_WORDS = 32;   // the tile-alive flags follow the header
 
 __device__ __forceinline__ void chunk_ranks(const uint32_t* words, int lo_num, int hi_num, uint32_t& r0, uint32_t& r1) {
@@ -492,7 +492,13 @@ __global__ void __launch_bounds__(1024) alive_sat_kernel(const uint32_t* __restr
   __syncthreads();
   for (int x = threadIdx.x + 1; x < SX; x += blockDim.x) {
     uint32_t run = 0;
-    for (int y = 1; y <= tiles_y; y++) { run += sat[(size_t)y * SX + x]; sat[(size_t)y * SX + x] = run; }
+    for (int y0 = 1; y0 <= tiles_y; y0 += 16) {   // loads of a batch are issued together, ahead of its stores
+      uint32_t v[16];
+#pragma unroll
+      for (int k = 0; k < 16; k++) v[k] = y0 + k <= tiles_y ? sat[(size_t)(y0 + k) * SX + x] : 0u;
+#pragma unroll
+      for (int k = 0; k < 16; k++) { run += v[k]; if (y0 + k <= tiles_y) sat[(size_t)(y0 + k) * SX + x] = run; }
+    }
   }
 }
 
@@ -812,7 +818,7 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   }
   const int emit_blocks = sm_count() * 4 > 1024 ? 1024 : sm_count() * 4;
   for (int ch = 0; ch < C; ch++) {
-    const int lo = ch == 0 ? 0 : 256 >> (C - ch), hi = 256 >> (C - 1 - ch);
+    const int lo = ch == 0 ? 0 : 256 >> (2 * (C - ch)), hi = 256 >> (2 * (C - 1 - ch));
     const uint32_t* live = ch == 0 ? nullptr : alive;   // the first chunk meets only live tiles
     B2K_CUDA(cudaMemsetAsync(big_count, 0, sizeof(uint32_t), s));
     if (live) alive_sat_kernel<<<1, 1024, 0, s>>>(live, c->tiles_x, c->tiles_y, sat);

@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
         vr[p] = vo.x; vg[p] = vo.y; vb[p] = vo.z;
         vow[p] = (vo.w - (bg.x * vo.x + bg.y * vo.y + bg.z * vo.z)) * T[p];
         ifa[p] = 1.f / fmaxf(out_rgba[pix].w, 1e-5f);
-        last[p] = last_idx[pix];
+        last[p] = last_idx[pix] & 0x7FFFFFFFu;   // a chunked forward keeps its saturation flag in bit 31
       }
     }
     st.T = make_float2(T[0], T[1]); st.Sr = st.Sg = st.Sb = f2(0.f);

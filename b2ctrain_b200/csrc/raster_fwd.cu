@@ -14,10 +14,11 @@ constexpr int FWD_WARPS = 4;
 constexpr int FWD_BATCH = 32;
 
 // CHUNKED: the view is composited in depth chunks (chunk `chunk` of `n_chunks`, one launch each, nearest first). Between
-// launches a pixel's state lives in the output buffers: colour sums in out_rgba.xyz, transmittance in out_feat.w, the
-// depth sum in out_depth, and last_idx with bit 31 set once the pixel has reached the cutoff. The last chunk turns the
-// state into the finished pixel. alive[tile] tells the binning of the next chunk whether any pixel of the tile can
-// still take a fragment.
+// launches a pixel's state lives in the output buffers: the colour sums in out_feat.xyz, the transmittance in
+// out_feat.w, and last_idx with bit 31 set once the pixel has reached the cutoff; out_rgba holds the finished pixel
+// after every chunk, so a launch only touches tiles that received fragments. With DEPTH the depth sum travels in
+// out_depth and the last chunk visits every pixel to divide it out. alive[tile] tells the binning of the next chunk
+// whether any pixel of the tile can still take a fragment.
 constexpr uint32_t DONE_BIT = 0x80000000u;
 
 template <bool BWD, bool DEPTH, bool CHUNKED>
@@ -35,7 +36,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
   const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
   const uint2 range = tile_ranges[tile];
   const bool first = !CHUNKED || chunk == 0, final = !CHUNKED || chunk == n_chunks - 1;
-  if (CHUNKED && !first && !final && range.y <= range.x) return;   // nothing of this chunk lands here: state and flag stay
+  if (CHUNKED && !first && range.y <= range.x && !(final && DEPTH)) return;   // nothing of this chunk lands here: pixels, state and flag stay
   float T[2] = {1.f, 1.f}, r[2] = {0.f, 0.f}, g[2] = {0.f, 0.f}, b[2] = {0.f, 0.f}, zs[2] = {0.f, 0.f};
   bool done[2] = {!in0, !in1};
   uint32_t last[2] = {range.x, range.x};
@@ -44,9 +45,8 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     for (int p = 0; p < 2; p++) {
       if (p == 0 ? in0 : in1) {
         const int pix = py * W + px0 + p;
-        const float4 acc = out_rgba[pix];
-        r[p] = acc.x; g[p] = acc.y; b[p] = acc.z;
-        T[p] = out_feat[pix].w;
+        const float4 acc = out_feat[pix];
+        r[p] = acc.x; g[p] = acc.y; b[p] = acc.z; T[p] = acc.w;
         if constexpr (DEPTH) zs[p] = out_depth[pix];
         const uint32_t l = last_idx[pix];
         done[p] = (l & DONE_BIT) != 0u;
@@ -94,16 +94,15 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
   for (int p = 0; p < 2; p++) {
     if (p == 0 ? in0 : in1) {
       const int pix = py * W + px0 + p;
-      if (final) {
-        out_rgba[pix] = make_float4(r[p] + T[p] * bg.x, g[p] + T[p] * bg.y, b[p] + T[p] * bg.z, 1.f - T[p]);
+      out_rgba[pix] = make_float4(r[p] + T[p] * bg.x, g[p] + T[p] * bg.y, b[p] + T[p] * bg.z, 1.f - T[p]);
+      if constexpr (CHUNKED) {
+        out_feat[pix] = make_float4(r[p], g[p], b[p], T[p]);
+        if constexpr (DEPTH) out_depth[pix] = !final ? zs[p] : ((1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY);
+        last_idx[pix] = last[p] | (done[p] ? DONE_BIT : 0u);
+      } else {
         out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
         if constexpr (DEPTH) out_depth[pix] = (1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY;
-        if constexpr (BWD || CHUNKED) last_idx[pix] = last[p];
-      } else {
-        out_rgba[pix] = make_float4(r[p], g[p], b[p], 0.f);
-        out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
-        if constexpr (DEPTH) out_depth[pix] = zs[p];
-        last_idx[pix] = last[p] | (done[p] ? DONE_BIT : 0u);
+        if constexpr (BWD) last_idx[pix] = last[p];
       }
     }
   }

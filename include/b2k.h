@@ -90,7 +90,7 @@ typedef struct {
                               instead of all n. */
   float* v_out;            /* [P][4] dL/d(rgba) */
   float* loss_accum;       /* [16] */
-  int32_t n_chunks;        /* 0 or 1: the view is binned whole, as the reference does. 2..8: b2k_render_chunked renders it
+  int32_t n_chunks;        /* 0 or 1: the view is binned whole, as the reference does. 2..5: b2k_render_chunked renders it
                               front to back in this many depth chunks; tile_ranges then holds [n_chunks][n_tiles][2] (one
                               range per chunk and tile, indices into vals_sorted) and b2k_raster_bwd walks them all */
   uint32_t* chunk_words;   /* [32 + n_tiles + (tiles_x + 1)(tiles_y + 1)] device scratch of b2k_render_chunked (chunk windows
@@ -163,12 +163,13 @@ uint32_t b2k_static_max_splats(void);
 int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s);
 /* render_forward (src/gpu/render.h:97) for dense scenes, with no counterpart in the reference, which always bins every
  * intersection of the view before compositing any: project, then bin + composite the splats in ctx->n_chunks chunks of
- * increasing depth (the nearest 1/2^(C-1) of the visible splats first, then as many again, ... the far half last). A
+ * increasing depth (the nearest 1/4^(C-1) of the visible splats first, each chunk four times the one before). A
  * tile whose pixels have all reached the transmittance cutoff emits no intersections in later chunks, so most of a
  * dense view is never sorted. out_rgba, out_feat.w, out_depth and every gradient of the backward are bit-identical to
  * b2k_project + b2k_bin_sort + b2k_raster_fwd; what differs is the bookkeeping a caller can see: vals_sorted /
  * keys_sorted hold one sorted window per chunk (without the intersections that were skipped), tile_ranges one range
- * per chunk and tile, last_idx an index into that layout, num_isect[0] the slots used. Needs last_idx and chunk_words;
+ * per chunk and tile, last_idx an index into that layout with bit 31 set on pixels that reached the cutoff,
+ * out_feat.xyz the colour sums without the background, num_isect[0] the slots used. Needs last_idx and chunk_words;
  * tile_off and depth_keys are scratch. Overflow of the intersection buffers is reported like b2k_bin_sort's. */
 int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s);
 /* Scratch bytes b2k_project and b2k_bin_sort need in ctx->sort_tmp for a context whose per-splat buffers hold n_cap

@@ -400,7 +400,7 @@ def test_adam_by_slices_equals_adam_over_the_whole_model():
     assert np.count_nonzero(results[0][2]) == n - len(range(0, n, 3))
 
 
-@pytest.mark.parametrize("n_chunks", [2, 5, 8])
+@pytest.mark.parametrize("n_chunks", [2, 3, 5])
 def test_chunked_front_to_back_render_matches_whole_view_binning(n_chunks):
     """b2k_render_chunked composites the same fragments in the same order as project + bin_sort + raster_fwd, so the
     image, transmittance, depth and (after the loss) the per-splat gradient lanes agree; dense, opaque splats make
@@ -439,4 +439,3 @@ def test_chunked_front_to_back_render_matches_whole_view_binning(n_chunks):
     # the ranges the backward walks are never longer than in the whole-view binning (a chunk's unused tail is dropped)
     walked = int((b["ranges"][:, :, 1].astype(np.int64) - b["ranges"][:, :, 0]).clip(min=0).sum())
     assert 0 < walked <= int((a["ranges"][0, :, 1].astype(np.int64) - a["ranges"][0, :, 0]).sum())
-    assert int(b["last"].max()) < 2 ** 31
