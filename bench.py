@@ -38,7 +38,8 @@ def parse():
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
     ap.add_argument("--views-in-flight", type=int, default=4, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--reduce-slices", type=int, default=4, help="slices of the gradient all-reduce pipelined with the Adam update (N > 1)")
-    ap.add_argument("--chunks", type=int, default=1, help="depth chunks of the front-to-back renderer (1 = bin the whole view first, as the reference does)")
+    ap.add_argument("--chunks", type=int, default=0, help="depth chunks of the front-to-back renderer (1 = bin the whole view first, as the reference "
+                    "does; 0 = choose: 4 for scenes of a million splats and more, where most intersections lie behind saturated pixels, else 1)")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
 
@@ -140,6 +141,9 @@ def cpu_reference_arm(args, cfg):
 def main():
     args = parse()
     cfg = WORKLOADS[args.workload]
+    if args.chunks <= 0:
+        from b2ctrain_b200 import scenes as _scenes
+        args.chunks = 4 if (args.splats or _scenes.CONFIG_SPLATS[cfg][0]) >= 1_000_000 else 1
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -323,7 +327,7 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     passes = (tr.ctx.tile_bits + 7) // 8
     launches_view = 1 + (1 + 12 + 2 + 3 * passes + 1) + 1 + 1 + 1 + 1 + 1
     if args.chunks > 1:   # projection 2, depth sort 13, chunk words 1, per chunk 6 (+1 after the first) + the tile-sort passes, then loss .. projection backward
-        launches_view = 2 + 13 + 1 + sum(6 + (1 if ch else 0) + 3 * passes for ch in range(args.chunks)) + 5
+        launches_view = 2 + 13 + 1 + sum(6 + (2 if ch else 0) + 3 * passes for ch in range(args.chunks)) + 5
     launches = args.steps * (n_views * launches_view + (0 if (world == 1 and n_views == 1) else world))   # all ranks
     res = {"metric": "train views/s", "value": value, "unit": "views/s", "ms_per_step": ms / args.steps, "scaling": "strong",
            "config": {"views_per_step": views_per_step, "render": ("front to back in %d depth chunks, saturated tiles stop emitting" % args.chunks) if args.chunks > 1 else "whole view binned before compositing", "splats": n, "sh_degree": deg, "resolution": f"{W}x{H}", "parallelism": f"dp{world} by view",
@@ -431,7 +435,11 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     kernel_ms = {"project_kernel": stages["project"]["ms"], "raster_fwd_kernel": stages["raster_fwd"]["ms"], "photometric_kernel": stages["loss"]["ms"],
                  "raster_bwd_kernel": stages["raster_bwd"]["ms"], "proj_bwd_kernel": stages["proj_bwd"]["ms"], "scan_emit_kernel": ph[1],
                  "radix_scatter_kernel": float(sum(scatter_ms))}
+    if chunks > 1:   # the timed steps ran the chunked renderer: the whole-view binning and forward kernels above were not in them
+        for k in ("radix_scatter_kernel", "scan_emit_kernel", "raster_fwd_kernel"):
+            kernel_ms.pop(k)
     top = max(kernel_ms, key=kernel_ms.get)
+    extra = {}
     if top == "radix_scatter_kernel":
         per_launch_ms = float(np.mean(scatter_ms))
         bytes_launch = 16 * I          # keys + values read, keys + values written
@@ -444,6 +452,12 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
         bytes_launch = alg[stage] if top != "scan_emit_kernel" else 24 * n + 8 * I
         note = "one launch per view"
         traffic = None
+        if top == "raster_bwd_kernel":
+            # dram read + write per launch from an ncu capture at half the splat count (78.5 MB at I_b = 1,243,915), scaled by
+            # the fragments inside the shrunk ranges. The kernel is bound by FP32 issue, not HBM (issue slots 65 % busy on the
+            # SMs that hold tiles with fragments, a quarter of the warp slots occupied): the FP32 figure is reported beside it.
+            traffic = int(63.1 * Ib)
+            note += "; FP32-issue / latency bound (see fp32), so the HBM fraction is small by construction"
     # Step roofline: every stage at the better of its HBM time and (for the two compositing kernels) its FP32 time.
     # F = fragment-pixel evaluations of the last timed view (per pixel: last contributing index - start of its tile's
     # list), charged 24 flop forward and 90 flop backward each; FP32 peak = 2 * 128 lanes * SMs * the SM clock.
@@ -463,16 +477,23 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     step_roof = {"t_roof_ms_per_view": sum(t_roof.values()), "t_measured_ms_per_view": measured, "frac": sum(t_roof.values()) / measured,
                  "per_stage_frac": {nm: t_roof[nm] / stages[nm]["ms"] for nm in names}, "fragment_pixel_evaluations": F,
                  "fp32_peak_tflops": fp32_peak / 1e12, "sm_mhz": sm_mhz,
-                 "note": "stages timed back to back on one stream; the optimizer update (once per step) is not included"}
+                 "note": "stages of the whole-view form timed back to back on one stream; the optimizer update (once per step) is not included"}
     stages["step_roofline"] = step_roof
     if chunked_ms is not None:
         ctx.n_chunks = chunks
         stages["render_chunked"] = {"ms": chunked_ms, "chunks": chunks, "replaces": "project + bin_sort + raster_fwd",
                                     "whole_view_ms": stages["project"]["ms"] + stages["bin_sort"]["ms"] + stages["raster_fwd"]["ms"]}
+        step_roof["chunked"] = {"t_measured_ms_per_view": chunked_ms + stages["loss"]["ms"] + stages["raster_bwd"]["ms"] + stages["proj_bwd"]["ms"],
+                                "frac": sum(t_roof.values()) / (chunked_ms + stages["loss"]["ms"] + stages["raster_bwd"]["ms"] + stages["proj_bwd"]["ms"])}
+    if top in ("raster_bwd_kernel", "raster_fwd_kernel"):
+        flop = (90 if top == "raster_bwd_kernel" else 24) * F
+        extra["fp32"] = {"flop_per_launch": flop, "achieved_tflops": flop / (per_launch_ms * 1e-3) / 1e12, "peak_tflops": fp32_peak / 1e12,
+                         "frac": flop / (per_launch_ms * 1e-3) / fp32_peak, "fragment_pixel_evaluations": F}
     a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": top, "achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src,
             "ms_per_launch": per_launch_ms, "algorithmic_bytes_per_launch": int(bytes_launch), "note": note,
             "kernel_ms_per_view": {k: float(v) for k, v in kernel_ms.items()}}
+    roof.update(extra)
     return roof, stages
 
 
@@ -481,7 +502,7 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
     from b2ctrain_b200.trainer import Renderer
     W, H = cams[0]["W"], cams[0]["H"]
     mine = list(range(rank, len(cams), world))
-    r = Renderer(scene, W, H, device, rank, world, want_depth=True)
+    r = Renderer(scene, W, H, device, rank, world, want_depth=True, render_chunks=args.chunks)
     stats = presize(r, cams, mine, None, False)
     host_out = torch.empty((W * H, 4), dtype=torch.float32).pin_memory()
 
@@ -505,9 +526,12 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
     clocks = sampler.stop()
     ms_e2e = timed(args.steps, True)
     mpix = len(cams) * W * H * args.steps / 1e6
-    launches_view = 1 + (1 + 12 + 2 + 3 * ((r.ctx.tile_bits + 7) // 8) + 1) + 1
+    passes = (r.ctx.tile_bits + 7) // 8
+    launches_view = 1 + (1 + 12 + 2 + 3 * passes + 1) + 1
+    if args.chunks > 1:
+        launches_view = 2 + 13 + 1 + sum(6 + (2 if ch else 0) + 3 * passes for ch in range(args.chunks))
     return {"metric": "render Mpix/s", "value": mpix / (ms / 1e3), "unit": "Mpix/s", "ms_per_step": ms / args.steps, "scaling": "strong",
-            "config": {"cameras": len(cams), "splats": scene["n"], "sh_degree": scene["degree"], "resolution": f"{W}x{H}", "parallelism": f"cameras over {world} GPUs",
+            "config": {"cameras": len(cams), "render": ("front to back in %d depth chunks, saturated tiles stop emitting" % args.chunks) if args.chunks > 1 else "whole view binned before compositing", "splats": scene["n"], "sh_degree": scene["degree"], "resolution": f"{W}x{H}", "parallelism": f"cameras over {world} GPUs",
                        "l2_policy": "inputs larger than L2", "scene_counts_view0": stats[0] if stats else None},
             "e2e": {"value": mpix / (ms_e2e / 1e3), "unit": "Mpix/s", "h2d_bytes_per_step": 100 * len(cams), "d2h_bytes_per_step": 16 * W * H * len(mine)},
             "gpu_launches": args.steps * len(mine) * launches_view, "clocks": clocks}
