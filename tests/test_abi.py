@@ -46,6 +46,10 @@ def test_null_arguments_are_rejected_without_a_device(lib):
     assert lib.b2k_raster_bwd(None, None, None, None) == api.B2K_ERR_ARG
     assert lib.b2k_optim_fused(None, None, None, None, None) == api.B2K_ERR_ARG
     assert lib.b2k_adam(None, None, None, None) == api.B2K_ERR_ARG
+    assert lib.b2k_adam_range(None, None, None, 0, 0, None) == api.B2K_ERR_ARG
+    assert lib.b2k_render_chunked(None, None, None, None, None) == api.B2K_ERR_ARG
+    one_chunk = api.B2kCtx(); one_chunk.n_chunks = 1   # the chunked renderer wants 2 to 5 chunks
+    assert lib.b2k_render_chunked(C.byref(api.B2kModel()), C.byref(api.B2kCamera()), C.byref(api.B2kRenderOpts()), C.byref(one_chunk), None) == api.B2K_ERR_ARG
     m = api.B2kModel(); m.n, m.cap, m.degree = 4, 2, 1   # cap < n
     assert lib.b2k_project(C.byref(m), C.byref(api.B2kCamera()), C.byref(api.B2kRenderOpts()), C.byref(api.B2kCtx()), None) == api.B2K_ERR_ARG
     assert lib.b2k_sort_tmp_bytes(1000, 1 << 22) > 0
