@@ -14,6 +14,7 @@
 //  * Sorting is LSD with 8-bit digits and is stable, so order = ascending (key, original position): exactly the
 //    order the reference's stable sorts define.
 #include "common.cuh"
+#include "sh.cuh"
 
 namespace b2k {
 namespace {
@@ -506,16 +507,24 @@ __device__ __forceinline__ uint32_t box_alive(const uint32_t* __restrict__ sat, 
   return sat[(size_t)y1 * SX + x1] - sat[(size_t)y0 * SX + x1] - sat[(size_t)y1 * SX + x0] + sat[(size_t)y0 * SX + x0];
 }
 
-// Tiles of a masked splat that are still alive (alive == nullptr: all of them).
-__device__ __forceinline__ uint32_t alive_hits(const uint4 hi, uint32_t cnt, const uint32_t* __restrict__ alive, const uint32_t* __restrict__ sat,
+// What the lazily evaluated kernels need to shade a splat.
+struct ShadeArgs { const float4* pos; const float* sh_dc; const float* sh_hi; size_t cap; int active; float cam_pos[3]; };
+
+// Hit mask of a splat whose tile box holds at most 64 tiles: bit (row * width + col) set when the ellipse reaches the tile.
+__device__ __forceinline__ unsigned long long box_hit_mask(const TileRec& rec, int min_x, int min_y, int bw, int bh) {
+  unsigned long long m = 0ull;
+  int bit = 0;
+  for (int ty = min_y; ty < min_y + bh; ty++)
+    for (int tx = min_x; tx < min_x + bw; tx++, bit++)
+      if (tile_hit(tx, ty, rec)) m |= 1ull << bit;
+  return m;
+}
+
+// Hits of a mask that fall on live tiles (alive == nullptr: all of them).
+__device__ __forceinline__ uint32_t alive_hits(unsigned long long bits, uint32_t bw, uint32_t min_x, uint32_t min_y, const uint32_t* __restrict__ alive,
                                                int tiles_x) {
-  if (!alive) return cnt;
-  unsigned long long bits = ((unsigned long long)hi.y << 32) | hi.x;
-  if (bits == 0ull) return 0u;
-  const uint32_t bw = hi.z >> 24, min_x = hi.z & 0xFFFu, min_y = (hi.z >> 12) & 0xFFFu;
+  if (!alive) return (uint32_t)__popcll(bits);
   const uint32_t inv_bw = bw ? (65536u + bw - 1u) / bw : 0u;
-  const uint32_t bh = (((63u - (uint32_t)__clzll((long long)bits)) * inv_bw) >> 16) + 1u;   // rows up to the highest hit
-  if (box_alive(sat, tiles_x + 1, (int)min_x, (int)min_y, (int)(min_x + bw), (int)(min_y + bh)) == 0u) return 0u;
   uint32_t f = 0;
   while (bits != 0ull) {
     const uint32_t bit = (uint32_t)__ffsll((long long)bits) - 1u;
@@ -526,55 +535,96 @@ __device__ __forceinline__ uint32_t alive_hits(const uint4 hi, uint32_t cnt, con
   return f;
 }
 
-// Per rank of the chunk: how many pairs the splat will emit. Big-box splats are listed (rank, index) for the
-// warp-per-splat kernels; with every tile alive their count is the projection's.
-__global__ void __launch_bounds__(256) chunk_count_kernel(const uint32_t* __restrict__ words, int lo_num, int hi_num, const uint32_t* __restrict__ order,
-                                                          const uint32_t* __restrict__ tile_count, const uint4* __restrict__ hit_info,
-                                                          const uint32_t* __restrict__ alive, const uint32_t* __restrict__ sat, int tiles_x,
-                                                          uint32_t* __restrict__ fcount,
-                                                          uint32_t* __restrict__ big_list, uint32_t* __restrict__ big_count) {
+// First step of a chunk's count, one thread per rank: a splat whose tile box is empty, or holds no live tile (four
+// loads of the summed-area table), emits nothing; the others are appended to the list of their kind, masked boxes and
+// big boxes, so that the expensive steps below run on dense lists instead of one live lane per warp.
+__global__ void __launch_bounds__(256) chunk_filter_kernel(const uint32_t* __restrict__ words, int lo_num, int hi_num, const uint32_t* __restrict__ order,
+                                                           const uint4* __restrict__ hit_info, const uint32_t* __restrict__ sat, int tiles_x,
+                                                           uint32_t* __restrict__ fcount, uint32_t* __restrict__ live_list, uint32_t* __restrict__ big_list,
+                                                           uint32_t* __restrict__ counts) {
   uint32_t r0, r1;
   chunk_ranks(words, lo_num, hi_num, r0, r1);
-  for (uint32_t r = r0 + blockIdx.x * blockDim.x + threadIdx.x; r < r1; r += gridDim.x * blockDim.x) {
-    const uint32_t i = order[r];
-    const uint32_t cnt = tile_count[i];
-    uint32_t f = 0;
-    if (cnt) {
-      const uint4 hi = hit_info[i];
-      if (hi.z == 0xFFFFFFFFu) {
-        const uint32_t e = atomicAdd(big_count, 1u);
-        big_list[2 * e] = r; big_list[2 * e + 1] = i;
-        f = cnt;                       // replaced by chunk_count_big_kernel when tiles have died
-      } else {
-        f = alive_hits(hi, cnt, alive, sat, tiles_x);
+  const int lane = threadIdx.x & 31;
+  const uint32_t span = (r1 - r0 + 31u) & ~31u;   // whole warps, so the votes below are convergent
+  for (uint32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < span; q += gridDim.x * blockDim.x) {
+    const uint32_t r = r0 + q;
+    int kind = 0;   // 0 emits nothing, 1 masked box, 2 big box
+    if (r < r1) {
+      const uint4 hi = hit_info[order[r]];
+      if (hi.w != 0u) {
+        int x0, y0, x1, y1;
+        if (hi.z == 0xFFFFFFFFu) { x0 = (int)(hi.x & 0xFFFFu); y0 = (int)(hi.x >> 16); x1 = x0 + (int)(hi.y & 0xFFFFu); y1 = y0 + (int)(hi.y >> 16); kind = 2; }
+        else { x0 = (int)(hi.z & 0xFFFu); y0 = (int)((hi.z >> 12) & 0xFFFu); x1 = x0 + (int)(hi.z >> 24); y1 = y0 + (int)hi.w; kind = 1; }
+        if (sat && box_alive(sat, tiles_x + 1, x0, y0, x1, y1) == 0u) kind = 0;
       }
+      if (kind == 0) fcount[r] = 0u;
+    }
+#pragma unroll
+    for (int k = 1; k <= 2; k++) {   // one atomic per warp and list
+      const uint32_t m = __ballot_sync(0xffffffffu, kind == k);
+      if (m) {
+        uint32_t base = 0;
+        if (lane == __ffs(m) - 1) base = atomicAdd(counts + (k - 1), (uint32_t)__popc(m));
+        base = __shfl_sync(0xffffffffu, base, __ffs(m) - 1);
+        if (kind == k) (k == 1 ? live_list : big_list)[base + __popc(m & ((1u << lane) - 1u))] = r;
+      }
+    }
+  }
+}
+
+// Second step, one thread per listed masked-box splat: the ellipse-tile tests the projection left out, the count of
+// hits on live tiles, and for a splat that emits its hit mask (kept for the emission) and its colour.
+template <int DEG>
+__global__ void __launch_bounds__(256) chunk_mask_kernel(const uint32_t* __restrict__ live_list, const uint32_t* __restrict__ counts,
+                                                         const uint32_t* __restrict__ order, uint4* __restrict__ hit_info, const float4* __restrict__ proj0,
+                                                         const float4* __restrict__ proj1, float4* __restrict__ proj2, ShadeArgs sa,
+                                                         const uint32_t* __restrict__ alive, int tiles_x, uint32_t* __restrict__ fcount) {
+  const uint32_t count = counts[0];
+  for (uint32_t e = blockIdx.x * blockDim.x + threadIdx.x; e < count; e += gridDim.x * blockDim.x) {
+    const uint32_t r = live_list[e], i = order[r];
+    const uint4 hi = hit_info[i];
+    const uint32_t bw = hi.z >> 24, min_x = hi.z & 0xFFFu, min_y = (hi.z >> 12) & 0xFFFu, bh = hi.w;
+    const float4 a = proj0[i], b = proj1[i];
+    const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
+    const unsigned long long m = box_hit_mask(rec, (int)min_x, (int)min_y, (int)bw, (int)bh);
+    const uint32_t f = alive_hits(m, bw, min_x, min_y, alive, tiles_x);
+    if (f) {
+      hit_info[i] = make_uint4((uint32_t)m, (uint32_t)(m >> 32), hi.z, hi.w);
+      const float4 p = sa.pos[i];
+      proj2[i] = splat_colour<DEG>((int)i, sa.cap, make_float3(p.x, p.y, p.z), sa.cam_pos, sa.active, sa.sh_dc, sa.sh_hi);
     }
     fcount[r] = f;
   }
 }
 
-__global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ big_count,
-                                                              const float4* __restrict__ proj0, const float4* __restrict__ proj1, int W, int H, int tiles_x,
-                                                              int tiles_y, const uint32_t* __restrict__ alive, const uint32_t* __restrict__ sat,
-                                                              uint32_t* __restrict__ fcount) {
+// Second step for the listed big-box splats, one warp each: lanes sweep the box 32 tiles at a time.
+template <int DEG>
+__global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ counts,
+                                                              const uint32_t* __restrict__ order, const uint4* __restrict__ hit_info,
+                                                              const float4* __restrict__ proj0, const float4* __restrict__ proj1, float4* __restrict__ proj2,
+                                                              ShadeArgs sa, int tiles_x, const uint32_t* __restrict__ alive, uint32_t* __restrict__ fcount) {
   const int lane = threadIdx.x & 31;
-  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = *big_count;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = counts[1];
   for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
-    const uint32_t r = big_list[2 * e], i = big_list[2 * e + 1];
+    const uint32_t r = big_list[e], i = order[r];
+    const uint4 hi = hit_info[i];
     const float4 a = proj0[i], b = proj1[i];
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
-    TileBox bb;
+    const int min_x = (int)(hi.x & 0xFFFFu), min_y = (int)(hi.x >> 16), bw = (int)(hi.y & 0xFFFFu), area = bw * (int)(hi.y >> 16);
     uint32_t hits = 0;
-    if (tile_box(rec, W, H, tiles_x, tiles_y, bb) && box_alive(sat, tiles_x + 1, bb.min_x, bb.min_y, bb.max_x, bb.max_y) != 0u) {
-      const int bw = bb.max_x - bb.min_x, area = bw * (bb.max_y - bb.min_y);
-      for (int t0 = 0; t0 < area; t0 += 32) {
-        const int t = t0 + lane;
-        const int tx = bb.min_x + t % bw, ty = bb.min_y + t / bw;
-        const bool hit = t < area && alive[ty * tiles_x + tx] != 0u && tile_hit(tx, ty, rec);
-        hits += __popc(__ballot_sync(0xffffffffu, hit));
+    for (int t0 = 0; t0 < area; t0 += 32) {
+      const int t = t0 + lane;
+      const int tx = min_x + t % bw, ty = min_y + t / bw;
+      const bool hit = t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec);
+      hits += __popc(__ballot_sync(0xffffffffu, hit));
+    }
+    if (lane == 0) {
+      fcount[r] = hits;
+      if (hits) {
+        const float4 p = sa.pos[i];
+        proj2[i] = splat_colour<DEG>((int)i, sa.cap, make_float3(p.x, p.y, p.z), sa.cam_pos, sa.active, sa.sh_dc, sa.sh_hi);
       }
     }
-    if (lane == 0) fcount[r] = hits;
   }
 }
 
@@ -675,26 +725,26 @@ __global__ void __launch_bounds__(EMIT_THREADS) chunk_emit_kernel(
   }
 }
 
-__global__ void __launch_bounds__(256) chunk_emit_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ big_count,
+__global__ void __launch_bounds__(256) chunk_emit_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ counts,
+                                                             const uint32_t* __restrict__ order, const uint4* __restrict__ hit_info,
                                                              const uint32_t* __restrict__ fcount, const uint32_t* __restrict__ big_start,
-                                                             const float4* __restrict__ proj0,
-                                                             const float4* __restrict__ proj1, int W, int H, int tiles_x, int tiles_y,
+                                                             const float4* __restrict__ proj0, const float4* __restrict__ proj1, int tiles_x,
                                                              const uint32_t* __restrict__ alive, uint32_t cap, uint32_t* __restrict__ keys,
                                                              uint32_t* __restrict__ vals) {
   const int lane = threadIdx.x & 31;
-  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = *big_count;
+  const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = counts[1];
   for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
-    const uint32_t r = big_list[2 * e], i = big_list[2 * e + 1];
-    if (fcount[r] == 0u) continue;   // every tile of the splat has died
+    const uint32_t r = big_list[e];
+    if (fcount[r] == 0u) continue;   // no live tile of the box is hit
+    const uint32_t i = order[r];
     uint32_t at = big_start[r];
+    const uint4 hi = hit_info[i];
     const float4 a = proj0[i], b = proj1[i];
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
-    TileBox bb;
-    if (!tile_box(rec, W, H, tiles_x, tiles_y, bb)) continue;
-    const int bw = bb.max_x - bb.min_x, area = bw * (bb.max_y - bb.min_y);
+    const int min_x = (int)(hi.x & 0xFFFFu), min_y = (int)(hi.x >> 16), bw = (int)(hi.y & 0xFFFFu), area = bw * (int)(hi.y >> 16);
     for (int t0 = 0; t0 < area; t0 += 32) {
       const int t = t0 + lane;
-      const int tx = bb.min_x + t % bw, ty = bb.min_y + t / bw;
+      const int tx = min_x + t % bw, ty = min_y + t / bw;
       const bool hit = t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec);
       const uint32_t m = __ballot_sync(0xffffffffu, hit);
       if (hit) {
@@ -779,8 +829,16 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   B2K_REQUIRE(c->out_rgba && c->out_feat && c->keys && c->vals && c->keys_sorted && c->vals_sorted && c->sort_tmp);
   cudaStream_t s = (cudaStream_t)stream;
   const int n = m->n;
-  int st = b2k_project(m, cam, o, c, stream);
-  if (st) return st;
+  B2K_REQUIRE(n >= 0 && m->cap >= n && m->degree >= 0 && m->degree <= 4 && c->proj0 && c->proj1 && c->proj2 && c->tile_count && c->hit_info);
+  B2K_REQUIRE(c->depth_keys_sorted && c->order && c->order_in);
+  B2K_REQUIRE(cam->W == c->W && cam->H == c->H && c->tiles_x == div_up(c->W, RT_W) && c->tiles_y == div_up(c->H, RT_W));
+  int st = B2K_OK;
+  if (n > 0) {
+    B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi));
+    if (c->n_cap < n) return B2K_ERR_CAPACITY;
+    st = launch_project_lite(m, cam, o, c, s);
+    if (st) return st;
+  }
   B2K_CUDA(cudaMemsetAsync(c->tile_ranges, 0, sizeof(uint32_t) * 2 * (size_t)c->n_tiles * C, s));
   if (n == 0) {
     B2K_CUDA(cudaMemsetAsync(c->num_isect, 0, sizeof(uint32_t), s));
@@ -806,8 +864,9 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   uint32_t* ov = (tile_passes % 2 == 0) ? c->vals : c->vals_sorted;
   uint32_t* fcount = c->depth_keys;          // scratch pair of the depth sort: free from here on
   uint32_t* big_start = c->tile_off;         // first slot of each listed big-box splat, by rank
-  uint32_t* big_list = big_emit_ptr(c);      // [n_cap][2] (rank, splat)
-  uint32_t* big_count = big_count_ptr(c) + 1;
+  uint32_t* live_list = big_emit_ptr(c);                    // ranks of the chunk's masked-box splats with a live tile in the box
+  uint32_t* big_list = big_emit_ptr(c) + (size_t)c->n_cap;  // the same for big-box splats
+  uint32_t* list_counts = big_count_ptr(c) + 2;             // entries of the two lists
   {
     static bool emit_attr[64] = {false};
     int dev = 0;
@@ -817,21 +876,30 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
     }
   }
   const int emit_blocks = sm_count() * 4 > 1024 ? 1024 : sm_count() * 4;
+  ShadeArgs sa;
+  sa.pos = (const float4*)(o->pos_override ? o->pos_override : m->pos_op);
+  sa.sh_dc = m->sh_dc; sa.sh_hi = m->sh_hi; sa.cap = (size_t)m->cap;
+  sa.active = o->sh_degree < m->degree ? (o->sh_degree < 0 ? 0 : o->sh_degree) : m->degree;
+  for (int k = 0; k < 3; k++) sa.cam_pos[k] = cam->pos[k];
+#define B2K_CHUNK_DEG(deg, CALL) \
+  switch (deg) { case 0: { constexpr int D = 0; CALL; } break; case 1: { constexpr int D = 1; CALL; } break; case 2: { constexpr int D = 2; CALL; } break; \
+                 case 3: { constexpr int D = 3; CALL; } break; default: { constexpr int D = 4; CALL; } break; }
   for (int ch = 0; ch < C; ch++) {
     const int lo = ch == 0 ? 0 : 256 >> (2 * (C - ch)), hi = 256 >> (2 * (C - 1 - ch));
     const uint32_t* live = ch == 0 ? nullptr : alive;   // the first chunk meets only live tiles
-    B2K_CUDA(cudaMemsetAsync(big_count, 0, sizeof(uint32_t), s));
+    B2K_CUDA(cudaMemsetAsync(list_counts, 0, 2 * sizeof(uint32_t), s));
     if (live) alive_sat_kernel<<<1, 1024, 0, s>>>(live, c->tiles_x, c->tiles_y, sat);
-    chunk_count_kernel<<<sm_count() * 8, 256, 0, s>>>(words, lo, hi, c->order, c->tile_count, (const uint4*)c->hit_info, live, sat, c->tiles_x, fcount,
-                                                      big_list, big_count);
-    if (live)
-      chunk_count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
-                                                            c->tiles_x, c->tiles_y, live, sat, fcount);
+    chunk_filter_kernel<<<sm_count() * 8, 256, 0, s>>>(words, lo, hi, c->order, (const uint4*)c->hit_info, live ? sat : nullptr, c->tiles_x, fcount,
+                                                       live_list, big_list, list_counts);
+    B2K_CHUNK_DEG(m->degree, (chunk_mask_kernel<D><<<sm_count() * 8, 256, 0, s>>>(live_list, list_counts, c->order, (uint4*)c->hit_info,
+        (const float4*)c->proj0, (const float4*)c->proj1, (float4*)c->proj2, sa, live, c->tiles_x, fcount)));
+    B2K_CHUNK_DEG(m->degree, (chunk_count_big_kernel<D><<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info,
+        (const float4*)c->proj0, (const float4*)c->proj1, (float4*)c->proj2, sa, c->tiles_x, live, fcount)));
     chunk_sums_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(words, lo, hi, fcount, sc.block_sums);
     chunk_emit_kernel<<<emit_blocks, EMIT_THREADS, EMIT_SMEM, s>>>(words, ch, lo, hi, c->order, fcount, sc.block_sums, (const uint4*)c->hit_info, live,
                                                                    c->tiles_x, (uint32_t)c->isect_cap, big_start, ek, ev, c->num_isect);
-    chunk_emit_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, fcount, big_start, (const float4*)c->proj0, (const float4*)c->proj1, c->W, c->H,
-                                                         c->tiles_x, c->tiles_y, live, (uint32_t)c->isect_cap, ek, ev);
+    chunk_emit_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info, fcount, big_start,
+                                                         (const float4*)c->proj0, (const float4*)c->proj1, c->tiles_x, live, (uint32_t)c->isect_cap, ek, ev);
     st = check_launch();
     if (st) return st;
     st = radix_sort(ek, ev, ok, ov, words + CW_COUNT + ch, (uint32_t)c->isect_cap, c->tile_bits, sc, blocks, s, words + CW_BASE + ch);
@@ -841,6 +909,7 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
     st = launch_raster_fwd(c, o, ch, C, alive, s);
     if (st) return st;
   }
+#undef B2K_CHUNK_DEG
   return B2K_OK;
 }
 

@@ -19,6 +19,8 @@ constexpr int NUM_SMS_HINT = 148;       // B200; grids of persistent kernels are
 extern int g_last_cuda_error;
 int check_launch();                     // cudaGetLastError -> status
 int sm_count();
+// Records, tile boxes and depth keys only (project.cu): the chunked renderer tests tiles and shades later.
+int launch_project_lite(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* o, const B2kCtx* c, cudaStream_t s);
 // One depth chunk of a chunked view, or the whole view when n_chunks <= 1 (raster_fwd.cu).
 int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_chunks, uint32_t* alive, cudaStream_t s);
 

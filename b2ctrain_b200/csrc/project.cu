@@ -73,27 +73,7 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
     proj0[i] = make_float4(pr.mx, pr.my, pr.c00, pr.c01);
     proj1[i] = make_float4(pr.c11, pr.opac, pr.mean_c.z, pr.power);
     if (shade) {
-      // Colour from SH along the direction camera -> splat (+0.5, clamped to +-100 as in project.cu:52-55).
-      float3 v = make_float3(po.x - cam.pos[0], po.y - cam.pos[1], po.z - cam.pos[2]);
-      const float inv = 1.f / fmaxf(sqrtf(v.x * v.x + v.y * v.y + v.z * v.z), 1e-12f);
-      v.x *= inv; v.y *= inv; v.z *= inv;
-      constexpr int K = (DEG + 1) * (DEG + 1);
-      float b[K];
-      sh_basis<DEG>(v, active, b);
-      float c[3];
-#pragma unroll
-      for (int ch = 0; ch < 3; ch++) c[ch] = b[0] * sh_dc[(size_t)ch * cap + i];
-      const int kact = (active + 1) * (active + 1);
-#pragma unroll
-      for (int k = 1; k < K; k++) {
-        if (k < kact) {
-#pragma unroll
-          for (int ch = 0; ch < 3; ch++) c[ch] += b[k] * sh_hi[(size_t)((k - 1) * 3 + ch) * cap + i];
-        }
-      }
-#pragma unroll
-      for (int ch = 0; ch < 3; ch++) { const float t = c[ch] + 0.5f; c[ch] = isfinite(t) ? fminf(fmaxf(t, -100.f), 100.f) : 0.f; }
-      proj2[i] = make_float4(c[0], c[1], c[2], 0.f);
+      proj2[i] = splat_colour<DEG>(i, cap, make_float3(po.x, po.y, po.z), cam.pos, active, sh_dc, sh_hi);
     }
   } else {
     proj1[i] = make_float4(0.f, 0.f, 0.f, -1.f);   // no record
@@ -104,6 +84,51 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
     tile_count[i] = hits;
     depth_keys[i] = hits ? __float_as_uint(pr.mean_c.z) : 0xFFFFFFFFu;
   }
+}
+
+
+// The record half of the projection for the chunked renderer, which decides tiles and colours later and only for the
+// splats whose tile box still holds a live tile: records, the tile box, the depth key, the screen-size statistic.
+// hit_info = (0, 0, box, height) with box = min_x | min_y << 12 | width << 24 for boxes of at most 64 tiles, and
+// (min_x | min_y << 16, width | height << 16, 0xFFFFFFFF, height) above that; height = 0 marks an empty box.
+// tile_count holds the box area, an upper bound of the tiles hit (zero exactly when the box is empty).
+__global__ void __launch_bounds__(PROJ_BLOCK) project_lite_kernel(
+    int n, const float4* __restrict__ pos_op, const float4* __restrict__ quat, const float4* __restrict__ lscale, CamDev cam, int tiles_x, int tiles_y,
+    float4* __restrict__ proj0, float4* __restrict__ proj1, uint32_t* __restrict__ tile_count, uint4* __restrict__ hit_info,
+    uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 po = pos_op[i], q = quat[i], ls = lscale[i];
+  Proj pr;
+  uint32_t area = 0, box = 0, bh_out = 0, w0 = 0, w1 = 0;
+  if (project_one(po, q, ls, cam, pr)) {
+    const TileRec rec = make_tile_rec(pr.mx, pr.my, pr.c00, pr.c01, pr.c11, pr.power);
+    TileBox bb;
+    if (tile_box(rec, cam.W, cam.H, tiles_x, tiles_y, bb)) {
+      const int bw = bb.max_x - bb.min_x, bh = bb.max_y - bb.min_y;
+      if (bw > 0 && bh > 0) {
+        area = (uint32_t)(bw * bh);
+        bh_out = (uint32_t)bh;
+        if (area > (uint32_t)MASK_TILES) {
+          box = 0xFFFFFFFFu;
+          w0 = (uint32_t)bb.min_x | ((uint32_t)bb.min_y << 16); w1 = (uint32_t)bw | ((uint32_t)bh << 16);
+        } else {
+          box = (uint32_t)bb.min_x | ((uint32_t)bb.min_y << 12) | ((uint32_t)bw << 24);
+        }
+      }
+      const float detc = pr.c00 * pr.c11 - pr.c01 * pr.c01;
+      const float ex = sqrtf(2.f * pr.power * pr.c11 / detc), ey = sqrtf(2.f * pr.power * pr.c00 / detc);
+      if (max_screen) { const float ms = fmaxf(ex / (float)cam.W, ey / (float)cam.H); if (ms > max_screen[i]) atomic_max_nonneg(max_screen + i, ms); }
+    }
+    proj0[i] = make_float4(pr.mx, pr.my, pr.c00, pr.c01);
+    proj1[i] = make_float4(pr.c11, pr.opac, pr.mean_c.z, pr.power);
+  } else {
+    proj1[i] = make_float4(0.f, 0.f, 0.f, -1.f);   // no record
+  }
+  hit_info[i] = make_uint4(w0, w1, box, bh_out);
+  order_in[i] = (uint32_t)i;
+  tile_count[i] = area;
+  depth_keys[i] = area ? __float_as_uint(pr.mean_c.z) : 0xFFFFFFFFu;
 }
 
 // One warp per listed splat: lanes sweep the tile box 32 tiles at a time.
@@ -182,6 +207,16 @@ int launch(const B2kModel* m, const CamDev& cam, const B2kRenderOpts* o, const B
 }
 
 }  // namespace
+
+int launch_project_lite(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* o, const B2kCtx* c, cudaStream_t s) {
+  const float4* pos = (const float4*)(o->pos_override ? o->pos_override : m->pos_op);
+  const float4* quat = (const float4*)(o->quat_override ? o->quat_override : m->quat);
+  const float4* lscale = (const float4*)(o->lscale_override ? o->lscale_override : m->lscale);
+  project_lite_kernel<<<div_up(m->n, PROJ_BLOCK), PROJ_BLOCK, 0, s>>>(m->n, pos, quat, lscale, to_camdev(*cam), c->tiles_x, c->tiles_y, (float4*)c->proj0,
+                                                                      (float4*)c->proj1, c->tile_count, (uint4*)c->hit_info, c->depth_keys_sorted, c->order,
+                                                                      m->max_screen);
+  return check_launch();
+}
 }  // namespace b2k
 
 using namespace b2k;

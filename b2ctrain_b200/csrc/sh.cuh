@@ -76,6 +76,33 @@ __device__ __forceinline__ float3 sh_dir_grad(const float3 v, const float* w) {
   return make_float3(gx, gy, gz);
 }
 
+// Colour of splat i seen from the camera at cam_pos: SH up to `active` along the direction camera -> splat, + 0.5,
+// clamped to +-100, non-finite -> 0 (src/gpu/project.cu:44-55). One definition, so every caller rounds alike.
+template <int DEG>
+__device__ __forceinline__ float4 splat_colour(int i, size_t cap, float3 mean, const float* __restrict__ cam_pos, int active,
+                                               const float* __restrict__ sh_dc, const float* __restrict__ sh_hi) {
+  float3 v = make_float3(mean.x - cam_pos[0], mean.y - cam_pos[1], mean.z - cam_pos[2]);
+  const float inv = 1.f / fmaxf(sqrtf(v.x * v.x + v.y * v.y + v.z * v.z), 1e-12f);
+  v.x *= inv; v.y *= inv; v.z *= inv;
+  constexpr int K = (DEG + 1) * (DEG + 1);
+  float b[K];
+  sh_basis<DEG>(v, active, b);
+  float c[3];
+#pragma unroll
+  for (int ch = 0; ch < 3; ch++) c[ch] = b[0] * sh_dc[(size_t)ch * cap + i];
+  const int kact = (active + 1) * (active + 1);
+#pragma unroll
+  for (int k = 1; k < K; k++) {
+    if (k < kact) {
+#pragma unroll
+      for (int ch = 0; ch < 3; ch++) c[ch] += b[k] * sh_hi[(size_t)((k - 1) * 3 + ch) * cap + i];
+    }
+  }
+#pragma unroll
+  for (int ch = 0; ch < 3; ch++) { const float t = c[ch] + 0.5f; c[ch] = isfinite(t) ? fminf(fmaxf(t, -100.f), 100.f) : 0.f; }
+  return make_float4(c[0], c[1], c[2], 0.f);
+}
+
 #endif
 
 }  // namespace b2k

@@ -42,6 +42,7 @@ B2kCtx view_of(const RenderCtx& c) {
   v.out_rgba = (float*)c.out_rgba.ptr; v.out_feat = (float*)c.out_feat.ptr; v.out_depth = c.out_depth.ptr;
   v.last_idx = c.last_idx.ptr; v.v_splat = c.v_splat.ptr; v.vis_flag = c.vis_flag.ptr; v.vis_list = c.vis_list.ptr; v.v_out = (float*)c.v_out.ptr;
   v.loss_accum = c.loss_accum.ptr;
+  v.n_chunks = c.n_chunks; v.chunk_words = c.chunk_words.ptr;
   return v;
 }
 
@@ -150,7 +151,8 @@ void RenderCtx::setup(int w, int h, int n, cudaStream_t stream) {
     vis_list.free(); vis_list.reserve(nn);
     n_cap = (int)nn;
   }
-  tile_ranges.reserve(n_tiles);
+  tile_ranges.reserve((size_t)n_tiles * (n_chunks > 1 ? n_chunks : 1));
+  if (n_chunks > 1) chunk_words.reserve(32 + (size_t)n_tiles + (size_t)(tiles_x + 1) * (tiles_y + 1));
   const size_t npx = (size_t)W * H;
   out_rgba.reserve(npx); out_feat.reserve(npx); last_idx.reserve(npx); v_out.reserve(npx);
   if (want_depth) out_depth.reserve(npx);
@@ -188,6 +190,18 @@ void rasterize_forward(RenderCtx& ctx, const RenderParams& p, cudaStream_t strea
 }
 
 void render_forward(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream) {
+  if (ctx.n_chunks > 1) {   // front to back in depth chunks: same image and gradients, saturated tiles stop emitting
+    for (;;) {
+      const B2kModel mv = view_of(m); const B2kCtx cv = view_of(ctx); const B2kCamera cam = camera_of(p.cam); const B2kRenderOpts o = opts_of(p, "render_forward");
+      check(b2k_render_chunked(&mv, &cam, &o, &cv, stream), "render_forward");
+      uint32_t total = 0;
+      const int st = b2k_read_num_isect(&cv, stream, &total);
+      ctx.num_isect = total;
+      if (st != B2K_ERR_OVERFLOW) { check(st, "render_forward"); return; }
+      size_t ncap = ctx.isect_cap; while (ncap < (size_t)total + 32u * (size_t)ctx.n_chunks) ncap *= 2;
+      alloc_isect(ctx, ncap);
+    }
+  }
   project_splats(ctx, m, p, stream);
   bin_and_sort(ctx, m, stream);
   rasterize_forward(ctx, p, stream);

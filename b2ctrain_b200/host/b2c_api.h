@@ -135,7 +135,7 @@ struct RenderCtx {
   uint32_t num_isect = 0;
   DevBuf<uint32_t> d_num_isect;
   DevBuf<unsigned char> cub_tmp;       // the radix sort's scratch
-  DevBuf<uint2> tile_ranges;
+  DevBuf<uint2> tile_ranges;           // [n_tiles], or [n_chunks][n_tiles] when rendering in chunks
   DevBuf<float4> out_rgba, out_feat;
   DevBuf<float> out_depth;             // optional expected depth (reserve it to enable)
   DevBuf<uint32_t> last_idx;
@@ -145,6 +145,8 @@ struct RenderCtx {
   DevBuf<float4> v_out;
   DevBuf<float> loss_accum;
   bool want_depth = false;
+  int n_chunks = 1;                 // set > 1 before setup(): render_forward composites front to back in depth chunks
+  DevBuf<uint32_t> chunk_words;     // scratch of the chunked renderer
   void setup(int W, int H, int n_splats, cudaStream_t stream);
 };
 

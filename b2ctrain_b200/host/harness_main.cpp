@@ -1,7 +1,8 @@
 // Test driver for the C++ host mirror, shaped like the reference's gradient-test Harness (tests/tests.cpp:61-102):
 // setup() uploads a scene, loss() = render_forward + photometric_loss + readback, analytic() = loss() + backward +
 // optimizer_step with grad_out set. Reads a scene file, writes loss, image and parameter gradients to a result file;
-// the Python test compares those with the oracle.
+// the Python test compares those with the oracle. An optional third argument renders front to back in that many depth
+// chunks.
 //
 // Scene file (little endian): int32 n, degree, W, H, composite, mask, alpha_lane, has_weights; float32 fx, fy, cx, cy,
 // R[9], t[3], bg[3], l1_w, ssim_w, match_alpha_weight, scale; then float32 pos[n*3], log_scale[n*3], quat[n*4],
@@ -44,7 +45,7 @@ struct Harness {
 template <typename T> static void rd(FILE* f, T* p, size_t n) { if (n && fread(p, sizeof(T), n, f) != n) { fprintf(stderr, "short read\n"); exit(2); } }
 
 int main(int argc, char** argv) {
-  if (argc < 3) { fprintf(stderr, "usage: %s scene.bin result.bin\n", argv[0]); return 2; }
+  if (argc < 3) { fprintf(stderr, "usage: %s scene.bin result.bin [depth chunks]\n", argv[0]); return 2; }
   try {
     FILE* f = fopen(argv[1], "rb"); if (!f) { perror("scene"); return 2; }
     int32_t hdr[8]; rd(f, hdr, 8);
@@ -61,6 +62,7 @@ int main(int argc, char** argv) {
     for (int i = 0; i < 3; i++) cam.t[i] = fl[13 + i];
     cam.update_pos();
     Harness hs;
+    if (argc > 3) hs.ctx.n_chunks = atoi(argv[3]);   // > 1: the front-to-back chunked renderer
     for (int i = 0; i < 3; i++) hs.lp.bg[i] = fl[16 + i];
     hs.lp.l1_w = fl[19]; hs.lp.ssim_w = fl[20]; hs.lp.match_alpha_weight = fl[21]; hs.lp.scale = fl[22];
     hs.lp.composite = hdr[4]; hs.lp.mask = hdr[5]; hs.lp.alpha_lane = hdr[6];

@@ -238,8 +238,10 @@ def presize(tr_or_r, cams, mine, targets, is_train):
             while cap < total:
                 cap *= 2
             ctx._alloc_isect(cap)
+        ranges = ctx.tile_ranges.view(-1, 2).clone()
+        if ctx.n_chunks > 1:   # the chunked renderer leaves box areas in tile_count: count the exact intersections with the whole-view projection
+            api.project_splats(ctx, m, rp)
         tc = ctx.tile_count[: m.n]
-        ranges = ctx.tile_ranges.view(-1, 2)
         stats.append(dict(V=int((tc != 0).sum().item()), I=int(tc.to(torch.int64).sum().item()), I_sorted=total,
                           I_b=int((ranges[:, 1].to(torch.int64) - ranges[:, 0]).clamp_(min=0).sum().item())))
     torch.cuda.synchronize()

@@ -170,7 +170,9 @@ int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s)
  * keys_sorted hold one sorted window per chunk (without the intersections that were skipped), tile_ranges one range
  * per chunk and tile, last_idx an index into that layout with bit 31 set on pixels that reached the cutoff,
  * out_feat.xyz the colour sums without the background, num_isect[0] the slots used. Needs last_idx and chunk_words;
- * tile_off and depth_keys are scratch. Overflow of the intersection buffers is reported like b2k_bin_sort's. */
+ * tile_off and depth_keys are scratch; tile_count holds each splat's
+ * tile-box area (an upper bound of its hits: the ellipse-tile tests and the SH colours are evaluated chunk by chunk,
+ * only for splats whose box still holds a live tile). Overflow of the intersection buffers is reported like b2k_bin_sort's. */
 int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s);
 /* Scratch bytes b2k_project and b2k_bin_sort need in ctx->sort_tmp for a context whose per-splat buffers hold n_cap
  * entries (replaces RenderCtx::cub_tmp, src/gpu/render.h:80). */

@@ -43,12 +43,12 @@ def write_scene(path, scene, cam, gt, wts, lp):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", [0, 1])
-def test_host_harness_matches_oracle_and_reference_golden(mode, tmp_path):
+@pytest.mark.parametrize("mode,chunks", [(0, 1), (1, 1), (1, 3)])
+def test_host_harness_matches_oracle_and_reference_golden(mode, chunks, tmp_path):
     exe = build_harness()
     scene, cam, gt, wts, lp, z = load_gradcheck(mode)
     write_scene(tmp_path / "scene.bin", scene, cam, gt, wts, lp)
-    r = subprocess.run([exe, str(tmp_path / "scene.bin"), str(tmp_path / "out.bin")], capture_output=True, text=True)
+    r = subprocess.run([exe, str(tmp_path / "scene.bin"), str(tmp_path / "out.bin")] + ([str(chunks)] if chunks > 1 else []), capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     raw = open(tmp_path / "out.bin", "rb").read()
     loss = np.frombuffer(raw, np.float64, 1, 0)[0]
