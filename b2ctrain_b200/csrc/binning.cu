@@ -14,7 +14,6 @@
 //  * Sorting is LSD with 8-bit digits and is stable, so order = ascending (key, original position): exactly the
 //    order the reference's stable sorts define.
 #include "common.cuh"
-#include "sh.cuh"
 
 namespace b2k {
 namespace {
@@ -474,41 +473,38 @@ __global__ void chunk_prepare_kernel(const uint32_t* __restrict__ keys_sorted, i
 
 // Summed-area table of the tile-alive flags, (tiles_y + 1) x (tiles_x + 1) words with a zero first row and column:
 // "is any tile of this box still alive" becomes four loads, which lets the count and emit kernels drop a splat whose
-// whole tile box has died without walking its hit mask. One CTA: rows are scanned by warps, then columns by threads.
-__global__ void __launch_bounds__(1024) alive_sat_kernel(const uint32_t* __restrict__ alive, int tiles_x, int tiles_y, uint32_t* __restrict__ sat) {
-  const int SX = tiles_x + 1, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int x = threadIdx.x; x < SX; x += blockDim.x) sat[x] = 0u;
-  for (int y = warp; y < tiles_y; y += (int)(blockDim.x >> 5)) {
-    uint32_t carry = 0;
-    if (lane == 0) sat[(size_t)(y + 1) * SX] = 0u;
-    for (int x0 = 0; x0 < tiles_x; x0 += 32) {
-      const int x = x0 + lane;
-      uint32_t v = x < tiles_x ? (alive[(size_t)y * tiles_x + x] != 0u ? 1u : 0u) : 0u;
+// whole tile box has died without walking its hit mask. Two short launches: a warp per tile row scans along x, then a
+// thread per column accumulates down y (loads of a batch issued together, ahead of its stores).
+__global__ void __launch_bounds__(32) alive_sat_rows_kernel(const uint32_t* __restrict__ alive, int tiles_x, uint32_t* __restrict__ sat) {
+  const int SX = tiles_x + 1, lane = threadIdx.x, y = blockIdx.x;
+  if (y == 0) for (int x = lane; x < SX; x += 32) sat[x] = 0u;
+  if (lane == 0) sat[(size_t)(y + 1) * SX] = 0u;
+  uint32_t carry = 0;
+  for (int x0 = 0; x0 < tiles_x; x0 += 32) {
+    const int x = x0 + lane;
+    uint32_t v = x < tiles_x ? (alive[(size_t)y * tiles_x + x] != 0u ? 1u : 0u) : 0u;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
-      if (x < tiles_x) sat[(size_t)(y + 1) * SX + x + 1] = carry + v;
-      carry += __shfl_sync(0xffffffffu, v, 31);
-    }
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+    if (x < tiles_x) sat[(size_t)(y + 1) * SX + x + 1] = carry + v;
+    carry += __shfl_sync(0xffffffffu, v, 31);
   }
-  __syncthreads();
-  for (int x = threadIdx.x + 1; x < SX; x += blockDim.x) {
-    uint32_t run = 0;
-    for (int y0 = 1; y0 <= tiles_y; y0 += 16) {   // loads of a batch are issued together, ahead of its stores
-      uint32_t v[16];
+}
+__global__ void __launch_bounds__(128) alive_sat_cols_kernel(int tiles_x, int tiles_y, uint32_t* __restrict__ sat) {
+  const int SX = tiles_x + 1, x = blockIdx.x * blockDim.x + threadIdx.x + 1;
+  if (x >= SX) return;
+  uint32_t run = 0;
+  for (int y0 = 1; y0 <= tiles_y; y0 += 16) {
+    uint32_t v[16];
 #pragma unroll
-      for (int k = 0; k < 16; k++) v[k] = y0 + k <= tiles_y ? sat[(size_t)(y0 + k) * SX + x] : 0u;
+    for (int k = 0; k < 16; k++) v[k] = y0 + k <= tiles_y ? sat[(size_t)(y0 + k) * SX + x] : 0u;
 #pragma unroll
-      for (int k = 0; k < 16; k++) { run += v[k]; if (y0 + k <= tiles_y) sat[(size_t)(y0 + k) * SX + x] = run; }
-    }
+    for (int k = 0; k < 16; k++) { run += v[k]; if (y0 + k <= tiles_y) sat[(size_t)(y0 + k) * SX + x] = run; }
   }
 }
 
 __device__ __forceinline__ uint32_t box_alive(const uint32_t* __restrict__ sat, int SX, int x0, int y0, int x1, int y1) {
   return sat[(size_t)y1 * SX + x1] - sat[(size_t)y0 * SX + x1] - sat[(size_t)y1 * SX + x0] + sat[(size_t)y0 * SX + x0];
 }
-
-// What the lazily evaluated kernels need to shade a splat.
-struct ShadeArgs { const float4* pos; const float* sh_dc; const float* sh_hi; size_t cap; int active; float cam_pos[3]; };
 
 // Hit mask of a splat whose tile box holds at most 64 tiles: bit (row * width + col) set when the ellipse reaches the tile.
 __device__ __forceinline__ unsigned long long box_hit_mask(const TileRec& rec, int min_x, int min_y, int bw, int bh) {
@@ -573,12 +569,11 @@ __global__ void __launch_bounds__(256) chunk_filter_kernel(const uint32_t* __res
 }
 
 // Second step, one thread per listed masked-box splat: the ellipse-tile tests the projection left out, the count of
-// hits on live tiles, and for a splat that emits its hit mask (kept for the emission) and its colour.
-template <int DEG>
+// hits on live tiles, and for a splat that emits its hit mask (kept for the emission).
 __global__ void __launch_bounds__(256) chunk_mask_kernel(const uint32_t* __restrict__ live_list, const uint32_t* __restrict__ counts,
                                                          const uint32_t* __restrict__ order, uint4* __restrict__ hit_info, const float4* __restrict__ proj0,
-                                                         const float4* __restrict__ proj1, float4* __restrict__ proj2, ShadeArgs sa,
-                                                         const uint32_t* __restrict__ alive, int tiles_x, uint32_t* __restrict__ fcount) {
+                                                         const float4* __restrict__ proj1, const uint32_t* __restrict__ alive, int tiles_x,
+                                                         uint32_t* __restrict__ fcount) {
   const uint32_t count = counts[0];
   for (uint32_t e = blockIdx.x * blockDim.x + threadIdx.x; e < count; e += gridDim.x * blockDim.x) {
     const uint32_t r = live_list[e], i = order[r];
@@ -588,21 +583,16 @@ __global__ void __launch_bounds__(256) chunk_mask_kernel(const uint32_t* __restr
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
     const unsigned long long m = box_hit_mask(rec, (int)min_x, (int)min_y, (int)bw, (int)bh);
     const uint32_t f = alive_hits(m, bw, min_x, min_y, alive, tiles_x);
-    if (f) {
-      hit_info[i] = make_uint4((uint32_t)m, (uint32_t)(m >> 32), hi.z, hi.w);
-      const float4 p = sa.pos[i];
-      proj2[i] = splat_colour<DEG>((int)i, sa.cap, make_float3(p.x, p.y, p.z), sa.cam_pos, sa.active, sa.sh_dc, sa.sh_hi);
-    }
+    if (f) hit_info[i] = make_uint4((uint32_t)m, (uint32_t)(m >> 32), hi.z, hi.w);
     fcount[r] = f;
   }
 }
 
 // Second step for the listed big-box splats, one warp each: lanes sweep the box 32 tiles at a time.
-template <int DEG>
 __global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ counts,
                                                               const uint32_t* __restrict__ order, const uint4* __restrict__ hit_info,
-                                                              const float4* __restrict__ proj0, const float4* __restrict__ proj1, float4* __restrict__ proj2,
-                                                              ShadeArgs sa, int tiles_x, const uint32_t* __restrict__ alive, uint32_t* __restrict__ fcount) {
+                                                              const float4* __restrict__ proj0, const float4* __restrict__ proj1, int tiles_x,
+                                                              const uint32_t* __restrict__ alive, uint32_t* __restrict__ fcount) {
   const int lane = threadIdx.x & 31;
   const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = counts[1];
   for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
@@ -618,13 +608,7 @@ __global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __
       const bool hit = t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec);
       hits += __popc(__ballot_sync(0xffffffffu, hit));
     }
-    if (lane == 0) {
-      fcount[r] = hits;
-      if (hits) {
-        const float4 p = sa.pos[i];
-        proj2[i] = splat_colour<DEG>((int)i, sa.cap, make_float3(p.x, p.y, p.z), sa.cam_pos, sa.active, sa.sh_dc, sa.sh_hi);
-      }
-    }
+    if (lane == 0) fcount[r] = hits;
   }
 }
 
@@ -674,12 +658,16 @@ __global__ void __launch_bounds__(EMIT_THREADS) chunk_emit_kernel(
   const uint32_t len = emit_seg_len(r1 - r0, gridDim.x);
   const uint64_t begin = (uint64_t)r0 + (uint64_t)blockIdx.x * len;
   const uint64_t seg_end = (begin + len) < (uint64_t)r1 ? begin + len : (uint64_t)r1;
+  uint32_t cnt_nx = begin + tid < seg_end ? fcount[begin + tid] : 0u;   // counts are fetched one group ahead
   for (uint64_t q0 = begin; q0 < seg_end; q0 += EMIT_THREADS) {
     const uint64_t r = q0 + tid;
     const bool valid = r < seg_end;
-    uint32_t i = 0, cnt = 0;
+    const uint32_t cnt = cnt_nx;
+    cnt_nx = r + EMIT_THREADS < seg_end ? fcount[r + EMIT_THREADS] : 0u;
+    if (!__syncthreads_or(cnt != 0u)) continue;   // in the later chunks most groups of 256 ranks emit nothing at all
+    uint32_t i = 0;
     uint4 hi = make_uint4(0u, 0u, 0u, 0u);
-    if (valid) { cnt = fcount[r]; if (cnt) { i = order[r]; hi = hit_info[i]; } }
+    if (valid && cnt) { i = order[r]; hi = hit_info[i]; }
     uint32_t incl = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) { uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
@@ -876,25 +864,20 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
     }
   }
   const int emit_blocks = sm_count() * 4 > 1024 ? 1024 : sm_count() * 4;
-  ShadeArgs sa;
-  sa.pos = (const float4*)(o->pos_override ? o->pos_override : m->pos_op);
-  sa.sh_dc = m->sh_dc; sa.sh_hi = m->sh_hi; sa.cap = (size_t)m->cap;
-  sa.active = o->sh_degree < m->degree ? (o->sh_degree < 0 ? 0 : o->sh_degree) : m->degree;
-  for (int k = 0; k < 3; k++) sa.cam_pos[k] = cam->pos[k];
-#define B2K_CHUNK_DEG(deg, CALL) \
-  switch (deg) { case 0: { constexpr int D = 0; CALL; } break; case 1: { constexpr int D = 1; CALL; } break; case 2: { constexpr int D = 2; CALL; } break; \
-                 case 3: { constexpr int D = 3; CALL; } break; default: { constexpr int D = 4; CALL; } break; }
   for (int ch = 0; ch < C; ch++) {
     const int lo = ch == 0 ? 0 : 256 >> (2 * (C - ch)), hi = 256 >> (2 * (C - 1 - ch));
     const uint32_t* live = ch == 0 ? nullptr : alive;   // the first chunk meets only live tiles
     B2K_CUDA(cudaMemsetAsync(list_counts, 0, 2 * sizeof(uint32_t), s));
-    if (live) alive_sat_kernel<<<1, 1024, 0, s>>>(live, c->tiles_x, c->tiles_y, sat);
+    if (live) {
+      alive_sat_rows_kernel<<<c->tiles_y, 32, 0, s>>>(live, c->tiles_x, sat);
+      alive_sat_cols_kernel<<<div_up(c->tiles_x + 1, 128), 128, 0, s>>>(c->tiles_x, c->tiles_y, sat);
+    }
     chunk_filter_kernel<<<sm_count() * 8, 256, 0, s>>>(words, lo, hi, c->order, (const uint4*)c->hit_info, live ? sat : nullptr, c->tiles_x, fcount,
                                                        live_list, big_list, list_counts);
-    B2K_CHUNK_DEG(m->degree, (chunk_mask_kernel<D><<<sm_count() * 8, 256, 0, s>>>(live_list, list_counts, c->order, (uint4*)c->hit_info,
-        (const float4*)c->proj0, (const float4*)c->proj1, (float4*)c->proj2, sa, live, c->tiles_x, fcount)));
-    B2K_CHUNK_DEG(m->degree, (chunk_count_big_kernel<D><<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info,
-        (const float4*)c->proj0, (const float4*)c->proj1, (float4*)c->proj2, sa, c->tiles_x, live, fcount)));
+    chunk_mask_kernel<<<sm_count() * 8, 256, 0, s>>>(live_list, list_counts, c->order, (uint4*)c->hit_info, (const float4*)c->proj0,
+                                                     (const float4*)c->proj1, live, c->tiles_x, fcount);
+    chunk_count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info, (const float4*)c->proj0,
+                                                          (const float4*)c->proj1, c->tiles_x, live, fcount);
     chunk_sums_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(words, lo, hi, fcount, sc.block_sums);
     chunk_emit_kernel<<<emit_blocks, EMIT_THREADS, EMIT_SMEM, s>>>(words, ch, lo, hi, c->order, fcount, sc.block_sums, (const uint4*)c->hit_info, live,
                                                                    c->tiles_x, (uint32_t)c->isect_cap, big_start, ek, ev, c->num_isect);
@@ -909,7 +892,6 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
     st = launch_raster_fwd(c, o, ch, C, alive, s);
     if (st) return st;
   }
-#undef B2K_CHUNK_DEG
   return B2K_OK;
 }
 
