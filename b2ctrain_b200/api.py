@@ -46,12 +46,12 @@ class B2kCtx(C.Structure):
                 ("vals_sorted", C.c_void_p), ("isect_cap", C.c_uint64), ("num_isect", C.c_void_p), ("sort_tmp", C.c_void_p),
                 ("sort_tmp_bytes", C.c_uint64), ("tile_ranges", C.c_void_p), ("out_rgba", C.c_void_p), ("out_feat", C.c_void_p),
                 ("out_depth", C.c_void_p), ("last_idx", C.c_void_p), ("v_splat", C.c_void_p), ("vis_flag", C.c_void_p), ("vis_list", C.c_void_p),
-                ("v_out", C.c_void_p), ("loss_accum", C.c_void_p), ("n_chunks", C.c_int32), ("chunk_words", C.c_void_p)]
+                ("v_out", C.c_void_p), ("loss_accum", C.c_void_p), ("n_chunks", C.c_int32), ("proj3", C.c_void_p), ("chunk_words", C.c_void_p)]
 
 
 class B2kRenderOpts(C.Structure):
     _fields_ = [("bg", C.c_float * 3), ("sh_degree", C.c_int32), ("bwd_info", C.c_int32), ("pos_override", C.c_void_p),
-                ("quat_override", C.c_void_p), ("lscale_override", C.c_void_p)]
+                ("quat_override", C.c_void_p), ("lscale_override", C.c_void_p), ("feat_mode", C.c_int32), ("feat_buffer", C.c_void_p)]
 
 
 class B2kLoss(C.Structure):
@@ -254,6 +254,7 @@ class RenderCtx:
         f32 = lambda *s: torch.zeros(s, dtype=torch.float32, device=dev)
         if n > self.n_cap:
             self.proj0, self.proj1, self.proj2 = f32(n, 4), f32(n, 4), f32(n, 4)
+            self.proj3 = f32(n, 2)
             self.tile_count, self.tile_off = u32(n), u32(n)
             self.hit_info = u32(n, 4)
             self.depth_keys, self.depth_keys_sorted, self.order_in, self.order = u32(n), u32(n), u32(n), u32(n)
@@ -285,7 +286,7 @@ class RenderCtx:
             setattr(s, k, getattr(self, k))
         for k in ("proj0", "proj1", "proj2", "tile_count", "hit_info", "depth_keys", "depth_keys_sorted", "order_in", "order", "tile_off", "keys",
                   "vals", "keys_sorted", "vals_sorted", "sort_tmp", "tile_ranges", "out_rgba", "out_feat", "out_depth", "last_idx",
-                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum", "chunk_words"):
+                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum", "chunk_words", "proj3"):
             t = getattr(self, k, None)
             setattr(s, k, None if t is None else t.data_ptr())
         s.num_isect = self.d_num_isect.data_ptr()
@@ -296,21 +297,27 @@ class RenderCtx:
 
 
 class RenderParams:
-    """RenderParams (src/gpu/render.h:29-63). Lanes this library does not implement raise when set."""
-    _UNSUPPORTED = ("feat_buffer", "warp", "sh_frame", "app", "col_base", "hollow_z")
+    """RenderParams (src/gpu/render.h:29-63). Lanes this library does not implement raise when set. feat: "None",
+    "Normals" or "Buffer" (FeatureMode, render.h:27; forward only); feat_buffer: [n][3] device tensor for "Buffer"."""
+    _UNSUPPORTED = ("warp", "sh_frame", "app", "col_base", "hollow_z")
+    _FEAT = {"None": 0, "Normals": 1, "Buffer": 2}
 
     def __init__(self, cam, bg=(0.0, 0.0, 0.0), sh_degree=3, bwd_info=True):
         self.cam, self.bg, self.sh_degree, self.bwd_info = cam, tuple(bg), sh_degree, bwd_info
         self.feat = "None"
+        self.feat_buffer = None
         self.mip = False
         self.pos_override = self.quat_override = self.lscale_override = None
         for k in self._UNSUPPORTED:
             setattr(self, k, None)
 
     def struct(self):
-        if self.feat != "None" or self.mip or any(getattr(self, k) is not None for k in self._UNSUPPORTED):
-            raise RuntimeError("RenderParams: feature / mip / warp / sh_frame / app / hollow lanes are not implemented (unsupported lane)")
+        if self.mip or any(getattr(self, k) is not None for k in self._UNSUPPORTED):
+            raise RuntimeError("RenderParams: mip / warp / sh_frame / app / hollow lanes are not implemented (unsupported lane)")
+        if self.feat not in self._FEAT or (self.feat == "Buffer") != (self.feat_buffer is not None):
+            raise RuntimeError("RenderParams: feat is None, Normals or Buffer, and feat_buffer goes with Buffer")
         s = B2kRenderOpts()
+        s.feat_mode, s.feat_buffer = self._FEAT[self.feat], _ptr(self.feat_buffer)
         for i in range(3):
             s.bg[i] = float(self.bg[i])
         s.sh_degree, s.bwd_info = int(self.sh_degree), int(bool(self.bwd_info))

@@ -36,13 +36,35 @@ constexpr int PROJ_BLOCK = 256;
 // ones go to a list that a warp-per-splat kernel counts (and later emits) cooperatively.
 constexpr int MASK_TILES = 64;
 
+
+// Feature lanes of a splat (src/gpu/project.cu:62-77). Mode 1: pseudo-normal = the local axis of the shortest scale,
+// turned to face the camera, in camera space. Mode 2: the caller's per-splat buffer, clamped to +-100, non-finite -> 0.
+__device__ __forceinline__ float3 splat_feature(int mode, int i, const float4 po, const float4 ls, const float* Rq, const CamDev& cam,
+                                                const float* __restrict__ feat_in) {
+  if (mode == 1) {
+    const int axis = (ls.x <= ls.y && ls.x <= ls.z) ? 0 : (ls.y <= ls.z ? 1 : 2);
+    const float3 a = make_float3(Rq[axis], Rq[3 + axis], Rq[6 + axis]);
+    const float inv = 1.f / fmaxf(sqrtf(a.x * a.x + a.y * a.y + a.z * a.z), 1e-12f);
+    const float3 u = make_float3(a.x * inv, a.y * inv, a.z * inv);
+    const float face = ((cam.pos[0] - po.x) * u.x + (cam.pos[1] - po.y) * u.y + (cam.pos[2] - po.z) * u.z) >= 0.f ? 1.f : -1.f;
+    const float3 w = make_float3(u.x * face, u.y * face, u.z * face);
+    const float* R = cam.R;
+    return make_float3(R[0] * w.x + R[1] * w.y + R[2] * w.z, R[3] * w.x + R[4] * w.y + R[5] * w.z, R[6] * w.x + R[7] * w.y + R[8] * w.z);
+  }
+  float3 f = make_float3(feat_in[(size_t)i * 3], feat_in[(size_t)i * 3 + 1], feat_in[(size_t)i * 3 + 2]);
+  f.x = isfinite(f.x) ? fminf(fmaxf(f.x, -100.f), 100.f) : 0.f;
+  f.y = isfinite(f.y) ? fminf(fmaxf(f.y, -100.f), 100.f) : 0.f;
+  f.z = isfinite(f.z) ? fminf(fmaxf(f.z, -100.f), 100.f) : 0.f;
+  return f;
+}
+
 template <int DEG>
 __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
     int n, size_t cap, const float4* __restrict__ pos_op, const float4* __restrict__ quat, const float4* __restrict__ lscale,
     const float* __restrict__ sh_dc, const float* __restrict__ sh_hi, CamDev cam, int active, int tiles_x, int tiles_y,
     float4* __restrict__ proj0, float4* __restrict__ proj1, float4* __restrict__ proj2, uint32_t* __restrict__ tile_count,
     uint4* __restrict__ hit_info, uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen,
-    uint32_t* __restrict__ big_list, uint32_t* __restrict__ big_count) {
+    uint32_t* __restrict__ big_list, uint32_t* __restrict__ big_count, int feat_mode, const float* __restrict__ feat_in, float2* __restrict__ proj3) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float4 po = pos_op[i], q = quat[i], ls = lscale[i];
@@ -73,7 +95,13 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_kernel(
     proj0[i] = make_float4(pr.mx, pr.my, pr.c00, pr.c01);
     proj1[i] = make_float4(pr.c11, pr.opac, pr.mean_c.z, pr.power);
     if (shade) {
-      proj2[i] = splat_colour<DEG>(i, cap, make_float3(po.x, po.y, po.z), cam.pos, active, sh_dc, sh_hi);
+      float4 col = splat_colour<DEG>(i, cap, make_float3(po.x, po.y, po.z), cam.pos, active, sh_dc, sh_hi);
+      if (feat_mode != 0) {
+        const float3 f = splat_feature(feat_mode, i, po, ls, pr.Rq, cam, feat_in);
+        col.w = f.x;
+        proj3[i] = make_float2(f.y, f.z);
+      }
+      proj2[i] = col;
     }
   } else {
     proj1[i] = make_float4(0.f, 0.f, 0.f, -1.f);   // no record
@@ -206,7 +234,7 @@ int launch(const B2kModel* m, const CamDev& cam, const B2kRenderOpts* o, const B
   project_kernel<DEG><<<div_up(m->n, PROJ_BLOCK), PROJ_BLOCK, 0, s>>>(
       m->n, (size_t)m->cap, pos, quat, lscale, m->sh_dc, m->sh_hi, cam, active < 0 ? 0 : active, c->tiles_x, c->tiles_y,
       (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, (uint4*)c->hit_info, c->depth_keys_sorted, c->order, m->max_screen,
-      big_list, big_count);
+      big_list, big_count, o->feat_mode, o->feat_buffer, (float2*)c->proj3);
   count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, big_count, (const float4*)c->proj0, (const float4*)c->proj1, cam.W, cam.H, c->tiles_x,
                                                   c->tiles_y, c->tile_count, c->depth_keys_sorted);
   return check_launch();
@@ -238,6 +266,7 @@ extern "C" int b2k_project(const B2kModel* m, const B2kCamera* cam, const B2kRen
   B2K_REQUIRE(ctx->proj0 && ctx->proj1 && ctx->proj2 && ctx->tile_count && ctx->hit_info && ctx->depth_keys_sorted && ctx->order && ctx->sort_tmp);
   if (ctx->sort_tmp_bytes < b2k_sort_tmp_bytes(ctx->n_cap, ctx->isect_cap)) return B2K_ERR_CAPACITY;
   B2K_REQUIRE(cam->W == ctx->W && cam->H == ctx->H && ctx->tiles_x == div_up(ctx->W, RT_W) && ctx->tiles_y == div_up(ctx->H, RT_W));
+  B2K_REQUIRE(opts->feat_mode >= 0 && opts->feat_mode <= 2 && (opts->feat_mode == 0 || ctx->proj3) && (opts->feat_mode != 2 || opts->feat_buffer));
   if (ctx->n_cap < m->n) return B2K_ERR_CAPACITY;
   const CamDev cd = to_camdev(*cam);
   cudaStream_t st = (cudaStream_t)s;

@@ -21,12 +21,16 @@ constexpr int FWD_BATCH = 32;
 // whether any pixel of the tile can still take a fragment.
 constexpr uint32_t DONE_BIT = 0x80000000u;
 
-template <bool BWD, bool DEPTH, bool CHUNKED>
+template <bool BWD, bool DEPTH, bool CHUNKED, bool FEAT>
 __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, int W, int H, int tiles_x, int n_tiles, float3 bg, float4* __restrict__ out_rgba, float4* __restrict__ out_feat,
-    float* __restrict__ out_depth, uint32_t* __restrict__ last_idx, int chunk, int n_chunks, uint32_t* __restrict__ alive) {
+    float* __restrict__ out_depth, uint32_t* __restrict__ last_idx, int chunk, int n_chunks, uint32_t* __restrict__ alive,
+    const float2* __restrict__ proj3) {
+  static_assert(!(FEAT && CHUNKED), "the chunked forward keeps its colour sums where the feature lanes go");
   __shared__ float4 s0[FWD_WARPS][FWD_BATCH], s1[FWD_WARPS][FWD_BATCH], s2[FWD_WARPS][FWD_BATCH];
+  __shared__ float2 s3[FEAT ? FWD_WARPS : 1][FEAT ? FWD_BATCH : 1];
+  float f0[2] = {0.f, 0.f}, f1[2] = {0.f, 0.f}, f2[2] = {0.f, 0.f};   // composited feature lanes (raster_fwd.cu:52)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x * FWD_WARPS + warp;
   if (tile >= n_tiles) return;
@@ -61,6 +65,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     if ((uint32_t)lane < remaining) {
       const uint32_t gid = vals_sorted[start + lane];
       s0[warp][lane] = proj0[gid]; s1[warp][lane] = proj1[gid]; s2[warp][lane] = proj2[gid];
+      if constexpr (FEAT) s3[warp][lane] = proj3[gid];
     }
     __syncwarp();
     for (uint32_t t = 0; t < remaining; t++) {
@@ -84,6 +89,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
           const float vis = alpha * T[p];
           r[p] += cr * vis; g[p] += cg * vis; b[p] += cb * vis;
           if constexpr (DEPTH) zs[p] += vis * c.z;
+          if constexpr (FEAT) { const float2 fz = s3[warp][t]; f0[p] += col.w * vis; f1[p] += fz.x * vis; f2[p] += fz.y * vis; }
           T[p] = next_T;
           last[p] = start + t + 1;
         }
@@ -100,7 +106,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
         if constexpr (DEPTH) out_depth[pix] = !final ? zs[p] : ((1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY);
         last_idx[pix] = last[p] | (done[p] ? DONE_BIT : 0u);
       } else {
-        out_feat[pix] = make_float4(0.f, 0.f, 0.f, T[p]);
+        out_feat[pix] = make_float4(f0[p], f1[p], f2[p], T[p]);
         if constexpr (DEPTH) out_depth[pix] = (1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY;
         if constexpr (BWD) last_idx[pix] = last[p];
       }
@@ -130,15 +136,18 @@ namespace b2k {
 int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_chunks, uint32_t* alive, cudaStream_t s) {
   const float3 bg = make_float3(o->bg[0], o->bg[1], o->bg[2]);
   uint2* ranges = (uint2*)c->tile_ranges + (n_chunks > 1 ? (size_t)chunk * c->n_tiles : 0);
-#define L(B, D, C) raster_fwd_kernel<B, D, C><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>(ranges, c->vals_sorted, (const float4*)c->proj0, \
+#define L(B, D, C, F) raster_fwd_kernel<B, D, C, F><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>(ranges, c->vals_sorted, (const float4*)c->proj0, \
     (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, c->n_tiles, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx, \
-    chunk, n_chunks, alive)
+    chunk, n_chunks, alive, (const float2*)c->proj3)
   if (n_chunks > 1) {
-    if (o->bwd_info) { if (c->out_depth) L(true, true, true); else L(true, false, true); }
-    else { if (c->out_depth) L(false, true, true); else L(false, false, true); }
+    if (o->bwd_info) { if (c->out_depth) L(true, true, true, false); else L(true, false, true, false); }
+    else { if (c->out_depth) L(false, true, true, false); else L(false, false, true, false); }
+  } else if (o->feat_mode != 0) {
+    if (o->bwd_info) { if (c->out_depth) L(true, true, false, true); else L(true, false, false, true); }
+    else { if (c->out_depth) L(false, true, false, true); else L(false, false, false, true); }
   } else {
-    if (o->bwd_info) { if (c->out_depth) L(true, true, false); else L(true, false, false); }
-    else { if (c->out_depth) L(false, true, false); else L(false, false, false); }
+    if (o->bwd_info) { if (c->out_depth) L(true, true, false, false); else L(true, false, false, false); }
+    else { if (c->out_depth) L(false, true, false, false); else L(false, false, false, false); }
   }
 #undef L
   return check_launch();
@@ -149,5 +158,6 @@ extern "C" int b2k_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, b2k_strea
   B2K_REQUIRE(c && o && c->tile_ranges && c->vals_sorted && c->proj0 && c->proj1 && c->proj2 && c->out_rgba && c->out_feat);
   B2K_REQUIRE(!o->bwd_info || c->last_idx);
   B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y);
+  B2K_REQUIRE(o->feat_mode >= 0 && o->feat_mode <= 2 && (o->feat_mode == 0 || c->proj3));
   return launch_raster_fwd(c, o, 0, 1, nullptr, (cudaStream_t)stream);
 }

@@ -42,7 +42,7 @@ B2kCtx view_of(const RenderCtx& c) {
   v.out_rgba = (float*)c.out_rgba.ptr; v.out_feat = (float*)c.out_feat.ptr; v.out_depth = c.out_depth.ptr;
   v.last_idx = c.last_idx.ptr; v.v_splat = c.v_splat.ptr; v.vis_flag = c.vis_flag.ptr; v.vis_list = c.vis_list.ptr; v.v_out = (float*)c.v_out.ptr;
   v.loss_accum = c.loss_accum.ptr;
-  v.n_chunks = c.n_chunks; v.chunk_words = c.chunk_words.ptr;
+  v.n_chunks = c.n_chunks; v.chunk_words = c.chunk_words.ptr; v.proj3 = (float*)c.proj3.ptr;
   return v;
 }
 
@@ -54,11 +54,13 @@ B2kCamera camera_of(const CameraGPU& g) {
 }
 
 B2kRenderOpts opts_of(const RenderParams& p, const char* what) {
-  if (p.feat != FeatureMode::None || p.feat_buffer || p.mip || p.warp || p.sh_frame || p.app || p.col_base || p.hollow_z) unsupported(what);
+  if (p.mip || p.warp || p.sh_frame || p.app || p.col_base || p.hollow_z) unsupported(what);
+  if ((p.feat == FeatureMode::Buffer) != (p.feat_buffer != nullptr)) unsupported(what);
   B2kRenderOpts o{};
   for (int i = 0; i < 3; i++) o.bg[i] = p.bg[i];
   o.sh_degree = p.sh_degree; o.bwd_info = p.bwd_info ? 1 : 0;
   o.pos_override = (const float*)p.pos_override; o.quat_override = (const float*)p.quat_override; o.lscale_override = (const float*)p.lscale_override;
+  o.feat_mode = p.feat == FeatureMode::Normals ? 1 : (p.feat == FeatureMode::Buffer ? 2 : 0); o.feat_buffer = p.feat_buffer;
   return o;
 }
 
@@ -144,7 +146,7 @@ void RenderCtx::setup(int w, int h, int n, cudaStream_t stream) {
   tile_bits = 1; while ((1 << tile_bits) < n_tiles + 1) tile_bits++;
   const size_t nn = (size_t)(n > 0 ? n : 1);
   if ((int)nn > n_cap) {
-    proj0.reserve(nn); proj1.reserve(nn); proj2.reserve(nn); tile_count.reserve(nn); tile_off.reserve(nn); hit_info.reserve(nn);
+    proj0.reserve(nn); proj1.reserve(nn); proj2.reserve(nn); proj3.reserve(nn); tile_count.reserve(nn); tile_off.reserve(nn); hit_info.reserve(nn);
     depth_keys.reserve(nn); depth_keys_sorted.reserve(nn); order_in.reserve(nn); order.reserve(nn);
     v_splat.free(); v_splat.reserve(nn * 13); v_splat.zero(stream);   // later clears are the optimizer's job (render.cu:13-14)
     vis_flag.free(); vis_flag.reserve(nn); vis_flag.zero(stream);

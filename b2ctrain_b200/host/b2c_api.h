@@ -106,6 +106,7 @@ struct CameraGPU {
 enum class FeatureMode { None, Normals, Buffer };
 
 // src/gpu/render.h:29-63. Fields of lanes libb2k does not implement are kept so callers compile; setting them throws.
+// feat / feat_buffer are implemented in the forward only (out_feat.xyz); the chunked renderer rejects them.
 struct RenderParams {
   CameraGPU cam;
   float bg[3] = {0, 0, 0};
@@ -127,6 +128,7 @@ struct RenderParams {
 struct RenderCtx {
   int W = 0, H = 0, tiles_x = 0, tiles_y = 0, n_tiles = 0, tile_bits = 0, n_cap = 0;
   DevBuf<float4> proj0, proj1, proj2;
+  DevBuf<float2> proj3;              // feature lanes y, z (x rides in proj2.w)
   DevBuf<uint32_t> tile_count, tile_off;
   DevBuf<uint4> hit_info;
   DevBuf<uint32_t> depth_keys, depth_keys_sorted, order_in, order;

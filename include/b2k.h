@@ -60,7 +60,7 @@ typedef struct {
   int32_t n_cap;           /* per-splat buffers hold this many entries */
   float* proj0;            /* [n][4] mean2d x, y, conic c00, c01 */
   float* proj1;            /* [n][4] conic c11, opacity, view depth z, power = ln(255 opacity); power = -1: no record */
-  float* proj2;            /* [n][4] r, g, b, 0 */
+  float* proj2;            /* [n][4] r, g, b, feature x (0 without a feature mode) */
   uint32_t* tile_count;    /* [n] tiles hit */
   uint32_t* hit_info;      /* [n][4] bit mask (lo, hi) of the hit tiles inside the splat's tile box, row-major; packed box
                               min_x | min_y << 12 | width << 24; unused. Boxes above 64 tiles carry box = 0xFFFFFFFF and are
@@ -79,7 +79,7 @@ typedef struct {
   uint32_t* tile_ranges;   /* [n_tiles][2] start, end into vals_sorted; end shrunk by the forward when bwd_info
                               ([n_chunks][n_tiles][2] when n_chunks > 1) */
   float* out_rgba;         /* [P][4] */
-  float* out_feat;         /* [P][4] feature lanes x, y, z (zero: feature modes are not implemented), w = final transmittance */
+  float* out_feat;         /* [P][4] composited feature lanes x, y, z (zero without a feature mode), w = final transmittance */
   float* out_depth;        /* [P] expected depth, or NULL: sum(vis z) / alpha where alpha > 0.05 else +inf (the mean-depth
                               mode of probe_kernel, src/gpu/probe.cu:30-46, fused into the forward) */
   uint32_t* last_idx;      /* [P] one past the last contributing sorted index */
@@ -93,6 +93,7 @@ typedef struct {
   int32_t n_chunks;        /* 0 or 1: the view is binned whole, as the reference does. 2..5: b2k_render_chunked renders it
                               front to back in this many depth chunks; tile_ranges then holds [n_chunks][n_tiles][2] (one
                               range per chunk and tile, indices into vals_sorted) and b2k_raster_bwd walks them all */
+  float* proj3;            /* [n][2] feature lanes y, z (x rides in proj2.w), render.h:70; NULL unless a feature mode is used */
   uint32_t* chunk_words;   /* [32 + n_tiles + (tiles_x + 1)(tiles_y + 1)] device scratch of b2k_render_chunked (chunk windows
                               and counts, one "some pixel can still take a fragment" flag per tile, the summed-area table
                               of those flags), or NULL when n_chunks <= 1 */
@@ -106,6 +107,11 @@ typedef struct {
   const float* pos_override;        /* [n][4] or NULL (render.h:42) */
   const float* quat_override;       /* render.h:46 */
   const float* lscale_override;     /* render.h:47 */
+  int32_t feat_mode;                /* FeatureMode (render.h:27,33): 0 none, 1 pseudo-normals (shortest-scale axis, camera
+                                       facing, camera space; project.cu:63-72), 2 per-splat buffer (project.cu:73-77).
+                                       Forward only: the backward of the feature lanes is not implemented. Needs
+                                       ctx->proj3; not available with b2k_render_chunked */
+  const float* feat_buffer;         /* [n][3] when feat_mode == 2 (render.h:34) */
 } B2kRenderOpts;
 
 /* ViewGPU + LossParams, src/gpu/loss.h:7-30. */

@@ -82,6 +82,13 @@ void orc_raster_fwd(int W, int H, const double* geo, const double* col, const ui
                     uint32_t* tile_ranges, const double* bg, int bwd_info, double* out_rgba, double* out_T,
                     uint32_t* last_idx, double* out_depth);
 
+/* Feature lanes (FeatureMode, src/gpu/render.h:27; project.cu:62-77; raster_fwd.cu:52,62): per-splat features [n][3]
+ * (mode 1 pseudo-normals, mode 2 the caller's buffer), and their compositing with the walk of orc_raster_fwd. */
+void orc_features(int n, int mode, const float* pos_op, const float* quat, const float* lscale, const float* feat_buffer,
+                  const OrcCamera* cam, double* feat);
+void orc_raster_feat(int W, int H, const double* geo, const double* feat, const uint32_t* vals_sorted,
+                     const uint32_t* tile_ranges, double* out_feat);
+
 /* Fused L1 + 11-tap SSIM + alpha lane (loss.cu:18-195). pred: [P][4] doubles; gt: packed RGBA8 [P]; weights: [P] u8
  * or NULL. v_out: [P][4] dL/d(rgba) times grad_scale. Returns the loss. */
 double orc_loss(int W, int H, const double* pred, const uint32_t* gt, const uint8_t* weights, const OrcLoss* lp,

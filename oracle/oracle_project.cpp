@@ -194,3 +194,34 @@ extern "C" int orc_num_threads(void) {
   return 1;
 #endif
 }
+
+// Per-splat feature lanes (src/gpu/project.cu:62-77). mode 1: pseudo-normal = the local axis of the shortest log
+// scale, turned to face the camera, rotated into camera space; mode 2: feat_buffer clamped to +-100, non-finite -> 0.
+// feat: [n][3] doubles. Pinned through the reference's normal lane (tests/reference.cpp:67-75,132-140).
+extern "C" void orc_features(int n, int mode, const float* pos_op, const float* quat, const float* lscale, const float* feat_buffer,
+                             const OrcCamera* cam, double* feat) {
+#pragma omp parallel for
+  for (int i = 0; i < n; i++) {
+    double* f = feat + (size_t)i * 3;
+    if (mode == 1) {
+      const float* ls = lscale + (size_t)i * 4;
+      const int axis = (ls[0] <= ls[1] && ls[0] <= ls[2]) ? 0 : (ls[1] <= ls[2] ? 1 : 2);
+      double q[4] = {quat[(size_t)i * 4], quat[(size_t)i * 4 + 1], quat[(size_t)i * 4 + 2], quat[(size_t)i * 4 + 3]};
+      const double qn = std::sqrt(q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3]);
+      for (double& c : q) c /= qn;
+      double Rq[9];
+      orc::quat_to_mat(q, Rq);
+      const double a[3] = {Rq[axis], Rq[3 + axis], Rq[6 + axis]};
+      const double al = std::max(std::sqrt(a[0] * a[0] + a[1] * a[1] + a[2] * a[2]), 1e-12);
+      const double u[3] = {a[0] / al, a[1] / al, a[2] / al};
+      const float* p = pos_op + (size_t)i * 4;
+      const double face = ((cam->pos[0] - p[0]) * u[0] + (cam->pos[1] - p[1]) * u[1] + (cam->pos[2] - p[2]) * u[2]) >= 0 ? 1.0 : -1.0;
+      for (int r = 0; r < 3; r++) f[r] = face * (cam->R[r * 3] * u[0] + cam->R[r * 3 + 1] * u[1] + cam->R[r * 3 + 2] * u[2]);
+    } else {
+      for (int k = 0; k < 3; k++) {
+        const double v = mode == 2 ? (double)feat_buffer[(size_t)i * 3 + k] : 0.0;
+        f[k] = std::isfinite(v) ? std::min(std::max(v, -100.0), 100.0) : 0.0;
+      }
+    }
+  }
+}

@@ -57,6 +57,41 @@ extern "C" void orc_raster_fwd(int W, int H, const double* geo, const double* co
   }
 }
 
+// The feature lanes of the forward (src/gpu/raster_fwd.cu:52,62): the same walk as orc_raster_fwd, accumulating
+// feat * alpha * T with no clamp. tile_ranges as orc_bin left them (or shrunk: fragments past the shrunk end contribute
+// to no pixel). out_feat: [P][3].
+extern "C" void orc_raster_feat(int W, int H, const double* geo, const double* feat, const uint32_t* vals_sorted,
+                                const uint32_t* tile_ranges, double* out_feat) {
+  const int txn = tiles_x(W), tyn = tiles_y(H);
+#pragma omp parallel for schedule(dynamic, 4)
+  for (int tile = 0; tile < txn * tyn; tile++) {
+    const int tx = tile % txn, ty = tile / txn;
+    const uint32_t r0 = tile_ranges[tile * 2], r1 = tile_ranges[tile * 2 + 1];
+    for (int ly = 0; ly < TILE; ly++) for (int lx = 0; lx < TILE; lx++) {
+      const int px = tx * TILE + lx, py = ty * TILE + ly;
+      if (px >= W || py >= H) continue;
+      const double pcx = px + 0.5, pcy = py + 0.5;
+      double T = 1, f0 = 0, f1 = 0, f2 = 0;
+      for (uint32_t idx = r0; idx < r1; idx++) {
+        const uint32_t gid = vals_sorted[idx];
+        const Frag f = frag_of(geo, gid);
+        const double dx = pcx - f.mx, dy = pcy - f.my;
+        const double sigma = 0.5 * (f.c00 * dx * dx + f.c11 * dy * dy) + f.c01 * dx * dy;
+        if (sigma < 0 || sigma > f.power) continue;
+        const double alpha = std::min(ALPHA_MAX, f.opac * std::exp(-sigma));
+        const double next_T = T * (1 - alpha);
+        if (next_T <= T_CUTOFF) break;
+        const double vis = alpha * T;
+        const double* c = feat + (size_t)gid * 3;
+        f0 += c[0] * vis; f1 += c[1] * vis; f2 += c[2] * vis;
+        T = next_T;
+      }
+      const size_t pix = (size_t)py * W + px;
+      out_feat[pix * 3] = f0; out_feat[pix * 3 + 1] = f1; out_feat[pix * 3 + 2] = f2;
+    }
+  }
+}
+
 extern "C" void orc_raster_bwd(int n, int W, int H, const double* geo, const double* col, const uint32_t* vals_sorted,
                                const uint32_t* tile_ranges, const double* bg, const double* out_rgba, const double* out_T,
                                const uint32_t* last_idx, const double* v_out, double* v_splat, uint32_t* vis_flag,

@@ -166,6 +166,58 @@ def raster_fwd(W, H, geo, col, vals, ranges, bg, bwd_info=True, want_depth=False
     return rgba, T, last, ranges, depth
 
 
+def features(scene, cam, mode, feat_buffer=None):
+    """Per-splat feature lanes [n][3]: mode 1 pseudo-normals, mode 2 the caller's buffer (clamped)."""
+    n = scene["n"]
+    out = np.zeros((n, 3), np.float64)
+    cs = camera_struct(cam)
+    fb = None if feat_buffer is None else _f32(feat_buffer)
+    lib().orc_features(n, int(mode), _p(_f32(scene["pos_op"])), _p(_f32(scene["quat"])), _p(_f32(scene["lscale"])), _p(fb), C.byref(cs), _p(out))
+    return out
+
+
+def raster_feat(W, H, geo, feat, vals, ranges):
+    """Composited feature image [P][3] over the lists of bin_sort (same walk as raster_fwd)."""
+    out = np.zeros((W * H, 3), np.float64)
+    vals = _u32(vals) if len(vals) else np.zeros(1, np.uint32)
+    rng = np.ascontiguousarray(ranges, dtype=np.uint32)
+    lib().orc_raster_feat(W, H, _p(_f64(geo)), _p(_f64(feat)), _p(vals), _p(rng), _p(out))
+    return out
+
+
+def normal_loss_of(feat_img, gtn, weights, normal_scale):
+    """The reference's normal loss (src/gpu/loss.cu normal_loss_kernel; tests/reference.cpp:132-140) of a composited
+    feature image, in numpy: L1 + (1 - cosine) on the pixels whose packed target has alpha > 127."""
+    g = np.asarray(gtn, np.uint32)
+    on = ((g >> 24) & 0xFF) > 127
+    gx = (g & 0xFF) * (2.0 / 255.0) - 1.0
+    gy = 1.0 - ((g >> 8) & 0xFF) * (2.0 / 255.0)
+    gz = 1.0 - ((g >> 16) & 0xFF) * (2.0 / 255.0)
+    wp = np.ones(len(g)) if weights is None else np.asarray(weights, np.float64) / 255.0
+    px, py, pz = feat_img[:, 0], feat_img[:, 1], feat_img[:, 2]
+    pl = np.maximum(np.sqrt(px * px + py * py + pz * pz), 1e-6)
+    gl = np.maximum(np.sqrt(gx * gx + gy * gy + gz * gz), 1e-6)
+    per = normal_scale * wp * (np.abs(px - gx) + np.abs(py - gy) + np.abs(pz - gz) + 1.0 - (px * gx + py * gy + pz * gz) / (pl * gl))
+    return float(per[on].sum())
+
+
+def reference_loss_normals(scene, cam, bg, gt, gtn, weights, normal_scale, l1_w=0.0, ssim_w=0.0, scale=1.0):
+    """The reference's `reference_loss` with its normal lane on (pseudo-normal features)."""
+    r = ref_lib()
+    if r is None or not hasattr(r, "ref_reference_loss_normals"):
+        return None
+    n, deg = scene["n"], scene["degree"]
+    assert deg <= 3 and not np.any(scene["lscale"][:, 3] != 0)
+    pos = _f32(scene["pos_op"][:, :3]); opac = _f32(scene["pos_op"][:, 3]); ls = _f32(scene["lscale"][:, :3])
+    intr = np.array([cam["fx"], cam["fy"], cam["cx"], cam["cy"]], np.float32)
+    w = None if weights is None else np.ascontiguousarray(weights, dtype=np.uint8)
+    d = C.c_double
+    r.ref_reference_loss_normals.restype = C.c_double
+    return r.ref_reference_loss_normals(n, deg, _p(pos), _p(ls), _p(_f32(scene["quat"])), _p(opac), _p(_f32(scene["sh"])), int(cam["W"]), int(cam["H"]),
+                                        _p(intr), _p(_f32(cam["R"])), _p(_f32(cam["t"])), _p(_f32(cam["pos"])), _p(_f64(bg)), d(l1_w), d(ssim_w),
+                                        d(scale), _p(_u32(gt)), _p(_u32(gtn)), d(normal_scale), _p(w))
+
+
 def loss(W, H, pred, gt, weights, lp, want_grad=True):
     pred = _f64(pred)
     v_out = np.zeros((W * H, 4)) if want_grad else None

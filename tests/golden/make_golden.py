@@ -77,11 +77,32 @@ def config0_fixture():
     return dict(ref_loss=ref, gt=gt)
 
 
+def normals_fixture():
+    """The reference's normal lane (tests/reference.cpp:67-75,132-140; gradient-test mode `normals`, tests/tests.cpp:399):
+    its loss with the photometric weights at zero is a function of the composited pseudo-normal image alone."""
+    scene, cam, gt, wts = scenes.gradcheck_scene(1234 + 2)
+    rng = np.random.Generator(np.random.PCG64(99))
+    P = cam["W"] * cam["H"]
+    gtn = rng.integers(0, 2 ** 32, P, dtype=np.uint64).astype(np.uint32)   # about half of the pixels carry alpha > 127
+    bg = np.array([0.2, 0.1, 0.3])
+    scale = 0.05 / 100.0
+    out = dict(gtn=gtn, wts=wts, normal_scale=scale,
+               ref_normal_loss=orc.reference_loss_normals(scene, cam, bg, gt, gtn, None, scale),
+               ref_normal_loss_weighted=orc.reference_loss_normals(scene, cam, bg, gt, gtn, wts, scale))
+    return out
+
+
 if __name__ == "__main__":
     assert orc.ref_lib() is not None, "oracle/_ref/libref.so is missing: run `make -C oracle` where the reference tree exists"
     here = os.path.dirname(os.path.abspath(__file__))
+    only = sys.argv[1:]   # e.g. `make_golden.py normals` regenerates one fixture
     for mode in range(3):
-        np.savez_compressed(os.path.join(here, f"gradcheck_mode{mode}.npz"), **gradcheck_fixture(mode))
-        print("wrote gradcheck mode", mode)
-    np.savez_compressed(os.path.join(here, "config0.npz"), **config0_fixture())
-    print("wrote config0")
+        if not only or f"gradcheck{mode}" in only:
+            np.savez_compressed(os.path.join(here, f"gradcheck_mode{mode}.npz"), **gradcheck_fixture(mode))
+            print("wrote gradcheck mode", mode)
+    if not only or "config0" in only:
+        np.savez_compressed(os.path.join(here, "config0.npz"), **config0_fixture())
+        print("wrote config0")
+    if not only or "normals" in only:
+        np.savez_compressed(os.path.join(here, "normals.npz"), **normals_fixture())
+        print("wrote normals")

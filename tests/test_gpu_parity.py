@@ -439,3 +439,39 @@ def test_chunked_front_to_back_render_matches_whole_view_binning(n_chunks):
     # the ranges the backward walks are never longer than in the whole-view binning (a chunk's unused tail is dropped)
     walked = int((b["ranges"][:, :, 1].astype(np.int64) - b["ranges"][:, :, 0]).clip(min=0).sum())
     assert 0 < walked <= int((a["ranges"][0, :, 1].astype(np.int64) - a["ranges"][0, :, 0]).sum())
+
+
+@pytest.mark.parametrize("mode", ["Normals", "Buffer"])
+def test_forward_feature_lanes_match_oracle(mode):
+    """FeatureMode::Normals / Buffer in the forward (project.cu:62-77, raster_fwd.cu:52,62): out_feat.xyz against the
+    oracle's feature compositing (itself pinned on the reference's normal lane), colour image unchanged."""
+    import torch
+    from b2ctrain_b200 import api
+    scene, cam = small_scene(n=3000, degree=2, seed=33)
+    n, W, H = scene["n"], cam["W"], cam["H"]
+    m = api.Model("cuda:0").upload(scene)
+    ctx = api.RenderCtx("cuda:0"); ctx.setup(W, H, m.cap)
+    rng = np.random.Generator(np.random.PCG64(8))
+    buf = rng.normal(0, 60, (n, 3)).astype(np.float32); buf[5, 1] = np.inf
+    rp = api.RenderParams(cam, bg=(0.1, 0.2, 0.3), sh_degree=2, bwd_info=True)
+    api.render_forward(ctx, m, rp, sync=True)
+    plain = ctx.out_rgba.cpu().numpy().copy()
+    assert float(ctx.out_feat[:, :3].abs().max()) == 0.0
+    rp.feat = mode
+    if mode == "Buffer":
+        rp.feat_buffer = torch.from_numpy(buf).cuda()
+    api.render_forward(ctx, m, rp, sync=True)
+    assert np.array_equal(ctx.out_rgba.cpu().numpy(), plain)
+    got = ctx.out_feat[:, :3].cpu().numpy()
+    rec = orc.project(scene, cam)
+    p0, p1 = orc.records_to_proj(rec)
+    tc, vals, keys, ranges = orc.bin_sort(p0, p1, W, H)
+    feat = orc.features(scene, cam, 1 if mode == "Normals" else 2, buf)
+    want = orc.raster_feat(W, H, np.ascontiguousarray(rec[:, :8]), feat, vals, ranges)
+    tol = TOL_IMAGE_ABS * (1.0 if mode == "Normals" else 100.0)   # buffer values reach +-100
+    assert np.max(np.abs(got - want)) <= tol
+    assert np.abs(want).max() > 0.5
+    # the chunked renderer says so instead of rendering without the lane
+    ctx2 = api.RenderCtx("cuda:0"); ctx2.setup(W, H, m.cap, n_chunks=3)
+    with pytest.raises(RuntimeError, match="unsupported lane"):
+        api.render_forward(ctx2, m, rp, sync=True)

@@ -118,3 +118,30 @@ def test_min_scale_matches_numpy():
     want = scenes.floor_for_cameras(scene, cams)["lscale"][:, 3]
     got = orc.min_scale(scene["pos_op"], scene["lscale"], np.stack([c["pos"] for c in cams]), np.array([64.0] * 3))[:, 3]
     assert np.allclose(got, want, rtol=1e-5)
+
+
+def test_feature_lanes_match_the_reference_normal_lane():
+    """Pseudo-normal features composited by the oracle reproduce the reference's normal loss (tests/reference.cpp:67-75,
+    132-140; fixture tests/golden/normals.npz): that loss, with the photometric weights at zero, is a function of the
+    composited feature image alone."""
+    import os
+    from tests.util import GOLDEN, load_gradcheck
+    scene, cam, gt, wts, lp, _ = load_gradcheck(2)
+    z = np.load(os.path.join(GOLDEN, "normals.npz"))
+    W, H = cam["W"], cam["H"]
+    rec = orc.project(scene, cam)
+    p0, p1 = orc.records_to_proj(rec)
+    tc, vals, keys, ranges = orc.bin_sort(p0, p1, W, H)
+    feat = orc.features(scene, cam, 1)
+    assert np.allclose(np.linalg.norm(feat, axis=1), 1.0, atol=1e-6)
+    img = orc.raster_feat(W, H, np.ascontiguousarray(rec[:, :8]), feat, vals, ranges)
+    scale = float(z["normal_scale"])
+    assert abs(orc.normal_loss_of(img, z["gtn"], None, scale) - float(z["ref_normal_loss"])) <= 1e-9 * abs(float(z["ref_normal_loss"]))
+    assert abs(orc.normal_loss_of(img, z["gtn"], z["wts"], scale) - float(z["ref_normal_loss_weighted"])) <= 1e-9 * abs(float(z["ref_normal_loss_weighted"]))
+    if orc.ref_lib() is not None:   # where the reference was built: the live call agrees with the stored value
+        live = orc.reference_loss_normals(scene, cam, np.array([0.2, 0.1, 0.3]), gt, z["gtn"], None, scale)
+        assert live is None or abs(live - float(z["ref_normal_loss"])) <= 1e-12
+    # buffer mode: clamped copy of the caller's values, non-finite -> 0
+    buf = np.array([[1.0, -200.0, np.nan]] * scene["n"], np.float32)
+    fb = orc.features(scene, cam, 2, buf)
+    assert np.array_equal(fb[0], [1.0, -100.0, 0.0])
