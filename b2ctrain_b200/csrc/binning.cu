@@ -516,19 +516,19 @@ __device__ __forceinline__ unsigned long long box_hit_mask(const TileRec& rec, i
   return m;
 }
 
-// Hits of a mask that fall on live tiles (alive == nullptr: all of them).
-__device__ __forceinline__ uint32_t alive_hits(unsigned long long bits, uint32_t bw, uint32_t min_x, uint32_t min_y, const uint32_t* __restrict__ alive,
-                                               int tiles_x) {
-  if (!alive) return (uint32_t)__popcll(bits);
+// The hits of a mask that fall on live tiles (alive == nullptr: all of them).
+__device__ __forceinline__ unsigned long long alive_mask(unsigned long long bits, uint32_t bw, uint32_t min_x, uint32_t min_y,
+                                                         const uint32_t* __restrict__ alive, int tiles_x) {
+  if (!alive) return bits;
   const uint32_t inv_bw = bw ? (65536u + bw - 1u) / bw : 0u;
-  uint32_t f = 0;
+  unsigned long long keep = 0ull;
   while (bits != 0ull) {
     const uint32_t bit = (uint32_t)__ffsll((long long)bits) - 1u;
     bits &= bits - 1ull;
     const uint32_t row = (bit * inv_bw) >> 16, col = bit - row * bw;
-    f += alive[(min_y + row) * (uint32_t)tiles_x + min_x + col] != 0u;
+    if (alive[(min_y + row) * (uint32_t)tiles_x + min_x + col] != 0u) keep |= 1ull << bit;
   }
-  return f;
+  return keep;
 }
 
 // First step of a chunk's count, one thread per rank: a splat whose tile box is empty, or holds no live tile (four
@@ -581,8 +581,9 @@ __global__ void __launch_bounds__(256) chunk_mask_kernel(const uint32_t* __restr
     const uint32_t bw = hi.z >> 24, min_x = hi.z & 0xFFFu, min_y = (hi.z >> 12) & 0xFFFu, bh = hi.w;
     const float4 a = proj0[i], b = proj1[i];
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
-    const unsigned long long m = box_hit_mask(rec, (int)min_x, (int)min_y, (int)bw, (int)bh);
-    const uint32_t f = alive_hits(m, bw, min_x, min_y, alive, tiles_x);
+    // The mask kept for the emission holds the hits on live tiles only: the emission then needs no flag lookups.
+    const unsigned long long m = alive_mask(box_hit_mask(rec, (int)min_x, (int)min_y, (int)bw, (int)bh), bw, min_x, min_y, alive, tiles_x);
+    const uint32_t f = (uint32_t)__popcll(m);
     if (f) hit_info[i] = make_uint4((uint32_t)m, (uint32_t)(m >> 32), hi.z, hi.w);
     fcount[r] = f;
   }
@@ -628,12 +629,13 @@ __global__ void __launch_bounds__(EMIT_THREADS) chunk_sums_kernel(const uint32_t
   if (threadIdx.x == 0) { uint32_t t = 0; for (int w = 0; w < EMIT_THREADS / 32; w++) t += s_red[w]; block_sums[blockIdx.x] = t; }
 }
 
-// scan_emit_kernel for one chunk: counts come from fcount, dead tiles are skipped, slots start at the chunk's window.
+// scan_emit_kernel for one chunk: counts come from fcount, the stored masks hold live tiles only, slots start at the
+// chunk's window.
 // The last block records the chunk's pair count, the next window's first slot (rounded up to 32 so that the sort's
 // vector loads stay aligned) and the running total of the view.
 __global__ void __launch_bounds__(EMIT_THREADS) chunk_emit_kernel(
     uint32_t* __restrict__ words, int chunk, int lo_num, int hi_num, const uint32_t* __restrict__ order, const uint32_t* __restrict__ fcount,
-    const uint32_t* __restrict__ block_sums, const uint4* __restrict__ hit_info, const uint32_t* __restrict__ alive, int tiles_x, uint32_t cap,
+    const uint32_t* __restrict__ block_sums, const uint4* __restrict__ hit_info, int tiles_x, uint32_t cap,
     uint32_t* __restrict__ big_start, uint32_t* __restrict__ keys, uint32_t* __restrict__ vals, uint32_t* __restrict__ num_isect) {
   __shared__ uint32_t s_warp[EMIT_THREADS / 32];
   __shared__ uint32_t s_base;
@@ -692,8 +694,7 @@ __global__ void __launch_bounds__(EMIT_THREADS) chunk_emit_kernel(
         const uint32_t bit = (uint32_t)__ffsll((long long)bits) - 1u;
         bits &= bits - 1ull;
         const uint32_t row = (bit * inv_bw) >> 16, col = bit - row * bw;
-        const uint32_t tile = (min_y + row) * (uint32_t)tiles_x + min_x + col;
-        if (alive && alive[tile] == 0u) continue;
+        const uint32_t tile = (min_y + row) * (uint32_t)tiles_x + min_x + col;   // the stored mask holds live tiles only
         wk[cur - w0] = tile;
         wv[cur - w0] = i;
         cur++;
@@ -880,7 +881,7 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
     chunk_count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info, (const float4*)c->proj0,
                                                           (const float4*)c->proj1, c->tiles_x, live, fcount);
     chunk_sums_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(words, lo, hi, fcount, sc.block_sums);
-    chunk_emit_kernel<<<emit_blocks, EMIT_THREADS, EMIT_SMEM, s>>>(words, ch, lo, hi, c->order, fcount, sc.block_sums, (const uint4*)c->hit_info, live,
+    chunk_emit_kernel<<<emit_blocks, EMIT_THREADS, EMIT_SMEM, s>>>(words, ch, lo, hi, c->order, fcount, sc.block_sums, (const uint4*)c->hit_info,
                                                                    c->tiles_x, (uint32_t)c->isect_cap, big_start, ek, ev, c->num_isect);
     chunk_emit_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info, fcount, big_start,
                                                          (const float4*)c->proj0, (const float4*)c->proj1, c->tiles_x, live, (uint32_t)c->isect_cap, ek, ev);
