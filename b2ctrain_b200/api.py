@@ -90,6 +90,9 @@ SIGNATURES = {
     "b2k_adam": (C.c_int, [_P, _P, _P, _S]),
     "b2k_adam_range": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _S]),
     "b2k_min_scale": (C.c_int, [_P, _P, _P, C.c_int32, _S]),
+    "b2k_select_tmp_words": (C.c_uint64, [C.c_int32]),
+    "b2k_select_flagged": (C.c_int, [_P, C.c_int32, _P, _P, _P, _S]),
+    "b2k_gather_lanes": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_uint64, C.c_int32, _S]),
     "b2k_pack_rgba8": (C.c_int, [_P, _P, C.c_int32, C.c_int32, _S]),
     "b2k_error_string": (C.c_char_p, [C.c_int]),
     "b2k_last_cuda_error": (C.c_int, []),
@@ -211,6 +214,38 @@ class Model:
         planar = torch.cat([self.sh_dc, self.sh_hi], 0)[:, :n]
         return dict(n=n, degree=self.degree, pos_op=self.pos_op[:n].cpu().numpy(), quat=self.quat[:n].cpu().numpy(),
                     lscale=self.lscale[:n].cpu().numpy(), sh=planar.t().reshape(n, K, 3).contiguous().cpu().numpy())
+
+    def compact(self, keep, extras=(), stream=None):
+        """Model::compact (src/model.cu:120-155): keeps the splats whose flag in `keep` (device int32 [n]) is non-zero,
+        in their order, across parameters, moments, statistics and the caller's extra per-splat float tensors (each
+        [cap], replaced in the returned list). Returns (new n, extras). Synchronises for the count, like the reference."""
+        if self.n == 0:
+            return 0, list(extras)
+        n, cap, dev = self.n, self.cap, self.device
+        idx = torch.zeros(n, dtype=torch.int32, device=dev)
+        cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+        tmp = torch.zeros(int(lib().b2k_select_tmp_words(n)), dtype=torch.int32, device=dev)
+        _check(lib().b2k_select_flagged(_ptr(keep), n, _ptr(idx), _ptr(cnt), _ptr(tmp), _stream(stream)), "Model.compact")
+        kept = int(cnt.item())
+        if kept == n:
+            return n, list(extras)
+
+        def gather(t, lanes, elem_bytes):
+            if t is None or t.numel() == 0 or lanes == 0:
+                return t
+            fresh = torch.zeros_like(t)   # an in-place gather would race
+            _check(lib().b2k_gather_lanes(_ptr(t), _ptr(fresh), _ptr(idx), kept, lanes, cap, elem_bytes, _stream(stream)), "Model.compact")
+            return fresh
+
+        hi_lanes = 3 * (self.K() - 1)
+        for k in ("pos_op", "quat", "lscale", "m_pos_op", "v_pos_op", "m_quat", "v_quat", "m_lscale", "v_lscale"):
+            setattr(self, k, gather(getattr(self, k), 1, 16))
+        for k, lanes in (("sh_dc", 3), ("sh_hi", hi_lanes), ("m_sh_dc", 3), ("m_sh_hi", hi_lanes), ("v_sh", 1), ("refine_norm", 1),
+                         ("max_screen", 1), ("vis_count", 1), ("vis_weight", 1), ("last_step", 1)):
+            setattr(self, k, gather(getattr(self, k), lanes, 4))
+        out = [gather(e, 1, 4) for e in extras]
+        self.n = kept
+        return kept, out
 
     def sh_planar_to_host(self, dc, hi):
         n, K = self.n, self.K()

@@ -545,6 +545,71 @@ __global__ void pack_rgba8_kernel(int n, const float4* __restrict__ img, uint32_
   out[i] = r | (g << 8) | (b << 16) | (a << 24);
 }
 
+
+// ---- Model::compact (src/model.cu:110-155): stable selection of the kept splats, then a gather of every array ----
+constexpr int SEL_BLOCK = 1024;
+
+// Kept entries per block of 1024.
+__global__ void __launch_bounds__(SEL_BLOCK) select_count_kernel(int n, const uint32_t* __restrict__ keep, uint32_t* __restrict__ block_counts) {
+  const int i = blockIdx.x * SEL_BLOCK + threadIdx.x;
+  const int c = __syncthreads_count(i < n && keep[i] != 0u);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)c;
+}
+// Exclusive scan of the block counts in place (one CTA), total to *count.
+__global__ void __launch_bounds__(1024) select_scan_kernel(int blocks, uint32_t* __restrict__ block_counts, uint32_t* __restrict__ count) {
+  __shared__ uint32_t s_warp[32];
+  __shared__ uint32_t s_carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_carry = 0u;
+  __syncthreads();
+  for (int b0 = 0; b0 < blocks; b0 += 1024) {
+    const int b = b0 + threadIdx.x;
+    const uint32_t v = b < blocks ? block_counts[b] : 0u;
+    uint32_t incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t pre = 0;
+    for (int w = 0; w < warp; w++) pre += s_warp[w];
+    const uint32_t carry = s_carry;
+    if (b < blocks) block_counts[b] = carry + pre + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) s_carry = carry + pre + incl;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *count = s_carry;
+}
+// idx[slot] = i for the kept i, in ascending order.
+__global__ void __launch_bounds__(SEL_BLOCK) select_write_kernel(int n, const uint32_t* __restrict__ keep, const uint32_t* __restrict__ block_offsets,
+                                                                 uint32_t* __restrict__ idx) {
+  __shared__ uint32_t s_warp[SEL_BLOCK / 32];
+  const int i = blockIdx.x * SEL_BLOCK + threadIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool on = i < n && keep[i] != 0u;
+  const uint32_t m = __ballot_sync(0xffffffffu, on);
+  if (lane == 0) s_warp[warp] = (uint32_t)__popc(m);
+  __syncthreads();
+  uint32_t pre = block_offsets[blockIdx.x];
+  for (int w = 0; w < warp; w++) pre += s_warp[w];
+  if (on) idx[pre + __popc(m & ((1u << lane) - 1u))] = (uint32_t)i;
+}
+// dst[l * stride + j] = src[l * stride + idx[j]] for every lane l (gather_kernel, src/model.cu:112-118), elements of
+// WORDS 32-bit words.
+template <int WORDS>
+__global__ void gather_lanes_kernel(int count, int lanes, size_t stride, const uint32_t* __restrict__ idx, const uint32_t* __restrict__ src,
+                                    uint32_t* __restrict__ dst) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= count) return;
+  const uint32_t i = idx[j];
+  for (int l = 0; l < lanes; l++) {
+    if constexpr (WORDS == 4) {
+      reinterpret_cast<uint4*>(dst)[(size_t)l * stride + j] = reinterpret_cast<const uint4*>(src)[(size_t)l * stride + i];
+    } else {
+      dst[(size_t)l * stride + j] = src[(size_t)l * stride + i];
+    }
+  }
+}
+
 }  // namespace
 }  // namespace b2k
 
@@ -619,5 +684,29 @@ extern "C" int b2k_pack_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels
   B2K_REQUIRE(rgba && out && n_pixels >= 0 && alpha_override <= 255);
   if (n_pixels == 0) return B2K_OK;
   pack_rgba8_kernel<<<div_up(n_pixels, 256), 256, 0, (cudaStream_t)stream>>>(n_pixels, (const float4*)rgba, out, alpha_override);
+  return check_launch();
+}
+
+extern "C" uint64_t b2k_select_tmp_words(int32_t n) { return (uint64_t)(n > 0 ? div_up(n, SEL_BLOCK) : 0) + 1u; }
+
+extern "C" int b2k_select_flagged(const uint32_t* keep, int32_t n, uint32_t* idx, uint32_t* count, uint32_t* tmp, b2k_stream_t stream) {
+  B2K_REQUIRE(n >= 0 && count && (n == 0 || (keep && idx && tmp)));
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n == 0) { B2K_CUDA(cudaMemsetAsync(count, 0, sizeof(uint32_t), s)); return B2K_OK; }
+  const int blocks = div_up(n, SEL_BLOCK);
+  select_count_kernel<<<blocks, SEL_BLOCK, 0, s>>>(n, keep, tmp);
+  select_scan_kernel<<<1, 1024, 0, s>>>(blocks, tmp, count);
+  select_write_kernel<<<blocks, SEL_BLOCK, 0, s>>>(n, keep, tmp, idx);
+  return check_launch();
+}
+
+extern "C" int b2k_gather_lanes(const void* src, void* dst, const uint32_t* idx, int32_t count, int32_t lanes, uint64_t stride, int32_t elem_bytes,
+                                b2k_stream_t stream) {
+  B2K_REQUIRE(count >= 0 && lanes >= 0 && (elem_bytes == 4 || elem_bytes == 16) && src != dst);
+  if (count == 0 || lanes == 0) return B2K_OK;
+  B2K_REQUIRE(src && dst && idx && stride >= (uint64_t)count);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (elem_bytes == 16) gather_lanes_kernel<4><<<div_up(count, 256), 256, 0, s>>>(count, lanes, (size_t)stride, idx, (const uint32_t*)src, (uint32_t*)dst);
+  else gather_lanes_kernel<1><<<div_up(count, 256), 256, 0, s>>>(count, lanes, (size_t)stride, idx, (const uint32_t*)src, (uint32_t*)dst);
   return check_launch();
 }

@@ -1,6 +1,7 @@
 // Bodies of the reference-named operators over the C ABI (include/b2k.h). Each function fills POD views of the
 // caller's objects and makes one b2k_* call; see the header for the interfaces mirrored.
 #include "b2c_api.h"
+#include <type_traits>
 #include "../../include/b2k.h"
 #include <cstring>
 
@@ -140,6 +141,31 @@ void Model::zero_optimizer(cudaStream_t stream) {
   m_sh_dc.zero(stream); m_sh_hi32.zero(stream); v_sh.zero(stream); last_step.zero(stream); adam_t = 0;
 }
 void Model::zero_stats(cudaStream_t stream) { refine_norm.zero(stream); max_screen.zero(stream); vis_count.zero(stream); vis_weight.zero(stream); }
+
+int Model::compact(const uint32_t* keep, const std::vector<DevBuf<float>*>& extras, cudaStream_t stream) {
+  if (n == 0) return 0;
+  DevBuf<uint32_t> idx, cnt, tmp;
+  idx.reserve((size_t)n); cnt.reserve(1); tmp.reserve((size_t)b2k_select_tmp_words(n));
+  check(b2k_select_flagged(keep, n, idx.ptr, cnt.ptr, tmp.ptr, stream), "Model::compact");
+  const uint32_t kept = cnt.download(1, stream)[0];
+  if ((int)kept == n) return n;
+  const int hi_lanes = (K() - 1) * 3;
+  auto gather = [&](auto& b, int lanes) {   // into a fresh buffer of the same capacity, which then replaces the old
+    using T = std::remove_reference_t<decltype(*b.ptr)>;
+    if (!b.ptr || lanes == 0) return;
+    DevBuf<T> nb; nb.reserve(b.count); nb.zero(stream);
+    check(b2k_gather_lanes(b.ptr, nb.ptr, idx.ptr, (int)kept, lanes, (uint64_t)cap, (int)sizeof(T), stream), "Model::compact");
+    B2C_CUDA_CHECK(cudaStreamSynchronize(stream));
+    b = std::move(nb);
+  };
+  gather(pos_op, 1); gather(quat, 1); gather(lscale, 1); gather(sh_dc, 3); gather(sh_hi32, hi_lanes);
+  gather(m_pos_op, 1); gather(v_pos_op, 1); gather(m_quat, 1); gather(v_quat, 1); gather(m_lscale, 1); gather(v_lscale, 1);
+  gather(m_sh_dc, 3); gather(m_sh_hi32, hi_lanes); gather(v_sh, 1);
+  gather(refine_norm, 1); gather(max_screen, 1); gather(vis_count, 1); gather(vis_weight, 1); gather(last_step, 1);
+  for (DevBuf<float>* e : extras) gather(*e, 1);
+  n = (int)kept;
+  return n;
+}
 
 void RenderCtx::setup(int w, int h, int n, cudaStream_t stream) {
   W = w; H = h; tiles_x = (W + RT_W - 1) / RT_W; tiles_y = (H + RT_W - 1) / RT_W; n_tiles = tiles_x * tiles_y;

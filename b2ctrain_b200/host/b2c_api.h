@@ -92,6 +92,9 @@ struct Model {
   SplatCloud download(cudaStream_t stream = 0) const;
   void zero_optimizer(cudaStream_t stream = 0);
   void zero_stats(cudaStream_t stream = 0);
+  // Keeps the splats flagged in `keep` ([n] device words), in order, across every per-splat array and the caller's extra
+  // [cap] float arrays (src/model.cu:120-155). Returns the new n.
+  int compact(const uint32_t* keep, const std::vector<DevBuf<float>*>& extras, cudaStream_t stream = 0);
 };
 
 // src/gpu/render.h:10-24.

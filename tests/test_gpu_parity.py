@@ -475,3 +475,34 @@ def test_forward_feature_lanes_match_oracle(mode):
     ctx2 = api.RenderCtx("cuda:0"); ctx2.setup(W, H, m.cap, n_chunks=3)
     with pytest.raises(RuntimeError, match="unsupported lane"):
         api.render_forward(ctx2, m, rp, sync=True)
+
+
+def test_model_compact_keeps_flagged_splats_in_order():
+    """Model::compact (src/model.cu:120-155): every per-splat array, planar SH lanes included, is gathered by the stable
+    list of kept indices."""
+    import torch
+    from b2ctrain_b200 import api
+    n, deg = 5000, 2
+    scene = scenes.make_splats(n, deg, 55)
+    m = api.Model("cuda:0").upload(scene)
+    g = torch.Generator(device="cuda:0"); g.manual_seed(3)
+    for k in ("m_pos_op", "v_quat", "m_sh_dc", "m_sh_hi", "v_sh", "refine_norm", "vis_count"):
+        getattr(m, k).copy_(torch.rand(getattr(m, k).shape, generator=g, device="cuda:0"))
+    m.last_step[:n] = torch.arange(n, dtype=torch.int32, device="cuda:0")
+    extra = torch.rand(m.cap, generator=g, device="cuda:0")
+    before = {k: getattr(m, k).clone() for k in api._MODEL_PTRS}
+    keep = (torch.rand(n, generator=g, device="cuda:0") < 0.37).to(torch.int32)
+    keep[0], keep[n - 1] = 1, 1
+    idx = torch.nonzero(keep).flatten()
+    kept, (extra2,) = m.compact(keep, [extra])
+    assert kept == len(idx) == m.n
+    for k in ("pos_op", "quat", "lscale", "m_pos_op", "v_quat"):
+        assert torch.equal(getattr(m, k)[:kept], before[k][idx]), k
+    for k in ("sh_dc", "sh_hi", "m_sh_dc", "m_sh_hi"):
+        assert torch.equal(getattr(m, k)[:, :kept], before[k][:, idx]), k
+    for k in ("v_sh", "refine_norm", "vis_count", "last_step"):
+        assert torch.equal(getattr(m, k)[:kept], before[k][idx]), k
+    assert torch.equal(extra2[:kept], extra[idx])
+    assert m.compact(torch.ones(kept, dtype=torch.int32, device="cuda:0"))[0] == kept   # nothing to drop: untouched
+    d = m.download()
+    assert np.array_equal(d["sh"], scene["sh"][idx.cpu().numpy()])
