@@ -1,4 +1,5 @@
-// Binning stage: depth-keyed radix sort of the splats, scan of tile counts in depth order fused with the emission of
+// Binning stage (and, at the end of the file, the front-to-back chunked renderer built from the same kernels):
+// depth-keyed radix sort of the splats, scan of tile counts in depth order fused with the emission of
 // (tile id, splat index) pairs, stable radix sort by tile id, per-tile ranges. Reference semantics: bin_and_sort
 // (src/gpu/binning.cu:109-145) with its kernels (:10-105); the two library sorts and the library scan of the
 // reference are replaced by the kernels in this file.
@@ -449,9 +450,11 @@ int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uin
 // sorted by tile, ranged) and composited before the next one is touched, and a tile whose pixels have all reached the
 // transmittance cutoff emits nothing from then on: in a dense scene most intersections lie behind saturated pixels and
 // are never composited, so they need not be sorted either. Chunk c covers the ranks [V b(c-1), V b(c)) of the V
-// splats that hit a tile, with b = 1/4^(C-1), ..., 1/16, 1/4, 1 (small chunks first: the nearest splats decide most
-// pixels, and every chunk costs a dozen launches whatever its size). Every chunk's sorted pairs occupy their own window of the key / value buffers, and a tile has one range per
-// chunk. The words that chain the chunks live on the device:
+// splats with a tile box, with b = 1/4^(C-1), ..., 1/16, 1/4, 1 (small chunks first: the nearest splats decide most
+// pixels, and every chunk costs a dozen launches whatever its size). The projection of this path leaves tile boxes,
+// not hit masks: the ellipse-tile tests run per chunk, on the splats whose box still holds a live tile. Every chunk's
+// sorted pairs occupy their own window of the key / value buffers, and a tile has one range per chunk. The words that
+// chain the chunks live on the device:
 //   words[0] = V, words[1 + c] = first slot of chunk c's window, words[16 + c] = pairs of chunk c.
 constexpr int MAX_CHUNKS = 5;
 constexpr int CW_V = 0, CW_BASE = 1, CW_COUNT = 16, CW_WORDS = 32;   // the tile-alive flags follow the header
