@@ -56,16 +56,37 @@ struct PairState { float2 T, Sr, Sg, Sb, vr, vg, vb, vow, inv_fa; uint32_t last0
 __device__ __forceinline__ float2 f2(float x) { return make_float2(x, x); }
 __device__ __forceinline__ float hsum(float2 v) { return v.x + v.y; }
 
+// Tiles in order of decreasing work, approximately: a counting sort on the bit length of the tile's fragment count (all
+// chunks together), longest first, tiles without fragments last. The replay kernel hands its warps out in this order,
+// so the longest lists start first instead of deciding the kernel's tail, and the four tiles of a CTA are alike.
+// One CTA; order[] holds n_tiles entries.
+__global__ void __launch_bounds__(1024) tile_order_kernel(const uint2* __restrict__ tile_ranges, int n_tiles, int n_chunks, uint32_t* __restrict__ order) {
+  __shared__ uint32_t s_hist[33], s_cursor[33];
+  if (threadIdx.x < 33) s_hist[threadIdx.x] = 0u;
+  __syncthreads();
+  auto bucket_of = [&](int tile) {
+    uint32_t len = 0;
+    for (int ch = 0; ch < n_chunks; ch++) { const uint2 rg = tile_ranges[(size_t)ch * n_tiles + tile]; len += rg.y > rg.x ? rg.y - rg.x : 0u; }
+    return len == 0u ? 0 : 32 - __clz(len);   // 0 for no fragments, else the bit length 1..32
+  };
+  for (int tile = threadIdx.x; tile < n_tiles; tile += blockDim.x) atomicAdd(&s_hist[bucket_of(tile)], 1u);
+  __syncthreads();
+  if (threadIdx.x == 0) { uint32_t at = 0; for (int b = 32; b >= 0; b--) { s_cursor[b] = at; at += s_hist[b]; } }
+  __syncthreads();
+  for (int tile = threadIdx.x; tile < n_tiles; tile += blockDim.x) order[atomicAdd(&s_cursor[bucket_of(tile)], 1u)] = (uint32_t)tile;
+}
+
 __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, const float4* __restrict__ out_rgba, const float4* __restrict__ out_feat, const uint32_t* __restrict__ last_idx,
     const float4* __restrict__ v_out, int W, int H, int tiles_x, int n_tiles, float3 bg, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
-    float* __restrict__ vis_weight, int n_chunks) {
+    float* __restrict__ vis_weight, int n_chunks, const uint32_t* __restrict__ order) {
   __shared__ Staged s_frag[BWD_WARPS][BWD_BATCH];
   __shared__ uint32_t s_gid[BWD_WARPS][BWD_BATCH];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x * BWD_WARPS + warp;
-  if (tile >= n_tiles) return;
+  const int slot = blockIdx.x * BWD_WARPS + warp;
+  if (slot >= n_tiles) return;
+  const int tile = order ? (int)order[slot] : slot;
   // A view composited in depth chunks has one range per chunk and tile ([chunk][tile]); the replay walks the chunks
   // from the farthest to the nearest, the pixel state running through.
   {
@@ -200,9 +221,13 @@ extern "C" int b2k_raster_bwd(const B2kCtx* c, const B2kModel* m, const B2kRende
   B2K_REQUIRE(c->out_rgba && c->out_feat && c->last_idx && c->v_out && c->v_splat && c->vis_flag);
   B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y);
   const float3 bg = make_float3(o->bg[0], o->bg[1], o->bg[2]);
+  const int chunks = c->n_chunks > 1 ? c->n_chunks : 1;
+  // The unsorted-pair buffer is scratch once the view is binned: it holds the tile order for this launch.
+  uint32_t* order = c->keys && c->isect_cap >= (uint64_t)c->n_tiles ? c->keys : nullptr;
+  if (order) tile_order_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((const uint2*)c->tile_ranges, c->n_tiles, chunks, order);
   raster_bwd_kernel<<<div_up(c->n_tiles, BWD_WARPS), BWD_WARPS * 32, 0, (cudaStream_t)stream>>>(
       (const uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, (const float4*)c->proj1, (const float4*)c->proj2,
       (const float4*)c->out_rgba, (const float4*)c->out_feat, c->last_idx, (const float4*)c->v_out, c->W, c->H, c->tiles_x, c->n_tiles, bg,
-      c->v_splat, c->vis_flag, m->vis_weight, c->n_chunks > 1 ? c->n_chunks : 1);
+      c->v_splat, c->vis_flag, m->vis_weight, chunks, order);
   return check_launch();
 }

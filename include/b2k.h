@@ -193,7 +193,8 @@ int b2k_loss_accumulate(const B2kCtx* ctx, b2k_stream_t s);
 int b2k_eval_metrics(const B2kCtx* ctx, const uint32_t* rgba, int32_t mask_weighted, b2k_stream_t s);
 
 /* ---- backward ---- */
-/* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). */
+/* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). Overwrites the first
+ * n_tiles words of ctx->keys (scratch once the view is binned) with the order in which it walks the tiles. */
 int b2k_raster_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kRenderOpts* opts, b2k_stream_t s);
 /* optimizer_step, src/gpu/optim.h:50 (optim_kernel, src/gpu/optim.cu:100-378): projection backward fused with
  * sparse Adam; consumes and clears ctx->v_splat / vis_flag. With grad_out set it writes gradients and returns. */
