@@ -506,3 +506,41 @@ def test_model_compact_keeps_flagged_splats_in_order():
     assert m.compact(torch.ones(kept, dtype=torch.int32, device="cuda:0"))[0] == kept   # nothing to drop: untouched
     d = m.download()
     assert np.array_equal(d["sh"], scene["sh"][idx.cpu().numpy()])
+
+
+def test_chunked_render_edge_cases():
+    """The chunked renderer on inputs with nothing to do: no splats, splats that are all culled (behind the camera), an
+    image smaller than a tile, and more chunks than visible splats. Output = the whole-view path's."""
+    import torch
+    from b2ctrain_b200 import api
+    cases = []
+    base = scenes.make_splats(40, 1, 5, log_scale=(-2.5, 0.3))
+    cam = scenes.look_at_camera(scenes.orbit_eye(3.0, 10.0, 5.0), 37, 21, 30.0)
+    cases.append(("few splats, five chunks", base, cam))
+    behind = {k: (v.copy() if hasattr(v, "copy") else v) for k, v in base.items()}
+    behind["pos_op"][:, :3] = np.asarray(cam["pos"], np.float32) * 3.0          # on the far side of the camera: every splat is culled
+    cases.append(("all culled", behind, cam))
+    tiny = scenes.look_at_camera(scenes.orbit_eye(3.0, 0.0, 0.0), 5, 3, 6.0)
+    cases.append(("image smaller than a tile", base, tiny))
+    for name, scene, c in cases:
+        m = api.Model("cuda:0").upload(scene)
+        imgs = []
+        for chunks in (1, 5):
+            ctx = api.RenderCtx("cuda:0"); ctx.want_depth = True
+            ctx.setup(c["W"], c["H"], m.cap, n_chunks=chunks)
+            rp = api.RenderParams(c, bg=(0.3, 0.2, 0.1), sh_degree=1, bwd_info=True)
+            api.render_forward(ctx, m, rp, sync=True)
+            gt = torch.zeros(c["W"] * c["H"], dtype=torch.int32, device="cuda:0")
+            api.photometric_loss(ctx, api.ViewGPU(gt, None, c["W"], c["H"]), api.LossParams())
+            api.rasterize_backward(ctx, m, rp)
+            torch.cuda.synchronize()
+            imgs.append((ctx.out_rgba.cpu().numpy(), ctx.out_depth.cpu().numpy(), ctx.v_splat[:m.n].cpu().numpy()))
+        assert np.array_equal(imgs[0][0], imgs[1][0]), name
+        assert np.array_equal(imgs[0][1], imgs[1][1]), name
+        assert rel_l2(imgs[1][2], imgs[0][2]) <= 1e-5 or float(np.abs(imgs[0][2]).max()) == 0.0, name
+    # an empty model
+    m = api.Model("cuda:0").upload(scenes.make_splats(0, 1, 1))
+    ctx = api.RenderCtx("cuda:0"); ctx.setup(16, 16, 1, n_chunks=3)
+    api.render_forward(ctx, m, api.RenderParams(cam | dict(W=16, H=16), bg=(0.5, 0.25, 0.125), sh_degree=1, bwd_info=True), sync=True)
+    img = ctx.out_rgba.cpu().numpy()
+    assert np.allclose(img[:, :3], [0.5, 0.25, 0.125]) and np.all(img[:, 3] == 0.0)
