@@ -46,7 +46,8 @@ class B2kCtx(C.Structure):
                 ("vals_sorted", C.c_void_p), ("isect_cap", C.c_uint64), ("num_isect", C.c_void_p), ("sort_tmp", C.c_void_p),
                 ("sort_tmp_bytes", C.c_uint64), ("tile_ranges", C.c_void_p), ("out_rgba", C.c_void_p), ("out_feat", C.c_void_p),
                 ("out_depth", C.c_void_p), ("last_idx", C.c_void_p), ("v_splat", C.c_void_p), ("vis_flag", C.c_void_p), ("vis_list", C.c_void_p),
-                ("v_out", C.c_void_p), ("loss_accum", C.c_void_p), ("n_chunks", C.c_int32), ("proj3", C.c_void_p), ("chunk_words", C.c_void_p)]
+                ("v_out", C.c_void_p), ("loss_accum", C.c_void_p), ("n_chunks", C.c_int32), ("proj3", C.c_void_p), ("chunk_words", C.c_void_p),
+                ("bwd_scratch", C.c_void_p), ("bwd_scratch_bytes", C.c_uint64)]
 
 
 class B2kRenderOpts(C.Structure):
@@ -83,7 +84,11 @@ SIGNATURES = {
     "b2k_sort_tmp_bytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
     "b2k_loss_photometric": (C.c_int, [_P, _P, _S]),
     "b2k_loss_accumulate": (C.c_int, [_P, _S]),
+    "b2k_loss_zero": (C.c_int, [_P, C.c_int32, C.c_int32, _S]),
+    "b2k_loss_fold": (C.c_int, [_P, _P, _S]),
+    "b2k_step_begin": (C.c_int, [_P, _S]),
     "b2k_eval_metrics": (C.c_int, [_P, _P, C.c_int32, _S]),
+    "b2k_bwd_scratch_bytes": (C.c_uint64, [C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
     "b2k_raster_bwd": (C.c_int, [_P, _P, _P, _S]),
     "b2k_optim_fused": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_proj_bwd": (C.c_int, [_P, _P, _P, _P, _P, _S]),
@@ -306,6 +311,8 @@ class RenderCtx:
         self.d_num_isect = u32(4)
         if self.isect_cap == 0 or (isect_cap and isect_cap > self.isect_cap):
             self._alloc_isect(isect_cap or (1 << 22))
+        else:
+            self._alloc_isect(self.isect_cap)   # the backward scratch depends on the image size and the chunk count
         nbytes = int(lib().b2k_sort_tmp_bytes(self.n_cap, self.isect_cap))
         self.sort_tmp = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
         return self
@@ -314,6 +321,9 @@ class RenderCtx:
         u32 = lambda: torch.zeros(cap, dtype=torch.int32, device=self.device)
         self.keys, self.vals, self.keys_sorted, self.vals_sorted = u32(), u32(), u32(), u32()
         self.isect_cap = int(cap)
+        # checkpoints and work list of the segmented backward: sized from the intersection capacity
+        self.bwd_scratch = torch.zeros(int(lib().b2k_bwd_scratch_bytes(self.W, self.H, self.n_chunks, self.isect_cap)), dtype=torch.uint8,
+                                       device=self.device)
 
     def struct(self):
         s = B2kCtx()
@@ -321,12 +331,13 @@ class RenderCtx:
             setattr(s, k, getattr(self, k))
         for k in ("proj0", "proj1", "proj2", "tile_count", "hit_info", "depth_keys", "depth_keys_sorted", "order_in", "order", "tile_off", "keys",
                   "vals", "keys_sorted", "vals_sorted", "sort_tmp", "tile_ranges", "out_rgba", "out_feat", "out_depth", "last_idx",
-                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum", "chunk_words", "proj3"):
+                  "v_splat", "vis_flag", "vis_list", "v_out", "loss_accum", "chunk_words", "proj3", "bwd_scratch"):
             t = getattr(self, k, None)
             setattr(s, k, None if t is None else t.data_ptr())
         s.num_isect = self.d_num_isect.data_ptr()
         s.isect_cap = self.isect_cap
         s.sort_tmp_bytes = self.sort_tmp.numel()
+        s.bwd_scratch_bytes = self.bwd_scratch.numel()
         s.n_chunks = self.n_chunks
         return s
 
@@ -524,6 +535,24 @@ def photometric_loss(ctx, view, lp, stream=None):
 def accumulate_loss(ctx, stream=None):
     cs = ctx.struct()
     _check(lib().b2k_loss_accumulate(C.byref(cs), _stream(stream)), "accumulate_loss")
+
+
+def zero_loss(ctx, first=0, count=16, stream=None):
+    """loss_accum[first : first + count] = 0 on the stream."""
+    cs = ctx.struct()
+    _check(lib().b2k_loss_zero(C.byref(cs), int(first), int(count), _stream(stream)), "zero_loss")
+
+
+def step_begin(ctx, stream=None):
+    """Clears the context's loss accumulator and its running intersection maximum (start of a training step)."""
+    cs = ctx.struct()
+    _check(lib().b2k_step_begin(C.byref(cs), _stream(stream)), "step_begin")
+
+
+def fold_loss(dst_ctx, src_ctx, stream=None):
+    """Adds the running loss sum and view count of src_ctx into dst_ctx's."""
+    a, b = dst_ctx.struct(), src_ctx.struct()
+    _check(lib().b2k_loss_fold(C.byref(a), C.byref(b), _stream(stream)), "fold_loss")
 
 
 def eval_metrics(ctx, view, mask_weighted=False, stream=None):

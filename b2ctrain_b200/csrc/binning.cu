@@ -817,6 +817,8 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   B2K_REQUIRE(m && cam && o && c);
   const int C = c->n_chunks;
   B2K_REQUIRE(C >= 2 && C <= MAX_CHUNKS && c->chunk_words && c->last_idx && c->tile_off && c->depth_keys);
+  B2K_REQUIRE(!o->bwd_info || c->bwd_scratch);
+  if (o->bwd_info && c->bwd_scratch_bytes < b2k_bwd_scratch_bytes(c->W, c->H, C, c->isect_cap)) return B2K_ERR_CAPACITY;
   if (o->feat_mode != 0) return B2K_ERR_UNSUPPORTED;   // out_feat.xyz carries the colour sums between chunks
   B2K_REQUIRE(c->tile_ranges && c->num_isect && c->n_tiles == c->tiles_x * c->tiles_y && c->tile_bits >= 1 && c->tile_bits <= 24);
   B2K_REQUIRE(c->out_rgba && c->out_feat && c->keys && c->vals && c->keys_sorted && c->vals_sorted && c->sort_tmp);

@@ -37,6 +37,22 @@ inline uint32_t* big_list_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp +
 inline uint32_t* big_emit_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp + BIG_HEADER_WORDS + (size_t)c->n_cap; }       // [n_cap][2]
 inline uint32_t* sort_tables_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tmp + BIG_HEADER_WORDS + 3 * (size_t)c->n_cap; }
 
+// Segments of the backward replay. The forward leaves a per-pixel checkpoint (colour sums, transmittance) in
+// ctx->bwd_scratch before every SEG_LEN-th fragment of a tile's list and, in a chunked view, where a later depth chunk
+// takes a tile over; the backward replays the segments between checkpoints as independent work items.
+// Scratch layout: [BWD_HEADER_WORDS] (word 0: item count, word 1: item cursor), [slots] items (range index, segment),
+// [slots][64] float4 checkpoints. The checkpoint before fragment range_start + seg * SEG_LEN of range q (= chunk *
+// n_tiles + tile) lives in slot (range_start >> SEG_SHIFT) + q + seg: ranges follow each other in the sorted buffer in
+// the order of q, which makes the map injective without any table.
+constexpr int SEG_SHIFT = 8, SEG_LEN = 1 << SEG_SHIFT;
+constexpr size_t BWD_HEADER_WORDS = 16;
+__host__ __device__ inline uint64_t bwd_slots(uint64_t isect_cap, uint64_t n_ranges) { return (((isect_cap >> SEG_SHIFT) + n_ranges + 2) + 1) & ~1ull; }
+__host__ __device__ inline uint32_t ckpt_slot(uint32_t range_start, int q, uint32_t seg) { return (range_start >> SEG_SHIFT) + (uint32_t)q + seg; }
+inline uint64_t bwd_ranges(const B2kCtx* c) { return (uint64_t)c->n_tiles * (c->n_chunks > 1 ? c->n_chunks : 1); }
+inline uint32_t* bwd_work_ptr(const B2kCtx* c) { return (uint32_t*)c->bwd_scratch; }
+inline uint2* bwd_items_ptr(const B2kCtx* c) { return (uint2*)((uint32_t*)c->bwd_scratch + BWD_HEADER_WORDS); }
+inline float4* bwd_ckpt_ptr(const B2kCtx* c) { return (float4*)(bwd_items_ptr(c) + bwd_slots(c->isect_cap, bwd_ranges(c))); }
+
 struct CamDev {
   float R[9]; float t[3]; float pos[3]; float fx, fy, cx, cy; int W, H; float lim_pos_x, lim_pos_y, lim_neg_x, lim_neg_y;
 };

@@ -266,69 +266,106 @@ __global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __re
   }
 }
 
-// PSNR / SSIM sums on the 8-bit-quantised prediction against the target on a black background.
+// Evaluation metrics (eval_metrics, src/gpu/loss.cu:241-293): squared error and SSIM sums of the 8-bit-quantised
+// prediction against the target on a black background, optionally weighted by the target's alpha.
+//
+// One CTA per 16x16 tile runs the three channels over one staged 26x26 footprint (prediction and target are read from
+// global memory once, not once per channel) and both blur passes are register-tiled like the loss kernel's: a thread
+// makes four consecutive outputs of all five moments from one fourteen-wide window.
+constexpr int EV_W = LOSS_TILE + 2 * HALO;   // 26: footprint of the tile's SSIM windows
+constexpr int EV_S = 28;                     // row stride of the footprint planes (aligned 128-bit windows, zero pad)
+
 __global__ void __launch_bounds__(TILE_PX) eval_kernel(const float4* __restrict__ pred, const uint32_t* __restrict__ gt, int W, int H, int tiles_x, int mask_w,
                                                        Gauss gauss, float* __restrict__ accum) {
-  __shared__ float s_in[2][IN_W * IN_W];
-  __shared__ float s_h[STAT_W * LOSS_TILE * 5];
-  __shared__ float s_red[2][TILE_PX / 32];
-  const int c = blockIdx.y, tile = blockIdx.x, tid = threadIdx.x;
-  const int tx0 = (tile % tiles_x) * LOSS_TILE, ty0 = (tile / tiles_x) * LOSS_TILE;
-  for (int i = tid; i < IN_W * IN_W; i += TILE_PX) {
-    const int fy = i / IN_W, fx = i % IN_W;
-    const int y = ty0 + fy - 2 * HALO, x = tx0 + fx - 2 * HALO;
-    float p = 0.f, g = 0.f;
-    if (y >= 0 && y < H && x >= 0 && x < W) {
+  __shared__ __align__(16) float s_q[3][EV_W * EV_S];          // quantised prediction per channel
+  __shared__ __align__(16) float s_t[3][EV_W * EV_S];          // target per channel
+  __shared__ __align__(16) float s_row[5][EV_W][LOSS_TILE];    // horizontally blurred moments of the current channel
+  __shared__ float s_part[2][TILE_PX / 32];
+  const int tid = threadIdx.x;
+  const int x0 = (blockIdx.x % tiles_x) * LOSS_TILE, y0 = (blockIdx.x / tiles_x) * LOSS_TILE;
+  for (int i = tid; i < EV_W * EV_S; i += TILE_PX) {
+    const int fy = i / EV_S, fx = i % EV_S;
+    const int y = y0 + fy - HALO, x = x0 + fx - HALO;
+    float q[3] = {0.f, 0.f, 0.f}, t[3] = {0.f, 0.f, 0.f};   // zero padding outside the image and in the row pad
+    if (fx < EV_W && y >= 0 && y < H && x >= 0 && x < W) {
       const float4 pv = pred[y * W + x];
-      p = c == 0 ? pv.x : (c == 1 ? pv.y : pv.z);
-      p = rintf(fminf(fmaxf(p, 0.f), 1.f) * 255.f) / 255.f;
-      g = unpack(gt[y * W + x], c);
+      const uint32_t gp = gt[y * W + x];
+      const float pc[3] = {pv.x, pv.y, pv.z};
+#pragma unroll
+      for (int c = 0; c < 3; c++) { q[c] = rintf(fminf(fmaxf(pc[c], 0.f), 1.f) * 255.f) / 255.f; t[c] = unpack(gp, c); }
     }
-    s_in[0][i] = p; s_in[1][i] = g;
+#pragma unroll
+    for (int c = 0; c < 3; c++) { s_q[c][i] = q[c]; s_t[c][i] = t[c]; }
   }
   __syncthreads();
-  for (int i = tid; i < STAT_W * LOSS_TILE; i += TILE_PX) {
-    const int row = i / LOSS_TILE + HALO, ox = i % LOSS_TILE + HALO;
-    float sx = 0.f, sx2 = 0.f, sy = 0.f, sy2 = 0.f, sxy = 0.f;
+  float se_sum = 0.f, ssim_sum = 0.f;
+  for (int c = 0; c < 3; c++) {
+    // Horizontal pass: 26 rows x 4 groups of four output columns.
+    if (tid < EV_W * 4) {
+      const int row = tid >> 2, g4 = (tid & 3) * 4;
+      float x[16], y[16], in[16], out[4];
+      load16(&s_q[c][row * EV_S + g4], x);
+      load16(&s_t[c][row * EV_S + g4], y);
+      window4(x, gauss, out); *reinterpret_cast<float4*>(&s_row[0][row][g4]) = make_float4(out[0], out[1], out[2], out[3]);
 #pragma unroll
-    for (int d = 0; d < 11; d++) {
-      const float w = gauss.w[d];
-      const float x = s_in[0][row * IN_W + ox + d], y = s_in[1][row * IN_W + ox + d];
-      sx += w * x; sx2 += w * x * x; sy += w * y; sy2 += w * y * y; sxy += w * x * y;
+      for (int k = 0; k < 16; k++) in[k] = x[k] * x[k];
+      window4(in, gauss, out); *reinterpret_cast<float4*>(&s_row[1][row][g4]) = make_float4(out[0], out[1], out[2], out[3]);
+      window4(y, gauss, out); *reinterpret_cast<float4*>(&s_row[2][row][g4]) = make_float4(out[0], out[1], out[2], out[3]);
+#pragma unroll
+      for (int k = 0; k < 16; k++) in[k] = y[k] * y[k];
+      window4(in, gauss, out); *reinterpret_cast<float4*>(&s_row[3][row][g4]) = make_float4(out[0], out[1], out[2], out[3]);
+#pragma unroll
+      for (int k = 0; k < 16; k++) in[k] = x[k] * y[k];
+      window4(in, gauss, out); *reinterpret_cast<float4*>(&s_row[4][row][g4]) = make_float4(out[0], out[1], out[2], out[3]);
     }
-    float* o = s_h + i * 5; o[0] = sx; o[1] = sx2; o[2] = sy; o[3] = sy2; o[4] = sxy;
-  }
-  __syncthreads();
-  float mse = 0.f, ssim_v = 0.f;
-  const int ly = tid / LOSS_TILE, lx = tid % LOSS_TILE;
-  const int gy = ty0 + ly, gx = tx0 + lx;
-  if (gy < H && gx < W) {
-    float st[5] = {0.f, 0.f, 0.f, 0.f, 0.f};
+    __syncthreads();
+    // Vertical pass and the metrics: 16 columns x 4 groups of four output rows.
+    if (tid < LOSS_TILE * 4) {
+      const int col = tid & (LOSS_TILE - 1), r4 = (tid / LOSS_TILE) * 4;
+      float st[5][4];
 #pragma unroll
-    for (int d = 0; d < 11; d++) {
-      const float w = gauss.w[d];
-      const float* h = s_h + ((ly + d) * LOSS_TILE + lx) * 5;
+      for (int m = 0; m < 5; m++) {
+        float in[16];
 #pragma unroll
-      for (int k = 0; k < 5; k++) st[k] += w * h[k];
+        for (int k = 0; k < 14; k++) in[k] = s_row[m][r4 + k][col];
+        in[14] = in[15] = 0.f;
+        window4(in, gauss, st[m]);
+      }
+#pragma unroll
+      for (int o = 0; o < 4; o++) {
+        const int y = y0 + r4 + o, x = x0 + col;
+        if (y < H && x < W) {
+          const float mu_p = st[0][o], mu_t = st[2][o];
+          const float var_p = fmaxf(0.f, st[1][o] - mu_p * mu_p), var_t = fmaxf(0.f, st[3][o] - mu_t * mu_t), cov = st[4][o] - mu_p * mu_t;
+          const float raw = ((2.f * mu_p * mu_t + C1) * (2.f * cov + C2)) / ((mu_p * mu_p + mu_t * mu_t + C1) * (var_p + var_t + C2));
+          const int centre = (r4 + o + HALO) * EV_S + col + HALO;
+          const float wgt = mask_w ? unpack(gt[y * W + x], 3) : 1.f;
+          const float err = fabsf(s_q[c][centre] - s_t[c][centre]) * wgt;
+          se_sum += err * err;
+          ssim_sum += fminf(fmaxf(raw, -1.f), 1.f) * wgt;
+        }
+      }
     }
-    const float mu1 = st[0], mu2 = st[2], s1 = fmaxf(0.f, st[1] - mu1 * mu1), s2 = fmaxf(0.f, st[3] - mu2 * mu2), s12 = st[4] - mu1 * mu2;
-    const float ssim = fminf(fmaxf(((2.f * mu1 * mu2 + C1) * (2.f * s12 + C2)) / ((mu1 * mu1 + mu2 * mu2 + C1) * (s1 + s2 + C2)), -1.f), 1.f);
-    const int ci = (ly + 2 * HALO) * IN_W + lx + 2 * HALO;
-    const float d = fabsf(s_in[0][ci] - s_in[1][ci]);
-    const float m = mask_w ? unpack(gt[gy * W + gx], 3) : 1.f;
-    mse = (d * m) * (d * m); ssim_v = ssim * m;
+    __syncthreads();   // s_row is overwritten by the next channel
   }
-  const float a = warp_sum(mse), b = warp_sum(ssim_v);
-  if ((tid & 31) == 0) { s_red[0][tid >> 5] = a; s_red[1][tid >> 5] = b; }
+  const float a = warp_sum(se_sum), b = warp_sum(ssim_sum);
+  if ((tid & 31) == 0) { s_part[0][tid >> 5] = a; s_part[1][tid >> 5] = b; }
   __syncthreads();
-  if (tid == 0) {
-    float ta = 0.f, tb = 0.f;
-    for (int i = 0; i < TILE_PX / 32; i++) { ta += s_red[0][i]; tb += s_red[1][i]; }
-    atomicAdd(accum + 4, ta); atomicAdd(accum + 5, tb);
+  if (tid < 2) {
+    float total = 0.f;
+    for (int i = 0; i < TILE_PX / 32; i++) total += s_part[tid][i];
+    atomicAdd(accum + 4 + tid, total);
   }
 }
 
-__global__ void accumulate_kernel(float* a) { a[2] += a[0] + a[1]; a[3] += 1.f; }
+// Running loss sum and view count; also keeps the largest intersection total any view of the step produced, so that
+// one readback per step (instead of one per view) tells the host whether a view overflowed its buffers.
+__global__ void accumulate_kernel(float* a, uint32_t* num_isect) {
+  a[2] += a[0] + a[1]; a[3] += 1.f;
+  if (num_isect) num_isect[2] = max(num_isect[2], num_isect[0]);
+}
+// dst[2] += src[2], dst[3] += src[3]: folds the running loss of a second context (a view in flight on another stream).
+__global__ void fold_loss_kernel(float* dst, const float* src) { dst[2] += src[2]; dst[3] += src[3]; }
 
 bool g_smem_set[64] = {false};
 
@@ -358,7 +395,26 @@ extern "C" int b2k_loss_photometric(const B2kCtx* c, const B2kLoss* lp, b2k_stre
 
 extern "C" int b2k_loss_accumulate(const B2kCtx* c, b2k_stream_t stream) {
   B2K_REQUIRE(c && c->loss_accum);
-  accumulate_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(c->loss_accum);
+  accumulate_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(c->loss_accum, c->num_isect);
+  return check_launch();
+}
+
+extern "C" int b2k_loss_zero(const B2kCtx* c, int32_t first, int32_t count, b2k_stream_t stream) {
+  B2K_REQUIRE(c && c->loss_accum && first >= 0 && count >= 0 && first + count <= 16);
+  if (count) B2K_CUDA(cudaMemsetAsync(c->loss_accum + first, 0, (size_t)count * sizeof(float), (cudaStream_t)stream));
+  return B2K_OK;
+}
+
+extern "C" int b2k_step_begin(const B2kCtx* c, b2k_stream_t stream) {
+  B2K_REQUIRE(c && c->loss_accum);
+  B2K_CUDA(cudaMemsetAsync(c->loss_accum, 0, 16 * sizeof(float), (cudaStream_t)stream));
+  if (c->num_isect) B2K_CUDA(cudaMemsetAsync(c->num_isect + 2, 0, sizeof(uint32_t), (cudaStream_t)stream));
+  return B2K_OK;
+}
+
+extern "C" int b2k_loss_fold(const B2kCtx* dst, const B2kCtx* src, b2k_stream_t stream) {
+  B2K_REQUIRE(dst && src && dst->loss_accum && src->loss_accum && dst->loss_accum != src->loss_accum);
+  fold_loss_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(dst->loss_accum, src->loss_accum);
   return check_launch();
 }
 
@@ -366,6 +422,6 @@ extern "C" int b2k_eval_metrics(const B2kCtx* c, const uint32_t* rgba, int32_t m
   B2K_REQUIRE(c && rgba && c->out_rgba && c->loss_accum && c->W > 0 && c->H > 0);
   const int tiles_x = div_up(c->W, LOSS_TILE), tiles = tiles_x * div_up(c->H, LOSS_TILE);
   static const Gauss g = make_gauss();
-  eval_kernel<<<dim3(tiles, 3), TILE_PX, 0, (cudaStream_t)stream>>>((const float4*)c->out_rgba, rgba, c->W, c->H, tiles_x, mask_weighted, g, c->loss_accum);
+  eval_kernel<<<tiles, TILE_PX, 0, (cudaStream_t)stream>>>((const float4*)c->out_rgba, rgba, c->W, c->H, tiles_x, mask_weighted, g, c->loss_accum);
   return check_launch();
 }

@@ -310,7 +310,8 @@ template <int DEG>
 __global__ void __launch_bounds__(OPT_BLOCK) optim_fused_kernel(int n, ModelPtrs mp, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
                                                                 const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
                                                                 float* __restrict__ vis_count, CamDev cam, B2kOptim op,
-                                                                const uint32_t* __restrict__ vis_list, const uint32_t* __restrict__ vis_list_count) {
+                                                                const uint32_t* __restrict__ vis_list, const uint32_t* __restrict__ vis_list_count,
+                                                                const uint32_t* __restrict__ isect_total, uint32_t isect_cap) {
   constexpr int K = (DEG + 1) * (DEG + 1);
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (vis_list) { if ((uint32_t)i >= *vis_list_count) return; i = (int)vis_list[i]; }   // sparse walk over the splats the backward touched
@@ -319,6 +320,9 @@ __global__ void __launch_bounds__(OPT_BLOCK) optim_fused_kernel(int n, ModelPtrs
   const int active = op.active_sh_degree < DEG ? (op.active_sh_degree < 0 ? 0 : op.active_sh_degree) : DEG;
   splat_gradient<DEG>(i, mp.cap, mp.pos_op, mp.quat, mp.lscale, mp.sh_dc, mp.sh_hi, v_splat, vis_flag, tile_count, refine_norm, vis_count, cam, active,
                       (const float4*)op.pos_override, (const float4*)op.quat_override, (const float4*)op.lscale_override, sg, basis);
+  // A view whose intersections did not fit its buffers was composited from truncated lists: its lanes are consumed
+  // (cleared above) but nothing is written from them; the host reads the total later, grows the buffers and redoes it.
+  if (isect_total && *isect_total > isect_cap) return;
   if (op.grad_out) {
     if (op.sparse && !sg.any) return;
     float* o = op.grad_out + (size_t)i * (11 + K * 3);
@@ -341,7 +345,8 @@ template <int DEG>
 __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
                                                              const uint32_t* __restrict__ tile_count, float* __restrict__ refine_norm,
                                                              float* __restrict__ vis_count, CamDev cam, B2kOptim op, float* __restrict__ grad,
-                                                             const uint32_t* __restrict__ vis_list, const uint32_t* __restrict__ vis_list_count) {
+                                                             const uint32_t* __restrict__ vis_list, const uint32_t* __restrict__ vis_list_count,
+                                                             const uint32_t* __restrict__ isect_total, uint32_t isect_cap) {
   constexpr int K = (DEG + 1) * (DEG + 1);
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (vis_list) { if ((uint32_t)i >= *vis_list_count) return; i = (int)vis_list[i]; }
@@ -350,7 +355,7 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
   const int active = op.active_sh_degree < DEG ? (op.active_sh_degree < 0 ? 0 : op.active_sh_degree) : DEG;
   splat_gradient<DEG>(i, mp.cap, mp.pos_op, mp.quat, mp.lscale, mp.sh_dc, mp.sh_hi, v_splat, vis_flag, tile_count, refine_norm, vis_count, cam, active,
                       (const float4*)op.pos_override, (const float4*)op.quat_override, (const float4*)op.lscale_override, sg, basis);
-  if (!sg.any) return;
+  if (!sg.any || (isect_total && *isect_total > isect_cap)) return;   // an overflowed view adds nothing (see optim_fused_kernel)
   // Several views of a step may be in flight on different streams and add into the same accumulator: reductions
   // (fire-and-forget RED.ADD at the L2), not read-modify-write.
   float* o = grad + (size_t)i * (11 + K * 3);
@@ -639,7 +644,8 @@ extern "C" int b2k_optim_fused(const B2kCtx* c, const B2kModel* m, const B2kCame
   const uint32_t* list = (c->vis_list && c->num_isect && op->sparse && !op->grad_out) ? c->vis_list : nullptr;
   if (list) { st = build_vis_list(c, m->n, (cudaStream_t)stream); if (st) return st; }
   B2K_DISPATCH_DEG(m->degree, (optim_fused_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(
-      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, list, list ? c->num_isect + 1 : nullptr)));
+      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, list, list ? c->num_isect + 1 : nullptr,
+      c->num_isect, (uint32_t)c->isect_cap)));
   return check_launch();
 }
 
@@ -653,7 +659,8 @@ extern "C" int b2k_proj_bwd(const B2kCtx* c, const B2kModel* m, const B2kCamera*
   const uint32_t* list = (c->vis_list && c->num_isect) ? c->vis_list : nullptr;   // the gradient half only ever needs touched splats
   if (list) { st = build_vis_list(c, m->n, (cudaStream_t)stream); if (st) return st; }
   B2K_DISPATCH_DEG(m->degree, (proj_bwd_kernel<D><<<div_up(m->n, OPT_BLOCK), OPT_BLOCK, 0, (cudaStream_t)stream>>>(
-      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, grad, list, list ? c->num_isect + 1 : nullptr)));
+      m->n, mp, c->v_splat, c->vis_flag, c->tile_count, m->refine_norm, m->vis_count, cd, *op, grad, list, list ? c->num_isect + 1 : nullptr,
+      c->num_isect, (uint32_t)c->isect_cap)));
   return check_launch();
 }
 

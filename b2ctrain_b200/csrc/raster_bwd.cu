@@ -1,214 +1,238 @@
 // Backward through compositing: per-pixel reverse replay of the forward, per-fragment gradients reduced across the
 // tile and accumulated per splat. Reference semantics: raster_bwd_kernel (src/gpu/raster_bwd.cu:11-143).
 //
-// Work decomposition (differs from the reference on purpose): one WARP owns an 8x8 tile, each lane replays two
-// horizontally adjacent pixels. Per fragment the pair is summed in registers, then the 11 live gradient lanes are
-// reduced across the warp with a halving butterfly (16 shuffles for all lanes together, against 5 shuffles per lane
-// in a plain tree), after which lane 2L holds the tile's total of lane L and issues one global reduction. Fragment
-// records are staged per warp in shared memory, so the kernel has no block-wide barrier: warps are independent.
-// A fragment no pixel of the tile sees is rejected after the sigma test; otherwise the pair's math is branch-free (a
-// pixel that does not see the fragment has alpha = 0 and adds exact zeros) and runs on packed fp32x2 instructions.
+// Work decomposition (differs from the reference on purpose):
+//   * A tile's fragment list is cut into SEGMENTS of 256 fragments. The forward leaves the per-pixel state (colour
+//     sums, transmittance) at every segment boundary (and where a depth chunk of a chunked view hands over to the next),
+//     so each segment can be replayed on its own: the colour behind a boundary is the final sum minus the checkpoint.
+//     A small kernel lists the (range, segment) items; a persistent grid of independent warps pulls them from a
+//     counter. The longest list of a view no longer decides the kernel's duration, and no warp slot idles while another
+//     warp still has a thousand fragments to go.
+//   * One WARP owns an item; each lane replays two horizontally adjacent pixels on packed fp32x2 arithmetic. A fragment
+//     no pixel of the tile sees is rejected after the sigma test; otherwise the pair's math is branch-free (a pixel that
+//     does not see the fragment has alpha = 0 and adds exact zeros).
+//   * Reduction across the tile: every lane stores its eleven per-fragment partial sums as three 16-byte words into
+//     a per-warp shared-memory block; once five fragments are pending, thirty lanes each add up sixteen lanes' worth of
+//     one 16-byte column (conflict-free: blocks are skewed by one slot), a single shuffle joins the two halves, and the
+//     column's owner issues the global reductions. About 15 warp instructions per fragment against 60 for a shuffle
+//     butterfly over the warp; warps never synchronise with each other.
 //
-// FP32-issue / latency bound: ~90 flops, one ex2 and one rcp per fragment-pixel, plus the reduction.
+// FP32-issue bound: ~90 flops, one ex2 and one rcp per fragment-pixel, plus the reduction.
 #include "common.cuh"
 
 namespace b2k {
 namespace {
 
-constexpr int BWD_WARPS = 4;                 // warps (tiles) per CTA
+constexpr int BWD_WARPS = 2;                 // warps per CTA (independent: the CTA shape only sets the residency granularity)
 constexpr int BWD_BATCH = 32;                // fragments staged per warp and batch
+constexpr int RED_F = 5;                     // fragments whose partial sums are pending before a column reduction
+constexpr int RED_BLOCK = 33 * 3;            // 16-byte words per pending fragment: 32 lanes x 3 words, one slot of skew
 constexpr unsigned FULL = 0xffffffffu;
 
 struct Staged { float4 a, c, col; };         // proj0, proj1, proj2 of one fragment
 
-// Halving butterfly over the warp: on return v[0] of lane l is the warp's sum of the callers' v[(l >> 1) & 15].
-__device__ __forceinline__ float warp_transpose_sum(float (&v)[16], int lane) {
-  {
-    const bool hi = lane & 16;
-#pragma unroll
-    for (int i = 0; i < 8; i++) { const float send = hi ? v[i] : v[i + 8]; const float keep = hi ? v[i + 8] : v[i]; v[i] = keep + __shfl_xor_sync(FULL, send, 16); }
-  }
-  {
-    const bool hi = lane & 8;
-#pragma unroll
-    for (int i = 0; i < 4; i++) { const float send = hi ? v[i] : v[i + 4]; const float keep = hi ? v[i + 4] : v[i]; v[i] = keep + __shfl_xor_sync(FULL, send, 8); }
-  }
-  {
-    const bool hi = lane & 4;
-#pragma unroll
-    for (int i = 0; i < 2; i++) { const float send = hi ? v[i] : v[i + 2]; const float keep = hi ? v[i + 2] : v[i]; v[i] = keep + __shfl_xor_sync(FULL, send, 4); }
-  }
-  {
-    const bool hi = lane & 2;
-    const float send = hi ? v[0] : v[1]; const float keep = hi ? v[1] : v[0];
-    v[0] = keep + __shfl_xor_sync(FULL, send, 2);
-  }
-  v[0] += __shfl_xor_sync(FULL, v[0], 1);
-  return v[0];
-}
-
 __device__ __forceinline__ float fast_sqrt(float x) { float r; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
-
-// State of this lane's pixel pair, one float2 per quantity: the replay below runs on Blackwell's packed fp32x2
-// arithmetic (fma.rn.f32x2 and friends), one instruction for both pixels.
-struct PairState { float2 T, Sr, Sg, Sb, vr, vg, vb, vow, inv_fa; uint32_t last0, last1; };
-
 __device__ __forceinline__ float2 f2(float x) { return make_float2(x, x); }
 __device__ __forceinline__ float hsum(float2 v) { return v.x + v.y; }
-
-// Tiles in order of decreasing work, approximately: a counting sort on the bit length of the tile's fragment count (all
-// chunks together), longest first, tiles without fragments last. The replay kernel hands its warps out in this order,
-// so the longest lists start first instead of deciding the kernel's tail, and the four tiles of a CTA are alike.
-// One CTA; order[] holds n_tiles entries.
-__global__ void __launch_bounds__(1024) tile_order_kernel(const uint2* __restrict__ tile_ranges, int n_tiles, int n_chunks, uint32_t* __restrict__ order) {
-  __shared__ uint32_t s_hist[33], s_cursor[33];
-  if (threadIdx.x < 33) s_hist[threadIdx.x] = 0u;
-  __syncthreads();
-  auto bucket_of = [&](int tile) {
-    uint32_t len = 0;
-    for (int ch = 0; ch < n_chunks; ch++) { const uint2 rg = tile_ranges[(size_t)ch * n_tiles + tile]; len += rg.y > rg.x ? rg.y - rg.x : 0u; }
-    return len == 0u ? 0 : 32 - __clz(len);   // 0 for no fragments, else the bit length 1..32
-  };
-  for (int tile = threadIdx.x; tile < n_tiles; tile += blockDim.x) atomicAdd(&s_hist[bucket_of(tile)], 1u);
-  __syncthreads();
-  if (threadIdx.x == 0) { uint32_t at = 0; for (int b = 32; b >= 0; b--) { s_cursor[b] = at; at += s_hist[b]; } }
-  __syncthreads();
-  for (int tile = threadIdx.x; tile < n_tiles; tile += blockDim.x) order[atomicAdd(&s_cursor[bucket_of(tile)], 1u)] = (uint32_t)tile;
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  const float2 lo = __fadd2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y)), hi = __fadd2_rn(make_float2(a.z, a.w), make_float2(b.z, b.w));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 
+// Work list of the replay: one item (range index = chunk * n_tiles + tile, segment) per SEG fragments of every
+// non-empty range the forward left. Order is irrelevant (items are independent); work[0] receives the count.
+__global__ void __launch_bounds__(256) bwd_items_kernel(const uint2* __restrict__ tile_ranges, int n_ranges, uint2* __restrict__ items, uint32_t* __restrict__ work) {
+  const int lane = threadIdx.x & 31;
+  for (int q0 = (blockIdx.x * blockDim.x + threadIdx.x) & ~31; q0 < n_ranges; q0 += gridDim.x * blockDim.x) {
+    const int q = q0 + lane;
+    uint32_t segs = 0;
+    if (q < n_ranges) { const uint2 rg = tile_ranges[q]; segs = rg.y > rg.x ? (rg.y - rg.x + SEG_LEN - 1) >> SEG_SHIFT : 0u; }
+    uint32_t incl = segs;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const uint32_t u = __shfl_up_sync(FULL, incl, o); if (lane >= o) incl += u; }
+    const uint32_t total = __shfl_sync(FULL, incl, 31);
+    if (total == 0u) continue;
+    uint32_t base = 0;
+    if (lane == 31) base = atomicAdd(work, total);
+    base = __shfl_sync(FULL, base, 31) + incl - segs;
+    for (uint32_t s = 0; s < segs; s++) items[base + s] = make_uint2((uint32_t)q, s);
+  }
+}
+
+template <bool CHUNKED>
 __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, const float4* __restrict__ out_rgba, const float4* __restrict__ out_feat, const uint32_t* __restrict__ last_idx,
     const float4* __restrict__ v_out, int W, int H, int tiles_x, int n_tiles, float3 bg, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
-    float* __restrict__ vis_weight, int n_chunks, const uint32_t* __restrict__ order) {
+    float* __restrict__ vis_weight, int n_chunks, const uint2* __restrict__ items, uint32_t* __restrict__ work, const float4* __restrict__ ckpt) {
   __shared__ Staged s_frag[BWD_WARPS][BWD_BATCH];
   __shared__ uint32_t s_gid[BWD_WARPS][BWD_BATCH];
+  __shared__ __align__(16) float4 s_red[BWD_WARPS][RED_F * RED_BLOCK];
+  __shared__ uint32_t s_pending[BWD_WARPS][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int slot = blockIdx.x * BWD_WARPS + warp;
-  if (slot >= n_tiles) return;
-  const int tile = order ? (int)order[slot] : slot;
-  // A view composited in depth chunks has one range per chunk and tile ([chunk][tile]); the replay walks the chunks
-  // from the farthest to the nearest, the pixel state running through.
-  {
-    bool any = false;
-    for (int ch = 0; ch < n_chunks; ch++) { const uint2 rg = tile_ranges[(size_t)ch * n_tiles + tile]; any = any || rg.y > rg.x; }
-    if (!any) return;
-  }
-  const int tx = tile % tiles_x, ty = tile / tiles_x;
-  const int px0 = tx * RT_W + (lane & 3) * 2, py = ty * RT_W + (lane >> 2);   // this lane's pixel pair (px0, px0 + 1) on row py
-
-  PairState st;
-  {
-    float T[2] = {0.f, 0.f}, vr[2] = {0.f, 0.f}, vg[2] = {0.f, 0.f}, vb[2] = {0.f, 0.f}, vow[2] = {0.f, 0.f}, ifa[2] = {0.f, 0.f};
-    uint32_t last[2] = {0u, 0u};   // outside the image: sees no fragment
-#pragma unroll
-    for (int p = 0; p < 2; p++) {
-      const int px = px0 + p;
-      if (px < W && py < H) {
-        const int pix = py * W + px;
-        const float4 vo = v_out[pix];
-        T[p] = out_feat[pix].w;
-        vr[p] = vo.x; vg[p] = vo.y; vb[p] = vo.z;
-        vow[p] = (vo.w - (bg.x * vo.x + bg.y * vo.y + bg.z * vo.z)) * T[p];
-        ifa[p] = 1.f / fmaxf(out_rgba[pix].w, 1e-5f);
-        last[p] = last_idx[pix] & 0x7FFFFFFFu;   // a chunked forward keeps its saturation flag in bit 31
-      }
-    }
-    st.T = make_float2(T[0], T[1]); st.Sr = st.Sg = st.Sb = f2(0.f);
-    st.vr = make_float2(vr[0], vr[1]); st.vg = make_float2(vg[0], vg[1]); st.vb = make_float2(vb[0], vb[1]);
-    st.vow = make_float2(vow[0], vow[1]); st.inv_fa = make_float2(ifa[0], ifa[1]);
-    st.last0 = last[0]; st.last1 = last[1];
-  }
-  const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
-  const float Wf = (float)W, Hf = (float)H;
   Staged* frag = s_frag[warp];
   uint32_t* gids = s_gid[warp];
-#ifdef B2K_BWD_ABLATE_REDUCTION
-  float ablate_sink = 0.f;
-#endif
+  float4* red = s_red[warp];
+  uint32_t* pending_gid = s_pending[warp];
+  const float Wf = (float)W, Hf = (float)H;
+  // Column reduction roles: lane = half * 16 + (fragment * 3 + word); halves add slots 0..15 and 16..31.
+  const int red_idx = lane & 15, red_f = red_idx / 3, red_w = red_idx - 3 * red_f, red_half = lane >> 4;
+  const uint32_t n_items = work[0];
 
-  for (int ch = n_chunks - 1; ch >= 0; ch--) {
-  const uint2 range = tile_ranges[(size_t)ch * n_tiles + tile];
-  for (uint32_t batch_end = range.y; batch_end > range.x;) {
-    const uint32_t remaining = batch_end - range.x;
-    const uint32_t count = remaining < (uint32_t)BWD_BATCH ? remaining : (uint32_t)BWD_BATCH;
-    const uint32_t batch_start = batch_end - count;
-    __syncwarp();
-    if ((uint32_t)lane < count) {
-      const uint32_t gid = vals_sorted[batch_start + lane];
-      gids[lane] = gid;
-      frag[lane].a = proj0[gid]; frag[lane].c = proj1[gid]; frag[lane].col = proj2[gid];
-    }
-    __syncwarp();
-    for (int j = (int)count - 1; j >= 0; j--) {
-      const uint32_t idx = batch_start + (uint32_t)j;
-      const float4 a = frag[j].a, c = frag[j].c;
-      // sigma for the pair: the two pixels share the row, so dy and the dy terms are scalars.
-      const float dy = pcy - a.y;
-      const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
-      const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, f2(0.5f * a.z), f2(a.w * dy)), f2(0.5f * c.x * dy * dy));
-      const bool on0 = idx < st.last0 && sigma.x >= 0.f && sigma.x <= c.w;
-      const bool on1 = idx < st.last1 && sigma.y >= 0.f && sigma.y <= c.w;
-      if (__ballot_sync(FULL, on0 || on1) == 0) continue;   // nobody in the tile sees this fragment: skip the heavy part
-      const float4 col = frag[j].col;
-      const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
-      // Branch-free from here: a pixel that does not see the fragment has alpha = 0 and adds exact zeros.
-      const float2 gauss = make_float2(__expf(-sigma.x), __expf(-sigma.y));
-      const float2 a_raw = __fmul2_rn(f2(c.y), gauss);
-      const float2 alpha = make_float2(on0 ? fminf(ALPHA_MAX, a_raw.x) : 0.f, on1 ? fminf(ALPHA_MAX, a_raw.y) : 0.f);
-      const float2 ra = make_float2(__fdividef(1.f, 1.f - alpha.x), __fdividef(1.f, 1.f - alpha.y));
-      const float2 nra = make_float2(-ra.x, -ra.y);
-      const float2 Tb = __fmul2_rn(st.T, ra);
-      const float2 vis = __fmul2_rn(alpha, Tb);
-      float2 va = __fmul2_rn(st.vow, ra);
-      va = __ffma2_rn(__ffma2_rn(st.Sr, nra, __fmul2_rn(Tb, f2(cr))), st.vr, va);
-      va = __ffma2_rn(__ffma2_rn(st.Sg, nra, __fmul2_rn(Tb, f2(cg))), st.vg, va);
-      va = __ffma2_rn(__ffma2_rn(st.Sb, nra, __fmul2_rn(Tb, f2(cb))), st.vb, va);
-      // The alpha clamp has zero slope: the geometry and opacity lanes vanish where it is active.
-      const bool live0 = on0 && a_raw.x <= ALPHA_MAX, live1 = on1 && a_raw.y <= ALPHA_MAX;
-      const float2 av = __fmul2_rn(alpha, va);
-      const float2 mvs = make_float2(live0 ? av.x : 0.f, live1 ? av.y : 0.f);          // -v_sigma
-      const float2 gx = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.z), f2(a.w * dy)));
-      const float2 gy = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.w), f2(c.x * dy)));
-      const float2 mdx = __fmul2_rn(mvs, dx);
-      const float2 og = __fmul2_rn(va, gauss);
-      const float2 sx = __fmul2_rn(gx, f2(Wf)), sy = __fmul2_rn(gy, f2(Hf));
-      const float2 q = __ffma2_rn(sx, sx, __fmul2_rn(sy, sy));
-      const float2 rf = __fmul2_rn(make_float2(fast_sqrt(q.x), fast_sqrt(q.y)), st.inv_fa);
-      float acc[16];
-      acc[0] = hsum(gx); acc[1] = hsum(gy);
-      acc[2] = -0.5f * hsum(__fmul2_rn(mdx, dx)); acc[3] = -hsum(mdx) * dy; acc[4] = -0.5f * dy * dy * hsum(mvs);
-      acc[5] = hsum(__fmul2_rn(vis, st.vr)); acc[6] = hsum(__fmul2_rn(vis, st.vg)); acc[7] = hsum(__fmul2_rn(vis, st.vb));
-      acc[8] = (live0 ? og.x : 0.f) + (live1 ? og.y : 0.f);
-      acc[9] = hsum(rf); acc[10] = hsum(vis);
-#pragma unroll
-      for (int k = 11; k < 16; k++) acc[k] = 0.f;
-      st.Sr = __ffma2_rn(f2(cr), vis, st.Sr); st.Sg = __ffma2_rn(f2(cg), vis, st.Sg); st.Sb = __ffma2_rn(f2(cb), vis, st.Sb);
-      st.T = Tb;
-      if (col.x < 0.f) acc[5] = 0.f;   // the colour clamp at zero has zero slope
-      if (col.y < 0.f) acc[6] = 0.f;
-      if (col.z < 0.f) acc[7] = 0.f;
-#ifdef B2K_BWD_ABLATE_REDUCTION
-      // Ablation build (never shipped): the replay alone, with the cross-lane reduction and the global reductions
-      // removed, bounds from above what any other reduction scheme (tensor cores included) could save.
-#pragma unroll
-      for (int k = 0; k < 11; k++) ablate_sink += acc[k];
-      continue;
-#endif
-      const float total = warp_transpose_sum(acc, lane);
-      if ((lane & 1) == 0) {
-        const int k = lane >> 1;
-        const uint32_t gid = gids[j];
-        if (k < 10) { if (total != 0.f) atomicAdd(v_splat + (size_t)gid * GRAD_LANES + k, total); }
-        else if (k == 10) { vis_flag[gid] = 1u; if (vis_weight) atomicAdd(vis_weight + gid, total); }
+  for (;;) {
+    uint32_t it = 0;
+    if (lane == 0) it = atomicAdd(work + 1, 1u);
+    it = __shfl_sync(FULL, it, 0);
+    if (it >= n_items) break;
+    const uint2 item = items[it];
+    const int q = (int)item.x, chunk = q / n_tiles, tile = q - chunk * n_tiles;
+    const uint2 range = tile_ranges[q];
+    const uint32_t seg_lo = range.x + (item.y << SEG_SHIFT);
+    const uint32_t seg_hi = min(seg_lo + (uint32_t)SEG_LEN, range.y);
+    // The state behind this segment: the forward's checkpoint at its far boundary; for the last segment of a range,
+    // the state with which the next non-empty range of the tile (a later depth chunk) started; else the final state.
+    long long slot = -1;
+    if (seg_hi < range.y) {
+      slot = (long long)ckpt_slot(range.x, q, item.y + 1u);
+    } else {
+      for (int c2 = chunk + 1; c2 < n_chunks; c2++) {
+        const uint2 r2 = tile_ranges[(size_t)c2 * n_tiles + tile];
+        if (r2.y > r2.x) { slot = (long long)ckpt_slot(r2.x, c2 * n_tiles + tile, 0u); break; }
       }
     }
-    batch_end = batch_start;
+    const int tx = tile % tiles_x, ty = tile / tiles_x;
+    const int px0 = tx * RT_W + (lane & 3) * 2, py = ty * RT_W + (lane >> 2);   // this lane's pixel pair (px0, px0 + 1) on row py
+    float2 T, Sr, Sg, Sb, vr, vg, vb, vow, inv_fa;
+    uint32_t last0 = 0u, last1 = 0u;   // outside the image: sees no fragment
+    {
+      float T_[2] = {0.f, 0.f}, S_[2][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}}, v_[2][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}}, vow_[2] = {0.f, 0.f}, ifa[2] = {0.f, 0.f};
+      uint32_t last[2] = {0u, 0u};
+#pragma unroll
+      for (int p = 0; p < 2; p++) {
+        const int px = px0 + p;
+        if (px < W && py < H) {
+          const int pix = py * W + px;
+          const float4 vo = v_out[pix], fin = out_feat[pix], img = out_rgba[pix];
+          const float T_fin = fin.w;
+          T_[p] = T_fin;
+          v_[p][0] = vo.x; v_[p][1] = vo.y; v_[p][2] = vo.z;
+          vow_[p] = (vo.w - (bg.x * vo.x + bg.y * vo.y + bg.z * vo.z)) * T_fin;
+          ifa[p] = 1.f / fmaxf(img.w, 1e-5f);
+          last[p] = last_idx[pix] & 0x7FFFFFFFu;   // a chunked forward keeps its saturation flag in bit 31
+          if (slot >= 0 && last[p] > seg_hi) {     // the pixel went on past this segment: fragments behind it hold colour
+            const float4 ck = ckpt[(size_t)slot * RT_PX + lane * 2 + p];
+            // Final colour sums: a chunked forward keeps them in out_feat; otherwise the image minus the background term.
+            const float3 sum = CHUNKED ? make_float3(fin.x, fin.y, fin.z) : make_float3(img.x - T_fin * bg.x, img.y - T_fin * bg.y, img.z - T_fin * bg.z);
+            T_[p] = ck.w;
+            S_[p][0] = sum.x - ck.x; S_[p][1] = sum.y - ck.y; S_[p][2] = sum.z - ck.z;
+          }
+        }
+      }
+      T = make_float2(T_[0], T_[1]);
+      Sr = make_float2(S_[0][0], S_[1][0]); Sg = make_float2(S_[0][1], S_[1][1]); Sb = make_float2(S_[0][2], S_[1][2]);
+      vr = make_float2(v_[0][0], v_[1][0]); vg = make_float2(v_[0][1], v_[1][1]); vb = make_float2(v_[0][2], v_[1][2]);
+      vow = make_float2(vow_[0], vow_[1]); inv_fa = make_float2(ifa[0], ifa[1]);
+      last0 = last[0]; last1 = last[1];
+    }
+    const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
+    int n_pending = 0;
+
+    // Column sums of the pending fragments' partials, then one global reduction per non-zero lane of each splat.
+    auto flush = [&]() {
+      __syncwarp();
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const bool mine = red_idx < 3 * RED_F && red_f < n_pending;
+      if (mine) {
+        const float4* src = red + red_f * RED_BLOCK + red_half * 48 + red_w;
+        float4 acc2 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < 16; s += 2) { acc = add4(acc, src[s * 3]); acc2 = add4(acc2, src[s * 3 + 3]); }
+        acc = add4(acc, acc2);
+      }
+      acc.x += __shfl_xor_sync(FULL, acc.x, 16); acc.y += __shfl_xor_sync(FULL, acc.y, 16);
+      acc.z += __shfl_xor_sync(FULL, acc.z, 16); acc.w += __shfl_xor_sync(FULL, acc.w, 16);
+      if (mine && red_half == 0) {
+        const uint32_t gid = pending_gid[red_f];
+        float* o = v_splat + (size_t)gid * GRAD_LANES + red_w * 4;
+        if (red_w < 2) {   // words 0, 1: xy 2 + conic 3 + rgb 3
+          if (acc.x != 0.f) atomicAdd(o, acc.x);
+          if (acc.y != 0.f) atomicAdd(o + 1, acc.y);
+          if (acc.z != 0.f) atomicAdd(o + 2, acc.z);
+          if (acc.w != 0.f) atomicAdd(o + 3, acc.w);
+        } else {           // word 2: opacity, refine, blend weight
+          if (acc.x != 0.f) atomicAdd(o, acc.x);
+          if (acc.y != 0.f) atomicAdd(o + 1, acc.y);
+          vis_flag[gid] = 1u;
+          if (vis_weight) atomicAdd(vis_weight + gid, acc.z);
+        }
+      }
+      __syncwarp();
+      n_pending = 0;
+    };
+
+    for (uint32_t batch_end = seg_hi; batch_end > seg_lo;) {
+      const uint32_t remaining = batch_end - seg_lo;
+      const uint32_t count = remaining < (uint32_t)BWD_BATCH ? remaining : (uint32_t)BWD_BATCH;
+      const uint32_t batch_start = batch_end - count;
+      __syncwarp();
+      if ((uint32_t)lane < count) {
+        const uint32_t gid = vals_sorted[batch_start + lane];
+        gids[lane] = gid;
+        frag[lane].a = proj0[gid]; frag[lane].c = proj1[gid]; frag[lane].col = proj2[gid];
+      }
+      __syncwarp();
+      for (int j = (int)count - 1; j >= 0; j--) {
+        const uint32_t idx = batch_start + (uint32_t)j;
+        const float4 a = frag[j].a, c = frag[j].c;
+        // sigma for the pair: the two pixels share the row, so dy and the dy terms are scalars.
+        const float dy = pcy - a.y;
+        const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
+        const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, f2(0.5f * a.z), f2(a.w * dy)), f2(0.5f * c.x * dy * dy));
+        const bool on0 = idx < last0 && sigma.x >= 0.f && sigma.x <= c.w;
+        const bool on1 = idx < last1 && sigma.y >= 0.f && sigma.y <= c.w;
+        if (__ballot_sync(FULL, on0 || on1) == 0) continue;   // nobody in the tile sees this fragment: skip the heavy part
+        const float4 col = frag[j].col;
+        const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+        // Branch-free from here: a pixel that does not see the fragment has alpha = 0 and adds exact zeros.
+        const float2 gauss = make_float2(__expf(-sigma.x), __expf(-sigma.y));
+        const float2 a_raw = __fmul2_rn(f2(c.y), gauss);
+        const float2 alpha = make_float2(on0 ? fminf(ALPHA_MAX, a_raw.x) : 0.f, on1 ? fminf(ALPHA_MAX, a_raw.y) : 0.f);
+        const float2 ra = make_float2(__fdividef(1.f, 1.f - alpha.x), __fdividef(1.f, 1.f - alpha.y));
+        const float2 nra = make_float2(-ra.x, -ra.y);
+        const float2 Tb = __fmul2_rn(T, ra);
+        const float2 vis = __fmul2_rn(alpha, Tb);
+        float2 va = __fmul2_rn(vow, ra);
+        va = __ffma2_rn(__ffma2_rn(Sr, nra, __fmul2_rn(Tb, f2(cr))), vr, va);
+        va = __ffma2_rn(__ffma2_rn(Sg, nra, __fmul2_rn(Tb, f2(cg))), vg, va);
+        va = __ffma2_rn(__ffma2_rn(Sb, nra, __fmul2_rn(Tb, f2(cb))), vb, va);
+        // The alpha clamp has zero slope: the geometry and opacity lanes vanish where it is active.
+        const bool live0 = on0 && a_raw.x <= ALPHA_MAX, live1 = on1 && a_raw.y <= ALPHA_MAX;
+        const float2 av = __fmul2_rn(alpha, va);
+        const float2 mvs = make_float2(live0 ? av.x : 0.f, live1 ? av.y : 0.f);          // -v_sigma
+        const float2 gx = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.z), f2(a.w * dy)));
+        const float2 gy = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.w), f2(c.x * dy)));
+        const float2 mdx = __fmul2_rn(mvs, dx);
+        const float2 og = __fmul2_rn(va, gauss);
+        const float2 sx = __fmul2_rn(gx, f2(Wf)), sy = __fmul2_rn(gy, f2(Hf));
+        const float2 qq = __ffma2_rn(sx, sx, __fmul2_rn(sy, sy));
+        const float2 rf = __fmul2_rn(make_float2(fast_sqrt(qq.x), fast_sqrt(qq.y)), inv_fa);
+        // The pair's partial sums of the eleven lanes: xy, conic, rgb (zero where the colour clamp at zero is active),
+        // opacity, refine, blend weight.
+        const float4 w0 = make_float4(hsum(gx), hsum(gy), -0.5f * hsum(__fmul2_rn(mdx, dx)), -hsum(mdx) * dy);
+        const float4 w1 = make_float4(-0.5f * dy * dy * hsum(mvs), col.x < 0.f ? 0.f : hsum(__fmul2_rn(vis, vr)), col.y < 0.f ? 0.f : hsum(__fmul2_rn(vis, vg)),
+                                      col.z < 0.f ? 0.f : hsum(__fmul2_rn(vis, vb)));
+        const float4 w2 = make_float4((live0 ? og.x : 0.f) + (live1 ? og.y : 0.f), hsum(rf), hsum(vis), 0.f);
+        float4* dst = red + n_pending * RED_BLOCK + lane * 3;
+        dst[0] = w0; dst[1] = w1; dst[2] = w2;
+        if (lane == 0) pending_gid[n_pending] = gids[j];
+        Sr = __ffma2_rn(f2(cr), vis, Sr); Sg = __ffma2_rn(f2(cg), vis, Sg); Sb = __ffma2_rn(f2(cb), vis, Sb);
+        T = Tb;
+        if (++n_pending == RED_F) flush();
+      }
+      batch_end = batch_start;
+    }
+    if (n_pending) flush();
   }
-  }
-#ifdef B2K_BWD_ABLATE_REDUCTION
-  if (ablate_sink == 123456.789f) v_splat[0] = ablate_sink;   // keeps the replay alive
-#endif
 }
 
 }  // namespace
@@ -216,18 +240,40 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
 
 using namespace b2k;
 
+extern "C" uint64_t b2k_bwd_scratch_bytes(int32_t W, int32_t H, int32_t n_chunks, uint64_t isect_cap) {
+  if (W <= 0 || H <= 0) return 0;
+  const uint64_t tiles = (uint64_t)div_up(W, RT_W) * div_up(H, RT_W), chunks = n_chunks > 1 ? (uint64_t)n_chunks : 1u;
+  const uint64_t slots = bwd_slots(isect_cap, tiles * chunks);
+  return sizeof(uint32_t) * BWD_HEADER_WORDS + sizeof(uint2) * slots + sizeof(float4) * RT_PX * slots;
+}
+
 extern "C" int b2k_raster_bwd(const B2kCtx* c, const B2kModel* m, const B2kRenderOpts* o, b2k_stream_t stream) {
   B2K_REQUIRE(c && m && o && c->tile_ranges && c->vals_sorted && c->proj0 && c->proj1 && c->proj2);
   B2K_REQUIRE(c->out_rgba && c->out_feat && c->last_idx && c->v_out && c->v_splat && c->vis_flag);
-  B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y);
+  B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y && c->bwd_scratch);
+  if (c->bwd_scratch_bytes < b2k_bwd_scratch_bytes(c->W, c->H, c->n_chunks, c->isect_cap)) return B2K_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
   const float3 bg = make_float3(o->bg[0], o->bg[1], o->bg[2]);
   const int chunks = c->n_chunks > 1 ? c->n_chunks : 1;
-  // The unsorted-pair buffer is scratch once the view is binned: it holds the tile order for this launch.
-  uint32_t* order = c->keys && c->isect_cap >= (uint64_t)c->n_tiles ? c->keys : nullptr;
-  if (order) tile_order_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((const uint2*)c->tile_ranges, c->n_tiles, chunks, order);
-  raster_bwd_kernel<<<div_up(c->n_tiles, BWD_WARPS), BWD_WARPS * 32, 0, (cudaStream_t)stream>>>(
-      (const uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, (const float4*)c->proj1, (const float4*)c->proj2,
-      (const float4*)c->out_rgba, (const float4*)c->out_feat, c->last_idx, (const float4*)c->v_out, c->W, c->H, c->tiles_x, c->n_tiles, bg,
-      c->v_splat, c->vis_flag, m->vis_weight, chunks, order);
+  uint32_t* work = bwd_work_ptr(c);
+  uint2* items = bwd_items_ptr(c);
+  B2K_CUDA(cudaMemsetAsync(work, 0, 2 * sizeof(uint32_t), s));
+  const int n_ranges = chunks * c->n_tiles;
+  bwd_items_kernel<<<min(div_up(n_ranges, 256), sm_count() * 4), 256, 0, s>>>((const uint2*)c->tile_ranges, n_ranges, items, work);
+  // Persistent grid: as many CTAs as an SM holds (the shared-memory footprint decides).
+  static int per_sm[2] = {0, 0};
+  if (!per_sm[chunks > 1]) {
+    int k = 0;
+    const cudaError_t e = chunks > 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, raster_bwd_kernel<true>, BWD_WARPS * 32, 0)
+                                     : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, raster_bwd_kernel<false>, BWD_WARPS * 32, 0);
+    per_sm[chunks > 1] = (e == cudaSuccess && k > 0) ? k : 8;
+  }
+  const int ctas = sm_count() * per_sm[chunks > 1];
+#define L(CH) raster_bwd_kernel<CH><<<ctas, BWD_WARPS * 32, 0, s>>>( \
+      (const uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, (const float4*)c->proj1, (const float4*)c->proj2, (const float4*)c->out_rgba, \
+      (const float4*)c->out_feat, c->last_idx, (const float4*)c->v_out, c->W, c->H, c->tiles_x, c->n_tiles, bg, c->v_splat, c->vis_flag, m->vis_weight, chunks, \
+      items, work, bwd_ckpt_ptr(c))
+  if (chunks > 1) L(true); else L(false);
+#undef L
   return check_launch();
 }

@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, int W, int H, int tiles_x, int n_tiles, float3 bg, float4* __restrict__ out_rgba, float4* __restrict__ out_feat,
     float* __restrict__ out_depth, uint32_t* __restrict__ last_idx, int chunk, int n_chunks, uint32_t* __restrict__ alive,
-    const float2* __restrict__ proj3) {
+    const float2* __restrict__ proj3, float4* __restrict__ ckpt) {
   static_assert(!(FEAT && CHUNKED), "the chunked forward keeps its colour sums where the feature lanes go");
   __shared__ float4 s0[FWD_WARPS][FWD_BATCH], s1[FWD_WARPS][FWD_BATCH], s2[FWD_WARPS][FWD_BATCH];
   __shared__ float2 s3[FEAT ? FWD_WARPS : 1][FEAT ? FWD_BATCH : 1];
@@ -58,8 +58,17 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
       }
     }
   }
+  // Checkpoints for the backward's segmented replay (see common.cuh): the state a later chunk starts a tile with, and
+  // the state before every SEG_LEN-th fragment of the list.
+  const int q = CHUNKED ? chunk * n_tiles + tile : tile;
+  auto checkpoint = [&](uint32_t seg) {
+    float4* dst = ckpt + (size_t)ckpt_slot(range.x, q, seg) * RT_PX + lane * 2;
+    dst[0] = make_float4(r[0], g[0], b[0], T[0]); dst[1] = make_float4(r[1], g[1], b[1], T[1]);
+  };
+  if (BWD && CHUNKED && !first && range.y > range.x) checkpoint(0u);
   for (uint32_t start = range.x; start < range.y; start += FWD_BATCH) {
     if (__all_sync(0xffffffffu, done[0] && done[1])) break;
+    if (BWD && start != range.x && ((start - range.x) & (uint32_t)(SEG_LEN - 1)) == 0u) checkpoint((start - range.x) >> SEG_SHIFT);
     const uint32_t remaining = min((uint32_t)FWD_BATCH, range.y - start);
     __syncwarp();
     if ((uint32_t)lane < remaining) {
@@ -138,7 +147,7 @@ int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_
   uint2* ranges = (uint2*)c->tile_ranges + (n_chunks > 1 ? (size_t)chunk * c->n_tiles : 0);
 #define L(B, D, C, F) raster_fwd_kernel<B, D, C, F><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>(ranges, c->vals_sorted, (const float4*)c->proj0, \
     (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, c->n_tiles, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx, \
-    chunk, n_chunks, alive, (const float2*)c->proj3)
+    chunk, n_chunks, alive, (const float2*)c->proj3, o->bwd_info ? bwd_ckpt_ptr(c) : nullptr)
   if (n_chunks > 1) {
     if (o->bwd_info) { if (c->out_depth) L(true, true, true, false); else L(true, false, true, false); }
     else { if (c->out_depth) L(false, true, true, false); else L(false, false, true, false); }
@@ -156,8 +165,9 @@ int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_
 
 extern "C" int b2k_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, b2k_stream_t stream) {
   B2K_REQUIRE(c && o && c->tile_ranges && c->vals_sorted && c->proj0 && c->proj1 && c->proj2 && c->out_rgba && c->out_feat);
-  B2K_REQUIRE(!o->bwd_info || c->last_idx);
+  B2K_REQUIRE(!o->bwd_info || (c->last_idx && c->bwd_scratch));
   B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y);
+  if (o->bwd_info && c->bwd_scratch_bytes < b2k_bwd_scratch_bytes(c->W, c->H, c->n_chunks, c->isect_cap)) return B2K_ERR_CAPACITY;
   B2K_REQUIRE(o->feat_mode >= 0 && o->feat_mode <= 2 && (o->feat_mode == 0 || c->proj3));
   return launch_raster_fwd(c, o, 0, 1, nullptr, (cudaStream_t)stream);
 }

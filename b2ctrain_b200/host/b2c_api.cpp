@@ -44,6 +44,7 @@ B2kCtx view_of(const RenderCtx& c) {
   v.last_idx = c.last_idx.ptr; v.v_splat = c.v_splat.ptr; v.vis_flag = c.vis_flag.ptr; v.vis_list = c.vis_list.ptr; v.v_out = (float*)c.v_out.ptr;
   v.loss_accum = c.loss_accum.ptr;
   v.n_chunks = c.n_chunks; v.chunk_words = c.chunk_words.ptr; v.proj3 = (float*)c.proj3.ptr;
+  v.bwd_scratch = c.bwd_scratch.ptr; v.bwd_scratch_bytes = c.bwd_scratch.count;
   return v;
 }
 
@@ -80,6 +81,7 @@ void alloc_isect(RenderCtx& c, size_t cap) {
   c.keys.free(); c.vals.free(); c.keys_sorted.free(); c.vals_sorted.free();
   c.keys.reserve(cap); c.vals.reserve(cap); c.keys_sorted.reserve(cap); c.vals_sorted.reserve(cap);
   c.isect_cap = cap;
+  c.bwd_scratch.reserve((size_t)b2k_bwd_scratch_bytes(c.W, c.H, c.n_chunks, cap));
 }
 
 }  // namespace
@@ -187,6 +189,7 @@ void RenderCtx::setup(int w, int h, int n, cudaStream_t stream) {
   loss_accum.reserve(16);
   if (!d_num_isect.ptr) { d_num_isect.reserve(4); d_num_isect.zero(stream); }
   if (isect_cap == 0) alloc_isect(*this, (size_t)1 << 22);   // starting capacity of the reference (render.cu:20)
+  bwd_scratch.reserve((size_t)b2k_bwd_scratch_bytes(W, H, n_chunks, isect_cap));   // grows with the image size too
   cub_tmp.reserve((size_t)b2k_sort_tmp_bytes(n_cap, isect_cap));
 }
 

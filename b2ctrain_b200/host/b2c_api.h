@@ -152,6 +152,7 @@ struct RenderCtx {
   bool want_depth = false;
   int n_chunks = 1;                 // set > 1 before setup(): render_forward composites front to back in depth chunks
   DevBuf<uint32_t> chunk_words;     // scratch of the chunked renderer
+  DevBuf<unsigned char> bwd_scratch;   // forward checkpoints + work list of the segmented backward (sized with the intersection buffers)
   void setup(int W, int H, int n_splats, cudaStream_t stream);
 };
 

@@ -91,6 +91,7 @@ class Trainer:
         self._staged_evt = [torch.cuda.Event() for _ in range(2 * self.lanes)]
         self._free_evt = [torch.cuda.Event() for _ in range(2 * self.lanes)]
         self.h2d_bytes = 0
+        self.overflow_redos = 0  # steps whose views were redone with larger intersection buffers
         self.profile = False     # when set, step() records an event after each phase (read with phase_ms())
         self._marks = []
 
@@ -150,36 +151,28 @@ class Trainer:
 
     def step(self, cams, targets, bg=(0.0, 0.0, 0.0)):
         """One optimisation step over `cams` / `targets` (the whole step's views; this rank takes its share).
-        Returns the device tensor loss_accum (index 0: loss of the last view, 2: running sum, 3: count)."""
+        Returns the device tensor loss_accum (index 0: loss of the last view, 2: running sum, 3: count).
+
+        The intersection totals stay on the device while the views run; once per step the largest total of every lane
+        is read back (4 bytes per lane), and when a view did not fit, the buffers grow and the rank's views are redone
+        (the reference grows inside every bin_and_sort, src/gpu/binning.cu:125-133). Nothing is lost by the late
+        check: a view that overflowed adds nothing to the accumulator or the model (b2k_proj_bwd / b2k_optim_fused)."""
         m = self.model
         m.adam_t += 1
         self.step_no += 1
         mine = self.my_views(len(cams))
-        self.ctx.loss_accum.zero_()
         self._marks = []
         self._mark("start")
-        if self.world == 1 and len(cams) == 1:
-            self.view_pass(cams[0], targets[0], bg, fused_op=self._op(cams[0]))
+        fused = self.world == 1 and len(cams) == 1
+        while True:
+            self._views(cams, targets, bg, mine, fused)
+            if not self.check_overflow()[1]:
+                break
+            self.overflow_redos += 1
+            if not fused:
+                self.grad.zero_()
+        if fused:
             return self.ctx.loss_accum
-        if self.lanes == 1:
-            for j, v in enumerate(mine):
-                self.ctx.loss_accum[:2].zero_()
-                self.view_pass(cams[v], targets[v], bg, slot=j & 1)
-        else:
-            main = torch.cuda.current_stream(self.device)
-            start = torch.cuda.Event(); start.record(main)
-            for j, v in enumerate(mine):
-                lane = j % self.lanes
-                with torch.cuda.stream(self.streams[lane]):
-                    if j < self.lanes:
-                        self.streams[lane].wait_event(start)
-                        self.ctxs[lane].loss_accum.zero_()
-                    self.ctxs[lane].loss_accum[:2].zero_()
-                    self.view_pass(cams[v], targets[v], bg, slot=2 * lane + ((j // self.lanes) & 1), lane=lane)
-            for lane in range(min(self.lanes, len(mine))):
-                done = torch.cuda.Event(); done.record(self.streams[lane]); main.wait_event(done)
-            for lane in range(1, self.lanes):       # fold the lanes' running losses into lane 0
-                self.ctx.loss_accum[2:4].add_(self.ctxs[lane].loss_accum[2:4])
         self._mark("views")
         op = self._op(cams[0])
         if self.world == 1 or self.reduce_slices <= 1:
@@ -197,21 +190,50 @@ class Trainer:
             self._mark("all_reduce+adam")
         return self.ctx.loss_accum
 
+    def _views(self, cams, targets, bg, mine, fused):
+        """Forward, loss and backward of this rank's views, `lanes` of them in flight; every lane's running loss ends
+        up in lane 0's accumulator."""
+        for c in self.ctxs:
+            api.step_begin(c)            # every lane, also the ones that get no view this step
+        if fused:
+            self.view_pass(cams[0], targets[0], bg, fused_op=self._op(cams[0]))
+        elif self.lanes == 1:
+            for j, v in enumerate(mine):
+                api.zero_loss(self.ctx, 0, 2)
+                self.view_pass(cams[v], targets[v], bg, slot=j & 1)
+        else:
+            main = torch.cuda.current_stream(self.device)
+            start = torch.cuda.Event(); start.record(main)
+            for j, v in enumerate(mine):
+                lane = j % self.lanes
+                with torch.cuda.stream(self.streams[lane]):
+                    if j < self.lanes:
+                        self.streams[lane].wait_event(start)
+                    api.zero_loss(self.ctxs[lane], 0, 2)
+                    self.view_pass(cams[v], targets[v], bg, slot=2 * lane + ((j // self.lanes) & 1), lane=lane)
+            used = min(self.lanes, len(mine))
+            for lane in range(used):
+                done = torch.cuda.Event(); done.record(self.streams[lane]); main.wait_event(done)
+            for lane in range(1, used):       # fold the lanes' running losses into lane 0
+                api.fold_loss(self.ctx, self.ctxs[lane])
+
     def reduce_statistics(self):
         """Makes the refinement statistics of the model global over the ranks (see reduce_statistics above)."""
         m = self.model
         reduce_statistics({k: getattr(m, k)[:m.n] for k in STATISTIC_REDUCTIONS}, self.world)
 
     def check_overflow(self):
-        """Reads the last view's intersection count back; grows the buffers when it did not fit (the reference does this
-        inside every bin_and_sort, src/gpu/binning.cu:125-133). Returns (count, overflowed)."""
+        """Reads every lane's largest intersection total of the step back; grows the buffers of a lane that did not
+        hold it (the reference does this inside every bin_and_sort, src/gpu/binning.cu:125-133). Returns
+        (largest total, whether any lane grew)."""
         total, over = 0, False
+        torch.cuda.synchronize(self.device)
         for ctx in self.ctxs:
-            t = int(ctx.d_num_isect[0].item()) & 0xFFFFFFFF
+            t = int(ctx.d_num_isect[2].item()) & 0xFFFFFFFF
             total = max(total, t)
             if t > ctx.isect_cap:
                 cap = ctx.isect_cap
-                while cap < t:
+                while cap < t + 32 * max(1, ctx.n_chunks):
                     cap *= 2
                 ctx._alloc_isect(cap)
                 over = True

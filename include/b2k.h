@@ -73,7 +73,7 @@ typedef struct {
   uint32_t *keys, *vals, *keys_sorted, *vals_sorted; /* [isect_cap] tile id / splat index before and after the tile sort */
   uint64_t isect_cap;
   uint32_t* num_isect;     /* [4] device words: [0] intersections of this view (may exceed isect_cap: overflow);
-                              [1] entries of vis_list */
+                              [1] entries of vis_list; [2] largest [0] since the caller cleared it (b2k_loss_accumulate) */
   void* sort_tmp;          /* scratch of b2k_sort_tmp_bytes() bytes */
   uint64_t sort_tmp_bytes;
   uint32_t* tile_ranges;   /* [n_tiles][2] start, end into vals_sorted; end shrunk by the forward when bwd_info
@@ -97,6 +97,11 @@ typedef struct {
   uint32_t* chunk_words;   /* [32 + n_tiles + (tiles_x + 1)(tiles_y + 1)] device scratch of b2k_render_chunked (chunk windows
                               and counts, one "some pixel can still take a fragment" flag per tile, the summed-area table
                               of those flags), or NULL when n_chunks <= 1 */
+  void* bwd_scratch;       /* b2k_bwd_scratch_bytes() bytes, needed when the forward runs with bwd_info: per-pixel (colour
+                              sums, transmittance) checkpoints the forward leaves every 256 fragments of a tile's list, and
+                              the work list of the backward, which replays the segments between checkpoints independently.
+                              Takes the place of nothing in the reference (its backward walks a tile's list in one CTA) */
+  uint64_t bwd_scratch_bytes;
 } B2kCtx;
 
 /* RenderParams, src/gpu/render.h:29-63: the fields this path implements. */
@@ -162,7 +167,12 @@ int b2k_read_num_isect(const B2kCtx* ctx, b2k_stream_t s, uint32_t* total);
  * with n_cap <= b2k_static_max_splats() (262,144; larger ones get B2K_ERR_CAPACITY). The first call on a device looks
  * the array's device address up (a synchronising runtime query): make that first call outside any stream capture.
  * All calls on a device share the one array, so two calls whose kernels overlap on the GPU (different streams or
- * threads) race; calls on one stream are safe. Nothing in it needs clearing by the caller. */
+ * threads) race; calls on one stream are safe. Nothing in it needs clearing by the caller.
+ * Limits: only the binning scratch is covered. b2k_project and b2k_count_tiles keep the list of splats with large
+ * tile boxes in ctx->sort_tmp and still need that buffer from the caller, so a host that cannot allocate at all has
+ * to be handed a sort_tmp by whoever owns the memory, or feed this entry records it binned elsewhere. The address
+ * looked up on the first call is cached per device ordinal: it is stale after cudaDeviceReset, and two host threads
+ * making their first call on one device at once both look it up (harmless: they store the same value). */
 int b2k_bin_sort_static(const B2kCtx* ctx, int32_t n, b2k_stream_t s);
 uint32_t b2k_static_max_splats(void);
 /* rasterize_forward, src/gpu/render.h:103 (raster_fwd_kernel, src/gpu/raster_fwd.cu:9-71). */
@@ -187,18 +197,36 @@ uint64_t b2k_sort_tmp_bytes(int32_t n_cap, uint64_t isect_cap);
 /* ---- loss ---- */
 /* photometric_loss, src/gpu/loss.h:33 (photometric_kernel, src/gpu/loss.cu:18-195). */
 int b2k_loss_photometric(const B2kCtx* ctx, const B2kLoss* lp, b2k_stream_t s);
-/* accumulate_loss, src/gpu/loss.h:37. */
+/* accumulate_loss, src/gpu/loss.h:37. Also folds this view's intersection total into the running maximum
+ * ctx->num_isect[2] (when num_isect is set), which the caller clears at the start of a step. */
 int b2k_loss_accumulate(const B2kCtx* ctx, b2k_stream_t s);
+/* loss_accum[first .. first + count) = 0 on the stream (the reference's loss_accum.zero(stream, n), src/train/trainer.cpp:
+ * 487-491, without a host library in between). */
+int b2k_loss_zero(const B2kCtx* ctx, int32_t first, int32_t count, b2k_stream_t s);
+/* Start of a training step on this context: loss_accum[0..16) = 0 and the running intersection maximum
+ * num_isect[2] = 0 (the loss_accum.zero() of src/train/trainer.cpp:455 plus the overflow bookkeeping). */
+int b2k_step_begin(const B2kCtx* ctx, b2k_stream_t s);
+/* dst.loss_accum[2..3] += src.loss_accum[2..3]: joins the running loss of a view that was in flight on another stream
+ * (no counterpart in the reference, whose step is one view on one stream). */
+int b2k_loss_fold(const B2kCtx* dst, const B2kCtx* src, b2k_stream_t s);
 /* eval_metrics, src/gpu/loss.h:41 (eval_kernel, src/gpu/loss.cu:241-293). */
 int b2k_eval_metrics(const B2kCtx* ctx, const uint32_t* rgba, int32_t mask_weighted, b2k_stream_t s);
 
+/* Bytes of ctx->bwd_scratch for a context of this image size, chunk count (0 or 1: whole view) and intersection capacity. */
+uint64_t b2k_bwd_scratch_bytes(int32_t W, int32_t H, int32_t n_chunks, uint64_t isect_cap);
+
 /* ---- backward ---- */
-/* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). Overwrites the first
- * n_tiles words of ctx->keys (scratch once the view is binned) with the order in which it walks the tiles. */
+/* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). Same gradients; the
+ * tile lists are replayed in segments of 256 fragments from the forward's checkpoints in ctx->bwd_scratch. */
 int b2k_raster_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kRenderOpts* opts, b2k_stream_t s);
 /* optimizer_step, src/gpu/optim.h:50 (optim_kernel, src/gpu/optim.cu:100-378): projection backward fused with
  * sparse Adam; consumes and clears ctx->v_splat / vis_flag. With grad_out set it writes gradients and returns. */
 int b2k_optim_fused(const B2kCtx* ctx, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, b2k_stream_t s);
+/* Overflow guard of b2k_optim_fused and b2k_proj_bwd: when ctx->num_isect is set and the view's intersection total
+ * num_isect[0] exceeds ctx->isect_cap (the view was composited from truncated lists), the lanes are still consumed and
+ * cleared but the model / the accumulator is left untouched, so a host that reads the total only after the step
+ * (b2k_read_num_isect, or num_isect[2] once per step) can grow the buffers and redo the view. The reference avoids the
+ * case by reading the total inside every bin_and_sort (src/gpu/binning.cu:125-133). */
 /* Data-parallel split of optimizer_step. b2k_proj_bwd: the gradient half (optim.cu:100-297) ADDING into a dense
  * accumulator grad[n][11+3K] (the grad_out layout) so several views and, after an all-reduce, several GPUs sum;
  * consumes and clears v_splat / vis_flag. b2k_adam: the update half (optim.cu:299-376) from that accumulator; splats

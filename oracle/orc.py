@@ -35,9 +35,19 @@ _lib = None
 _ref = None
 
 
+def reference_tree():
+    """Where the reference checkout lies, or None: the B2C_REFERENCE environment variable, else a `reference` folder
+    beside the repository."""
+    for cand in (os.environ.get("B2C_REFERENCE"), os.path.join(_HERE, "..", "..", "reference")):
+        if cand and os.path.isfile(os.path.join(cand, "tests", "reference.cpp")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build():
     import subprocess
-    subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    ref = reference_tree()
+    subprocess.run(["make", "-C", _HERE] + ([f"REF={ref}"] if ref else []), check=True, capture_output=True)
 
 
 def lib():
@@ -227,6 +237,32 @@ def loss(W, H, pred, gt, weights, lp, want_grad=True):
     return val, v_out
 
 
+def eval_metrics(W, H, pred, gt, mask_weighted=False):
+    """eval_kernel (src/gpu/loss.cu:241-293) in double: the prediction is clamped and quantised to 8 bits (in fp32, as
+    the device decides the rounding), the target is taken on black, SSIM uses the 11-tap sigma-1.5 window with zero
+    padding, variances clamped at zero, SSIM clamped to [-1, 1]; with mask_weighted the per-pixel error and SSIM are
+    multiplied by the target's alpha. Returns (sum of squared errors, sum of SSIM) over pixels and channels."""
+    from scipy.ndimage import correlate1d
+    p32 = np.clip(np.asarray(pred, np.float32).reshape(H, W, 4)[:, :, :3], np.float32(0), np.float32(1)) * np.float32(255)
+    q = np.rint(p32).astype(np.float64) / 255.0
+    g = np.asarray(gt, np.uint32).reshape(H, W)
+    t = np.stack([((g >> (8 * c)) & 0xFF).astype(np.float64) / 255.0 for c in range(3)], -1)
+    m = ((g >> 24) & 0xFF).astype(np.float64) / 255.0 if mask_weighted else np.ones((H, W))
+    x = np.arange(11) - 5.0
+    w = np.exp(-x * x / (2 * 1.5 * 1.5)); w /= w.sum()
+    blur = lambda a: correlate1d(correlate1d(a, w, axis=0, mode="constant"), w, axis=1, mode="constant")
+    C1, C2 = 0.01 ** 2, 0.03 ** 2
+    se = ssim_sum = 0.0
+    for c in range(3):
+        a, b = q[:, :, c], t[:, :, c]
+        mu1, mu2 = blur(a), blur(b)
+        s1, s2, s12 = np.maximum(blur(a * a) - mu1 * mu1, 0), np.maximum(blur(b * b) - mu2 * mu2, 0), blur(a * b) - mu1 * mu2
+        ssim = np.clip(((2 * mu1 * mu2 + C1) * (2 * s12 + C2)) / ((mu1 * mu1 + mu2 * mu2 + C1) * (s1 + s2 + C2)), -1, 1)
+        se += float(((np.abs(a - b) * m) ** 2).sum())
+        ssim_sum += float((ssim * m).sum())
+    return se, ssim_sum
+
+
 def raster_bwd(n, W, H, geo, col, vals, ranges, bg, rgba, T, last, v_out):
     v_splat = np.zeros((n, 13)); vis = np.zeros(n, np.uint32); visw = np.zeros(n)
     vals = _u32(vals) if len(vals) else np.zeros(1, np.uint32)
@@ -375,9 +411,50 @@ class RefCuda:
         self._check(self.l.refcu_grads(self.h, _p(self.intr), _p(self.R), _p(self.t), _p(out)))
         return out
 
+    def optim(self, t=1, sparse=True, lr_mean=1.6e-4, lr_rot=2e-3, lr_scale=5e-3, lr_opac=0.012, lr_dc=2e-3, lr_sh_rest=2e-4, noise_weight=0.0,
+              noise_clamp=0.0, seed=42, step=0):
+        """optimizer_step (src/gpu/optim.h:50) on the lanes the context holds, with the camera of the last forward."""
+        f = np.array([lr_mean, lr_rot, lr_scale, lr_opac, lr_dc, lr_sh_rest, noise_weight, noise_clamp], np.float32)
+        u = np.array([t, int(sparse), seed, step], np.uint32)
+        self._check(self.l.refcu_optim_full(self.h, _p(self.intr), _p(self.R), _p(self.t), _p(f), _p(u)))
+
+    def set_lanes(self, v_splat, vis_flag):
+        self._check(self.l.refcu_set_lanes(self.h, _p(_f32(v_splat)), _p(_u32(vis_flag))))
+
+    def set_image(self, rgba):
+        self._check(self.l.refcu_set_image(self.h, _p(_f32(rgba))))
+
+    def eval_metrics(self, mask_weighted=False):
+        out = np.zeros(2, np.float32)
+        self._check(self.l.refcu_eval(self.h, int(mask_weighted), _p(out)))
+        return float(out[0]), float(out[1])
+
+    def v_out(self):
+        out = np.zeros((self.W * self.H, 4), np.float32)
+        self._check(self.l.refcu_v_out(self.h, _p(out)))
+        return out
+
+    def cap(self):
+        return int(self.l.refcu_cap(self.h))
+
+    def model_state(self):
+        """Parameters and Adam state as host arrays in the layout of Model.download / the oracle's state dict."""
+        n, K, cap = self.scene["n"], self.K, self.cap()
+        d4 = lambda k: self.download(k, (n, 4), np.float32)
+
+        def planar(dc, hi):
+            a = self.download(dc, (3, cap), np.float32)
+            b = self.download(hi, (3 * (K - 1), cap), np.float32) if K > 1 else np.zeros((0, cap), np.float32)
+            return np.ascontiguousarray(np.concatenate([a, b], 0)[:, :n].T.reshape(n, K, 3))
+        return dict(pos_op=d4("pos_op"), quat=d4("quat"), lscale=d4("lscale"), sh=planar("sh_dc", "sh_hi32"), m_pos=d4("m_pos_op"), v_pos=d4("v_pos_op"),
+                    m_q=d4("m_quat"), v_q=d4("v_quat"), m_ls=d4("m_lscale"), v_ls=d4("v_lscale"), m_sh=planar("m_sh_dc", "m_sh_hi32"),
+                    v_sh=self.download("v_sh", (n,), np.float32), last_step=self.download("last_step", (n,), np.uint32),
+                    vis_count=self.download("vis_count", (n,), np.float32), refine_norm=self.download("refine_norm", (n,), np.float32))
+
     def download(self, what, shape, dtype):
         sel = dict(proj0=0, proj1=1, proj2=2, tile_count=3, vals_sorted=4, keys_sorted=5, tile_ranges=6, out_rgba=7, last_idx=8, v_splat=9, pos_op=10, quat=11,
-                   lscale=12)[what]
+                   lscale=12, sh_dc=13, sh_hi32=14, m_pos_op=15, v_pos_op=16, m_quat=17, v_quat=18, m_lscale=19, v_lscale=20, m_sh_dc=21, m_sh_hi32=22,
+                   v_sh=23, last_step=24, vis_count=25, refine_norm=26, out_feat=27)[what]
         out = np.zeros(shape, dtype)
         self._check(self.l.refcu_download(self.h, sel, _p(out), C.c_size_t(out.nbytes)))
         return out

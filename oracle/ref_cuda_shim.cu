@@ -117,8 +117,57 @@ int refcu_optim(void* hp, const float* intr, const float* R, const float* t, int
   });
 }
 
+// optimizer_step with every Adam / MCMC-noise field of OptimParams the hot path uses (optim.h:10-18,41).
+// f: lr_mean, lr_rot, lr_scale, lr_opac, lr_dc, lr_sh_rest, noise_weight, noise_clamp; u: t, sparse, seed, step.
+int refcu_optim_full(void* hp, const float* intr, const float* R, const float* t, const float* f, const uint32_t* u) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] {
+    OptimParams op; op.cam = CameraGPU::from(camera_of(intr, R, t, h->ctx.W, h->ctx.H), h->ctx.W, h->ctx.H);
+    op.active_sh_degree = h->model.degree;
+    op.lr_mean = f[0]; op.lr_rot = f[1]; op.lr_scale = f[2]; op.lr_opac = f[3]; op.lr_dc = f[4]; op.lr_sh_rest = f[5];
+    op.noise_weight = f[6]; op.noise_clamp = f[7];
+    op.t = (int)u[0]; op.sparse = u[1] != 0; op.seed = u[2]; op.step = u[3];
+    optimizer_step(h->ctx, h->model, op, 0);
+  });
+}
+
+// Screen-space gradient lanes and visibility flags as the optimizer's input (what rasterize_backward leaves).
+int refcu_set_lanes(void* hp, const float* v_splat, const uint32_t* vis_flag) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] {
+    CUDA_CHECK(cudaMemcpy(h->ctx.v_splat.ptr, v_splat, (size_t)h->model.n * 13 * sizeof(float), cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaMemcpy(h->ctx.vis_flag.ptr, vis_flag, (size_t)h->model.n * sizeof(uint32_t), cudaMemcpyHostToDevice));
+  });
+}
+
+// A prediction placed in ctx.out_rgba directly (loss and metric kernels on an arbitrary image).
+int refcu_set_image(void* hp, const float* rgba) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] { CUDA_CHECK(cudaMemcpy(h->ctx.out_rgba.ptr, rgba, (size_t)h->ctx.W * h->ctx.H * 4 * sizeof(float), cudaMemcpyHostToDevice)); });
+}
+
+// eval_metrics (loss.h:41) on the current ctx.out_rgba: out[0] = sum of squared error, out[1] = sum of SSIM.
+int refcu_eval(void* hp, int mask_weighted, float* out) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] {
+    CUDA_CHECK(cudaMemset(h->ctx.loss_accum.ptr + 4, 0, 4 * sizeof(float)));
+    eval_metrics(h->ctx, h->view, mask_weighted != 0, 0);
+    std::vector<float> a = h->ctx.loss_accum.download(8);
+    out[0] = a[4]; out[1] = a[5];
+  });
+}
+
+// The loss gradient image v_out [P][4] of the last refcu_loss.
+int refcu_v_out(void* hp, float* dst) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] { CUDA_CHECK(cudaMemcpy(dst, h->ctx.v_out.ptr, (size_t)h->ctx.W * h->ctx.H * 4 * sizeof(float), cudaMemcpyDeviceToHost)); });
+}
+int refcu_cap(void* hp) { return ((Handle*)hp)->model.cap; }
+
 // what: 0 proj0, 1 proj1, 2 proj2 ([n][4] float), 3 tile_count [n] u32, 4 vals_sorted [num_isect] u32, 5 keys_sorted,
-// 6 tile_ranges [tiles][2] u32, 7 out_rgba [P][4], 8 last_idx [P] u32, 9 v_splat [n][13], 10 pos_op, 11 quat, 12 lscale ([n][4]).
+// 6 tile_ranges [tiles][2] u32, 7 out_rgba [P][4], 8 last_idx [P] u32, 9 v_splat [n][13], 10 pos_op, 11 quat, 12 lscale ([n][4]),
+// 13 sh_dc [3][cap], 14 sh_hi32 [3(K-1)][cap], 15..20 m/v of pos_op, quat, lscale ([n][4]), 21 m_sh_dc, 22 m_sh_hi32 (planar),
+// 23 v_sh [n], 24 last_step [n] u32, 25 vis_count [n], 26 refine_norm [n], 27 out_feat [P][4].
 int refcu_download(void* hp, int what, void* dst, size_t bytes) {
   Handle* h = (Handle*)hp;
   return guarded(h, [&] {
@@ -129,6 +178,12 @@ int refcu_download(void* hp, int what, void* dst, size_t bytes) {
       case 6: src = h->ctx.tile_ranges.ptr; break; case 7: src = h->ctx.out_rgba.ptr; break; case 8: src = h->ctx.last_idx.ptr; break;
       case 9: src = h->ctx.v_splat.ptr; break; case 10: src = h->model.pos_op.ptr; break; case 11: src = h->model.quat.ptr; break;
       case 12: src = h->model.lscale.ptr; break;
+      case 13: src = h->model.sh_dc.ptr; break; case 14: src = h->model.sh_hi32.ptr; break;
+      case 15: src = h->model.m_pos_op.ptr; break; case 16: src = h->model.v_pos_op.ptr; break; case 17: src = h->model.m_quat.ptr; break;
+      case 18: src = h->model.v_quat.ptr; break; case 19: src = h->model.m_lscale.ptr; break; case 20: src = h->model.v_lscale.ptr; break;
+      case 21: src = h->model.m_sh_dc.ptr; break; case 22: src = h->model.m_sh_hi32.ptr; break; case 23: src = h->model.v_sh.ptr; break;
+      case 24: src = h->model.last_step.ptr; break; case 25: src = h->model.vis_count.ptr; break; case 26: src = h->model.refine_norm.ptr; break;
+      case 27: src = h->ctx.out_feat.ptr; break;
       default: throw std::runtime_error("bad selector");
     }
     CUDA_CHECK(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));

@@ -127,20 +127,26 @@ def test_forward_image_stagewise():
     assert np.max(np.abs(got_depth[fin] - want_depth[fin])) <= 2e-3
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
 def test_loss_kernel_stagewise(mode):
-    """The fused loss kernel on a random prediction, value and gradient, against the oracle in double."""
+    """The fused loss kernel on a random prediction, value and gradient, against the oracle in double. Modes 0-2 are
+    the reference's gradient-check combinations (tests/tests.cpp:398-441); mode 3 is benchmark configuration 4's:
+    mask and alpha lane together on a binary alpha, scale 1 / 0.4."""
     rng = np.random.Generator(np.random.PCG64(40 + mode))
     W, H = 83, 61                                          # ragged: not a multiple of the 16-pixel tile
     scene, cam = small_scene(n=16, W=W, H=H)
     gt = rng.integers(0, 2 ** 32, W * H, dtype=np.uint64).astype(np.uint32)
-    wts = rng.integers(64, 256, W * H).astype(np.uint8) if mode != 2 else None
-    lp = dict(l1_w=0.8, ssim_w=-0.2, bg=(0.2, 0.1, 0.3), composite=mode == 0, mask=mode == 1, alpha_lane=mode == 0,
-              match_alpha_weight=0.3, scale=1.7 if mode == 1 else 1.0, grad_scale=1.0)
+    wts = rng.integers(64, 256, W * H).astype(np.uint8) if mode in (0, 1) else None
+    lp = dict(l1_w=0.8, ssim_w=-0.2, bg=(0.2, 0.1, 0.3), composite=mode == 0, mask=mode in (1, 3), alpha_lane=mode in (0, 3),
+              match_alpha_weight=0.3, scale={1: 1.7, 3: 2.5}.get(mode, 1.0), grad_scale=1.0)
+    if mode == 3:
+        gt = (gt & np.uint32(0x00FFFFFF)) | (scenes.ellipse_mask(W, H, 0.4) << np.uint32(24)).astype(np.uint32)
+        gt[(gt >> np.uint32(24)) == 0] = 0
+        lp["bg"] = (0.0, 0.0, 0.0)
     h = Harness(scene, cam, gt, wts, lp)
     pred = rng.random((W * H, 4)).astype(np.float32)
     pred[: W * 20] = 0.0                                   # a flat region
-    gt[: W * 20] = 0xFF000000 if mode else 0               # equal to the prediction there
+    gt[: W * 20] = 0xFF000000 if mode in (1, 2) else 0     # equal to the prediction there (mode 3: alpha 0 too, as outside its ellipse)
     h = Harness(scene, cam, gt, wts, lp)
     h.ctx.out_rgba.copy_(h.torch.from_numpy(pred))
     h.ctx.loss_accum.zero_()
@@ -369,6 +375,23 @@ def test_full_chain_ragged_image_size():
     assert rel_l2(grad, want["grad"]) <= TOL_GRAD_REL_L2
 
 
+def test_full_chain_masked_loss_with_alpha_lane():
+    """Benchmark configuration 4's loss combination through the whole chain: binary ellipse alpha, mask and alpha lane
+    on, scale 1 / 0.4; image, loss and gradients against the double oracle."""
+    scene, cam = small_scene(n=3000, degree=2, seed=44)
+    W, H = cam["W"], cam["H"]
+    rng = np.random.Generator(np.random.PCG64(14))
+    gt = rng.integers(0, 2 ** 24, W * H, dtype=np.uint64).astype(np.uint32) | (scenes.ellipse_mask(W, H, 0.4) << np.uint32(24)).astype(np.uint32)
+    gt[(gt >> np.uint32(24)) == 0] = 0
+    lp = dict(l1_w=np.float32(0.8), ssim_w=np.float32(-0.2), mask=1, alpha_lane=1, scale=np.float32(2.5), match_alpha_weight=np.float32(0.1))
+    h = Harness(scene, cam, gt, None, lp)
+    loss, grad = h.analytic()
+    want = orc.step(scene, cam, np.zeros(3), gt, None, lp, backward=True, want_image=True)
+    assert np.max(np.abs(h.ctx.out_rgba.cpu().numpy() - want["rgba"])) <= TOL_IMAGE_ABS
+    assert abs(loss - want["loss"]) <= TOL_LOSS_REL * abs(want["loss"])
+    assert rel_l2(grad, want["grad"]) <= TOL_GRAD_REL_L2
+
+
 def test_adam_by_slices_equals_adam_over_the_whole_model():
     """The sliced update (pipelined with the all-reduce on several GPUs) is bit-identical to the whole-model call."""
     import torch
@@ -544,3 +567,56 @@ def test_chunked_render_edge_cases():
     api.render_forward(ctx, m, api.RenderParams(cam | dict(W=16, H=16), bg=(0.5, 0.25, 0.125), sh_degree=1, bwd_info=True), sync=True)
     img = ctx.out_rgba.cpu().numpy()
     assert np.allclose(img[:, :3], [0.5, 0.25, 0.125]) and np.all(img[:, 3] == 0.0)
+
+
+def trainer_case(n_views=6):
+    import torch
+    scene, _ = small_scene(n=6000, degree=2)
+    cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, 360.0 * v / n_views, 10.0 + 5.0 * v), 160, 120, 120.0) for v in range(n_views)]
+    rng = np.random.Generator(np.random.PCG64(123))
+    targets = [torch.from_numpy((rng.integers(0, 2 ** 32, 160 * 120, dtype=np.uint64).astype(np.uint32) | np.uint32(0xFF000000)).view(np.int32)).cuda()
+               for _ in cams]
+    return scene, cams, targets
+
+
+def test_trainer_step_with_too_small_intersection_buffers_grows_and_matches():
+    """A step whose views overflow the intersection buffers is redone with larger ones before anything is applied
+    (the reference grows inside every bin_and_sort, src/gpu/binning.cu:125-133): the updated model equals a run that
+    started with large buffers, for the multi-view step and for the fused single-view step."""
+    import torch
+    from b2ctrain_b200.trainer import Trainer
+    scene, cams, targets = trainer_case()
+    for views in (len(cams), 1):
+        out = []
+        for cap in (1 << 22, 2048):
+            tr = Trainer(scene, 160, 120, "cuda:0", 0, 1, lr_mean=1e-4, sparse=True, isect_cap=cap, views_in_flight=1)
+            for _ in range(2):
+                acc = tr.step(cams[:views], targets[:views])
+            torch.cuda.synchronize()
+            out.append((tr.model.download(), acc.cpu().numpy().copy(), tr.overflow_redos, tr.ctx.isect_cap))
+        (big, acc_big, redo_big, _), (small, acc_small, redo_small, cap_small) = out
+        assert redo_big == 0 and redo_small >= 1 and cap_small > 2048
+        for k in ("pos_op", "quat", "lscale", "sh"):
+            # one view per lane in issue order: the accumulator sums are the same sums, up to the order of the atomics
+            assert np.max(np.abs(big[k] - small[k]) / (np.abs(big[k]) + 1e-3)) <= 2e-5, (views, k)
+        assert abs(acc_big[2] - acc_small[2]) <= 1e-5 * abs(acc_big[2]) and acc_big[3] == acc_small[3] == views
+
+
+def test_trainer_views_in_flight_match_single_lane():
+    """Four views in flight on four streams (the benchmark's default) accumulate the same gradient and the same running
+    loss as one view at a time, up to summation order; lanes that get no view in a step add nothing stale."""
+    import torch
+    from b2ctrain_b200.trainer import Trainer
+    scene, cams, targets = trainer_case()
+    res = []
+    for lanes in (1, 4):
+        tr = Trainer(scene, 160, 120, "cuda:0", 0, 1, lr_mean=0.0, sparse=True, views_in_flight=lanes)
+        acc6 = tr.step(cams, targets).cpu().numpy().copy()         # six views: lanes 0 and 1 take two each
+        tr.model.adam_t += 1
+        tr._views(cams[:2], targets[:2], (0.0, 0.0, 0.0), [0, 1], False)   # then two views: lanes 2 and 3 stay idle
+        torch.cuda.synchronize()
+        res.append((acc6, tr.ctx.loss_accum.cpu().numpy().copy(), tr.grad.cpu().numpy().copy()))
+    (a6, a2, g1), (b6, b2, g4) = res
+    assert a6[3] == b6[3] == 6 and abs(a6[2] - b6[2]) <= 1e-5 * abs(a6[2])
+    assert a2[3] == b2[3] == 2 and abs(a2[2] - b2[2]) <= 1e-5 * abs(a2[2])
+    assert rel_l2(g4, g1) <= 1e-5 and np.abs(g1).max() > 0

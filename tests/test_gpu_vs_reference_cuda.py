@@ -43,17 +43,23 @@ def test_records_image_loss_and_gradients_match_the_reference_kernels():
     got, want = np.concatenate([p0, p1], 1)[both], np.concatenate([ref_p0, ref_p1], 1)[both]
     scale = np.abs(want) + np.array([1.0, 1.0, 0, 0, 0, 0, 0, 1.0])[None, :]
     scale[:, [2, 3, 4]] = np.abs(want[:, [2, 3, 4]]).max(1, keepdims=True)
-    assert np.max(np.abs(got - want) / scale) <= 1e-4          # the reference runs under --use_fast_math
-    assert np.mean(tc != ref_tc) < 2e-3                        # tile counts may differ on boundary tiles only
-    assert np.max(np.abs(h.ctx.out_rgba.cpu().numpy() - ref_img)) <= 1e-3
-    assert abs(loss - ref_loss) <= 1e-4 * abs(ref_loss)
-    assert rel_l2(grad, ref_grad) <= 2e-3                      # fp32 fast-math kernels on both sides of the comparison
+    err_rec, err_tc = float(np.max(np.abs(got - want) / scale)), float(np.mean(tc != ref_tc))
+    err_img, err_loss, err_grad = float(np.max(np.abs(h.ctx.out_rgba.cpu().numpy() - ref_img))), abs(loss - ref_loss) / abs(ref_loss), rel_l2(grad, ref_grad)
+    print(f"records {err_rec:.2e}, tile counts differing {err_tc:.2e}, image {err_img:.2e}, loss {err_loss:.2e}, grad_out rel L2 {err_grad:.2e}")
+    # Observed on B200: records 2.4e-6, no tile count differing, image 1.5e-6, loss 3.6e-7, grad_out 1.2e-6 (the reference
+    # runs under --use_fast_math); held with an order of magnitude of margin.
+    assert err_rec <= 2e-5
+    assert err_tc <= 1e-4                                      # a tile count may differ where the two records differ in the last bits
+    assert err_img <= 2e-5
+    assert err_loss <= 1e-5
+    assert err_grad <= 2e-5
 
 
 def test_binning_of_the_reference_records_matches_the_reference_lists():
     """The reference's own projection records go through the product's tile decisions, sort and ranges; the result is
-    compared with the reference's own bin_and_sort. Differences can only come from the reference's fast-math division
-    inside its tile test on boundary tiles: they are counted, and must be rare."""
+    compared with the reference's own bin_and_sort: the same pairs, in the same order. (The reference's tile test divides
+    under fast-math, src/gpu/splat_math.cuh:35-36, so a boundary tile could in principle fall the other way; on this
+    scene of 336,769 pairs none does.)"""
     scene, cam, gt = scene_and_view(n=30000, seed=9)
     n = scene["n"]
     ref = orc.RefCuda(scene, cam)
@@ -73,7 +79,7 @@ def test_binning_of_the_reference_records_matches_the_reference_lists():
     a = set(zip(keys.tolist(), vals.tolist())); b = set(zip(ref_keys.tolist(), ref_vals.tolist()))
     differing = len(a ^ b)
     print(f"intersections: product {I}, reference {I_ref}; differing (tile, splat) pairs: {differing}")
-    assert I > 100000 and differing <= 2e-4 * I
+    assert I > 100000 and I == I_ref and differing == 0        # on identical records the tile decisions and lists are identical
     # Order inside every tile: identical wherever the two lists hold the same pairs.
     common = a & b
     mine = [(k, v) for k, v in zip(keys.tolist(), vals.tolist()) if (k, v) in common]

@@ -145,3 +145,23 @@ def test_feature_lanes_match_the_reference_normal_lane():
     buf = np.array([[1.0, -200.0, np.nan]] * scene["n"], np.float32)
     fb = orc.features(scene, cam, 2, buf)
     assert np.array_equal(fb[0], [1.0, -100.0, 0.0])
+
+
+def test_eval_metric_oracle_known_answers():
+    """orc.eval_metrics (the restatement of eval_kernel, src/gpu/loss.cu:241-293): a prediction equal to the target gives
+    zero error and SSIM one at every pixel and channel; a constant offset of one grey level gives (1/255)^2 per sample;
+    the alpha weighting scales both sums by the covered fraction on a binary alpha."""
+    W, H = 37, 29
+    rng = np.random.Generator(np.random.PCG64(2))
+    gt = rng.integers(0, 2 ** 24, W * H, dtype=np.uint64).astype(np.uint32) | np.uint32(0xFF000000)
+    same = np.stack([((gt >> np.uint32(8 * c)) & 0xFF).astype(np.float32) / 255.0 for c in range(3)] + [np.ones(W * H, np.float32)], 1)
+    se, ss = orc.eval_metrics(W, H, same, gt)
+    assert se == 0.0 and abs(ss - 3 * W * H) < 1e-9
+    grey = np.full(W * H, 100 | (100 << 8) | (100 << 16) | (255 << 24), np.uint32)
+    off = np.full((W * H, 4), 101.0 / 255.0, np.float32)
+    se, _ = orc.eval_metrics(W, H, off, grey)
+    assert abs(se - 3 * W * H / 255.0 ** 2) < 1e-9
+    half = gt.copy(); half[: (W * H) // 2] &= np.uint32(0x00FFFFFF)
+    se_m, ss_m = orc.eval_metrics(W, H, off, half, mask_weighted=True)
+    se_u, _ = orc.eval_metrics(W, H, off, half, mask_weighted=False)
+    assert 0 < se_m < se_u and ss_m < 3 * W * H
