@@ -90,10 +90,20 @@ SIGNATURES = {
     "b2k_eval_metrics": (C.c_int, [_P, _P, C.c_int32, _S]),
     "b2k_bwd_scratch_bytes": (C.c_uint64, [C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
     "b2k_raster_bwd": (C.c_int, [_P, _P, _P, _S]),
+    "b2k_raster_bwd_scaled": (C.c_int, [_P, _P, _P, C.c_float, _S]),
     "b2k_optim_fused": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_proj_bwd": (C.c_int, [_P, _P, _P, _P, _P, _S]),
     "b2k_adam": (C.c_int, [_P, _P, _P, _S]),
     "b2k_adam_range": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _S]),
+    "b2k_dp_unique_id": (C.c_int, [_P]),
+    "b2k_dp_init": (C.c_int, [_P, _P, C.c_int32, C.c_int32]),
+    "b2k_dp_destroy": (C.c_int, [_P]),
+    "b2k_dp_allreduce_grads": (C.c_int, [_P, _P, C.c_uint64, _S]),
+    "b2k_dp_allreduce_stat": (C.c_int, [_P, _P, C.c_uint64, C.c_int32, _S]),
+    "b2k_dp_barrier": (C.c_int, [_P, _S]),
+    "b2k_dp_share": (C.c_int, [_P, _P, _P, _S]),
+    "b2k_dp_slice": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, _P, _P]),
+    "b2k_dp_adam_shard": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_min_scale": (C.c_int, [_P, _P, _P, C.c_int32, _S]),
     "b2k_select_tmp_words": (C.c_uint64, [C.c_int32]),
     "b2k_select_flagged": (C.c_int, [_P, C.c_int32, _P, _P, _P, _S]),
@@ -563,6 +573,12 @@ def eval_metrics(ctx, view, mask_weighted=False, stream=None):
 def rasterize_backward(ctx, m, p, stream=None):
     cs, ms, os_ = ctx.struct(), m.struct(), p.struct()
     _check(lib().b2k_raster_bwd(C.byref(cs), C.byref(ms), C.byref(os_), _stream(stream)), "rasterize_backward")
+
+
+def rasterize_backward_tc(ctx, m, p, grad_scale, stream=None):
+    """rasterize_backward_tc (src/gpu/render.h:107-109): v_out carries grad_scale, the per-splat lanes leave divided by it."""
+    cs, ms, os_ = ctx.struct(), m.struct(), p.struct()
+    _check(lib().b2k_raster_bwd_scaled(C.byref(cs), C.byref(ms), C.byref(os_), C.c_float(grad_scale), _stream(stream)), "rasterize_backward_tc")
 
 
 def optimizer_step(ctx, m, op, stream=None):

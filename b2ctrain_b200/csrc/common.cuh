@@ -44,7 +44,10 @@ inline uint32_t* sort_tables_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tm
 // [slots][64] float4 checkpoints. The checkpoint before fragment range_start + seg * SEG_LEN of range q (= chunk *
 // n_tiles + tile) lives in slot (range_start >> SEG_SHIFT) + q + seg: ranges follow each other in the sorted buffer in
 // the order of q, which makes the map injective without any table.
-constexpr int SEG_SHIFT = 8, SEG_LEN = 1 << SEG_SHIFT;
+#ifndef B2K_SEG_SHIFT
+#define B2K_SEG_SHIFT 8
+#endif
+constexpr int SEG_SHIFT = B2K_SEG_SHIFT, SEG_LEN = 1 << SEG_SHIFT;
 constexpr size_t BWD_HEADER_WORDS = 16;
 __host__ __device__ inline uint64_t bwd_slots(uint64_t isect_cap, uint64_t n_ranges) { return (((isect_cap >> SEG_SHIFT) + n_ranges + 2) + 1) & ~1ull; }
 __host__ __device__ inline uint32_t ckpt_slot(uint32_t range_start, int q, uint32_t seg) { return (range_start >> SEG_SHIFT) + (uint32_t)q + seg; }

@@ -9,7 +9,9 @@
 // All are HBM-bound streams over the model: one thread per splat, 128-bit loads of the float4 parameter and moment
 // groups, planar (coalesced) SH lanes.
 #include "common.cuh"
+#include "dp.cuh"
 #include "sh.cuh"
+#include <type_traits>
 
 namespace b2k {
 namespace {
@@ -387,8 +389,24 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
 #endif
 template <int DEG> struct AdamShape { static constexpr int SPLATS = DEG <= 3 ? B2K_ADAM_SPLATS : 64, THREADS = 4 * SPLATS; };
 
-template <int DEG>
-__global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>::THREADS) adam_kernel(int first, int end, ModelPtrs mp, B2kOptim op, float* __restrict__ grad) {
+// PEERS = NoPeers: the update of this GPU's replica from its own accumulator (rows cleared on the way).
+// PEERS = PeerArgs: the sharded data-parallel update (b2k_dp_adam_shard). The rows of this rank's slice are summed from
+// every rank's accumulator with peer loads (a reduce-scatter done by the consumer), the update runs once, here, and the
+// new parameters are stored into every rank's replica (an all-gather done by the producer); moments stay with the
+// owner. Accumulators are left as they are: each rank clears its own afterwards.
+struct NoPeers {};
+struct PeerArgs {
+  int world;
+  const float* grad[B2K_DP_MAX_RANKS];
+  float4* pos_op[B2K_DP_MAX_RANKS]; float4* quat[B2K_DP_MAX_RANKS]; float4* lscale[B2K_DP_MAX_RANKS];
+  float* sh_dc[B2K_DP_MAX_RANKS]; float* sh_hi[B2K_DP_MAX_RANKS];
+};
+__device__ __forceinline__ float4 sum4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+
+template <int DEG, class PEERS>
+__global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>::THREADS) adam_kernel(int first, int end, ModelPtrs mp, B2kOptim op, float* __restrict__ grad,
+                                                                                                       const PEERS peers) {
+  constexpr bool SHARD = !std::is_same<PEERS, NoPeers>::value;
   constexpr int SPLATS = AdamShape<DEG>::SPLATS, THREADS = AdamShape<DEG>::THREADS;
   constexpr int K = (DEG + 1) * (DEG + 1), L = 3 * K, PER = 11 + L, QUARTER = (PER + 3) / 4, LPT = (L + 3) / 4;
   __shared__ __align__(16) float s_rows[SPLATS * PER];
@@ -400,24 +418,44 @@ __global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>
   float* gblock = grad + (size_t)base * PER;
   if (rows == SPLATS) {
     constexpr int WORDS = SPLATS * PER / 4, BATCH = (WORDS + THREADS - 1) / THREADS;   // whole 16-byte words from an aligned start
-    float4* g4 = reinterpret_cast<float4*>(gblock);
     float4* s4 = reinterpret_cast<float4*>(s_rows);
     float4 r[BATCH];
+    if constexpr (SHARD) {
 #pragma unroll
-    for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) r[u] = __ldcs(g4 + k); }
+      for (int u = 0; u < BATCH; u++) r[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < peers.world; p++) {   // fixed order: every rank would form the same sums
+        const float4* g4 = reinterpret_cast<const float4*>(peers.grad[p] + (size_t)base * PER);
+        float4 t[BATCH];
+#pragma unroll
+        for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) t[u] = __ldcs(g4 + k); }
+#pragma unroll
+        for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) r[u] = sum4(r[u], t[u]); }
+      }
+    } else {
+      const float4* g4 = reinterpret_cast<const float4*>(gblock);
+#pragma unroll
+      for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) r[u] = __ldcs(g4 + k); }
+    }
 #pragma unroll
     for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) s4[k] = r[u]; }
+  } else if constexpr (SHARD) {
+    for (int k = threadIdx.x; k < rows * PER; k += THREADS) {
+      float t = 0.f;
+      for (int p = 0; p < peers.world; p++) t += peers.grad[p][(size_t)base * PER + k];
+      s_rows[k] = t;
+    }
   } else {
     for (int k = threadIdx.x; k < rows * PER; k += THREADS) { s_rows[k] = gblock[k]; gblock[k] = 0.f; }
   }
   __syncthreads();
   // The rows are cleared only now, once the loads above have landed: a store issued right behind the load of the same
   // line measured 2.5x slower for the whole kernel than one issued after it.
-  if (rows == SPLATS) {
+  if (!SHARD && rows == SPLATS) {
     constexpr int WORDS = SPLATS * PER / 4;
     float4* g4 = reinterpret_cast<float4*>(gblock);
     for (int k = threadIdx.x; k < WORDS; k += THREADS) __stcs(g4 + k, make_float4(0.f, 0.f, 0.f, 0.f));
   }
+
   const int role = threadIdx.x / SPLATS, sp = threadIdx.x % SPLATS, i = base + sp;
   const float* g = s_rows + sp * PER;
   {
@@ -457,13 +495,15 @@ __global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>
     } else if (role == 1) {
       float4 q = mp.quat[i], m = mp.m_q[i], v = mp.v_q[i];
       adam4(q, m, v, make_float4(g[4], g[5], g[6], g[7]), make_float4(op.lr_rot, op.lr_rot, op.lr_rot, op.lr_rot), a);
-      mp.m_q[i] = m; mp.v_q[i] = v; mp.quat[i] = q;
+      mp.m_q[i] = m; mp.v_q[i] = v;
+      if constexpr (SHARD) { for (int p = 0; p < peers.world; p++) peers.quat[p][i] = q; } else mp.quat[i] = q;
     } else if (role == 2) {
       float4 ls = mp.lscale[i], m = mp.m_ls[i], v = mp.v_ls[i];
       const float keep = ls.w;
       adam4(ls, m, v, make_float4(g[8], g[9], g[10], 0.f), make_float4(op.lr_scale, op.lr_scale, op.lr_scale, 0.f), a);
       ls.w = keep; m.w = 0.f; v.w = 0.f;   // the floor lane is a frozen constant
-      mp.m_ls[i] = m; mp.v_ls[i] = v; mp.lscale[i] = ls;
+      mp.m_ls[i] = m; mp.v_ls[i] = v;
+      if constexpr (SHARD) { for (int p = 0; p < peers.world; p++) peers.lscale[p][i] = ls; } else mp.lscale[i] = ls;
       s_ls[sp] = ls;
     } else {
       // Adam-mini: one second moment per splat, the EMA of the mean squared SH gradient (optim.cu:337-345).
@@ -485,12 +525,13 @@ __global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>
     if (l < L) {
       adam_sh_lane(p_in[u], m_in[u], g[11 + l], l < 3 ? op.lr_dc : op.lr_sh_rest, op.beta1, st);
       *sh_lane_ptr(mp.m_sh_dc, mp.m_sh_hi, mp.cap, l, i) = m_in[u];
-      *sh_lane_ptr(mp.sh_dc, mp.sh_hi, mp.cap, l, i) = p_in[u];
+      if constexpr (SHARD) { for (int p = 0; p < peers.world; p++) *sh_lane_ptr(peers.sh_dc[p], peers.sh_hi[p], mp.cap, l, i) = p_in[u]; }
+      else *sh_lane_ptr(mp.sh_dc, mp.sh_hi, mp.cap, l, i) = p_in[u];
     }
   }
   if (role == 0) {
     add_mcmc_noise(po, s_ls[sp], i, op, any);
-    mp.pos_op[i] = po;
+    if constexpr (SHARD) { for (int p = 0; p < peers.world; p++) peers.pos_op[p][i] = po; } else mp.pos_op[i] = po;
   } else if (role == 3 && op.sparse) {
     mp.last_step[i] = (uint32_t)op.t;
   }
@@ -670,8 +711,29 @@ extern "C" int b2k_adam_range(const B2kModel* m, const B2kOptim* op, float* grad
   B2K_REQUIRE(first >= 0 && count >= 0 && first % 4 == 0 && (int64_t)first + count <= m->n);
   if (count == 0) return B2K_OK;
   const ModelPtrs mp = model_ptrs(m);
-  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D><<<div_up(count, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
-      first, first + count, mp, *op, grad)));
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D, NoPeers><<<div_up(count, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
+      first, first + count, mp, *op, grad, NoPeers{})));
+  return check_launch();
+}
+
+extern "C" int b2k_dp_adam_shard(B2kDp* dp, const B2kModel* m, const B2kOptim* op, const B2kDpPeers* pr, b2k_stream_t stream) {
+  B2K_REQUIRE(dp && m && op && pr && m->n >= 0 && m->cap >= m->n && m->degree >= 0 && m->degree <= 4 && dp->world <= B2K_DP_MAX_RANKS);
+  B2K_REQUIRE(m->pos_op && m->quat && m->lscale && m->sh_dc && (m->degree == 0 || m->sh_hi) && has_moments(m) && op->t >= 1);
+  PeerArgs pa;
+  pa.world = dp->world;
+  for (int r = 0; r < dp->world; r++) {
+    B2K_REQUIRE(pr->grad[r] && pr->pos_op[r] && pr->quat[r] && pr->lscale[r] && pr->sh_dc[r] && (m->degree == 0 || pr->sh_hi[r]));
+    pa.grad[r] = pr->grad[r]; pa.pos_op[r] = (float4*)pr->pos_op[r]; pa.quat[r] = (float4*)pr->quat[r]; pa.lscale[r] = (float4*)pr->lscale[r];
+    pa.sh_dc[r] = pr->sh_dc[r]; pa.sh_hi[r] = pr->sh_hi[r];
+  }
+  B2K_REQUIRE(pr->pos_op[dp->rank] == m->pos_op && pr->sh_dc[dp->rank] == m->sh_dc);   // the replica named by `m` is this rank's
+  int32_t first = 0, count = 0;
+  int st = b2k_dp_slice(m->n, dp->rank, dp->world, &first, &count);
+  if (st) return st;
+  if (count == 0) return B2K_OK;
+  const ModelPtrs mp = model_ptrs(m);
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D, PeerArgs><<<div_up(count, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
+      first, first + count, mp, *op, pr->grad[dp->rank], pa)));
   return check_launch();
 }
 

@@ -23,7 +23,10 @@
 namespace b2k {
 namespace {
 
-constexpr int BWD_WARPS = 2;                 // warps per CTA (independent: the CTA shape only sets the residency granularity)
+#ifndef B2K_BWD_WARPS
+#define B2K_BWD_WARPS 2
+#endif
+constexpr int BWD_WARPS = B2K_BWD_WARPS;     // warps per CTA (independent: the CTA shape only sets the residency granularity)
 constexpr int BWD_BATCH = 32;                // fragments staged per warp and batch
 constexpr int RED_F = 5;                     // fragments whose partial sums are pending before a column reduction
 constexpr int RED_BLOCK = 33 * 3;            // 16-byte words per pending fragment: 32 lanes x 3 words, one slot of skew
@@ -64,7 +67,8 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     const uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, const float4* __restrict__ out_rgba, const float4* __restrict__ out_feat, const uint32_t* __restrict__ last_idx,
     const float4* __restrict__ v_out, int W, int H, int tiles_x, int n_tiles, float3 bg, float* __restrict__ v_splat, uint32_t* __restrict__ vis_flag,
-    float* __restrict__ vis_weight, int n_chunks, const uint2* __restrict__ items, uint32_t* __restrict__ work, const float4* __restrict__ ckpt) {
+    float* __restrict__ vis_weight, int n_chunks, const uint2* __restrict__ items, uint32_t* __restrict__ work, const float4* __restrict__ ckpt,
+    float out_scale) {
   __shared__ Staged s_frag[BWD_WARPS][BWD_BATCH];
   __shared__ uint32_t s_gid[BWD_WARPS][BWD_BATCH];
   __shared__ __align__(16) float4 s_red[BWD_WARPS][RED_F * RED_BLOCK];
@@ -154,6 +158,9 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
       if (mine && red_half == 0) {
         const uint32_t gid = pending_gid[red_f];
         float* o = v_splat + (size_t)gid * GRAD_LANES + red_w * 4;
+        // out_scale undoes a scale the caller put on the pixel gradients (1 unless asked for); the blend weight is no gradient.
+        acc.x *= out_scale; acc.y *= out_scale;
+        if (red_w < 2) { acc.z *= out_scale; acc.w *= out_scale; }
         if (red_w < 2) {   // words 0, 1: xy 2 + conic 3 + rgb 3
           if (acc.x != 0.f) atomicAdd(o, acc.x);
           if (acc.y != 0.f) atomicAdd(o + 1, acc.y);
@@ -248,6 +255,11 @@ extern "C" uint64_t b2k_bwd_scratch_bytes(int32_t W, int32_t H, int32_t n_chunks
 }
 
 extern "C" int b2k_raster_bwd(const B2kCtx* c, const B2kModel* m, const B2kRenderOpts* o, b2k_stream_t stream) {
+  return b2k_raster_bwd_scaled(c, m, o, 1.f, stream);
+}
+
+extern "C" int b2k_raster_bwd_scaled(const B2kCtx* c, const B2kModel* m, const B2kRenderOpts* o, float grad_scale, b2k_stream_t stream) {
+  B2K_REQUIRE(grad_scale > 0.f && isfinite(grad_scale));
   B2K_REQUIRE(c && m && o && c->tile_ranges && c->vals_sorted && c->proj0 && c->proj1 && c->proj2);
   B2K_REQUIRE(c->out_rgba && c->out_feat && c->last_idx && c->v_out && c->v_splat && c->vis_flag);
   B2K_REQUIRE(c->W > 0 && c->H > 0 && c->n_tiles == c->tiles_x * c->tiles_y && c->bwd_scratch);
@@ -272,7 +284,7 @@ extern "C" int b2k_raster_bwd(const B2kCtx* c, const B2kModel* m, const B2kRende
 #define L(CH) raster_bwd_kernel<CH><<<ctas, BWD_WARPS * 32, 0, s>>>( \
       (const uint2*)c->tile_ranges, c->vals_sorted, (const float4*)c->proj0, (const float4*)c->proj1, (const float4*)c->proj2, (const float4*)c->out_rgba, \
       (const float4*)c->out_feat, c->last_idx, (const float4*)c->v_out, c->W, c->H, c->tiles_x, c->n_tiles, bg, c->v_splat, c->vis_flag, m->vis_weight, chunks, \
-      items, work, bwd_ckpt_ptr(c))
+      items, work, bwd_ckpt_ptr(c), 1.f / grad_scale)
   if (chunks > 1) L(true); else L(false);
 #undef L
   return check_launch();

@@ -6,7 +6,7 @@
 #include <cstring>
 
 namespace b2c {
-namespace {
+namespace abi {
 
 void check(int status, const char* what) {
   if (status == B2K_OK) return;
@@ -67,7 +67,7 @@ B2kRenderOpts opts_of(const RenderParams& p, const char* what) {
 }
 
 B2kOptim optim_of(const OptimParams& op, const char* what) {
-  if (op.mip || op.g_pos_out || op.sh_frame || op.frozen || op.update_mask || op.canon_rot) unsupported(what);
+  if (op.mip || op.g_pos_out || op.sh_frame || op.frozen || op.update_mask || op.canon_rot || op.spa_z || op.spa_u || op.stretch_w || op.g_app_out) unsupported(what);
   B2kOptim o{};
   o.active_sh_degree = op.active_sh_degree; o.t = op.t; o.beta1 = op.beta1; o.beta2 = op.beta2; o.eps = op.eps;
   o.lr_mean = op.lr_mean; o.lr_rot = op.lr_rot; o.lr_scale = op.lr_scale; o.lr_opac = op.lr_opac; o.lr_dc = op.lr_dc; o.lr_sh_rest = op.lr_sh_rest;
@@ -84,7 +84,8 @@ void alloc_isect(RenderCtx& c, size_t cap) {
   c.bwd_scratch.reserve((size_t)b2k_bwd_scratch_bytes(c.W, c.H, c.n_chunks, cap));
 }
 
-}  // namespace
+}  // namespace abi
+using namespace abi;
 
 CameraGPU CameraGPU::from(const Camera& c, int W, int H) {
   CameraGPU g;
@@ -238,15 +239,35 @@ void render_forward(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaS
   rasterize_forward(ctx, p, stream);
 }
 
+void render_forward_async(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream) {
+  const B2kModel mv = view_of(m); const B2kCtx cv = view_of(ctx); const B2kCamera cam = camera_of(p.cam); const B2kRenderOpts o = opts_of(p, "render_forward");
+  if (ctx.n_chunks > 1) { check(b2k_render_chunked(&mv, &cam, &o, &cv, stream), "render_forward"); return; }
+  if (m.n > 0) check(b2k_project(&mv, &cam, &o, &cv, stream), "project_splats");
+  check(b2k_bin_sort(&cv, m.n, stream), "bin_and_sort");
+  check(b2k_raster_fwd(&cv, &o, stream), "rasterize_forward");
+}
+
+bool grow_intersections(RenderCtx& ctx, uint32_t needed) {
+  if ((size_t)needed <= ctx.isect_cap) return false;
+  size_t ncap = ctx.isect_cap; while (ncap < (size_t)needed + 32u * (size_t)(ctx.n_chunks > 1 ? ctx.n_chunks : 1)) ncap *= 2;
+  alloc_isect(ctx, ncap);
+  return true;
+}
+
+void step_begin(RenderCtx& ctx, cudaStream_t stream) { const B2kCtx cv = view_of(ctx); check(b2k_step_begin(&cv, stream), "step_begin"); }
+void fold_loss(RenderCtx& dst, const RenderCtx& src, cudaStream_t stream) {
+  const B2kCtx a = view_of(dst), b = view_of(src); check(b2k_loss_fold(&a, &b, stream), "fold_loss");
+}
+
 void rasterize_backward(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream) {
   const B2kCtx cv = view_of(ctx); const B2kModel mv = view_of(m); const B2kRenderOpts o = opts_of(p, "rasterize_backward");
   check(b2k_raster_bwd(&cv, &mv, &o, stream), "rasterize_backward");
 }
 
 void rasterize_backward_tc(RenderCtx& ctx, const Model& m, const RenderParams& p, float grad_scale, cudaStream_t stream) {
-  // The reduction here is full fp32, so no pre-scaling of the pixel gradients is needed; only the identity is accepted.
-  if (grad_scale != 1.f) unsupported("rasterize_backward_tc with grad_scale != 1 (use rasterize_backward)");
-  rasterize_backward(ctx, m, p, stream);
+  // The reduction here is fp32 throughout, so the scale is not needed for range; it is honoured as the contract says.
+  const B2kCtx cv = view_of(ctx); const B2kModel mv = view_of(m); const B2kRenderOpts o = opts_of(p, "rasterize_backward_tc");
+  check(b2k_raster_bwd_scaled(&cv, &mv, &o, grad_scale, stream), "rasterize_backward_tc");
 }
 
 void photometric_loss(RenderCtx& ctx, const ViewGPU& view, const LossParams& lp, cudaStream_t stream) {
@@ -259,6 +280,9 @@ void photometric_loss(RenderCtx& ctx, const ViewGPU& view, const LossParams& lp,
   l.match_alpha_weight = lp.match_alpha_weight; l.scale = lp.scale; l.grad_scale = lp.grad_scale;
   check(b2k_loss_photometric(&cv, &l, stream), "photometric_loss");
 }
+
+void normal_loss(RenderCtx&, const ViewGPU&, const LossParams&, cudaStream_t) { unsupported("normal_loss"); }
+void hollow_loss(RenderCtx&, float, cudaStream_t) { unsupported("hollow_loss"); }
 
 void accumulate_loss(RenderCtx& ctx, cudaStream_t stream) { const B2kCtx cv = view_of(ctx); check(b2k_loss_accumulate(&cv, stream), "accumulate_loss"); }
 

@@ -6,6 +6,7 @@
 // the reference (src/gpu/util.cuh:13-15). Lanes that libb2k does not implement throw "unsupported lane".
 #pragma once
 #include <cuda_runtime.h>
+#include <cmath>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -16,7 +17,14 @@ namespace b2c {
 #define B2C_CUDA_CHECK(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) \
   throw std::runtime_error(std::string("CUDA error ") + cudaGetErrorString(e_) + " at " + __FILE__ + ":" + std::to_string(__LINE__)); } while (0)
 
+// The reference's spelling of the same checks (src/gpu/util.cuh:13-16), for callers written against it.
+#ifndef CUDA_CHECK
+#define CUDA_CHECK(expr) B2C_CUDA_CHECK(expr)
+#define CUDA_KERNEL_CHECK() B2C_CUDA_CHECK(cudaGetLastError())
+#endif
+
 constexpr int RT_W = 8;   // rasteriser tile edge
+inline int sh_coeffs_for_degree(int d) { return (d + 1) * (d + 1); }
 
 // Owning, grow-only device buffer (the role of DevBuf in src/gpu/util.cuh:26-57).
 template <typename T>
@@ -53,6 +61,17 @@ struct DevBuf {
   operator T*() const { return ptr; }
 };
 
+// Pinned host memory for readbacks (src/gpu/util.cuh:59-64).
+template <typename T>
+struct PinnedBuf {
+  T* ptr = nullptr; size_t count = 0;
+  PinnedBuf() = default;
+  PinnedBuf(const PinnedBuf&) = delete;
+  PinnedBuf& operator=(const PinnedBuf&) = delete;
+  void reserve(size_t n) { if (n <= count) return; if (ptr) cudaFreeHost(ptr); ptr = nullptr; B2C_CUDA_CHECK(cudaMallocHost(&ptr, n * sizeof(T))); count = n; }
+  ~PinnedBuf() { if (ptr) cudaFreeHost(ptr); }
+};
+
 // Host splat cloud in the layout of SplatCloud (src/ply.h:12-22).
 struct SplatCloud {
   size_t n = 0;
@@ -74,6 +93,21 @@ struct Camera {
   float t[3] = {0, 0, 0};
   float pos[3] = {0, 0, 0};
   void update_pos() { for (int i = 0; i < 3; i++) pos[i] = -(R[i] * t[0] + R[3 + i] * t[1] + R[6 + i] * t[2]); }
+  // World-to-camera pose from a rotation quaternion (normalised here) and a translation.
+  void set_w2c_quat(float qw, float qx, float qy, float qz, float tx, float ty, float tz) {
+    const float inv = 1.f / std::sqrt(qw * qw + qx * qx + qy * qy + qz * qz);
+    const float w = qw * inv, x = qx * inv, y = qy * inv, z = qz * inv;
+    const float m[9] = {1 - 2 * (y * y + z * z), 2 * (x * y - z * w), 2 * (x * z + y * w), 2 * (x * y + z * w), 1 - 2 * (x * x + z * z), 2 * (y * z - x * w),
+                        2 * (x * z - y * w), 2 * (y * z + x * w), 1 - 2 * (x * x + y * y)};
+    for (int i = 0; i < 9; i++) R[i] = m[i];
+    t[0] = tx; t[1] = ty; t[2] = tz;
+    update_pos();
+  }
+  void rescale(int new_w, int new_h) {   // intrinsics follow the image size
+    const float sx = (float)new_w / (float)width, sy = (float)new_h / (float)height;
+    fx *= sx; cx *= sx; fy *= sy; cy *= sy; width = new_w; height = new_h;
+  }
+  float focal_px() const { return 0.5f * (fx + fy); }
 };
 
 // Device model (src/model.h:14-40): float4 parameter groups, planar SH with stride cap, moments, refine statistics.
@@ -148,6 +182,8 @@ struct RenderCtx {
   DevBuf<uint32_t> vis_flag;
   DevBuf<uint32_t> vis_list;        // splats the backward touched (count in d_num_isect[1]); walked by the sparse optimizer
   DevBuf<float4> v_out;
+  DevBuf<float4> v_feat;            // dL/d(feat) per pixel: kept for callers that name it; the feature lanes have no backward here
+  DevBuf<float> hollow_pen;         // likewise (hollow loss lane, unsupported)
   DevBuf<float> loss_accum;
   bool want_depth = false;
   int n_chunks = 1;                 // set > 1 before setup(): render_forward composites front to back in depth chunks
@@ -173,6 +209,8 @@ struct ViewGPU {
   int W = 0, H = 0;
   bool has_alpha = false, masked = false;
   float alpha_coverage = 1.f;
+  float normal_count = 0.f;
+  const float2* warp = nullptr; int warp_w = 0, warp_h = 0;
 };
 struct LossParams {
   float l1_w = 0.8f, ssim_w = -0.2f;
@@ -184,6 +222,9 @@ struct LossParams {
   float grad_scale = 1.f;
 };
 void photometric_loss(RenderCtx& ctx, const ViewGPU& view, const LossParams& lp, cudaStream_t stream);
+// src/gpu/loss.h:35,39: lanes outside this path; declared so callers compile, they throw "unsupported lane".
+void normal_loss(RenderCtx& ctx, const ViewGPU& view, const LossParams& lp, cudaStream_t stream);
+void hollow_loss(RenderCtx& ctx, float lam, cudaStream_t stream);
 void accumulate_loss(RenderCtx& ctx, cudaStream_t stream);
 void eval_metrics(RenderCtx& ctx, const ViewGPU& view, bool mask_weighted, cudaStream_t stream);
 
@@ -207,6 +248,9 @@ struct OptimParams {
   const uint8_t* update_mask = nullptr;
   const float4* canon_rot = nullptr;
   bool sparse = false;
+  const float* spa_z = nullptr; const float* spa_u = nullptr; float spa_rho = 0.f;   // sparsification penalty: throws when set
+  const float* stretch_w = nullptr; float stretch_log_tau = 0.f;                     // cage stretch regulariser: throws when set
+  float2* g_app_out = nullptr;                                                        // pose-dependent appearance: throws when set
   float* grad_out = nullptr;
 };
 void optimizer_step(RenderCtx& ctx, Model& m, const OptimParams& op, cudaStream_t stream);
@@ -215,4 +259,25 @@ void projection_backward(RenderCtx& ctx, Model& m, const OptimParams& op, float*
 void adam_step(Model& m, const OptimParams& op, float* grad, cudaStream_t stream);
 void update_min_scale(Model& m, const float* cam_pos, const float* cam_focal, int n_cams, cudaStream_t stream);
 
+// ---- additions for a step that keeps several views in flight (no counterpart in the reference) ----
+// render_forward without the host readback of the intersection total: nothing waits for the stream. The total stays in
+// ctx.d_num_isect (word 0: this view, word 2: largest since step_begin); grow_intersections() is the reference's
+// doubling (src/gpu/binning.cu:129-133) applied afterwards, after which the caller redoes the views.
+void render_forward_async(RenderCtx& ctx, const Model& m, const RenderParams& p, cudaStream_t stream);
+bool grow_intersections(RenderCtx& ctx, uint32_t needed);
+void step_begin(RenderCtx& ctx, cudaStream_t stream);                          // loss_accum and the running maximum = 0
+void fold_loss(RenderCtx& dst, const RenderCtx& src, cudaStream_t stream);    // dst.loss_accum[2..3] += src's
+
 }  // namespace b2c
+
+// POD views of the owning objects for direct calls into the C ABI (include/b2k.h).
+#include "../../include/b2k.h"
+namespace b2c { namespace abi {
+void check(int status, const char* what);            // throws std::runtime_error on a non-zero status
+B2kModel view_of(const Model& m);
+B2kCtx view_of(const RenderCtx& c);
+B2kCamera camera_of(const CameraGPU& g);
+B2kRenderOpts opts_of(const RenderParams& p, const char* what);
+B2kOptim optim_of(const OptimParams& op, const char* what);
+void alloc_isect(RenderCtx& c, size_t cap);
+} }

@@ -1,0 +1,98 @@
+// C entry points of the C++ host (libb2chost.so): what a launcher written in another language (the benchmark driver, a
+// test) calls to run StepTrainer steps without any of the step loop living on its side. Exceptions of the C++ layer
+// become a non-zero return; b2ch_last_error() has the message.
+#include "host_c.h"
+#include <cstring>
+#include <string>
+#include "trainer.h"
+
+using namespace b2c;
+
+namespace {
+thread_local std::string g_error;
+template <class F> int guarded(F&& f) {
+  try { f(); return 0; } catch (const std::exception& e) { g_error = e.what(); return 1; }
+}
+StepConfig config_of(const B2chConfig& c) {
+  StepConfig s;
+  s.views_in_flight = c.views_in_flight; s.render_chunks = c.render_chunks; s.isect_cap = (size_t)c.isect_cap; s.ssim_weight = c.ssim_weight;
+  s.mask = c.mask != 0; s.alpha_lane = c.alpha_lane != 0; s.composite = c.composite != 0; s.match_alpha_weight = c.match_alpha_weight; s.loss_scale = c.loss_scale;
+  for (int k = 0; k < 3; k++) s.bg[k] = c.bg[k];
+  s.lr_mean = c.lr_mean; s.lr_rot = c.lr_rot; s.lr_scale = c.lr_scale; s.lr_opac = c.lr_opac; s.lr_dc = c.lr_dc; s.lr_sh_rest = c.lr_sh_rest;
+  s.sparse = c.sparse != 0; s.noise_weight = c.noise_weight; s.noise_clamp = c.noise_clamp; s.seed = c.seed; s.shard_update = c.shard_update != 0;
+  return s;
+}
+}  // namespace
+
+extern "C" const char* b2ch_last_error(void) { return g_error.c_str(); }
+
+extern "C" void* b2ch_trainer_create(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, int32_t W, int32_t H,
+                                     const B2chConfig* cfg, int32_t rank, int32_t world, const uint8_t* dp_id) {
+  StepTrainer* tr = nullptr;
+  const int st = guarded([&] {
+    if (!cfg || n < 0 || (n > 0 && (!pos_op || !quat || !lscale || !sh))) throw std::runtime_error("b2ch_trainer_create: bad argument");
+    SplatCloud c; c.resize((size_t)n, degree); c.floor.assign((size_t)n, 0.f);
+    const int K = c.K();
+    for (int i = 0; i < n; i++) {
+      for (int k = 0; k < 3; k++) { c.pos[i * 3 + k] = pos_op[i * 4 + k]; c.log_scale[i * 3 + k] = lscale[i * 4 + k]; }
+      c.opacity[i] = pos_op[i * 4 + 3]; c.floor[i] = lscale[i * 4 + 3];
+      for (int k = 0; k < 4; k++) c.quat[i * 4 + k] = quat[i * 4 + k];
+    }
+    std::memcpy(c.sh.data(), sh, (size_t)n * K * 3 * sizeof(float));
+    tr = new StepTrainer(c, W, H, config_of(*cfg), rank, world, dp_id);
+  });
+  return st ? nullptr : tr;
+}
+
+extern "C" void b2ch_trainer_destroy(void* h) { delete (StepTrainer*)h; }
+
+extern "C" int b2ch_trainer_add_view(void* h, const B2kCamera* cam, const uint32_t* rgba) {
+  int idx = -1;
+  const int st = guarded([&] {
+    StepTrainer& tr = *(StepTrainer*)h;
+    Camera c; c.width = cam->W; c.height = cam->H; c.fx = cam->fx; c.fy = cam->fy; c.cx = cam->cx; c.cy = cam->cy;
+    for (int i = 0; i < 9; i++) c.R[i] = cam->R[i];
+    for (int i = 0; i < 3; i++) { c.t[i] = cam->t[i]; c.pos[i] = cam->pos[i]; }
+    idx = tr.add_view(c, rgba);
+  });
+  return st ? -1 : idx;
+}
+
+extern "C" int b2ch_trainer_step(void* h, const int32_t* views, int32_t n_views, void* stream, int32_t from_host) {
+  return guarded([&] { ((StepTrainer*)h)->step(std::vector<int>(views, views + n_views), (cudaStream_t)stream, from_host != 0); });
+}
+
+extern "C" int b2ch_trainer_read_loss(void* h, float* out16, void* stream) { return guarded([&] { ((StepTrainer*)h)->read_loss(out16, (cudaStream_t)stream); }); }
+
+extern "C" int b2ch_trainer_set_profile(void* h, int32_t on) { ((StepTrainer*)h)->profile = on != 0; return 0; }
+
+extern "C" int b2ch_trainer_info(void* h, uint64_t* out8) {
+  return guarded([&] {
+    StepTrainer& tr = *(StepTrainer*)h;
+    out8[0] = tr.ctxs[0]->isect_cap; out8[1] = (uint64_t)tr.overflow_redos; out8[2] = tr.h2d_bytes; out8[3] = (uint64_t)tr.model.n;
+    out8[4] = (uint64_t)tr.model.adam_t; out8[5] = (uint64_t)tr.ctxs.size(); out8[6] = (uint64_t)tr.views.size(); out8[7] = (uint64_t)tr.ctxs[0]->tile_bits;
+    float ms[3] = {tr.phase_ms[0], tr.phase_ms[1], tr.phase_ms[2]};
+    std::memcpy(out8 + 8, ms, sizeof ms);   // out8[8..9]: the three phase times of the last profiled step as floats
+    tr.h2d_bytes = 0;
+  });
+}
+
+extern "C" int b2ch_trainer_download(void* h, float* pos_op, float* quat, float* lscale, float* sh) {
+  return guarded([&] {
+    const SplatCloud c = ((StepTrainer*)h)->model.download(0);
+    for (size_t i = 0; i < c.n; i++) {
+      for (int k = 0; k < 3; k++) { pos_op[i * 4 + k] = c.pos[i * 3 + k]; lscale[i * 4 + k] = c.log_scale[i * 3 + k]; }
+      pos_op[i * 4 + 3] = c.opacity[i]; lscale[i * 4 + 3] = c.floor[i];
+      for (int k = 0; k < 4; k++) quat[i * 4 + k] = c.quat[i * 4 + k];
+    }
+    std::memcpy(sh, c.sh.data(), c.sh.size() * sizeof(float));
+  });
+}
+
+extern "C" int b2ch_trainer_reduce_statistics(void* h, void* stream) { return guarded([&] { ((StepTrainer*)h)->reduce_statistics((cudaStream_t)stream); }); }
+
+extern "C" uint64_t b2ch_trainer_checksum(void* h, void* stream) {
+  uint64_t v = 0;
+  guarded([&] { v = ((StepTrainer*)h)->replica_checksum((cudaStream_t)stream); });
+  return v;
+}

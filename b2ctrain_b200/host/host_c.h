@@ -1,0 +1,50 @@
+/* C entry points of the C++ host library (libb2chost.so): the step loop of the reference's trainer
+ * (src/train/trainer.cpp:452-529), with views in flight and view-level data parallelism, driven from any language.
+ * Every function returns 0 on success (creation: a handle, or NULL); b2ch_last_error() describes the last failure of
+ * the calling thread. */
+#ifndef B2CH_HOST_C_H
+#define B2CH_HOST_C_H
+#include <stdint.h>
+#include "../../include/b2k.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+  int32_t views_in_flight, render_chunks;
+  uint64_t isect_cap;
+  float ssim_weight;
+  int32_t mask, alpha_lane, composite;
+  float match_alpha_weight, loss_scale;
+  float bg[3];
+  float lr_mean, lr_rot, lr_scale, lr_opac, lr_dc, lr_sh_rest;
+  int32_t sparse;
+  float noise_weight, noise_clamp;
+  uint32_t seed;
+  int32_t shard_update;
+} B2chConfig;
+
+const char* b2ch_last_error(void);
+/* Splats in the host layout pos_op [n][4] (xyz, opacity logit), quat [n][4], lscale [n][4] (log scales, floor), sh [n][K][3].
+ * Collective over the ranks when world > 1 (dp_id: the 128 bytes of b2k_dp_unique_id from rank 0); uses the current device. */
+void* b2ch_trainer_create(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, int32_t W, int32_t H,
+                          const B2chConfig* cfg, int32_t rank, int32_t world, const uint8_t* dp_id);
+void b2ch_trainer_destroy(void* trainer);
+/* Registers a view (camera record with intrinsics for W x H, packed RGBA8 target on the host); returns its index or -1. */
+int b2ch_trainer_add_view(void* trainer, const B2kCamera* cam, const uint32_t* rgba);
+/* One optimisation step over the listed views (the whole step's list on every rank). */
+int b2ch_trainer_step(void* trainer, const int32_t* views, int32_t n_views, void* stream, int32_t from_host);
+int b2ch_trainer_read_loss(void* trainer, float* out16, void* stream);
+int b2ch_trainer_set_profile(void* trainer, int32_t on);
+/* out[0] intersection capacity, [1] steps redone after an overflow, [2] host-to-device bytes since the last call, [3] n,
+ * [4] Adam step, [5] lanes, [6] views, [7] tile bits; out[8..9] hold three floats: ms of the views, the update and the whole
+ * of the last profiled step. out must hold 10 words. */
+int b2ch_trainer_info(void* trainer, uint64_t* out);
+int b2ch_trainer_download(void* trainer, float* pos_op, float* quat, float* lscale, float* sh);
+int b2ch_trainer_reduce_statistics(void* trainer, void* stream);
+uint64_t b2ch_trainer_checksum(void* trainer, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,145 @@
+"""ctypes binding of the C++ host library (libb2chost.so): the reference's step loop (src/train/trainer.cpp:452-529)
+with views in flight and view-level data parallelism, run entirely in C++ (b2ctrain_b200/host/trainer.cpp). Python only
+hands over the scene, the views and a CUDA stream; no step logic, collective or kernel launch happens on this side.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import api
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb2chost.so")
+
+
+class B2chConfig(C.Structure):
+    _fields_ = [("views_in_flight", C.c_int32), ("render_chunks", C.c_int32), ("isect_cap", C.c_uint64), ("ssim_weight", C.c_float),
+                ("mask", C.c_int32), ("alpha_lane", C.c_int32), ("composite", C.c_int32), ("match_alpha_weight", C.c_float), ("loss_scale", C.c_float),
+                ("bg", C.c_float * 3), ("lr_mean", C.c_float), ("lr_rot", C.c_float), ("lr_scale", C.c_float), ("lr_opac", C.c_float), ("lr_dc", C.c_float),
+                ("lr_sh_rest", C.c_float), ("sparse", C.c_int32), ("noise_weight", C.c_float), ("noise_clamp", C.c_float), ("seed", C.c_uint32),
+                ("shard_update", C.c_int32)]
+
+
+_P = C.c_void_p
+SIGNATURES = {
+    "b2ch_last_error": (C.c_char_p, []),
+    "b2ch_trainer_create": (C.c_void_p, [C.c_int32, C.c_int32, _P, _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P]),
+    "b2ch_trainer_destroy": (None, [_P]),
+    "b2ch_trainer_add_view": (C.c_int, [_P, _P, _P]),
+    "b2ch_trainer_step": (C.c_int, [_P, _P, C.c_int32, _P, C.c_int32]),
+    "b2ch_trainer_read_loss": (C.c_int, [_P, _P, _P]),
+    "b2ch_trainer_set_profile": (C.c_int, [_P, C.c_int32]),
+    "b2ch_trainer_info": (C.c_int, [_P, _P]),
+    "b2ch_trainer_download": (C.c_int, [_P, _P, _P, _P, _P]),
+    "b2ch_trainer_reduce_statistics": (C.c_int, [_P, _P]),
+    "b2ch_trainer_checksum": (C.c_uint64, [_P, _P]),
+}
+
+_lib = None
+
+
+def lib():
+    """Loads libb2chost.so (and libb2k.so, which it links); raises when it has not been built."""
+    global _lib
+    if _lib is None:
+        api.lib()
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `make -C b2ctrain_b200/host`")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(l, name)
+            f.restype, f.argtypes = res, args
+        _lib = l
+    return _lib
+
+
+def _check(status, what):
+    if status != 0:
+        raise RuntimeError(f"{what}: {lib().b2ch_last_error().decode()}")
+
+
+def make_dp_id():
+    """The 128-byte rendezvous id rank 0 creates (b2k_dp_unique_id) and sends to the other ranks."""
+    buf = (C.c_uint8 * 128)()
+    api._check(api.lib().b2k_dp_unique_id(buf), "b2k_dp_unique_id")
+    return bytes(buf)
+
+
+def dp_slice(n, rank, world):
+    """(first, count) of the splats whose update `rank` owns in the sharded data-parallel step (b2k_dp_slice)."""
+    a, b = C.c_int32(0), C.c_int32(0)
+    api._check(api.lib().b2k_dp_slice(int(n), int(rank), int(world), C.byref(a), C.byref(b)), "b2k_dp_slice")
+    return a.value, b.value
+
+
+class HostTrainer:
+    """b2c::StepTrainer behind the C entry points. `scene` is the host dict of b2ctrain_b200.scenes."""
+
+    def __init__(self, scene, W, H, rank=0, world=1, dp_id=None, views_in_flight=4, render_chunks=1, isect_cap=0, ssim_weight=0.2, mask=False,
+                 alpha_lane=False, composite=False, match_alpha_weight=0.1, loss_scale=1.0, bg=(0.0, 0.0, 0.0), lr_mean=0.0, lr_rot=2e-3, lr_scale=5e-3,
+                 lr_opac=0.012, lr_dc=2e-3, lr_sh_rest=2e-4, sparse=True, noise_weight=0.0, noise_clamp=0.0, seed=42, shard_update=True):
+        cfg = B2chConfig()
+        cfg.views_in_flight, cfg.render_chunks, cfg.isect_cap, cfg.ssim_weight = int(views_in_flight), int(render_chunks), int(isect_cap or 0), ssim_weight
+        cfg.mask, cfg.alpha_lane, cfg.composite = int(mask), int(alpha_lane), int(composite)
+        cfg.match_alpha_weight, cfg.loss_scale = match_alpha_weight, loss_scale
+        for i in range(3):
+            cfg.bg[i] = float(bg[i])
+        cfg.lr_mean, cfg.lr_rot, cfg.lr_scale, cfg.lr_opac, cfg.lr_dc, cfg.lr_sh_rest = lr_mean, lr_rot, lr_scale, lr_opac, lr_dc, lr_sh_rest
+        cfg.sparse, cfg.noise_weight, cfg.noise_clamp, cfg.seed, cfg.shard_update = int(sparse), noise_weight, noise_clamp, int(seed), int(shard_update)
+        f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+        self.n, self.degree, self.W, self.H = int(scene["n"]), int(scene["degree"]), int(W), int(H)
+        arrays = [f32(scene[k]) for k in ("pos_op", "quat", "lscale", "sh")]
+        idbuf = None if dp_id is None else (C.c_uint8 * 128).from_buffer_copy(dp_id)
+        self.h = lib().b2ch_trainer_create(self.n, self.degree, *[a.ctypes.data_as(_P) for a in arrays], self.W, self.H, C.byref(cfg), int(rank), int(world), idbuf)
+        if not self.h:
+            raise RuntimeError(f"b2ch_trainer_create: {lib().b2ch_last_error().decode()}")
+        self.h = C.c_void_p(self.h)
+
+    def close(self):
+        if self.h:
+            lib().b2ch_trainer_destroy(self.h)
+            self.h = None
+
+    def add_view(self, cam, rgba):
+        """cam: camera dict of b2ctrain_b200.scenes; rgba: packed RGBA8 target as a numpy array (or anything exposing a
+        buffer of W * H 32-bit words). Returns the view's index."""
+        c = api.camera_from(cam)
+        t = np.ascontiguousarray(np.asarray(rgba).view(np.uint32))
+        assert t.size == self.W * self.H
+        idx = lib().b2ch_trainer_add_view(self.h, C.byref(c), t.ctypes.data_as(_P))
+        if idx < 0:
+            raise RuntimeError(f"b2ch_trainer_add_view: {lib().b2ch_last_error().decode()}")
+        return idx
+
+    def step(self, views, stream, from_host=False):
+        """One optimisation step over the views (indices), enqueued on the CUDA stream given as an integer handle."""
+        arr = (C.c_int32 * len(views))(*views)
+        _check(lib().b2ch_trainer_step(self.h, arr, len(views), C.c_void_p(int(stream)), int(from_host)), "b2ch_trainer_step")
+
+    def read_loss(self, stream):
+        out = (C.c_float * 16)()
+        _check(lib().b2ch_trainer_read_loss(self.h, out, C.c_void_p(int(stream))), "b2ch_trainer_read_loss")
+        return np.array(out[:], np.float32)
+
+    def set_profile(self, on):
+        lib().b2ch_trainer_set_profile(self.h, int(on))
+
+    def info(self):
+        out = (C.c_uint64 * 10)()
+        _check(lib().b2ch_trainer_info(self.h, out), "b2ch_trainer_info")
+        ms = np.frombuffer(bytes(out)[64:76], np.float32)
+        return dict(isect_cap=int(out[0]), overflow_redos=int(out[1]), h2d_bytes=int(out[2]), n=int(out[3]), adam_t=int(out[4]), lanes=int(out[5]),
+                    views=int(out[6]), tile_bits=int(out[7]), phase_ms=dict(views=float(ms[0]), update=float(ms[1]), step=float(ms[2])))
+
+    def download(self):
+        K = (self.degree + 1) ** 2
+        a = [np.zeros((self.n, 4), np.float32) for _ in range(3)] + [np.zeros((self.n, K, 3), np.float32)]
+        _check(lib().b2ch_trainer_download(self.h, *[x.ctypes.data_as(_P) for x in a]), "b2ch_trainer_download")
+        return dict(n=self.n, degree=self.degree, pos_op=a[0], quat=a[1], lscale=a[2], sh=a[3])
+
+    def reduce_statistics(self, stream):
+        _check(lib().b2ch_trainer_reduce_statistics(self.h, C.c_void_p(int(stream))), "b2ch_trainer_reduce_statistics")
+
+    def checksum(self, stream):
+        return int(lib().b2ch_trainer_checksum(self.h, C.c_void_p(int(stream))))

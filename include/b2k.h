@@ -219,6 +219,11 @@ uint64_t b2k_bwd_scratch_bytes(int32_t W, int32_t H, int32_t n_chunks, uint64_t 
 /* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). Same gradients; the
  * tile lists are replayed in segments of 256 fragments from the forward's checkpoints in ctx->bwd_scratch. */
 int b2k_raster_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kRenderOpts* opts, b2k_stream_t s);
+/* rasterize_backward_tc, src/gpu/render.h:107-109 (raster_bwd_tc_kernel, src/gpu/raster_bwd_tc.cu:30-225), as far as its
+ * contract goes: the pixel gradients in v_out were produced with LossParams::grad_scale applied and the per-splat
+ * lanes leave divided by it (raster_bwd_tc.cu:198). The reference needs the scale to keep fp16 operands in range; the
+ * reduction here is fp32 throughout, so this is b2k_raster_bwd with the division folded into its reduction. */
+int b2k_raster_bwd_scaled(const B2kCtx* ctx, const B2kModel* m, const B2kRenderOpts* opts, float grad_scale, b2k_stream_t s);
 /* optimizer_step, src/gpu/optim.h:50 (optim_kernel, src/gpu/optim.cu:100-378): projection backward fused with
  * sparse Adam; consumes and clears ctx->v_splat / vis_flag. With grad_out set it writes gradients and returns. */
 int b2k_optim_fused(const B2kCtx* ctx, const B2kModel* m, const B2kCamera* cam, const B2kOptim* op, b2k_stream_t s);
@@ -237,6 +242,51 @@ int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t s)
  * that the update of one slice can run while the all-reduce of the next slice is in flight. Same device code and the
  * same results as b2k_adam over the whole model (optim.cu:299-376). */
 int b2k_adam_range(const B2kModel* m, const B2kOptim* op, float* grad, int32_t first, int32_t count, b2k_stream_t s);
+
+/* ---- data parallelism over the GPUs of one node ----
+ * The reference is single-GPU; these entry points shard its step by view (one process or thread per GPU, a full model
+ * replica each) as its design allows: views are independent until optimizer_step (src/train/trainer.cpp:464-529).
+ * NCCL is loaded at run time (libnccl.so.2) by the first b2k_dp_init; nothing else in the library needs it. */
+typedef struct B2kDp B2kDp;
+#define B2K_DP_ID_BYTES 128
+#define B2K_DP_MAX_RANKS 16
+/* Rank 0 makes the rendezvous id and hands the 128 bytes to the other ranks over any host channel. */
+int b2k_dp_unique_id(uint8_t* id);
+/* Joins the communicator of `world` ranks on the current device (collective: every rank calls it). */
+int b2k_dp_init(B2kDp** dp, const uint8_t* id, int32_t rank, int32_t world);
+int b2k_dp_destroy(B2kDp* dp);
+/* In-place sum over ranks of the dense gradient accumulator grad[count] (count = n * (11 + 3K) floats): the plain
+ * ncclAllReduce form of the step, after which every rank runs the identical b2k_adam. */
+int b2k_dp_allreduce_grads(B2kDp* dp, float* grad, uint64_t count, b2k_stream_t s);
+/* In-place all-reduce of a refinement statistic over ranks: op 0 = sum (vis_count, vis_weight), 1 = max (refine_norm,
+ * max_screen; src/gpu/optim.cu:122-124, src/gpu/project.cu:82-83). */
+int b2k_dp_allreduce_stat(B2kDp* dp, float* stat, uint64_t count, int32_t op, b2k_stream_t s);
+/* Stream-ordered barrier over the ranks (a 4-byte all-reduce): work enqueued after it on any rank starts only when
+ * every rank's work enqueued before it has finished. */
+int b2k_dp_barrier(B2kDp* dp, b2k_stream_t s);
+/* Makes a device buffer of every rank addressable from this one: `base` must be the start of a cudaMalloc allocation
+ * of this rank; on return peers[r] is rank r's buffer mapped into this process (peers[rank] == base). Collective;
+ * synchronises the stream. The mappings live until b2k_dp_destroy. Needs peer access between the GPUs (NVLink). */
+int b2k_dp_share(B2kDp* dp, void* base, void** peers, b2k_stream_t s);
+/* The splats [first, first + count) whose update rank `rank` of `world` owns in b2k_dp_adam_shard: contiguous, starts
+ * multiples of 128, together covering [0, n) exactly. Pure host arithmetic (no GPU needed). */
+int b2k_dp_slice(int32_t n, int32_t rank, int32_t world, int32_t* first, int32_t* count);
+/* Replica pointers for b2k_dp_adam_shard, each array indexed by rank (from b2k_dp_share). */
+typedef struct {
+  float* grad[B2K_DP_MAX_RANKS];     /* every rank's gradient accumulator [n][11+3K] */
+  float* pos_op[B2K_DP_MAX_RANKS];   /* every rank's parameter buffers, laid out like B2kModel's */
+  float* quat[B2K_DP_MAX_RANKS];
+  float* lscale[B2K_DP_MAX_RANKS];
+  float* sh_dc[B2K_DP_MAX_RANKS];
+  float* sh_hi[B2K_DP_MAX_RANKS];
+} B2kDpPeers;
+/* Reduce-scatter + Adam + all-gather of the data-parallel step as ONE kernel over peer memory: this rank sums the rows
+ * of its slice (b2k_dp_slice) from every rank's accumulator with plain peer loads, runs the update of b2k_adam on them
+ * (moments, last_step and the Adam-mini second moment live only on the owner) and stores the updated parameters
+ * into every rank's replica. Replicas stay bit-identical because each splat is updated by exactly one rank. The caller
+ * brackets it with b2k_dp_barrier (before: all ranks' accumulators complete; after: all replicas written) and clears
+ * its own accumulator afterwards. Same arithmetic as optim_kernel's update half (src/gpu/optim.cu:299-376). */
+int b2k_dp_adam_shard(B2kDp* dp, const B2kModel* m, const B2kOptim* op, const B2kDpPeers* peers, b2k_stream_t s);
 
 /* ---- helpers around the path ---- */
 /* min_scale_kernel, src/gpu/refine.cu:27-38: lscale.w = sqrt(0.1) * min over cameras of distance / focal. */

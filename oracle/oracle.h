@@ -124,6 +124,7 @@ double orc_step(int n, int degree, int active_degree, const float* pos_op, const
                 const OrcLoss* lp, int backward, double* out_rgba, double* grad, int64_t* counters);
 
 int orc_num_threads(void);
+void orc_set_num_threads(int n);   /* OpenMP threads of the loops (overrides an inherited OMP_NUM_THREADS) */
 
 #ifdef __cplusplus
 }

@@ -187,6 +187,14 @@ extern "C" void orc_min_scale(int n, const float* pos_op, float* lscale, const f
   }
 }
 
+extern "C" void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 extern "C" int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

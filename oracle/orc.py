@@ -341,6 +341,11 @@ def num_threads():
     return int(lib().orc_num_threads())
 
 
+def set_num_threads(n):
+    """OpenMP threads of the oracle's loops (a launcher may have exported OMP_NUM_THREADS=1 to this process)."""
+    lib().orc_set_num_threads(int(n))
+
+
 # ---- the reference's own CUDA kernels (oracle/_ref/librefcuda.so), second oracle and speed incumbent ----
 
 _refcu = None

@@ -1,0 +1,58 @@
+"""Worker of the two-rank data-parallel test (launched by torch.distributed.run, one process per GPU): runs the C++ step
+trainer on this rank's GPU and compares replicas and the one-rank result. Not collected by pytest."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from b2ctrain_b200 import host_trainer as ht   # noqa: E402
+from tests.test_host_trainer import case      # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("gloo")
+    ident = [ht.make_dp_id() if rank == 0 else None]
+    dist.broadcast_object_list(ident, src=0)
+    scene, cams, targets = case()
+    kw = dict(lr_mean=1e-4, sparse=True, noise_weight=5e-3, noise_clamp=2e-3, views_in_flight=2)
+    tr = ht.HostTrainer(scene, 160, 120, rank=rank, world=world, dp_id=ident[0], shard_update=os.environ.get("B2K_DP_SHARD", "1") == "1", **kw)
+    for cam, t in zip(cams, targets):
+        tr.add_view(cam, t)
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        tr.step(list(range(len(cams))), stream)
+    torch.cuda.synchronize()
+    sums = [None] * world
+    dist.all_gather_object(sums, tr.checksum(stream))
+    assert len(set(sums)) == 1, f"replicas differ: {sums}"
+    got = tr.download()
+    loss = tr.read_loss(stream)
+    losses = [None] * world
+    dist.all_gather_object(losses, (float(loss[2]), float(loss[3])))
+    if rank == 0:
+        one = ht.HostTrainer(scene, 160, 120, **kw)
+        for cam, t in zip(cams, targets):
+            one.add_view(cam, t)
+        for _ in range(3):
+            one.step(list(range(len(cams))), stream)
+        want = one.download()
+        for k in ("pos_op", "quat", "lscale", "sh"):
+            err = float(np.max(np.abs(got[k] - want[k]) / (np.abs(want[k]) + 1e-3)))
+            assert err <= 5e-5, (k, err)
+        l1 = one.read_loss(stream)
+        assert sum(c for _, c in losses) == l1[3] == len(cams)
+        assert abs(sum(s for s, _ in losses) - l1[2]) <= 1e-5 * abs(l1[2])
+        one.close()
+        print("dp worker ok", sums[0])
+    dist.barrier()
+    tr.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

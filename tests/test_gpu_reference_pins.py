@@ -12,8 +12,10 @@ from tests.util import Harness, rel_l2
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(orc.refcuda_lib() is None, reason="oracle/_ref/librefcuda.so was not built (no reference tree at build time)")]
 
 # Stated tolerances. Both sides are fp32 kernels; the reference side is compiled with --use_fast_math.
-TOL_STEP_PARAM = 2e-5        # parameters after a plain Adam step: |a - b| / (|b| + 1e-3)
-TOL_STEP_PARAM_GAP = 1e-4    # ... after a lazy catch-up over skipped steps (fp32 1 - 0.999^t cancels)
+TOL_STEP_UPDATE = 1e-4       # a parameter's update (new - old) after a plain Adam step, relative to the update
+TOL_STEP_UPDATE_GAP = 2e-3   # ... at the third step, a lazy catch-up over skipped steps (fp32 1 - 0.999^t cancels, and the two
+                             # sides have run on their own states since the first step; observed 9e-4)
+TOL_STEP_VALUE = 4e-7        # plus this much of (|value| + 1): fp32 rounding of the stored parameter
 TOL_STEP_MOMENT = 2e-5       # Adam moments, relative L2
 TOL_FULL_IMAGE = 1e-3        # full-size image, abs, for all but TOL_FULL_IMAGE_OFF of the pixels
 TOL_FULL_IMAGE_OFF = 1e-5    # fraction of pixels that may sit on a discrete decision (alpha cut, transmittance stop)
@@ -86,7 +88,8 @@ def test_optimizer_step_matches_the_reference_kernel(variant):
         # the gradient pass above also counted the visibility statistic: put it back, the step below counts it once
         h.model.vis_count[:n].copy_(h.torch.from_numpy(ref.download("vis_count", (n,), np.float32)))
         set_product_lanes()
-        before = h.model.pos_op[:n, :3].cpu().numpy().copy()
+        start = product_state(h)
+        before = start["pos_op"][:, :3].copy()
         ref.optim(t=t, sparse=sparse, step=t, **kw)
         op = h.api.OptimParams(cam, active_sh_degree=degree, t=t, sparse=sparse, step=t, **kw)
         if variant == "split":
@@ -97,13 +100,17 @@ def test_optimizer_step_matches_the_reference_kernel(variant):
             h.api.optimizer_step(h.ctx, h.model, op)
         h.torch.cuda.synchronize()
         want, got = ref.model_state(), product_state(h)
-        tol = TOL_STEP_PARAM if t <= 2 else TOL_STEP_PARAM_GAP
+        # A parameter is held through its UPDATE: the two steps may differ by TOL_STEP_UPDATE of the step taken (fp32
+        # bias corrections 1 - beta^t cancel, and the reference evaluates powf under fast-math), plus the rounding of the
+        # value itself. The same bound relative to the value would be meaningless for a logit that lands next to zero.
+        tol = TOL_STEP_UPDATE if t <= 2 else TOL_STEP_UPDATE_GAP
         for k in ("pos_op", "quat", "lscale", "sh"):
-            rel = (np.abs(got[k] - want[k]) / (np.abs(want[k]) + 1e-3))[rows]
+            bound = tol * np.abs(want[k] - start[k]) + TOL_STEP_VALUE * (np.abs(want[k]) + 1.0)
+            excess = (np.abs(got[k] - want[k]) / bound)[rows]
             if k in sure:
                 assert sure[k].mean() > 0.995, (k, sure[k].mean())
-                rel = rel[sure[k][rows]]
-            assert float(rel.max()) <= tol, (variant, t, k, float(rel.max()))
+                excess = excess[sure[k][rows]]
+            assert float(excess.max()) <= 1.0, (variant, t, k, float(excess.max()))
         for k in ("m_pos", "v_pos", "m_q", "v_q", "m_ls", "v_ls", "m_sh", "v_sh"):
             assert rel_l2(got[k][rows], want[k][rows]) <= TOL_STEP_MOMENT, (variant, t, k, rel_l2(got[k][rows], want[k][rows]))
         assert np.array_equal(got["last_step"][rows], want["last_step"][rows]), (variant, t)
