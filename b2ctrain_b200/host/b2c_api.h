@@ -78,12 +78,27 @@ struct SplatCloud {
   int sh_degree = 0;
   std::vector<float> pos, log_scale, quat, opacity, sh;   // [n][3], [n][3], [n][4] (w,x,y,z), [n], [n][K][3]
   std::vector<float> floor;                               // [n] 3D-filter floor, empty = none
+  bool has_scales = true;                                 // false when the file carried no scale_* columns
+  bool has_evidence = false; std::vector<float> evidence; // [n][7] w_in, w_all, err, views, dir xyz (the evidence pass)
+  bool has_labels = false; std::vector<float> labels;     // [n][2] class id, winner's share (the label vote)
   int K() const { return (sh_degree + 1) * (sh_degree + 1); }
   void resize(size_t count, int degree) {
     n = count; sh_degree = degree;
     pos.assign(n * 3, 0.f); log_scale.assign(n * 3, 0.f); quat.assign(n * 4, 0.f); opacity.assign(n, 0.f); sh.assign(n * K() * 3, 0.f);
+    for (size_t i = 0; i < n; i++) quat[i * 4] = 1.f;
+    if (has_evidence) evidence.assign(n * 7, 0.f);
+    if (has_labels) labels.assign(n * 2, 0.f);
   }
 };
+
+// Splat PLY files (src/ply.h:44-53, src/ply.cpp:80-226) and the camera list of the render subcommand.
+constexpr float SH_C0 = 0.28209479177387814f;
+extern const char* const EVIDENCE_FIELDS[7];
+extern const char* const LABEL_FIELDS[2];
+bool ply_is_vertex_only(const std::string& path);
+SplatCloud read_ply(const std::string& path);
+std::vector<std::string> read_ply_comments(const std::string& path);
+void write_ply(const std::string& path, const SplatCloud& c, const std::vector<std::string>& comments);
 
 // Pinhole camera, world-to-camera, OpenCV axes (src/dataset/camera.h:9-16).
 struct Camera {

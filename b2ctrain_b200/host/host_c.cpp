@@ -4,6 +4,7 @@
 #include "host_c.h"
 #include <cstring>
 #include <string>
+#include "render_io.h"
 #include "trainer.h"
 
 using namespace b2c;
@@ -95,4 +96,42 @@ extern "C" uint64_t b2ch_trainer_checksum(void* h, void* stream) {
   uint64_t v = 0;
   guarded([&] { v = ((StepTrainer*)h)->replica_checksum((cudaStream_t)stream); });
   return v;
+}
+
+// ---- files: splat PLY and the headless render front end ----
+extern "C" int b2ch_render_headless(const char* splat, const char* cameras, const char* output_dir, const float* background, int32_t sh_degree, int32_t depth,
+                                    int32_t render_chunks, int32_t rank, int32_t world, int32_t* rendered) {
+  return guarded([&] {
+    HeadlessOptions o;
+    if (background) for (int k = 0; k < 3; k++) o.background[k] = background[k];
+    o.sh_degree = sh_degree; o.depth = depth != 0; o.render_chunks = render_chunks; o.rank = rank; o.world = world;
+    const int n = render_headless(splat, cameras, output_dir, o);
+    if (rendered) *rendered = n;
+  });
+}
+
+// Reads a PLY into caller arrays in two calls: with every pointer NULL it only reports n and the SH degree.
+extern "C" int b2ch_ply_read(const char* path, int32_t* n, int32_t* degree, float* pos, float* log_scale, float* quat, float* opacity, float* sh, float* evidence,
+                             float* labels, int32_t* flags) {
+  return guarded([&] {
+    const SplatCloud c = read_ply(path);
+    *n = (int32_t)c.n; *degree = c.sh_degree;
+    if (flags) *flags = (c.has_scales ? 1 : 0) | (c.has_evidence ? 2 : 0) | (c.has_labels ? 4 : 0);
+    auto put = [](float* dst, const std::vector<float>& src) { if (dst && !src.empty()) std::memcpy(dst, src.data(), src.size() * sizeof(float)); };
+    put(pos, c.pos); put(log_scale, c.log_scale); put(quat, c.quat); put(opacity, c.opacity); put(sh, c.sh); put(evidence, c.evidence); put(labels, c.labels);
+  });
+}
+
+extern "C" int b2ch_ply_write(const char* path, int32_t n, int32_t degree, const float* pos, const float* log_scale, const float* quat, const float* opacity,
+                              const float* sh, const float* evidence, const float* labels, const char* comment) {
+  return guarded([&] {
+    SplatCloud c;
+    c.has_evidence = evidence != nullptr; c.has_labels = labels != nullptr;
+    c.resize((size_t)n, degree);
+    auto take = [](std::vector<float>& dst, const float* src) { if (src && !dst.empty()) std::memcpy(dst.data(), src, dst.size() * sizeof(float)); };
+    take(c.pos, pos); take(c.log_scale, log_scale); take(c.quat, quat); take(c.opacity, opacity); take(c.sh, sh); take(c.evidence, evidence); take(c.labels, labels);
+    std::vector<std::string> comments;
+    if (comment && *comment) comments.push_back(comment);
+    write_ply(path, c, comments);
+  });
 }

@@ -44,6 +44,20 @@ int b2ch_trainer_download(void* trainer, float* pos_op, float* quat, float* lsca
 int b2ch_trainer_reduce_statistics(void* trainer, void* stream);
 uint64_t b2ch_trainer_checksum(void* trainer, void* stream);
 
+/* ---- files ---- */
+/* The reference's `render` subcommand without the PNG step (src/render/renderer.cpp:199-368): reads the splat PLY and
+ * cameras.json, renders this rank's cameras (rank, rank + world, ...) and writes <output_dir>/<name>.rgba8 (W x H x 4
+ * bytes) and, with depth, <name>.depth.f32. background: 3 floats or NULL; sh_degree < 0: the model's. */
+int b2ch_render_headless(const char* splat, const char* cameras, const char* output_dir, const float* background, int32_t sh_degree, int32_t depth,
+                         int32_t render_chunks, int32_t rank, int32_t world, int32_t* rendered);
+/* read_ply / write_ply (src/ply.h:51-53). Reading: call once with the array pointers NULL for n and the degree, then
+ * with arrays of [n][3], [n][3], [n][4], [n], [n][K][3], [n][7], [n][2] (any may stay NULL). flags: 1 scales present,
+ * 2 evidence columns, 4 label columns. */
+int b2ch_ply_read(const char* path, int32_t* n, int32_t* degree, float* pos, float* log_scale, float* quat, float* opacity, float* sh, float* evidence,
+                  float* labels, int32_t* flags);
+int b2ch_ply_write(const char* path, int32_t n, int32_t degree, const float* pos, const float* log_scale, const float* quat, const float* opacity,
+                   const float* sh, const float* evidence, const float* labels, const char* comment);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,117 @@
+// The file side of the reference's `render` subcommand, headless: the camera list (camera_from_json,
+// src/render/renderer.cpp:185-197; width / height / cameras[] of cameras.json, renderer.cpp:207-212) and the per-camera
+// loop (renderer.cpp:345-363) up to raw buffers on disk: <name>.rgba8 (W x H x 4 bytes, quantised like the reference's
+// PNG rows, renderer.cpp:183,366-368) and, on request, <name>.depth.f32 (W x H floats, expected depth). PNG encoding
+// stays with whoever consumes the buffers.
+#include "render_io.h"
+#include <cmath>
+#include <fstream>
+#include <sstream>
+#include "json_min.h"
+
+namespace b2c {
+
+namespace {
+std::string slurp(const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) throw std::runtime_error("failed to open '" + path + "'");
+  std::ostringstream ss; ss << f.rdbuf();
+  return ss.str();
+}
+float num(const Json& j) { return (float)j.number(); }
+}  // namespace
+
+Camera camera_from_json(const Json& c, int W, int H) {
+  Camera cam;
+  cam.width = W; cam.height = H;
+  cam.fx = num(c.at("fx")); cam.fy = num(c.at("fy")); cam.cx = num(c.at("cx")); cam.cy = num(c.at("cy"));
+  // "rotation" is an OpenGL camera-to-world matrix (columns = the camera's axes, Y up, Z backward). The OpenCV
+  // world-to-camera rotation is its transpose with the Y and Z axes flipped.
+  const Json& rot = c.at("rotation");
+  for (int r = 0; r < 3; r++)
+    for (int col = 0; col < 3; col++) cam.R[r * 3 + col] = num(rot[(size_t)col][(size_t)r]) * (r == 0 ? 1.f : -1.f);
+  const Json& p = c.at("position");
+  const float pos[3] = {num(p[0]), num(p[1]), num(p[2])};
+  for (int r = 0; r < 3; r++) cam.t[r] = -(cam.R[r * 3] * pos[0] + cam.R[r * 3 + 1] * pos[1] + cam.R[r * 3 + 2] * pos[2]);
+  cam.update_pos();
+  return cam;
+}
+
+CameraList read_cameras_json(const std::string& path) {
+  const Json j = Json::parse(slurp(path));
+  CameraList out;
+  out.W = (int)j.at("width").number(); out.H = (int)j.at("height").number();
+  if (out.W <= 0 || out.H <= 0) throw std::runtime_error("cameras: bad image size");
+  const Json& cams = j.at("cameras");
+  for (size_t i = 0; i < cams.items.size(); i++) {
+    const Json& c = cams[i];
+    out.names.push_back(c.at("name").string());
+    out.cams.push_back(camera_from_json(c, out.W, out.H));
+  }
+  return out;
+}
+
+void write_cameras_json(const std::string& path, const CameraList& list) {
+  std::ofstream f(path);
+  if (!f) throw std::runtime_error("failed to open '" + path + "' for writing");
+  f.precision(9);
+  f << "{\"width\": " << list.W << ", \"height\": " << list.H << ", \"cameras\": [";
+  for (size_t i = 0; i < list.cams.size(); i++) {
+    const Camera& c = list.cams[i];
+    f << (i ? ",\n" : "\n") << "  {\"name\": \"" << list.names[i] << "\", \"fx\": " << c.fx << ", \"fy\": " << c.fy << ", \"cx\": " << c.cx << ", \"cy\": " << c.cy
+      << ", \"position\": [" << c.pos[0] << ", " << c.pos[1] << ", " << c.pos[2] << "], \"rotation\": [";
+    for (int r = 0; r < 3; r++) {   // back to OpenGL camera-to-world: transpose, Y and Z columns flipped
+      f << (r ? ", [" : "[");
+      for (int col = 0; col < 3; col++) f << (col ? ", " : "") << c.R[col * 3 + r] * (col == 0 ? 1.f : -1.f);
+      f << "]";
+    }
+    f << "]}";
+  }
+  f << "\n]}\n";
+}
+
+static unsigned char to_u8(float v) { return (unsigned char)std::lround(std::min(std::max(v, 0.f), 1.f) * 255.f); }
+
+int render_headless(const std::string& splat_path, const std::string& cameras_path, const std::string& output_dir, const HeadlessOptions& opt) {
+  SplatCloud cloud = read_ply(splat_path);
+  if (!cloud.has_scales) throw std::runtime_error("ply '" + splat_path + "' has no scales");
+  const CameraList list = read_cameras_json(cameras_path);
+  const int W = list.W, H = list.H;
+  cudaStream_t stream = 0;
+  Model model; model.upload(cloud, stream);
+  RenderCtx ctx;
+  ctx.want_depth = opt.depth;
+  ctx.n_chunks = opt.render_chunks > 1 ? opt.render_chunks : 1;
+  ctx.setup(W, H, model.cap, stream);
+  const int sh_degree = opt.sh_degree >= 0 ? std::min(opt.sh_degree, model.degree) : model.degree;
+  std::vector<unsigned char> img((size_t)W * H * 4);
+  int count = 0;
+  for (size_t i = (size_t)opt.rank; i < list.cams.size(); i += (size_t)std::max(1, opt.world)) {   // cameras split round-robin over ranks
+    RenderParams p; p.cam = CameraGPU::from(list.cams[i], W, H);
+    for (int k = 0; k < 3; k++) p.bg[k] = opt.background[k];
+    p.sh_degree = sh_degree; p.bwd_info = false;
+    render_forward(ctx, model, p, stream);
+    const std::vector<float4> out = ctx.out_rgba.download((size_t)W * H, stream);
+    for (size_t px = 0; px < (size_t)W * H; px++) {
+      img[px * 4] = to_u8(out[px].x); img[px * 4 + 1] = to_u8(out[px].y); img[px * 4 + 2] = to_u8(out[px].z); img[px * 4 + 3] = to_u8(out[px].w);
+    }
+    std::string name = list.names[i];
+    const size_t dot = name.rfind('.');
+    if (dot != std::string::npos) name = name.substr(0, dot);
+    {
+      std::ofstream f(output_dir + "/" + name + ".rgba8", std::ios::binary);
+      f.write((const char*)img.data(), (std::streamsize)img.size());
+      if (!f) throw std::runtime_error("failed to write '" + output_dir + "/" + name + ".rgba8'");
+    }
+    if (opt.depth) {
+      const std::vector<float> d = ctx.out_depth.download((size_t)W * H, stream);
+      std::ofstream f(output_dir + "/" + name + ".depth.f32", std::ios::binary);
+      f.write((const char*)d.data(), (std::streamsize)(d.size() * sizeof(float)));
+      if (!f) throw std::runtime_error("failed to write '" + output_dir + "/" + name + ".depth.f32'");
+    }
+    count++;
+  }
+  return count;
+}
+
+}  // namespace b2c

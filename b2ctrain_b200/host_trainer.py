@@ -34,6 +34,9 @@ SIGNATURES = {
     "b2ch_trainer_download": (C.c_int, [_P, _P, _P, _P, _P]),
     "b2ch_trainer_reduce_statistics": (C.c_int, [_P, _P]),
     "b2ch_trainer_checksum": (C.c_uint64, [_P, _P]),
+    "b2ch_render_headless": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
+    "b2ch_ply_read": (C.c_int, [C.c_char_p, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "b2ch_ply_write": (C.c_int, [C.c_char_p, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_char_p]),
 }
 
 _lib = None
@@ -105,9 +108,12 @@ class HostTrainer:
         """cam: camera dict of b2ctrain_b200.scenes; rgba: packed RGBA8 target as a numpy array (or anything exposing a
         buffer of W * H 32-bit words). Returns the view's index."""
         c = api.camera_from(cam)
-        t = np.ascontiguousarray(np.asarray(rgba).view(np.uint32))
-        assert t.size == self.W * self.H
-        idx = lib().b2ch_trainer_add_view(self.h, C.byref(c), t.ctypes.data_as(_P))
+        ptr = None
+        if rgba is not None:   # None: a view another rank renders (only its camera is known here)
+            t = np.ascontiguousarray(np.asarray(rgba).view(np.uint32))
+            assert t.size == self.W * self.H
+            ptr = t.ctypes.data_as(_P)
+        idx = lib().b2ch_trainer_add_view(self.h, C.byref(c), ptr)
         if idx < 0:
             raise RuntimeError(f"b2ch_trainer_add_view: {lib().b2ch_last_error().decode()}")
         return idx
@@ -143,3 +149,46 @@ class HostTrainer:
 
     def checksum(self, stream):
         return int(lib().b2ch_trainer_checksum(self.h, C.c_void_p(int(stream))))
+
+
+# ---- files: splat PLY (src/ply.cpp:80-226) and the headless render front end (src/render/renderer.cpp:199-368) ----
+
+def read_ply(path):
+    """Host cloud dict of the reference's SplatCloud fields: n, degree, pos [n][3], log_scale [n][3], quat [n][4], opacity
+    [n], sh [n][K][3], plus evidence [n][7] / labels [n][2] when the file carries them, and has_scales."""
+    n, deg, flags = C.c_int32(0), C.c_int32(0), C.c_int32(0)
+    p = path.encode()
+    _check(lib().b2ch_ply_read(p, C.byref(n), C.byref(deg), None, None, None, None, None, None, None, C.byref(flags)), "read_ply")
+    n, K = n.value, (deg.value + 1) ** 2
+    out = dict(n=n, degree=deg.value, pos=np.zeros((n, 3), np.float32), log_scale=np.zeros((n, 3), np.float32), quat=np.zeros((n, 4), np.float32),
+               opacity=np.zeros(n, np.float32), sh=np.zeros((n, K, 3), np.float32), has_scales=bool(flags.value & 1))
+    if flags.value & 2:
+        out["evidence"] = np.zeros((n, 7), np.float32)
+    if flags.value & 4:
+        out["labels"] = np.zeros((n, 2), np.float32)
+    ptr = lambda k: out[k].ctypes.data_as(_P) if k in out else None
+    _check(lib().b2ch_ply_read(p, C.byref(C.c_int32()), C.byref(C.c_int32()), ptr("pos"), ptr("log_scale"), ptr("quat"), ptr("opacity"), ptr("sh"),
+                               ptr("evidence"), ptr("labels"), None), "read_ply")
+    return out
+
+
+def write_ply(path, cloud, comment=""):
+    f32 = lambda k: None if cloud.get(k) is None else np.ascontiguousarray(cloud[k], dtype=np.float32)
+    arrs = {k: f32(k) for k in ("pos", "log_scale", "quat", "opacity", "sh", "evidence", "labels")}
+    ptr = lambda k: None if arrs[k] is None else arrs[k].ctypes.data_as(_P)
+    _check(lib().b2ch_ply_write(path.encode(), int(cloud["n"]), int(cloud["degree"]), ptr("pos"), ptr("log_scale"), ptr("quat"), ptr("opacity"), ptr("sh"),
+                                ptr("evidence"), ptr("labels"), comment.encode()), "write_ply")
+
+
+def cloud_from_scene(scene):
+    """The SplatCloud-style dict of a scene dict of b2ctrain_b200.scenes (the floor lane is not part of the file format)."""
+    return dict(n=scene["n"], degree=scene["degree"], pos=scene["pos_op"][:, :3], log_scale=scene["lscale"][:, :3], quat=scene["quat"],
+                opacity=scene["pos_op"][:, 3], sh=scene["sh"])
+
+
+def render_headless(splat, cameras, output_dir, background=(0.0, 0.0, 0.0), sh_degree=-1, depth=False, render_chunks=1, rank=0, world=1):
+    bg = (C.c_float * 3)(*background)
+    done = C.c_int32(0)
+    _check(lib().b2ch_render_headless(splat.encode(), cameras.encode(), output_dir.encode(), bg, int(sh_degree), int(depth), int(render_chunks), int(rank),
+                                      int(world), C.byref(done)), "render_headless")
+    return done.value

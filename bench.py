@@ -37,7 +37,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
     ap.add_argument("--views-in-flight", type=int, default=4, help="views of a step processed concurrently on separate streams")
-    ap.add_argument("--reduce-slices", type=int, default=4, help="slices of the gradient all-reduce pipelined with the Adam update (N > 1)")
+    ap.add_argument("--allreduce", action="store_true", help="N > 1: ncclAllReduce of the dense gradient + replicated Adam instead of the sharded "
+                    "peer-memory update")
     ap.add_argument("--chunks", type=int, default=0, help="depth chunks of the front-to-back renderer (1 = bin the whole view first, as the reference "
                     "does; 0 = choose: 4 for scenes of a million splats and more, where most intersections lie behind saturated pixels, else 1)")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
@@ -276,16 +277,25 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     del gt_scene
     torch.cuda.empty_cache()
     host_targets = [None] * n_views
-    dev_targets = [None] * n_views
     for j, v in enumerate(mine):
         host_targets[v] = host_targets_mine[j]
-        dev_targets[v] = host_targets_mine[j].to(device)
+    if args.chunks > 1:   # the chunked renderer sorts a fraction of what the whole-view target renders needed; the trainer regrows if it must
+        cap = min(cap, 1 << 24)
     median_scale = float(np.median(np.exp(scene["lscale"][:, :3])))
-    # MCMC noise on, as the reference's trainer applies it every step (src/train/trainer.cpp:524): lr_mean * mean_noise_weight,
-    # clamp = median scale.
-    tr = Trainer(scene, W, H, device, rank, world, lr_mean=2e-5 * median_scale, sparse=True, noise_weight=2e-5 * median_scale * 50.0,
-                 noise_clamp=median_scale, isect_cap=cap,
-                 views_in_flight=1 if n_views == 1 else args.views_in_flight, reduce_slices=args.reduce_slices, render_chunks=args.chunks)
+    # The timed step runs in the C++ host (b2ctrain_b200/host/trainer.cpp behind libb2chost.so): views in flight, the
+    # data-parallel split and every collective are C++ over the C ABI; this script only hands over scene, views and a stream.
+    # MCMC noise on, as the reference's trainer applies it every step (src/train/trainer.cpp:524): lr_mean * mean_noise_weight
+    # (default 50), clamp = median scale.
+    from b2ctrain_b200 import host_trainer as ht
+    lr_mean = 2e-5 * median_scale
+    loss_kw = dict(mask=True, alpha_lane=True, loss_scale=1.0 / 0.4) if cfg == 4 else {}
+    ident = [None]
+    if world > 1:
+        ident = [ht.make_dp_id() if rank == 0 else None]
+        dist.broadcast_object_list(ident, src=0)
+    lanes = 1 if n_views == 1 else args.views_in_flight
+    tr = ht.HostTrainer(scene, W, H, rank=rank, world=world, dp_id=ident[0], views_in_flight=lanes, render_chunks=args.chunks, isect_cap=cap,
+                        lr_mean=lr_mean, sparse=True, noise_weight=lr_mean * 50.0, noise_clamp=median_scale, shard_update=not args.allreduce, **loss_kw)
     if cfg == 4:   # per-pixel binary mask in the alpha byte, alpha-match lane, --normalize-masked-loss
         mask = torch.from_numpy(scenes.ellipse_mask(W, H, 0.4).astype(np.int64))
         for v in mine:
@@ -293,55 +303,68 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
             t = torch.where(mask > 0, (t & 0x00FFFFFF) | (255 << 24), torch.zeros_like(t))
             t = torch.where(t >= 2 ** 31, t - 2 ** 32, t).to(torch.int32)
             host_targets[v].copy_(t)
-            dev_targets[v] = host_targets[v].to(device)
-        tr.lp.mask, tr.lp.alpha_lane, tr.lp.scale = True, True, 1.0 / 0.4
-    stats = presize(tr, cams, mine, dev_targets, True)
-    for c in tr.ctxs[1:]:   # every lane gets the sized intersection buffers
-        if c.isect_cap < tr.ctx.isect_cap:
-            c._alloc_isect(tr.ctx.isect_cap)
+    for v in range(n_views):   # every rank knows every camera; targets only for the views it renders
+        tr.add_view(cams[v], host_targets[v].numpy() if host_targets[v] is not None else None)
+    all_views = list(range(n_views))
+    stream = torch.cuda.current_stream().cuda_stream
 
-    def timed(targets, steps):
+    def timed(from_host, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         loss = None
         for _ in range(steps):
-            acc = tr.step(cams, targets)
-            loss = acc.cpu() if targets is host_targets else None   # the step's result read back (16 floats)
+            tr.step(all_views, stream, from_host=from_host)
+            loss = tr.read_loss(stream) if from_host else None   # the step's result read back (16 floats)
         e1.record()
         barrier()
         return max_over_ranks(e0.elapsed_time(e1)), loss
 
     sampler.start()
-    timed(dev_targets, args.warmup)
+    timed(False, args.warmup)       # also grows the intersection buffers to what the views need
+    redos_warm = tr.info()["overflow_redos"]
     sampler.mark()
-    ms, _ = timed(dev_targets, args.steps)
+    ms, _ = timed(False, args.steps)
     clocks = sampler.stop()
-    tr.h2d_bytes = 0
-    timed(host_targets, 1)
-    tr.h2d_bytes = 0
-    ms_e2e, loss = timed(host_targets, args.steps)
-    h2d = tr.h2d_bytes / args.steps
+    timed(True, 1)
+    tr.info()                       # resets the byte counter
+    ms_e2e, loss = timed(True, args.steps)
+    info = tr.info()
+    h2d = info["h2d_bytes"] / args.steps
     if world > 1:   # whole-job totals
         t = torch.tensor([h2d], dtype=torch.float64, device=device)
         dist.all_reduce(t)
         h2d = float(t.item())
-    total_isect, over = tr.check_overflow()
-    assert not over, "intersection buffers overflowed inside the timed region"
+    assert info["overflow_redos"] == redos_warm, "intersection buffers overflowed inside the timed region"
     phases = None
     if n_views > 1:   # one more step with an event after each phase; every phase reported as the max over ranks
         barrier()
-        tr.profile = True
-        tr.step(cams, dev_targets)
-        tr.profile = False
-        mine_ms = tr.phase_ms()
+        tr.set_profile(True)
+        tr.step(all_views, stream)
+        tr.set_profile(False)
+        mine_ms = tr.info()["phase_ms"]
         phases = {k: max_over_ranks(v) for k, v in sorted(mine_ms.items())}
         phases["views_fastest_rank"] = -max_over_ranks(-mine_ms["views"])
+        phases["update_form"] = "all-reduce + replicated Adam" if (args.allreduce or world == 1) else "sharded: peer-memory reduce + Adam + parameter broadcast in one kernel"
+    tile_bits = info["tile_bits"]
+    cap = info["isect_cap"]
+    tr.close()
+    del tr
+    torch.cuda.empty_cache()
+    # Stage timing, counts and the roofline object: the same operators one stage at a time through the Python mirror (rank 0).
+    py = stats = None
+    if rank == 0:
+        py = Trainer(scene, W, H, device, 0, 1, lr_mean=lr_mean, sparse=True, noise_weight=lr_mean * 50.0, noise_clamp=median_scale, isect_cap=cap,
+                     views_in_flight=1, render_chunks=args.chunks)
+        if cfg == 4:
+            py.lp.mask, py.lp.alpha_lane, py.lp.scale = True, True, 1.0 / 0.4
+        dev_targets = {v: host_targets[v].to(device) for v in mine[: max(1, args.stage_views)]}
+        stats = presize(py, cams, mine[: max(1, args.stage_views)], dev_targets, True)
 
     views_per_step = n_views
     value = views_per_step * args.steps / (ms / 1e3)
     e2e_value = views_per_step * args.steps / (ms_e2e / 1e3)
-    passes = (tr.ctx.tile_bits + 7) // 8
+    passes = (tile_bits + 7) // 8
     launches_view = 1 + (1 + 12 + 2 + 3 * passes + 1) + 1 + 1 + 1 + 1 + 1
     if args.chunks > 1:   # projection 2, depth sort 13, chunk words 1, per chunk 6 (+1 after the first) + the tile-sort passes, then loss .. projection backward
         launches_view = 2 + 13 + 1 + sum(6 + (2 if ch else 0) + 3 * passes for ch in range(args.chunks)) + 5
@@ -354,8 +377,9 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
            "gpu_launches": launches, "clocks": clocks, "loss_last_view": float(loss[0]) if loss is not None else None}
     if phases:
         res["step_phases_ms_max_over_ranks"] = phases
+    res["config"]["host"] = "C++ (libb2chost.so): step loop, streams and collectives; Python passes scene, views and a stream"
     if rank == 0:
-        res["roofline"], res["stages"] = stage_roofline(args, tr, cams, dev_targets, mine, stats, clocks)
+        res["roofline"], res["stages"] = stage_roofline(args, py, cams, dev_targets, mine, stats, clocks)
         if world == 1 and not args.no_incumbent:
             res["reference_cuda"] = incumbent(scene, cams[mine[0]], host_targets[mine[0]], cfg == 4)
     return res
@@ -383,8 +407,11 @@ def incumbent(scene, cam, host_target, masked):
 
 
 def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
-    """Times each stage of a view with CUDA events (on the launching stream), a few views, and derives the roofline
-    object for the dominant kernel. Algorithmic bytes per stage are the `alg` table below (per-unit figures times the counts V, I, I_b, P of the view)."""
+    """Times the stages of a view one at a time with CUDA events (on the launching stream) over a few views, in the
+    form the timed steps ran (chunked or whole-view rendering), and derives the roofline object for the stage that takes
+    longest. Algorithmic bytes / flops per stage: the `alg` / `flop` tables below, from the counts of the view measured
+    on the device (n splats, V visible, I_sorted pairs sorted, I_b fragments inside the shrunk ranges, touched splats, P
+    pixels, F fragment-pixel evaluations)."""
     import torch
     from b2ctrain_b200 import api
     peaks = {}
@@ -395,129 +422,97 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     hbm = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if peaks else "fallback 6650 GB/s"
     m, ctx = tr.model, tr.ctx
-    K = m.K()
-    chunks = ctx.n_chunks
-    chunked_ms = None
-    if chunks > 1:   # the chunked renderer as one stage (project + per-chunk binning and compositing), then the stages of the whole-view form
-        views0 = mine[: max(1, args.stage_views)]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        tot = 0.0
-        for v in views0:
-            rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True)
-            torch.cuda.synchronize()
-            e0.record(); api.render_forward(ctx, m, rp, sync=False); e1.record()
-            torch.cuda.synchronize()
-            tot += e0.elapsed_time(e1)
-        chunked_ms = tot / len(views0)
-        ctx.n_chunks = 1
-    names = ["project", "bin_sort", "raster_fwd", "loss", "raster_bwd", "proj_bwd"]
-    acc = {k: 0.0 for k in names}
+    K, chunks = m.K(), ctx.n_chunks
     views = mine[: max(1, args.stage_views)]
+    names = (["render_chunked"] if chunks > 1 else ["project", "bin_sort", "raster_fwd"]) + ["loss", "raster_bwd", "proj_bwd"]
+    acc = {k: 0.0 for k in names}
+    touched = F = 0
     for v in views:
         rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True)
         view = api.ViewGPU(targets[v], None, ctx.W, ctx.H)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)]
         torch.cuda.synchronize()
-        ev[0].record(); api.project_splats(ctx, m, rp)
-        ev[1].record(); api.bin_and_sort(ctx, m, sync=False)
-        ev[2].record(); api.rasterize_forward(ctx, rp)
-        ev[3].record(); api.photometric_loss(ctx, view, tr.lp)
-        ev[4].record(); api.rasterize_backward(ctx, m, rp)
-        ev[5].record(); api.projection_backward(ctx, m, tr._op(cams[v]), tr.grad)
-        ev[6].record()
+        ev[0].record()
+        if chunks > 1:
+            api.render_forward(ctx, m, rp, sync=False)
+            k = 1
+        else:
+            api.project_splats(ctx, m, rp); ev[1].record()
+            api.bin_and_sort(ctx, m, sync=False); ev[2].record()
+            api.rasterize_forward(ctx, rp)
+            k = 3
+        ev[k].record(); api.photometric_loss(ctx, view, tr.lp)
+        ev[k + 1].record(); api.rasterize_backward(ctx, m, rp)
+        ev[k + 2].record(); api.projection_backward(ctx, m, tr._op(cams[v]), tr.grad)
+        ev[k + 3].record()
         torch.cuda.synchronize()
-        for k, nm in enumerate(names):
-            acc[nm] += ev[k].elapsed_time(ev[k + 1])
-        touched = int(ctx.d_num_isect[1].item()) & 0xFFFFFFFF   # splats the backward touched: the list the projection backward walks
+        for j, nm in enumerate(names):
+            acc[nm] += ev[j].elapsed_time(ev[j + 1])
+        touched = int(ctx.d_num_isect[1].item()) & 0xFFFFFFFF     # splats the backward touched: the list the projection backward walks
+        assert (int(ctx.d_num_isect[0].item()) & 0xFFFFFFFF) <= ctx.isect_cap, "a stage-timing view overflowed the intersection buffers"
+        # F: fragments every pixel walked = sum over the tile's ranges of min(last, range end) - range start.
+        last = (ctx.last_idx.to(torch.int64) & 0x7FFFFFFF)
+        tx = (torch.arange(ctx.W, device=last.device) // 8).repeat(ctx.H)
+        ty = (torch.arange(ctx.H, device=last.device) // 8).repeat_interleave(ctx.W)
+        rg = ctx.tile_ranges.view(max(chunks, 1), ctx.n_tiles, 2).to(torch.int64)[:, ty * ctx.tiles_x + tx]
+        F = int((torch.minimum(last[None, :], rg[:, :, 1]) - rg[:, :, 0]).clamp_(min=0).sum().item())
     tr.grad.zero_()
     nv = len(views)
-    # Kernel-level split of the binning stage (events inside the library) on the same views.
-    passes = (ctx.tile_bits + 7) // 8
-    ph = np.zeros(10)
-    for v in views:
-        rp = api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True)
-        api.project_splats(ctx, m, rp)
-        ph += np.array(api.bin_and_sort_profile(ctx, m))
-    ph /= nv
-    scatter_ms = [ph[3 + 2 * p] for p in range(min(passes, 3))]
     st = stats[0]
-    V, I, Ib, n, P, tiles = st["V"], st["I"], st["I_b"], m.n, ctx.W * ctx.H, ctx.n_tiles
+    V, I, Is, Ib, n, P, tiles = st["V"], st["I"], st["I_sorted"], st["I_b"], m.n, ctx.W * ctx.H, ctx.n_tiles
+    passes = (ctx.tile_bits + 7) // 8
     alg = {"project": 48 * n + 12 * K * V + 48 * V + 28 * n,
-           "bin_sort": 16 * n * 4 + 24 * n + 8 * I + 20 * I * passes + 4 * I + 8 * tiles,
-           "raster_fwd": 52 * Ib + 36 * P, "loss": 20 * P + 16 * P, "raster_bwd": 28 * P + 52 * Ib + 52 * V,
+           "bin_sort": 16 * n * 4 + 24 * n + 8 * I + 16 * I * passes + 4 * I + 8 * tiles,
+           "raster_fwd": 52 * Ib + 36 * P,
+           # chunked renderer: records + colours of every splat, the depth sort, per chunk the rank / box words, then emit, tile
+           # sort and ranges on the pairs that survive, and the compositing of what the ranges hold
+           "render_chunked": (48 * n + 12 * K * V + 64 * n) + 16 * n * 4 + 20 * n + (8 + 16 * passes + 4) * Is + 8 * tiles * max(chunks, 1) + 52 * Ib + 36 * P,
+           "loss": 20 * P + 16 * P, "raster_bwd": 28 * P + 52 * Ib + 52 * touched,
            "proj_bwd": (52 + 48 + 12 * K) * touched + 2 * 4 * (11 + 3 * K) * touched + 8 * n}   # flags of all splats, records of the touched ones
+    flop = {"raster_fwd": 24 * F, "render_chunked": 24 * F, "raster_bwd": 90 * F}
     stages = {nm: {"ms": acc[nm] / nv, "algorithmic_bytes": int(alg[nm]), "achieved_gbs": alg[nm] / (acc[nm] / nv * 1e-3) / 1e9} for nm in names}
-    stages["bin_sort"]["phases_ms"] = {"depth_sort": ph[0], "scan_emit": ph[1], "tile_count": [ph[2 + 2 * p] for p in range(min(passes, 3))],
-                                       "tile_scatter": scatter_ms, "tile_ranges": ph[8], "total": ph[9]}
-    # Dominant kernel: by total time per view among the single-kernel stages and the radix scatter launches.
-    kernel_ms = {"project_kernel": stages["project"]["ms"], "raster_fwd_kernel": stages["raster_fwd"]["ms"], "photometric_kernel": stages["loss"]["ms"],
-                 "raster_bwd_kernel": stages["raster_bwd"]["ms"], "proj_bwd_kernel": stages["proj_bwd"]["ms"], "scan_emit_kernel": ph[1],
-                 "radix_scatter_kernel": float(sum(scatter_ms))}
-    if chunks > 1:   # the timed steps ran the chunked renderer: the whole-view binning and forward kernels above were not in them
-        for k in ("project_kernel", "radix_scatter_kernel", "scan_emit_kernel", "raster_fwd_kernel"):
-            kernel_ms.pop(k)
-    top = max(kernel_ms, key=kernel_ms.get)
-    extra = {}
-    if top == "radix_scatter_kernel":
-        per_launch_ms = float(np.mean(scatter_ms))
-        bytes_launch = 16 * I          # keys + values read, keys + values written
-        note = f"{len(scatter_ms)} launches per view on I = {I} pairs; 16 B per pair per launch"
-        traffic = int(16.7 * I)   # dram read + write per launch: ncu capture at half the splat count, scaled by pairs
-    else:
-        stage = {"project_kernel": "project", "raster_fwd_kernel": "raster_fwd", "photometric_kernel": "loss", "raster_bwd_kernel": "raster_bwd",
-                 "proj_bwd_kernel": "proj_bwd", "scan_emit_kernel": "bin_sort"}[top]
-        per_launch_ms = kernel_ms[top]
-        bytes_launch = alg[stage] if top != "scan_emit_kernel" else 24 * n + 8 * I
-        note = "one launch per view"
-        traffic = None
-        if top == "raster_bwd_kernel":
-            # dram read + write per launch from an ncu capture at half the splat count (78.5 MB at I_b = 1,243,915), scaled by
-            # the fragments inside the shrunk ranges. The kernel is bound by FP32 issue, not HBM (issue slots 65 % busy on the
-            # SMs that hold tiles with fragments, a quarter of the warp slots occupied): the FP32 figure is reported beside it.
-            traffic = int(63.1 * Ib)
-            note += "; FP32-issue / latency bound (see fp32), so the HBM fraction is small by construction"
-    # Step roofline: every stage at the better of its HBM time and (for the two compositing kernels) its FP32 time.
-    # F = fragment-pixel evaluations of the last timed view (per pixel: last contributing index - start of its tile's
-    # list), charged 24 flop forward and 90 flop backward each; FP32 peak = 2 * 128 lanes * SMs * the SM clock.
-    rp = api.RenderParams(cams[views[-1]], sh_degree=m.degree, bwd_info=True)
-    api.render_forward(ctx, m, rp, sync=True)
-    tx = (torch.arange(ctx.W, device=ctx.last_idx.device) // 8).repeat(ctx.H)
-    ty = (torch.arange(ctx.H, device=ctx.last_idx.device) // 8).repeat_interleave(ctx.W)
-    start = ctx.tile_ranges.view(-1, 2)[:, 0].to(torch.int64)[ty * ctx.tiles_x + tx]
-    F = int((ctx.last_idx[:P].to(torch.int64) - start).clamp_(min=0).sum().item())
+    if chunks <= 1:   # kernel-level split of the binning stage (events inside the library)
+        ph = np.zeros(10)
+        for v in views:
+            api.project_splats(ctx, m, api.RenderParams(cams[v], sh_degree=m.degree, bwd_info=True))
+            ph += np.array(api.bin_and_sort_profile(ctx, m))
+        ph /= nv
+        stages["bin_sort"]["phases_ms"] = {"depth_sort": ph[0], "scan_emit": ph[1], "tile_count": [ph[2 + 2 * p] for p in range(min(passes, 3))],
+                                           "tile_scatter": [ph[3 + 2 * p] for p in range(min(passes, 3))], "tile_ranges": ph[8], "total": ph[9]}
     props = torch.cuda.get_device_properties(ctx.last_idx.device)
     sm_mhz = float((clocks or {}).get("sm_mhz") or 1965.0)   # median SM clock sampled during the timed region
     fp32_peak = 2 * 128 * props.multi_processor_count * sm_mhz * 1e6
-    t_roof = {nm: alg[nm] / (hbm * 1e9) * 1e3 for nm in names}
-    t_roof["raster_fwd"] = max(t_roof["raster_fwd"], 24 * F / fp32_peak * 1e3)
-    t_roof["raster_bwd"] = max(t_roof["raster_bwd"], 90 * F / fp32_peak * 1e3)
-    t_roof = {nm: min(t_roof[nm], stages[nm]["ms"]) for nm in names}   # a stage cannot be credited more than it took
+    # Step roofline of the path that was timed: every stage at the larger of its HBM time and its FP32 time, never more than it took.
+    t_roof = {nm: max(alg[nm] / (hbm * 1e9), flop.get(nm, 0) / fp32_peak) * 1e3 for nm in names}
+    t_roof = {nm: min(t_roof[nm], stages[nm]["ms"]) for nm in names}
     measured = sum(stages[nm]["ms"] for nm in names)
-    step_roof = {"t_roof_ms_per_view": sum(t_roof.values()), "t_measured_ms_per_view": measured, "frac": sum(t_roof.values()) / measured,
-                 "per_stage_frac": {nm: t_roof[nm] / stages[nm]["ms"] for nm in names}, "fragment_pixel_evaluations": F,
-                 "fp32_peak_tflops": fp32_peak / 1e12, "sm_mhz": sm_mhz,
-                 "note": "stages of the whole-view form timed back to back on one stream; the optimizer update (once per step) is not included"}
-    stages["step_roofline"] = step_roof
-    if chunked_ms is not None:
-        ctx.n_chunks = chunks
-        stages["render_chunked"] = {"ms": chunked_ms, "chunks": chunks, "replaces": "project + bin_sort + raster_fwd",
-                                    "whole_view_ms": stages["project"]["ms"] + stages["bin_sort"]["ms"] + stages["raster_fwd"]["ms"]}
-        step_roof["chunked"] = {"t_measured_ms_per_view": chunked_ms + stages["loss"]["ms"] + stages["raster_bwd"]["ms"] + stages["proj_bwd"]["ms"],
-                                "frac": sum(t_roof.values()) / (chunked_ms + stages["loss"]["ms"] + stages["raster_bwd"]["ms"] + stages["proj_bwd"]["ms"]),
-                                "note": "t_roof charges the whole-view algorithm (every intersection sorted); the chunked renderer sorts a fraction, "
-                                        "so this ratio can exceed 1"}
-    if top in ("raster_bwd_kernel", "raster_fwd_kernel"):
-        flop = (90 if top == "raster_bwd_kernel" else 24) * F
-        extra["fp32"] = {"flop_per_launch": flop, "achieved_tflops": flop / (per_launch_ms * 1e-3) / 1e12, "peak_tflops": fp32_peak / 1e12,
-                         "frac": flop / (per_launch_ms * 1e-3) / fp32_peak, "fragment_pixel_evaluations": F}
+    stages["step_roofline"] = {"t_roof_ms_per_view": sum(t_roof.values()), "t_measured_ms_per_view": measured, "frac": sum(t_roof.values()) / measured,
+                               "per_stage_frac": {nm: t_roof[nm] / stages[nm]["ms"] for nm in names}, "fragment_pixel_evaluations": F,
+                               "fp32_peak_tflops": fp32_peak / 1e12, "sm_mhz": sm_mhz, "touched_splats": touched,
+                               "note": "stages of the timed form (" + ("chunked" if chunks > 1 else "whole-view") + " rendering) back to back on one stream; the "
+                                       "optimizer update (once per step) is not included"}
+    # The roofline object: the single-kernel stage with the largest time per view (the chunked renderer is ~70 launches, not one kernel).
+    kernel_of = {"project": "project_kernel", "raster_fwd": "raster_fwd_kernel", "loss": "photometric_kernel", "raster_bwd": "raster_bwd_kernel", "proj_bwd": "proj_bwd_kernel"}
+    kernel_ms = {kernel_of[nm]: stages[nm]["ms"] for nm in names if nm in kernel_of}
+    if chunks <= 1:
+        kernel_ms["radix_scatter_kernel"] = float(np.mean(stages["bin_sort"]["phases_ms"]["tile_scatter"]))
+    top = max(kernel_ms, key=kernel_ms.get)
+    per_launch_ms = kernel_ms[top]
+    if top == "radix_scatter_kernel":
+        stage, bytes_launch, traffic = "bin_sort", 16 * I, int(16.7 * I)   # dram read + write per launch: ncu capture at half the splat count, scaled by pairs
+        note = f"{passes} launches per view on I = {I} pairs; 16 B per pair per launch"
+    else:
+        stage = [k for k, v in kernel_of.items() if v == top][0]
+        bytes_launch, traffic, note = alg[stage], None, "one launch per view"
+        if top == "raster_bwd_kernel":
+            traffic = int(72.5 * Ib)   # dram read + write per launch from an ncu capture at half the splat count (90.1 MB at I_b = 1,243,915), scaled by fragments
     a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
-    hbm_view = {"achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src,
-                "algorithmic_bytes_per_launch": int(bytes_launch)}
-    if "fp32" in extra:   # the two compositing kernels are bound by FP32 issue: that roof is the headline, the HBM figure rides beside it
-        f = extra["fp32"]
-        roof = {"bound": "fp32", "kernel": top, "achieved": f["achieved_tflops"], "peak": f["peak_tflops"], "unit": "TFLOP/s", "frac": f["frac"],
-                "traffic": traffic, "peak_source": "2 x 128 lanes x SMs x the SM clock sampled in the timed region (no tensor pipe on this path)",
-                "flop_per_launch": f["flop_per_launch"], "fragment_pixel_evaluations": f["fragment_pixel_evaluations"], "hbm": hbm_view}
+    hbm_view = {"achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_launch": int(bytes_launch)}
+    if stage in flop:   # the compositing kernels are bound by FP32 issue: that roof is the headline, the HBM figure rides beside it
+        f = flop[stage] / (per_launch_ms * 1e-3)
+        roof = {"bound": "fp32", "kernel": top, "achieved": f / 1e12, "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": f / fp32_peak, "traffic": traffic,
+                "peak_source": "2 x 128 lanes x SMs x the SM clock sampled in the timed region (no tensor pipe on this path)",
+                "flop_per_launch": flop[stage], "fragment_pixel_evaluations": F, "hbm": hbm_view}
     else:
         roof = {"bound": "hbm", "kernel": top, **hbm_view}
     roof.update({"ms_per_launch": per_launch_ms, "note": note, "kernel_ms_per_view": {k: float(v) for k, v in kernel_ms.items()}})

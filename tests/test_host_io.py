@@ -1,0 +1,104 @@
+"""Files of the headless front end (b2ctrain_b200/host/ply.cpp, render_io.cpp): splat PLY in the layout the reference
+reads and writes (src/ply.cpp:80-226), cameras.json (src/render/renderer.cpp:185-197, 207-212), and the per-camera render
+loop to raw buffers."""
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+
+from b2ctrain_b200 import host_trainer as ht
+from b2ctrain_b200 import scenes
+
+
+def cloud(n=257, degree=2, seed=3):
+    s = scenes.make_splats(n, degree, seed)
+    return ht.cloud_from_scene(s), s
+
+
+def test_ply_round_trip_binary(tmp_path):
+    c, _ = cloud()
+    rng = np.random.Generator(np.random.PCG64(1))
+    c["evidence"] = rng.random((c["n"], 7)).astype(np.float32)
+    c["labels"] = np.stack([rng.integers(0, 5, c["n"]).astype(np.float32), rng.random(c["n"]).astype(np.float32)], 1)
+    path = str(tmp_path / "a.ply")
+    ht.write_ply(path, c, comment="SH degree: 2")
+    back = ht.read_ply(path)
+    assert back["n"] == c["n"] and back["degree"] == 2 and back["has_scales"]
+    for k in ("pos", "log_scale", "opacity", "sh", "evidence", "labels"):
+        assert np.array_equal(back[k], np.asarray(c[k], np.float32)), k
+    q = c["quat"] / np.linalg.norm(c["quat"], axis=1, keepdims=True)          # the writer normalises rotations
+    assert np.allclose(back["quat"], q, atol=1e-6)
+    head = open(path, "rb").read(400).decode("latin1")
+    assert head.startswith("ply\nformat binary_little_endian 1.0\ncomment SH degree: 2\nelement vertex 257\nproperty float x\n")
+    # f_rest is channel-major in the file: column 14 is coefficient 1 of the red channel, column 14 + (K - 1) of green
+    body = open(path, "rb").read().split(b"end_header\n", 1)[1]
+    row0 = np.frombuffer(body[: 4 * (14 + 24 + 9)], np.float32)
+    assert row0[14] == c["sh"][0, 1, 0] and row0[14 + 8] == c["sh"][0, 1, 1] and row0[11] == c["sh"][0, 0, 0]
+
+
+def test_ply_ascii_mixed_types_and_rgb_fallback(tmp_path):
+    path = str(tmp_path / "pts.ply")
+    with open(path, "w") as f:
+        f.write("ply\nformat ascii 1.0\ncomment made by a test\nelement vertex 2\nproperty double x\nproperty float y\nproperty float z\n"
+                "property uchar red\nproperty uchar green\nproperty uchar blue\nend_header\n0.5 1 -2 255 0 128\n1e-1 2 3 0 255 64\n")
+    c = ht.read_ply(path)
+    assert c["n"] == 2 and c["degree"] == 0 and not c["has_scales"]
+    assert np.allclose(c["pos"], [[0.5, 1, -2], [0.1, 2, 3]])
+    C0 = 0.28209479177387814
+    assert np.allclose(c["sh"][:, 0, :], (np.array([[255, 0, 128], [0, 255, 64]]) / 255.0 - 0.5) / C0, atol=1e-6)
+    assert np.array_equal(c["quat"], [[1, 0, 0, 0], [1, 0, 0, 0]])            # identity where the file has none
+
+
+def test_ply_errors(tmp_path):
+    bad = str(tmp_path / "bad.ply")
+    open(bad, "w").write("ply\nformat binary_little_endian 1.0\nelement vertex 3\nproperty float x\nproperty float y\nproperty float z\nend_header\n")
+    with pytest.raises(RuntimeError, match="truncated"):
+        ht.read_ply(bad)
+    open(bad, "w").write("ply\nformat binary_big_endian 1.0\nelement vertex 0\nproperty float x\nend_header\n")
+    with pytest.raises(RuntimeError, match="big-endian"):
+        ht.read_ply(bad)
+    open(bad, "w").write("ply\nformat ascii 1.0\nelement vertex 1\nproperty float x\nproperty float y\nproperty float z\nproperty float f_rest_0\nend_header\n0 0 0 0\n")
+    with pytest.raises(RuntimeError, match="not a valid SH layout"):
+        ht.read_ply(bad)
+    with pytest.raises(RuntimeError, match="failed to open"):
+        ht.read_ply(str(tmp_path / "missing.ply"))
+
+
+def gl_camera_entry(name, cam):
+    """A cameras.json entry (OpenGL camera-to-world rotation, position) of a camera dict of b2ctrain_b200.scenes."""
+    R = np.asarray(cam["R"], np.float64).reshape(3, 3)
+    c2w = R.T * np.array([1.0, -1.0, -1.0])[None, :]
+    return dict(name=name, fx=float(cam["fx"]), fy=float(cam["fy"]), cx=float(cam["cx"]), cy=float(cam["cy"]), position=[float(x) for x in cam["pos"]],
+                rotation=c2w.tolist())
+
+
+@pytest.mark.gpu
+def test_headless_render_writes_what_the_operators_render(tmp_path):
+    """PLY + cameras.json in, raw RGBA8 / depth buffers out: the same bytes as quantising the image render_forward leaves
+    for the same splats and cameras (cameras split over two 'ranks' to cover the round-robin share)."""
+    import torch
+    from b2ctrain_b200 import api
+    c, scene = cloud(n=4000, degree=2, seed=8)
+    W, H = 96, 64
+    cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, a, 15.0), W, H, 80.0) for a in (0.0, 70.0, 200.0)]
+    ply, cj = str(tmp_path / "s.ply"), str(tmp_path / "cameras.json")
+    ht.write_ply(ply, c)
+    json.dump(dict(width=W, height=H, cameras=[gl_camera_entry(f"view{i}.png", cam) for i, cam in enumerate(cams)]), open(cj, "w"))
+    assert ht.render_headless(ply, cj, str(tmp_path), background=(0.1, 0.2, 0.3), depth=True, rank=0, world=2) == 2
+    assert ht.render_headless(ply, cj, str(tmp_path), background=(0.1, 0.2, 0.3), depth=True, rank=1, world=2) == 1
+    flat = dict(scene); flat["lscale"] = scene["lscale"].copy(); flat["lscale"][:, 3] = 0                      # the file format has no floor lane
+    flat["quat"] = (scene["quat"] / np.linalg.norm(scene["quat"], axis=1, keepdims=True)).astype(np.float32)   # as written
+    m = api.Model("cuda:0").upload(flat)
+    ctx = api.RenderCtx("cuda:0"); ctx.want_depth = True
+    ctx.setup(W, H, m.cap)
+    for i, cam in enumerate(cams):
+        api.render_forward(ctx, m, api.RenderParams(cam, bg=(0.1, 0.2, 0.3), sh_degree=2, bwd_info=False))
+        want = np.rint(np.clip(ctx.out_rgba.cpu().numpy(), 0, 1) * 255).astype(np.uint8)
+        got = np.fromfile(str(tmp_path / f"view{i}.rgba8"), np.uint8).reshape(-1, 4)
+        assert np.mean(got != want) < 1e-4 and np.max(np.abs(got.astype(int) - want.astype(int))) <= 1   # a rounding tie may fall either way
+        depth = np.fromfile(str(tmp_path / f"view{i}.depth.f32"), np.float32)
+        ref = ctx.out_depth.cpu().numpy()
+        fin = np.isfinite(ref)
+        assert np.array_equal(np.isfinite(depth), fin) and np.allclose(depth[fin], ref[fin], rtol=1e-5)
