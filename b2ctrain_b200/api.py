@@ -95,6 +95,22 @@ SIGNATURES = {
     "b2k_proj_bwd": (C.c_int, [_P, _P, _P, _P, _P, _S]),
     "b2k_adam": (C.c_int, [_P, _P, _P, _S]),
     "b2k_adam_range": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, _S]),
+    "b2k_sort_pairs_tmp_bytes": (C.c_uint64, []),
+    "b2k_sort_pairs_u32": (C.c_int, [_P, _P, _P, _P, C.c_uint32, _P, C.c_uint64, _S]),
+    "b2k_refine_flags": (C.c_int, [_P, _P, C.c_float, C.c_float, _P, _P, _P, _S]),
+    "b2k_refine_sample_keys": (C.c_int, [_P, _P, _P, C.c_int32, C.c_float, C.c_uint32, _P, _P, _P, _S]),
+    "b2k_refine_oversized": (C.c_int, [_P, _P, _P, C.c_float, _P, _S]),
+    "b2k_refine_mark": (C.c_int, [_P, C.c_int32, _P, _S]),
+    "b2k_refine_split": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_int32, C.c_float, _P, _S]),
+    "b2k_refine_kill": (C.c_int, [_P, _P, C.c_int32, _S]),
+    "b2k_refine_opacity_decay": (C.c_int, [_P, C.c_float, _S]),
+    "b2k_refine_bake_floor": (C.c_int, [_P, _S]),
+    "b2k_refine_axis_keys": (C.c_int, [_P, C.c_int32, _P, _P, _S]),
+    "b2k_key_to_float": (C.c_float, [C.c_uint32]),
+    "b2k_evidence_view": (C.c_int, [_P, _P, _P, _P, C.c_int32, C.c_float, _P, _S]),
+    "b2k_evidence_fold": (C.c_int, [_P, _P, _P, _P, _S]),
+    "b2k_label_vote": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P, _S]),
+    "b2k_label_bins": (C.c_int32, []),
     "b2k_dp_unique_id": (C.c_int, [_P]),
     "b2k_dp_init": (C.c_int, [_P, _P, C.c_int32, C.c_int32]),
     "b2k_dp_destroy": (C.c_int, [_P]),
@@ -102,6 +118,8 @@ SIGNATURES = {
     "b2k_dp_allreduce_stat": (C.c_int, [_P, _P, C.c_uint64, C.c_int32, _S]),
     "b2k_dp_barrier": (C.c_int, [_P, _S]),
     "b2k_dp_share": (C.c_int, [_P, _P, _P, _S]),
+    "b2k_dp_release_shares": (C.c_int, [_P, _S]),
+    "b2k_dp_gather_slices": (C.c_int, [_P, _P, C.c_uint64, C.c_int32, C.c_uint64, C.c_int32, _S]),
     "b2k_dp_slice": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "b2k_dp_adam_shard": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_min_scale": (C.c_int, [_P, _P, _P, C.c_int32, _S]),

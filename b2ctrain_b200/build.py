@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb2k.so")
-SOURCES = ["project.cu", "binning.cu", "raster_fwd.cu", "loss.cu", "raster_bwd.cu", "optim.cu", "dp.cu"]
+SOURCES = ["project.cu", "binning.cu", "raster_fwd.cu", "loss.cu", "raster_bwd.cu", "optim.cu", "dp.cu", "evidence.cu", "refine.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "--extended-lambda"]
 

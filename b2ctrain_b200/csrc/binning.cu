@@ -924,6 +924,22 @@ extern "C" int b2k_bin_sort_profile(const B2kCtx* c, int32_t n, b2k_stream_t str
   return st;
 }
 
+// The radix sort above for callers outside the binning (the refinement pass): stable, ascending, 32-bit keys, four
+// passes, so the result returns to the pair it started from.
+extern "C" uint64_t b2k_sort_pairs_tmp_bytes(void) { return (uint64_t)sizeof(uint32_t) * ((uint64_t)RADIX * 1024 + RADIX + 1024 + 16); }
+
+extern "C" int b2k_sort_pairs_u32(uint32_t* keys, uint32_t* vals, uint32_t* keys_alt, uint32_t* vals_alt, uint32_t n, void* tmp, uint64_t tmp_bytes, b2k_stream_t stream) {
+  B2K_REQUIRE(n == 0 || (keys && vals && keys_alt && vals_alt && tmp));
+  if (n == 0) return B2K_OK;
+  if (tmp_bytes < b2k_sort_pairs_tmp_bytes() || n > 0xFFFFFFF0u) return B2K_ERR_CAPACITY;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = sort_blocks();
+  SortScratch sc;
+  sc.hist = (uint32_t*)tmp; sc.totals = sc.hist + (size_t)RADIX * blocks; sc.block_sums = sc.totals + RADIX; sc.n_word = sc.block_sums + 1024;
+  set_word_kernel<<<1, 1, 0, s>>>(sc.n_word, n);
+  return radix_sort(keys, vals, keys_alt, vals_alt, sc.n_word, n, 32, sc, blocks, s);
+}
+
 extern "C" int b2k_read_num_isect(const B2kCtx* c, b2k_stream_t stream, uint32_t* total) {
   B2K_REQUIRE(c && c->num_isect && total);
   cudaStream_t s = (cudaStream_t)stream;

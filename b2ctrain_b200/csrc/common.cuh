@@ -45,7 +45,7 @@ inline uint32_t* sort_tables_ptr(const B2kCtx* c) { return (uint32_t*)c->sort_tm
 // n_tiles + tile) lives in slot (range_start >> SEG_SHIFT) + q + seg: ranges follow each other in the sorted buffer in
 // the order of q, which makes the map injective without any table.
 #ifndef B2K_SEG_SHIFT
-#define B2K_SEG_SHIFT 8
+#define B2K_SEG_SHIFT 7
 #endif
 constexpr int SEG_SHIFT = B2K_SEG_SHIFT, SEG_LEN = 1 << SEG_SHIFT;
 constexpr size_t BWD_HEADER_WORDS = 16;

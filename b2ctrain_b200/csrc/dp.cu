@@ -19,6 +19,9 @@ struct Nccl {
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
   bool ok = false;
 };
 
@@ -35,7 +38,10 @@ Nccl& nccl() {
   n.CommDestroy = (decltype(n.CommDestroy))dlsym(n.lib, "ncclCommDestroy");
   n.AllReduce = (decltype(n.AllReduce))dlsym(n.lib, "ncclAllReduce");
   n.AllGather = (decltype(n.AllGather))dlsym(n.lib, "ncclAllGather");
-  n.ok = n.GetUniqueId && n.CommInitRank && n.CommDestroy && n.AllReduce && n.AllGather;
+  n.Broadcast = (decltype(n.Broadcast))dlsym(n.lib, "ncclBroadcast");
+  n.GroupStart = (decltype(n.GroupStart))dlsym(n.lib, "ncclGroupStart");
+  n.GroupEnd = (decltype(n.GroupEnd))dlsym(n.lib, "ncclGroupEnd");
+  n.ok = n.GetUniqueId && n.CommInitRank && n.CommDestroy && n.AllReduce && n.AllGather && n.Broadcast && n.GroupStart && n.GroupEnd;
   return n;
 }
 
@@ -136,6 +142,33 @@ extern "C" int b2k_dp_share(B2kDp* dp, void* base, void** peers, b2k_stream_t st
     dp->opened[dp->n_opened++] = p;
     peers[r] = p;
   }
+  return B2K_OK;
+}
+
+extern "C" int b2k_dp_release_shares(B2kDp* dp, b2k_stream_t stream) {
+  B2K_REQUIRE(dp);
+  B2K_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  for (int i = 0; i < dp->n_opened; i++) cudaIpcCloseMemHandle(dp->opened[i]);
+  dp->n_opened = 0;
+  return B2K_OK;
+}
+
+extern "C" int b2k_dp_gather_slices(B2kDp* dp, void* base, uint64_t elem_bytes, int32_t lanes, uint64_t lane_stride, int32_t n, b2k_stream_t stream) {
+  B2K_REQUIRE(dp && dp->comm && base && elem_bytes > 0 && lanes >= 0 && n >= 0 && lane_stride >= (uint64_t)n);
+  if (dp->world == 1 || n == 0 || lanes == 0) return B2K_OK;
+  Nccl& nc = nccl();
+  B2K_NCCL(nc.GroupStart());
+  for (int r = 0; r < dp->world; r++) {
+    int32_t first = 0, count = 0;
+    b2k_dp_slice(n, r, dp->world, &first, &count);
+    if (count == 0) continue;
+    for (int l = 0; l < lanes; l++) {
+      char* p = (char*)base + ((uint64_t)l * lane_stride + (uint64_t)first) * elem_bytes;
+      const int st = nccl_status(nc.Broadcast(p, p, (size_t)count * elem_bytes, ncclChar, r, (ncclComm_t)dp->comm, (cudaStream_t)stream));
+      if (st) { nc.GroupEnd(); return st; }
+    }
+  }
+  B2K_NCCL(nc.GroupEnd());
   return B2K_OK;
 }
 

@@ -2,7 +2,7 @@
 // tile and accumulated per splat. Reference semantics: raster_bwd_kernel (src/gpu/raster_bwd.cu:11-143).
 //
 // Work decomposition (differs from the reference on purpose):
-//   * A tile's fragment list is cut into SEGMENTS of 256 fragments. The forward leaves the per-pixel state (colour
+//   * A tile's fragment list is cut into SEGMENTS of 128 fragments. The forward leaves the per-pixel state (colour
 //     sums, transmittance) at every segment boundary (and where a depth chunk of a chunked view hands over to the next),
 //     so each segment can be replayed on its own: the colour behind a boundary is the final sum minus the checkpoint.
 //     A small kernel lists the (range, segment) items; a persistent grid of independent warps pulls them from a
@@ -23,8 +23,11 @@
 namespace b2k {
 namespace {
 
+#ifndef B2K_BWD_REDUCE
+#define B2K_BWD_REDUCE 0     // 0: FADD column sums (shipped); 1: mma.sync tf32 column sums (the measured alternative)
+#endif
 #ifndef B2K_BWD_WARPS
-#define B2K_BWD_WARPS 2
+#define B2K_BWD_WARPS 4
 #endif
 constexpr int BWD_WARPS = B2K_BWD_WARPS;     // warps per CTA (independent: the CTA shape only sets the residency granularity)
 constexpr int BWD_BATCH = 32;                // fragments staged per warp and batch
@@ -144,6 +147,51 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     // Column sums of the pending fragments' partials, then one global reduction per non-zero lane of each splat.
     auto flush = [&]() {
       __syncwarp();
+#if B2K_BWD_REDUCE == 1
+      // Tensor-core variant of the column sums (measured against the FADD form, see profiles/): per pending fragment the
+      // [32 lanes][12 values] block is the B operand of mma.sync.m16n8k8 (tf32 inputs, fp32 accumulate) against a matrix of
+      // ones, four k-steps of eight lanes by two n-tiles of eight values; each value is split into a tf32 head and a tf32
+      // tail so that the sum keeps fp32 accuracy (two MMAs per tile). Every row of D holds the totals; lanes 0..3 read row 0.
+      for (int f = 0; f < n_pending; f++) {
+        const float* blk = reinterpret_cast<const float*>(red + f * RED_BLOCK);
+        float tot[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+          const int col = nt * 8 + (lane >> 2);
+#pragma unroll
+          for (int ks = 0; ks < 4; ks++) {
+            const int slot = ks * 8 + (lane & 3);
+            const float x0 = col < 12 ? blk[slot * 12 + col] : 0.f, x1 = col < 12 ? blk[(slot + 4) * 12 + col] : 0.f;
+            uint32_t h0, h1, l0, l1;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h0) : "f"(x0)); asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h1) : "f"(x1));
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l0) : "f"(x0 - __uint_as_float(h0))); asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l1) : "f"(x1 - __uint_as_float(h1)));
+            const uint32_t one = 0x3f800000u;
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%5,%6}, {%0,%1,%2,%3};"
+                         : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3) : "r"(one), "r"(h0), "r"(h1));
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%5,%6}, {%0,%1,%2,%3};"
+                         : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3) : "r"(one), "r"(l0), "r"(l1));
+          }
+          tot[nt][0] = d0; tot[nt][1] = d1;   // lanes 0..3: row 0, columns nt * 8 + 2 * lane + {0, 1}
+        }
+        if (lane < 4) {
+          const uint32_t gid = pending_gid[f];
+          float* o = v_splat + (size_t)gid * GRAD_LANES;
+#pragma unroll
+          for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int k = nt * 8 + lane * 2 + e;
+              const float v = tot[nt][e] * (k == 10 ? 1.f : out_scale);
+              if (k < 10) { if (v != 0.f) atomicAdd(o + k, v); }
+              else if (k == 10) { vis_flag[gid] = 1u; if (vis_weight) atomicAdd(vis_weight + gid, v); }
+            }
+        }
+      }
+      __syncwarp();
+      n_pending = 0;
+      return;
+#endif
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       const bool mine = red_idx < 3 * RED_F && red_f < n_pending;
       if (mine) {

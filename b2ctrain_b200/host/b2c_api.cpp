@@ -3,6 +3,7 @@
 #include "b2c_api.h"
 #include <type_traits>
 #include "../../include/b2k.h"
+#include <algorithm>
 #include <cstring>
 
 namespace b2c {
@@ -96,6 +97,32 @@ CameraGPU CameraGPU::from(const Camera& c, int W, int H) {
   g.lim_pos_x = (1.15f * W - g.cx) / g.fx; g.lim_pos_y = (1.15f * H - g.cy) / g.fy;
   g.lim_neg_x = (-0.15f * W - g.cx) / g.fx; g.lim_neg_y = (-0.15f * H - g.cy) / g.fy;
   return g;
+}
+
+void Model::reserve(int want, cudaStream_t stream) {
+  if (want <= cap) return;
+  int ncap = cap > 0 ? cap : 1024;
+  while (ncap < want) ncap *= 2;
+  const int hi = (K() - 1) * 3;
+  // New buffers first, copies enqueued, one wait, then the old ones go.
+  auto grown = [&](auto& b, int lanes) {
+    using T = std::remove_reference_t<decltype(*b.ptr)>;
+    DevBuf<T> nb;
+    nb.reserve((size_t)ncap * (size_t)std::max(lanes, 1)); nb.zero(stream);
+    if (b.ptr && n > 0 && lanes > 0)
+      B2C_CUDA_CHECK(cudaMemcpy2DAsync(nb.ptr, (size_t)ncap * sizeof(T), b.ptr, (size_t)cap * sizeof(T), (size_t)n * sizeof(T), (size_t)lanes, cudaMemcpyDeviceToDevice, stream));
+    return nb;
+  };
+  auto p0 = grown(pos_op, 1), p1 = grown(quat, 1), p2 = grown(lscale, 1), m0 = grown(m_pos_op, 1), m1 = grown(v_pos_op, 1), m2 = grown(m_quat, 1), m3 = grown(v_quat, 1),
+       m4 = grown(m_lscale, 1), m5 = grown(v_lscale, 1);
+  auto s0 = grown(sh_dc, 3), s1 = grown(sh_hi32, hi), s2 = grown(m_sh_dc, 3), s3 = grown(m_sh_hi32, hi), s4 = grown(v_sh, 1), t0 = grown(refine_norm, 1),
+       t1 = grown(max_screen, 1), t2 = grown(vis_count, 1), t3 = grown(vis_weight, 1);
+  auto l0 = grown(last_step, 1);
+  B2C_CUDA_CHECK(cudaStreamSynchronize(stream));
+  pos_op = std::move(p0); quat = std::move(p1); lscale = std::move(p2); m_pos_op = std::move(m0); v_pos_op = std::move(m1); m_quat = std::move(m2); v_quat = std::move(m3);
+  m_lscale = std::move(m4); v_lscale = std::move(m5); sh_dc = std::move(s0); sh_hi32 = std::move(s1); m_sh_dc = std::move(s2); m_sh_hi32 = std::move(s3); v_sh = std::move(s4);
+  refine_norm = std::move(t0); max_screen = std::move(t1); vis_count = std::move(t2); vis_weight = std::move(t3); last_step = std::move(l0);
+  cap = ncap;
 }
 
 void Model::upload(const SplatCloud& c, cudaStream_t stream) {

@@ -137,6 +137,9 @@ struct Model {
   DevBuf<uint32_t> last_step;
   int adam_t = 0;
   int K() const { return (degree + 1) * (degree + 1); }
+  // Capacity for at least `want` splats, contents kept (capacity doubles, src/model.cu:10-11; the planar SH lanes are
+  // re-laid out for the new stride).
+  void reserve(int want, cudaStream_t stream = 0);
   void upload(const SplatCloud& c, cudaStream_t stream = 0);
   SplatCloud download(cudaStream_t stream = 0) const;
   void zero_optimizer(cudaStream_t stream = 0);

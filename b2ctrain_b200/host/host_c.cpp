@@ -4,6 +4,7 @@
 #include "host_c.h"
 #include <cstring>
 #include <string>
+#include "refine.h"
 #include "render_io.h"
 #include "trainer.h"
 
@@ -133,5 +134,57 @@ extern "C" int b2ch_ply_write(const char* path, int32_t n, int32_t degree, const
     std::vector<std::string> comments;
     if (comment && *comment) comments.push_back(comment);
     write_ply(path, c, comments);
+  });
+}
+
+// ---- refinement: one RefineState::run on a model built from host arrays (the pass as a library call; tests drive it) ----
+extern "C" int b2ch_refine_once(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, const float* stats,
+                                const float* cam_pos, const float* cam_focal, int32_t n_cams, const float* fp, const uint32_t* up, int32_t W, int32_t H,
+                                int32_t* out, int32_t capacity, float* o_pos_op, float* o_quat, float* o_lscale, float* o_sh, uint32_t* o_pairs) {
+  return guarded([&] {
+    SplatCloud c; c.resize((size_t)n, degree); c.floor.assign((size_t)n, 0.f);
+    const int K = c.K();
+    for (int i = 0; i < n; i++) {
+      for (int k = 0; k < 3; k++) { c.pos[i * 3 + k] = pos_op[i * 4 + k]; c.log_scale[i * 3 + k] = lscale[i * 4 + k]; }
+      c.opacity[i] = pos_op[i * 4 + 3]; c.floor[i] = lscale[i * 4 + 3];
+      for (int k = 0; k < 4; k++) c.quat[i * 4 + k] = quat[i * 4 + k];
+    }
+    std::memcpy(c.sh.data(), sh, (size_t)n * K * 3 * sizeof(float));
+    Model m; m.upload(c, 0);
+    RenderCtx ctx; ctx.setup(W, H, m.cap, 0);
+    float* dst[4] = {m.refine_norm.ptr, m.max_screen.ptr, m.vis_count.ptr, m.vis_weight.ptr};
+    for (int k = 0; k < 4; k++) B2C_CUDA_CHECK(cudaMemcpy(dst[k], stats + (size_t)k * n, (size_t)n * sizeof(float), cudaMemcpyHostToDevice));
+    RefineState st;
+    st.init(m, 0);
+    st.set_cameras(std::vector<float>(cam_pos, cam_pos + 3 * n_cams), std::vector<float>(cam_focal, cam_focal + n_cams));
+    RefineParams p;
+    p.growth_grad_threshold = fp[0]; p.growth_select_fraction = fp[1]; p.split_at_screen_size = fp[2]; p.opac_decay = fp[3]; p.cull_weight = fp[4];
+    p.iter = up[0]; p.total = up[1]; p.growth_allowed = up[2] != 0; p.max_splats = up[3]; p.seed = up[4]; p.no_new = up[5] != 0;
+    const RefineStats r = st.run(m, ctx, p, 0);
+    out[0] = m.n; out[1] = r.pruned; out[2] = r.relocated; out[3] = r.grown; out[4] = r.split_oversized; out[5] = r.culled; out[6] = (int32_t)st.last_pairs;
+    if (m.n > capacity) throw std::runtime_error("b2ch_refine_once: output arrays too small");
+    const SplatCloud d = m.download(0);
+    for (size_t i = 0; i < d.n; i++) {
+      for (int k = 0; k < 3; k++) { o_pos_op[i * 4 + k] = d.pos[i * 3 + k]; o_lscale[i * 4 + k] = d.log_scale[i * 3 + k]; }
+      o_pos_op[i * 4 + 3] = d.opacity[i]; o_lscale[i * 4 + 3] = d.floor[i];
+      for (int k = 0; k < 4; k++) o_quat[i * 4 + k] = d.quat[i * 4 + k];
+    }
+    std::memcpy(o_sh, d.sh.data(), d.sh.size() * sizeof(float));
+    if (o_pairs && st.last_pairs) {
+      B2C_CUDA_CHECK(cudaMemcpy(o_pairs, st.sel_parent.ptr, st.last_pairs * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+      B2C_CUDA_CHECK(cudaMemcpy(o_pairs + st.last_pairs, st.sel_child.ptr, st.last_pairs * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    }
+  });
+}
+
+extern "C" int b2ch_trainer_refine(void* h, const float* cam_pos, const float* cam_focal, int32_t n_cams, const float* fp, const uint32_t* up, void* stream, int32_t* out) {
+  return guarded([&] {
+    StepTrainer& tr = *(StepTrainer*)h;
+    if (n_cams > 0) tr.refiner.set_cameras(std::vector<float>(cam_pos, cam_pos + 3 * n_cams), std::vector<float>(cam_focal, cam_focal + n_cams));
+    RefineParams p;
+    p.growth_grad_threshold = fp[0]; p.growth_select_fraction = fp[1]; p.split_at_screen_size = fp[2]; p.opac_decay = fp[3]; p.cull_weight = fp[4];
+    p.iter = up[0]; p.total = up[1]; p.growth_allowed = up[2] != 0; p.max_splats = up[3]; p.seed = up[4]; p.no_new = up[5] != 0;
+    const RefineStats r = tr.refine(p, (cudaStream_t)stream);
+    out[0] = tr.model.n; out[1] = r.pruned; out[2] = r.relocated; out[3] = r.grown; out[4] = r.split_oversized; out[5] = r.culled;
   });
 }

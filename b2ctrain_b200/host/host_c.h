@@ -58,6 +58,20 @@ int b2ch_ply_read(const char* path, int32_t* n, int32_t* degree, float* pos, flo
 int b2ch_ply_write(const char* path, int32_t n, int32_t degree, const float* pos, const float* log_scale, const float* quat, const float* opacity,
                    const float* sh, const float* evidence, const float* labels, const char* comment);
 
+/* ---- refinement ---- */
+/* StepTrainer::refine: the refinement pass on the trainer's model between steps, collective over the ranks (statistics
+ * reduced, optimizer state made whole, buffers shared again). Parameters as b2ch_refine_once; out[6]: new n, pruned,
+ * relocated, grown, split_oversized, culled. */
+int b2ch_trainer_refine(void* trainer, const float* cam_pos, const float* cam_focal, int32_t n_cams, const float* fp, const uint32_t* up, void* stream, int32_t* out);
+/* One RefineState::run (src/gpu/refine.cu:244-342) on a model built from the host arrays, with the statistics [4][n]
+ * (refine_norm, max_screen, vis_count, vis_weight) and the cameras of the floor. fp: growth_grad_threshold,
+ * growth_select_fraction, split_at_screen_size, opac_decay, cull_weight; up: iter, total, growth_allowed, max_splats, seed,
+ * no_new. out[7]: new n, pruned, relocated, grown, split_oversized, culled, pairs. The refined splats land in the o_* arrays
+ * (room for `capacity` splats); o_pairs (or NULL) receives [2][pairs]: the parents, then the slots of their children. */
+int b2ch_refine_once(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, const float* stats,
+                     const float* cam_pos, const float* cam_focal, int32_t n_cams, const float* fp, const uint32_t* up, int32_t W, int32_t H, int32_t* out,
+                     int32_t capacity, float* o_pos_op, float* o_quat, float* o_lscale, float* o_sh, uint32_t* o_pairs);
+
 #ifdef __cplusplus
 }
 #endif

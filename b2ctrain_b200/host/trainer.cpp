@@ -52,15 +52,47 @@ StepTrainer::StepTrainer(const SplatCloud& cloud, int W_, int H_, const StepConf
   if (world > 1) {
     if (!dp_id) throw std::runtime_error("StepTrainer: several ranks need the rendezvous id of rank 0");
     check(b2k_dp_init(&dp_, dp_id, rank, world), "b2k_dp_init");
-    if (cfg.shard_update) {
-      check(b2k_dp_share(dp_, grad.ptr, (void**)peers_.grad, 0), "b2k_dp_share(grad)");
-      check(b2k_dp_share(dp_, model.pos_op.ptr, (void**)peers_.pos_op, 0), "b2k_dp_share(pos_op)");
-      check(b2k_dp_share(dp_, model.quat.ptr, (void**)peers_.quat, 0), "b2k_dp_share(quat)");
-      check(b2k_dp_share(dp_, model.lscale.ptr, (void**)peers_.lscale, 0), "b2k_dp_share(lscale)");
-      check(b2k_dp_share(dp_, model.sh_dc.ptr, (void**)peers_.sh_dc, 0), "b2k_dp_share(sh_dc)");
-      check(b2k_dp_share(dp_, model.sh_hi32.ptr, (void**)peers_.sh_hi, 0), "b2k_dp_share(sh_hi)");
-    }
+    if (cfg.shard_update) share_buffers();
   }
+  refiner.init(model, 0);
+}
+
+void StepTrainer::share_buffers() {
+  check(b2k_dp_share(dp_, grad.ptr, (void**)peers_.grad, 0), "b2k_dp_share(grad)");
+  check(b2k_dp_share(dp_, model.pos_op.ptr, (void**)peers_.pos_op, 0), "b2k_dp_share(pos_op)");
+  check(b2k_dp_share(dp_, model.quat.ptr, (void**)peers_.quat, 0), "b2k_dp_share(quat)");
+  check(b2k_dp_share(dp_, model.lscale.ptr, (void**)peers_.lscale, 0), "b2k_dp_share(lscale)");
+  check(b2k_dp_share(dp_, model.sh_dc.ptr, (void**)peers_.sh_dc, 0), "b2k_dp_share(sh_dc)");
+  check(b2k_dp_share(dp_, model.sh_hi32.ptr, (void**)peers_.sh_hi, 0), "b2k_dp_share(sh_hi)");
+}
+
+RefineStats StepTrainer::refine(const RefineParams& p, cudaStream_t stream) {
+  const bool sharded = world > 1 && cfg.shard_update;
+  if (grad_clear_pending_) { cuda(cudaStreamWaitEvent(stream, cleared_evt_, 0), "wait"); grad_clear_pending_ = false; }
+  if (sharded) {   // moments, the Adam-mini second moment and the lazy-update stamp: whole on every rank again
+    const int n = model.n, hi = (model.K() - 1) * 3;
+    for (DevBuf<float4>* b : {&model.m_pos_op, &model.v_pos_op, &model.m_quat, &model.v_quat, &model.m_lscale, &model.v_lscale})
+      check(b2k_dp_gather_slices(dp_, b->ptr, 16, 1, (uint64_t)model.cap, n, stream), "b2k_dp_gather_slices");
+    check(b2k_dp_gather_slices(dp_, model.m_sh_dc.ptr, 4, 3, (uint64_t)model.cap, n, stream), "b2k_dp_gather_slices");
+    check(b2k_dp_gather_slices(dp_, model.m_sh_hi32.ptr, 4, hi, (uint64_t)model.cap, n, stream), "b2k_dp_gather_slices");
+    check(b2k_dp_gather_slices(dp_, model.v_sh.ptr, 4, 1, (uint64_t)model.cap, n, stream), "b2k_dp_gather_slices");
+    check(b2k_dp_gather_slices(dp_, model.last_step.ptr, 4, 1, (uint64_t)model.cap, n, stream), "b2k_dp_gather_slices");
+  }
+  reduce_statistics(stream);
+  const int n_before = model.n;
+  const void* before[2] = {model.pos_op.ptr, model.sh_hi32.ptr};
+  if (sharded) check(b2k_dp_release_shares(dp_, stream), "b2k_dp_release_shares");   // the pass may reallocate what the peers have mapped
+  const RefineStats st = refiner.run(model, *ctxs[0], p, stream);
+  for (size_t l = 1; l < ctxs.size(); l++) if (model.cap > ctxs[l]->n_cap) ctxs[l]->setup(W, H, model.cap, stream);
+  if (model.n != n_before || model.pos_op.ptr != before[0] || model.sh_hi32.ptr != before[1]) {
+    cuda(cudaStreamSynchronize(stream), "sync");
+    grad.free();
+    grad.reserve((size_t)std::max(model.n, 1) * (11 + 3 * (size_t)model.K()));
+  }
+  grad.zero(stream);
+  cuda(cudaStreamSynchronize(stream), "sync");
+  if (sharded) share_buffers();
+  return st;
 }
 
 StepTrainer::~StepTrainer() {

@@ -13,6 +13,7 @@
 #pragma once
 #include <memory>
 #include "b2c_api.h"
+#include "refine.h"
 
 namespace b2c {
 
@@ -59,6 +60,12 @@ class StepTrainer {
   void read_loss(float* out16, cudaStream_t stream);
   // The refinement statistics made global over the ranks (max: refine_norm, max_screen; sum: vis_count, vis_weight).
   void reduce_statistics(cudaStream_t stream);
+  // The refinement pass between steps (RefineState::run, src/gpu/refine.cu:244-342) on every rank's replica: first the
+  // optimizer state of every splat is made whole on every rank (after the sharded update only its owner holds it) and the
+  // statistics are reduced over the ranks; the pass itself is deterministic, so the replicas stay identical without any
+  // further exchange. Buffers that grew are shared again and the gradient accumulator follows the new count.
+  RefineStats refine(const RefineParams& p, cudaStream_t stream);
+  RefineState refiner;
   // Sum of all parameter words of the replica as 64-bit integers: equal on every rank when the replicas are identical.
   uint64_t replica_checksum(cudaStream_t stream);
 
@@ -82,6 +89,7 @@ class StepTrainer {
   OptimParams optim_params(const CameraGPU& cam) const;
   const uint32_t* target(int view, int slot, cudaStream_t s, bool from_host);
 
+  void share_buffers();
   B2kDp* dp_ = nullptr;
   B2kDpPeers peers_{};
   std::vector<cudaStream_t> streams_;

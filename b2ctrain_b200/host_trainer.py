@@ -34,6 +34,8 @@ SIGNATURES = {
     "b2ch_trainer_download": (C.c_int, [_P, _P, _P, _P, _P]),
     "b2ch_trainer_reduce_statistics": (C.c_int, [_P, _P]),
     "b2ch_trainer_checksum": (C.c_uint64, [_P, _P]),
+    "b2ch_trainer_refine": (C.c_int, [_P, _P, _P, C.c_int32, _P, _P, _P, _P]),
+    "b2ch_refine_once": (C.c_int, [C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P, _P, _P, _P, _P]),
     "b2ch_render_headless": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "b2ch_ply_read": (C.c_int, [C.c_char_p, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b2ch_ply_write": (C.c_int, [C.c_char_p, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_char_p]),
@@ -144,6 +146,18 @@ class HostTrainer:
         _check(lib().b2ch_trainer_download(self.h, *[x.ctypes.data_as(_P) for x in a]), "b2ch_trainer_download")
         return dict(n=self.n, degree=self.degree, pos_op=a[0], quat=a[1], lscale=a[2], sh=a[3])
 
+    def refine(self, stream, cam_pos, cam_focal, iter=1000, total=30000, growth_allowed=True, max_splats=10_000_000, growth_grad_threshold=0.0025,
+               growth_select_fraction=0.25, split_at_screen_size=0.5, opac_decay=0.004, seed=42, no_new=False, cull_weight=0.0):
+        """StepTrainer::refine (collective over the ranks). Returns the counts; the model's size follows."""
+        f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+        fp = np.array([growth_grad_threshold, growth_select_fraction, split_at_screen_size, opac_decay, cull_weight], np.float32)
+        up = np.array([iter, total, int(growth_allowed), max_splats, seed, int(no_new)], np.uint32)
+        cp, cf, out = f32(cam_pos), f32(cam_focal), np.zeros(6, np.int32)
+        p = lambda a: a.ctypes.data_as(_P)
+        _check(lib().b2ch_trainer_refine(self.h, p(cp), p(cf), len(cf), p(fp), p(up), C.c_void_p(int(stream)), p(out)), "b2ch_trainer_refine")
+        self.n = int(out[0])
+        return dict(zip(("n", "pruned", "relocated", "grown", "split_oversized", "culled"), (int(x) for x in out)))
+
     def reduce_statistics(self, stream):
         _check(lib().b2ch_trainer_reduce_statistics(self.h, C.c_void_p(int(stream))), "b2ch_trainer_reduce_statistics")
 
@@ -192,3 +206,24 @@ def render_headless(splat, cameras, output_dir, background=(0.0, 0.0, 0.0), sh_d
     _check(lib().b2ch_render_headless(splat.encode(), cameras.encode(), output_dir.encode(), bg, int(sh_degree), int(depth), int(render_chunks), int(rank),
                                       int(world), C.byref(done)), "render_headless")
     return done.value
+
+
+def refine_once(scene, stats, cam_pos, cam_focal, W=64, H=64, iter=1000, total=30000, growth_allowed=True, max_splats=10_000_000, growth_grad_threshold=0.0025,
+                growth_select_fraction=0.25, split_at_screen_size=0.5, opac_decay=0.004, seed=42, no_new=False, cull_weight=0.0):
+    """One RefineState::run of the C++ host (src/gpu/refine.cu:244-342) on a scene dict with statistics [4][n] = refine_norm,
+    max_screen, vis_count, vis_weight. Returns (refined scene dict, counts dict, pairs [2][k] parent -> child slot)."""
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+    n, deg = int(scene["n"]), int(scene["degree"])
+    K, capn = (deg + 1) ** 2, 2 * n + 16
+    fp = np.array([growth_grad_threshold, growth_select_fraction, split_at_screen_size, opac_decay, cull_weight], np.float32)
+    up = np.array([iter, total, int(growth_allowed), max_splats, seed, int(no_new)], np.uint32)
+    ins = [f32(scene[k]) for k in ("pos_op", "quat", "lscale", "sh")] + [f32(stats), f32(cam_pos), f32(cam_focal)]
+    outs = [np.zeros((capn, 4), np.float32) for _ in range(3)] + [np.zeros((capn, K, 3), np.float32)]
+    pairs, out = np.zeros((2, capn), np.uint32), np.zeros(7, np.int32)
+    p = lambda a: a.ctypes.data_as(_P)
+    _check(lib().b2ch_refine_once(n, deg, *[p(a) for a in ins[:6]], p(ins[6]), len(ins[6]), p(fp), p(up), int(W), int(H), p(out), capn, *[p(a) for a in outs],
+                                  p(pairs)), "refine_once")
+    m, k = int(out[0]), int(out[6])
+    counts = dict(zip(("n", "pruned", "relocated", "grown", "split_oversized", "culled"), (int(x) for x in out[:6])))
+    refined = dict(n=m, degree=deg, pos_op=outs[0][:m], quat=outs[1][:m], lscale=outs[2][:m], sh=outs[3][:m])
+    return refined, counts, np.ascontiguousarray(pairs.reshape(-1)[: 2 * k].reshape(2, k))

@@ -36,6 +36,8 @@ def parse():
     ap.add_argument("--views", type=int, default=None, help="override views per step / cameras (testing only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
+    ap.add_argument("--no-render", action="store_true", help="train workload: skip the render sub-object (config 3 sample)")
+    ap.add_argument("--render-splats", type=int, default=None, help="override config 3's splat count in the render sub-object (testing only)")
     ap.add_argument("--views-in-flight", type=int, default=4, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--allreduce", action="store_true", help="N > 1: ncclAllReduce of the dense gradient + replicated Adam instead of the sharded "
                     "peer-memory update")
@@ -211,6 +213,18 @@ def main():
         result = bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks, sampler)
     else:
         result = bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_ranks, sampler)
+        if args.workload == "train" and not args.no_render:
+            # The second half of the metric: render Mpix/s on config 3 (6M splats SH4, 3840x2160, RGB + alpha + depth),
+            # cameras split over the ranks, a bounded sample of the 256-camera orbit (16 cameras per rank).
+            del scene
+            torch.cuda.empty_cache()
+            n3 = args.render_splats or scenes.CONFIG_SPLATS[3][0]
+            cams3 = scenes.config_cameras(3)[:: max(1, 256 // (16 * world))][: 16 * world]
+            rargs = argparse.Namespace(**{**vars(args), "steps": 1, "warmup": 3, "chunks": 4 if n3 >= 1_000_000 else 1})
+            r = bench_render(rargs, scenes.config_scene(3, n=n3), cams3, device, rank, world, barrier, max_over_ranks, ClockSampler(local_rank))
+            if rank == 0:
+                r["config"]["workload"] = workload_name(argparse.Namespace(splats=args.render_splats, views=None), 3, n3) + f" [sample: {len(cams3)} of its 256 cameras]"
+                result["render"] = r
     if rank == 0:
         result.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None, "data": "synthetic",
                        "dtype": "f32"})

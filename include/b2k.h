@@ -98,7 +98,7 @@ typedef struct {
                               and counts, one "some pixel can still take a fragment" flag per tile, the summed-area table
                               of those flags), or NULL when n_chunks <= 1 */
   void* bwd_scratch;       /* b2k_bwd_scratch_bytes() bytes, needed when the forward runs with bwd_info: per-pixel (colour
-                              sums, transmittance) checkpoints the forward leaves every 256 fragments of a tile's list, and
+                              sums, transmittance) checkpoints the forward leaves every 128 fragments of a tile's list, and
                               the work list of the backward, which replays the segments between checkpoints independently.
                               Takes the place of nothing in the reference (its backward walks a tile's list in one CTA) */
   uint64_t bwd_scratch_bytes;
@@ -217,7 +217,7 @@ uint64_t b2k_bwd_scratch_bytes(int32_t W, int32_t H, int32_t n_chunks, uint64_t 
 
 /* ---- backward ---- */
 /* rasterize_backward, src/gpu/render.h:106 (raster_bwd_kernel, src/gpu/raster_bwd.cu:11-143). Same gradients; the
- * tile lists are replayed in segments of 256 fragments from the forward's checkpoints in ctx->bwd_scratch. */
+ * tile lists are replayed in segments of 128 fragments from the forward's checkpoints in ctx->bwd_scratch. */
 int b2k_raster_bwd(const B2kCtx* ctx, const B2kModel* m, const B2kRenderOpts* opts, b2k_stream_t s);
 /* rasterize_backward_tc, src/gpu/render.h:107-109 (raster_bwd_tc_kernel, src/gpu/raster_bwd_tc.cu:30-225), as far as its
  * contract goes: the pixel gradients in v_out were produced with LossParams::grad_scale applied and the per-splat
@@ -242,6 +242,54 @@ int b2k_adam(const B2kModel* m, const B2kOptim* op, float* grad, b2k_stream_t s)
  * that the update of one slice can run while the all-reduce of the next slice is in flight. Same device code and the
  * same results as b2k_adam over the whole model (optim.cu:299-376). */
 int b2k_adam_range(const B2kModel* m, const B2kOptim* op, float* grad, int32_t first, int32_t count, b2k_stream_t s);
+
+/* ---- refinement (RefineState::run, src/gpu/refine.cu:244-342), as the device steps its host sequence calls ----
+ * All index / flag arrays are [n] device words; none of the calls synchronises. */
+/* Stable ascending sort of (key, value) pairs on 32-bit keys (the role of cub::DeviceRadixSort in refine.cu:206-223): the
+ * sorted pairs end in (keys, vals); (keys_alt, vals_alt) is scratch of the same size; tmp holds b2k_sort_pairs_tmp_bytes(). */
+uint64_t b2k_sort_pairs_tmp_bytes(void);
+int b2k_sort_pairs_u32(uint32_t* keys, uint32_t* vals, uint32_t* keys_alt, uint32_t* vals_alt, uint32_t n, void* tmp, uint64_t tmp_bytes, b2k_stream_t s);
+/* prune_flags_kernel, refine.cu:54-72: keep / dead / culled flags (non-finite, transparent, oversized or far splats; with
+ * cull_weight > 0 also those whose vis_weight is below it). center: 3 host floats. */
+int b2k_refine_flags(const B2kModel* m, const float* center, float max_allowed, float cull_weight, uint32_t* keep, uint32_t* dead, uint32_t* culled, b2k_stream_t s);
+/* gumbel_keys_kernel, refine.cu:75-93: keys of a weighted draw without replacement, stored so that an ASCENDING unsigned
+ * sort lists the largest key first (the reference sorts floats descending); vals = the splat index. mode 0: weight =
+ * effective opacity of kept visible splats; mode 1: refine_norm above `threshold` (also written to `above` when given). */
+int b2k_refine_sample_keys(const B2kModel* m, const uint32_t* keep, const uint32_t* excluded, int32_t mode, float threshold, uint32_t seed, uint32_t* keys,
+                           uint32_t* vals, uint32_t* above, b2k_stream_t s);
+/* oversized_flags_kernel, refine.cu:95-99. */
+int b2k_refine_oversized(const B2kModel* m, const uint32_t* keep, const uint32_t* excluded, float threshold, uint32_t* flags, b2k_stream_t s);
+/* mark_kernel, refine.cu:101-104: flags[idx[k]] = 1 for k < count. */
+int b2k_refine_mark(const uint32_t* idx, int32_t count, uint32_t* flags, b2k_stream_t s);
+/* split_kernel, refine.cu:107-152: parent parents[k] becomes itself + one child, for k < count. The child's slot is
+ * dead_idx[k] for k < from_dead and m->n + (k - from_dead) after that (m->n = the count before this call; the caller raises
+ * it by count - from_dead afterwards and must have grown the buffers first). children[k] receives the slot;
+ * tile_count (a RenderCtx's, may be NULL) is cleared at the child's slot. */
+int b2k_refine_split(const B2kModel* m, uint32_t* tile_count, const uint32_t* parents, const uint32_t* dead_idx, int32_t from_dead, int32_t count,
+                     float split_at_screen_size, uint32_t* children, b2k_stream_t s);
+/* kill_slots_kernel, opacity_decay_kernel, bake_kernel (refine.cu:231, 154-161, 40-51). */
+int b2k_refine_kill(const B2kModel* m, const uint32_t* idx, int32_t count, b2k_stream_t s);
+int b2k_refine_opacity_decay(const B2kModel* m, float delta, b2k_stream_t s);
+int b2k_refine_bake_floor(const B2kModel* m, b2k_stream_t s);
+/* axis_kernel, refine.cu:179-185, for the percentile bounds: ascending-sortable keys of one coordinate (non-finite -> 0) and
+ * the splat indices; b2k_key_to_float turns a sorted key back into the coordinate (host arithmetic). */
+int b2k_refine_axis_keys(const B2kModel* m, int32_t axis, uint32_t* keys, uint32_t* vals, b2k_stream_t s);
+float b2k_key_to_float(uint32_t ascending_key_bits);
+
+/* ---- evidence and label vote (forward replays of a rendered view) ----
+ * evidence_kernel, src/train/evidence.cu:48-121: for the view just rendered with bwd_info (ranges shrunk, last_idx
+ * set), acc[i][0..2] += sum over pixels of vis * (m, m * res, k) with m = target alpha * weight, res the mean absolute
+ * colour error of the pixel (+ normal_weight * the normal residual when `normals` is given and the view was rendered
+ * with the pseudo-normal feature lane), k = (masked_has_alpha ? target alpha : 1) * weight. acc is [n][3]. */
+int b2k_evidence_view(const B2kCtx* ctx, const uint32_t* rgba, const uint32_t* normals, const uint8_t* weights, int32_t masked_has_alpha, float normal_weight,
+                      float* acc, b2k_stream_t s);
+/* fold_view_kernel, src/train/evidence.cu:123-136: evidence[i][8] += (w_in, w_all, err, -, w_in * dir xyz, w_in^2) of one
+ * view's acc, dir the unit vector from the splat to cam_pos (3 host floats). */
+int b2k_evidence_fold(const B2kModel* m, const float* acc, const float* cam_pos, float* evidence, b2k_stream_t s);
+/* label_vote_kernel, src/train/evidence.cu:142-196: votes[i][class of the pixel] += vis * k over the view's pixels;
+ * votes is [n][b2k_label_bins()], class ids at or above the bin count are ignored. */
+int b2k_label_vote(const B2kCtx* ctx, const uint32_t* rgba, const uint8_t* labels, const uint8_t* weights, int32_t masked_has_alpha, float* votes, b2k_stream_t s);
+int32_t b2k_label_bins(void);
 
 /* ---- data parallelism over the GPUs of one node ----
  * The reference is single-GPU; these entry points shard its step by view (one process or thread per GPU, a full model
@@ -268,6 +316,14 @@ int b2k_dp_barrier(B2kDp* dp, b2k_stream_t s);
  * of this rank; on return peers[r] is rank r's buffer mapped into this process (peers[rank] == base). Collective;
  * synchronises the stream. The mappings live until b2k_dp_destroy. Needs peer access between the GPUs (NVLink). */
 int b2k_dp_share(B2kDp* dp, void* base, void** peers, b2k_stream_t s);
+/* Closes every mapping b2k_dp_share opened (after the stream has drained): call it on all ranks before buffers that were
+ * shared are freed or reallocated, then share the new ones. */
+int b2k_dp_release_shares(B2kDp* dp, b2k_stream_t s);
+/* After the sharded update only the owner of a splat holds its current optimizer state. This makes a per-splat array
+ * whole again on every rank, in place: for every rank r its slice (b2k_dp_slice) of each of `lanes` lanes (lane l starts
+ * at base + l * lane_stride elements) is broadcast from r. Used before anything that moves splats between slices or
+ * reads other ranks' moments (refinement, compaction, a checkpoint written by one rank). */
+int b2k_dp_gather_slices(B2kDp* dp, void* base, uint64_t elem_bytes, int32_t lanes, uint64_t lane_stride, int32_t n, b2k_stream_t s);
 /* The splats [first, first + count) whose update rank `rank` of `world` owns in b2k_dp_adam_shard: contiguous, starts
  * multiples of 128, together covering [0, n) exactly. Pure host arithmetic (no GPU needed). */
 int b2k_dp_slice(int32_t n, int32_t rank, int32_t world, int32_t* first, int32_t* count);

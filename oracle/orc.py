@@ -456,6 +456,28 @@ class RefCuda:
                     v_sh=self.download("v_sh", (n,), np.float32), last_step=self.download("last_step", (n,), np.uint32),
                     vis_count=self.download("vis_count", (n,), np.float32), refine_norm=self.download("refine_norm", (n,), np.float32))
 
+    def refine(self, stats, cam_pos, cam_focal, iter=1000, total=30000, growth_allowed=True, max_splats=10_000_000, growth_grad_threshold=0.0025,
+               growth_select_fraction=0.25, split_at_screen_size=0.5, opac_decay=0.004, seed=42, no_new=False, cull_weight=0.0):
+        """RefineState::run (src/gpu/refine.h) on the handle's model; stats [4][n] = refine_norm, max_screen, vis_count, vis_weight.
+        Returns dict(n, pruned, relocated, grown, split_oversized, culled); the model's n changes with it."""
+        fp = np.array([growth_grad_threshold, growth_select_fraction, split_at_screen_size, opac_decay, cull_weight], np.float32)
+        up = np.array([iter, total, int(growth_allowed), max_splats, seed, int(no_new)], np.uint32)
+        out = np.zeros(6, np.int32)
+        self._check(self.l.refcu_refine(self.h, _p(_f32(stats)), _p(_f32(cam_pos)), _p(_f32(cam_focal)), len(cam_focal), _p(fp), _p(up), _p(out)))
+        self.scene = dict(self.scene, n=int(out[0]))
+        return dict(zip(("n", "pruned", "relocated", "grown", "split_oversized", "culled"), (int(x) for x in out)))
+
+    def evidence(self, cams, labels=None, masked=False, has_alpha=False):
+        """compute_evidence (src/train/evidence.h) over the cameras, all against the view set with set_view; returns
+        (evidence [n][7], labels [n][2] or None)."""
+        rows = np.concatenate([np.concatenate([[c["fx"], c["fy"], c["cx"], c["cy"]], _f32(c["R"]), _f32(c["t"])]) for c in cams]).astype(np.float32)
+        n = self.scene["n"]
+        ev = np.zeros((n, 7), np.float32)
+        lab = None if labels is None else np.zeros((n, 2), np.float32)
+        lb = None if labels is None else np.ascontiguousarray(labels, dtype=np.uint8)
+        self._check(self.l.refcu_evidence(self.h, len(cams), _p(rows), _p(lb), int(masked), int(has_alpha), _p(ev), _p(lab)))
+        return ev, lab
+
     def download(self, what, shape, dtype):
         sel = dict(proj0=0, proj1=1, proj2=2, tile_count=3, vals_sorted=4, keys_sorted=5, tile_ranges=6, out_rgba=7, last_idx=8, v_splat=9, pos_op=10, quat=11,
                    lscale=12, sh_dc=13, sh_hi32=14, m_pos_op=15, v_pos_op=16, m_quat=17, v_quat=18, m_lscale=19, v_lscale=20, m_sh_dc=21, m_sh_hi32=22,

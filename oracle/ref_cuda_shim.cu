@@ -7,7 +7,20 @@
 #include "gpu/loss.h"
 #include "gpu/optim.h"
 #include "model.h"
+#include "gpu/cage.h"
+#include "gpu/deform.h"
+#include "gpu/refine.h"
+#include "train/evidence.h"
+#include <algorithm>
 #include <cstring>
+
+// Link-time stand-ins for lanes of the reference that this checker never drives (the evidence pass takes optional rigs,
+// always null here; the refinement reads one accessor of the trainer's bounds). They are not reference code.
+namespace b2c {
+void BodyRig::pose(int, const Model&, cudaStream_t) { throw std::runtime_error("BodyRig::pose is not part of the checker"); }
+void CageRig::pose(int, const Model&, cudaStream_t) { throw std::runtime_error("CageRig::pose is not part of the checker"); }
+float Bounds::max_extent() const { return std::max(extent[0], std::max(extent[1], extent[2])); }
+}
 
 using namespace b2c;
 
@@ -190,6 +203,46 @@ int refcu_download(void* hp, int what, void* dst, size_t bytes) {
   });
 }
 uint32_t refcu_num_isect(void* hp) { return ((Handle*)hp)->ctx.num_isect; }
+
+// RefineState::run (gpu/refine.h) on the handle's model with the given statistics ([4][n]: refine_norm, max_screen, vis_count,
+// vis_weight) and cameras. fp: growth_grad_threshold, growth_select_fraction, split_at_screen_size, opac_decay, cull_weight;
+// up: iter, total, growth_allowed, max_splats, seed, no_new. out: new n, pruned, relocated, grown, split_oversized, culled.
+int refcu_refine(void* hp, const float* stats, const float* cam_pos, const float* cam_focal, int n_cams, const float* fp, const uint32_t* up, int* out) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] {
+    const size_t n = (size_t)h->model.n;
+    float* dst[4] = {h->model.refine_norm.ptr, h->model.max_screen.ptr, h->model.vis_count.ptr, h->model.vis_weight.ptr};
+    for (int k = 0; k < 4; k++) CUDA_CHECK(cudaMemcpy(dst[k], stats + k * n, n * sizeof(float), cudaMemcpyHostToDevice));
+    RefineState st;
+    st.init(h->model, 0);
+    st.set_cameras(std::vector<float>(cam_pos, cam_pos + 3 * n_cams), std::vector<float>(cam_focal, cam_focal + n_cams));
+    RefineParams p;
+    p.growth_grad_threshold = fp[0]; p.growth_select_fraction = fp[1]; p.split_at_screen_size = fp[2]; p.opac_decay = fp[3]; p.cull_weight = fp[4];
+    p.iter = up[0]; p.total = up[1]; p.growth_allowed = up[2] != 0; p.max_splats = up[3]; p.seed = up[4]; p.no_new = up[5] != 0;
+    const RefineStats r = st.run(h->model, h->ctx, p, 0);
+    out[0] = h->model.n; out[1] = r.pruned; out[2] = r.relocated; out[3] = r.grown; out[4] = r.split_oversized; out[5] = r.culled;
+  });
+}
+int refcu_n(void* hp) { return ((Handle*)hp)->model.n; }
+
+// compute_evidence (train/evidence.h) over n_views cameras that share the handle's target view; labels: per-pixel class
+// ids or null. out_ev [n][7], out_labels [n][2] (or null). cams: per view intr[4], R[9], t[3] = 16 floats.
+int refcu_evidence(void* hp, int n_views, const float* cams, const uint8_t* labels, int masked, int has_alpha, float* out_ev, float* out_labels) {
+  Handle* h = (Handle*)hp;
+  return guarded(h, [&] {
+    DevBuf<uint8_t> lab;
+    ViewGPU v = h->view; v.masked = masked != 0; v.has_alpha = has_alpha != 0;
+    if (labels) { lab.upload(labels, (size_t)h->ctx.W * h->ctx.H); v.labels = lab; }
+    std::vector<ViewGPU> views((size_t)n_views, v);
+    std::vector<Camera> cs;
+    for (int i = 0; i < n_views; i++) cs.push_back(camera_of(cams + i * 16, cams + i * 16 + 4, cams + i * 16 + 13, h->ctx.W, h->ctx.H));
+    Config cfg; cfg.export_labels = labels != nullptr;
+    compute_evidence(h->ctx, h->model, views, cs, cfg, 0);
+    const std::vector<float> ev = download_evidence(h->model, 0);
+    std::memcpy(out_ev, ev.data(), ev.size() * sizeof(float));
+    if (out_labels) { const std::vector<float> l = download_labels(h->model, 0); std::memcpy(out_labels, l.data(), l.size() * sizeof(float)); }
+  });
+}
 
 // One training step of the reference (trainer.cpp:487-529): forward, loss, backward (tensor-core or warp), optimizer.
 // Returns the average milliseconds per step over `iters` timed steps (after `warm` untimed ones), CUDA events.

@@ -243,3 +243,82 @@ def test_loss_value_and_gradient_image_match_reference_kernel_in_the_masked_alph
     assert abs(got - want) <= 2e-5 * abs(want), (got, want)
     v = h.ctx.v_out.cpu().numpy()
     assert rel_l2(v, v_ref) <= 2e-4 and np.max(np.abs(v - v_ref)) <= 2e-3 * np.max(np.abs(v_ref))
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_evidence_and_label_vote_match_the_reference_kernels(masked):
+    """compute_evidence over three views (src/train/evidence.cu:48-196): per-splat in-mask weight, total weight, error,
+    effective view count and direction, and the winning class with its share, against the reference's kernels."""
+    import torch
+    from b2ctrain_b200 import api
+    from b2ctrain_b200.evidence import Evidence
+    W, H = 160, 120
+    scene = scenes.make_splats(5000, 2, 61, log_scale=(-3.0, 0.5))
+    cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, a, 10.0), W, H, 120.0) for a in (0.0, 50.0, 140.0)]
+    scene = scenes.floor_for_cameras(scene, cams)
+    rng = np.random.Generator(np.random.PCG64(9))
+    gt = rng.integers(0, 2 ** 32, W * H, dtype=np.uint64).astype(np.uint32)
+    wts = rng.integers(0, 256, W * H).astype(np.uint8)
+    labels = (np.arange(W * H) // (W * 8) % 7).astype(np.uint8)        # bands of classes; one band beyond the bin count
+    labels[: W * 4] = 40
+    ref = orc.RefCuda(scene, cams[0])
+    ref.set_view(gt, wts)
+    want_ev, want_lab = ref.evidence(cams, labels, masked=masked, has_alpha=True)
+    ref.close()
+    m = api.Model("cuda:0").upload(scene)
+    ctx = api.RenderCtx("cuda:0"); ctx.setup(W, H, m.cap)
+    view = api.ViewGPU(torch.from_numpy(gt.view(np.int32)).cuda(), torch.from_numpy(wts).cuda(), W, H)
+    ev = Evidence(m)
+    lab_t = torch.from_numpy(labels).cuda()
+    for cam in cams:
+        ev.add_view(ctx, cam, view, masked=masked, has_alpha=True, labels=lab_t)
+    got_ev, got_lab = ev.download_evidence(), ev.download_labels()
+    assert np.abs(want_ev[:, 1]).max() > 1.0
+    for k, name in enumerate(("w_in", "w_all", "err")):
+        assert rel_l2(got_ev[:, k], want_ev[:, k]) <= 2e-5, name
+    assert rel_l2(got_ev[:, 4:7], want_ev[:, 4:7]) <= 2e-5
+    seen = want_ev[:, 0] > 1e-3                                          # the ratio of two tiny sums is ill-conditioned
+    assert np.max(np.abs(got_ev[seen, 3] - want_ev[seen, 3])) <= 1e-3 and np.all(got_ev[:, 3] <= 3.0 + 1e-4)
+    sure = want_lab[:, 1] > 0.55                                         # a clear winner: the class must agree
+    assert sure.sum() > 500 and np.array_equal(got_lab[sure, 0], want_lab[sure, 0])
+    assert np.max(np.abs(got_lab[sure, 1] - want_lab[sure, 1])) <= 1e-4
+    assert np.array_equal(got_lab[:, 1] > 0, want_lab[:, 1] > 0)
+
+
+@pytest.mark.parametrize("case", ["grow", "relocate_and_cull", "no_new"])
+def test_refinement_pass_matches_the_reference(case):
+    """RefineState::run (src/gpu/refine.cu:244-342) of the C++ host against the reference's, from the same model,
+    statistics, cameras and seeds: the same counts, the same parents chosen in the same order, the same refined splats."""
+    from b2ctrain_b200 import host_trainer as ht
+    n, deg = 20000, 2
+    scene = scenes.make_splats(n, deg, 71, log_scale=(-3.5, 0.6))
+    cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, a, 10.0), 64, 64, 64.0) for a in (0.0, 120.0, 240.0)]
+    scene = scenes.floor_for_cameras(scene, cams)
+    rng = np.random.Generator(np.random.PCG64(3))
+    dead = rng.random(n) < (0.001 if case == "grow" else 0.08)
+    scene["pos_op"][dead, 3] = -9.0                                     # transparent: pruned
+    scene["pos_op"][5, 0] = np.nan; scene["lscale"][7, 1] = 12.0        # non-finite, absurdly large
+    stats = np.stack([np.abs(rng.normal(0.002, 0.002, n)), np.abs(rng.normal(0.2, 0.2, n)), (rng.random(n) < 0.8) * rng.integers(1, 9, n), rng.random(n) * 5.0]).astype(np.float32)
+    kw = dict(iter=3000, total=30000, seed=11, cull_weight=0.3 if case == "relocate_and_cull" else 0.0, no_new=case == "no_new",
+              max_splats=n + 2500 if case == "grow" else 10_000_000)
+    cam_pos, cam_focal = np.stack([c["pos"] for c in cams]).astype(np.float32), np.full(3, 64.0, np.float32)
+    ref = orc.RefCuda(scene, cams[0])
+    want_counts = ref.refine(stats, cam_pos, cam_focal, **kw)
+    want = ref.model_state()
+    ref.close()
+    got, counts, pairs = ht.refine_once(scene, stats, cam_pos, cam_focal, **kw)
+    print(case, counts)
+    assert counts == want_counts
+    if case == "no_new":
+        assert counts["relocated"] == counts["grown"] == counts["split_oversized"] == 0 and counts["n"] == n and counts["pruned"] > 1000
+    elif case == "grow":
+        assert counts["grown"] > 100 and counts["split_oversized"] > 100 and counts["n"] > n
+    else:
+        assert counts["relocated"] > 1000 and counts["culled"] > 1000
+    assert pairs.shape[1] == counts["relocated"] + counts["grown"] + counts["split_oversized"]
+    fin = np.isfinite(want["pos_op"]).all(1) & np.isfinite(got["pos_op"]).all(1)
+    assert fin.mean() > 0.999
+    for k in ("pos_op", "quat", "lscale", "sh"):
+        a, b = got[k][fin].reshape(fin.sum(), -1), want[k][fin].reshape(fin.sum(), -1)
+        close = (np.abs(a - b) <= 2e-4 * (np.abs(b) + 1e-2)).all(1)
+        assert close.mean() >= 0.999, (k, close.mean())                # a draw decided in the last bits of a key may swap two parents

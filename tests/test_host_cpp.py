@@ -63,3 +63,28 @@ def test_host_harness_matches_oracle_and_reference_golden(mode, chunks, tmp_path
     assert rel_l2(grad, want["grad"]) <= TOL_GRAD_REL_L2
     fails, total, _ = check_against_fd(grad, z)
     assert fails == 0 and total > 150
+
+
+def test_reference_test_harness_compiles_against_the_mirror_headers(tmp_path):
+    """The reference's own gradient-test scaffolding (Scene, make_scene and Harness, tests/tests.cpp:22-102), taken from the
+    reference checkout at test time and compiled UNCHANGED against the mirror's header set (gpu/render.h, gpu/loss.h,
+    gpu/optim.h, model.h, ply.h on the include path), then linked with the host library. Skipped where no reference tree
+    is present (nothing of the reference is stored in this repository)."""
+    ref = orc.reference_tree()
+    if ref is None:
+        pytest.skip("no reference checkout here")
+    build_harness()
+    lines = open(os.path.join(ref, "tests", "tests.cpp")).read().splitlines()
+    start = next(i for i, l in enumerate(lines) if l.startswith("struct Scene {"))
+    end = next(i for i, l in enumerate(lines) if l.startswith("static float g_eps"))
+    body = "\n".join(lines[start:end])
+    assert "struct Harness {" in body and "optimizer_step(ctx, model, op, 0);" in body
+    src = tmp_path / "ref_harness.cpp"
+    src.write_text('#include "gpu/render.h"\n#include "gpu/loss.h"\n#include "gpu/optim.h"\n#include "model.h"\n#include "ply.h"\n#include "gpu/refine.h"\n'
+                   '#include "train/evidence.h"\n#include <random>\n#include <cstdio>\n#include <cmath>\n#include <cstdlib>\nusing namespace b2c;\n' + body +
+                   "\nint main() { Scene s = make_scene(1, 8); Harness h; h.tc = true; return (int)s.cloud.n - 8; }\n")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    pkg = os.path.join(ROOT, "b2ctrain_b200")
+    r = subprocess.run(["g++", "-std=c++17", "-O1", f"-I{HOST}", f"-I{cuda}/include", str(src), "-o", str(tmp_path / "ref_harness"), f"-L{pkg}", "-lb2chost", "-lb2k",
+                        f"-L{cuda}/lib64", "-lcudart", f"-Wl,-rpath,{pkg}", f"-Wl,-rpath,{cuda}/lib64"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
