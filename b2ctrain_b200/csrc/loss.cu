@@ -208,42 +208,39 @@ __global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __re
       }
     }
     __syncthreads();
-    // Pass 3, backward blur, horizontal: rows 0..25, output columns 0..15. One thread = one row x four columns.
-    if (tid < STAT_W * 4) {
-      const int row = tid / 4, g4 = (tid % 4) * 4;
-#pragma unroll
-      for (int m = 0; m < 5; m++) {
-        float in[16], out[4];
-        load16(s_v + m * STAT_W * ST_S + row * ST_S + g4, in);
-        window4(in, gauss, out);
-        *reinterpret_cast<float4*>(s_h + m * H_ROWS * ST_S + row * ST_S + g4) = make_float4(out[0], out[1], out[2], out[3]);
-      }
+    // Pass 3, backward blur, horizontal: rows 0..25, output columns 0..15. One task = one moment x one row x four columns
+    // (520 tasks over the 256 threads: two rounds, where one thread per row and column group would run five in a row).
+    for (int task = tid; task < 5 * STAT_W * 4; task += TILE_PX) {
+      const int m = task / (STAT_W * 4), rem = task - m * (STAT_W * 4), row = rem >> 2, g4 = (rem & 3) * 4;
+      float in[16], out[4];
+      load16(s_v + m * STAT_W * ST_S + row * ST_S + g4, in);
+      window4(in, gauss, out);
+      *reinterpret_cast<float4*>(s_h + m * H_ROWS * ST_S + row * ST_S + g4) = make_float4(out[0], out[1], out[2], out[3]);
     }
     __syncthreads();
-    // Pass 4, backward blur, vertical, then the chain rule through the five moments. One thread = one column x four rows.
-    if (tid < LOSS_TILE * 4) {
-      const int col = tid % LOSS_TILE, r4 = (tid / LOSS_TILE) * 4;
-      float acc[5][4];
+    // Pass 4, backward blur, vertical. One task = one moment x one column x four rows (320 tasks, two rounds); the five
+    // blurred maps of the tile go to shared memory (the plane pass 3 has finished reading) for the per-pixel chain rule.
+    float* s_b = s_v;   // [5][16][16]
+    for (int task = tid; task < 5 * LOSS_TILE * 4; task += TILE_PX) {
+      const int m = task / (LOSS_TILE * 4), rem = task - m * (LOSS_TILE * 4), col = rem % LOSS_TILE, r4 = (rem / LOSS_TILE) * 4;
+      float in[16], out[4];
+      const float* hp = s_h + m * H_ROWS * ST_S + r4 * ST_S + col;
 #pragma unroll
-      for (int m = 0; m < 5; m++) {
-        float in[16];
-        const float* hp = s_h + m * H_ROWS * ST_S + r4 * ST_S + col;
+      for (int k = 0; k < 14; k++) in[k] = hp[k * ST_S];
+      in[14] = in[15] = 0.f;
+      window4(in, gauss, out);
 #pragma unroll
-        for (int k = 0; k < 14; k++) in[k] = hp[k * ST_S];
-        in[14] = in[15] = 0.f;
-        window4(in, gauss, acc[m]);
-      }
-#pragma unroll
-      for (int o = 0; o < 4; o++) {
-        const int row = r4 + o;
-        const int fi = (row + 2 * HALO) * IN_S + col + 2 * HALO;
-        const uint32_t gp = s_gt[fi];
-        const float p = P[fi], g = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
-        const float sgn = p > g ? 1.f : (p < g ? -1.f : 0.f);
-        const float M = s_m[(row + HALO) * ST_S + col + HALO];
-        s_grad[c * TILE_PX + row * LOSS_TILE + col] =
-            (M * lp.l1_w * sgn + acc[0][o] + 2.f * p * acc[1][o] - 2.f * acc[2][o] + g * acc[3][o] - acc[4][o]) * lp.grad_scale;
-      }
+      for (int o = 0; o < 4; o++) s_b[m * TILE_PX + (r4 + o) * LOSS_TILE + col] = out[o];
+    }
+    __syncthreads();
+    {   // the chain rule through the five moments, one pixel per thread
+      const int fi = (ly + 2 * HALO) * IN_S + lx + 2 * HALO;
+      const uint32_t gp = s_gt[fi];
+      const float p = P[fi], g = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
+      const float sgn = p > g ? 1.f : (p < g ? -1.f : 0.f);
+      const float M = s_m[centre_m];
+      s_grad[c * TILE_PX + tid] = (M * lp.l1_w * sgn + s_b[tid] + 2.f * p * s_b[TILE_PX + tid] - 2.f * s_b[2 * TILE_PX + tid] + g * s_b[3 * TILE_PX + tid] -
+                                   s_b[4 * TILE_PX + tid]) * lp.grad_scale;
     }
     __syncthreads();   // s_h / s_v are reused by the next channel; s_grad is read below
   }

@@ -38,7 +38,7 @@ def parse():
     ap.add_argument("--no-incumbent", action="store_true", help="skip timing the reference CUDA kernels beside the product")
     ap.add_argument("--no-render", action="store_true", help="train workload: skip the render sub-object (config 3 sample)")
     ap.add_argument("--render-splats", type=int, default=None, help="override config 3's splat count in the render sub-object (testing only)")
-    ap.add_argument("--views-in-flight", type=int, default=4, help="views of a step processed concurrently on separate streams")
+    ap.add_argument("--views-in-flight", type=int, default=8, help="views of a step processed concurrently on separate streams")
     ap.add_argument("--allreduce", action="store_true", help="N > 1: ncclAllReduce of the dense gradient + replicated Adam instead of the sharded "
                     "peer-memory update")
     ap.add_argument("--chunks", type=int, default=0, help="depth chunks of the front-to-back renderer (1 = bin the whole view first, as the reference "
@@ -152,6 +152,11 @@ def cpu_reference_arm(args, cfg):
 
 
 def main():
+    # Stdout carries exactly one JSON line: anything a library prints there meanwhile (NCCL's version banner, for one) goes
+    # to stderr instead.
+    out_fd = os.dup(1)
+    os.dup2(2, 1)
+    emit = lambda obj: os.write(out_fd, (json.dumps(obj) + "\n").encode())
     args = parse()
     cfg = WORKLOADS[args.workload]
     if args.chunks <= 0:
@@ -171,9 +176,10 @@ def main():
                 "ms_per_step": r["sec_per_unit"] * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
                 "data": "synthetic", "impl": "reference",
                 "config": {"workload": workload_name(args, cfg, r["n"]), "views_per_step": 1, "l2_policy": "inputs larger than L2"},
-                "cpu_baseline": {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                "cpu_baseline": {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": "port", "sample": r["sample"], "dtype": "f64",
+                                 "views_per_step": 1},
                 "e2e": {"value": r["value"], "unit": r["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
-        print(json.dumps(line))
+        emit(line)
         return
 
     import torch
@@ -231,8 +237,9 @@ def main():
         result["config"]["workload"] = workload_name(args, cfg, n)
         if not args.no_cpu_baseline and world == 1:
             r = cpu_reference_arm(argparse.Namespace(**{**vars(args), "steps": 1, "warmup": 0}), cfg)
-            result["cpu_baseline"] = {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": "port", "sample": r["sample"]}
-        print(json.dumps(result))
+            result["cpu_baseline"] = {"value": r["value"], "unit": r["unit"], "cores": r["cores"], "kind": "port", "sample": r["sample"], "dtype": "f64",
+                                      "views_per_step": 1}
+        emit(result)
     if world > 1:
         dist.destroy_process_group()
 
@@ -359,7 +366,8 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
         mine_ms = tr.info()["phase_ms"]
         phases = {k: max_over_ranks(v) for k, v in sorted(mine_ms.items())}
         phases["views_fastest_rank"] = -max_over_ranks(-mine_ms["views"])
-        phases["update_form"] = "all-reduce + replicated Adam" if (args.allreduce or world == 1) else "sharded: peer-memory reduce + Adam + parameter broadcast in one kernel"
+        phases["update_form"] = ("Adam from the accumulator (one rank)" if world == 1 else "all-reduce + replicated Adam" if args.allreduce
+                                 else "sharded: peer-memory reduce + Adam + parameter broadcast in one kernel")
     tile_bits = info["tile_bits"]
     cap = info["isect_cap"]
     tr.close()

@@ -347,7 +347,6 @@ int b2k_dp_adam_shard(B2kDp* dp, const B2kModel* m, const B2kOptim* op, const B2
 /* ---- helpers around the path ---- */
 /* min_scale_kernel, src/gpu/refine.cu:27-38: lscale.w = sqrt(0.1) * min over cameras of distance / focal. */
 int b2k_min_scale(const B2kModel* m, const float* cam_pos, const float* cam_focal, int32_t n_cams, b2k_stream_t s);
-/* pack_kernel, src/train/teacher.cu:11-17: float RGBA -> packed RGBA8 target. alpha_override < 0 keeps the image's. */
 /* Model::compact, src/model.h:33 (src/model.cu:110-155), as its two device steps. b2k_select_flagged: the indices i
  * with keep[i] != 0 in ascending order into idx, their number into *count (device); tmp holds b2k_select_tmp_words(n)
  * words. b2k_gather_lanes: dst[l * stride + j] = src[l * stride + idx[j]] for l < lanes, j < count, with elements of 4
@@ -357,6 +356,7 @@ uint64_t b2k_select_tmp_words(int32_t n);
 int b2k_select_flagged(const uint32_t* keep, int32_t n, uint32_t* idx, uint32_t* count, uint32_t* tmp, b2k_stream_t s);
 int b2k_gather_lanes(const void* src, void* dst, const uint32_t* idx, int32_t count, int32_t lanes, uint64_t stride, int32_t elem_bytes,
                      b2k_stream_t s);
+/* pack_kernel, src/train/teacher.cu:11-17: float RGBA -> packed RGBA8 target. alpha_override < 0 keeps the image's. */
 int b2k_pack_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, int32_t alpha_override, b2k_stream_t s);
 
 const char* b2k_error_string(int status);

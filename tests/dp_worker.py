@@ -24,9 +24,23 @@ def main():
     for cam, t in zip(cams, targets):
         tr.add_view(cam, t)
     stream = torch.cuda.current_stream().cuda_stream
-    for _ in range(3):
-        tr.step(list(range(len(cams))), stream)
+    cam_pos, cam_focal = np.stack([c["pos"] for c in cams]).astype(np.float32), np.full(len(cams), 120.0, np.float32)
+    rkw = dict(iter=500, total=30000, seed=5, growth_grad_threshold=1e-5, split_at_screen_size=0.05)   # low thresholds: a small scene must still grow and split
+
+    def run(t):
+        for _ in range(3):
+            t.step(list(range(len(cams))), stream)
+        counts = t.refine(stream, cam_pos, cam_focal, **rkw)      # statistics reduced over the ranks, then the deterministic pass on every replica
+        for _ in range(2):
+            t.step(list(range(len(cams))), stream)
+        return counts
+
+    counts = run(tr)
     torch.cuda.synchronize()
+    all_counts = [None] * world
+    dist.all_gather_object(all_counts, counts)
+    assert all(c == all_counts[0] for c in all_counts), all_counts   # every rank pruned, relocated, split and grew alike
+    assert counts["grown"] + counts["split_oversized"] + counts["relocated"] > 0, counts
     sums = [None] * world
     dist.all_gather_object(sums, tr.checksum(stream))
     assert len(set(sums)) == 1, f"replicas differ: {sums}"
@@ -38,14 +52,16 @@ def main():
         one = ht.HostTrainer(scene, 160, 120, **kw)
         for cam, t in zip(cams, targets):
             one.add_view(cam, t)
-        for _ in range(3):
-            one.step(list(range(len(cams))), stream)
+        one_counts = run(one)
+        assert one_counts == counts, (one_counts, counts)
         want = one.download()
         for k in ("pos_op", "quat", "lscale", "sh"):
-            err = float(np.max(np.abs(got[k] - want[k]) / (np.abs(want[k]) + 1e-3)))
-            assert err <= 5e-5, (k, err)
+            # Adam turns a gradient component that is zero up to summation order into a full +-lr step, so a few elements
+            # legitimately differ by a step between one and two ranks; all but a few must agree closely.
+            rel = np.abs(got[k] - want[k]) / (np.abs(want[k]) + 1e-3)
+            assert float(np.mean(rel <= 2e-4)) >= 0.995 and float(np.median(rel)) <= 1e-6, (k, float(np.mean(rel <= 2e-4)), float(rel.max()))
         l1 = one.read_loss(stream)
-        assert sum(c for _, c in losses) == l1[3] == len(cams)
+        assert sum(c for _, c in losses) == l1[3] == len(cams)   # of the last step
         assert abs(sum(s for s, _ in losses) - l1[2]) <= 1e-5 * abs(l1[2])
         one.close()
         print("dp worker ok", sums[0])

@@ -48,7 +48,35 @@ for k in ("refine_norm", "max_screen"):
     assert np.array_equal(local[k].numpy(), np.maximum(both[0][k], both[1][k])), k
 for k in ("vis_count", "vis_weight"):
     assert np.array_equal(local[k].numpy(), both[0][k] + both[1][k]), k
-np.savez(os.path.join(os.environ["B2K_OUT"], f"rank{rank}.npz"), mine=np.array(mine), g=g, pos=state["pos_op"], sh=state["sh"])
+# The sharded form of the update (what b2k_dp_adam_shard does over peer memory), three steps: every rank sums only the
+# rows of its slice (b2k_dp_slice) from all ranks' accumulators, updates those splats, and the new parameters of every
+# slice reach every replica; moments stay with the owner. Replicas must end identical, and equal to the replicated update.
+from b2ctrain_b200.host_trainer import dp_slice
+first, count = dp_slice(scene["n"], rank, world)
+sl = slice(first, first + count)
+shard = dict(pos_op=scene["pos_op"].copy(), quat=scene["quat"].copy(), lscale=scene["lscale"].copy(), sh=scene["sh"].copy(), m_pos=z4(), v_pos=z4(), m_q=z4(),
+             v_q=z4(), m_ls=z4(), v_ls=z4(), m_sh=np.zeros((scene["n"], 4, 3), np.float32), v_sh=np.zeros(scene["n"], np.float32), last_step=np.zeros(scene["n"], np.uint32))
+full = {k: v.copy() for k, v in shard.items()}
+for t in (1, 2, 3):
+    every = [torch.zeros_like(torch.from_numpy(acc)) for _ in range(world)]
+    dist.all_gather(every, torch.from_numpy(acc * t))                      # the peers' accumulators, as the kernel reads them
+    rows = sum(e.numpy()[sl] for e in every)                               # fixed order of ranks: the same sums everywhere
+    mine_state = {k: np.ascontiguousarray(v[sl]) for k, v in shard.items()}
+    orc.adam(mine_state, rows, np.any(rows != 0, axis=1), dict(t=t, lr_mean=1e-4, sparse=1), 1)
+    for k, v in mine_state.items(): shard[k][sl] = v
+    for k in ("pos_op", "quat", "lscale", "sh"):                           # parameter broadcast: every slice from its owner
+        for r in range(world):
+            a, c = dp_slice(scene["n"], r, world)
+            part = torch.from_numpy(np.ascontiguousarray(shard[k][a:a + c]))
+            dist.broadcast(part, src=r)
+            shard[k][a:a + c] = part.numpy()
+    gt_all = sum(e.numpy() for e in every)
+    orc.adam(full, gt_all, np.any(gt_all != 0, axis=1), dict(t=t, lr_mean=1e-4, sparse=1), 1)
+checksum = int(sum(int(shard[k].view(np.uint32).astype(np.uint64).sum()) for k in ("pos_op", "quat", "lscale", "sh")))
+for k in ("pos_op", "quat", "lscale", "sh"):
+    assert np.array_equal(shard[k], full[k]), k                           # sharded == replicated, bit for bit
+np.savez(os.path.join(os.environ["B2K_OUT"], f"rank{rank}.npz"), mine=np.array(mine), g=g, pos=state["pos_op"], sh=state["sh"], checksum=np.uint64(checksum),
+         slice=np.array([first, count]))
 if rank == 0:
     total = np.zeros_like(acc)
     for v in range(len(cams)): total += view_grad(v)
@@ -73,6 +101,9 @@ def test_two_rank_gloo_step(tmp_path):
     assert np.allclose(r0["g"], serial, rtol=1e-12, atol=1e-15)    # = the sum of the per-view gradients
     assert np.array_equal(r0["pos"], r1["pos"]) and np.array_equal(r0["sh"], r1["sh"])   # replicas stay bit-identical
     assert np.abs(r0["g"]).max() > 0
+    # the sharded update: slices partition the splats, replicas carry the same checksum after three steps
+    assert r0["slice"][0] == 0 and r0["slice"][0] + r0["slice"][1] == r1["slice"][0] and r1["slice"][0] + r1["slice"][1] == 300
+    assert int(r0["checksum"]) == int(r1["checksum"])
 
 
 def test_slice_bounds_cover_the_model_on_block_boundaries():

@@ -95,7 +95,8 @@ def test_headless_render_writes_what_the_operators_render(tmp_path):
     ctx.setup(W, H, m.cap)
     for i, cam in enumerate(cams):
         api.render_forward(ctx, m, api.RenderParams(cam, bg=(0.1, 0.2, 0.3), sh_degree=2, bwd_info=False))
-        want = np.floor(np.clip(ctx.out_rgba.cpu().numpy(), 0, 1) * np.float32(255) + np.float32(0.5)).astype(np.uint8)   # lround: halves away from zero
+        scaled = (np.clip(ctx.out_rgba.cpu().numpy(), 0, 1) * np.float32(255)).astype(np.float64)   # the product in fp32, as the front end forms it
+        want = np.floor(scaled + 0.5).astype(np.uint8)                                                # lround: halves away from zero
         got = np.fromfile(str(tmp_path / f"view{i}.rgba8"), np.uint8).reshape(-1, 4)
         diff = np.abs(got.astype(int) - want.astype(int))
         print(f"view {i}: differing {np.mean(diff > 0):.2e}, max {diff.max()}, per channel {np.mean(diff > 0, axis=0)}")
