@@ -23,14 +23,15 @@
 namespace b2k {
 namespace {
 
-#ifndef B2K_BWD_REDUCE
-#define B2K_BWD_REDUCE 0     // 0: FADD column sums (shipped); 1: mma.sync tf32 column sums (the measured alternative)
-#endif
 #ifndef B2K_BWD_WARPS
 #define B2K_BWD_WARPS 4
 #endif
 constexpr int BWD_WARPS = B2K_BWD_WARPS;     // warps per CTA (independent: the CTA shape only sets the residency granularity)
 constexpr int BWD_BATCH = 32;                // fragments staged per warp and batch
+#ifndef B2K_BWD_GROUP
+#define B2K_BWD_GROUP 2
+#endif
+constexpr int BWD_GROUP = B2K_BWD_GROUP;                 // fragments whose state-independent math is issued together
 constexpr int RED_F = 5;                     // fragments whose partial sums are pending before a column reduction
 constexpr int RED_BLOCK = 33 * 3;            // 16-byte words per pending fragment: 32 lanes x 3 words, one slot of skew
 constexpr unsigned FULL = 0xffffffffu;
@@ -147,51 +148,6 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
     // Column sums of the pending fragments' partials, then one global reduction per non-zero lane of each splat.
     auto flush = [&]() {
       __syncwarp();
-#if B2K_BWD_REDUCE == 1
-      // Tensor-core variant of the column sums (measured against the FADD form, see profiles/): per pending fragment the
-      // [32 lanes][12 values] block is the B operand of mma.sync.m16n8k8 (tf32 inputs, fp32 accumulate) against a matrix of
-      // ones, four k-steps of eight lanes by two n-tiles of eight values; each value is split into a tf32 head and a tf32
-      // tail so that the sum keeps fp32 accuracy (two MMAs per tile). Every row of D holds the totals; lanes 0..3 read row 0.
-      for (int f = 0; f < n_pending; f++) {
-        const float* blk = reinterpret_cast<const float*>(red + f * RED_BLOCK);
-        float tot[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-#pragma unroll
-        for (int nt = 0; nt < 2; nt++) {
-          float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-          const int col = nt * 8 + (lane >> 2);
-#pragma unroll
-          for (int ks = 0; ks < 4; ks++) {
-            const int slot = ks * 8 + (lane & 3);
-            const float x0 = col < 12 ? blk[slot * 12 + col] : 0.f, x1 = col < 12 ? blk[(slot + 4) * 12 + col] : 0.f;
-            uint32_t h0, h1, l0, l1;
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h0) : "f"(x0)); asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h1) : "f"(x1));
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l0) : "f"(x0 - __uint_as_float(h0))); asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l1) : "f"(x1 - __uint_as_float(h1)));
-            const uint32_t one = 0x3f800000u;
-            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%5,%6}, {%0,%1,%2,%3};"
-                         : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3) : "r"(one), "r"(h0), "r"(h1));
-            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%4,%4,%4}, {%5,%6}, {%0,%1,%2,%3};"
-                         : "+f"(d0), "+f"(d1), "+f"(d2), "+f"(d3) : "r"(one), "r"(l0), "r"(l1));
-          }
-          tot[nt][0] = d0; tot[nt][1] = d1;   // lanes 0..3: row 0, columns nt * 8 + 2 * lane + {0, 1}
-        }
-        if (lane < 4) {
-          const uint32_t gid = pending_gid[f];
-          float* o = v_splat + (size_t)gid * GRAD_LANES;
-#pragma unroll
-          for (int nt = 0; nt < 2; nt++)
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-              const int k = nt * 8 + lane * 2 + e;
-              const float v = tot[nt][e] * (k == 10 ? 1.f : out_scale);
-              if (k < 10) { if (v != 0.f) atomicAdd(o + k, v); }
-              else if (k == 10) { vis_flag[gid] = 1u; if (vis_weight) atomicAdd(vis_weight + gid, v); }
-            }
-        }
-      }
-      __syncwarp();
-      n_pending = 0;
-      return;
-#endif
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       const bool mine = red_idx < 3 * RED_F && red_f < n_pending;
       if (mine) {
@@ -236,53 +192,72 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
         frag[lane].a = proj0[gid]; frag[lane].c = proj1[gid]; frag[lane].col = proj2[gid];
       }
       __syncwarp();
-      for (int j = (int)count - 1; j >= 0; j--) {
-        const uint32_t idx = batch_start + (uint32_t)j;
-        const float4 a = frag[j].a, c = frag[j].c;
-        // sigma for the pair: the two pixels share the row, so dy and the dy terms are scalars.
-        const float dy = pcy - a.y;
-        const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
-        const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, f2(0.5f * a.z), f2(a.w * dy)), f2(0.5f * c.x * dy * dy));
-        const bool on0 = idx < last0 && sigma.x >= 0.f && sigma.x <= c.w;
-        const bool on1 = idx < last1 && sigma.y >= 0.f && sigma.y <= c.w;
-        if (__ballot_sync(FULL, on0 || on1) == 0) continue;   // nobody in the tile sees this fragment: skip the heavy part
-        const float4 col = frag[j].col;
-        const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
-        // Branch-free from here: a pixel that does not see the fragment has alpha = 0 and adds exact zeros.
-        const float2 gauss = make_float2(__expf(-sigma.x), __expf(-sigma.y));
-        const float2 a_raw = __fmul2_rn(f2(c.y), gauss);
-        const float2 alpha = make_float2(on0 ? fminf(ALPHA_MAX, a_raw.x) : 0.f, on1 ? fminf(ALPHA_MAX, a_raw.y) : 0.f);
-        const float2 ra = make_float2(__fdividef(1.f, 1.f - alpha.x), __fdividef(1.f, 1.f - alpha.y));
-        const float2 nra = make_float2(-ra.x, -ra.y);
-        const float2 Tb = __fmul2_rn(T, ra);
-        const float2 vis = __fmul2_rn(alpha, Tb);
-        float2 va = __fmul2_rn(vow, ra);
-        va = __ffma2_rn(__ffma2_rn(Sr, nra, __fmul2_rn(Tb, f2(cr))), vr, va);
-        va = __ffma2_rn(__ffma2_rn(Sg, nra, __fmul2_rn(Tb, f2(cg))), vg, va);
-        va = __ffma2_rn(__ffma2_rn(Sb, nra, __fmul2_rn(Tb, f2(cb))), vb, va);
-        // The alpha clamp has zero slope: the geometry and opacity lanes vanish where it is active.
-        const bool live0 = on0 && a_raw.x <= ALPHA_MAX, live1 = on1 && a_raw.y <= ALPHA_MAX;
-        const float2 av = __fmul2_rn(alpha, va);
-        const float2 mvs = make_float2(live0 ? av.x : 0.f, live1 ? av.y : 0.f);          // -v_sigma
-        const float2 gx = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.z), f2(a.w * dy)));
-        const float2 gy = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.w), f2(c.x * dy)));
-        const float2 mdx = __fmul2_rn(mvs, dx);
-        const float2 og = __fmul2_rn(va, gauss);
-        const float2 sx = __fmul2_rn(gx, f2(Wf)), sy = __fmul2_rn(gy, f2(Hf));
-        const float2 qq = __ffma2_rn(sx, sx, __fmul2_rn(sy, sy));
-        const float2 rf = __fmul2_rn(make_float2(fast_sqrt(qq.x), fast_sqrt(qq.y)), inv_fa);
-        // The pair's partial sums of the eleven lanes: xy, conic, rgb (zero where the colour clamp at zero is active),
-        // opacity, refine, blend weight.
-        const float4 w0 = make_float4(hsum(gx), hsum(gy), -0.5f * hsum(__fmul2_rn(mdx, dx)), -hsum(mdx) * dy);
-        const float4 w1 = make_float4(-0.5f * dy * dy * hsum(mvs), col.x < 0.f ? 0.f : hsum(__fmul2_rn(vis, vr)), col.y < 0.f ? 0.f : hsum(__fmul2_rn(vis, vg)),
-                                      col.z < 0.f ? 0.f : hsum(__fmul2_rn(vis, vb)));
-        const float4 w2 = make_float4((live0 ? og.x : 0.f) + (live1 ? og.y : 0.f), hsum(rf), hsum(vis), 0.f);
-        float4* dst = red + n_pending * RED_BLOCK + lane * 3;
-        dst[0] = w0; dst[1] = w1; dst[2] = w2;
-        if (lane == 0) pending_gid[n_pending] = gids[j];
-        Sr = __ffma2_rn(f2(cr), vis, Sr); Sg = __ffma2_rn(f2(cg), vis, Sg); Sb = __ffma2_rn(f2(cb), vis, Sb);
-        T = Tb;
-        if (++n_pending == RED_F) flush();
+      // Fragments are replayed BWD_GROUP at a time: first what does not depend on the pixels' running state (sigma, the
+      // visibility test, the exponential, alpha and 1 / (1 - alpha)) for the whole group, so that those chains overlap;
+      // then the state-dependent part fragment by fragment, back to front. The arithmetic per pixel is unchanged.
+      for (int j0 = (int)count - 1; j0 >= 0; j0 -= BWD_GROUP) {
+        float2 g_dx[BWD_GROUP], g_gauss[BWD_GROUP], g_araw[BWD_GROUP], g_alpha[BWD_GROUP], g_ra[BWD_GROUP];
+        float g_dy[BWD_GROUP];
+        bool g_on0[BWD_GROUP], g_on1[BWD_GROUP];
+#pragma unroll
+        for (int u = 0; u < BWD_GROUP; u++) {
+          const int j = max(j0 - u, 0);   // a short last group recomputes fragment 0, unused
+          const uint32_t idx = batch_start + (uint32_t)j;
+          const float4 a = frag[j].a, c = frag[j].c;
+          // sigma for the pair: the two pixels share the row, so dy and the dy terms are scalars.
+          const float dy = pcy - a.y;
+          const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
+          const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, f2(0.5f * a.z), f2(a.w * dy)), f2(0.5f * c.x * dy * dy));
+          const bool live = j0 - u >= 0;
+          g_on0[u] = live && idx < last0 && sigma.x >= 0.f && sigma.x <= c.w;
+          g_on1[u] = live && idx < last1 && sigma.y >= 0.f && sigma.y <= c.w;
+          g_dx[u] = dx; g_dy[u] = dy;
+          g_gauss[u] = make_float2(__expf(-sigma.x), __expf(-sigma.y));
+          g_araw[u] = __fmul2_rn(f2(c.y), g_gauss[u]);
+          // a pixel that does not see the fragment has alpha = 0 and adds exact zeros below
+          g_alpha[u] = make_float2(g_on0[u] ? fminf(ALPHA_MAX, g_araw[u].x) : 0.f, g_on1[u] ? fminf(ALPHA_MAX, g_araw[u].y) : 0.f);
+          g_ra[u] = make_float2(__fdividef(1.f, 1.f - g_alpha[u].x), __fdividef(1.f, 1.f - g_alpha[u].y));
+        }
+#pragma unroll
+        for (int u = 0; u < BWD_GROUP; u++) {
+          const int j = j0 - u;
+          const bool on0 = g_on0[u], on1 = g_on1[u];
+          if (__ballot_sync(FULL, on0 || on1) == 0) continue;   // nobody in the tile sees this fragment: skip the heavy part
+          const float4 a = frag[j].a, c = frag[j].c, col = frag[j].col;
+          const float dy = g_dy[u];
+          const float2 dx = g_dx[u], gauss = g_gauss[u], a_raw = g_araw[u], alpha = g_alpha[u], ra = g_ra[u];
+          const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+          const float2 nra = make_float2(-ra.x, -ra.y);
+          const float2 Tb = __fmul2_rn(T, ra);
+          const float2 vis = __fmul2_rn(alpha, Tb);
+          float2 va = __fmul2_rn(vow, ra);
+          va = __ffma2_rn(__ffma2_rn(Sr, nra, __fmul2_rn(Tb, f2(cr))), vr, va);
+          va = __ffma2_rn(__ffma2_rn(Sg, nra, __fmul2_rn(Tb, f2(cg))), vg, va);
+          va = __ffma2_rn(__ffma2_rn(Sb, nra, __fmul2_rn(Tb, f2(cb))), vb, va);
+          // The alpha clamp has zero slope: the geometry and opacity lanes vanish where it is active.
+          const bool live0 = on0 && a_raw.x <= ALPHA_MAX, live1 = on1 && a_raw.y <= ALPHA_MAX;
+          const float2 av = __fmul2_rn(alpha, va);
+          const float2 mvs = make_float2(live0 ? av.x : 0.f, live1 ? av.y : 0.f);          // -v_sigma
+          const float2 gx = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.z), f2(a.w * dy)));
+          const float2 gy = __fmul2_rn(mvs, __ffma2_rn(dx, f2(a.w), f2(c.x * dy)));
+          const float2 mdx = __fmul2_rn(mvs, dx);
+          const float2 og = __fmul2_rn(va, gauss);
+          const float2 sx = __fmul2_rn(gx, f2(Wf)), sy = __fmul2_rn(gy, f2(Hf));
+          const float2 qq = __ffma2_rn(sx, sx, __fmul2_rn(sy, sy));
+          const float2 rf = __fmul2_rn(make_float2(fast_sqrt(qq.x), fast_sqrt(qq.y)), inv_fa);
+          // The pair's partial sums of the eleven lanes: xy, conic, rgb (zero where the colour clamp at zero is active),
+          // opacity, refine, blend weight.
+          const float4 w0 = make_float4(hsum(gx), hsum(gy), -0.5f * hsum(__fmul2_rn(mdx, dx)), -hsum(mdx) * dy);
+          const float4 w1 = make_float4(-0.5f * dy * dy * hsum(mvs), col.x < 0.f ? 0.f : hsum(__fmul2_rn(vis, vr)), col.y < 0.f ? 0.f : hsum(__fmul2_rn(vis, vg)),
+                                        col.z < 0.f ? 0.f : hsum(__fmul2_rn(vis, vb)));
+          const float4 w2 = make_float4((live0 ? og.x : 0.f) + (live1 ? og.y : 0.f), hsum(rf), hsum(vis), 0.f);
+          float4* dst = red + n_pending * RED_BLOCK + lane * 3;
+          dst[0] = w0; dst[1] = w1; dst[2] = w2;
+          if (lane == 0) pending_gid[n_pending] = gids[j];
+          Sr = __ffma2_rn(f2(cr), vis, Sr); Sg = __ffma2_rn(f2(cg), vis, Sg); Sb = __ffma2_rn(f2(cb), vis, Sb);
+          T = Tb;
+          if (++n_pending == RED_F) flush();
+        }
       }
       batch_end = batch_start;
     }

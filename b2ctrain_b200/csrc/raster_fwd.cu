@@ -12,6 +12,10 @@ namespace {
 
 constexpr int FWD_WARPS = 4;
 constexpr int FWD_BATCH = 32;
+#ifndef B2K_FWD_GROUP
+#define B2K_FWD_GROUP 4
+#endif
+constexpr int FWD_GROUP = B2K_FWD_GROUP;                 // fragments whose state-independent math is issued together
 
 // CHUNKED: the view is composited in depth chunks (chunk `chunk` of `n_chunks`, one launch each, nearest first). Between
 // launches a pixel's state lives in the output buffers: the colour sums in out_feat.xyz, the transmittance in
@@ -77,30 +81,47 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
       if constexpr (FEAT) s3[warp][lane] = proj3[gid];
     }
     __syncwarp();
-    for (uint32_t t = 0; t < remaining; t++) {
-      const float4 a = s0[warp][t], c = s1[warp][t];
-      // sigma for the pixel pair in one packed fp32x2 chain (the pixels share the row: dy terms are scalars)
-      const float dy = pcy - a.y;
-      const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
-      const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, make_float2(0.5f * a.z, 0.5f * a.z), make_float2(a.w * dy, a.w * dy)),
-                                      make_float2(0.5f * c.x * dy * dy, 0.5f * c.x * dy * dy));
-      bool hit[2] = {!done[0] && sigma.x >= 0.f && sigma.x <= c.w, !done[1] && sigma.y >= 0.f && sigma.y <= c.w};   // alpha >= 1/255
-      if (!__any_sync(0xffffffffu, hit[0] || hit[1])) continue;
-      const float4 col = s2[warp][t];
-      const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
-      const float sg[2] = {sigma.x, sigma.y};
+    // Fragments are taken FWD_GROUP at a time: first everything that does not depend on the pixels' running state (sigma,
+    // the hit test, alpha with its exponential) for the whole group, so that those chains overlap, then the short serial
+    // part (transmittance and colour sums) fragment by fragment in list order. The arithmetic per pixel is unchanged.
+    for (uint32_t t0 = 0; t0 < remaining; t0 += FWD_GROUP) {
+      float alpha[FWD_GROUP][2];
+      bool inside[FWD_GROUP][2];
 #pragma unroll
-      for (int p = 0; p < 2; p++) {
-        const float alpha = fminf(ALPHA_MAX, c.y * __expf(-sg[p]));
-        const float next_T = T[p] * (1.f - alpha);
-        if (hit[p] && next_T <= T_CUTOFF) { done[p] = true; hit[p] = false; }   // stop before the fragment that would saturate the pixel
-        if (hit[p]) {
-          const float vis = alpha * T[p];
-          r[p] += cr * vis; g[p] += cg * vis; b[p] += cb * vis;
-          if constexpr (DEPTH) zs[p] += vis * c.z;
-          if constexpr (FEAT) { const float2 fz = s3[warp][t]; f0[p] += col.w * vis; f1[p] += fz.x * vis; f2[p] += fz.y * vis; }
-          T[p] = next_T;
-          last[p] = start + t + 1;
+      for (int u = 0; u < FWD_GROUP; u++) {
+        const uint32_t t = min(t0 + (uint32_t)u, remaining - 1u);   // a short last group recomputes its last fragment, unused
+        const float4 a = s0[warp][t], c = s1[warp][t];
+        // sigma for the pixel pair in one packed fp32x2 chain (the pixels share the row: dy terms are scalars)
+        const float dy = pcy - a.y;
+        const float2 dx = make_float2(pcx - a.x, pcx + 1.f - a.x);
+        const float2 sigma = __ffma2_rn(dx, __ffma2_rn(dx, make_float2(0.5f * a.z, 0.5f * a.z), make_float2(a.w * dy, a.w * dy)),
+                                        make_float2(0.5f * c.x * dy * dy, 0.5f * c.x * dy * dy));
+        const bool live = t0 + (uint32_t)u < remaining;
+        inside[u][0] = live && sigma.x >= 0.f && sigma.x <= c.w;   // alpha >= 1/255
+        inside[u][1] = live && sigma.y >= 0.f && sigma.y <= c.w;
+        alpha[u][0] = fminf(ALPHA_MAX, c.y * __expf(-sigma.x));
+        alpha[u][1] = fminf(ALPHA_MAX, c.y * __expf(-sigma.y));
+      }
+#pragma unroll
+      for (int u = 0; u < FWD_GROUP; u++) {
+        const uint32_t t = t0 + (uint32_t)u;
+        bool hit[2] = {!done[0] && inside[u][0], !done[1] && inside[u][1]};
+        if (!__any_sync(0xffffffffu, hit[0] || hit[1])) continue;
+        const float4 col = s2[warp][t];
+        const float cr = fmaxf(col.x, 0.f), cg = fmaxf(col.y, 0.f), cb = fmaxf(col.z, 0.f);
+        const float cz = s1[warp][t].z;
+#pragma unroll
+        for (int p = 0; p < 2; p++) {
+          const float next_T = T[p] * (1.f - alpha[u][p]);
+          if (hit[p] && next_T <= T_CUTOFF) { done[p] = true; hit[p] = false; }   // stop before the fragment that would saturate the pixel
+          if (hit[p]) {
+            const float vis = alpha[u][p] * T[p];
+            r[p] += cr * vis; g[p] += cg * vis; b[p] += cb * vis;
+            if constexpr (DEPTH) zs[p] += vis * cz;
+            if constexpr (FEAT) { const float2 fz = s3[warp][t]; f0[p] += col.w * vis; f1[p] += fz.x * vis; f2[p] += fz.y * vis; }
+            T[p] = next_T;
+            last[p] = start + t + 1;
+          }
         }
       }
     }
