@@ -181,17 +181,30 @@ __global__ void __launch_bounds__(BWD_WARPS * 32) raster_bwd_kernel(
       n_pending = 0;
     };
 
+    // The records of a batch are gathered one batch ahead, into registers: the two dependent loads (list entry, then the
+    // splat's records) are in flight while the batch behind them is replayed.
+    uint32_t n_gid = 0u;
+    float4 n_a = make_float4(0.f, 0.f, 0.f, 0.f), n_c = n_a, n_col = n_a;
+    auto gather = [&](uint32_t end) {   // the batch that ends at `end`
+      if (end <= seg_lo) return;
+      const uint32_t cnt = min(end - seg_lo, (uint32_t)BWD_BATCH);
+      if ((uint32_t)lane < cnt) {
+        n_gid = vals_sorted[end - cnt + lane];
+        n_a = proj0[n_gid]; n_c = proj1[n_gid]; n_col = proj2[n_gid];
+      }
+    };
+    gather(seg_hi);
     for (uint32_t batch_end = seg_hi; batch_end > seg_lo;) {
       const uint32_t remaining = batch_end - seg_lo;
       const uint32_t count = remaining < (uint32_t)BWD_BATCH ? remaining : (uint32_t)BWD_BATCH;
       const uint32_t batch_start = batch_end - count;
       __syncwarp();
       if ((uint32_t)lane < count) {
-        const uint32_t gid = vals_sorted[batch_start + lane];
-        gids[lane] = gid;
-        frag[lane].a = proj0[gid]; frag[lane].c = proj1[gid]; frag[lane].col = proj2[gid];
+        gids[lane] = n_gid;
+        frag[lane].a = n_a; frag[lane].c = n_c; frag[lane].col = n_col;
       }
       __syncwarp();
+      gather(batch_start);
       // Fragments are replayed BWD_GROUP at a time: first what does not depend on the pixels' running state (sigma, the
       // visibility test, the exponential, alpha and 1 / (1 - alpha)) for the whole group, so that those chains overlap;
       // then the state-dependent part fragment by fragment, back to front. The arithmetic per pixel is unchanged.

@@ -4,7 +4,7 @@
 //
 // FP32-issue / latency bound (one ex2 and ~25 flops per fragment-pixel); memory traffic is the gather of 48 B per
 // staged fragment, served mostly by L2. Fragments are staged 32 at a time per warp in shared memory with 128-bit
-// loads; warps never synchronise with each other.
+// loads, gathered one batch ahead; warps never synchronise with each other.
 #include "common.cuh"
 
 namespace b2k {
@@ -70,17 +70,29 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     dst[0] = make_float4(r[0], g[0], b[0], T[0]); dst[1] = make_float4(r[1], g[1], b[1], T[1]);
   };
   if (BWD && CHUNKED && !first && range.y > range.x) checkpoint(0u);
+  // The records of a batch are gathered one batch ahead, into registers: the two dependent loads (list entry, then the
+  // splat's records) are in flight while the batch before them is composited.
+  float4 n0 = make_float4(0.f, 0.f, 0.f, 0.f), n1 = n0, n2 = n0;
+  float2 n3 = make_float2(0.f, 0.f);
+  auto gather = [&](uint32_t from) {
+    if (from < range.y && (uint32_t)lane < range.y - from) {
+      const uint32_t gid = vals_sorted[from + lane];
+      n0 = proj0[gid]; n1 = proj1[gid]; n2 = proj2[gid];
+      if constexpr (FEAT) n3 = proj3[gid];
+    }
+  };
+  gather(range.x);
   for (uint32_t start = range.x; start < range.y; start += FWD_BATCH) {
     if (__all_sync(0xffffffffu, done[0] && done[1])) break;
     if (BWD && start != range.x && ((start - range.x) & (uint32_t)(SEG_LEN - 1)) == 0u) checkpoint((start - range.x) >> SEG_SHIFT);
     const uint32_t remaining = min((uint32_t)FWD_BATCH, range.y - start);
     __syncwarp();
     if ((uint32_t)lane < remaining) {
-      const uint32_t gid = vals_sorted[start + lane];
-      s0[warp][lane] = proj0[gid]; s1[warp][lane] = proj1[gid]; s2[warp][lane] = proj2[gid];
-      if constexpr (FEAT) s3[warp][lane] = proj3[gid];
+      s0[warp][lane] = n0; s1[warp][lane] = n1; s2[warp][lane] = n2;
+      if constexpr (FEAT) s3[warp][lane] = n3;
     }
     __syncwarp();
+    gather(start + FWD_BATCH);
     // Fragments are taken FWD_GROUP at a time: first everything that does not depend on the pixels' running state (sigma,
     // the hit test, alpha with its exponential) for the whole group, so that those chains overlap, then the short serial
     // part (transmittance and colour sums) fragment by fragment in list order. The arithmetic per pixel is unchanged.

@@ -192,7 +192,10 @@ def test_full_size_view_chunked_equals_whole_and_matches_reference_kernels(cfg):
     h.forward(); api.zero_loss(h.ctx); api.photometric_loss(h.ctx, h.view, h.lp); api.rasterize_backward(h.ctx, h.model, h.rp)
     v_whole, v_chunk = h.ctx.v_splat[:n].cpu().numpy(), ctx.v_splat[:n].cpu().numpy()
     assert torch.equal(h.ctx.vis_flag[:n], ctx.vis_flag[:n])
-    assert rel_l2(v_chunk, v_whole) <= 1e-5, rel_l2(v_chunk, v_whole)
+    # Same fragments, same per-pixel arithmetic; the two forms cut a tile's list into replay segments at different places
+    # (every 128 fragments, and additionally where a depth chunk hands over), and a segment's colour-behind term starts from
+    # final sum - checkpoint, so the sums differ in rounding. Observed 4e-6 .. 1.2e-5 over configs 1, 2, 4 and runs.
+    assert rel_l2(v_chunk, v_whole) <= 2e-5, rel_l2(v_chunk, v_whole)
     assert ctx.num_isect < h.ctx.num_isect
     del ctx
     img = whole["rgba"].cpu().numpy()

@@ -89,7 +89,7 @@ def test_headless_render_writes_what_the_operators_render(tmp_path):
     assert ht.render_headless(ply, cj, str(tmp_path), background=(0.1, 0.2, 0.3), depth=True, rank=0, world=2) == 2
     assert ht.render_headless(ply, cj, str(tmp_path), background=(0.1, 0.2, 0.3), depth=True, rank=1, world=2) == 1
     flat = dict(scene); flat["lscale"] = scene["lscale"].copy(); flat["lscale"][:, 3] = 0                      # the file format has no floor lane
-    flat["quat"] = (scene["quat"] / np.linalg.norm(scene["quat"], axis=1, keepdims=True)).astype(np.float32)   # as written
+    flat["quat"] = ht.read_ply(ply)["quat"]                                                                    # as written: the writer normalises in fp32
     m = api.Model("cuda:0").upload(flat)
     ctx = api.RenderCtx("cuda:0"); ctx.want_depth = True
     ctx.setup(W, H, m.cap)
@@ -100,7 +100,10 @@ def test_headless_render_writes_what_the_operators_render(tmp_path):
         got = np.fromfile(str(tmp_path / f"view{i}.rgba8"), np.uint8).reshape(-1, 4)
         diff = np.abs(got.astype(int) - want.astype(int))
         print(f"view {i}: differing {np.mean(diff > 0):.2e}, max {diff.max()}, per channel {np.mean(diff > 0, axis=0)}")
-        assert diff.max() == 0
+        # The front end composes the camera from the JSON entry in fp32 (translation = -R * position, as the reference's
+        # camera_from_json does); the operator call above takes the float64 camera of the scene generator. The images agree
+        # to an ulp, which can move a value that sits on a rounding boundary by one step.
+        assert diff.max() <= 1 and np.mean(diff > 0) <= 1e-3
         depth = np.fromfile(str(tmp_path / f"view{i}.depth.f32"), np.float32)
         ref = ctx.out_depth.cpu().numpy()
         fin = np.isfinite(ref)
