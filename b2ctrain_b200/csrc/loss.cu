@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
   const int x_end = min(x0 + STRIP_W, W);
   const float norm = lp.scale / (3.f * (float)W * (float)H);
   const float bg_c = lp.composite ? lp.bg[c] : 0.f;
+  const float alpha_norm = lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
   const float* pred_c = reinterpret_cast<const float*>(pred) + c;
   float* out_c = reinterpret_cast<float*>(v_out) + c;
 
@@ -167,14 +168,14 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
             const float sigma1_sq = fmaxf(0.f, s1_raw), sigma2_sq = fmaxf(0.f, s2_raw);
             const float sigma12 = st[4][o] - mu1 * mu2;
             const float A1 = 2.f * mu1 * mu2 + C1, A2 = 2.f * sigma12 + C2, B1 = mu1_sq + mu2_sq + C1, B2 = sigma1_sq + sigma2_sq + C2;
-            const float inv_BB = 1.f / (B1 * B2);
+            const float inv_BB = __fdividef(1.f, B1 * B2);   // approximate divisions, as in the reference's fast-math build
             const float raw = A1 * A2 * inv_BB;
             const float ssim = fminf(fmaxf(raw, -1.f), 1.f);
             if (y >= y0 && y < y1 && xg >= x0 && xg < x_end) loss_local += M * lp.ssim_w * ssim;
             if (raw > -1.f && raw < 1.f) {
               const float k = M * lp.ssim_w;
-              const float d_mu1 = 2.f * mu2 * A2 * inv_BB - 2.f * mu1 * ssim / B1;
-              const float d_s1 = s1_raw > 0.f ? -ssim / B2 : 0.f;
+              const float d_mu1 = 2.f * mu2 * A2 * inv_BB - __fdividef(2.f * mu1 * ssim, B1);
+              const float d_s1 = s1_raw > 0.f ? -__fdividef(ssim, B2) : 0.f;
               const float d_s12 = 2.f * A1 * inv_BB;
               const float Am = k * d_mu1, Bv = k * d_s1, Cc = k * d_s12;
               // gradient = blur(Am) + 2 p blur(Bv) - 2 blur(Bv mu1) + target blur(Cc) - blur(Cc mu2): the three maps
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
                 if (lp.alpha_lane) {
                   const float da = pa - ga;
                   const float sa = da > 0.f ? 1.f : (da < 0.f ? -1.f : 0.f);
-                  const float Ma = wp * lp.match_alpha_weight * lp.scale / ((float)W * (float)H);
+                  const float Ma = wp * alpha_norm;
                   ga_grad = Ma * sa * lp.grad_scale;
                   loss_local += Ma * fabsf(da);
                 }
