@@ -387,7 +387,12 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
 #ifndef B2K_ADAM_SPLATS
 #define B2K_ADAM_SPLATS 128
 #endif
-template <int DEG> struct AdamShape { static constexpr int SPLATS = DEG <= 3 ? B2K_ADAM_SPLATS : 64, THREADS = 4 * SPLATS; };
+#ifndef B2K_ADAM_SHARD_SPLATS
+#define B2K_ADAM_SHARD_SPLATS 128
+#endif
+template <int DEG, bool SHARD = false> struct AdamShape {
+  static constexpr int SPLATS = DEG <= 3 ? (SHARD ? B2K_ADAM_SHARD_SPLATS : B2K_ADAM_SPLATS) : 64, THREADS = 4 * SPLATS;
+};
 
 // PEERS = NoPeers: the update of this GPU's replica from its own accumulator (rows cleared on the way).
 // PEERS = PeerArgs: the sharded data-parallel update (b2k_dp_adam_shard). The rows of this rank's slice are summed from
@@ -404,10 +409,10 @@ struct PeerArgs {
 __device__ __forceinline__ float4 sum4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 
 template <int DEG, class PEERS>
-__global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>::THREADS) adam_kernel(int first, int end, ModelPtrs mp, B2kOptim op, float* __restrict__ grad,
+__global__ void __launch_bounds__(AdamShape<DEG, !std::is_same<PEERS, NoPeers>::value>::THREADS, 1024 / AdamShape<DEG, !std::is_same<PEERS, NoPeers>::value>::THREADS) adam_kernel(int first, int end, ModelPtrs mp, B2kOptim op, float* __restrict__ grad,
                                                                                                        const PEERS peers) {
   constexpr bool SHARD = !std::is_same<PEERS, NoPeers>::value;
-  constexpr int SPLATS = AdamShape<DEG>::SPLATS, THREADS = AdamShape<DEG>::THREADS;
+  constexpr int SPLATS = AdamShape<DEG, SHARD>::SPLATS, THREADS = AdamShape<DEG, SHARD>::THREADS;
   constexpr int K = (DEG + 1) * (DEG + 1), L = 3 * K, PER = 11 + L, QUARTER = (PER + 3) / 4, LPT = (L + 3) / 4;
   __shared__ __align__(16) float s_rows[SPLATS * PER];
   __shared__ float s_sq[4][SPLATS], s_denom[SPLATS], s_denom_old[SPLATS];
@@ -423,13 +428,23 @@ __global__ void __launch_bounds__(AdamShape<DEG>::THREADS, 1024 / AdamShape<DEG>
     if constexpr (SHARD) {
 #pragma unroll
       for (int u = 0; u < BATCH; u++) r[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int p = 0; p < peers.world; p++) {   // fixed order: every rank would form the same sums
-        const float4* g4 = reinterpret_cast<const float4*>(peers.grad[p] + (size_t)base * PER);
-        float4 t[BATCH];
+      // Two ranks' rows per round, so that twice the loads are in flight over the links; the sums are formed in rank
+      // order (every rank would form the same ones).
+      for (int p = 0; p < peers.world; p += 2) {
+        const bool two = p + 1 < peers.world;
+        const float4* ga = reinterpret_cast<const float4*>(peers.grad[p] + (size_t)base * PER);
+        const float4* gb = reinterpret_cast<const float4*>(peers.grad[two ? p + 1 : p] + (size_t)base * PER);
+        float4 ta[BATCH], tb[BATCH];
 #pragma unroll
-        for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) t[u] = __ldcs(g4 + k); }
+        for (int u = 0; u < BATCH; u++) {
+          const int k = threadIdx.x + u * THREADS;
+          if (k < WORDS) { ta[u] = __ldcs(ga + k); tb[u] = two ? __ldcs(gb + k) : make_float4(0.f, 0.f, 0.f, 0.f); }
+        }
 #pragma unroll
-        for (int u = 0; u < BATCH; u++) { const int k = threadIdx.x + u * THREADS; if (k < WORDS) r[u] = sum4(r[u], t[u]); }
+        for (int u = 0; u < BATCH; u++) {
+          const int k = threadIdx.x + u * THREADS;
+          if (k < WORDS) { r[u] = sum4(r[u], ta[u]); if (two) r[u] = sum4(r[u], tb[u]); }
+        }
       }
     } else {
       const float4* g4 = reinterpret_cast<const float4*>(gblock);
@@ -732,7 +747,7 @@ extern "C" int b2k_dp_adam_shard(B2kDp* dp, const B2kModel* m, const B2kOptim* o
   if (st) return st;
   if (count == 0) return B2K_OK;
   const ModelPtrs mp = model_ptrs(m);
-  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D, PeerArgs><<<div_up(count, AdamShape<D>::SPLATS), AdamShape<D>::THREADS, 0, (cudaStream_t)stream>>>(
+  B2K_DISPATCH_DEG(m->degree, (adam_kernel<D, PeerArgs><<<div_up(count, AdamShape<D, true>::SPLATS), AdamShape<D, true>::THREADS, 0, (cudaStream_t)stream>>>(
       first, first + count, mp, *op, pr->grad[dp->rank], pa)));
   return check_launch();
 }

@@ -73,8 +73,7 @@ extern "C" int b2ch_trainer_info(void* h, uint64_t* out8) {
     StepTrainer& tr = *(StepTrainer*)h;
     out8[0] = tr.ctxs[0]->isect_cap; out8[1] = (uint64_t)tr.overflow_redos; out8[2] = tr.h2d_bytes; out8[3] = (uint64_t)tr.model.n;
     out8[4] = (uint64_t)tr.model.adam_t; out8[5] = (uint64_t)tr.ctxs.size(); out8[6] = (uint64_t)tr.views.size(); out8[7] = (uint64_t)tr.ctxs[0]->tile_bits;
-    float ms[3] = {tr.phase_ms[0], tr.phase_ms[1], tr.phase_ms[2]};
-    std::memcpy(out8 + 8, ms, sizeof ms);   // out8[8..9]: the three phase times of the last profiled step as floats
+    std::memcpy(out8 + 8, tr.phase_ms, sizeof tr.phase_ms);   // out8[8..10]: the six phase times of the last profiled step as floats
     tr.h2d_bytes = 0;
   });
 }

@@ -37,8 +37,9 @@ int b2ch_trainer_step(void* trainer, const int32_t* views, int32_t n_views, void
 int b2ch_trainer_read_loss(void* trainer, float* out16, void* stream);
 int b2ch_trainer_set_profile(void* trainer, int32_t on);
 /* out[0] intersection capacity, [1] steps redone after an overflow, [2] host-to-device bytes since the last call, [3] n,
- * [4] Adam step, [5] lanes, [6] views, [7] tile bits; out[8..9] hold three floats: ms of the views, the update and the whole
- * of the last profiled step. out must hold 10 words. */
+ * [4] Adam step, [5] lanes, [6] views, [7] tile bits; out[8..10] hold six floats, ms of the last profiled step: the views,
+ * the update, the whole step, and on several ranks the update's parts (the barrier before the sharded kernel, which also
+ * waits for the slowest rank's views; the kernel; the barrier behind it). out must hold 11 words. */
 int b2ch_trainer_info(void* trainer, uint64_t* out);
 int b2ch_trainer_download(void* trainer, float* pos_op, float* quat, float* lscale, float* sh);
 int b2ch_trainer_reduce_statistics(void* trainer, void* stream);

@@ -216,7 +216,9 @@ void StepTrainer::update(cudaStream_t stream) {
     return;
   }
   check(b2k_dp_barrier(dp_, stream), "b2k_dp_barrier");          // every rank's accumulator is complete
+  if (profile) cuda(cudaEventRecord(mark_[3], stream), "record");
   check(b2k_dp_adam_shard(dp_, &mv, &o, &peers_, stream), "b2k_dp_adam_shard");
+  if (profile) cuda(cudaEventRecord(mark_[4], stream), "record");
   check(b2k_dp_barrier(dp_, stream), "b2k_dp_barrier");          // every replica is written, every accumulator read
   // This rank's accumulator is cleared beside the start of the next step; the first projection backward waits for it.
   cuda(cudaEventRecord(start_evt_, stream), "record");
@@ -250,6 +252,12 @@ void StepTrainer::step(const std::vector<int>& all, cudaStream_t stream, bool fr
     cudaEventElapsedTime(&phase_ms[0], mark_[0], mark_[1]);
     cudaEventElapsedTime(&phase_ms[1], mark_[1], mark_[2]);
     cudaEventElapsedTime(&phase_ms[2], mark_[0], mark_[2]);
+    phase_ms[3] = phase_ms[4] = phase_ms[5] = 0.f;
+    if (!fused && world > 1 && cfg.shard_update) {
+      cudaEventElapsedTime(&phase_ms[3], mark_[1], mark_[3]);
+      cudaEventElapsedTime(&phase_ms[4], mark_[3], mark_[4]);
+      cudaEventElapsedTime(&phase_ms[5], mark_[4], mark_[2]);
+    }
   }
 }
 

@@ -78,7 +78,9 @@ class StepTrainer {
   uint32_t step_no = 0;
   int overflow_redos = 0;
   uint64_t h2d_bytes = 0;
-  float phase_ms[3] = {0.f, 0.f, 0.f};   // views, update, whole step of the last step when `profile` is set
+  // Of the last step when `profile` is set: views, update, whole step; then the update's parts on several ranks: the barrier
+  // before it (which also waits for the slowest rank's views), the sharded kernel, the barrier behind it.
+  float phase_ms[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   bool profile = false;
 
  private:
@@ -96,7 +98,7 @@ class StepTrainer {
   cudaStream_t copy_stream_ = nullptr, clear_stream_ = nullptr;
   std::vector<DevBuf<uint32_t>> stage_;
   std::vector<cudaEvent_t> staged_evt_, free_evt_, lane_done_;
-  cudaEvent_t start_evt_ = nullptr, cleared_evt_ = nullptr, mark_[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t start_evt_ = nullptr, cleared_evt_ = nullptr, mark_[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
   PinnedBuf<uint32_t> h_isect_;
   bool grad_clear_pending_ = false;
 };

@@ -134,11 +134,12 @@ class HostTrainer:
         lib().b2ch_trainer_set_profile(self.h, int(on))
 
     def info(self):
-        out = (C.c_uint64 * 10)()
+        out = (C.c_uint64 * 11)()
         _check(lib().b2ch_trainer_info(self.h, out), "b2ch_trainer_info")
-        ms = np.frombuffer(bytes(out)[64:76], np.float32)
+        ms = np.frombuffer(bytes(out)[64:88], np.float32)
         return dict(isect_cap=int(out[0]), overflow_redos=int(out[1]), h2d_bytes=int(out[2]), n=int(out[3]), adam_t=int(out[4]), lanes=int(out[5]),
-                    views=int(out[6]), tile_bits=int(out[7]), phase_ms=dict(views=float(ms[0]), update=float(ms[1]), step=float(ms[2])))
+                    views=int(out[6]), tile_bits=int(out[7]), phase_ms=dict(views=float(ms[0]), update=float(ms[1]), step=float(ms[2]), update_wait=float(ms[3]), update_kernel=float(ms[4]),
+                                  update_barrier=float(ms[5])))
 
     def download(self):
         K = (self.degree + 1) ** 2
