@@ -66,7 +66,7 @@ class B2kOptim(C.Structure):
                 ("lr_mean", C.c_float), ("lr_rot", C.c_float), ("lr_scale", C.c_float), ("lr_opac", C.c_float), ("lr_dc", C.c_float),
                 ("lr_sh_rest", C.c_float), ("noise_weight", C.c_float), ("noise_clamp", C.c_float), ("seed", C.c_uint32),
                 ("step", C.c_uint32), ("sparse", C.c_int32), ("pos_override", C.c_void_p), ("quat_override", C.c_void_p),
-                ("lscale_override", C.c_void_p), ("grad_out", C.c_void_p)]
+                ("lscale_override", C.c_void_p), ("grad_out", C.c_void_p), ("touched_out", C.c_void_p)]
 
 
 # Every entry point include/b2k.h declares, with its argument types (the symbol-table test walks this list).

@@ -358,6 +358,7 @@ __global__ void __launch_bounds__(OPT_BLOCK) proj_bwd_kernel(int n, ModelPtrs mp
   splat_gradient<DEG>(i, mp.cap, mp.pos_op, mp.quat, mp.lscale, mp.sh_dc, mp.sh_hi, v_splat, vis_flag, tile_count, refine_norm, vis_count, cam, active,
                       (const float4*)op.pos_override, (const float4*)op.quat_override, (const float4*)op.lscale_override, sg, basis);
   if (!sg.any || (isect_total && *isect_total > isect_cap)) return;   // an overflowed view adds nothing (see optim_fused_kernel)
+  if (op.touched_out) atomicOr(op.touched_out + (i >> 5), 1u << (i & 31));
   // Several views of a step may be in flight on different streams and add into the same accumulator: reductions
   // (fire-and-forget RED.ADD at the L2), not read-modify-write.
   float* o = grad + (size_t)i * (11 + K * 3);
@@ -405,6 +406,8 @@ struct PeerArgs {
   const float* grad[B2K_DP_MAX_RANKS];
   float4* pos_op[B2K_DP_MAX_RANKS]; float4* quat[B2K_DP_MAX_RANKS]; float4* lscale[B2K_DP_MAX_RANKS];
   float* sh_dc[B2K_DP_MAX_RANKS]; float* sh_hi[B2K_DP_MAX_RANKS];
+  const uint32_t* touched[B2K_DP_MAX_RANKS];   // per rank: bit i set when its accumulator holds a row for splat i; used when sparse_rows
+  int sparse_rows;
 };
 __device__ __forceinline__ float4 sum4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 
@@ -418,6 +421,7 @@ __global__ void __launch_bounds__(AdamShape<DEG, !std::is_same<PEERS, NoPeers>::
   __shared__ float s_sq[4][SPLATS], s_denom[SPLATS], s_denom_old[SPLATS];
   __shared__ int s_any[4][SPLATS];
   __shared__ float4 s_ls[SPLATS];
+  __shared__ uint32_t s_touch[SHARD ? B2K_DP_MAX_RANKS : 1][SPLATS / 32];
   const int base = first + blockIdx.x * SPLATS;   // first is a multiple of four, which keeps the block 16-byte aligned
   const int rows = end - base < SPLATS ? end - base : SPLATS;
   float* gblock = grad + (size_t)base * PER;
@@ -426,6 +430,21 @@ __global__ void __launch_bounds__(AdamShape<DEG, !std::is_same<PEERS, NoPeers>::
     float4* s4 = reinterpret_cast<float4*>(s_rows);
     float4 r[BATCH];
     if constexpr (SHARD) {
+      // Rows a rank never added to are zero: with the ranks' bitmaps at hand they are not fetched at all (a rank that
+      // rendered 8 of a step's 64 views touches about a third of the splats).
+      constexpr int TW = SPLATS / 32;
+      int row0[BATCH], row1[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; u++) { const int f = (threadIdx.x + u * THREADS) * 4; row0[u] = f / PER; row1[u] = (f + 3) / PER; }
+      if (peers.sparse_rows) {
+        if ((int)threadIdx.x < peers.world * TW) s_touch[threadIdx.x / TW][threadIdx.x % TW] = peers.touched[threadIdx.x / TW][base / 32 + threadIdx.x % TW];
+        __syncthreads();
+      }
+      auto wanted = [&](int p, int u) {
+        if (!peers.sparse_rows) return true;
+        const uint32_t b0 = s_touch[p][row0[u] >> 5] >> (row0[u] & 31), b1 = s_touch[p][row1[u] >> 5] >> (row1[u] & 31);
+        return ((b0 | b1) & 1u) != 0u;
+      };
 #pragma unroll
       for (int u = 0; u < BATCH; u++) r[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       // Two ranks' rows per round, so that twice the loads are in flight over the links; the sums are formed in rank
@@ -438,7 +457,8 @@ __global__ void __launch_bounds__(AdamShape<DEG, !std::is_same<PEERS, NoPeers>::
 #pragma unroll
         for (int u = 0; u < BATCH; u++) {
           const int k = threadIdx.x + u * THREADS;
-          if (k < WORDS) { ta[u] = __ldcs(ga + k); tb[u] = two ? __ldcs(gb + k) : make_float4(0.f, 0.f, 0.f, 0.f); }
+          const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (k < WORDS) { ta[u] = wanted(p, u) ? __ldcs(ga + k) : zero; tb[u] = two && wanted(p + 1, u) ? __ldcs(gb + k) : zero; }
         }
 #pragma unroll
         for (int u = 0; u < BATCH; u++) {
@@ -740,7 +760,10 @@ extern "C" int b2k_dp_adam_shard(B2kDp* dp, const B2kModel* m, const B2kOptim* o
     B2K_REQUIRE(pr->grad[r] && pr->pos_op[r] && pr->quat[r] && pr->lscale[r] && pr->sh_dc[r] && (m->degree == 0 || pr->sh_hi[r]));
     pa.grad[r] = pr->grad[r]; pa.pos_op[r] = (float4*)pr->pos_op[r]; pa.quat[r] = (float4*)pr->quat[r]; pa.lscale[r] = (float4*)pr->lscale[r];
     pa.sh_dc[r] = pr->sh_dc[r]; pa.sh_hi[r] = pr->sh_hi[r];
+    pa.touched[r] = pr->touched[r];
   }
+  pa.sparse_rows = pr->touched[0] != nullptr;
+  for (int r = 0; r < dp->world; r++) B2K_REQUIRE((pr->touched[r] != nullptr) == (pa.sparse_rows != 0));   // all ranks' bitmaps or none
   B2K_REQUIRE(pr->pos_op[dp->rank] == m->pos_op && pr->sh_dc[dp->rank] == m->sh_dc);   // the replica named by `m` is this rank's
   int32_t first = 0, count = 0;
   int st = b2k_dp_slice(m->n, dp->rank, dp->world, &first, &count);

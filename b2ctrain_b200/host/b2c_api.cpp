@@ -324,8 +324,9 @@ void optimizer_step(RenderCtx& ctx, Model& m, const OptimParams& op, cudaStream_
   check(b2k_optim_fused(&cv, &mv, &cam, &o, stream), "optimizer_step");
 }
 
-void projection_backward(RenderCtx& ctx, Model& m, const OptimParams& op, float* grad, cudaStream_t stream) {
-  const B2kCtx cv = view_of(ctx); const B2kModel mv = view_of(m); const B2kCamera cam = camera_of(op.cam); const B2kOptim o = optim_of(op, "projection_backward");
+void projection_backward(RenderCtx& ctx, Model& m, const OptimParams& op, float* grad, cudaStream_t stream, uint32_t* touched) {
+  const B2kCtx cv = view_of(ctx); const B2kModel mv = view_of(m); const B2kCamera cam = camera_of(op.cam); B2kOptim o = optim_of(op, "projection_backward");
+  o.touched_out = touched;
   check(b2k_proj_bwd(&cv, &mv, &cam, &o, grad, stream), "projection_backward");
 }
 

@@ -273,7 +273,8 @@ struct OptimParams {
 };
 void optimizer_step(RenderCtx& ctx, Model& m, const OptimParams& op, cudaStream_t stream);
 // Data-parallel split of optimizer_step: gradient half adding into grad[n][11+3K], update half from it.
-void projection_backward(RenderCtx& ctx, Model& m, const OptimParams& op, float* grad, cudaStream_t stream);
+// touched: optional bitmap of (n + 31) / 32 words in which the splats that received a row are marked (B2kOptim.touched_out).
+void projection_backward(RenderCtx& ctx, Model& m, const OptimParams& op, float* grad, cudaStream_t stream, uint32_t* touched = nullptr);
 void adam_step(Model& m, const OptimParams& op, float* grad, cudaStream_t stream);
 void update_min_scale(Model& m, const float* cam_pos, const float* cam_focal, int n_cams, cudaStream_t stream);
 

@@ -46,7 +46,7 @@ StepTrainer::StepTrainer(const SplatCloud& cloud, int W_, int H_, const StepConf
   cuda(cudaEventCreateWithFlags(&cleared_evt_, cudaEventDisableTiming), "event");
   for (auto& m : mark_) cuda(cudaEventCreate(&m), "event");
   h_isect_.reserve((size_t)lanes);
-  grad.reserve((size_t)std::max(model.n, 1) * (11 + 3 * (size_t)model.K()));
+  grad.reserve(grad_words());
   grad.zero(0);
   cuda(cudaDeviceSynchronize(), "setup");
   if (world > 1) {
@@ -57,8 +57,17 @@ StepTrainer::StepTrainer(const SplatCloud& cloud, int W_, int H_, const StepConf
   refiner.init(model, 0);
 }
 
+// The accumulator [n][11 + 3K], followed by the bitmap of the splats that received a row this step (one allocation, so
+// that the peers reach both through one mapping).
+size_t StepTrainer::grad_words() const {
+  const size_t n = (size_t)std::max(model.n, 1);
+  return n * (11 + 3 * (size_t)model.K()) + (n + 31) / 32;
+}
+uint32_t* StepTrainer::touched() { return reinterpret_cast<uint32_t*>(grad.ptr + (size_t)std::max(model.n, 1) * (11 + 3 * (size_t)model.K())); }
+
 void StepTrainer::share_buffers() {
   check(b2k_dp_share(dp_, grad.ptr, (void**)peers_.grad, 0), "b2k_dp_share(grad)");
+  for (int r = 0; r < world; r++) peers_.touched[r] = reinterpret_cast<const uint32_t*>(peers_.grad[r] + (size_t)std::max(model.n, 1) * (11 + 3 * (size_t)model.K()));
   check(b2k_dp_share(dp_, model.pos_op.ptr, (void**)peers_.pos_op, 0), "b2k_dp_share(pos_op)");
   check(b2k_dp_share(dp_, model.quat.ptr, (void**)peers_.quat, 0), "b2k_dp_share(quat)");
   check(b2k_dp_share(dp_, model.lscale.ptr, (void**)peers_.lscale, 0), "b2k_dp_share(lscale)");
@@ -87,7 +96,7 @@ RefineStats StepTrainer::refine(const RefineParams& p, cudaStream_t stream) {
   if (model.n != n_before || model.pos_op.ptr != before[0] || model.sh_hi32.ptr != before[1]) {
     cuda(cudaStreamSynchronize(stream), "sync");
     grad.free();
-    grad.reserve((size_t)std::max(model.n, 1) * (11 + 3 * (size_t)model.K()));
+    grad.reserve(grad_words());
   }
   grad.zero(stream);
   cuda(cudaStreamSynchronize(stream), "sync");
@@ -171,7 +180,7 @@ void StepTrainer::view_pass(int lane, int view, int slot, cudaStream_t s, bool f
   const OptimParams op = optim_params(rp.cam);
   if (fused) { optimizer_step(ctx, model, op, s); return; }
   if (first_of_lane && grad_clear_pending_) cuda(cudaStreamWaitEvent(s, cleared_evt_, 0), "wait");   // the accumulator of the last step has been cleared
-  projection_backward(ctx, model, op, grad.ptr, s);
+  projection_backward(ctx, model, op, grad.ptr, s, world > 1 && cfg.shard_update ? touched() : nullptr);
 }
 
 void StepTrainer::run_views(const std::vector<int>& mine, cudaStream_t stream, bool from_host, bool fused) {

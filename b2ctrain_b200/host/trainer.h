@@ -92,6 +92,8 @@ class StepTrainer {
   const uint32_t* target(int view, int slot, cudaStream_t s, bool from_host);
 
   void share_buffers();
+  size_t grad_words() const;
+  uint32_t* touched();
   B2kDp* dp_ = nullptr;
   B2kDpPeers peers_{};
   std::vector<cudaStream_t> streams_;

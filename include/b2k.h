@@ -142,6 +142,9 @@ typedef struct {
   const float* quat_override;
   const float* lscale_override;
   float* grad_out;         /* [n][11+3K]: write parameter gradients and skip the update (optim.h:44) */
+  uint32_t* touched_out;   /* NULL, or a bitmap of (n + 31) / 32 words beside the accumulator of b2k_proj_bwd: bit i is set when a
+                              row is added for splat i, so that a reader can skip the rows that are still zero (no counterpart
+                              in the reference) */
 } B2kOptim;
 
 /* ---- forward ---- */
@@ -335,6 +338,9 @@ typedef struct {
   float* lscale[B2K_DP_MAX_RANKS];
   float* sh_dc[B2K_DP_MAX_RANKS];
   float* sh_hi[B2K_DP_MAX_RANKS];
+  const uint32_t* touched[B2K_DP_MAX_RANKS]; /* all NULL: every row of every accumulator is fetched. Else each rank's bitmap
+                                                (B2kOptim.touched_out of its b2k_proj_bwd calls): rows whose bit is clear
+                                                are zero and are not fetched over the links */
 } B2kDpPeers;
 /* Reduce-scatter + Adam + all-gather of the data-parallel step as ONE kernel over peer memory: this rank sums the rows
  * of its slice (b2k_dp_slice) from every rank's accumulator with plain peer loads, runs the update of b2k_adam on them
