@@ -454,6 +454,7 @@ class OptimParams:
         self.frozen = False
         self.sparse = False
         self.grad_out = None
+        self.touched_out = None   # bitmap of (n + 31) // 32 words: projection_backward marks the splats it adds a row for
         for k in self._UNSUPPORTED:
             setattr(self, k, None)
         for k, v in kw.items():
@@ -471,6 +472,7 @@ class OptimParams:
         s.sparse = int(bool(self.sparse))
         s.pos_override, s.quat_override, s.lscale_override = _ptr(self.pos_override), _ptr(self.quat_override), _ptr(self.lscale_override)
         s.grad_out = _ptr(self.grad_out)
+        s.touched_out = _ptr(self.touched_out)
         return s
 
     def camera(self):

@@ -109,6 +109,17 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
   }
   __syncthreads();
 
+  // What does not change from step to step: the input elements a C / D thread fetches, and which columns are inside.
+  int st_row[3], st_x[3];
+  bool st_ok[3];
+#pragma unroll
+  for (int k = 0; k < 3; k++) {
+    const int e = tid - 192 + k * 128;
+    st_row[k] = e / STRIP_IN;
+    const int col = e - st_row[k] * STRIP_IN;
+    st_x[k] = x0 - 2 * HALO + col;
+    st_ok[k] = tid >= 192 && e < STRIP_ROWS * STRIP_IN && col < STRIP_W + 4 * HALO && st_x[k] >= 0 && st_x[k] < W;
+  }
   float loss_local = 0.f;
   const int steps = 8 + (y1 - y0 + STRIP_ROWS - 1) / STRIP_ROWS;
   for (int it = 0; it < steps; it++) {
@@ -154,11 +165,12 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
           st[m][0] = o0; st[m][1] = o1;
         }
         const int xg = x0 - HALO + col;
+        const bool x_in = xg >= 0 && xg < W, x_own = xg >= x0 && xg < x_end;
 #pragma unroll
         for (int o = 0; o < 2; o++) {
           const int y = b + r2 + o;
           float E0 = 0.f, E1 = 0.f, E2 = 0.f;
-          if (y >= 0 && y < H && xg >= 0 && xg < W) {
+          if (x_in && y >= 0 && y < H) {
             const size_t q = (size_t)y * W + xg;
             const float wp = weights ? (float)weights[q] * (1.f / 255.f) : 1.f;
             const float M = wp * (lp.mask ? unpack(gt[q], 3) : 1.f) * norm;
@@ -171,7 +183,7 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
             const float inv_BB = __fdividef(1.f, B1 * B2);   // approximate divisions, as in the reference's fast-math build
             const float raw = A1 * A2 * inv_BB;
             const float ssim = fminf(fmaxf(raw, -1.f), 1.f);
-            if (y >= y0 && y < y1 && xg >= x0 && xg < x_end) loss_local += M * lp.ssim_w * ssim;
+            if (x_own && y >= y0 && y < y1) loss_local += M * lp.ssim_w * ssim;
             if (raw > -1.f && raw < 1.f) {
               const float k = M * lp.ssim_w;
               const float d_mu1 = 2.f * mu2 * A2 * inv_BB - __fdividef(2.f * mu1 * ssim, B1);
@@ -194,9 +206,14 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
       const bool more = a + STRIP_ROWS <= y1 - 1 + 2 * HALO;
 #pragma unroll
       for (int k = 0; k < 3; k++) {
-        const int e = t + k * 128;
+        const int y = a + STRIP_ROWS + st_row[k];
         nx[k] = 0.f; ny[k] = 0.f;
-        if (more && e < STRIP_ROWS * STRIP_IN) fetch(a + STRIP_ROWS, e, nx[k], ny[k]);
+        if (more && st_ok[k] && y >= 0 && y < H) {
+          const size_t q = (size_t)y * W + st_x[k];
+          const uint32_t gp = gt[q];
+          nx[k] = pred_c[q * 4];
+          ny[k] = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
+        }
       }
       if (warp < 8) {
         // C: rows cr .. cr+3 of the three derivative maps blurred down the column, one column per thread.

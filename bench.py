@@ -492,7 +492,9 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
            "render_chunked": (48 * n + 12 * K * V + 64 * n) + 16 * n * 4 + 20 * n + (8 + 16 * passes + 4) * Is + 8 * tiles * max(chunks, 1) + 52 * Ib + 36 * P,
            "loss": 20 * P + 16 * P, "raster_bwd": 28 * P + 52 * Ib + 52 * touched,
            "proj_bwd": (52 + 48 + 12 * K) * touched + 2 * 4 * (11 + 3 * K) * touched + 8 * n}   # flags of all splats, records of the touched ones
-    flop = {"raster_fwd": 24 * F, "render_chunked": 24 * F, "raster_bwd": 90 * F}
+    # Loss: per pixel and channel 64/54 x (5 + 5 + 3) + 3 eleven-tap blurs (the strip's horizontal halo) = 203 FMA, plus the
+    # moment products and the SSIM expression (~60 flop).
+    flop = {"raster_fwd": 24 * F, "render_chunked": 24 * F, "raster_bwd": 90 * F, "loss": 3 * P * (2 * 203 + 60)}
     stages = {nm: {"ms": acc[nm] / nv, "algorithmic_bytes": int(alg[nm]), "achieved_gbs": alg[nm] / (acc[nm] / nv * 1e-3) / 1e9} for nm in names}
     if chunks <= 1:   # kernel-level split of the binning stage (events inside the library)
         ph = np.zeros(10)
@@ -528,14 +530,18 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
         stage = [k for k, v in kernel_of.items() if v == top][0]
         bytes_launch, traffic, note = alg[stage], None, "one launch per view"
         if top == "raster_bwd_kernel":
-            traffic = int(72.5 * Ib)   # dram read + write per launch from an ncu capture at half the splat count (90.1 MB at I_b = 1,243,915), scaled by fragments
+            traffic = int(80.7 * Ib)   # dram read + write per launch from an ncu capture at half the splat count (100.3 MB at I_b = 1,243,915), scaled by fragments
+        elif top == "photometric_strip_kernel":
+            traffic = int(22.7 * P)    # ncu capture of one 1920x1080 view: 43.1 MB read + 4.0 MB written (the gradient image stays in L2)
     a = bytes_launch / (per_launch_ms * 1e-3) / 1e9
     hbm_view = {"achieved": a, "peak": hbm, "unit": "GB/s", "frac": a / hbm, "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_launch": int(bytes_launch)}
     if stage in flop:   # the compositing kernels are bound by FP32 issue: that roof is the headline, the HBM figure rides beside it
         f = flop[stage] / (per_launch_ms * 1e-3)
         roof = {"bound": "fp32", "kernel": top, "achieved": f / 1e12, "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": f / fp32_peak, "traffic": traffic,
                 "peak_source": "2 x 128 lanes x SMs x the SM clock sampled in the timed region (no tensor pipe on this path)",
-                "flop_per_launch": flop[stage], "fragment_pixel_evaluations": F, "hbm": hbm_view}
+                "flop_per_launch": flop[stage], "hbm": hbm_view}
+        if stage != "loss":
+            roof["fragment_pixel_evaluations"] = F
     else:
         roof = {"bound": "hbm", "kernel": top, **hbm_view}
     roof.update({"ms_per_launch": per_launch_ms, "note": note, "kernel_ms_per_view": {k: float(v) for k, v in kernel_ms.items()}})

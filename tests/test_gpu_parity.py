@@ -265,7 +265,13 @@ def test_adam_fused_and_split_match_oracle():
             op = h.api.OptimParams(cam, active_sh_degree=2, t=t, lr_mean=1.6e-4, sparse=True)
             if split:
                 g = h.torch.zeros((n, 11 + 3 * K), dtype=h.torch.float32, device="cuda:0")
+                op.touched_out = h.torch.zeros(((n + 31) // 32,), dtype=h.torch.int32, device="cuda:0")
                 h.api.projection_backward(h.ctx, h.model, op, g)
+                # the bitmap the sharded data-parallel update reads: every row that holds something is marked, nothing else
+                # but splats whose gradient came out as exact zeros
+                rows = (g != 0).any(dim=1).cpu().numpy()
+                bits = np.unpackbits(op.touched_out.cpu().numpy().view(np.uint8), bitorder="little")[:n].astype(bool)
+                assert np.all(bits[rows]) and bits.sum() <= rows.sum() + 8 and bits.sum() > 0
                 h.api.adam_step(h.model, op, g)
                 assert float(g.abs().max()) == 0.0
             else:
