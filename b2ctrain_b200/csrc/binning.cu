@@ -509,29 +509,17 @@ __device__ __forceinline__ uint32_t box_alive(const uint32_t* __restrict__ sat, 
   return sat[(size_t)y1 * SX + x1] - sat[(size_t)y0 * SX + x1] - sat[(size_t)y1 * SX + x0] + sat[(size_t)y0 * SX + x0];
 }
 
-// Hit mask of a splat whose tile box holds at most 64 tiles: bit (row * width + col) set when the ellipse reaches the tile.
-__device__ __forceinline__ unsigned long long box_hit_mask(const TileRec& rec, int min_x, int min_y, int bw, int bh) {
+// Hit mask of a splat whose tile box holds at most 64 tiles: bit (row * width + col) set when the ellipse reaches the
+// tile and the tile is still alive (alive == nullptr: every tile is). The flag is looked at first: in the later depth
+// chunks most tiles of a box are dead, and the ellipse test is the expensive half.
+__device__ __forceinline__ unsigned long long box_hit_mask(const TileRec& rec, int min_x, int min_y, int bw, int bh, const uint32_t* __restrict__ alive,
+                                                           int tiles_x) {
   unsigned long long m = 0ull;
   int bit = 0;
   for (int ty = min_y; ty < min_y + bh; ty++)
     for (int tx = min_x; tx < min_x + bw; tx++, bit++)
-      if (tile_hit(tx, ty, rec)) m |= 1ull << bit;
+      if ((!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec)) m |= 1ull << bit;
   return m;
-}
-
-// The hits of a mask that fall on live tiles (alive == nullptr: all of them).
-__device__ __forceinline__ unsigned long long alive_mask(unsigned long long bits, uint32_t bw, uint32_t min_x, uint32_t min_y,
-                                                         const uint32_t* __restrict__ alive, int tiles_x) {
-  if (!alive) return bits;
-  const uint32_t inv_bw = bw ? (65536u + bw - 1u) / bw : 0u;
-  unsigned long long keep = 0ull;
-  while (bits != 0ull) {
-    const uint32_t bit = (uint32_t)__ffsll((long long)bits) - 1u;
-    bits &= bits - 1ull;
-    const uint32_t row = (bit * inv_bw) >> 16, col = bit - row * bw;
-    if (alive[(min_y + row) * (uint32_t)tiles_x + min_x + col] != 0u) keep |= 1ull << bit;
-  }
-  return keep;
 }
 
 // First step of a chunk's count, one thread per rank: a splat whose tile box is empty, or holds no live tile (four
@@ -545,27 +533,40 @@ __global__ void __launch_bounds__(256) chunk_filter_kernel(const uint32_t* __res
   chunk_ranks(words, lo_num, hi_num, r0, r1);
   const int lane = threadIdx.x & 31;
   const uint32_t span = (r1 - r0 + 31u) & ~31u;   // whole warps, so the votes below are convergent
-  for (uint32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < span; q += gridDim.x * blockDim.x) {
-    const uint32_t r = r0 + q;
-    int kind = 0;   // 0 emits nothing, 1 masked box, 2 big box
-    if (r < r1) {
-      const uint4 hi = hit_info[order[r]];
-      if (hi.w != 0u) {
+  const uint32_t T = gridDim.x * blockDim.x;
+  constexpr int U = 4;   // ranks per thread and round: three dependent loads each (rank -> splat -> box -> table), kept in flight together
+  for (uint32_t q = blockIdx.x * blockDim.x + threadIdx.x; q < span; q += U * T) {
+    uint32_t idx[U];
+    uint4 hi[U];
+    int kind[U];   // 0 emits nothing, 1 masked box, 2 big box
+#pragma unroll
+    for (int u = 0; u < U; u++) { const uint32_t r = r0 + q + u * T; idx[u] = r < r1 ? order[r] : 0xFFFFFFFFu; }
+#pragma unroll
+    for (int u = 0; u < U; u++) hi[u] = idx[u] != 0xFFFFFFFFu ? hit_info[idx[u]] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      kind[u] = 0;
+      if (hi[u].w != 0u) {
         int x0, y0, x1, y1;
-        if (hi.z == 0xFFFFFFFFu) { x0 = (int)(hi.x & 0xFFFFu); y0 = (int)(hi.x >> 16); x1 = x0 + (int)(hi.y & 0xFFFFu); y1 = y0 + (int)(hi.y >> 16); kind = 2; }
-        else { x0 = (int)(hi.z & 0xFFFu); y0 = (int)((hi.z >> 12) & 0xFFFu); x1 = x0 + (int)(hi.z >> 24); y1 = y0 + (int)hi.w; kind = 1; }
-        if (sat && box_alive(sat, tiles_x + 1, x0, y0, x1, y1) == 0u) kind = 0;
+        if (hi[u].z == 0xFFFFFFFFu) { x0 = (int)(hi[u].x & 0xFFFFu); y0 = (int)(hi[u].x >> 16); x1 = x0 + (int)(hi[u].y & 0xFFFFu); y1 = y0 + (int)(hi[u].y >> 16); kind[u] = 2; }
+        else { x0 = (int)(hi[u].z & 0xFFFu); y0 = (int)((hi[u].z >> 12) & 0xFFFu); x1 = x0 + (int)(hi[u].z >> 24); y1 = y0 + (int)hi[u].w; kind[u] = 1; }
+        if (sat && box_alive(sat, tiles_x + 1, x0, y0, x1, y1) == 0u) kind[u] = 0;
       }
-      if (kind == 0) fcount[r] = 0u;
     }
 #pragma unroll
-    for (int k = 1; k <= 2; k++) {   // one atomic per warp and list
-      const uint32_t m = __ballot_sync(0xffffffffu, kind == k);
-      if (m) {
-        uint32_t base = 0;
-        if (lane == __ffs(m) - 1) base = atomicAdd(counts + (k - 1), (uint32_t)__popc(m));
-        base = __shfl_sync(0xffffffffu, base, __ffs(m) - 1);
-        if (kind == k) (k == 1 ? live_list : big_list)[base + __popc(m & ((1u << lane) - 1u))] = r;
+    for (int u = 0; u < U; u++) {
+      if (q + u * T >= span) break;   // warp-uniform: q + u * T and span are whole warps apart
+      const uint32_t r = r0 + q + u * T;
+      if (r < r1 && kind[u] == 0) fcount[r] = 0u;
+#pragma unroll
+      for (int k = 1; k <= 2; k++) {   // one atomic per warp and list
+        const uint32_t m = __ballot_sync(0xffffffffu, kind[u] == k);
+        if (m) {
+          uint32_t base = 0;
+          if (lane == __ffs(m) - 1) base = atomicAdd(counts + (k - 1), (uint32_t)__popc(m));
+          base = __shfl_sync(0xffffffffu, base, __ffs(m) - 1);
+          if (kind[u] == k) (k == 1 ? live_list : big_list)[base + __popc(m & ((1u << lane) - 1u))] = r;
+        }
       }
     }
   }
@@ -585,7 +586,7 @@ __global__ void __launch_bounds__(256) chunk_mask_kernel(const uint32_t* __restr
     const float4 a = proj0[i], b = proj1[i];
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
     // The mask kept for the emission holds the hits on live tiles only: the emission then needs no flag lookups.
-    const unsigned long long m = alive_mask(box_hit_mask(rec, (int)min_x, (int)min_y, (int)bw, (int)bh), bw, min_x, min_y, alive, tiles_x);
+    const unsigned long long m = box_hit_mask(rec, (int)min_x, (int)min_y, (int)bw, (int)bh, alive, tiles_x);
     const uint32_t f = (uint32_t)__popcll(m);
     if (f) hit_info[i] = make_uint4((uint32_t)m, (uint32_t)(m >> 32), hi.z, hi.w);
     fcount[r] = f;
