@@ -127,6 +127,7 @@ SIGNATURES = {
     "b2k_select_flagged": (C.c_int, [_P, C.c_int32, _P, _P, _P, _S]),
     "b2k_gather_lanes": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_uint64, C.c_int32, _S]),
     "b2k_pack_rgba8": (C.c_int, [_P, _P, C.c_int32, C.c_int32, _S]),
+    "b2k_quantize_rgba8": (C.c_int, [_P, _P, C.c_int32, _S]),
     "b2k_error_string": (C.c_char_p, [C.c_int]),
     "b2k_last_cuda_error": (C.c_int, []),
     "b2k_version": (C.c_char_p, []),

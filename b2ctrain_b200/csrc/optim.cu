@@ -787,6 +787,27 @@ extern "C" int b2k_min_scale(const B2kModel* m, const float* cam_pos, const floa
   return check_launch();
 }
 
+// The renderer's 8-bit output (src/render/renderer.cpp:353-358 does it on the host after a float download): every channel
+// clamped to [0, 1], scaled by 255 and rounded half away from zero, as lround does; no premultiplied clamp.
+__global__ void quantize_rgba8_kernel(int n, const float4* __restrict__ img, uint32_t* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 v = img[i];
+  auto q = [](float x) {
+    const float p = __fmul_rn(fminf(fmaxf(x, 0.f), 1.f), 255.f);   // the product rounded once, then the exact half test
+    const float r = truncf(p);
+    return (uint32_t)r + (p - r >= 0.5f ? 1u : 0u);
+  };
+  out[i] = q(v.x) | (q(v.y) << 8) | (q(v.z) << 16) | (q(v.w) << 24);
+}
+
+extern "C" int b2k_quantize_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, b2k_stream_t stream) {
+  B2K_REQUIRE(n_pixels >= 0 && (n_pixels == 0 || (rgba && out)));
+  if (n_pixels == 0) return B2K_OK;
+  quantize_rgba8_kernel<<<div_up(n_pixels, 256), 256, 0, (cudaStream_t)stream>>>(n_pixels, (const float4*)rgba, out);
+  return check_launch();
+}
+
 extern "C" int b2k_pack_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, int32_t alpha_override, b2k_stream_t stream) {
   B2K_REQUIRE(rgba && out && n_pixels >= 0 && alpha_override <= 255);
   if (n_pixels == 0) return B2K_OK;

@@ -99,6 +99,47 @@ extern "C" uint64_t b2ch_trainer_checksum(void* h, void* stream) {
 }
 
 // ---- files: splat PLY and the headless render front end ----
+static SplatCloud cloud_of(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh) {
+  if (n < 0 || (n > 0 && (!pos_op || !quat || !lscale || !sh))) throw std::runtime_error("bad splat arrays");
+  SplatCloud c; c.resize((size_t)n, degree); c.floor.assign((size_t)n, 0.f);
+  const int K = c.K();
+  for (int i = 0; i < n; i++) {
+    for (int k = 0; k < 3; k++) { c.pos[i * 3 + k] = pos_op[i * 4 + k]; c.log_scale[i * 3 + k] = lscale[i * 4 + k]; }
+    c.opacity[i] = pos_op[i * 4 + 3]; c.floor[i] = lscale[i * 4 + 3];
+    for (int k = 0; k < 4; k++) c.quat[i * 4 + k] = quat[i * 4 + k];
+  }
+  std::memcpy(c.sh.data(), sh, (size_t)n * K * 3 * sizeof(float));
+  return c;
+}
+
+extern "C" void* b2ch_renderer_create(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, int32_t W, int32_t H,
+                                      int32_t depth, int32_t render_chunks) {
+  StreamRenderer* r = nullptr;
+  const int st = guarded([&] { r = new StreamRenderer(cloud_of(n, degree, pos_op, quat, lscale, sh), W, H, depth != 0, render_chunks); });
+  return st ? nullptr : r;
+}
+
+extern "C" void b2ch_renderer_destroy(void* h) { delete (StreamRenderer*)h; }
+
+extern "C" int b2ch_renderer_render(void* h, const B2kCamera* cam, const float* background, int32_t sh_degree, uint32_t* host_rgba8, float* host_depth, void* stream) {
+  return guarded([&] {
+    Camera c; c.width = cam->W; c.height = cam->H; c.fx = cam->fx; c.fy = cam->fy; c.cx = cam->cx; c.cy = cam->cy;
+    for (int i = 0; i < 9; i++) c.R[i] = cam->R[i];
+    for (int i = 0; i < 3; i++) { c.t[i] = cam->t[i]; c.pos[i] = cam->pos[i]; }
+    ((StreamRenderer*)h)->render(c, background, sh_degree, host_rgba8, host_depth, (cudaStream_t)stream);
+  });
+}
+
+extern "C" int b2ch_renderer_finish(void* h) { return guarded([&] { ((StreamRenderer*)h)->finish(); }); }
+
+extern "C" int b2ch_renderer_info(void* h, uint64_t* out4) {
+  return guarded([&] {
+    StreamRenderer& r = *(StreamRenderer*)h;
+    out4[0] = r.ctx.num_isect; out4[1] = r.ctx.isect_cap; out4[2] = r.d2h_bytes; out4[3] = (uint64_t)r.ctx.tile_bits;
+    r.d2h_bytes = 0;
+  });
+}
+
 extern "C" int b2ch_render_headless(const char* splat, const char* cameras, const char* output_dir, const float* background, int32_t sh_degree, int32_t depth,
                                     int32_t render_chunks, int32_t rank, int32_t world, int32_t* rendered) {
   return guarded([&] {

@@ -70,6 +70,53 @@ void write_cameras_json(const std::string& path, const CameraList& list) {
   f << "\n]}\n";
 }
 
+StreamRenderer::StreamRenderer(const SplatCloud& cloud, int W_, int H_, bool depth, int render_chunks) : W(W_), H(H_) {
+  model.upload(cloud, 0);
+  ctx.want_depth = depth;
+  ctx.n_chunks = render_chunks > 1 ? render_chunks : 1;
+  ctx.setup(W, H, model.cap, 0);
+  B2C_CUDA_CHECK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
+  for (int k = 0; k < 2; k++) {
+    B2C_CUDA_CHECK(cudaEventCreateWithFlags(&ready_[k], cudaEventDisableTiming));
+    B2C_CUDA_CHECK(cudaEventCreateWithFlags(&free_[k], cudaEventDisableTiming));
+  }
+  B2C_CUDA_CHECK(cudaDeviceSynchronize());
+}
+
+StreamRenderer::~StreamRenderer() {
+  cudaDeviceSynchronize();
+  for (int k = 0; k < 2; k++) { if (ready_[k]) cudaEventDestroy(ready_[k]); if (free_[k]) cudaEventDestroy(free_[k]); }
+  if (copy_stream_) cudaStreamDestroy(copy_stream_);
+}
+
+void StreamRenderer::render(const Camera& cam, const float bg[3], int sh_degree, uint32_t* host_rgba8, float* host_depth, cudaStream_t stream) {
+  RenderParams p; p.cam = CameraGPU::from(cam, W, H);
+  for (int k = 0; k < 3; k++) p.bg[k] = bg ? bg[k] : 0.f;
+  p.sh_degree = sh_degree >= 0 ? std::min(sh_degree, model.degree) : model.degree; p.bwd_info = false;
+  render_forward(ctx, model, p, stream);
+  if (!host_rgba8 && !host_depth) return;
+  if (host_depth && !ctx.want_depth) throw std::runtime_error("StreamRenderer: depth was not asked for at construction");
+  const size_t P = (size_t)W * H;
+  const int k = slot_; slot_ ^= 1;
+  if (used_[k]) B2C_CUDA_CHECK(cudaStreamWaitEvent(stream, free_[k], 0));   // the copies that read this slot last have run
+  if (host_rgba8) {
+    stage_rgba_[k].reserve(P);
+    abi::check(b2k_quantize_rgba8((const float*)ctx.out_rgba.ptr, stage_rgba_[k].ptr, (int32_t)P, stream), "b2k_quantize_rgba8");
+  }
+  if (host_depth) {
+    stage_depth_[k].reserve(P);
+    B2C_CUDA_CHECK(cudaMemcpyAsync(stage_depth_[k].ptr, ctx.out_depth.ptr, P * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  }
+  B2C_CUDA_CHECK(cudaEventRecord(ready_[k], stream));
+  B2C_CUDA_CHECK(cudaStreamWaitEvent(copy_stream_, ready_[k], 0));
+  if (host_rgba8) { B2C_CUDA_CHECK(cudaMemcpyAsync(host_rgba8, stage_rgba_[k].ptr, P * sizeof(uint32_t), cudaMemcpyDeviceToHost, copy_stream_)); d2h_bytes += P * 4; }
+  if (host_depth) { B2C_CUDA_CHECK(cudaMemcpyAsync(host_depth, stage_depth_[k].ptr, P * sizeof(float), cudaMemcpyDeviceToHost, copy_stream_)); d2h_bytes += P * 4; }
+  B2C_CUDA_CHECK(cudaEventRecord(free_[k], copy_stream_));
+  used_[k] = true;
+}
+
+void StreamRenderer::finish() { B2C_CUDA_CHECK(cudaStreamSynchronize(copy_stream_)); }
+
 static unsigned char to_u8(float v) { return (unsigned char)std::lround(std::min(std::max(v, 0.f), 1.f) * 255.f); }
 
 int render_headless(const std::string& splat_path, const std::string& cameras_path, const std::string& output_dir, const HeadlessOptions& opt) {

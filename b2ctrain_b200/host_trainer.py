@@ -36,6 +36,11 @@ SIGNATURES = {
     "b2ch_trainer_checksum": (C.c_uint64, [_P, _P]),
     "b2ch_trainer_refine": (C.c_int, [_P, _P, _P, C.c_int32, _P, _P, _P, _P]),
     "b2ch_refine_once": (C.c_int, [C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P, _P, _P, _P, _P]),
+    "b2ch_renderer_create": (_P, [C.c_int32, C.c_int32, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "b2ch_renderer_destroy": (None, [_P]),
+    "b2ch_renderer_render": (C.c_int, [_P, _P, _P, C.c_int32, _P, _P, _P]),
+    "b2ch_renderer_finish": (C.c_int, [_P]),
+    "b2ch_renderer_info": (C.c_int, [_P, _P]),
     "b2ch_render_headless": (C.c_int, [C.c_char_p, C.c_char_p, C.c_char_p, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P]),
     "b2ch_ply_read": (C.c_int, [C.c_char_p, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "b2ch_ply_write": (C.c_int, [C.c_char_p, C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_char_p]),
@@ -199,6 +204,42 @@ def cloud_from_scene(scene):
     """The SplatCloud-style dict of a scene dict of b2ctrain_b200.scenes (the floor lane is not part of the file format)."""
     return dict(n=scene["n"], degree=scene["degree"], pos=scene["pos_op"][:, :3], log_scale=scene["lscale"][:, :3], quat=scene["quat"],
                 opacity=scene["pos_op"][:, 3], sh=scene["sh"])
+
+
+class HostRenderer:
+    """b2c::StreamRenderer: many cameras of one model; the 8-bit image and the depth map of a camera are copied to (pinned)
+    host arrays on a second stream while the next camera renders."""
+
+    def __init__(self, scene, W, H, depth=True, render_chunks=1):
+        f = lambda a: np.ascontiguousarray(a, np.float32)
+        self._keep = [f(scene["pos_op"]), f(scene["quat"]), f(scene["lscale"]), f(scene["sh"])]
+        p = [a.ctypes.data_as(C.c_void_p) for a in self._keep]
+        self.W, self.H = W, H
+        self.h = lib().b2ch_renderer_create(int(scene["n"]), int(scene["degree"]), p[0], p[1], p[2], p[3], int(W), int(H), int(depth), int(render_chunks))
+        if not self.h:
+            raise RuntimeError("b2ch_renderer_create: " + lib().b2ch_last_error().decode())
+        self.h = C.c_void_p(self.h)
+
+    def close(self):
+        if self.h:
+            lib().b2ch_renderer_destroy(self.h)
+            self.h = None
+
+    def render(self, cam, stream, background=None, sh_degree=-1, host_rgba8=None, host_depth=None):
+        """host_rgba8 / host_depth: data pointers (ints) of pinned host buffers of W * H words, or None."""
+        from .api import camera_from
+        cs = cam if not isinstance(cam, dict) else camera_from(cam)
+        bg = (C.c_float * 3)(*background) if background is not None else None
+        _check(lib().b2ch_renderer_render(self.h, C.byref(cs), bg, int(sh_degree), C.c_void_p(host_rgba8) if host_rgba8 else None,
+                                          C.c_void_p(host_depth) if host_depth else None, C.c_void_p(int(stream))), "b2ch_renderer_render")
+
+    def finish(self):
+        _check(lib().b2ch_renderer_finish(self.h), "b2ch_renderer_finish")
+
+    def info(self):
+        out = (C.c_uint64 * 4)()
+        _check(lib().b2ch_renderer_info(self.h, out), "b2ch_renderer_info")
+        return dict(num_isect=int(out[0]), isect_cap=int(out[1]), d2h_bytes=int(out[2]), tile_bits=int(out[3]))
 
 
 def render_headless(splat, cameras, output_dir, background=(0.0, 0.0, 0.0), sh_degree=-1, depth=False, render_chunks=1, rank=0, world=1):

@@ -364,6 +364,9 @@ int b2k_gather_lanes(const void* src, void* dst, const uint32_t* idx, int32_t co
                      b2k_stream_t s);
 /* pack_kernel, src/train/teacher.cu:11-17: float RGBA -> packed RGBA8 target. alpha_override < 0 keeps the image's. */
 int b2k_pack_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, int32_t alpha_override, b2k_stream_t s);
+/* The 8-bit image the render front end writes (src/render/renderer.cpp:353-358: lround(clamp(x, 0, 1) * 255) per channel,
+ * there on the host after downloading floats), on the device so that a quarter of the bytes cross to the host. */
+int b2k_quantize_rgba8(const float* rgba, uint32_t* out, int32_t n_pixels, b2k_stream_t s);
 
 const char* b2k_error_string(int status);
 int b2k_last_cuda_error(void);

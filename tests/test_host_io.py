@@ -110,3 +110,40 @@ def test_headless_render_writes_what_the_operators_render(tmp_path):
         assert np.array_equal(np.isfinite(depth), fin)
         off = np.abs(depth[fin] - ref[fin]) > 2e-4 * np.abs(ref[fin])   # a ratio of two sums under the same ulp-level camera difference;
         assert off.mean() <= 1e-3                                      # a pixel where a fragment sits on the 1/255 cut may move further
+
+
+@pytest.mark.gpu
+def test_stream_renderer_reads_back_quantised_images_and_depth():
+    """b2c::StreamRenderer (device-side quantisation, read-back overlapped with the next camera) against render_forward of
+    the operator mirror quantised with numpy: the same bytes up to the ulp-level camera difference described above, for a
+    run of cameras that reuses the two staging slots, whole-view and chunked."""
+    import torch
+    from b2ctrain_b200 import api
+    scene = scenes.make_splats(5000, 2, 21)
+    W, H = 112, 80
+    cams = [scenes.look_at_camera(scenes.orbit_eye(3.0, a, 10.0), W, H, 70.0) for a in (0.0, 45.0, 130.0, 220.0, 300.0)]
+    m = api.Model("cuda:0").upload(scene)
+    ctx = api.RenderCtx("cuda:0"); ctx.want_depth = True
+    ctx.setup(W, H, m.cap)
+    stream = torch.cuda.current_stream().cuda_stream
+    for chunks in (1, 3):
+        hr = ht.HostRenderer(scene, W, H, depth=True, render_chunks=chunks)
+        rgba = [torch.zeros(W * H, dtype=torch.int32).pin_memory() for _ in cams]
+        depth = [torch.zeros(W * H, dtype=torch.float32).pin_memory() for _ in cams]
+        for i, cam in enumerate(cams):
+            hr.render(cam, stream, background=(0.2, 0.1, 0.3), host_rgba8=rgba[i].data_ptr(), host_depth=depth[i].data_ptr())
+        hr.finish()
+        assert hr.info()["d2h_bytes"] == len(cams) * W * H * 8
+        hr.close()
+        for i, cam in enumerate(cams):
+            api.render_forward(ctx, m, api.RenderParams(cam, bg=(0.2, 0.1, 0.3), sh_degree=2, bwd_info=False))
+            scaled = (np.clip(ctx.out_rgba.cpu().numpy(), 0, 1) * np.float32(255)).astype(np.float64)
+            want = np.floor(scaled + 0.5).astype(np.uint8)
+            got = rgba[i].numpy().view(np.uint8).reshape(-1, 4)
+            diff = np.abs(got.astype(int) - want.astype(int))
+            assert diff.max() <= 1 and np.mean(diff > 0) <= 1e-3, (chunks, i, diff.max(), np.mean(diff > 0))
+            ref = ctx.out_depth.cpu().numpy()
+            fin = np.isfinite(ref)
+            d = depth[i].numpy()
+            assert np.array_equal(np.isfinite(d), fin)
+            assert (np.abs(d[fin] - ref[fin]) > 2e-4 * np.abs(ref[fin])).mean() <= 1e-3
