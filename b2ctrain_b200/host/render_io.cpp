@@ -117,47 +117,44 @@ void StreamRenderer::render(const Camera& cam, const float bg[3], int sh_degree,
 
 void StreamRenderer::finish() { B2C_CUDA_CHECK(cudaStreamSynchronize(copy_stream_)); }
 
-static unsigned char to_u8(float v) { return (unsigned char)std::lround(std::min(std::max(v, 0.f), 1.f) * 255.f); }
-
 int render_headless(const std::string& splat_path, const std::string& cameras_path, const std::string& output_dir, const HeadlessOptions& opt) {
   SplatCloud cloud = read_ply(splat_path);
   if (!cloud.has_scales) throw std::runtime_error("ply '" + splat_path + "' has no scales");
   const CameraList list = read_cameras_json(cameras_path);
   const int W = list.W, H = list.H;
+  const size_t P = (size_t)W * H;
   cudaStream_t stream = 0;
-  Model model; model.upload(cloud, stream);
-  RenderCtx ctx;
-  ctx.want_depth = opt.depth;
-  ctx.n_chunks = opt.render_chunks > 1 ? opt.render_chunks : 1;
-  ctx.setup(W, H, model.cap, stream);
-  const int sh_degree = opt.sh_degree >= 0 ? std::min(opt.sh_degree, model.degree) : model.degree;
-  std::vector<unsigned char> img((size_t)W * H * 4);
-  int count = 0;
-  for (size_t i = (size_t)opt.rank; i < list.cams.size(); i += (size_t)std::max(1, opt.world)) {   // cameras split round-robin over ranks
-    RenderParams p; p.cam = CameraGPU::from(list.cams[i], W, H);
-    for (int k = 0; k < 3; k++) p.bg[k] = opt.background[k];
-    p.sh_degree = sh_degree; p.bwd_info = false;
-    render_forward(ctx, model, p, stream);
-    const std::vector<float4> out = ctx.out_rgba.download((size_t)W * H, stream);
-    for (size_t px = 0; px < (size_t)W * H; px++) {
-      img[px * 4] = to_u8(out[px].x); img[px * 4 + 1] = to_u8(out[px].y); img[px * 4 + 2] = to_u8(out[px].z); img[px * 4 + 3] = to_u8(out[px].w);
-    }
-    std::string name = list.names[i];
+  StreamRenderer renderer(cloud, W, H, opt.depth, opt.render_chunks);
+  // Two host slots: camera k is written to its files while camera k + 1 renders and reads back.
+  PinnedBuf<uint32_t> img[2];
+  PinnedBuf<float> dep[2];
+  for (int k = 0; k < 2; k++) { img[k].reserve(P); if (opt.depth) dep[k].reserve(P); }
+  auto write_out = [&](const std::string& file, int k) {
+    std::string name = file;
     const size_t dot = name.rfind('.');
     if (dot != std::string::npos) name = name.substr(0, dot);
     {
       std::ofstream f(output_dir + "/" + name + ".rgba8", std::ios::binary);
-      f.write((const char*)img.data(), (std::streamsize)img.size());
+      f.write((const char*)img[k].ptr, (std::streamsize)(P * sizeof(uint32_t)));
       if (!f) throw std::runtime_error("failed to write '" + output_dir + "/" + name + ".rgba8'");
     }
     if (opt.depth) {
-      const std::vector<float> d = ctx.out_depth.download((size_t)W * H, stream);
       std::ofstream f(output_dir + "/" + name + ".depth.f32", std::ios::binary);
-      f.write((const char*)d.data(), (std::streamsize)(d.size() * sizeof(float)));
+      f.write((const char*)dep[k].ptr, (std::streamsize)(P * sizeof(float)));
       if (!f) throw std::runtime_error("failed to write '" + output_dir + "/" + name + ".depth.f32'");
     }
+  };
+  int count = 0;
+  std::string pending;
+  for (size_t i = (size_t)opt.rank; i < list.cams.size(); i += (size_t)std::max(1, opt.world)) {   // cameras split round-robin over ranks
+    const int k = count & 1;
+    renderer.render(list.cams[i], opt.background, opt.sh_degree, img[k].ptr, opt.depth ? dep[k].ptr : nullptr, stream);
+    if (count > 0) write_out(pending, k ^ 1);   // the previous camera's copies were waited for below
+    renderer.finish();
+    pending = list.names[i];
     count++;
   }
+  if (count > 0) write_out(pending, (count - 1) & 1);
   return count;
 }
 
