@@ -7,6 +7,49 @@
 #include <cstring>
 
 namespace b2c {
+
+namespace mem {
+
+void* device_block(size_t bytes) {
+  void* p = nullptr;
+  if (bytes) B2C_CUDA_CHECK(cudaMalloc(&p, bytes));
+  return p;
+}
+
+void release_device(void* block) noexcept { if (block) cudaFree(block); }
+
+void* regrown(void* old, size_t old_bytes, size_t new_bytes, bool keep, cudaStream_t stream) {
+  void* fresh = device_block(new_bytes);
+  if (!old) return fresh;
+  try {
+    if (keep && old_bytes) B2C_CUDA_CHECK(cudaMemcpyAsync(fresh, old, std::min(old_bytes, new_bytes), cudaMemcpyDeviceToDevice, stream));
+    B2C_CUDA_CHECK(cudaStreamSynchronize(stream));   // nothing queued on the stream reads the old block any more
+  } catch (...) { release_device(fresh); throw; }
+  release_device(old);
+  return fresh;
+}
+
+void clear(void* block, size_t bytes, cudaStream_t stream) { if (block && bytes) B2C_CUDA_CHECK(cudaMemsetAsync(block, 0, bytes, stream)); }
+
+void to_device(void* dst, const void* host_src, size_t bytes, cudaStream_t stream) {
+  if (bytes) B2C_CUDA_CHECK(cudaMemcpyAsync(dst, host_src, bytes, cudaMemcpyHostToDevice, stream));
+}
+
+void to_host_now(void* host_dst, const void* src, size_t bytes, cudaStream_t stream) {
+  if (!bytes) return;
+  B2C_CUDA_CHECK(cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, stream));
+  B2C_CUDA_CHECK(cudaStreamSynchronize(stream));
+}
+
+void* pinned_block(size_t bytes) {
+  void* p = nullptr;
+  if (bytes) B2C_CUDA_CHECK(cudaMallocHost(&p, bytes));
+  return p;
+}
+
+void release_pinned(void* block) noexcept { if (block) cudaFreeHost(block); }
+
+}  // namespace mem
 namespace abi {
 
 void check(int status, const char* what) {

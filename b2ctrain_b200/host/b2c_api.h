@@ -6,10 +6,12 @@
 // the reference (src/gpu/util.cuh:13-15). Lanes that libb2k does not implement throw "unsupported lane".
 #pragma once
 #include <cuda_runtime.h>
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace b2c {
@@ -26,50 +28,69 @@ namespace b2c {
 constexpr int RT_W = 8;   // rasteriser tile edge
 inline int sh_coeffs_for_degree(int d) { return (d + 1) * (d + 1); }
 
-// Owning, grow-only device buffer (the role of DevBuf in src/gpu/util.cuh:26-57).
+// Byte-level device and pinned-host memory primitives (b2c_api.cpp). Every CUDA failure throws std::runtime_error.
+namespace mem {
+void* device_block(size_t bytes);
+void release_device(void* block) noexcept;
+// A block of new_bytes that starts with the first old_bytes of `old` when keep is set; `old` is released once the copy
+// (and whatever else is queued on the stream and may still read it) has finished.
+void* regrown(void* old, size_t old_bytes, size_t new_bytes, bool keep, cudaStream_t stream);
+void clear(void* block, size_t bytes, cudaStream_t stream);
+void to_device(void* dst, const void* host_src, size_t bytes, cudaStream_t stream);
+void to_host_now(void* host_dst, const void* src, size_t bytes, cudaStream_t stream);   // returns once the bytes have landed
+void* pinned_block(size_t bytes);
+void release_pinned(void* block) noexcept;
+}  // namespace mem
+
+// Owning, grow-only device array: the interface of DevBuf in src/gpu/util.cuh:26-57 (ptr, count, reserve / zero /
+// upload / download, implicit conversion to T*), which the reference's callers use directly, over the primitives above.
 template <typename T>
 struct DevBuf {
   T* ptr = nullptr;
   size_t count = 0;
   DevBuf() = default;
+  ~DevBuf() { free(); }
   DevBuf(const DevBuf&) = delete;
   DevBuf& operator=(const DevBuf&) = delete;
-  DevBuf(DevBuf&& o) noexcept : ptr(o.ptr), count(o.count) { o.ptr = nullptr; o.count = 0; }
-  DevBuf& operator=(DevBuf&& o) noexcept { if (this != &o) { free(); ptr = o.ptr; count = o.count; o.ptr = nullptr; o.count = 0; } return *this; }
-  ~DevBuf() { free(); }
-  void free() { if (ptr) cudaFree(ptr); ptr = nullptr; count = 0; }
+  DevBuf(DevBuf&& other) noexcept { exchange(other); }
+  DevBuf& operator=(DevBuf&& other) noexcept { DevBuf taken(static_cast<DevBuf&&>(other)); exchange(taken); return *this; }
+  void free() noexcept { mem::release_device(ptr); ptr = nullptr; count = 0; }
   void reserve(size_t n, bool keep = false, cudaStream_t stream = 0) {
     if (n <= count) return;
-    T* fresh = nullptr;
-    B2C_CUDA_CHECK(cudaMalloc(&fresh, n * sizeof(T)));
-    if (ptr) {
-      if (keep && count) B2C_CUDA_CHECK(cudaMemcpyAsync(fresh, ptr, count * sizeof(T), cudaMemcpyDeviceToDevice, stream));
-      B2C_CUDA_CHECK(cudaStreamSynchronize(stream));
-      cudaFree(ptr);
-    }
-    ptr = fresh; count = n;
+    ptr = static_cast<T*>(mem::regrown(ptr, count * sizeof(T), n * sizeof(T), keep, stream));
+    count = n;
   }
-  void zero(cudaStream_t stream = 0, size_t n = (size_t)-1) { if (ptr) B2C_CUDA_CHECK(cudaMemsetAsync(ptr, 0, (n == (size_t)-1 ? count : n) * sizeof(T), stream)); }
-  void upload(const T* src, size_t n, cudaStream_t stream = 0) { reserve(n); B2C_CUDA_CHECK(cudaMemcpyAsync(ptr, src, n * sizeof(T), cudaMemcpyHostToDevice, stream)); }
+  void zero(cudaStream_t stream = 0, size_t n = (size_t)-1) { mem::clear(ptr, std::min(n, count) * sizeof(T), stream); }
+  void upload(const T* src, size_t n, cudaStream_t stream = 0) { reserve(n); mem::to_device(ptr, src, n * sizeof(T), stream); }
   void upload(const std::vector<T>& v, cudaStream_t stream = 0) { upload(v.data(), v.size(), stream); }
   std::vector<T> download(size_t n = (size_t)-1, cudaStream_t stream = 0) const {
-    if (n == (size_t)-1) n = count;
-    std::vector<T> v(n);
-    if (n) { B2C_CUDA_CHECK(cudaMemcpyAsync(v.data(), ptr, n * sizeof(T), cudaMemcpyDeviceToHost, stream)); B2C_CUDA_CHECK(cudaStreamSynchronize(stream)); }
-    return v;
+    std::vector<T> out(n == (size_t)-1 ? count : n);
+    mem::to_host_now(out.data(), ptr, out.size() * sizeof(T), stream);
+    return out;
   }
+  size_t bytes() const { return count * sizeof(T); }
   operator T*() const { return ptr; }
+
+ private:
+  void exchange(DevBuf& other) noexcept { std::swap(ptr, other.ptr); std::swap(count, other.count); }
 };
 
-// Pinned host memory for readbacks (src/gpu/util.cuh:59-64).
+// Pinned host array for asynchronous copies in both directions (the role of src/gpu/util.cuh:59-64).
 template <typename T>
 struct PinnedBuf {
-  T* ptr = nullptr; size_t count = 0;
+  T* ptr = nullptr;
+  size_t count = 0;
   PinnedBuf() = default;
+  ~PinnedBuf() { mem::release_pinned(ptr); }
   PinnedBuf(const PinnedBuf&) = delete;
   PinnedBuf& operator=(const PinnedBuf&) = delete;
-  void reserve(size_t n) { if (n <= count) return; if (ptr) cudaFreeHost(ptr); ptr = nullptr; B2C_CUDA_CHECK(cudaMallocHost(&ptr, n * sizeof(T))); count = n; }
-  ~PinnedBuf() { if (ptr) cudaFreeHost(ptr); }
+  void reserve(size_t n) {
+    if (n <= count) return;
+    mem::release_pinned(ptr);
+    ptr = nullptr; count = 0;
+    ptr = static_cast<T*>(mem::pinned_block(n * sizeof(T)));
+    count = n;
+  }
 };
 
 // Host splat cloud in the layout of SplatCloud (src/ply.h:12-22).
