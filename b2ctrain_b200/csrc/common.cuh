@@ -168,58 +168,82 @@ __device__ __forceinline__ void quat_to_mat(float w, float x, float y, float z, 
   R[6] = 2.f * (xz - wy);       R[7] = 2.f * (yz + wx);       R[8] = 1.f - 2.f * (x2 + y2);
 }
 
-__device__ __forceinline__ bool project_one(const float4 po, const float4 q, const float4 ls, const CamDev& cam, Proj& r) {
-  const float* R = cam.R;
-  r.mean_c = make_float3(R[0] * po.x + R[1] * po.y + R[2] * po.z + cam.t[0], R[3] * po.x + R[4] * po.y + R[5] * po.z + cam.t[1],
-                         R[6] * po.x + R[7] * po.y + R[8] * po.z + cam.t[2]);
-  const float3 mc = r.mean_c;
-  if (!(isfinite(mc.x) && isfinite(mc.y) && isfinite(mc.z) && mc.z <= 1e10f)) return false;
-  if (!(mc.z >= 0.01f)) return false;
+// The projection of one splat, in the stages the backward walks in reverse (geometry_backward): camera-space mean,
+// scales with the 3D-filter floor, rotation, the axes of the splat in camera space, the perspective Jacobian with its
+// clamp, the screen covariance with the 0.3 px blur, and its inverse. Returns false where the reference culls
+// (src/gpu/splat_math.cuh:224-293); the expression trees are the reference's so that both make the same decisions.
+__device__ __forceinline__ bool finite3(const float3 v) { return isfinite(v.x) && isfinite(v.y) && isfinite(v.z); }
+
+__device__ __forceinline__ float3 to_camera(const CamDev& cam, const float4 po) {
+  const float* W2C = cam.R;
+  return make_float3(W2C[0] * po.x + W2C[1] * po.y + W2C[2] * po.z + cam.t[0], W2C[3] * po.x + W2C[4] * po.y + W2C[5] * po.z + cam.t[1],
+                     W2C[6] * po.x + W2C[7] * po.y + W2C[8] * po.z + cam.t[2]);
+}
+
+// Squared scales from the log scales, the scales with the floor f folded in, and the opacity compensation of the floor.
+__device__ __forceinline__ void floored_scales(const float4 ls, Proj& r) {
   r.s2_raw = make_float3(expf(2.f * ls.x), expf(2.f * ls.y), expf(2.f * ls.z));
-  const float f2 = ls.w * ls.w;
-  const float3 s2f = make_float3(r.s2_raw.x + f2, r.s2_raw.y + f2, r.s2_raw.z + f2);
-  r.s = make_float3(sqrtf(s2f.x), sqrtf(s2f.y), sqrtf(s2f.z));
-  r.comp_floor = ls.w > 0.f ? sqrtf((r.s2_raw.x * r.s2_raw.y * r.s2_raw.z) / (s2f.x * s2f.y * s2f.z)) : 1.f;
-  if (!(isfinite(r.s.x) && isfinite(r.s.y) && isfinite(r.s.z))) return false;
-  const float qn2 = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
-  if (!(qn2 >= 1e-6f && isfinite(qn2))) return false;
-  if (!isfinite(po.w)) return false;
-  const float inv_qn = 1.f / sqrtf(qn2);
-  quat_to_mat(q.x * inv_qn, q.y * inv_qn, q.z * inv_qn, q.w * inv_qn, r.Rq);
-  float M[9];   // R_view * Rq * diag(s)
+  const float floor_sq = ls.w * ls.w;
+  const float3 widened = make_float3(r.s2_raw.x + floor_sq, r.s2_raw.y + floor_sq, r.s2_raw.z + floor_sq);
+  r.s = make_float3(sqrtf(widened.x), sqrtf(widened.y), sqrtf(widened.z));
+  r.comp_floor = ls.w > 0.f ? sqrtf((r.s2_raw.x * r.s2_raw.y * r.s2_raw.z) / (widened.x * widened.y * widened.z)) : 1.f;
+}
+
+// axes = R_view * R(q) * diag(s), row-major: column j is the splat's j-th semi-axis in camera space.
+__device__ __forceinline__ void camera_axes(const CamDev& cam, const Proj& r, float (&axes)[9]) {
+  const float* W2C = cam.R;
 #pragma unroll
-  for (int i = 0; i < 3; i++) {
-    M[i * 3 + 0] = (R[i * 3] * r.Rq[0] + R[i * 3 + 1] * r.Rq[3] + R[i * 3 + 2] * r.Rq[6]) * r.s.x;
-    M[i * 3 + 1] = (R[i * 3] * r.Rq[1] + R[i * 3 + 1] * r.Rq[4] + R[i * 3 + 2] * r.Rq[7]) * r.s.y;
-    M[i * 3 + 2] = (R[i * 3] * r.Rq[2] + R[i * 3 + 1] * r.Rq[5] + R[i * 3 + 2] * r.Rq[8]) * r.s.z;
+  for (int row = 0; row < 3; row++) {
+    axes[row * 3 + 0] = (W2C[row * 3] * r.Rq[0] + W2C[row * 3 + 1] * r.Rq[3] + W2C[row * 3 + 2] * r.Rq[6]) * r.s.x;
+    axes[row * 3 + 1] = (W2C[row * 3] * r.Rq[1] + W2C[row * 3 + 1] * r.Rq[4] + W2C[row * 3 + 2] * r.Rq[7]) * r.s.y;
+    axes[row * 3 + 2] = (W2C[row * 3] * r.Rq[2] + W2C[row * 3 + 1] * r.Rq[5] + W2C[row * 3 + 2] * r.Rq[8]) * r.s.z;
   }
-  const float inv_z = 1.f / mc.z;
-  const float rx = mc.x * inv_z, ry = mc.y * inv_z;
-  const float cxr = fminf(fmaxf(rx, cam.lim_neg_x), cam.lim_pos_x), cyr = fminf(fmaxf(ry, cam.lim_neg_y), cam.lim_pos_y);
-  r.clamp_x = !(rx <= cam.lim_pos_x && rx >= cam.lim_neg_x);
-  r.clamp_y = !(ry <= cam.lim_pos_y && ry >= cam.lim_neg_y);
-  r.dx = cam.fx * inv_z; r.dy = cam.fy * inv_z;
-  r.J02 = -r.dx * cxr; r.J12 = -r.dy * cyr;
-  float V[6];
+}
+
+__device__ __forceinline__ bool project_one(const float4 po, const float4 q, const float4 ls, const CamDev& cam, Proj& r) {
+  // 1. camera space, near plane
+  r.mean_c = to_camera(cam, po);
+  if (!(finite3(r.mean_c) && r.mean_c.z <= 1e10f)) return false;
+  if (!(r.mean_c.z >= 0.01f)) return false;
+  // 2. scales and rotation
+  floored_scales(ls, r);
+  if (!finite3(r.s)) return false;
+  const float quat_sq = q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+  if (!(quat_sq >= 1e-6f && isfinite(quat_sq))) return false;
+  if (!isfinite(po.w)) return false;
+  const float unit = 1.f / sqrtf(quat_sq);
+  quat_to_mat(q.x * unit, q.y * unit, q.z * unit, q.w * unit, r.Rq);
+  float axes[9];
+  camera_axes(cam, r, axes);
+  // 3. perspective Jacobian [[dx, 0, J02], [0, dy, J12]], the ray clamped to the guard band around the image
+  const float depth_inv = 1.f / r.mean_c.z;
+  const float ray_x = r.mean_c.x * depth_inv, ray_y = r.mean_c.y * depth_inv;
+  const float held_x = fminf(fmaxf(ray_x, cam.lim_neg_x), cam.lim_pos_x), held_y = fminf(fmaxf(ray_y, cam.lim_neg_y), cam.lim_pos_y);
+  r.clamp_x = !(ray_x <= cam.lim_pos_x && ray_x >= cam.lim_neg_x);
+  r.clamp_y = !(ray_y <= cam.lim_pos_y && ray_y >= cam.lim_neg_y);
+  r.dx = cam.fx * depth_inv; r.dy = cam.fy * depth_inv;
+  r.J02 = -r.dx * held_x; r.J12 = -r.dy * held_y;
+  // 4. screen covariance = (J axes)(J axes)^T, kept in range, + 0.3 px of blur
+  float JA[6];
 #pragma unroll
-  for (int j = 0; j < 3; j++) { V[j] = r.dx * M[j] + r.J02 * M[6 + j]; V[3 + j] = r.dy * M[3 + j] + r.J12 * M[6 + j]; }
-  float c00 = V[0] * V[0] + V[1] * V[1] + V[2] * V[2], c01 = V[0] * V[3] + V[1] * V[4] + V[2] * V[5], c11 = V[3] * V[3] + V[4] * V[4] + V[5] * V[5];
-  const float max_abs = fmaxf(fabsf(c00), fmaxf(fabsf(c01), fabsf(c11)));
-  if (max_abs > 1e18f) { const float k = 1e18f / max_abs; c00 *= k; c01 *= k; c11 *= k; }
-  c00 += 0.3f; c11 += 0.3f;   // screen-space blur
+  for (int j = 0; j < 3; j++) { JA[j] = r.dx * axes[j] + r.J02 * axes[6 + j]; JA[3 + j] = r.dy * axes[3 + j] + r.J12 * axes[6 + j]; }
+  float cov_xx = JA[0] * JA[0] + JA[1] * JA[1] + JA[2] * JA[2], cov_xy = JA[0] * JA[3] + JA[1] * JA[4] + JA[2] * JA[5],
+        cov_yy = JA[3] * JA[3] + JA[4] * JA[4] + JA[5] * JA[5];
+  const float largest = fmaxf(fabsf(cov_xx), fmaxf(fabsf(cov_xy), fabsf(cov_yy)));
+  if (largest > 1e18f) { const float shrink = 1e18f / largest; cov_xx *= shrink; cov_xy *= shrink; cov_yy *= shrink; }
+  cov_xx += 0.3f; cov_yy += 0.3f;
+  // 5. opacity, conic, centre, cut-off radius
   r.sig = 1.f / (1.f + expf(-po.w));
   r.opac = r.sig * r.comp_floor;
-  if (!(isfinite(c00) && isfinite(c01) && isfinite(c11))) return false;
-  const float det = c00 * c11 - c01 * c01;
-  if (!(det > 0.f)) return false;
-  const float inv_det = 1.f / det;
-  r.c00 = c11 * inv_det; r.c01 = -c01 * inv_det; r.c11 = c00 * inv_det;
-  r.mx = cam.fx * rx + cam.cx; r.my = cam.fy * ry + cam.cy;
+  if (!(isfinite(cov_xx) && isfinite(cov_xy) && isfinite(cov_yy))) return false;
+  const float cov_det = cov_xx * cov_yy - cov_xy * cov_xy;
+  if (!(cov_det > 0.f)) return false;
+  const float cov_det_inv = 1.f / cov_det;
+  r.c00 = cov_yy * cov_det_inv; r.c01 = -cov_xy * cov_det_inv; r.c11 = cov_xx * cov_det_inv;
+  r.mx = cam.fx * ray_x + cam.cx; r.my = cam.fy * ray_y + cam.cy;
   if (!(r.opac >= ALPHA_CUTOFF)) return false;
   r.power = logf(r.opac * 255.f);
-  const float detc = r.c00 * r.c11 - r.c01 * r.c01;
-  if (!(detc > 0.f)) return false;
-  return true;
+  return r.c00 * r.c11 - r.c01 * r.c01 > 0.f;
 }
 
 #endif  // __CUDACC__

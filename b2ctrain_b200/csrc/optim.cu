@@ -193,16 +193,27 @@ __device__ __forceinline__ void adam4(float4& p, float4& m, float4& v, float4 g,
   adam1(p.x, m.x, v.x, g.x, lr.x, a); adam1(p.y, m.y, v.y, g.y, lr.y, a); adam1(p.z, m.z, v.z, g.z, lr.z, a); adam1(p.w, m.w, v.w, g.w, lr.w, a);
 }
 
-// lowbias32 integer hash and the counter-based uniform / normal draws of the reference's per-step noise
-// (src/gpu/util.cuh:103-116), restated so a seeded run reproduces the same perturbations.
-__device__ __forceinline__ uint32_t hash_u32(uint32_t x) { x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16; return x; }
-__device__ __forceinline__ float hash_uniform(uint32_t a, uint32_t b, uint32_t c) {
-  const uint32_t h = hash_u32(a * 0x9E3779B1U ^ hash_u32(b * 0x85EBCA77U ^ hash_u32(c * 0xC2B2AE3DU)));
-  return (float)(h >> 8) * (1.0f / 16777216.0f);
+// Random draws of the per-step noise. They must be the reference's, value for value, so that a seeded run makes the same
+// perturbations (src/gpu/util.cuh:103-116): the lowbias32 mixer chained over three counters, the top 24 bits as a
+// uniform in [0, 1), and a Box-Muller normal from two such uniforms (the second with the last counter moved on).
+__device__ __forceinline__ uint32_t lowbias32(uint32_t v) {
+  v ^= v >> 16;
+  v *= 0x7feb352dU;
+  v ^= v >> 15;
+  v *= 0x846ca68bU;
+  v ^= v >> 16;
+  return v;
 }
-__device__ __forceinline__ float hash_normal(uint32_t a, uint32_t b, uint32_t c) {
-  const float u1 = fmaxf(hash_uniform(a, b, c), 1e-7f), u2 = hash_uniform(a, b, c + 0x1234567U);
-  return sqrtf(-2.f * __logf(u1)) * __cosf(6.28318530718f * u2);
+__device__ __forceinline__ float unit_draw(uint32_t key, uint32_t item, uint32_t lane) {
+  const uint32_t inner = lowbias32(lane * 0xC2B2AE3DU);
+  const uint32_t middle = lowbias32(item * 0x85EBCA77U ^ inner);
+  const uint32_t bits = lowbias32(key * 0x9E3779B1U ^ middle);
+  return (float)(bits >> 8) * (1.0f / 16777216.0f);
+}
+__device__ __forceinline__ float normal_draw(uint32_t key, uint32_t item, uint32_t lane) {
+  const float radius_u = fmaxf(unit_draw(key, item, lane), 1e-7f);
+  const float angle_u = unit_draw(key, item, lane + 0x1234567U);
+  return sqrtf(-2.f * __logf(radius_u)) * __cosf(6.28318530718f * angle_u);
 }
 
 struct ModelPtrs {
@@ -212,23 +223,23 @@ struct ModelPtrs {
   size_t cap;
 };
 
-// MCMC noise on the means, strongest for near-transparent splats (optim.cu:363-376). ls holds the updated log scales
-// and the 3D-filter floor.
+// MCMC noise on the mean of a splat some view saw: a clamped normal step per axis whose size falls with the 150th power
+// of (1 - effective opacity), so only near-transparent splats wander (src/gpu/optim.cu:363-376). ls holds the updated
+// log scales and the 3D-filter floor, po.w the updated opacity logit.
 __device__ __forceinline__ void add_mcmc_noise(float4& po, const float4& ls, int i, const B2kOptim& op, bool visible) {
-  if (!(op.noise_weight > 0.f) || !visible) return;
-  const float sig = 1.f / (1.f + __expf(-po.w));
-  const float f2 = ls.w * ls.w;
-  const float3 s2 = make_float3(__expf(2.f * ls.x), __expf(2.f * ls.y), __expf(2.f * ls.z));
-  const float comp = ls.w > 0.f ? sqrtf((s2.x * s2.y * s2.z) / ((s2.x + f2) * (s2.y + f2) * (s2.z + f2))) : 1.f;
-  const float o = fminf(fmaxf(sig * comp, 0.f), 1.f);
-  const float w = fminf(fmaxf(powf(1.f - o, 150.f), 0.f), 1.f) * op.noise_weight;
-  if (w > 0.f) {
-    const uint32_t s = op.seed ^ (op.step * 0x9E3779B9u);
-    const float cl = op.noise_clamp;
-    po.x += fminf(fmaxf(hash_normal(s, (uint32_t)i, 0u) * w, -cl), cl);
-    po.y += fminf(fmaxf(hash_normal(s, (uint32_t)i, 1u) * w, -cl), cl);
-    po.z += fminf(fmaxf(hash_normal(s, (uint32_t)i, 2u) * w, -cl), cl);
-  }
+  if (!visible || !(op.noise_weight > 0.f)) return;
+  const float floor_sq = ls.w * ls.w;
+  const float3 var = make_float3(__expf(2.f * ls.x), __expf(2.f * ls.y), __expf(2.f * ls.z));
+  float floor_comp = 1.f;
+  if (ls.w > 0.f) floor_comp = sqrtf((var.x * var.y * var.z) / ((var.x + floor_sq) * (var.y + floor_sq) * (var.z + floor_sq)));
+  const float logistic = 1.f / (1.f + __expf(-po.w));
+  const float opacity = fminf(fmaxf(logistic * floor_comp, 0.f), 1.f);
+  const float size = fminf(fmaxf(powf(1.f - opacity, 150.f), 0.f), 1.f) * op.noise_weight;
+  if (!(size > 0.f)) return;
+  const uint32_t key = op.seed ^ (op.step * 0x9E3779B9u);
+  float* axis = &po.x;
+#pragma unroll
+  for (uint32_t k = 0; k < 3u; k++) axis[k] += fminf(fmaxf(normal_draw(key, (uint32_t)i, k) * size, -op.noise_clamp), op.noise_clamp);
 }
 
 // What the SH lanes of a splat need from its per-splat part of the update.

@@ -147,3 +147,26 @@ def test_stream_renderer_reads_back_quantised_images_and_depth():
             d = depth[i].numpy()
             assert np.array_equal(np.isfinite(d), fin)
             assert (np.abs(d[fin] - ref[fin]) > 2e-4 * np.abs(ref[fin])).mean() <= 1e-3
+
+
+@pytest.mark.gpu
+def test_quantize_rgba8_rounds_like_lround():
+    """b2k_quantize_rgba8 against lround(clamp(x, 0, 1) * 255) with the product formed in fp32, on values that sit on and
+    next to the rounding boundaries, outside [0, 1], and on random ones."""
+    import ctypes as C
+    import torch
+    from b2ctrain_b200 import api
+    rng = np.random.Generator(np.random.PCG64(7))
+    k = np.arange(256, dtype=np.float64)
+    edge = np.concatenate([(k + 0.5) / 255.0, np.nextafter(((k + 0.5) / 255.0).astype(np.float32), np.float32(0)), np.nextafter(((k + 0.5) / 255.0).astype(np.float32), np.float32(2)),
+                           [-1.0, -0.0, 0.0, 1.0, 1.5, 0.49999997 / 255.0]])
+    vals = np.concatenate([edge.astype(np.float32), rng.random(4096 * 4 - edge.size).astype(np.float32)]).reshape(-1, 4)
+    x = torch.from_numpy(vals).cuda()
+    out = torch.zeros(vals.shape[0], dtype=torch.int32, device="cuda:0")
+    st = api.lib().b2k_quantize_rgba8(C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int32(vals.shape[0]), None)
+    assert st == 0
+    torch.cuda.synchronize()
+    p = (np.clip(vals, np.float32(0), np.float32(1)) * np.float32(255)).astype(np.float64)   # the fp32 product, exactly
+    want = np.floor(p + 0.5).astype(np.uint8)
+    got = out.cpu().numpy().view(np.uint8).reshape(-1, 4)
+    assert np.array_equal(got, want)
