@@ -820,7 +820,11 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   B2K_REQUIRE(C >= 2 && C <= MAX_CHUNKS && c->chunk_words && c->last_idx && c->tile_off && c->depth_keys);
   B2K_REQUIRE(!o->bwd_info || c->bwd_scratch);
   if (o->bwd_info && c->bwd_scratch_bytes < b2k_bwd_scratch_bytes(c->W, c->H, C, c->isect_cap)) return B2K_ERR_CAPACITY;
-  if (o->feat_mode != 0) return B2K_ERR_UNSUPPORTED;   // out_feat.xyz carries the colour sums between chunks
+  if (o->feat_mode != 0) {   // out_feat.xyz carries the colour sums between chunks: the feature sums ride in the backward's scratch
+    if (o->bwd_info) return B2K_ERR_UNSUPPORTED;
+    B2K_REQUIRE(o->feat_mode >= 1 && o->feat_mode <= 2 && c->proj3 && c->bwd_scratch && (o->feat_mode != 2 || o->feat_buffer));
+    if (c->bwd_scratch_bytes < sizeof(float4) * (uint64_t)c->W * (uint64_t)c->H) return B2K_ERR_CAPACITY;
+  }
   B2K_REQUIRE(c->tile_ranges && c->num_isect && c->n_tiles == c->tiles_x * c->tiles_y && c->tile_bits >= 1 && c->tile_bits <= 24);
   B2K_REQUIRE(c->out_rgba && c->out_feat && c->keys && c->vals && c->keys_sorted && c->vals_sorted && c->sort_tmp);
   cudaStream_t s = (cudaStream_t)stream;

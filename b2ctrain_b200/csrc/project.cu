@@ -125,7 +125,8 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_lite_kernel(
     int n, size_t cap, const float4* __restrict__ pos_op, const float4* __restrict__ quat, const float4* __restrict__ lscale,
     const float* __restrict__ sh_dc, const float* __restrict__ sh_hi, int active, CamDev cam, int tiles_x, int tiles_y,
     float4* __restrict__ proj0, float4* __restrict__ proj1, float4* __restrict__ proj2, uint32_t* __restrict__ tile_count, uint4* __restrict__ hit_info,
-    uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen) {
+    uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in, float* __restrict__ max_screen, int feat_mode, const float* __restrict__ feat_in,
+    float2* __restrict__ proj3) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float4 po = pos_op[i], q = quat[i], ls = lscale[i];
@@ -155,7 +156,15 @@ __global__ void __launch_bounds__(PROJ_BLOCK) project_lite_kernel(
     // The colour is evaluated here for every splat with a tile box: this kernel reads the planar SH lanes coalesced,
     // while a colour evaluated later, for the emitting splats only and in depth order, costs one 32-byte sector per
     // lane and splat (it measured slower although it shades a tenth of the splats).
-    if (area) proj2[i] = splat_colour<DEG>(i, cap, make_float3(po.x, po.y, po.z), cam.pos, active, sh_dc, sh_hi);
+    if (area) {
+      float4 col = splat_colour<DEG>(i, cap, make_float3(po.x, po.y, po.z), cam.pos, active, sh_dc, sh_hi);
+      if (feat_mode != 0) {
+        const float3 f = splat_feature(feat_mode, i, po, ls, pr.Rq, cam, feat_in);
+        col.w = f.x;
+        proj3[i] = make_float2(f.y, f.z);
+      }
+      proj2[i] = col;
+    }
   } else {
     proj1[i] = make_float4(0.f, 0.f, 0.f, -1.f);   // no record
   }
@@ -249,7 +258,8 @@ int launch_project_lite(const B2kModel* m, const B2kCamera* cam, const B2kRender
   const int active = o->sh_degree < m->degree ? (o->sh_degree < 0 ? 0 : o->sh_degree) : m->degree;
   const CamDev cd = to_camdev(*cam);
 #define L(D) project_lite_kernel<D><<<div_up(m->n, PROJ_BLOCK), PROJ_BLOCK, 0, s>>>(m->n, (size_t)m->cap, pos, quat, lscale, m->sh_dc, m->sh_hi, active, cd, \
-      c->tiles_x, c->tiles_y, (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, (uint4*)c->hit_info, c->depth_keys_sorted, c->order, m->max_screen)
+      c->tiles_x, c->tiles_y, (float4*)c->proj0, (float4*)c->proj1, (float4*)c->proj2, c->tile_count, (uint4*)c->hit_info, c->depth_keys_sorted, c->order, m->max_screen, \
+      o->feat_mode, o->feat_buffer, (float2*)c->proj3)
   switch (m->degree) { case 0: L(0); break; case 1: L(1); break; case 2: L(2); break; case 3: L(3); break; default: L(4); break; }
 #undef L
   return check_launch();

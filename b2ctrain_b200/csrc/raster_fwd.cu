@@ -30,8 +30,10 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
     uint2* __restrict__ tile_ranges, const uint32_t* __restrict__ vals_sorted, const float4* __restrict__ proj0, const float4* __restrict__ proj1,
     const float4* __restrict__ proj2, int W, int H, int tiles_x, int n_tiles, float3 bg, float4* __restrict__ out_rgba, float4* __restrict__ out_feat,
     float* __restrict__ out_depth, uint32_t* __restrict__ last_idx, int chunk, int n_chunks, uint32_t* __restrict__ alive,
-    const float2* __restrict__ proj3, float4* __restrict__ ckpt) {
-  static_assert(!(FEAT && CHUNKED), "the chunked forward keeps its colour sums where the feature lanes go");
+    const float2* __restrict__ proj3, float4* __restrict__ ckpt, float4* __restrict__ feat_acc) {
+  // CHUNKED with FEAT (forward only): between chunks out_feat.xyz carries the colour sums, so the feature sums of a
+  // pixel travel in feat_acc and move into out_feat.xyz when the last chunk, which then visits every pixel, is done.
+  static_assert(!(FEAT && CHUNKED && BWD), "the chunked backward reads the colour sums from out_feat.xyz");
   __shared__ float4 s0[FWD_WARPS][FWD_BATCH], s1[FWD_WARPS][FWD_BATCH], s2[FWD_WARPS][FWD_BATCH];
   __shared__ float2 s3[FEAT ? FWD_WARPS : 1][FEAT ? FWD_BATCH : 1];
   float f0[2] = {0.f, 0.f}, f1[2] = {0.f, 0.f}, f2[2] = {0.f, 0.f};   // composited feature lanes (raster_fwd.cu:52)
@@ -44,7 +46,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
   const float pcx = (float)px0 + 0.5f, pcy = (float)py + 0.5f;
   const uint2 range = tile_ranges[tile];
   const bool first = !CHUNKED || chunk == 0, final = !CHUNKED || chunk == n_chunks - 1;
-  if (CHUNKED && !first && range.y <= range.x && !(final && DEPTH)) return;   // nothing of this chunk lands here: pixels, state and flag stay
+  if (CHUNKED && !first && range.y <= range.x && !(final && (DEPTH || FEAT))) return;   // nothing of this chunk lands here: pixels, state and flag stay
   float T[2] = {1.f, 1.f}, r[2] = {0.f, 0.f}, g[2] = {0.f, 0.f}, b[2] = {0.f, 0.f}, zs[2] = {0.f, 0.f};
   bool done[2] = {!in0, !in1};
   uint32_t last[2] = {range.x, range.x};
@@ -56,6 +58,7 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
         const float4 acc = out_feat[pix];
         r[p] = acc.x; g[p] = acc.y; b[p] = acc.z; T[p] = acc.w;
         if constexpr (DEPTH) zs[p] = out_depth[pix];
+        if constexpr (FEAT) { const float4 fa = feat_acc[pix]; f0[p] = fa.x; f1[p] = fa.y; f2[p] = fa.z; }
         const uint32_t l = last_idx[pix];
         done[p] = (l & DONE_BIT) != 0u;
         last[p] = l & ~DONE_BIT;
@@ -144,7 +147,9 @@ __global__ void __launch_bounds__(FWD_WARPS * 32) raster_fwd_kernel(
       const int pix = py * W + px0 + p;
       out_rgba[pix] = make_float4(r[p] + T[p] * bg.x, g[p] + T[p] * bg.y, b[p] + T[p] * bg.z, 1.f - T[p]);
       if constexpr (CHUNKED) {
-        out_feat[pix] = make_float4(r[p], g[p], b[p], T[p]);
+        if (FEAT && final) out_feat[pix] = make_float4(f0[p], f1[p], f2[p], T[p]);
+        else out_feat[pix] = make_float4(r[p], g[p], b[p], T[p]);
+        if constexpr (FEAT) { if (!final) feat_acc[pix] = make_float4(f0[p], f1[p], f2[p], 0.f); }
         if constexpr (DEPTH) out_depth[pix] = !final ? zs[p] : ((1.f - T[p]) > 0.05f ? zs[p] / (1.f - T[p]) : INFINITY);
         last_idx[pix] = last[p] | (done[p] ? DONE_BIT : 0u);
       } else {
@@ -180,8 +185,10 @@ int launch_raster_fwd(const B2kCtx* c, const B2kRenderOpts* o, int chunk, int n_
   uint2* ranges = (uint2*)c->tile_ranges + (n_chunks > 1 ? (size_t)chunk * c->n_tiles : 0);
 #define L(B, D, C, F) raster_fwd_kernel<B, D, C, F><<<div_up(c->n_tiles, FWD_WARPS), FWD_WARPS * 32, 0, s>>>(ranges, c->vals_sorted, (const float4*)c->proj0, \
     (const float4*)c->proj1, (const float4*)c->proj2, c->W, c->H, c->tiles_x, c->n_tiles, bg, (float4*)c->out_rgba, (float4*)c->out_feat, c->out_depth, c->last_idx, \
-    chunk, n_chunks, alive, (const float2*)c->proj3, o->bwd_info ? bwd_ckpt_ptr(c) : nullptr)
-  if (n_chunks > 1) {
+    chunk, n_chunks, alive, (const float2*)c->proj3, o->bwd_info ? bwd_ckpt_ptr(c) : nullptr, (n_chunks > 1 && o->feat_mode != 0) ? (float4*)c->bwd_scratch : nullptr)
+  if (n_chunks > 1 && o->feat_mode != 0) {   // forward only (checked by the caller): the scratch of the backward carries the feature sums
+    if (c->out_depth) L(false, true, true, true); else L(false, false, true, true);
+  } else if (n_chunks > 1) {
     if (o->bwd_info) { if (c->out_depth) L(true, true, true, false); else L(true, false, true, false); }
     else { if (c->out_depth) L(false, true, true, false); else L(false, false, true, false); }
   } else if (o->feat_mode != 0) {

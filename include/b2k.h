@@ -115,7 +115,8 @@ typedef struct {
   int32_t feat_mode;                /* FeatureMode (render.h:27,33): 0 none, 1 pseudo-normals (shortest-scale axis, camera
                                        facing, camera space; project.cu:63-72), 2 per-splat buffer (project.cu:73-77).
                                        Forward only: the backward of the feature lanes is not implemented. Needs
-                                       ctx->proj3; not available with b2k_render_chunked */
+                                       ctx->proj3; with b2k_render_chunked also ctx->bwd_scratch (16 bytes per pixel) and
+                                       bwd_info = 0 */
   const float* feat_buffer;         /* [n][3] when feat_mode == 2 (render.h:34) */
 } B2kRenderOpts;
 
@@ -188,10 +189,11 @@ int b2k_raster_fwd(const B2kCtx* ctx, const B2kRenderOpts* opts, b2k_stream_t s)
  * b2k_project + b2k_bin_sort + b2k_raster_fwd; what differs is the bookkeeping a caller can see: vals_sorted /
  * keys_sorted hold one sorted window per chunk (without the intersections that were skipped), tile_ranges one range
  * per chunk and tile, last_idx an index into that layout with bit 31 set on pixels that reached the cutoff,
- * out_feat.xyz the colour sums without the background, num_isect[0] the slots used. Needs last_idx and chunk_words;
+ * out_feat.xyz the colour sums without the background (with a feature mode, forward only: the feature lanes, as in the
+ * whole-view path; their running sums travel in ctx->bwd_scratch between chunks), num_isect[0] the slots used. Needs last_idx and chunk_words;
  * tile_off and depth_keys are scratch; tile_count holds each splat's
- * tile-box area (an upper bound of its hits: the ellipse-tile tests and the SH colours are evaluated chunk by chunk,
- * only for splats whose box still holds a live tile). Overflow of the intersection buffers is reported like b2k_bin_sort's. */
+ * tile-box area (an upper bound of its hits: the ellipse-tile tests are made chunk by chunk, only for splats whose box
+ * still holds a live tile). Overflow of the intersection buffers is reported like b2k_bin_sort's. */
 int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const B2kRenderOpts* opts, const B2kCtx* ctx, b2k_stream_t s);
 /* Scratch bytes b2k_project and b2k_bin_sort need in ctx->sort_tmp for a context whose per-splat buffers hold n_cap
  * entries (replaces RenderCtx::cub_tmp, src/gpu/render.h:80). */

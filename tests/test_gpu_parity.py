@@ -500,10 +500,16 @@ def test_forward_feature_lanes_match_oracle(mode):
     tol = TOL_IMAGE_ABS * (1.0 if mode == "Normals" else 100.0)   # buffer values reach +-100
     assert np.max(np.abs(got - want)) <= tol
     assert np.abs(want).max() > 0.5
-    # the chunked renderer says so instead of rendering without the lane
-    ctx2 = api.RenderCtx("cuda:0"); ctx2.setup(W, H, m.cap, n_chunks=3)
-    with pytest.raises(RuntimeError, match="unsupported lane"):
+    # the chunked renderer composites the same lanes (forward only: its backward reads colour sums where they would go)
+    whole_feat, whole_depth_T = ctx.out_feat.clone(), ctx.out_rgba.clone()
+    for chunks in (2, 4):
+        ctx2 = api.RenderCtx("cuda:0"); ctx2.setup(W, H, m.cap, n_chunks=chunks)
+        with pytest.raises(RuntimeError, match="unsupported lane"):
+            api.render_forward(ctx2, m, rp, sync=True)        # bwd_info is still set
+        rp.bwd_info = False
         api.render_forward(ctx2, m, rp, sync=True)
+        assert torch.equal(ctx2.out_feat, whole_feat) and torch.equal(ctx2.out_rgba, whole_depth_T), chunks
+        rp.bwd_info = True
 
 
 def test_model_compact_keeps_flagged_splats_in_order():
