@@ -82,6 +82,7 @@ SIGNATURES = {
     "b2k_raster_fwd": (C.c_int, [_P, _P, _S]),
     "b2k_render_chunked": (C.c_int, [_P, _P, _P, _P, _S]),
     "b2k_sort_tmp_bytes": (C.c_uint64, [C.c_int32, C.c_uint64]),
+    "b2k_sort_passes": (C.c_int32, [C.c_int32]),
     "b2k_loss_photometric": (C.c_int, [_P, _P, _S]),
     "b2k_loss_accumulate": (C.c_int, [_P, _S]),
     "b2k_loss_zero": (C.c_int, [_P, C.c_int32, C.c_int32, _S]),

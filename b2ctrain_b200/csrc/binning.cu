@@ -15,6 +15,7 @@
 //  * Sorting is LSD with 8-bit digits and is stable, so order = ascending (key, original position): exactly the
 //    order the reference's stable sorts define.
 #include "common.cuh"
+#include <algorithm>
 
 namespace b2k {
 namespace {
@@ -24,7 +25,7 @@ constexpr int SORT_ITEMS = 16;
 constexpr int COUNT_TILE = SORT_THREADS * SORT_ITEMS;   // 4096 keys per counting step of a CTA
 constexpr int SORT_TILE = 4096;                         // pairs per scatter tile (a multiple of COUNT_TILE)
 constexpr int SORT_WARPS = SORT_THREADS / 32;
-constexpr int RADIX = 256;
+constexpr int RADIX_MAX = 512;                 // widest digit (9 bits): sizes the histogram scratch
 constexpr int BLOCKS_PER_SM = 2;               // resident scatter CTAs per SM: one wave covers the input
 
 __device__ __forceinline__ uint32_t seg_len(uint32_t n, uint32_t blocks) {
@@ -44,8 +45,10 @@ __device__ __forceinline__ uint32_t load_n(const uint32_t* n_ptr, uint32_t n_max
 
 // Pass kernel 1: digit counts of each block's segment. hist is [RADIX][blocks]. Each lane keeps 16 keys in flight
 // (four 128-bit loads) so that a few hundred resident warps cover the HBM latency-bandwidth product.
+template <int BITS>
 __global__ void __launch_bounds__(SORT_THREADS) radix_count_kernel(const uint32_t* __restrict__ keys_base, const uint32_t* __restrict__ n_ptr, uint32_t n_max,
                                                                    int shift, uint32_t mask, uint32_t* __restrict__ hist, const uint32_t* __restrict__ off_ptr) {
+  constexpr int RADIX = 1 << BITS;
   __shared__ uint32_t s_hist[SORT_WARPS][RADIX];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < SORT_WARPS * RADIX; i += SORT_THREADS) (&s_hist[0][0])[i] = 0;
@@ -114,6 +117,7 @@ constexpr int SCAT_ITEMS = SORT_TILE / SCAT_THREADS;   // 8
 constexpr int SCAT_WARPS = SCAT_THREADS / 32;
 constexpr size_t SCAT_SMEM = 2 * SORT_TILE * sizeof(uint32_t);
 
+template <int BITS>
 __global__ void __launch_bounds__(SCAT_THREADS, SCAT_THREADS <= 512 ? 2 : 1) radix_scatter_kernel(
     const uint32_t* __restrict__ keys_in_base, const uint32_t* __restrict__ vals_in_base, uint32_t* __restrict__ keys_out_base,
     uint32_t* __restrict__ vals_out_base, const uint32_t* __restrict__ n_ptr, uint32_t n_max, int shift, uint32_t mask,
@@ -123,6 +127,8 @@ __global__ void __launch_bounds__(SCAT_THREADS, SCAT_THREADS <= 512 ? 2 : 1) rad
   const uint32_t* __restrict__ vals_in = vals_in_base + off;
   uint32_t* __restrict__ keys_out = keys_out_base + off;
   uint32_t* __restrict__ vals_out = vals_out_base + off;
+  constexpr int RADIX = 1 << BITS;
+  static_assert(RADIX <= SCAT_THREADS, "one thread per digit in the scans below");
   __shared__ uint32_t s_cnt[SCAT_WARPS][RADIX];   // per-warp digit counts, then per-warp offsets inside the digit
   __shared__ uint32_t s_gbase[RADIX];             // running global slot of the digit for this block
   __shared__ uint32_t s_delta[RADIX];             // global slot = s_delta[digit] + local slot (mod 2^32)
@@ -180,7 +186,7 @@ __global__ void __launch_bounds__(SCAT_THREADS, SCAT_THREADS <= 512 ? 2 : 1) rad
       const uint32_t d = (key[j] >> shift) & mask;
       uint32_t peers = full ? 0xffffffffu : __ballot_sync(0xffffffffu, valid);   // lanes holding the same digit: one vote per digit bit
 #pragma unroll                                                                   // (measured 3x cheaper here than match.any)
-      for (int b = 0; b < 8; b++) {
+      for (int b = 0; b < BITS; b++) {
         const bool bit = (d >> b) & 1u;
         const uint32_t vote = __ballot_sync(0xffffffffu, bit);
         peers &= bit ? vote : ~vote;
@@ -406,8 +412,8 @@ int sort_blocks() { int b = sm_count() * BLOCKS_PER_SM; return b > 1024 ? 1024 :
 SortScratch carve(const B2kCtx* c, int blocks) {
   SortScratch s;
   s.hist = sort_tables_ptr(c);
-  s.totals = s.hist + (size_t)RADIX * blocks;
-  s.block_sums = s.totals + RADIX;
+  s.totals = s.hist + (size_t)RADIX_MAX * blocks;
+  s.block_sums = s.totals + RADIX_MAX;
   s.n_word = s.block_sums + 1024;   // block_sums holds up to 1024 entries (the emit grid differs from the sort grid)
   return s;
 }
@@ -417,27 +423,41 @@ struct Marks { cudaEvent_t ev[32]; int n = 0; bool armed = false; };
 thread_local Marks g_marks;
 void mark(cudaStream_t s) { if (g_marks.armed && g_marks.n < 32) cudaEventRecord(g_marks.ev[g_marks.n++], s); }
 
-// LSD radix sort of (key, value) pairs over bits [0, bits). The element count is read from *n_ptr on the device and
-// clamped to n_max. Buffers (k0, v0) hold the input; the result lands in (k0, v0) when the number of passes is even
-// and in (k1, v1) when it is odd.
-int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uint32_t* n_ptr, uint32_t n_max, int bits, const SortScratch& sc,
-               int blocks, cudaStream_t s, const uint32_t* off_ptr = nullptr) {
-  const int passes = (bits + 7) / 8;
+// Digit width of a sort over `bits` key bits: 8, except where 9 saves a whole pass (17 or 18 bits, the tile ids of a 4K
+// image: two passes instead of three).
+int sort_digit_bits(int bits) { return (bits > 16 && bits <= 18) ? 9 : 8; }
+int sort_passes(int bits) { const int d = sort_digit_bits(bits); return (bits + d - 1) / d; }
+
+template <int BITS>
+int radix_pass(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uint32_t* n_ptr, uint32_t n_max, int shift, uint32_t mask, const SortScratch& sc,
+               int blocks, cudaStream_t s, const uint32_t* off_ptr) {
   static bool attr_set[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(radix_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAT_SMEM) != cudaSuccess) return check_launch();
+    if (cudaFuncSetAttribute(radix_scatter_kernel<BITS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SCAT_SMEM) != cudaSuccess) return check_launch();
     attr_set[dev] = true;
   }
+  radix_count_kernel<BITS><<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist, off_ptr);
+  radix_rows_kernel<<<1 << BITS, 1024, 0, s>>>(sc.hist, blocks, sc.totals);
+  mark(s);
+  radix_scatter_kernel<BITS><<<blocks, SCAT_THREADS, SCAT_SMEM, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals, off_ptr);
+  mark(s);
+  return B2K_OK;
+}
+
+// LSD radix sort of (key, value) pairs over bits [0, bits). The element count is read from *n_ptr on the device and
+// clamped to n_max. Buffers (k0, v0) hold the input; the result lands in (k0, v0) when sort_passes(bits) is even and in
+// (k1, v1) when it is odd.
+int radix_sort(uint32_t* k0, uint32_t* v0, uint32_t* k1, uint32_t* v1, const uint32_t* n_ptr, uint32_t n_max, int bits, const SortScratch& sc,
+               int blocks, cudaStream_t s, const uint32_t* off_ptr = nullptr) {
+  const int digit = sort_digit_bits(bits), passes = sort_passes(bits);
   for (int p = 0; p < passes; p++) {
-    const int shift = p * 8;
-    const int pb = bits - shift < 8 ? bits - shift : 8;
+    const int shift = p * digit;
+    const int pb = bits - shift < digit ? bits - shift : digit;
     const uint32_t mask = (1u << pb) - 1u;
-    radix_count_kernel<<<blocks, SORT_THREADS, 0, s>>>(k0, n_ptr, n_max, shift, mask, sc.hist, off_ptr);
-    radix_rows_kernel<<<RADIX, 1024, 0, s>>>(sc.hist, blocks, sc.totals);
-    mark(s);
-    radix_scatter_kernel<<<blocks, SCAT_THREADS, SCAT_SMEM, s>>>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc.hist, sc.totals, off_ptr);
-    mark(s);
+    const int st = digit == 9 ? radix_pass<9>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc, blocks, s, off_ptr)
+                              : radix_pass<8>(k0, v0, k1, v1, n_ptr, n_max, shift, mask, sc, blocks, s, off_ptr);
+    if (st) return st;
     uint32_t* t = k0; k0 = k1; k1 = t;
     t = v0; v0 = v1; v1 = t;
   }
@@ -593,11 +613,20 @@ __global__ void __launch_bounds__(256) chunk_mask_kernel(const uint32_t* __restr
   }
 }
 
+// The hit words (one ballot per 32 tiles) of the e-th listed big box live in a fixed slot of BALLOT_WORDS words, written
+// by the count pass and read back by the emission, which then makes no ellipse tests of its own. Boxes above
+// 32 * BALLOT_WORDS tiles, and entries past the end of the buffer, have no slot (0xFFFFFFFF) and are tested twice.
+constexpr uint32_t BALLOT_WORDS = 16;
+__device__ __forceinline__ uint32_t ballot_slot(uint32_t e, int area, uint32_t cap_words) {
+  return (area <= (int)(32u * BALLOT_WORDS) && (uint64_t)(e + 1u) * BALLOT_WORDS <= (uint64_t)cap_words) ? e * BALLOT_WORDS : 0xFFFFFFFFu;
+}
+
 // Second step for the listed big-box splats, one warp each: lanes sweep the box 32 tiles at a time.
 __global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __restrict__ big_list, const uint32_t* __restrict__ counts,
                                                               const uint32_t* __restrict__ order, const uint4* __restrict__ hit_info,
                                                               const float4* __restrict__ proj0, const float4* __restrict__ proj1, int tiles_x,
-                                                              const uint32_t* __restrict__ alive, uint32_t* __restrict__ fcount) {
+                                                              const uint32_t* __restrict__ alive, uint32_t* __restrict__ fcount,
+                                                              uint32_t* __restrict__ ballots, uint32_t ballot_cap) {
   const int lane = threadIdx.x & 31;
   const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = counts[1];
   for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
@@ -606,12 +635,15 @@ __global__ void __launch_bounds__(256) chunk_count_big_kernel(const uint32_t* __
     const float4 a = proj0[i], b = proj1[i];
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
     const int min_x = (int)(hi.x & 0xFFFFu), min_y = (int)(hi.x >> 16), bw = (int)(hi.y & 0xFFFFu), area = bw * (int)(hi.y >> 16);
+    const uint32_t keep = ballot_slot(e, area, ballot_cap);   // where this box's hit words go for its emission
     uint32_t hits = 0;
     for (int t0 = 0; t0 < area; t0 += 32) {
       const int t = t0 + lane;
       const int tx = min_x + t % bw, ty = min_y + t / bw;
       const bool hit = t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec);
-      hits += __popc(__ballot_sync(0xffffffffu, hit));
+      const uint32_t m = __ballot_sync(0xffffffffu, hit);
+      hits += __popc(m);
+      if (keep != 0xFFFFFFFFu && lane == 0) ballots[keep + (uint32_t)(t0 >> 5)] = m;
     }
     if (lane == 0) fcount[r] = hits;
   }
@@ -723,7 +755,7 @@ __global__ void __launch_bounds__(256) chunk_emit_big_kernel(const uint32_t* __r
                                                              const uint32_t* __restrict__ fcount, const uint32_t* __restrict__ big_start,
                                                              const float4* __restrict__ proj0, const float4* __restrict__ proj1, int tiles_x,
                                                              const uint32_t* __restrict__ alive, uint32_t cap, uint32_t* __restrict__ keys,
-                                                             uint32_t* __restrict__ vals) {
+                                                             uint32_t* __restrict__ vals, const uint32_t* __restrict__ ballots, uint32_t ballot_cap) {
   const int lane = threadIdx.x & 31;
   const uint32_t warps = gridDim.x * (blockDim.x >> 5), count = counts[1];
   for (uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); e < count; e += warps) {
@@ -735,11 +767,14 @@ __global__ void __launch_bounds__(256) chunk_emit_big_kernel(const uint32_t* __r
     const float4 a = proj0[i], b = proj1[i];
     const TileRec rec = make_tile_rec(a.x, a.y, a.z, a.w, b.x, b.w);
     const int min_x = (int)(hi.x & 0xFFFFu), min_y = (int)(hi.x >> 16), bw = (int)(hi.y & 0xFFFFu), area = bw * (int)(hi.y >> 16);
+    const uint32_t kept = ballot_slot(e, area, ballot_cap);   // the count pass left this box's hit words there, unless it had no room
     for (int t0 = 0; t0 < area; t0 += 32) {
       const int t = t0 + lane;
       const int tx = min_x + t % bw, ty = min_y + t / bw;
-      const bool hit = t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec);
-      const uint32_t m = __ballot_sync(0xffffffffu, hit);
+      uint32_t m;
+      if (kept != 0xFFFFFFFFu) m = ballots[kept + (uint32_t)(t0 >> 5)];
+      else m = __ballot_sync(0xffffffffu, t < area && (!alive || alive[ty * tiles_x + tx] != 0u) && tile_hit(tx, ty, rec));
+      const bool hit = (m >> lane) & 1u;
       if (hit) {
         const uint32_t s = at + __popc(m & ((1u << lane) - 1u));
         if (s < cap) { keys[s] = (uint32_t)(ty * tiles_x + tx); vals[s] = i; }
@@ -758,7 +793,7 @@ extern "C" uint64_t b2k_sort_tmp_bytes(int32_t n, uint64_t isect_cap) {
   (void)isect_cap;
   const int blocks = 1024;   // upper bound of sort_blocks()
   const uint64_t n_cap = n > 0 ? (uint64_t)n : 0;
-  return (uint64_t)sizeof(uint32_t) * (BIG_HEADER_WORDS + 3 * n_cap + (uint64_t)RADIX * blocks + RADIX + blocks + 16);
+  return (uint64_t)sizeof(uint32_t) * (BIG_HEADER_WORDS + 3 * n_cap + (uint64_t)RADIX_MAX * blocks + RADIX_MAX + blocks + 16);
 }
 
 extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
@@ -782,7 +817,7 @@ extern "C" int b2k_bin_sort(const B2kCtx* c, int32_t n, b2k_stream_t stream) {
   int st = radix_sort(c->depth_keys_sorted, c->order, c->depth_keys, c->order_in, sc.n_word, (uint32_t)n, 32, sc, blocks, s);
   if (st) return st;
   // 2 + 3. Scan of the counts in depth order and emission, into the pair the tile sort will read first.
-  const int tile_passes = (c->tile_bits + 7) / 8;
+  const int tile_passes = sort_passes(c->tile_bits);
   uint32_t* ek = (tile_passes % 2 == 0) ? c->keys_sorted : c->keys;
   uint32_t* ev = (tile_passes % 2 == 0) ? c->vals_sorted : c->vals;
   uint32_t* ok = (tile_passes % 2 == 0) ? c->keys : c->keys_sorted;
@@ -857,7 +892,7 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   st = radix_sort(c->depth_keys_sorted, c->order, c->depth_keys, c->order_in, sc.n_word, (uint32_t)n, 32, sc, blocks, s);
   if (st) return st;
   chunk_prepare_kernel<<<1, 32, 0, s>>>(c->depth_keys_sorted, n, words);
-  const int tile_passes = (c->tile_bits + 7) / 8;
+  const int tile_passes = sort_passes(c->tile_bits);
   uint32_t* ek = (tile_passes % 2 == 0) ? c->keys_sorted : c->keys;
   uint32_t* ev = (tile_passes % 2 == 0) ? c->vals_sorted : c->vals;
   uint32_t* ok = (tile_passes % 2 == 0) ? c->keys : c->keys_sorted;
@@ -867,6 +902,10 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
   uint32_t* live_list = big_emit_ptr(c);                    // ranks of the chunk's masked-box splats with a live tile in the box
   uint32_t* big_list = big_emit_ptr(c) + (size_t)c->n_cap;  // the same for big-box splats
   uint32_t* list_counts = big_count_ptr(c) + 2;             // entries of the two lists
+  // Hit words of the big boxes (see ballot_slot) go to the spare key buffer of the tile sort, free until the chunk's sort
+  // starts; with an odd number of sort passes that buffer holds the earlier chunks' results, and the emission re-tests.
+  uint32_t* ballots = (tile_passes % 2 == 0) ? ok : nullptr;
+  const uint32_t ballot_cap = ballots ? (uint32_t)std::min<uint64_t>(c->isect_cap, 0xFFFFFFF0ull) : 0u;
   {
     static bool emit_attr[64] = {false};
     int dev = 0;
@@ -889,12 +928,13 @@ extern "C" int b2k_render_chunked(const B2kModel* m, const B2kCamera* cam, const
     chunk_mask_kernel<<<sm_count() * 8, 256, 0, s>>>(live_list, list_counts, c->order, (uint4*)c->hit_info, (const float4*)c->proj0,
                                                      (const float4*)c->proj1, live, c->tiles_x, fcount);
     chunk_count_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info, (const float4*)c->proj0,
-                                                          (const float4*)c->proj1, c->tiles_x, live, fcount);
+                                                          (const float4*)c->proj1, c->tiles_x, live, fcount, ballots, ballot_cap);
     chunk_sums_kernel<<<emit_blocks, EMIT_THREADS, 0, s>>>(words, lo, hi, fcount, sc.block_sums);
     chunk_emit_kernel<<<emit_blocks, EMIT_THREADS, EMIT_SMEM, s>>>(words, ch, lo, hi, c->order, fcount, sc.block_sums, (const uint4*)c->hit_info,
                                                                    c->tiles_x, (uint32_t)c->isect_cap, big_start, ek, ev, c->num_isect);
     chunk_emit_big_kernel<<<sm_count() * 8, 256, 0, s>>>(big_list, list_counts, c->order, (const uint4*)c->hit_info, fcount, big_start,
-                                                         (const float4*)c->proj0, (const float4*)c->proj1, c->tiles_x, live, (uint32_t)c->isect_cap, ek, ev);
+                                                         (const float4*)c->proj0, (const float4*)c->proj1, c->tiles_x, live, (uint32_t)c->isect_cap, ek, ev,
+                                                         ballots, ballot_cap);
     st = check_launch();
     if (st) return st;
     st = radix_sort(ek, ev, ok, ov, words + CW_COUNT + ch, (uint32_t)c->isect_cap, c->tile_bits, sc, blocks, s, words + CW_BASE + ch);
@@ -916,7 +956,7 @@ extern "C" int b2k_bin_sort_profile(const B2kCtx* c, int32_t n, b2k_stream_t str
   mk.armed = false;
   cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
   // Marks: [0] start, then per depth pass (after count+rows, after scatter) x 4, [9] after emit, then per tile pass x P, last after ranges.
-  const int tile_passes = (c->tile_bits + 7) / 8, expect = 1 + 8 + 1 + 2 * tile_passes + 1;
+  const int tile_passes = sort_passes(c->tile_bits), expect = 1 + 8 + 1 + 2 * tile_passes + 1;
   for (int i = 0; i < 10; i++) ms[i] = 0.f;
   if (st == B2K_OK && e == cudaSuccess && mk.n == expect && n > 0) {
     auto dt = [&](int a, int b) { float t = 0.f; cudaEventElapsedTime(&t, mk.ev[a], mk.ev[b]); return t; };
@@ -931,7 +971,9 @@ extern "C" int b2k_bin_sort_profile(const B2kCtx* c, int32_t n, b2k_stream_t str
 
 // The radix sort above for callers outside the binning (the refinement pass): stable, ascending, 32-bit keys, four
 // passes, so the result returns to the pair it started from.
-extern "C" uint64_t b2k_sort_pairs_tmp_bytes(void) { return (uint64_t)sizeof(uint32_t) * ((uint64_t)RADIX * 1024 + RADIX + 1024 + 16); }
+extern "C" int32_t b2k_sort_passes(int32_t bits) { return bits >= 1 && bits <= 32 ? sort_passes(bits) : 0; }
+
+extern "C" uint64_t b2k_sort_pairs_tmp_bytes(void) { return (uint64_t)sizeof(uint32_t) * ((uint64_t)RADIX_MAX * 1024 + RADIX_MAX + 1024 + 16); }
 
 extern "C" int b2k_sort_pairs_u32(uint32_t* keys, uint32_t* vals, uint32_t* keys_alt, uint32_t* vals_alt, uint32_t n, void* tmp, uint64_t tmp_bytes, b2k_stream_t stream) {
   B2K_REQUIRE(n == 0 || (keys && vals && keys_alt && vals_alt && tmp));
@@ -940,7 +982,7 @@ extern "C" int b2k_sort_pairs_u32(uint32_t* keys, uint32_t* vals, uint32_t* keys
   cudaStream_t s = (cudaStream_t)stream;
   const int blocks = sort_blocks();
   SortScratch sc;
-  sc.hist = (uint32_t*)tmp; sc.totals = sc.hist + (size_t)RADIX * blocks; sc.block_sums = sc.totals + RADIX; sc.n_word = sc.block_sums + 1024;
+  sc.hist = (uint32_t*)tmp; sc.totals = sc.hist + (size_t)RADIX_MAX * blocks; sc.block_sums = sc.totals + RADIX_MAX; sc.n_word = sc.block_sums + 1024;
   set_word_kernel<<<1, 1, 0, s>>>(sc.n_word, n);
   return radix_sort(keys, vals, keys_alt, vals_alt, sc.n_word, n, 32, sc, blocks, s);
 }
@@ -960,13 +1002,13 @@ extern "C" int b2k_read_num_isect(const B2kCtx* c, b2k_stream_t stream, uint32_t
 // cannot: a plugin loaded into a process whose memory pool is owned and fully reserved by the host application, a
 // render thread that must never take the allocator's lock, or a caller inside a region where the CUDA allocator is
 // off limits. For them the same scratch lives here, inside the library image, as a fixed device array. It is sized
-// for contexts of at most B2K_STATIC_MAX_SPLATS per-splat entries (about 4.2 MB, held by every GPU that loads the
+// for contexts of at most B2K_STATIC_MAX_SPLATS per-splat entries (about 5.2 MB, held by every GPU that loads the
 // library, until the process exits).
 // ---------------------------------------------------------------------------------------------------------------
 namespace b2k {
 namespace {
 constexpr uint32_t STATIC_MAX_SPLATS = 262144;
-constexpr size_t STATIC_WORDS = BIG_HEADER_WORDS + 3 * (size_t)STATIC_MAX_SPLATS + (size_t)RADIX * 1024 + RADIX + 1024 + 16;
+constexpr size_t STATIC_WORDS = BIG_HEADER_WORDS + 3 * (size_t)STATIC_MAX_SPLATS + (size_t)RADIX_MAX * 1024 + RADIX_MAX + 1024 + 16;
 static __device__ __align__(256) uint32_t g_static_sort_tmp[STATIC_WORDS];
 // Device address of the array above, per device. In host code the array's name is only a handle for the runtime,
 // never a pointer a kernel may be given; the address has to be asked for, once per device, with that device current.

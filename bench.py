@@ -387,7 +387,8 @@ def bench_train(args, cfg, scene, cams, device, rank, world, barrier, max_over_r
     views_per_step = n_views
     value = views_per_step * args.steps / (ms / 1e3)
     e2e_value = views_per_step * args.steps / (ms_e2e / 1e3)
-    passes = (tile_bits + 7) // 8
+    from b2ctrain_b200 import api as _api
+    passes = int(_api.lib().b2k_sort_passes(int(tile_bits)))
     launches_view = 1 + (1 + 12 + 2 + 3 * passes + 1) + 1 + 1 + 1 + 1 + 1
     if args.chunks > 1:   # projection 2, depth sort 13, chunk words 1, per chunk 6 (+1 after the first) + the tile-sort passes, then loss .. projection backward
         launches_view = 2 + 13 + 1 + sum(6 + (2 if ch else 0) + 3 * passes for ch in range(args.chunks)) + 5
@@ -483,7 +484,7 @@ def stage_roofline(args, tr, cams, targets, mine, stats, clocks=None):
     nv = len(views)
     st = stats[0]
     V, I, Is, Ib, n, P, tiles = st["V"], st["I"], st["I_sorted"], st["I_b"], m.n, ctx.W * ctx.H, ctx.n_tiles
-    passes = (ctx.tile_bits + 7) // 8
+    passes = int(api.lib().b2k_sort_passes(int(ctx.tile_bits)))
     alg = {"project": 48 * n + 12 * K * V + 48 * V + 28 * n,
            "bin_sort": 16 * n * 4 + 24 * n + 8 * I + 16 * I * passes + 4 * I + 8 * tiles,
            "raster_fwd": 52 * Ib + 36 * P,
@@ -590,7 +591,8 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
     ms_e2e = timed(args.steps, True)
     hr.close()
     mpix = len(cams) * W * H * args.steps / 1e6
-    passes = (tile_bits + 7) // 8
+    from b2ctrain_b200 import api as _api
+    passes = int(_api.lib().b2k_sort_passes(int(tile_bits)))
     launches_view = 1 + (1 + 12 + 2 + 3 * passes + 1) + 1
     if args.chunks > 1:
         launches_view = 2 + 13 + 1 + sum(6 + (2 if ch else 0) + 3 * passes for ch in range(args.chunks))

@@ -253,6 +253,9 @@ int b2k_adam_range(const B2kModel* m, const B2kOptim* op, float* grad, int32_t f
 /* Stable ascending sort of (key, value) pairs on 32-bit keys (the role of cub::DeviceRadixSort in refine.cu:206-223): the
  * sorted pairs end in (keys, vals); (keys_alt, vals_alt) is scratch of the same size; tmp holds b2k_sort_pairs_tmp_bytes(). */
 uint64_t b2k_sort_pairs_tmp_bytes(void);
+/* Passes the library's LSD radix sort makes over keys of `bits` bits (8-bit digits; 9-bit ones where that saves a pass:
+ * 17 or 18 bits, the tile ids of a 4K image). An even count leaves the result in the buffer pair the sort started from. */
+int32_t b2k_sort_passes(int32_t bits);
 int b2k_sort_pairs_u32(uint32_t* keys, uint32_t* vals, uint32_t* keys_alt, uint32_t* vals_alt, uint32_t n, void* tmp, uint64_t tmp_bytes, b2k_stream_t s);
 /* prune_flags_kernel, refine.cu:54-72: keep / dead / culled flags (non-finite, transparent, oversized or far splats; with
  * cull_weight > 0 also those whose vis_weight is below it). center: 3 host floats. */

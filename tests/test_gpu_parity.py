@@ -69,6 +69,28 @@ def test_binning_bit_exact():
     assert np.array_equal(order, want_order.astype(np.uint32))
 
 
+def test_binning_bit_exact_at_4k_where_the_tile_sort_uses_nine_bit_digits():
+    """A 3840x2160 image has 129,600 tiles, 17 bits of tile id: the tile sort runs two passes of nine-bit digits instead of
+    three of eight. Same contract as above, plus the chunked renderer on the same view."""
+    import torch
+    scene, cam = small_scene(n=1200, W=3840, H=2160)
+    h = Harness(scene, cam)
+    assert h.ctx.tile_bits == 17 and h.api.lib().b2k_sort_passes(17) == 2 and h.api.lib().b2k_sort_passes(15) == 2 and h.api.lib().b2k_sort_passes(32) == 4
+    h.api.project_splats(h.ctx, h.model, h.rp)
+    h.api.bin_and_sort(h.ctx, h.model)
+    p0, p1, _, tc = gpu_records(h)
+    tc_o, vals_o, keys_o, ranges_o = orc.bin_sort(p0, p1, cam["W"], cam["H"])
+    assert np.array_equal(tc, tc_o)
+    assert h.ctx.num_isect == len(vals_o) and len(vals_o) > 200000 and int(keys_o.max()) >= 1 << 16
+    assert np.array_equal(h.u32(h.ctx.vals_sorted, len(vals_o)), vals_o)
+    assert np.array_equal(h.u32(h.ctx.keys_sorted, len(vals_o)), keys_o)
+    assert np.array_equal(h.u32(h.ctx.tile_ranges).reshape(-1, 2), ranges_o)
+    h.api.rasterize_forward(h.ctx, h.rp)
+    chunked = h.api.RenderCtx("cuda:0"); chunked.setup(cam["W"], cam["H"], h.model.cap, n_chunks=3)
+    h.api.render_forward(chunked, h.model, h.rp, sync=True)
+    assert torch.equal(chunked.out_rgba, h.ctx.out_rgba)
+
+
 def test_binning_depth_ties_and_big_splats():
     scene, cam = small_scene(n=3000, degree=0)
     scene["lscale"][:40, :3] = -1.0                       # splats spanning hundreds of tiles
