@@ -113,9 +113,9 @@ static SplatCloud cloud_of(int32_t n, int32_t degree, const float* pos_op, const
 }
 
 extern "C" void* b2ch_renderer_create(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, int32_t W, int32_t H,
-                                      int32_t depth, int32_t render_chunks) {
+                                      int32_t depth, int32_t render_chunks, int32_t lanes, uint64_t isect_cap) {
   StreamRenderer* r = nullptr;
-  const int st = guarded([&] { r = new StreamRenderer(cloud_of(n, degree, pos_op, quat, lscale, sh), W, H, depth != 0, render_chunks); });
+  const int st = guarded([&] { r = new StreamRenderer(cloud_of(n, degree, pos_op, quat, lscale, sh), W, H, depth != 0, render_chunks, lanes, (size_t)isect_cap); });
   return st ? nullptr : r;
 }
 
@@ -132,10 +132,11 @@ extern "C" int b2ch_renderer_render(void* h, const B2kCamera* cam, const float* 
 
 extern "C" int b2ch_renderer_finish(void* h) { return guarded([&] { ((StreamRenderer*)h)->finish(); }); }
 
-extern "C" int b2ch_renderer_info(void* h, uint64_t* out4) {
+extern "C" int b2ch_renderer_info(void* h, uint64_t* out4) {   // five words
   return guarded([&] {
     StreamRenderer& r = *(StreamRenderer*)h;
-    out4[0] = r.ctx.num_isect; out4[1] = r.ctx.isect_cap; out4[2] = r.d2h_bytes; out4[3] = (uint64_t)r.ctx.tile_bits;
+    out4[0] = r.last_num_isect; out4[1] = r.ctx_of(0).isect_cap; out4[2] = r.d2h_bytes; out4[3] = (uint64_t)r.ctx_of(0).tile_bits;
+    out4[4] = (uint64_t)r.redone;
     r.d2h_bytes = 0;
   });
 }

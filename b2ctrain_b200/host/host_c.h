@@ -47,19 +47,24 @@ uint64_t b2ch_trainer_checksum(void* trainer, void* stream);
 
 /* ---- rendering many cameras of one model ---- */
 /* Splats as for b2ch_trainer_create. depth != 0: an expected-depth map is made with every image. render_chunks > 1: the
- * front-to-back chunked renderer. Uses the current device. */
+ * front-to-back chunked renderer. lanes: cameras in flight, each with its own render context and stream (1: one after
+ * the other). isect_cap: starting capacity of the intersection buffers (0: 2^22); they grow on demand. Uses the current
+ * device. */
 void* b2ch_renderer_create(int32_t n, int32_t degree, const float* pos_op, const float* quat, const float* lscale, const float* sh, int32_t W, int32_t H,
-                           int32_t depth, int32_t render_chunks);
+                           int32_t depth, int32_t render_chunks, int32_t lanes, uint64_t isect_cap);
 void b2ch_renderer_destroy(void* renderer);
-/* Renders one camera on `stream`. With host_rgba8 (W * H words) and / or host_depth (W * H floats) the image is
- * quantised on the device (b2k_quantize_rgba8) and it, and the depth map, are copied out on a second stream while the
- * next camera renders; the buffers should be pinned and are valid after b2ch_renderer_finish. background: 3 floats or
+/* Queues one camera behind whatever is on `stream` and returns without waiting for it. With host_rgba8 (W * H words)
+ * and / or host_depth (W * H floats) the image is quantised on the device (b2k_quantize_rgba8) and it, and the depth
+ * map, are copied out on a copy stream while later cameras render; the buffers should be pinned and are valid after
+ * b2ch_renderer_finish (a camera whose intersections did not fit its buffers is rendered again there, or when its lane
+ * comes round again). background: 3 floats or
  * NULL; sh_degree < 0: the model's. */
 int b2ch_renderer_render(void* renderer, const B2kCamera* cam, const float* background, int32_t sh_degree, uint32_t* host_rgba8, float* host_depth,
                          void* stream);
 int b2ch_renderer_finish(void* renderer);
-/* out[0] intersections of the last camera, [1] intersection capacity, [2] device-to-host bytes since the last call, [3] tile bits. */
-int b2ch_renderer_info(void* renderer, uint64_t* out4);
+/* out[0] intersections of the camera checked last, [1] intersection capacity of lane 0, [2] device-to-host bytes since the
+ * last call, [3] tile bits, [4] cameras rendered twice because their intersections had not fit. out holds 5 words. */
+int b2ch_renderer_info(void* renderer, uint64_t* out5);
 
 /* ---- files ---- */
 /* The reference's `render` subcommand without the PNG step (src/render/renderer.cpp:199-368): reads the splat PLY and

@@ -70,52 +70,101 @@ void write_cameras_json(const std::string& path, const CameraList& list) {
   f << "\n]}\n";
 }
 
-StreamRenderer::StreamRenderer(const SplatCloud& cloud, int W_, int H_, bool depth, int render_chunks) : W(W_), H(H_) {
+StreamRenderer::StreamRenderer(const SplatCloud& cloud, int W_, int H_, bool depth, int render_chunks, int lanes, size_t isect_cap) : W(W_), H(H_) {
   model.upload(cloud, 0);
-  ctx.want_depth = depth;
-  ctx.n_chunks = render_chunks > 1 ? render_chunks : 1;
-  ctx.setup(W, H, model.cap, 0);
   B2C_CUDA_CHECK(cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking));
-  for (int k = 0; k < 2; k++) {
-    B2C_CUDA_CHECK(cudaEventCreateWithFlags(&ready_[k], cudaEventDisableTiming));
-    B2C_CUDA_CHECK(cudaEventCreateWithFlags(&free_[k], cudaEventDisableTiming));
+  B2C_CUDA_CHECK(cudaEventCreateWithFlags(&start_, cudaEventDisableTiming));
+  for (int l = 0; l < std::max(1, lanes); l++) {
+    auto lane = std::make_unique<Lane>();
+    lane->ctx = std::make_unique<RenderCtx>();
+    lane->ctx->want_depth = depth;
+    lane->ctx->n_chunks = render_chunks > 1 ? render_chunks : 1;
+    lane->ctx->setup(W, H, model.cap, 0);
+    if (isect_cap) abi::alloc_isect(*lane->ctx, isect_cap);
+    B2C_CUDA_CHECK(cudaStreamCreateWithFlags(&lane->stream, cudaStreamNonBlocking));
+    B2C_CUDA_CHECK(cudaEventCreateWithFlags(&lane->rendered, cudaEventDisableTiming));
+    B2C_CUDA_CHECK(cudaEventCreateWithFlags(&lane->copied, cudaEventDisableTiming));
+    lane->total.reserve(4);
+    lanes_.push_back(std::move(lane));
   }
   B2C_CUDA_CHECK(cudaDeviceSynchronize());
 }
 
 StreamRenderer::~StreamRenderer() {
   cudaDeviceSynchronize();
-  for (int k = 0; k < 2; k++) { if (ready_[k]) cudaEventDestroy(ready_[k]); if (free_[k]) cudaEventDestroy(free_[k]); }
+  for (auto& lane : lanes_) {
+    if (lane->rendered) cudaEventDestroy(lane->rendered);
+    if (lane->copied) cudaEventDestroy(lane->copied);
+    if (lane->stream) cudaStreamDestroy(lane->stream);
+  }
+  if (start_) cudaEventDestroy(start_);
   if (copy_stream_) cudaStreamDestroy(copy_stream_);
 }
 
-void StreamRenderer::render(const Camera& cam, const float bg[3], int sh_degree, uint32_t* host_rgba8, float* host_depth, cudaStream_t stream) {
-  RenderParams p; p.cam = CameraGPU::from(cam, W, H);
-  for (int k = 0; k < 3; k++) p.bg[k] = bg ? bg[k] : 0.f;
-  p.sh_degree = sh_degree >= 0 ? std::min(sh_degree, model.degree) : model.degree; p.bwd_info = false;
-  render_forward(ctx, model, p, stream);
-  if (!host_rgba8 && !host_depth) return;
-  if (host_depth && !ctx.want_depth) throw std::runtime_error("StreamRenderer: depth was not asked for at construction");
-  const size_t P = (size_t)W * H;
-  const int k = slot_; slot_ ^= 1;
-  if (used_[k]) B2C_CUDA_CHECK(cudaStreamWaitEvent(stream, free_[k], 0));   // the copies that read this slot last have run
-  if (host_rgba8) {
-    stage_rgba_[k].reserve(P);
-    abi::check(b2k_quantize_rgba8((const float*)ctx.out_rgba.ptr, stage_rgba_[k].ptr, (int32_t)P, stream), "b2k_quantize_rgba8");
+// Queues the lane's camera: render, intersection total to pinned memory, then (when asked for) quantise / stage and copy out.
+void StreamRenderer::issue(Lane& lane, bool wait_total) {
+  RenderCtx& ctx = *lane.ctx;
+  cudaStream_t s = lane.stream;
+  render_forward_async(ctx, model, lane.params, s);
+  B2C_CUDA_CHECK(cudaMemcpyAsync(lane.total.ptr, ctx.d_num_isect.ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+  if (wait_total) B2C_CUDA_CHECK(cudaStreamSynchronize(s));
+  if (lane.host_rgba8 || lane.host_depth) {
+    const size_t P = (size_t)W * H;
+    if (lane.staged) B2C_CUDA_CHECK(cudaStreamWaitEvent(s, lane.copied, 0));   // the copies that read the staging buffers last have run
+    if (lane.host_rgba8) {
+      lane.stage_rgba.reserve(P);
+      abi::check(b2k_quantize_rgba8((const float*)ctx.out_rgba.ptr, lane.stage_rgba.ptr, (int32_t)P, s), "b2k_quantize_rgba8");
+    }
+    if (lane.host_depth) {
+      lane.stage_depth.reserve(P);
+      B2C_CUDA_CHECK(cudaMemcpyAsync(lane.stage_depth.ptr, ctx.out_depth.ptr, P * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    }
+    B2C_CUDA_CHECK(cudaEventRecord(lane.rendered, s));
+    B2C_CUDA_CHECK(cudaStreamWaitEvent(copy_stream_, lane.rendered, 0));
+    if (lane.host_rgba8) { B2C_CUDA_CHECK(cudaMemcpyAsync(lane.host_rgba8, lane.stage_rgba.ptr, P * sizeof(uint32_t), cudaMemcpyDeviceToHost, copy_stream_)); d2h_bytes += P * 4; }
+    if (lane.host_depth) { B2C_CUDA_CHECK(cudaMemcpyAsync(lane.host_depth, lane.stage_depth.ptr, P * sizeof(float), cudaMemcpyDeviceToHost, copy_stream_)); d2h_bytes += P * 4; }
+    B2C_CUDA_CHECK(cudaEventRecord(lane.copied, copy_stream_));
+    lane.staged = true;
+  } else {
+    B2C_CUDA_CHECK(cudaEventRecord(lane.rendered, s));
   }
-  if (host_depth) {
-    stage_depth_[k].reserve(P);
-    B2C_CUDA_CHECK(cudaMemcpyAsync(stage_depth_[k].ptr, ctx.out_depth.ptr, P * sizeof(float), cudaMemcpyDeviceToDevice, stream));
-  }
-  B2C_CUDA_CHECK(cudaEventRecord(ready_[k], stream));
-  B2C_CUDA_CHECK(cudaStreamWaitEvent(copy_stream_, ready_[k], 0));
-  if (host_rgba8) { B2C_CUDA_CHECK(cudaMemcpyAsync(host_rgba8, stage_rgba_[k].ptr, P * sizeof(uint32_t), cudaMemcpyDeviceToHost, copy_stream_)); d2h_bytes += P * 4; }
-  if (host_depth) { B2C_CUDA_CHECK(cudaMemcpyAsync(host_depth, stage_depth_[k].ptr, P * sizeof(float), cudaMemcpyDeviceToHost, copy_stream_)); d2h_bytes += P * 4; }
-  B2C_CUDA_CHECK(cudaEventRecord(free_[k], copy_stream_));
-  used_[k] = true;
 }
 
-void StreamRenderer::finish() { B2C_CUDA_CHECK(cudaStreamSynchronize(copy_stream_)); }
+// The lane's camera is done; if its intersections did not fit, the buffers grow and it is rendered (and copied) again.
+void StreamRenderer::settle(Lane& lane) {
+  if (!lane.pending) return;
+  B2C_CUDA_CHECK(cudaEventSynchronize(lane.rendered));
+  for (int guard = 0; guard < 8 && grow_intersections(*lane.ctx, lane.total.ptr[0]); guard++) {
+    if (lane.staged) B2C_CUDA_CHECK(cudaEventSynchronize(lane.copied));
+    redone++;
+    issue(lane, true);
+    B2C_CUDA_CHECK(cudaEventSynchronize(lane.rendered));
+  }
+  lane.ctx->num_isect = lane.total.ptr[0];
+  last_num_isect = lane.total.ptr[0];
+  lane.pending = false;
+}
+
+void StreamRenderer::render(const Camera& cam, const float bg[3], int sh_degree, uint32_t* host_rgba8, float* host_depth, cudaStream_t stream) {
+  Lane& lane = *lanes_[next_++ % lanes_.size()];
+  settle(lane);
+  if (host_depth && !lane.ctx->want_depth) throw std::runtime_error("StreamRenderer: depth was not asked for at construction");
+  lane.params = RenderParams();
+  lane.params.cam = CameraGPU::from(cam, W, H);
+  for (int k = 0; k < 3; k++) lane.params.bg[k] = bg ? bg[k] : 0.f;
+  lane.params.sh_degree = sh_degree >= 0 ? std::min(sh_degree, model.degree) : model.degree;
+  lane.params.bwd_info = false;
+  lane.host_rgba8 = host_rgba8; lane.host_depth = host_depth;
+  B2C_CUDA_CHECK(cudaEventRecord(start_, stream));
+  B2C_CUDA_CHECK(cudaStreamWaitEvent(lane.stream, start_, 0));
+  issue(lane, false);
+  lane.pending = true;
+}
+
+void StreamRenderer::finish() {
+  for (auto& lane : lanes_) settle(*lane);
+  B2C_CUDA_CHECK(cudaStreamSynchronize(copy_stream_));
+}
 
 int render_headless(const std::string& splat_path, const std::string& cameras_path, const std::string& output_dir, const HeadlessOptions& opt) {
   SplatCloud cloud = read_ply(splat_path);
@@ -124,7 +173,7 @@ int render_headless(const std::string& splat_path, const std::string& cameras_pa
   const int W = list.W, H = list.H;
   const size_t P = (size_t)W * H;
   cudaStream_t stream = 0;
-  StreamRenderer renderer(cloud, W, H, opt.depth, opt.render_chunks);
+  StreamRenderer renderer(cloud, W, H, opt.depth, opt.render_chunks, 1);
   // Two host slots: camera k is written to its files while camera k + 1 renders and reads back.
   PinnedBuf<uint32_t> img[2];
   PinnedBuf<float> dep[2];

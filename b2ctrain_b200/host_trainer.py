@@ -36,7 +36,7 @@ SIGNATURES = {
     "b2ch_trainer_checksum": (C.c_uint64, [_P, _P]),
     "b2ch_trainer_refine": (C.c_int, [_P, _P, _P, C.c_int32, _P, _P, _P, _P]),
     "b2ch_refine_once": (C.c_int, [C.c_int32, C.c_int32, _P, _P, _P, _P, _P, _P, _P, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P, C.c_int32, _P, _P, _P, _P, _P]),
-    "b2ch_renderer_create": (_P, [C.c_int32, C.c_int32, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "b2ch_renderer_create": (_P, [C.c_int32, C.c_int32, _P, _P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
     "b2ch_renderer_destroy": (None, [_P]),
     "b2ch_renderer_render": (C.c_int, [_P, _P, _P, C.c_int32, _P, _P, _P]),
     "b2ch_renderer_finish": (C.c_int, [_P]),
@@ -207,15 +207,15 @@ def cloud_from_scene(scene):
 
 
 class HostRenderer:
-    """b2c::StreamRenderer: many cameras of one model; the 8-bit image and the depth map of a camera are copied to (pinned)
-    host arrays on a second stream while the next camera renders."""
+    """b2c::StreamRenderer: many cameras of one model, `lanes` of them in flight on separate streams; the 8-bit image and
+    the depth map of a camera are copied to (pinned) host arrays on a copy stream while later cameras render."""
 
-    def __init__(self, scene, W, H, depth=True, render_chunks=1):
+    def __init__(self, scene, W, H, depth=True, render_chunks=1, lanes=1, isect_cap=0):
         f = lambda a: np.ascontiguousarray(a, np.float32)
         self._keep = [f(scene["pos_op"]), f(scene["quat"]), f(scene["lscale"]), f(scene["sh"])]
         p = [a.ctypes.data_as(C.c_void_p) for a in self._keep]
         self.W, self.H = W, H
-        self.h = lib().b2ch_renderer_create(int(scene["n"]), int(scene["degree"]), p[0], p[1], p[2], p[3], int(W), int(H), int(depth), int(render_chunks))
+        self.h = lib().b2ch_renderer_create(int(scene["n"]), int(scene["degree"]), p[0], p[1], p[2], p[3], int(W), int(H), int(depth), int(render_chunks), int(lanes), int(isect_cap))
         if not self.h:
             raise RuntimeError("b2ch_renderer_create: " + lib().b2ch_last_error().decode())
         self.h = C.c_void_p(self.h)
@@ -237,9 +237,9 @@ class HostRenderer:
         _check(lib().b2ch_renderer_finish(self.h), "b2ch_renderer_finish")
 
     def info(self):
-        out = (C.c_uint64 * 4)()
+        out = (C.c_uint64 * 5)()
         _check(lib().b2ch_renderer_info(self.h, out), "b2ch_renderer_info")
-        return dict(num_isect=int(out[0]), isect_cap=int(out[1]), d2h_bytes=int(out[2]), tile_bits=int(out[3]))
+        return dict(num_isect=int(out[0]), isect_cap=int(out[1]), d2h_bytes=int(out[2]), tile_bits=int(out[3]), redone=int(out[4]))
 
 
 def render_headless(splat, cameras, output_dir, background=(0.0, 0.0, 0.0), sh_degree=-1, depth=False, render_chunks=1, rank=0, world=1):

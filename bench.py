@@ -43,6 +43,7 @@ def parse():
                     "peer-memory update")
     ap.add_argument("--chunks", type=int, default=0, help="depth chunks of the front-to-back renderer (1 = bin the whole view first, as the reference "
                     "does; 0 = choose: 4 for scenes of a million splats and more, where most intersections lie behind saturated pixels, else 1)")
+    ap.add_argument("--render-lanes", type=int, default=4, help="render workload: cameras in flight on separate streams")
     ap.add_argument("--stage-views", type=int, default=4, help="views timed stage by stage for the roofline object")
     return ap.parse_args()
 
@@ -557,14 +558,16 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
     from b2ctrain_b200 import host_trainer as ht
     r = Renderer(scene, W, H, device, rank, world, want_depth=True, render_chunks=args.chunks)
     stats = presize(r, cams, mine, None, False)   # counts of the first camera through the Python mirror, outside any timed region
-    tile_bits = r.ctx.tile_bits
+    tile_bits, r_cap = r.ctx.tile_bits, r.ctx.isect_cap
     del r
     torch.cuda.empty_cache()
     # The timed loops run in the C++ host (b2c::StreamRenderer). e2e: every camera's RGBA8 image and depth map land in pinned
     # host memory, copied on a second stream while the next camera renders; the last copy is inside the timed region.
-    hr = ht.HostRenderer(scene, W, H, depth=True, render_chunks=args.chunks)
-    host_rgba = [torch.empty(W * H, dtype=torch.int32).pin_memory() for _ in range(2)]
-    host_depth = [torch.empty(W * H, dtype=torch.float32).pin_memory() for _ in range(2)]
+    lanes = max(1, args.render_lanes)
+    hr = ht.HostRenderer(scene, W, H, depth=True, render_chunks=args.chunks, lanes=lanes, isect_cap=r_cap)
+    slots = lanes + 1
+    host_rgba = [torch.empty(W * H, dtype=torch.int32).pin_memory() for _ in range(slots)]
+    host_depth = [torch.empty(W * H, dtype=torch.float32).pin_memory() for _ in range(slots)]
     stream = torch.cuda.current_stream().cuda_stream
 
     def timed(steps, e2e):
@@ -574,11 +577,10 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
         for _ in range(steps):
             for j, v in enumerate(mine):
                 if e2e:
-                    hr.render(cams[v], stream, host_rgba8=host_rgba[j & 1].data_ptr(), host_depth=host_depth[j & 1].data_ptr())
+                    hr.render(cams[v], stream, host_rgba8=host_rgba[j % slots].data_ptr(), host_depth=host_depth[j % slots].data_ptr())
                 else:
                     hr.render(cams[v], stream)
-        if e2e:
-            hr.finish()
+        hr.finish()   # every camera rendered (and, end to end, read back)
         e1.record()
         barrier()
         return max_over_ranks(e0.elapsed_time(e1))
@@ -597,7 +599,7 @@ def bench_render(args, scene, cams, device, rank, world, barrier, max_over_ranks
     if args.chunks > 1:
         launches_view = 2 + 13 + 1 + sum(6 + (2 if ch else 0) + 3 * passes for ch in range(args.chunks))
     return {"metric": "render Mpix/s", "value": mpix / (ms / 1e3), "unit": "Mpix/s", "ms_per_step": ms / args.steps, "scaling": "strong",
-            "config": {"cameras": len(cams), "render": ("front to back in %d depth chunks, saturated tiles stop emitting" % args.chunks) if args.chunks > 1 else "whole view binned before compositing", "splats": scene["n"], "sh_degree": scene["degree"], "resolution": f"{W}x{H}", "parallelism": f"cameras over {world} GPUs",
+            "config": {"cameras": len(cams), "render": ("front to back in %d depth chunks, saturated tiles stop emitting" % args.chunks) if args.chunks > 1 else "whole view binned before compositing", "splats": scene["n"], "sh_degree": scene["degree"], "resolution": f"{W}x{H}", "parallelism": f"cameras over {world} GPUs", "cameras_in_flight": lanes,
                        "l2_policy": "inputs larger than L2", "scene_counts_view0": stats[0] if stats else None},
             "e2e": {"value": mpix / (ms_e2e / 1e3), "unit": "Mpix/s", "h2d_bytes_per_step": 100 * len(cams), "d2h_bytes_per_step": 8 * W * H * len(mine),
                     "what": "RGBA8 image (quantised on the device) + fp32 depth map of every camera into pinned host memory, copies overlapped with the next render"},

@@ -126,14 +126,16 @@ def test_stream_renderer_reads_back_quantised_images_and_depth():
     ctx = api.RenderCtx("cuda:0"); ctx.want_depth = True
     ctx.setup(W, H, m.cap)
     stream = torch.cuda.current_stream().cuda_stream
-    for chunks in (1, 3):
-        hr = ht.HostRenderer(scene, W, H, depth=True, render_chunks=chunks)
+    for chunks, lanes, cap in ((1, 1, 0), (3, 1, 0), (3, 3, 0), (1, 2, 4096), (3, 2, 4096)):
+        hr = ht.HostRenderer(scene, W, H, depth=True, render_chunks=chunks, lanes=lanes, isect_cap=cap)
         rgba = [torch.zeros(W * H, dtype=torch.int32).pin_memory() for _ in cams]
         depth = [torch.zeros(W * H, dtype=torch.float32).pin_memory() for _ in cams]
         for i, cam in enumerate(cams):
             hr.render(cam, stream, background=(0.2, 0.1, 0.3), host_rgba8=rgba[i].data_ptr(), host_depth=depth[i].data_ptr())
         hr.finish()
-        assert hr.info()["d2h_bytes"] == len(cams) * W * H * 8
+        info = hr.info()
+        assert info["d2h_bytes"] == (len(cams) + info["redone"]) * W * H * 8
+        assert (info["redone"] > 0) == (cap != 0)          # buffers that start too small: those cameras are rendered again
         hr.close()
         for i, cam in enumerate(cams):
             api.render_forward(ctx, m, api.RenderParams(cam, bg=(0.2, 0.1, 0.3), sh_degree=2, bwd_info=False))
