@@ -25,6 +25,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
+def pick_chunks(n_splats):
+    """Depth chunks of the front-to-back renderer by scene size, from measurements on one B200: 500k splats at 1080p 1.40 ms
+    per step with 2 chunks (1.51 whole-view, 1.48 / 1.61 with 3 / 4); 3M splats at 1080p 604 / 623 / 618 views/s with 3 / 4 /
+    5; 6M splats at 4K 2,012 / 2,406 / 2,485 Mpix/s with 3 / 4 / 5."""
+    if n_splats >= 4_000_000:
+        return 5
+    if n_splats >= 1_000_000:
+        return 4
+    return 2 if n_splats >= 250_000 else 1
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -163,7 +174,7 @@ def main():
     if args.chunks <= 0:
         from b2ctrain_b200 import scenes as _scenes
         n_splats = args.splats or _scenes.CONFIG_SPLATS[cfg][0]
-        args.chunks = 4 if n_splats >= 1_000_000 else (2 if n_splats >= 250_000 else 1)   # measured at 500k splats: 1.40 ms per step with 2 chunks, 1.51 whole-view, 1.48 / 1.61 with 3 / 4
+        args.chunks = pick_chunks(n_splats)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -228,7 +239,7 @@ def main():
             torch.cuda.empty_cache()
             n3 = args.render_splats or scenes.CONFIG_SPLATS[3][0]
             cams3 = scenes.config_cameras(3)[:: max(1, 256 // (16 * world))][: 16 * world]
-            rargs = argparse.Namespace(**{**vars(args), "steps": 1, "warmup": 3, "chunks": 4 if n3 >= 1_000_000 else 1})
+            rargs = argparse.Namespace(**{**vars(args), "steps": 1, "warmup": 3, "chunks": pick_chunks(n3)})
             r = bench_render(rargs, scenes.config_scene(3, n=n3), cams3, device, rank, world, barrier, max_over_ranks, ClockSampler(local_rank))
             if rank == 0:
                 r["config"]["workload"] = workload_name(argparse.Namespace(splats=args.render_splats, views=None), 3, n3) + f" [sample: {len(cams3)} of its 256 cameras]"
