@@ -55,7 +55,7 @@ __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
 //                                   rule multiplies by p and by the target, and the sum of the three it does not)
 //   C (2 warps)  rows a-18..a-15  : derivative maps blurred down the column
 //   D (2 warps)  rows a-22..a-19  : blurred along the row, chain rule, L1 term, one component of v_out per pixel
-// Warps C and D also fetch the next four input rows while they work. Against one CTA per 16x16 tile (a 36x36 footprint
+// Every thread also fetches one element of the next four input rows while it works. Against one CTA per 16x16 tile (a 36x36 footprint
 // blurred for 256 outputs, the reference's shape) this spends about a quarter of the warp instructions per pixel:
 // measured 0.41 -> 0.20 ms for a 1920x1080 view.
 constexpr int STRIP_W = 54;                   // output columns of a strip
@@ -109,22 +109,27 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
   }
   __syncthreads();
 
-  // What does not change from step to step: the input elements a C / D thread fetches, and which columns are inside.
-  int st_row[3], st_x[3];
-  bool st_ok[3];
-#pragma unroll
-  for (int k = 0; k < 3; k++) {
-    const int e = tid - 192 + k * 128;
-    st_row[k] = e / STRIP_IN;
-    const int col = e - st_row[k] * STRIP_IN;
-    st_x[k] = x0 - 2 * HALO + col;
-    st_ok[k] = tid >= 192 && e < STRIP_ROWS * STRIP_IN && col < STRIP_W + 4 * HALO && st_x[k] >= 0 && st_x[k] < W;
-  }
+  // Every thread fetches one element of the next four input rows while it does its stage's work (304 elements, 320
+  // threads): which element, and whether its column is inside the image, does not change from step to step.
+  const int st_row = tid / STRIP_IN, st_col = tid - st_row * STRIP_IN, st_x = x0 - 2 * HALO + st_col;
+  const bool st_slot = tid < STRIP_ROWS * STRIP_IN;
+  const bool st_ok = st_slot && st_col < STRIP_W + 4 * HALO && st_x >= 0 && st_x < W;
   float loss_local = 0.f;
   const int steps = 8 + (y1 - y0 + STRIP_ROWS - 1) / STRIP_ROWS;
   for (int it = 0; it < steps; it++) {
     const int a = y0 - 2 * HALO + STRIP_ROWS * it, b = a - 9, cr = b - 9, d = cr - STRIP_ROWS;
     const int buf = it & 1;
+    const bool more = a + STRIP_ROWS <= y1 - 1 + 2 * HALO;   // stage A has rows to blur in the next step
+    float nx = 0.f, ny = 0.f;
+    {
+      const int y = a + STRIP_ROWS + st_row;
+      if (more && st_ok && y >= 0 && y < H) {
+        const size_t q = (size_t)y * W + st_x;
+        const uint32_t gp = gt[q];
+        nx = pred_c[q * 4];
+        ny = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
+      }
+    }
     if (warp < 2) {
       // A: rows a .. a+3, sixteen groups of four statistics columns each.
       if (a <= y1 - 1 + 2 * HALO) {
@@ -200,21 +205,7 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
         }
       }
     } else {
-      // C and D warps first issue the loads of the next four input rows (consumed by A in the next step).
       const int t = tid - 192;   // 0 .. 127
-      float nx[3], ny[3];
-      const bool more = a + STRIP_ROWS <= y1 - 1 + 2 * HALO;
-#pragma unroll
-      for (int k = 0; k < 3; k++) {
-        const int y = a + STRIP_ROWS + st_row[k];
-        nx[k] = 0.f; ny[k] = 0.f;
-        if (more && st_ok[k] && y >= 0 && y < H) {
-          const size_t q = (size_t)y * W + st_x[k];
-          const uint32_t gp = gt[q];
-          nx[k] = pred_c[q * 4];
-          ny[k] = unpack(gp, c) + (1.f - unpack(gp, 3)) * bg_c;
-        }
-      }
       if (warp < 8) {
         // C: rows cr .. cr+3 of the three derivative maps blurred down the column, one column per thread.
         if (cr + STRIP_ROWS - 1 >= y0 && cr < y1) {
@@ -276,14 +267,8 @@ __global__ void __launch_bounds__(STRIP_THREADS, STRIP_CTAS_PER_SM) photometric_
           }
         }
       }
-      if (more) {
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-          const int e = t + k * 128;
-          if (e < STRIP_ROWS * STRIP_IN) { (&s_in[buf ^ 1][0][0][0])[e] = nx[k]; (&s_in[buf ^ 1][1][0][0])[e] = ny[k]; }
-        }
-      }
     }
+    if (more && st_slot) { (&s_in[buf ^ 1][0][0][0])[tid] = nx; (&s_in[buf ^ 1][1][0][0])[tid] = ny; }   // consumed by stage A in the next step
     __syncthreads();
   }
   const float s = warp_sum(loss_local);
