@@ -61,6 +61,11 @@ for t in (1, 2, 3):
     every = [torch.zeros_like(torch.from_numpy(acc)) for _ in range(world)]
     dist.all_gather(every, torch.from_numpy(acc * t))                      # the peers' accumulators, as the kernel reads them
     rows = sum(e.numpy()[sl] for e in every)                               # fixed order of ranks: the same sums everywhere
+    # The kernel fetches a peer's row only when that peer's bitmap (one bit per splat, set by its projection backward when
+    # it adds a row) marks it: rows left out are zero, so the sums are the same bits.
+    marks = [np.packbits(np.any(e.numpy() != 0, axis=1), bitorder="little") for e in every]
+    marked = [np.unpackbits(m, bitorder="little")[: scene["n"]].astype(bool) for m in marks]
+    assert np.array_equal(sum(np.where(b[sl, None], e.numpy()[sl], 0.0) for b, e in zip(marked, every)), rows)
     mine_state = {k: np.ascontiguousarray(v[sl]) for k, v in shard.items()}
     orc.adam(mine_state, rows, np.any(rows != 0, axis=1), dict(t=t, lr_mean=1e-4, sparse=1), 1)
     for k, v in mine_state.items(): shard[k][sl] = v
